@@ -1,0 +1,253 @@
+"""Model description and flat parameter layout.
+
+A decoder is described by a ``ModelSpec`` (convertible from / to a Hugging Face ``config.json``
+for the Llama, Qwen2/2.5/3, OLMo-2 and Mistral families, which share this block structure) and
+its weights live in ONE flat buffer laid out in consumer order with the fused shapes the
+kernels use (``wqkv`` = q|k|v rows, ``w_gate_up`` = gate|up rows).  Hugging Face names are only a
+view used for checkpoint I/O.  Parameters that take no weight decay (norm weights, biases) are
+grouped at the end of the buffer so that the sharded optimizer sees two contiguous regions.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+
+
+@dataclass
+class ModelSpec:
+    vocab_size: int = 128256
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    rope_scaling: dict | None = None
+    max_position_embeddings: int = 131072
+    tie_word_embeddings: bool = False
+    qk_norm: bool = False  # Qwen3 / OLMo-2 style per-head q/k RMSNorm
+    attention_bias: bool = False  # Qwen2 style q/k/v bias
+    model_type: str = "llama"
+    bos_token_id: int | None = None
+    eos_token_id: int | None = None
+    pad_token_id: int | None = None
+
+    # ---- derived
+    @property
+    def q_dim(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def qkv_dim(self) -> int:
+        return self.q_dim + 2 * self.kv_dim
+
+    def num_params(self) -> int:
+        return ParamLayout(self).total
+
+    # ---- HF config.json
+    @classmethod
+    def from_hf_config(cls, cfg: dict) -> "ModelSpec":
+        mt = cfg.get("model_type", "llama")
+        heads = cfg["num_attention_heads"]
+        hd = cfg.get("head_dim") or cfg["hidden_size"] // heads
+        return cls(
+            vocab_size=cfg["vocab_size"],
+            hidden_size=cfg["hidden_size"],
+            intermediate_size=cfg["intermediate_size"],
+            num_layers=cfg["num_hidden_layers"],
+            num_heads=heads,
+            num_kv_heads=cfg.get("num_key_value_heads", heads),
+            head_dim=hd,
+            rms_norm_eps=cfg.get("rms_norm_eps", 1e-5),
+            rope_theta=cfg.get("rope_theta", (cfg.get("rope_parameters") or {}).get("rope_theta", 10000.0)),
+            rope_scaling=cfg.get("rope_scaling"),
+            max_position_embeddings=cfg.get("max_position_embeddings", 8192),
+            tie_word_embeddings=cfg.get("tie_word_embeddings", False),
+            qk_norm=mt in ("qwen3", "olmo2", "olmo3"),
+            attention_bias=cfg.get("attention_bias", mt == "qwen2"),
+            model_type=mt,
+            bos_token_id=cfg.get("bos_token_id"),
+            eos_token_id=cfg.get("eos_token_id") if not isinstance(cfg.get("eos_token_id"), list) else cfg["eos_token_id"][0],
+            pad_token_id=cfg.get("pad_token_id"),
+        )
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelSpec":
+        return cls.from_hf_config(json.loads((Path(path) / "config.json").read_text()))
+
+    def to_hf_config(self) -> dict:
+        arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+                "mistral": "MistralForCausalLM", "olmo2": "Olmo2ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+        cfg = {
+            "architectures": [arch],
+            "model_type": self.model_type,
+            "vocab_size": self.vocab_size,
+            "hidden_size": self.hidden_size,
+            "intermediate_size": self.intermediate_size,
+            "num_hidden_layers": self.num_layers,
+            "num_attention_heads": self.num_heads,
+            "num_key_value_heads": self.num_kv_heads,
+            "head_dim": self.head_dim,
+            "hidden_act": "silu",
+            "rms_norm_eps": self.rms_norm_eps,
+            "rope_theta": self.rope_theta,
+            "rope_scaling": self.rope_scaling,
+            "max_position_embeddings": self.max_position_embeddings,
+            "tie_word_embeddings": self.tie_word_embeddings,
+            "attention_bias": self.attention_bias,
+            "mlp_bias": False,
+            "torch_dtype": "bfloat16",
+            "bos_token_id": self.bos_token_id,
+            "eos_token_id": self.eos_token_id,
+            "pad_token_id": self.pad_token_id,
+            "use_cache": True,
+        }
+        return cfg
+
+    def replace(self, **kw) -> "ModelSpec":
+        return dataclasses.replace(self, **kw)
+
+
+LLAMA31_SCALING = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                   "original_max_position_embeddings": 8192}
+
+PRESETS: dict[str, ModelSpec] = {
+    # the CPU plumbing configuration: 2 layers, d 64, 4 heads, ffn 256, vocab 512, theta 1e4
+    "tiny": ModelSpec(vocab_size=512, hidden_size=64, intermediate_size=256, num_layers=2, num_heads=4,
+                      num_kv_heads=4, head_dim=16, rope_theta=1e4, max_position_embeddings=2048),
+    # tiny but with head_dim 128 so the tcgen05 attention path is exercised
+    "tiny128": ModelSpec(vocab_size=512, hidden_size=256, intermediate_size=512, num_layers=2, num_heads=2,
+                         num_kv_heads=1, head_dim=128, rope_theta=1e4, max_position_embeddings=4096),
+    "llama3.2-1b": ModelSpec(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_layers=16,
+                             num_heads=32, num_kv_heads=8, head_dim=64, rope_scaling=dict(LLAMA31_SCALING, factor=32.0),
+                             tie_word_embeddings=True),
+    "llama3.1-8b": ModelSpec(rope_scaling=dict(LLAMA31_SCALING)),
+    "llama3.1-70b": ModelSpec(hidden_size=8192, intermediate_size=28672, num_layers=80, num_heads=64, num_kv_heads=8,
+                              rope_scaling=dict(LLAMA31_SCALING)),
+    "qwen2.5-7b": ModelSpec(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_layers=28, num_heads=28,
+                            num_kv_heads=4, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, attention_bias=True,
+                            model_type="qwen2", max_position_embeddings=32768),
+    "qwen3-0.6b": ModelSpec(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_layers=28, num_heads=16,
+                            num_kv_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True,
+                            model_type="qwen3", tie_word_embeddings=True, max_position_embeddings=40960),
+    "olmo2-7b": ModelSpec(vocab_size=100352, hidden_size=4096, intermediate_size=11008, num_layers=32, num_heads=32,
+                          num_kv_heads=32, head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2",
+                          max_position_embeddings=4096),
+}
+
+
+def get_spec(name_or_path: str) -> ModelSpec:
+    """Preset name, or a directory holding a Hugging Face ``config.json``."""
+    if name_or_path in PRESETS:
+        return dataclasses.replace(PRESETS[name_or_path])
+    p = Path(name_or_path)
+    if (p / "config.json").exists():
+        return ModelSpec.from_pretrained(name_or_path)
+    raise ValueError(f"unknown model '{name_or_path}': not a preset {sorted(PRESETS)} nor a directory with config.json")
+
+
+@dataclass
+class ParamEntry:
+    name: str
+    offset: int
+    shape: tuple[int, ...]
+    decay: bool
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+
+class ParamLayout:
+    """Offsets of every fused parameter inside the flat buffer.
+
+    Order: embed, then per layer (wqkv, wo, w_gate_up, w_down), then lm_head (absent when tied),
+    then the no-decay region: per layer (attn_norm, mlp_norm[, q_norm, k_norm, bqkv]), final_norm.
+    Every entry starts on a 128-element boundary (256 bytes in bf16) so TMA bases stay aligned.
+    """
+
+    ALIGN = 128
+
+    def __init__(self, spec: ModelSpec, with_lm_head: bool = True):
+        self.spec = spec
+        self.entries: dict[str, ParamEntry] = {}
+        off = 0
+
+        def add(name, shape, decay):
+            nonlocal off
+            e = ParamEntry(name, off, tuple(shape), decay)
+            self.entries[name] = e
+            off = (off + e.numel + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+
+        s = spec
+        add("embed", (s.vocab_size, s.hidden_size), True)
+        for i in range(s.num_layers):
+            add(f"l{i}.wqkv", (s.qkv_dim, s.hidden_size), True)
+            add(f"l{i}.wo", (s.hidden_size, s.q_dim), True)
+            add(f"l{i}.w_gate_up", (2 * s.intermediate_size, s.hidden_size), True)
+            add(f"l{i}.w_down", (s.hidden_size, s.intermediate_size), True)
+        if with_lm_head and not s.tie_word_embeddings:
+            add("lm_head", (s.vocab_size, s.hidden_size), True)
+        self.decay_end = off
+        for i in range(s.num_layers):
+            add(f"l{i}.attn_norm", (s.hidden_size,), False)
+            add(f"l{i}.mlp_norm", (s.hidden_size,), False)
+            if s.qk_norm:
+                add(f"l{i}.q_norm", (s.head_dim,), False)
+                add(f"l{i}.k_norm", (s.head_dim,), False)
+            if s.attention_bias:
+                add(f"l{i}.bqkv", (s.qkv_dim,), False)
+        add("final_norm", (s.hidden_size,), False)
+        self.total = off
+
+    def view(self, flat, name: str):
+        e = self.entries[name]
+        return flat[e.offset : e.offset + e.numel].view(e.shape)
+
+    def views(self, flat) -> dict:
+        return {n: self.view(flat, n) for n in self.entries}
+
+    # ---- Hugging Face tensor names <-> fused entries
+    def hf_names(self, name: str) -> list[tuple[str, int, int]]:
+        """For a fused entry: list of (hf_name, row_start, row_end) slices that make it up."""
+        s = self.spec
+        if name == "embed":
+            return [("model.embed_tokens.weight", 0, s.vocab_size)]
+        if name == "lm_head":
+            return [("lm_head.weight", 0, s.vocab_size)]
+        if name == "final_norm":
+            return [("model.norm.weight", 0, s.hidden_size)]
+        layer, leaf = name.split(".", 1)
+        p = f"model.layers.{int(layer[1:])}."
+        if leaf == "wqkv" or leaf == "bqkv":
+            suf = "weight" if leaf == "wqkv" else "bias"
+            return [(p + f"self_attn.q_proj.{suf}", 0, s.q_dim), (p + f"self_attn.k_proj.{suf}", s.q_dim, s.q_dim + s.kv_dim),
+                    (p + f"self_attn.v_proj.{suf}", s.q_dim + s.kv_dim, s.qkv_dim)]
+        if leaf == "wo":
+            return [(p + "self_attn.o_proj.weight", 0, s.hidden_size)]
+        if leaf == "w_gate_up":
+            return [(p + "mlp.gate_proj.weight", 0, s.intermediate_size),
+                    (p + "mlp.up_proj.weight", s.intermediate_size, 2 * s.intermediate_size)]
+        if leaf == "w_down":
+            return [(p + "mlp.down_proj.weight", 0, s.hidden_size)]
+        if leaf == "attn_norm":
+            return [(p + "input_layernorm.weight", 0, s.hidden_size)]
+        if leaf == "mlp_norm":
+            return [(p + "post_attention_layernorm.weight", 0, s.hidden_size)]
+        if leaf == "q_norm":
+            return [(p + "self_attn.q_norm.weight", 0, s.head_dim)]
+        if leaf == "k_norm":
+            return [(p + "self_attn.k_norm.weight", 0, s.head_dim)]
+        raise KeyError(name)

@@ -1,0 +1,189 @@
+"""Tensor-level wrappers over the sm_100a kernels (no autograd; the model drives fwd and bwd).
+
+Every function launches on the current CUDA stream and returns immediately.  Inputs must be
+contiguous bf16 / fp32 CUDA tensors as documented; shapes are checked here so that a bad
+call fails in Python instead of on the device.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import lib
+from .lib import call, ptr, status_word, stream_ptr
+
+OUT_BF16, OUT_F32, OUT_F32_ACC = 0, 1, 2
+
+
+def _check(t: torch.Tensor, dtype, name: str):
+    if t.dtype != dtype or not t.is_cuda:
+        raise TypeError(f"{name}: expected CUDA {dtype}, got {t.dtype} on {t.device}")
+    if t.data_ptr() % 16:
+        raise ValueError(f"{name}: pointer must be 16-byte aligned")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a_mn: bool = False,
+         b_mn: bool = False, out_mode: int = OUT_BF16, max_ctas: int = 0) -> torch.Tensor:
+    """C[M,N] (op)= A_op[M,K] @ B_op[N,K]^T on the tcgen05 kernel.
+
+    ``a_mn=False``: ``a`` is [M,K]; ``a_mn=True``: ``a`` is [K,M] (used transposed, no copy).
+    ``b_mn=False``: ``b`` is [N,K]; ``b_mn=True``: ``b`` is [K,N].
+    ``out_mode``: bf16 store, fp32 store, or fp32 accumulate into ``out``.
+    Rows may be strided (last dim contiguous, stride multiple of 8 elements).
+    """
+    _check(a, torch.bfloat16, "a")
+    _check(b, torch.bfloat16, "b")
+    if a.stride(-1) != 1 or b.stride(-1) != 1:
+        raise ValueError("gemm operands need a contiguous last dimension")
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"gemm reduction mismatch: {K} vs {Kb}")
+    lda, ldb = a.stride(0), b.stride(0)
+    if lda % 8 or ldb % 8:
+        raise ValueError("gemm row strides must be multiples of 8 elements (TMA 16-byte rule)")
+    odt = torch.bfloat16 if out_mode == OUT_BF16 else torch.float32
+    if out is None:
+        if out_mode == OUT_F32_ACC:
+            raise ValueError("accumulate mode needs an output tensor")
+        out = torch.empty(M, N, dtype=odt, device=a.device)
+    else:
+        _check(out, odt, "out")
+        if tuple(out.shape) != (M, N) or out.stride(-1) != 1:
+            raise ValueError(f"gemm out shape {tuple(out.shape)} != {(M, N)}")
+    ldc = out.stride(0)
+    if ldc % 8 and N >= 8:
+        raise ValueError("gemm output row stride must be a multiple of 8 elements")
+    call("b200_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), out_mode,
+         ptr(status_word(a.device)), stream_ptr(), max_ctas)
+    return out
+
+
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, res: torch.Tensor | None = None):
+    """Returns (y, h, rstd): h = x (+ res) is the residual stream that was normalised."""
+    T, D = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    h = torch.empty_like(x) if res is not None else x
+    call("b200_rmsnorm_fwd", ptr(x), ptr(res), ptr(w), ptr(h), ptr(y), ptr(rstd), T, D, eps, stream_ptr())
+    return y, h, rstd
+
+
+def rmsnorm_bwd(h: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor, dy: torch.Tensor,
+                dres: torch.Tensor | None, dw_out: torch.Tensor | None) -> torch.Tensor:
+    """dx = d/dh RMSNorm (+ dres); ``dw_out`` (fp32 [D]) is accumulated into when given."""
+    T, D = h.shape
+    dx = torch.empty_like(h)
+    ctas = lib.load_ops().b200_rmsnorm_bwd_ctas(T)
+    partial = torch.empty(ctas, D, dtype=torch.float32, device=h.device)
+    call("b200_rmsnorm_bwd", ptr(h), ptr(w), ptr(rstd), ptr(dy), ptr(dres), ptr(dx), ptr(partial), ptr(dw_out), T, D,
+         stream_ptr())
+    return dx
+
+
+def rope_(qkv: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+          backward: bool = False) -> torch.Tensor:
+    """In-place rotary embedding of the q and k heads of fused qkv; ``pos`` int32 [T]."""
+    if pos.dtype != torch.int32:
+        raise TypeError("rope positions must be int32")
+    call("b200_rope", ptr(qkv), ptr(pos), ptr(inv_freq), qkv.shape[0], n_q, n_kv, head_dim, int(backward), stream_ptr())
+    return qkv
+
+
+def swiglu_fwd(gate_up: torch.Tensor) -> torch.Tensor:
+    T, F2 = gate_up.shape
+    act = torch.empty(T, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    call("b200_swiglu_fwd", ptr(gate_up), ptr(act), T, F2 // 2, stream_ptr())
+    return act
+
+
+def swiglu_bwd_(gate_up: torch.Tensor, dact: torch.Tensor) -> torch.Tensor:
+    """Overwrites ``gate_up`` with d(gate|up)."""
+    T, F2 = gate_up.shape
+    call("b200_swiglu_bwd", ptr(gate_up), ptr(dact), ptr(gate_up), T, F2 // 2, stream_ptr())
+    return gate_up
+
+
+def embedding_fwd(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    V, D = table.shape
+    T = ids.numel()
+    out = torch.empty(T, D, dtype=table.dtype, device=table.device)
+    call("b200_embedding_fwd", ptr(table), ptr(ids), ptr(out), T, D, V, stream_ptr())
+    return out
+
+
+def embedding_bwd(grad_table: torch.Tensor, ids: torch.Tensor, dout: torch.Tensor) -> None:
+    V, D = grad_table.shape
+    call("b200_embedding_bwd", ptr(grad_table), ptr(ids), ptr(dout), ids.numel(), D, V, stream_ptr())
+
+
+_sumsq_scratch: dict[int, torch.Tensor] = {}
+
+
+def sumsq(g: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """out[0] (+)= sum(g^2) for an fp32 tensor, deterministic two-stage reduction."""
+    dev = g.device.index
+    sc = _sumsq_scratch.get(dev)
+    if sc is None:
+        sc = torch.empty(lib.load_ops().b200_sumsq_scratch_floats(), dtype=torch.float32, device=g.device)
+        _sumsq_scratch[dev] = sc
+    call("b200_sumsq", ptr(g), g.numel(), ptr(sc), ptr(out), int(accumulate), stream_ptr())
+    return out
+
+
+def adamw(master, m, v, grad, param_bf16, *, lr, beta1, beta2, eps, wd, step, gscale=None, zero_grad=True) -> None:
+    """Partitioned AdamW on fp32 shards; refreshes the bf16 working copy; zeroes the grad shard."""
+    call("b200_adamw", ptr(master), ptr(m), ptr(v), ptr(grad), ptr(param_bf16), master.numel(), ptr(gscale), lr, beta1,
+         beta2, eps, wd, step, int(zero_grad), stream_ptr())
+
+
+def logprob_fwd(logits: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0, want_entropy: bool = False):
+    """(logp, lse, entropy|None) in fp32 from bf16 logits [T, V]; labels int64, <0 ignored."""
+    T, V = logits.shape
+    lp = torch.empty(T, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(T, dtype=torch.float32, device=logits.device)
+    ent = torch.empty(T, dtype=torch.float32, device=logits.device) if want_entropy else None
+    call("b200_logprob_fwd", ptr(logits), ptr(labels), ptr(lp), ptr(lse), ptr(ent), T, V, logits.stride(0), temperature,
+         stream_ptr())
+    return lp, lse, ent
+
+
+def logprob_bwd_(logits: torch.Tensor, labels: torch.Tensor, lse: torch.Tensor, g: torch.Tensor,
+                 temperature: float = 1.0) -> torch.Tensor:
+    """Rewrites ``logits`` in place with dL/dlogits given g = dL/dlogp (fp32 [T])."""
+    T, V = logits.shape
+    call("b200_logprob_bwd", ptr(logits), ptr(labels), ptr(lse), ptr(g), T, V, logits.stride(0), temperature,
+         stream_ptr())
+    return logits
+
+
+def attn_max_tiles(total_tokens: int, num_docs: int) -> int:
+    return (total_tokens + 127) // 128 + num_docs
+
+
+def attn_fwd(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_q: int, n_kv: int, head_dim: int, scale: float):
+    """Varlen causal attention forward.  Returns (out [T, n_q*hd] bf16, lse [n_q, T] fp32)."""
+    T = qkv.shape[0]
+    B = cu_seqlens.numel() - 1
+    out = torch.empty(T, n_q * head_dim, dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty(n_q, T, dtype=torch.float32, device=qkv.device)
+    call("b200_attn_fwd", ptr(qkv), ptr(cu_seqlens), ptr(out), ptr(lse), ptr(status_word(qkv.device)), T, B, n_q, n_kv,
+         head_dim, attn_max_tiles(T, B), scale, stream_ptr())
+    return out, lse
+
+
+def attn_bwd(qkv, out, d_out, lse, cu_seqlens, n_q: int, n_kv: int, head_dim: int, scale: float) -> torch.Tensor:
+    """Returns dqkv [T, (n_q + 2 n_kv) * hd] bf16 (gradient w.r.t. the post-RoPE fused qkv)."""
+    T = qkv.shape[0]
+    B = cu_seqlens.numel() - 1
+    dqkv = torch.empty_like(qkv)
+    scratch = torch.empty(n_q * T + T * n_q * head_dim, dtype=torch.float32, device=qkv.device)
+    call("b200_attn_bwd", ptr(qkv), ptr(out), ptr(d_out), ptr(lse), ptr(cu_seqlens), ptr(dqkv), ptr(scratch),
+         ptr(status_word(qkv.device)), T, B, n_q, n_kv, head_dim, attn_max_tiles(T, B), scale, stream_ptr())
+    return dqkv

@@ -1,0 +1,140 @@
+"""ctypes binding to ``libb200ops.so`` (the sm_100a kernels) and ``libb200host.so``.
+
+The kernels export a plain C ABI taking raw device pointers and a CUDA stream, so the same
+library serves PyTorch tensors here and any other caller.  On a machine with a GPU the
+library MUST load: there is no silent PyTorch fallback for the fused path; a missing library
+raises.  On a CPU-only machine ``available()`` is False and the ``ref`` ops are used.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_OPS_PATH = _HERE / "libb200ops.so"
+_HOST_PATH = _HERE / "libb200host.so"
+_lock = threading.Lock()
+_ops = None
+_host = None
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+# name -> argtypes; every function returns int (0 = ok, else CUDA / driver error code)
+_SIGNATURES = {
+    "b200_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, I],
+    "b200_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "b200_rmsnorm_bwd_ctas": [I],
+    "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, P],
+    "b200_rope": [P, P, P, I, I, I, I, I, P],
+    "b200_swiglu_fwd": [P, P, L, I, P],
+    "b200_swiglu_bwd": [P, P, P, L, I, P],
+    "b200_embedding_fwd": [P, P, P, I, I, I, P],
+    "b200_embedding_bwd": [P, P, P, I, I, I, P],
+    "b200_sumsq_scratch_floats": [],
+    "b200_sumsq": [P, L, P, P, I, P],
+    "b200_adamw": [P, P, P, P, P, L, P, F, F, F, F, F, I, I, P],
+    "b200_cast_f32_bf16": [P, P, L, F, P],
+    "b200_accum_bf16_f32": [P, P, L, P],
+    "b200_logprob_fwd": [P, P, P, P, P, I, I, L, F, P],
+    "b200_logprob_bwd": [P, P, P, P, I, I, L, F, P],
+    "b200_attn_fwd": [P, P, P, P, P, I, I, I, I, I, I, F, P],
+    "b200_attn_bwd": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P],
+}
+
+
+class KernelError(RuntimeError):
+    """A kernel launch failed or one of its bounded waits ran out."""
+
+
+def ops_library_path() -> Path:
+    return _OPS_PATH
+
+
+def load_ops():
+    """Load (building first if the shared object is missing and nvcc exists)."""
+    global _ops
+    with _lock:
+        if _ops is not None:
+            return _ops
+        if not _OPS_PATH.exists():
+            from . import build
+
+            build.build_ops(verbose=False)
+        lib = ctypes.CDLL(str(_OPS_PATH))
+        for name, argtypes in _SIGNATURES.items():
+            if hasattr(lib, name):
+                fn = getattr(lib, name)
+                fn.argtypes = argtypes
+                fn.restype = c_int
+        _ops = lib
+        return lib
+
+
+def load_host():
+    global _host
+    with _lock:
+        if _host is not None:
+            return _host
+        if not _HOST_PATH.exists():
+            from . import build
+
+            build.build_host(verbose=False)
+        _host = ctypes.CDLL(str(_HOST_PATH))
+        return _host
+
+
+def available() -> bool:
+    """True when the fused sm_100a path can run in this process."""
+    if not torch.cuda.is_available():
+        return False
+    major, _ = torch.cuda.get_device_capability()
+    if major != 10:
+        return False
+    load_ops()  # raises when the library is missing on a GPU machine: fail loudly
+    return True
+
+
+def ptr(t):
+    """Device pointer of a tensor (``None`` -> NULL)."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_status = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 status word the tcgen05 kernels write when a bounded wait runs out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[key] = t
+    return t
+
+
+def check_status(sync: bool = True) -> None:
+    """Raise ``KernelError`` when any kernel recorded a timed-out wait (synchronises the device)."""
+    for key, t in _status.items():
+        code = int(t.item()) if sync else 0
+        if code:
+            t.zero_()
+            raise KernelError(f"kernel on cuda:{key} gave up a bounded wait (status {code})")
+
+
+def call(name: str, *args) -> None:
+    lib = load_ops()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")

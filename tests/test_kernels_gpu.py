@@ -1,0 +1,197 @@
+"""Numerics of every sm_100a kernel against the plain-PyTorch fp32 statement of the same op."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    from open_instruct_b200.ops import lib
+
+    yield
+    lib.check_status()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (384, 320, 192), (1000, 136, 72), (4096, 1024, 4096)])
+def test_gemm_layouts(a_mn, b_mn, shape):
+    from open_instruct_b200.ops import fused
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    ref = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    out = fused.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    assert _rel(out, ref) < 5e-3
+    out32 = fused.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32)
+    assert _rel(out32, ref) < 1e-4
+    acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    fused.gemm(a_in, b_in, acc, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32_ACC)
+    assert _rel(acc, ref + 1) < 1e-4
+
+
+def test_gemm_strided_views():
+    from open_instruct_b200.ops import fused
+
+    x = torch.randn(512, 1024, device="cuda").bfloat16()
+    w = torch.randn(256, 512, device="cuda").bfloat16()
+    a = x[:, 256:768]  # row stride 1024
+    out = fused.gemm(a, w)
+    assert _rel(out, a.float() @ w.float().t()) < 5e-3
+
+
+@pytest.mark.parametrize("T,D", [(7, 64), (300, 4096), (1024, 8192)])
+def test_rmsnorm(T, D):
+    from open_instruct_b200.ops import fused, ref
+
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    r = torch.randn(T, D, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    y, h, rstd = fused.rmsnorm_fwd(x, w, 1e-5, res=r)
+    h_ref = (x + r)
+    assert torch.equal(h, h_ref)
+    y_ref = ref.rmsnorm(h_ref, w, 1e-5)
+    assert _rel(y, y_ref) < 4e-3
+    y2, h2, _ = fused.rmsnorm_fwd(x, w, 1e-5)
+    assert h2 is x and _rel(y2, ref.rmsnorm(x, w, 1e-5)) < 4e-3
+    # backward against autograd on the fp32 statement
+    hf = h_ref.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    yf = wf * (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5))
+    dy = torch.randn(T, D, device="cuda").bfloat16()
+    dres = torch.randn(T, D, device="cuda").bfloat16()
+    yf.backward(dy.float())
+    dw = torch.zeros(D, device="cuda")
+    dx = fused.rmsnorm_bwd(h, w, rstd, dy, dres, dw)
+    assert _rel(dx, hf.grad + dres.float()) < 6e-3
+    assert _rel(dw, wf.grad) < 5e-3
+
+
+def test_rope_roundtrip_and_ref():
+    from open_instruct_b200.ops import fused, ref
+
+    T, Hq, Hkv, Dh = 333, 8, 2, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * Dh, device="cuda").bfloat16()
+    pos = torch.randint(0, 4096, (T,), device="cuda", dtype=torch.int32)
+    inv = ref.rope_inv_freq(Dh, 5e5, device="cuda")
+    expect = ref.rope(qkv, pos, inv, Hq, Hkv, Dh)
+    got = fused.rope_(qkv.clone(), pos, inv, Hq, Hkv, Dh)
+    assert _rel(got, expect) < 4e-3
+    back = fused.rope_(got.clone(), pos, inv, Hq, Hkv, Dh, backward=True)
+    assert _rel(back, qkv) < 8e-3
+    assert torch.equal(got[:, (Hq + Hkv) * Dh:], qkv[:, (Hq + Hkv) * Dh:])
+
+
+def test_swiglu():
+    from open_instruct_b200.ops import fused, ref
+
+    T, Fd = 257, 1024
+    gu = torch.randn(T, 2 * Fd, device="cuda").bfloat16()
+    act = fused.swiglu_fwd(gu)
+    assert _rel(act, ref.swiglu(gu.float())) < 4e-3
+    guf = gu.float().requires_grad_(True)
+    d = torch.randn(T, Fd, device="cuda").bfloat16()
+    ref.swiglu(guf).backward(d.float())
+    dgu = fused.swiglu_bwd_(gu.clone(), d)
+    assert _rel(dgu, guf.grad) < 5e-3
+
+
+def test_embedding():
+    from open_instruct_b200.ops import fused
+
+    V, D, T = 1000, 256, 777
+    table = torch.randn(V, D, device="cuda").bfloat16()
+    ids = torch.randint(0, V, (T,), device="cuda")
+    out = fused.embedding_fwd(table, ids)
+    assert torch.equal(out, table[ids])
+    dout = torch.randn(T, D, device="cuda").bfloat16()
+    g = torch.zeros(V, D, device="cuda")
+    fused.embedding_bwd(g, ids, dout)
+    expect = torch.zeros(V, D, device="cuda").index_add_(0, ids, dout.float())
+    assert _rel(g, expect) < 1e-5
+
+
+def test_sumsq_and_adamw():
+    from open_instruct_b200.ops import fused, ref
+
+    n = 1_000_003
+    g = torch.randn(n, device="cuda")
+    out = torch.zeros(1, device="cuda")
+    fused.sumsq(g, out)
+    assert abs(out.item() - g.double().pow(2).sum().item()) / n < 1e-4
+    fused.sumsq(g, out, accumulate=True)
+    assert abs(out.item() - 2 * g.double().pow(2).sum().item()) / n < 2e-4
+    master = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    rm, rmm, rv = master.clone(), m.clone(), v.clone()
+    gs = torch.tensor([0.5], device="cuda")
+    for step in (1, 2, 3):
+        grad = torch.randn(n, device="cuda")
+        ref.adamw_step(rm, rmm, rv, grad, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, gscale=0.5)
+        fused.adamw(master, m, v, grad, p16, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.01, step=step, gscale=gs)
+        assert float(grad.abs().max()) == 0.0
+    assert _rel(master, rm) < 1e-5 and _rel(m, rmm) < 1e-5 and _rel(v, rv) < 1e-4
+    assert torch.equal(p16, master.bfloat16())
+
+
+@pytest.mark.parametrize("T,V,temp", [(64, 512, 1.0), (300, 128256, 1.0), (37, 32003, 0.7)])
+def test_logprob(T, V, temp):
+    from open_instruct_b200.ops import fused, ref
+
+    Vp = (V + 7) // 8 * 8
+    buf = (3 * torch.randn(T, Vp, device="cuda")).bfloat16()
+    logits = buf[:, :V]
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::5] = -100
+    lp, lse, ent = fused.logprob_fwd(logits, labels, temp, want_entropy=True)
+    rlp, rent = ref.token_logprobs(logits, labels, temp, with_entropy=True)
+    assert (lp - rlp).abs().max().item() < 2e-3
+    assert (ent - rent).abs().max().item() < 2e-3
+    lf = logits.float().requires_grad_(True)
+    g = torch.randn(T, device="cuda")
+    (ref.token_logprobs(lf, labels, temp)[0] * g).sum().backward()
+    d = fused.logprob_bwd_(logits.clone() if V == Vp else buf.clone()[:, :V], labels, lse, g, temp)
+    assert _rel(d, lf.grad) < 1e-2
+
+
+def _attn_case(lens, Hq, Hkv):
+    from open_instruct_b200.ops import fused, ref
+
+    Dh = 128
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * Dh, device="cuda").bfloat16()
+    scale = Dh ** -0.5
+    out, lse = fused.attn_fwd(qkv, cu, Hq, Hkv, Dh, scale)
+    qf = qkv.float().requires_grad_(True)
+    ref_out = ref.attention_varlen(qf, cu, Hq, Hkv, Dh, scale)
+    assert _rel(out, ref_out) < 1e-2, "forward"
+    d_out = torch.randn(T, Hq * Dh, device="cuda").bfloat16()
+    ref_out.backward(d_out.float())
+    dqkv = fused.attn_bwd(qkv, out, d_out, lse, cu, Hq, Hkv, Dh, scale)
+    w = Hq * Dh
+    assert _rel(dqkv[:, :w], qf.grad[:, :w]) < 2e-2, "dq"
+    assert _rel(dqkv[:, w:w + Hkv * Dh], qf.grad[:, w:w + Hkv * Dh]) < 2e-2, "dk"
+    assert _rel(dqkv[:, w + Hkv * Dh:], qf.grad[:, w + Hkv * Dh:]) < 2e-2, "dv"
+
+
+@pytest.mark.parametrize("lens", [[128], [256], [100], [1, 130, 255, 384], [513, 77]])
+def test_attention_varlen(lens):
+    _attn_case(lens, 4, 2)
+
+
+def test_attention_gqa_llama_heads():
+    _attn_case([700, 324], 32, 8)
