@@ -1,0 +1,366 @@
+"""Decoder-only transformer (Llama / Qwen / Mistral block structure) over a flat parameter buffer.
+
+Two execution paths share the same weights:
+
+* ``ops="fused"`` - the B200 path.  Forward and backward are driven explicitly, layer by layer,
+  through the sm_100a kernels in ``open_instruct_b200.ops.fused``: tcgen05 GEMMs for the
+  projections (weight gradients are accumulated in fp32 straight from the GEMM epilogue into
+  the flat ``main_grad`` buffer), varlen packed attention, fused residual-add RMSNorm, in-place
+  RoPE, SwiGLU and the in-place log-prob gradient.  Cheap ops (RMSNorm output, SwiGLU
+  activation) are recomputed in the backward instead of stored.
+* ``ops="ref"`` - plain PyTorch autograd over the same buffer; runs on CPU (fp32) and is the
+  oracle the fused path is tested against, and the compute path of the library baseline.
+
+The public entry points return per-token log-probabilities (or final hidden states) that are
+differentiable with respect to the flat parameter buffer on both paths, so SFT, DPO, GRPO and
+reward-model losses are written once in PyTorch on ``[T]``-sized tensors.
+
+Packed input convention (same as the reference's padding-free collator,
+``open_instruct/padding_free_collator.py:67-120``): ``input_ids`` and ``position_ids`` are 1-D over
+all tokens of the micro-batch, ``cu_seqlens`` int32 ``[num_docs + 1]`` gives document boundaries.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import ref
+from .spec import ModelSpec, ParamLayout
+
+
+def _fused():
+    from ..ops import fused
+
+    return fused
+
+
+@dataclass
+class _LayerStash:
+    h_in: torch.Tensor  # residual stream entering the layer
+    rstd1: torch.Tensor
+    qkv: torch.Tensor  # post-RoPE
+    attn: torch.Tensor
+    lse: torch.Tensor
+    h_mid: torch.Tensor  # residual stream after attention
+    rstd2: torch.Tensor
+    gate_up: torch.Tensor
+
+
+class LlamaModel:
+    """Weights + forward/backward engine.  Not an ``nn.Module``: state is one flat tensor."""
+
+    def __init__(self, spec: ModelSpec, device="cpu", dtype=torch.float32, ops: str = "ref", seed: int = 0,
+                 init: str = "normal", with_lm_head: bool = True, flat: torch.Tensor | None = None,
+                 gradient_checkpointing: bool = False):
+        if ops not in ("ref", "fused"):
+            raise ValueError("ops must be 'ref' or 'fused'")
+        self.spec = spec
+        self.ops = ops
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.layout = ParamLayout(spec, with_lm_head=with_lm_head)
+        self.with_lm_head = with_lm_head
+        self.gradient_checkpointing = gradient_checkpointing
+        if ops == "fused":
+            if dtype != torch.bfloat16 or self.device.type != "cuda":
+                raise ValueError("the fused path runs bf16 on CUDA")
+            if spec.head_dim != 128:
+                raise NotImplementedError("fused attention is built for head_dim 128")
+            if spec.qk_norm or spec.attention_bias:
+                raise NotImplementedError("qk_norm / attention_bias run on ops='ref' only")
+            from ..ops import lib
+
+            if not lib.available():
+                raise RuntimeError("ops='fused' needs a B200 (sm_100) device and libb200ops.so")
+        if flat is None:
+            flat = torch.empty(self.layout.total, dtype=dtype, device=self.device)
+            self.flat = flat
+            self.init_weights(seed, init)
+        else:
+            if flat.numel() != self.layout.total:
+                raise ValueError("flat buffer size does not match the layout")
+            self.flat = flat
+        self.p = self.layout.views(self.flat)
+        self.main_grad: torch.Tensor | None = None  # fp32 flat gradient (fused path)
+        self.g: dict[str, torch.Tensor] = {}
+        self.inv_freq = ref.rope_inv_freq(spec.head_dim, spec.rope_theta, spec.rope_scaling, device=self.device)
+        if ops == "ref":
+            self.flat.requires_grad_(True)
+        # autograd anchor for the fused path: the custom Functions take it as an input so that
+        # loss.backward() reaches their manual backward
+        self._anchor = torch.zeros(1, device=self.device, requires_grad=True) if ops == "fused" else None
+
+    # ------------------------------------------------------------------ weights
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, init: str = "normal", std: float = 0.02) -> None:
+        """Random init: N(0, 0.02) matrices, unit norm weights (HF ``_init_weights`` convention)."""
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        views = self.layout.views(self.flat)
+        self.flat.zero_()
+        for name, v in views.items():
+            e = self.layout.entries[name]
+            if name.endswith("norm"):
+                v.fill_(1.0)
+            elif name.endswith("bqkv"):
+                v.zero_()
+            elif init == "normal":
+                if v.device.type == "cuda":
+                    # generate on device in chunks: 8B parameters on the host would take minutes
+                    gg = torch.Generator(device=v.device).manual_seed(seed * 1000003 + e.offset % 1000003)
+                    flatv = v.view(-1)
+                    step = 1 << 26
+                    for s in range(0, flatv.numel(), step):
+                        n = min(step, flatv.numel() - s)
+                        flatv[s:s + n].copy_(torch.randn(n, device=v.device, generator=gg, dtype=torch.float32) * std)
+                else:
+                    v.copy_((torch.randn(v.shape, generator=g, dtype=torch.float32) * std).to(v.dtype))
+        # tied output head shares the embedding; nothing else to do
+
+    def lm_head_weight(self) -> torch.Tensor:
+        return self.p["embed"] if self.spec.tie_word_embeddings or "lm_head" not in self.p else self.p["lm_head"]
+
+    def ensure_main_grad(self) -> torch.Tensor:
+        if self.main_grad is None:
+            self.main_grad = torch.zeros(self.layout.total, dtype=torch.float32, device=self.device)
+            self.g = self.layout.views(self.main_grad)
+        return self.main_grad
+
+    def bind_main_grad(self, buf: torch.Tensor) -> None:
+        """Use an externally owned fp32 gradient buffer (e.g. a symmetric-memory bucket)."""
+        if buf.numel() != self.layout.total or buf.dtype != torch.float32:
+            raise ValueError("main_grad must be fp32 with the layout's size")
+        self.main_grad = buf
+        self.g = self.layout.views(buf)
+
+    def rebind(self, flat: torch.Tensor) -> None:
+        """Point the model at another flat buffer of the same layout (no copy)."""
+        self.flat = flat
+        self.p = self.layout.views(flat)
+        if self.ops == "ref":
+            self.flat.requires_grad_(True)
+
+    def grad_flat(self) -> torch.Tensor | None:
+        """Flat gradient: fp32 ``main_grad`` (fused) or autograd's ``flat.grad`` (ref)."""
+        return self.main_grad if self.ops == "fused" else self.flat.grad
+
+    def zero_grad(self) -> None:
+        if self.ops == "fused":
+            if self.main_grad is not None:
+                self.main_grad.zero_()
+        else:
+            self.flat.grad = None
+
+    # ------------------------------------------------------------------ public API
+    def token_logprobs(self, input_ids, position_ids, cu_seqlens, labels, temperature: float = 1.0,
+                       want_entropy: bool = False):
+        """log p(labels[t] | prefix) for every packed position (0 where ``labels < 0``).
+
+        ``labels`` is already shifted: ``labels[t]`` is the token that follows position ``t``.
+        Returns ``(logp [T] fp32, entropy [T] fp32 | None)``; ``logp`` is differentiable.
+        """
+        if self.ops == "ref":
+            h = self._ref_hidden(input_ids, position_ids, cu_seqlens)
+            logits = ref.linear(h, self.lm_head_weight_ref())
+            return ref.token_logprobs(logits, labels, temperature, with_entropy=want_entropy)
+        keep = torch.is_grad_enabled()
+        logp, ent = _FusedLogprobFn.apply(self, input_ids, position_ids, cu_seqlens, labels, temperature, want_entropy,
+                                          keep, self._anchor if keep else None)
+        return logp, (ent if want_entropy else None)
+
+    def hidden_states(self, input_ids, position_ids, cu_seqlens) -> torch.Tensor:
+        """Final-norm hidden states [T, D] (differentiable); used by the reward-model head."""
+        if self.ops == "ref":
+            return self._ref_hidden(input_ids, position_ids, cu_seqlens)
+        keep = torch.is_grad_enabled()
+        return _FusedHiddenFn.apply(self, input_ids, position_ids, cu_seqlens, keep, self._anchor if keep else None)
+
+    @torch.no_grad()
+    def logits(self, input_ids, position_ids, cu_seqlens) -> torch.Tensor:
+        """Full logits [T, V] (inference / tests only; training never materialises fp32 logits)."""
+        if self.ops == "ref":
+            return ref.linear(self._ref_hidden(input_ids, position_ids, cu_seqlens), self.lm_head_weight_ref())
+        h, _ = self._fused_forward_hidden(input_ids, position_ids, cu_seqlens, keep=False)
+        return _fused().gemm(h, self.lm_head_weight())
+
+    # ------------------------------------------------------------------ ref path
+    def lm_head_weight_ref(self) -> torch.Tensor:
+        v = self.layout.views(self.flat)
+        return v["embed"] if self.spec.tie_word_embeddings or "lm_head" not in v else v["lm_head"]
+
+    def _ref_hidden(self, input_ids, position_ids, cu_seqlens) -> torch.Tensor:
+        s = self.spec
+        v = self.layout.views(self.flat)  # autograd views of the single leaf
+        x = v["embed"][input_ids]
+        for i in range(s.num_layers):
+            x = self._ref_layer(x, v, i, position_ids, cu_seqlens)
+        return ref.rmsnorm(x, v["final_norm"], s.rms_norm_eps)
+
+    def _ref_layer(self, x, v, i, position_ids, cu_seqlens):
+        s = self.spec
+        n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
+        qkv = ref.linear(n1, v[f"l{i}.wqkv"])
+        if s.attention_bias:
+            qkv = qkv + v[f"l{i}.bqkv"]
+        if s.qk_norm:
+            T = qkv.shape[0]
+            heads = qkv.view(T, s.num_heads + 2 * s.num_kv_heads, s.head_dim)
+            q = ref.rmsnorm(heads[:, : s.num_heads], v[f"l{i}.q_norm"], s.rms_norm_eps)
+            k = ref.rmsnorm(heads[:, s.num_heads : s.num_heads + s.num_kv_heads], v[f"l{i}.k_norm"], s.rms_norm_eps)
+            qkv = torch.cat([q, k, heads[:, s.num_heads + s.num_kv_heads :]], dim=1).reshape(T, -1)
+        qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+        attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim)
+        x = x + ref.linear(attn, v[f"l{i}.wo"])
+        n2 = ref.rmsnorm(x, v[f"l{i}.mlp_norm"], s.rms_norm_eps)
+        act = ref.swiglu(ref.linear(n2, v[f"l{i}.w_gate_up"]))
+        return x + ref.linear(act, v[f"l{i}.w_down"])
+
+    # ------------------------------------------------------------------ fused path
+    def _fused_forward_hidden(self, input_ids, position_ids, cu_seqlens, keep: bool):
+        """Runs the stack; returns final-norm hidden states.  ``keep`` stores what backward needs."""
+        f = _fused()
+        s, p = self.spec, self.p
+        pos = position_ids.to(torch.int32)
+        cu = cu_seqlens.to(torch.int32)
+        scale = s.head_dim ** -0.5
+        stash: list[_LayerStash] = []
+        stream = f.embedding_fwd(p["embed"], input_ids)
+        delta = None  # pending residual contribution, added inside the next RMSNorm
+        for i in range(s.num_layers):
+            n1, h_in, rstd1 = f.rmsnorm_fwd(delta if delta is not None else stream, p[f"l{i}.attn_norm"], s.rms_norm_eps,
+                                            res=stream if delta is not None else None)
+            qkv = f.gemm(n1, p[f"l{i}.wqkv"])
+            del n1
+            f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+            o = f.gemm(attn, p[f"l{i}.wo"])
+            n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=h_in)
+            del o
+            gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
+            del n2
+            act = f.swiglu_fwd(gate_up)
+            delta = f.gemm(act, p[f"l{i}.w_down"])
+            del act
+            stream = h_mid
+            if keep:
+                if self.gradient_checkpointing:
+                    stash.append(_LayerStash(h_in, None, None, None, None, None, None, None))
+                else:
+                    stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up))
+        nf, h_last, rstd_f = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
+        state = None
+        if keep:
+            state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu}
+        return nf, state
+
+    def _recompute_layer(self, i: int, st: _LayerStash, pos, cu) -> _LayerStash:
+        """Gradient checkpointing: rebuild a layer's activations from its input stream."""
+        f = _fused()
+        s, p = self.spec, self.p
+        n1, _, rstd1 = f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)
+        qkv = f.gemm(n1, p[f"l{i}.wqkv"])
+        f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+        attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, s.head_dim ** -0.5)
+        o = f.gemm(attn, p[f"l{i}.wo"])
+        n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=st.h_in)
+        gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
+        return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up)
+
+    def _fused_backward_hidden(self, state: dict, d_nf: torch.Tensor) -> None:
+        """Backward from d(final-norm hidden) to the embedding; accumulates into ``main_grad``."""
+        f = _fused()
+        s, p = self.spec, self.p
+        self.ensure_main_grad()
+        g = self.g
+        h_last, rstd_f = state["final"]
+        stash, pos, cu = state["stash"], state["pos"], state["cu"]
+        # final norm: h_last = stream + delta ; both get the same gradient
+        d_stream = f.rmsnorm_bwd(h_last, p["final_norm"], rstd_f, d_nf, None, g["final_norm"])
+        del d_nf
+        scale = s.head_dim ** -0.5
+        for i in reversed(range(s.num_layers)):
+            st = stash[i]
+            if st.qkv is None:
+                st = self._recompute_layer(i, st, pos, cu)
+            stash[i] = None
+            # ---- MLP: out = h_mid + down(swiglu(gate_up(norm(h_mid))))
+            act = f.swiglu_fwd(st.gate_up)
+            f.gemm(d_stream, act, g[f"l{i}.w_down"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            d_act = f.gemm(d_stream, p[f"l{i}.w_down"], b_mn=True)
+            del act
+            dgu = f.swiglu_bwd_(st.gate_up, d_act)
+            del d_act
+            n2, _, _ = f.rmsnorm_fwd(st.h_mid, p[f"l{i}.mlp_norm"], s.rms_norm_eps)
+            f.gemm(dgu, n2, g[f"l{i}.w_gate_up"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            del n2
+            d_n2 = f.gemm(dgu, p[f"l{i}.w_gate_up"], b_mn=True)
+            del dgu
+            d_mid = f.rmsnorm_bwd(st.h_mid, p[f"l{i}.mlp_norm"], st.rstd2, d_n2, d_stream, g[f"l{i}.mlp_norm"])
+            del d_n2, d_stream
+            # ---- attention: h_mid = h_in + wo(attn(rope(wqkv(norm(h_in)))))
+            f.gemm(d_mid, st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            d_attn = f.gemm(d_mid, p[f"l{i}.wo"], b_mn=True)
+            dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+            del d_attn
+            f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True)
+            n1, _, _ = f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)
+            f.gemm(dqkv, n1, g[f"l{i}.wqkv"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            del n1
+            d_n1 = f.gemm(dqkv, p[f"l{i}.wqkv"], b_mn=True)
+            del dqkv
+            d_stream = f.rmsnorm_bwd(st.h_in, p[f"l{i}.attn_norm"], st.rstd1, d_n1, d_mid, g[f"l{i}.attn_norm"])
+            del d_n1, d_mid
+        f.embedding_bwd(g["embed"], state["ids"], d_stream)
+        state.clear()
+
+
+class _FusedHiddenFn(torch.autograd.Function):
+    """Autograd bridge: hidden states out, manual backward in.  ``flat`` only anchors the graph."""
+
+    @staticmethod
+    def forward(ctx, model: LlamaModel, input_ids, position_ids, cu_seqlens, keep, anchor):
+        ctx.model = model
+        nf, ctx.state = model._fused_forward_hidden(input_ids, position_ids, cu_seqlens, keep=keep)
+        return nf
+
+    @staticmethod
+    def backward(ctx, d_nf):
+        ctx.model._fused_backward_hidden(ctx.state, d_nf.contiguous())
+        return None, None, None, None, None, None
+
+
+class _FusedLogprobFn(torch.autograd.Function):
+    """lm_head GEMM + streaming log-softmax; backward rewrites the bf16 logits in place."""
+
+    @staticmethod
+    def forward(ctx, model: LlamaModel, input_ids, position_ids, cu_seqlens, labels, temperature, want_entropy, keep,
+                anchor):
+        f = _fused()
+        needs_grad = keep
+        nf, ctx.state = model._fused_forward_hidden(input_ids, position_ids, cu_seqlens, keep=needs_grad)
+        w = model.lm_head_weight()
+        logits = f.gemm(nf, w)
+        logp, lse, ent = f.logprob_fwd(logits, labels, temperature, want_entropy)
+        ctx.model = model
+        ctx.temperature = temperature
+        if needs_grad:
+            ctx.save_for_backward(nf, logits, lse, labels)
+        if ent is None:
+            ent = torch.zeros(0, device=logp.device)
+        ctx.mark_non_differentiable(ent)
+        return logp, ent
+
+    @staticmethod
+    def backward(ctx, d_logp, _d_ent):
+        f = _fused()
+        model = ctx.model
+        nf, logits, lse, labels = ctx.saved_tensors
+        model.ensure_main_grad()
+        d_logits = f.logprob_bwd_(logits, labels, lse, d_logp.contiguous().float(), ctx.temperature)
+        head = "embed" if (model.spec.tie_word_embeddings or "lm_head" not in model.p) else "lm_head"
+        f.gemm(d_logits, nf, model.g[head], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+        d_nf = f.gemm(d_logits, model.lm_head_weight(), b_mn=True)
+        del d_logits, logits
+        model._fused_backward_hidden(ctx.state, d_nf)
+        return None, None, None, None, None, None, None, None, None

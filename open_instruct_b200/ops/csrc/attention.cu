@@ -605,7 +605,8 @@ extern "C" int b200_attn_fwd(const void* qkv, const int* cu_seqlens, void* out, 
   return static_cast<int>(cudaGetLastError());
 }
 
-// scratch layout (caller-allocated, (Hq*T + T*Hq*128) floats): [delta: Hq*T][dq_acc: T*Hq*128]
+// scratch layout (caller-allocated, 16-byte aligned, (T*Hq*128 + Hq*T) floats):
+// [dq_acc: T*Hq*128][delta: Hq*T] - dq_acc first so that its 16-byte vector reductions stay aligned
 
 // d_out [T, Hq*128] bf16 -> dqkv [T, (Hq+2Hkv)*128] bf16 (every element written for rows < T).
 extern "C" int b200_attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse,
@@ -614,8 +615,8 @@ extern "C" int b200_attn_bwd(const void* qkv, const void* out, const void* d_out
   if (T <= 0 || B <= 0) return 0;
   if (Dh != DH || Hq % Hkv) return -1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  float* delta = reinterpret_cast<float*>(scratch);
-  float* dq_acc = delta + static_cast<long long>(Hq) * T;
+  float* dq_acc = reinterpret_cast<float*>(scratch);
+  float* delta = dq_acc + static_cast<long long>(T) * Hq * DH;
   cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * Hq * DH * sizeof(float), st);
   {
     const long long warps = static_cast<long long>(T) * Hq;

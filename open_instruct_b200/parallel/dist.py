@@ -1,0 +1,92 @@
+"""Process-group plumbing: one process per GPU, ``torch.distributed`` over NCCL (gloo on CPU).
+
+Replaces the accelerate / DeepSpeed launcher glue of the reference (``open_instruct/finetune.py:396-404``,
+``open_instruct/grpo_fast.py:327-329``): ranks come from the ``torchrun`` environment, the rendezvous
+address defaults to 127.0.0.1, and every helper degrades to a no-op in a single process.
+"""
+
+from __future__ import annotations
+
+import datetime
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def env_rank() -> int:
+    return int(os.environ.get("RANK", "0"))
+
+
+def env_world_size() -> int:
+    return int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def env_local_rank() -> int:
+    return int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def init_distributed(backend: str | None = None, timeout_s: float = 1800.0) -> tuple[int, int, torch.device]:
+    """Initialise the default group from the environment.  Returns (rank, world, device)."""
+    world = env_world_size()
+    use_cuda = torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(env_local_rank())
+        device = torch.device("cuda", env_local_rank())
+    else:
+        device = torch.device("cpu")
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        backend = backend or ("nccl" if use_cuda else "gloo")
+        kwargs = {}
+        if backend == "nccl":
+            kwargs["device_id"] = device
+        dist.init_process_group(backend=backend, rank=env_rank(), world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    return env_rank() if world > 1 else 0, world, device
+
+
+def is_dist() -> bool:
+    return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+
+
+def rank(group=None) -> int:
+    return dist.get_rank(group) if is_dist() else 0
+
+
+def world_size(group=None) -> int:
+    return dist.get_world_size(group) if is_dist() else 1
+
+
+def barrier(group=None) -> None:
+    if is_dist():
+        dist.barrier(group)
+
+
+def all_reduce_(t: torch.Tensor, op=None, group=None) -> torch.Tensor:
+    if is_dist():
+        dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=group)
+    return t
+
+
+def max_over_ranks(value: float, device=None) -> float:
+    """MAX-reduce a host scalar (device-time measurements are reported as the slowest rank)."""
+    if not is_dist():
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def broadcast_object(obj, src: int = 0, group=None):
+    if not is_dist():
+        return obj
+    box = [obj]
+    dist.broadcast_object_list(box, src=src, group=group)
+    return box[0]
+
+
+def destroy() -> None:
+    if dist.is_available() and dist.is_initialized():
+        dist.destroy_process_group()
