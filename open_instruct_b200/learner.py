@@ -1,0 +1,157 @@
+"""The learner: model + sharded optimizer + the per-step state machine shared by every trainer.
+
+One ``Learner`` lives in each rank's process (one process per GPU).  SFT, DPO, reward-model and
+GRPO trainers differ only in the loss they build from per-token log-probabilities or hidden
+states; gradient accumulation, the once-per-step gradient exchange, clipping, the partitioned
+AdamW and the bf16 refresh are here.  It stands where ``accelerator.prepare`` +
+``deepspeed.initialize`` stand in the reference (``open_instruct/finetune.py:707-709``,
+``open_instruct/grpo_fast.py:384-391``).
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from .data.collate import IGNORE
+from .models import LlamaModel, ModelSpec
+from .parallel import dist as pdist
+from .parallel.zero import ZeroOptimizer, lr_at, padded_numel
+
+
+@dataclass
+class LearnerConfig:
+    ops: str = "auto"  # "fused" (sm_100a kernels), "ref" (PyTorch), "auto"
+    comm: str = "auto"  # "fused" (symmetric-memory kernels), "nccl", "none", "auto"
+    learning_rate: float = 2e-5
+    weight_decay: float = 0.0
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    max_grad_norm: float | None = None
+    lr_scheduler_type: str = "linear"
+    warmup_steps: int = 0
+    total_steps: int = 1
+    final_lr_ratio: float | None = None
+    gradient_checkpointing: bool = False
+    seed: int = 0
+    dtype: torch.dtype | None = None
+
+
+class Learner:
+    def __init__(self, spec: ModelSpec, cfg: LearnerConfig, device=None, group=None, flat_init: torch.Tensor | None = None):
+        self.spec, self.cfg, self.group = spec, cfg, group
+        self.rank, self.world = pdist.rank(group), pdist.world_size(group)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        ops = cfg.ops
+        if ops == "auto":
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.qk_norm
+                              and not spec.attention_bias and torch.cuda.get_device_capability(self.device)[0] == 10) else "ref"
+        self.ops = ops
+        dtype = cfg.dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        comm = cfg.comm
+        if comm == "auto":
+            comm = "none" if self.world == 1 else ("fused" if ops == "fused" else "nccl")
+        self.comm = comm
+        from .models.spec import ParamLayout
+
+        layout = ParamLayout(spec)
+        n = padded_numel(layout.total, self.world)
+        self.symm = None
+        if comm == "fused":
+            from .parallel.symm import SymmetricState
+
+            self.symm = SymmetricState(n, self.device, group)
+            flat = self.symm.params
+        else:
+            flat = torch.zeros(n, dtype=dtype, device=self.device)
+        self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, seed=cfg.seed, flat=flat,
+                                gradient_checkpointing=cfg.gradient_checkpointing)
+        if flat_init is not None:
+            with torch.no_grad():
+                self.model.flat[: flat_init.numel()].copy_(flat_init.to(dtype))
+        else:
+            self.model.init_weights(cfg.seed)
+            if self.world > 1:  # identical start on every rank
+                torch.distributed.broadcast(self.model.flat.detach(), src=0, group=group)
+        if self.symm is not None:
+            self.model.bind_main_grad(self.symm.grads)
+        self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, lr=cfg.learning_rate,
+                                 betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay,
+                                 max_grad_norm=cfg.max_grad_norm, group=group, comm=comm, symm=self.symm,
+                                 use_kernels=(ops == "fused"))
+        self.global_step = 0
+        self._accum = 0
+
+    # ------------------------------------------------------------------ pieces
+    def lr(self, step: int | None = None) -> float:
+        c = self.cfg
+        return lr_at(self.global_step if step is None else step, c.learning_rate, c.total_steps, c.warmup_steps,
+                     c.lr_scheduler_type, c.final_lr_ratio)
+
+    def token_logprobs(self, batch: dict, temperature: float = 1.0, want_entropy: bool = False):
+        return self.model.token_logprobs(batch["input_ids"], batch["position_ids"], batch["cu_seq_lens_q"],
+                                         batch["labels_shifted"], temperature, want_entropy)
+
+    def backward(self, loss: torch.Tensor) -> None:
+        loss.backward()
+        self._accum += 1
+
+    def optimizer_step(self, grad_scale: float | None = None) -> torch.Tensor:
+        """Exchange + clip + AdamW + refresh.  ``grad_scale`` defaults to 1/(micro-batches * world):
+        the mean over everything accumulated since the last step, DeepSpeed's convention."""
+        if grad_scale is None:
+            grad_scale = 1.0 / (max(self._accum, 1) * self.world)
+        grad = self.model.grad_flat()
+        if grad is None:
+            raise RuntimeError("optimizer_step called without any backward")
+        if grad.numel() < self.opt.flat.numel():  # ref path: autograd grad has the padded size already
+            raise RuntimeError("gradient buffer smaller than the parameter buffer")
+        norm = self.opt.step(grad, lr=self.lr(), grad_scale=grad_scale)
+        if self.ops == "fused":
+            if self.world > 1 or self.comm != "none":
+                self.model.main_grad.zero_()
+            else:
+                # single rank: AdamW zeroed the (only) shard in place, padding included
+                pass
+        else:
+            self.model.flat.grad = None
+        self._accum = 0
+        self.global_step += 1
+        return norm
+
+    # ------------------------------------------------------------------ SFT
+    def sft_micro_step(self, batch: dict, reduce_loss: str = "mean") -> tuple[torch.Tensor, torch.Tensor]:
+        """Forward + backward of one packed micro-batch.  Returns (loss, number of target tokens).
+
+        ``mean``: mean CE over this micro-batch's target tokens (HF default, ``finetune.py:822-826``);
+        ``sum`` : summed CE; the caller normalises by the global token count at the step.
+        """
+        logp, _ = self.token_logprobs(batch)
+        n = (batch["labels_shifted"] != IGNORE).sum()
+        total = -logp.sum()
+        loss = total / n.clamp(min=1) if reduce_loss == "mean" else total
+        self.backward(loss)
+        return loss.detach(), n
+
+    def sft_step(self, micro_batches: list[dict], reduce_loss: str = "mean") -> dict:
+        """One optimizer step over a list of packed micro-batches already on the device."""
+        losses, toks = [], []
+        for mb in micro_batches:
+            loss, n = self.sft_micro_step(mb, reduce_loss)
+            losses.append(loss)
+            toks.append(n)
+        loss_t = torch.stack(losses)
+        tok_t = torch.stack(toks).sum()
+        if reduce_loss == "sum":
+            tot = tok_t.clone().float()
+            pdist.all_reduce_(tot, group=self.group)
+            norm = self.optimizer_step(grad_scale=None if False else float(1.0 / max(tot.item(), 1.0)))
+            loss_out = loss_t.sum() / tok_t.clamp(min=1)
+        else:
+            norm = self.optimizer_step()
+            loss_out = loss_t.mean()
+        return {"loss": loss_out, "grad_norm": norm, "target_tokens": tok_t}

@@ -79,8 +79,8 @@ class LlamaModel:
             self.flat = flat
             self.init_weights(seed, init)
         else:
-            if flat.numel() != self.layout.total:
-                raise ValueError("flat buffer size does not match the layout")
+            if flat.numel() < self.layout.total:
+                raise ValueError("flat buffer is smaller than the layout")
             self.flat = flat
         self.p = self.layout.views(self.flat)
         self.main_grad: torch.Tensor | None = None  # fp32 flat gradient (fused path)
@@ -123,14 +123,14 @@ class LlamaModel:
 
     def ensure_main_grad(self) -> torch.Tensor:
         if self.main_grad is None:
-            self.main_grad = torch.zeros(self.layout.total, dtype=torch.float32, device=self.device)
+            self.main_grad = torch.zeros(self.flat.numel(), dtype=torch.float32, device=self.device)
             self.g = self.layout.views(self.main_grad)
         return self.main_grad
 
     def bind_main_grad(self, buf: torch.Tensor) -> None:
         """Use an externally owned fp32 gradient buffer (e.g. a symmetric-memory bucket)."""
-        if buf.numel() != self.layout.total or buf.dtype != torch.float32:
-            raise ValueError("main_grad must be fp32 with the layout's size")
+        if buf.numel() < self.layout.total or buf.dtype != torch.float32:
+            raise ValueError("main_grad must be fp32 and at least the layout's size")
         self.main_grad = buf
         self.g = self.layout.views(buf)
 

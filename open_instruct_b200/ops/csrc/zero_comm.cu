@@ -1,0 +1,262 @@
+// Optimizer-step collectives fused with their compute, over NVLink peer memory.
+//
+// Every rank holds its fp32 gradient buffer and its bf16 working parameters in symmetric
+// memory (same layout on every GPU, every peer's copy mapped locally).  Per optimizer step:
+//
+//   symm_barrier            all ranks' backward kernels have finished (flag exchange, bounded)
+//   zero_reduce_scatter     owner reads its slice from EVERY peer's gradient buffer with P2P
+//                           loads (or one multimem.ld_reduce through the switch), sums in fp32,
+//                           writes the reduced shard and accumulates its squared norm
+//   symm_allreduce_scalar   squared norms exchanged through the signal pads (deterministic order)
+//   zero_adamw_allgather    AdamW on the fp32 shard; the refreshed bf16 values are stored straight
+//                           into every peer's working copy (P2P stores, or one multimem.st)
+//   symm_barrier            all stores have landed before anyone starts the next forward
+//
+// No TMA is used here: all remote traffic is ordinary ld/st (or multimem) from this GPU's SMs.
+// Every wait is bounded and reports through the status word instead of hanging.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int MAX_PEERS = 8;
+struct PeerPtrs {
+  void* p[MAX_PEERS];
+};
+
+// signal-pad slots (uint32 index from the pad base); torch's own channels live below 1024
+constexpr int PAD_BARRIER = 1024;       // [+rank]
+constexpr int PAD_SCALAR_FLAG = 1040;   // [+rank]
+constexpr int PAD_SCALAR_VAL = 1056;    // [+parity*8 + rank] (float bits)
+
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+// wait until *addr has reached `epoch` (wrap-safe); false when the time limit ran out
+__device__ __forceinline__ bool wait_epoch(const uint32_t* addr, uint32_t epoch, long long limit_cycles) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_sys(addr) - epoch) < 0) {
+    if (clock64() - t0 > limit_cycles) return false;
+    __nanosleep(64);
+  }
+  return true;
+}
+
+// One thread per peer: publish my arrival in the peer's pad, then wait for the peer's in mine.
+__global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, long long limit_cycles,
+                                    int* __restrict__ status) {
+  const int peer = threadIdx.x;
+  if (peer >= world) return;
+  __threadfence_system();
+  st_release_sys(reinterpret_cast<uint32_t*>(pads.p[peer]) + PAD_BARRIER + rank, epoch);
+  if (!wait_epoch(reinterpret_cast<const uint32_t*>(pads.p[rank]) + PAD_BARRIER + peer, epoch, limit_cycles))
+    atomicCAS(status, 0, ST_TIMEOUT_PEER);
+}
+
+// out[0] = sum over ranks of in[0], summed in rank order on every rank (bitwise identical everywhere).
+__global__ void symm_allreduce_scalar_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch,
+                                             const float* __restrict__ in, float* __restrict__ out,
+                                             long long limit_cycles, int* __restrict__ status) {
+  __shared__ int failed;
+  const int peer = threadIdx.x;
+  const int par = epoch & 1;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (peer < world) {
+    uint32_t* pad = reinterpret_cast<uint32_t*>(pads.p[peer]);
+    reinterpret_cast<volatile float*>(pad)[PAD_SCALAR_VAL + par * 8 + rank] = in[0];
+    __threadfence_system();
+    st_release_sys(pad + PAD_SCALAR_FLAG + rank, epoch);
+    if (!wait_epoch(reinterpret_cast<const uint32_t*>(pads.p[rank]) + PAD_SCALAR_FLAG + peer, epoch, limit_cycles)) {
+      atomicCAS(status, 0, ST_TIMEOUT_PEER);
+      failed = 1;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    if (!failed) {
+      const volatile float* mine = reinterpret_cast<const volatile float*>(pads.p[rank]) + PAD_SCALAR_VAL + par * 8;
+      for (int r = 0; r < world; ++r) s += mine[r];
+    } else {
+      s = in[0];
+    }
+    out[0] = s;
+  }
+}
+
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// out[i] = sum_r grads_r[lo + i],  i in [0, n);  sumsq += sum out[i]^2.   n % 4 == 0.
+template <bool MULTIMEM>
+__global__ void __launch_bounds__(256)
+zero_reduce_scatter_kernel(PeerPtrs grads, const float* __restrict__ mc_grads, int rank, int world, long long lo,
+                           long long n, float* __restrict__ out, float* __restrict__ sumsq) {
+  __shared__ float red[8];
+  float ss = 0.f;
+  const long long nv = n / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 acc;
+    if (MULTIMEM) {
+      acc = multimem_ld_reduce_f32x4(mc_grads + lo + i * 4);
+    } else {
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      // fixed rank order keeps the sum bitwise identical from run to run
+#pragma unroll 1
+      for (int r = 0; r < world; ++r) {
+        const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) atomicAdd(sumsq, v);
+  }
+}
+
+// AdamW on n (multiple of 8) fp32 elements; bf16 result stored at element offset `goff` of every
+// peer's parameter buffer.
+template <bool MULTIMEM>
+__global__ void __launch_bounds__(256)
+zero_adamw_allgather_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                            const float* __restrict__ grad, PeerPtrs params, void* mc_params, int world, long long goff,
+                            long long n, const float* __restrict__ gscale, float lr, float beta1, float beta2,
+                            float eps, float wd, float bc1, float bc2) {
+  const float gs = gscale ? gscale[0] : 1.f;
+  const long long nv = n / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float p[8], mm[8], vv[8], g[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float4 a = reinterpret_cast<const float4*>(master)[i * 2 + h];
+      const float4 b = reinterpret_cast<const float4*>(m)[i * 2 + h];
+      const float4 c = reinterpret_cast<const float4*>(v)[i * 2 + h];
+      const float4 d = reinterpret_cast<const float4*>(grad)[i * 2 + h];
+      p[4 * h] = a.x; p[4 * h + 1] = a.y; p[4 * h + 2] = a.z; p[4 * h + 3] = a.w;
+      mm[4 * h] = b.x; mm[4 * h + 1] = b.y; mm[4 * h + 2] = b.z; mm[4 * h + 3] = b.w;
+      vv[4 * h] = c.x; vv[4 * h + 1] = c.y; vv[4 * h + 2] = c.z; vv[4 * h + 3] = c.w;
+      g[4 * h] = d.x; g[4 * h + 1] = d.y; g[4 * h + 2] = d.z; g[4 * h + 3] = d.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = g[j] * gs;
+      mm[j] = beta1 * mm[j] + (1.f - beta1) * gj;
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
+      p[j] *= (1.f - lr * wd);
+      p[j] -= lr * (mm[j] / bc1) / (sqrtf(vv[j] / bc2) + eps);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      reinterpret_cast<float4*>(master)[i * 2 + h] = make_float4(p[4 * h], p[4 * h + 1], p[4 * h + 2], p[4 * h + 3]);
+      reinterpret_cast<float4*>(m)[i * 2 + h] = make_float4(mm[4 * h], mm[4 * h + 1], mm[4 * h + 2], mm[4 * h + 3]);
+      reinterpret_cast<float4*>(v)[i * 2 + h] = make_float4(vv[4 * h], vv[4 * h + 1], vv[4 * h + 2], vv[4 * h + 3]);
+    }
+    uint4 pk;
+    pk.x = pack_bf16x2(p[0], p[1]);
+    pk.y = pack_bf16x2(p[2], p[3]);
+    pk.z = pack_bf16x2(p[4], p[5]);
+    pk.w = pack_bf16x2(p[6], p[7]);
+    if (MULTIMEM) {
+      multimem_st_b128(reinterpret_cast<__nv_bfloat16*>(mc_params) + goff + i * 8, pk);
+    } else {
+#pragma unroll 1
+      for (int r = 0; r < world; ++r)
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + goff + i * 8) = pk;
+    }
+  }
+}
+
+static PeerPtrs make_ptrs(const void* const* host, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < world ? const_cast<void*>(host[i]) : nullptr;
+  return pp;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// `limit_ms`: how long a rank waits for its peers before it records ST_TIMEOUT_PEER and returns.
+extern "C" int b200_symm_barrier(const void* const* pad_ptrs, int rank, int world, unsigned epoch, int limit_ms,
+                                 int* status, void* stream) {
+  if (world > MAX_PEERS) return -1;
+  const long long cycles = static_cast<long long>(limit_ms) * 1900000LL;
+  symm_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_ptrs(pad_ptrs, world), rank, world,
+                                                                         epoch, cycles, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int b200_symm_allreduce_scalar(const void* const* pad_ptrs, int rank, int world, unsigned epoch,
+                                          const float* in, float* out, int limit_ms, int* status, void* stream) {
+  if (world > MAX_PEERS) return -1;
+  const long long cycles = static_cast<long long>(limit_ms) * 1900000LL;
+  symm_allreduce_scalar_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_ptrs(pad_ptrs, world), rank, world, epoch, in, out, cycles, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out_shard[n] = sum over ranks of grads_r[lo .. lo+n); sumsq[0] = |out_shard|^2 (overwritten).
+extern "C" int b200_zero_reduce_scatter(const void* const* grad_ptrs, const void* mc_grads, int rank, int world,
+                                        long long lo, long long n, float* out_shard, float* sumsq, int use_multimem,
+                                        void* stream) {
+  if (world > MAX_PEERS || n % 4) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaMemsetAsync(sumsq, 0, sizeof(float), st);
+  const int grid = 148 * 8;
+  if (use_multimem && mc_grads)
+    zero_reduce_scatter_kernel<true><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world),
+                                                            reinterpret_cast<const float*>(mc_grads), rank, world, lo, n,
+                                                            out_shard, sumsq);
+  else
+    zero_reduce_scatter_kernel<false><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world), nullptr, rank, world, lo, n,
+                                                             out_shard, sumsq);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int b200_zero_adamw_allgather(float* master, float* m, float* v, const float* grad,
+                                         const void* const* param_ptrs, void* mc_params, int world, long long goff,
+                                         long long n, const float* gscale, float lr, float beta1, float beta2,
+                                         float eps, float wd, int step, int use_multimem, void* stream) {
+  if (world > MAX_PEERS || n % 8 || goff % 8) return -1;
+  if (n == 0) return 0;
+  const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
+  const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = 148 * 8;
+  if (use_multimem && mc_params)
+    zero_adamw_allgather_kernel<true><<<grid, 256, 0, st>>>(master, m, v, grad, make_ptrs(param_ptrs, world), mc_params,
+                                                             world, goff, n, gscale, lr, beta1, beta2, eps, wd, bc1, bc2);
+  else
+    zero_adamw_allgather_kernel<false><<<grid, 256, 0, st>>>(master, m, v, grad, make_ptrs(param_ptrs, world), nullptr,
+                                                              world, goff, n, gscale, lr, beta1, beta2, eps, wd, bc1,
+                                                              bc2);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -133,8 +133,15 @@ def check_status(sync: bool = True) -> None:
             raise KernelError(f"kernel on cuda:{key} gave up a bounded wait (status {code})")
 
 
+# kernels launched per library call (for launch accounting in benchmarks)
+_KERNELS_PER_CALL = {"b200_attn_bwd": 3, "b200_rmsnorm_bwd": 2, "b200_sumsq": 2}
+launch_count = 0
+
+
 def call(name: str, *args) -> None:
+    global launch_count
     lib = load_ops()
+    launch_count += _KERNELS_PER_CALL.get(name, 1)
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(f"{name} failed with code {rc}")

@@ -82,7 +82,7 @@ class ZeroOptimizer:
         self.device = flat.device
         self.use_kernels = (flat.is_cuda and flat.dtype == torch.bfloat16) if use_kernels is None else use_kernels
         with torch.no_grad():
-            self.master = flat.detach()[self.lo:self.hi].float().clone()
+            self.master = flat.detach()[self.lo:self.hi].to(torch.float32, copy=True)
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
         self.grad_shard = torch.zeros_like(self.master) if self.world > 1 else None
