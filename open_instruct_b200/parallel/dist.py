@@ -47,25 +47,33 @@ def init_distributed(backend: str | None = None, timeout_s: float = 1800.0) -> t
     return env_rank() if world > 1 else 0, world, device
 
 
+class _SoloGroup:
+    """A group of exactly this process: lets one rank of a larger job run a component alone
+    (single-process oracles in tests, rank-0-only evaluation)."""
+
+
+SOLO = _SoloGroup()
+
+
 def is_dist() -> bool:
     return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
 
 
 def rank(group=None) -> int:
-    return dist.get_rank(group) if is_dist() else 0
+    return dist.get_rank(group) if is_dist() and group is not SOLO else 0
 
 
 def world_size(group=None) -> int:
-    return dist.get_world_size(group) if is_dist() else 1
+    return dist.get_world_size(group) if is_dist() and group is not SOLO else 1
 
 
 def barrier(group=None) -> None:
-    if is_dist():
+    if is_dist() and group is not SOLO:
         dist.barrier(group)
 
 
 def all_reduce_(t: torch.Tensor, op=None, group=None) -> torch.Tensor:
-    if is_dist():
+    if is_dist() and group is not SOLO:
         dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=group)
     return t
 

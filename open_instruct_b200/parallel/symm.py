@@ -1,0 +1,123 @@
+"""Symmetric-memory state of the learner group and the fused optimizer-step collectives.
+
+The bf16 working parameters and the fp32 gradient accumulator of every rank are allocated in
+symmetric memory (``torch.distributed._symmetric_memory`` does the allocation, the handle
+exchange between the rank processes and the optional NVLS multicast binding - that is plumbing).
+Everything that moves data is done by this package's own kernels
+(``open_instruct_b200/ops/csrc/zero_comm.cu``), which dereference the peers' pointers directly:
+
+* ``reduce_scatter_grad``  barrier, then each owner sums its slice out of all peers' gradient
+  buffers, accumulating the squared norm in the same pass; norms are exchanged through the
+  signal pads.  (What DeepSpeed does with bucketed NCCL reduce-scatter + a separate norm pass.)
+* ``adamw_allgather``      AdamW on the owner's fp32 shard with the bf16 result stored into every
+  peer's working copy from inside the optimizer kernel.  (DeepSpeed: optimizer step, bf16 copy,
+  then NCCL all-gather.)
+* ``finish_step``          barrier: all stores have landed.
+
+``use_multimem=True`` switches the two data kernels to ``multimem.ld_reduce`` / ``multimem.st`` through
+the NVSwitch when the allocation has a multicast address.  Waits on peers are bounded
+(``peer_timeout_ms``): a rank whose peer never arrives gets ``ST_TIMEOUT_PEER`` in the status word and
+an exception at the next ``lib.check_status()`` instead of a hung GPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import lib
+from ..ops.lib import ptr, status_word, stream_ptr
+
+_P, _I, _L, _F, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_uint
+_PP = ctypes.POINTER(ctypes.c_void_p)
+
+lib._SIGNATURES.update({
+    "b200_symm_barrier": [_PP, _I, _I, _U, _I, _P, _P],
+    "b200_symm_allreduce_scalar": [_PP, _I, _I, _U, _P, _P, _I, _P, _P],
+    "b200_zero_reduce_scatter": [_PP, _P, _I, _I, _L, _L, _P, _P, _I, _P],
+    "b200_zero_adamw_allgather": [_P, _P, _P, _P, _PP, _P, _I, _L, _L, _P, _F, _F, _F, _F, _F, _I, _I, _P],
+})
+
+
+def _ptr_array(ptrs) -> ctypes.Array:
+    arr = (ctypes.c_void_p * 8)()
+    for i, p in enumerate(ptrs):
+        arr[i] = int(p)
+    return arr
+
+
+class SymmetricState:
+    """Symmetric ``params`` (bf16) and ``grads`` (fp32) buffers of ``n`` elements + their peer maps."""
+
+    def __init__(self, n: int, device, group=None, use_multimem: bool | None = None, peer_timeout_ms: int = 20000):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if not dist.is_initialized():
+            raise RuntimeError("SymmetricState needs an initialised process group")
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > 8:
+            raise ValueError("one NVSwitch domain: at most 8 ranks")
+        self.device = torch.device(device)
+        self.n = n
+        self.peer_timeout_ms = peer_timeout_ms
+        self.params = symm_mem.empty(n, dtype=torch.bfloat16, device=self.device)
+        self.grads = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        self.params.zero_()
+        self.grads.zero_()
+        self._hp = symm_mem.rendezvous(self.params, self.group)
+        self._hg = symm_mem.rendezvous(self.grads, self.group)
+        self._param_ptrs = _ptr_array(self._hp.buffer_ptrs)
+        self._grad_ptrs = _ptr_array(self._hg.buffer_ptrs)
+        self._pads = _ptr_array(self._hg.signal_pad_ptrs)
+        self._mc_params = int(self._hp.multicast_ptr or 0)
+        self._mc_grads = int(self._hg.multicast_ptr or 0)
+        if use_multimem is None:
+            use_multimem = os.environ.get("B200_MULTIMEM", "0") == "1"
+        self.use_multimem = bool(use_multimem and self._mc_params and self._mc_grads)
+        self._barrier_epoch = 0
+        self._scalar_epoch = 0
+        self._local_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        lib.load_ops()
+        for name, sig in lib._SIGNATURES.items():
+            fn = getattr(lib.load_ops(), name, None)
+            if fn is not None:
+                fn.argtypes = sig
+                fn.restype = ctypes.c_int
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every rank has mapped every peer before any kernel touches them
+        self.shard = n // self.world
+
+    # ------------------------------------------------------------------ primitives
+    def barrier(self) -> None:
+        """Device-side barrier on the current stream (no host synchronisation)."""
+        self._barrier_epoch += 1
+        lib.call("b200_symm_barrier", self._pads, self.rank, self.world, self._barrier_epoch, self.peer_timeout_ms,
+                 ptr(status_word(self.device)), stream_ptr())
+
+    def allreduce_scalar(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        self._scalar_epoch += 1
+        lib.call("b200_symm_allreduce_scalar", self._pads, self.rank, self.world, self._scalar_epoch, ptr(src), ptr(dst),
+                 self.peer_timeout_ms, ptr(status_word(self.device)), stream_ptr())
+
+    # ------------------------------------------------------------------ optimizer-step collectives
+    def reduce_scatter_grad(self, out_shard: torch.Tensor, norm_sq: torch.Tensor) -> torch.Tensor:
+        """``out_shard`` = sum over ranks of my slice of ``grads``; ``norm_sq`` = global |sum grad|^2."""
+        self.barrier()  # every rank's backward has finished writing its gradient buffer
+        lo = self.rank * self.shard
+        lib.call("b200_zero_reduce_scatter", self._grad_ptrs, self._mc_grads or None, self.rank, self.world, lo,
+                 self.shard, ptr(out_shard), ptr(self._local_sq), int(self.use_multimem), stream_ptr())
+        # also the point after which every rank has finished READING the peers' gradients
+        self.allreduce_scalar(self._local_sq, norm_sq)
+        return out_shard
+
+    def adamw_allgather(self, master, m, v, grad, global_offset: int, *, gscale, lr, beta1, beta2, eps, wd, step) -> None:
+        lib.call("b200_zero_adamw_allgather", ptr(master), ptr(m), ptr(v), ptr(grad), self._param_ptrs,
+                 self._mc_params or None, self.world, global_offset, master.numel(), ptr(gscale), lr, beta1, beta2, eps,
+                 wd, step, int(self.use_multimem), stream_ptr())
+
+    def finish_step(self) -> None:
+        self.barrier()

@@ -139,7 +139,7 @@ class ZeroOptimizer:
             fused.sumsq(gs, self._norm_sq)
         else:
             self._norm_sq.copy_(gs.double().pow(2).sum().float().reshape(1))
-        if self.world > 1:
+        if self.world > 1 and not fused_comm:
             dist.all_reduce(self._norm_sq, op=dist.ReduceOp.SUM, group=self.group)
         norm = self._norm_sq.sqrt() * grad_scale
         self.last_grad_norm = norm
