@@ -446,3 +446,49 @@ extern "C" int b200_accum_bf16_f32(const void* src, float* dst, long long n, voi
   axpy_bf16_to_f32_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(CBF(src), dst, n);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------ allocation-free RMSNorm backward
+// See no_alloc.h.  The per-CTA weight-gradient partials, which b200_rmsnorm_bwd takes from the
+// caller, live here in a fixed array that is part of the loaded module.
+namespace b200 {
+constexpr int NOALLOC_MAX_D = 8192;
+constexpr int NOALLOC_MAX_CTAS = 296;
+static __device__ __align__(256) float g_rmsnorm_bwd_partials[NOALLOC_MAX_CTAS * NOALLOC_MAX_D];
+// Device address of the array above, per device ordinal.  In host code the array's name is only
+// a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress.
+static float* g_partials_addr[64] = {nullptr};
+}  // namespace b200
+
+extern "C" int b200_rmsnorm_bwd_noalloc_max_d() { return b200::NOALLOC_MAX_D; }
+
+extern "C" int b200_rmsnorm_bwd_noalloc(const void* h, const void* w, const float* rstd, const void* dy,
+                                        const void* dres, void* dx, float* dw_out, int T, int D, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8 || D <= 0) return -1;
+  if (D > NOALLOC_MAX_D) {
+    fprintf(stderr, "b200_rmsnorm_bwd_noalloc: D=%d exceeds the built-in scratch (max D %d); use b200_rmsnorm_bwd\n", D,
+            NOALLOC_MAX_D);
+    return -3;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -4;
+  if (!g_partials_addr[dev]) {
+    // first call on this device (it is the current one): resolve the array and opt in to the
+    // kernel's dynamic shared memory.  Neither call allocates.
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_bwd_partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_partials_addr[dev] = p;
+  }
+  float* partials = g_partials_addr[dev];
+  const int ctas = b200_rmsnorm_bwd_ctas(T);  // <= NOALLOC_MAX_CTAS
+  // every CTA overwrites its whole [D] row of the partials, so nothing left by an earlier call is read
+  rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx),
+                                                                   partials, T, D);
+  if (dw_out) rmsnorm_dw_reduce_kernel<<<(D + 255) / 256, 256, 0, ST(stream)>>>(partials, dw_out, ctas, D);
+  return static_cast<int>(cudaGetLastError());
+}
