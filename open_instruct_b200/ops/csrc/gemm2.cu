@@ -1,0 +1,383 @@
+// bf16 GEMM for sm_100a on CTA PAIRS: tcgen05.mma.cta_group::2, 256x256 output tile per pair.
+//
+// Same contract as gemm.cu (C[M,N] (op)= A_op[M,K] * B_op[N,K]^T, K-major or MN-major operands,
+// bf16 / fp32 / fp32-accumulate epilogues).  Two CTAs of a cluster share one tile:
+//   * CTA r loads its own 128 rows of A and HALF of the B tile (128 of the 256 columns), so the
+//     shared-memory fill per k-block drops from 48 KB to 32 KB per SM for the same tensor work;
+//     that ratio, not the tensor pipe, is what limits the one-CTA kernel;
+//   * every TMA load of both CTAs reports its bytes to the LEADER CTA's full barrier
+//     (cp.async.bulk.tensor with .cta_group::2, no cluster broadcast form is used);
+//   * the leader's elected thread issues tcgen05.mma.cta_group::2 (M = 256 split over the two
+//     CTAs' tensor memories, N = 256) and commits completion to BOTH CTAs' barriers with two
+//     plain commits (one per CTA);
+//   * each CTA drains its own 128 x 256 fp32 accumulator; 2 accumulators per CTA (all 512 TMEM
+//     columns) so the epilogue of tile i overlaps the main loop of tile i+1.
+// 6 stages x 32 KB of shared memory per CTA.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace g2 {
+
+constexpr int BM = 128;        // rows per CTA (pair tile = 256)
+constexpr int BN = 256;        // pair tile columns
+constexpr int BNH = 128;       // B columns loaded by each CTA
+constexpr int BK = 64, UK = 16;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_BYTES = BNH * BK * 2;  // 16 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+
+enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// arrives on the barrier at shared::cluster address `bar` once all prior MMAs of this thread are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+struct Sched {
+  int num_m, num_n, total;  // in 256x256 pair tiles
+  __device__ __forceinline__ void get(int t, int& m_blk, int& n_blk) const {
+    constexpr int GROUP = 4;  // 4 x 256 rows per sweep of the column tiles
+    const int per_group = GROUP * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP;
+    const int gsz = min(num_m - first_m, GROUP);
+    const int r = t - g * per_group;
+    m_blk = first_m + r % gsz;
+    n_blk = r / gsz;
+  }
+};
+
+template <bool A_MN, bool B_MN, int OUT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+             void* __restrict__ Cout, int M, int N, int K, long long ldc, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                       // [STAGES]  used in the leader only
+  uint64_t* empty = bars + STAGES;             // [STAGES]  one per CTA
+  uint64_t* tfull = bars + 2 * STAGES;         // [2]       one per CTA
+  uint64_t* tempty = bars + 2 * STAGES + 2;    // [2]       used in the leader only (8 arrivals)
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  Sched sched;
+  sched.num_m = (M + 2 * BM - 1) / (2 * BM);
+  sched.num_n = (N + BN - 1) / BN;
+  sched.total = sched.num_m * sched.num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_ptr, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync();  // both CTAs' barriers are initialised before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      prefetch_tensormap(&tma_a);
+      prefetch_tensormap(&tma_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = pair; t < sched.total && ok; t += num_pairs) {
+        int m_blk, n_blk;
+        sched.get(t, m_blk, n_blk);
+        const int m0 = m_blk * 2 * BM + cta * BM;   // my rows of A / C
+        const int n0 = n_blk * BN + cta * BNH;      // my half of the B tile
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
+            atomicCAS(status, 0, ST_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          const uint32_t leader_full = mapa(smem_u32(&full[s]), 0);
+          if (cta == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_BYTES;
+          uint8_t* b_dst = sB + s * B_BYTES;
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d_pair(a_dst, &tma_a, leader_full, k0, m0);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BM / 64; ++b) tma_load_2d_pair(a_dst + b * (BK * 128), &tma_a, leader_full, m0 + b * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(b_dst, &tma_b, leader_full, k0, n0);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BNH / 64; ++b) tma_load_2d_pair(b_dst + b * (BK * 128), &tma_b, leader_full, n0 + b * 64, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (cta == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int t = pair; t < sched.total && ok; t += num_pairs, ++tile_i) {
+        const uint32_t acc = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag)) {
+          atomicCAS(status, 0, ST_TIMEOUT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag)) {
+            atomicCAS(status, 0, ST_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t ad = A_MN ? umma_desc_sw128(a_addr + k * (UK * 128), BK * 128, 1024)
+                                     : umma_desc_sw128(a_addr + k * (UK * 2), 16, 1024);
+            const uint64_t bd = B_MN ? umma_desc_sw128(b_addr + k * (UK * 128), BK * 128, 1024)
+                                     : umma_desc_sw128(b_addr + k * (UK * 2), 16, 1024);
+            umma_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // release this stage in both CTAs once the MMAs above have read it
+          umma_commit_pair(mapa(smem_u32(&empty[s]), 0));
+          umma_commit_pair(mapa(smem_u32(&empty[s]), 1));
+        }
+        if (ok) {
+          umma_commit_pair(mapa(smem_u32(&tfull[acc]), 0));
+          umma_commit_pair(mapa(smem_u32(&tfull[acc]), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int lane_grp = warp & 3;
+    uint32_t tile_i = 0;
+    for (int t = pair; t < sched.total; t += num_pairs, ++tile_i) {
+      int m_blk, n_blk;
+      sched.get(t, m_blk, n_blk);
+      const uint32_t acc = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      const bool ready = __all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag));
+      if (!ready) {
+        if (lane == 0) atomicCAS(status, 0, ST_TIMEOUT_TMEM_FULL);
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * 2 * BM + cta * BM + lane_grp * 32 + lane;
+      const int n0 = n_blk * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col = n0 + c * 32;
+        if (col >= N) break;
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row < M) {
+          if (OUT == OUT_BF16) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<long long>(row) * ldc + col;
+            if (col + 32 <= N) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                reinterpret_cast<uint4*>(crow)[j] = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < N; ++j) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          } else {
+            float* crow = reinterpret_cast<float*>(Cout) + static_cast<long long>(row) * ldc + col;
+            if (col + 32 <= N) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                if (OUT == OUT_F32_ACC) {
+                  const float4 o = reinterpret_cast<float4*>(crow)[j];
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                reinterpret_cast<float4*>(crow)[j] = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < N; ++j) {
+                float v = __uint_as_float(r[j]);
+                if (OUT == OUT_F32_ACC) v += crow[j];
+                crow[j] = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty[acc]), 0));  // leader counts 4 warps x 2 CTAs
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {
+    }
+  }
+  cluster_sync();  // neither CTA leaves while its partner may still signal into it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+static int max_pairs_cache = 0;
+
+template <bool A_MN, bool B_MN, int OUT>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc,
+                  int* status, cudaStream_t stream, int max_ctas) {
+  auto kern = gemm2_kernel<A_MN, B_MN, OUT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (!max_pairs_cache) {
+    int n = 0;
+    cfg.gridDim = dim3(148);
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = 64;
+    max_pairs_cache = n;
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  int pairs = tiles < max_pairs_cache ? tiles : max_pairs_cache;
+  if (max_ctas > 1 && pairs > max_ctas / 2) pairs = max_ctas / 2;
+  cfg.gridDim = dim3(2 * pairs);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, status);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+}  // namespace g2
+}  // namespace b200
+
+// Same arguments as b200_gemm_bf16 (see gemm.cu); runs the CTA-pair kernel.
+extern "C" int b200_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                               long long ldc, int a_mn, int b_mn, int out_mode, int* status, void* stream,
+                               int max_ctas) {
+  using namespace b200;
+  using namespace b200::g2;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2, true);
+  else r = make_tmap_2d(&ta, A, K, M, lda, BK, 64, 2, true);
+  if (r) return 10000 + r;
+  if (!b_mn) r = make_tmap_2d(&tb, B, N, K, ldb, BNH, BK, 2, true);
+  else r = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2, true);
+  if (r) return 20000 + r;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define B200_DISPATCH2(AM, BMN)                                                                              \
+  switch (out_mode) {                                                                                         \
+    case 0: return g2::launch<AM, BMN, g2::OUT_BF16>(ta, tb, C, M, N, K, ldc, status, st, max_ctas);          \
+    case 1: return g2::launch<AM, BMN, g2::OUT_F32>(ta, tb, C, M, N, K, ldc, status, st, max_ctas);           \
+    case 2: return g2::launch<AM, BMN, g2::OUT_F32_ACC>(ta, tb, C, M, N, K, ldc, status, st, max_ctas);       \
+    default: return -2;                                                                                       \
+  }
+  if (!a_mn && !b_mn) { B200_DISPATCH2(false, false) }
+  if (!a_mn && b_mn) { B200_DISPATCH2(false, true) }
+  if (a_mn && !b_mn) { B200_DISPATCH2(true, false) }
+  B200_DISPATCH2(true, true)
+#undef B200_DISPATCH2
+}

@@ -12,7 +12,11 @@ import torch
 from . import lib
 from .lib import call, ptr, status_word, stream_ptr
 
+import os
+
 OUT_BF16, OUT_F32, OUT_F32_ACC = 0, 1, 2
+# "2cta": tcgen05 cta_group::2 kernel on CTA pairs (256x256 tiles); "1cta": one CTA per 128x256 tile
+GEMM_IMPL = os.environ.get("B200_GEMM_IMPL", "2cta")
 
 
 def _check(t: torch.Tensor, dtype, name: str):
@@ -23,7 +27,7 @@ def _check(t: torch.Tensor, dtype, name: str):
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a_mn: bool = False,
-         b_mn: bool = False, out_mode: int = OUT_BF16, max_ctas: int = 0) -> torch.Tensor:
+         b_mn: bool = False, out_mode: int = OUT_BF16, max_ctas: int = 0, impl: str | None = None) -> torch.Tensor:
     """C[M,N] (op)= A_op[M,K] @ B_op[N,K]^T on the tcgen05 kernel.
 
     ``a_mn=False``: ``a`` is [M,K]; ``a_mn=True``: ``a`` is [K,M] (used transposed, no copy).
@@ -60,7 +64,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a
     ldc = out.stride(0)
     if ldc % 8 and N >= 8:
         raise ValueError("gemm output row stride must be a multiple of 8 elements")
-    call("b200_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), out_mode,
+    impl = impl or GEMM_IMPL
+    call("b200_gemm2_bf16" if impl == "2cta" else "b200_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, lda, ldb, ldc,
+         int(a_mn), int(b_mn), out_mode,
          ptr(status_word(a.device)), stream_ptr(), max_ctas)
     return out
 

@@ -1,0 +1,141 @@
+"""Per-kernel timing at Llama-3.1-8B layer shapes (CUDA events, L2 flushed between iterations).
+
+    python -m open_instruct_b200.utils.kernel_bench [--tokens 4096] [--only gemm,attn,...] [--json out.json]
+
+Reports achieved TFLOP/s or GB/s per kernel and the fraction of the measured peaks found in
+``MEASURED_PEAKS.json`` at the repository root (copy bandwidth and cuBLAS bf16 GEMM throughput).
+With ``--cublas`` the same GEMM shapes are also timed through ``torch.matmul`` for comparison.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush_buf = None
+
+
+def _flush_l2():
+    global _flush_buf
+    if _flush_buf is None:
+        _flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush_buf.zero_()
+
+
+def time_op(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        _flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--only", default="")
+    ap.add_argument("--cublas", action="store_true")
+    ap.add_argument("--json", default="")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--impl", default=None, help="GEMM kernel: 1cta | 2cta (default: library default)")
+    ap.add_argument("--doc_len", type=int, default=0, help="attention: document length (0 = one document of --tokens)")
+    args = ap.parse_args()
+    from open_instruct_b200.ops import fused, lib
+
+    hbm, tf, src = _peaks()
+    T, D, F, V, Hq, Hkv, Dh = args.tokens, 4096, 14336, 128256, 32, 8, 128
+    only = set(filter(None, args.only.split(",")))
+    rows = []
+
+    def rec(name, ms, flops=None, bytes_=None):
+        r = {"kernel": name, "ms": round(ms, 4)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["frac_of_peak"] = round(flops / ms / 1e9 / tf, 3)
+        if bytes_:
+            r["gbs"] = round(bytes_ / ms / 1e6, 1)
+            r["frac_of_peak"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        rows.append(r)
+        print(r, flush=True)
+
+    bf = lambda *s: torch.randn(*s, device="cuda").bfloat16()
+    if not only or "gemm" in only:
+        shapes = {"qkv": (T, (Hq + 2 * Hkv) * Dh, D), "o": (T, D, Hq * Dh), "gate_up": (T, 2 * F, D), "down": (T, D, F),
+                  "lm_head": (T, V, D)}
+        for name, (M, N, K) in shapes.items():
+            x, w, dy = bf(M, K), bf(N, K), bf(M, N)
+            fl = 2.0 * M * N * K
+            rec(f"gemm_fwd_{name}", time_op(lambda: fused.gemm(x, w, impl=args.impl), args.iters), fl)
+            rec(f"gemm_dgrad_{name}", time_op(lambda: fused.gemm(dy, w, b_mn=True, impl=args.impl), args.iters), fl)
+            g = torch.zeros(N, K, device="cuda")
+            rec(f"gemm_wgrad_{name}", time_op(lambda: fused.gemm(dy, x, g, a_mn=True, b_mn=True, out_mode=fused.OUT_F32_ACC, impl=args.impl), args.iters), fl)
+            if args.cublas:
+                rec(f"cublas_fwd_{name}", time_op(lambda: torch.matmul(x, w.t()), args.iters), fl)
+                rec(f"cublas_dgrad_{name}", time_op(lambda: torch.matmul(dy, w), args.iters), fl)
+                rec(f"cublas_wgrad_{name}", time_op(lambda: torch.matmul(dy.t(), x), args.iters), fl)
+            del x, w, dy, g
+    if not only or "attn" in only:
+        L = args.doc_len or T
+        lens = [L] * (T // L) + ([T % L] if T % L else [])
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+        qkv = bf(T, (Hq + 2 * Hkv) * Dh)
+        scale = Dh ** -0.5
+        out, lse = fused.attn_fwd(qkv, cu, Hq, Hkv, Dh, scale)
+        d_out = bf(T, Hq * Dh)
+        fl = sum(4.0 * l * l * Dh * Hq / 2 for l in lens)  # causal: half of the full score matrix
+        rec(f"attn_fwd_L{L}", time_op(lambda: fused.attn_fwd(qkv, cu, Hq, Hkv, Dh, scale), args.iters), fl)
+        rec(f"attn_bwd_L{L}", time_op(lambda: fused.attn_bwd(qkv, out, d_out, lse, cu, Hq, Hkv, Dh, scale), args.iters), 2.5 * fl)
+    if not only or "elementwise" in only:
+        x, r, w = bf(T, D), bf(T, D), bf(D)
+        rec("rmsnorm_fwd_res", time_op(lambda: fused.rmsnorm_fwd(x, w, 1e-5, res=r), args.iters), bytes_=T * D * 2 * 4)
+        y, h, rstd = fused.rmsnorm_fwd(x, w, 1e-5, res=r)
+        dw = torch.zeros(D, device="cuda")
+        rec("rmsnorm_bwd", time_op(lambda: fused.rmsnorm_bwd(h, w, rstd, y, r, dw), args.iters), bytes_=T * D * 2 * 4)
+        gu = bf(T, 2 * F)
+        rec("swiglu_fwd", time_op(lambda: fused.swiglu_fwd(gu), args.iters), bytes_=T * F * 2 * 3)
+        da = bf(T, F)
+        rec("swiglu_bwd", time_op(lambda: fused.swiglu_bwd_(gu, da), args.iters), bytes_=T * F * 2 * 5)
+        qkv = bf(T, (Hq + 2 * Hkv) * Dh)
+        pos = torch.arange(T, device="cuda", dtype=torch.int32)
+        inv = torch.rand(Dh // 2, device="cuda")
+        rec("rope", time_op(lambda: fused.rope_(qkv, pos, inv, Hq, Hkv, Dh), args.iters), bytes_=T * (Hq + Hkv) * Dh * 2 * 2)
+        logits = bf(T, V)
+        labels = torch.randint(0, V, (T,), device="cuda")
+        rec("logprob_fwd", time_op(lambda: fused.logprob_fwd(logits, labels), args.iters), bytes_=T * V * 2)
+        lp, lse, _ = fused.logprob_fwd(logits, labels)
+        g = torch.ones(T, device="cuda")
+        rec("logprob_bwd", time_op(lambda: fused.logprob_bwd_(logits, labels, lse, g), args.iters), bytes_=T * V * 2 * 2)
+        n = 1 << 28
+        ma, m_, v_, gr = (torch.zeros(n, device="cuda") for _ in range(4))
+        p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        rec("adamw", time_op(lambda: fused.adamw(ma, m_, v_, gr, p16, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, step=1), args.iters),
+            bytes_=n * (4 * 4 + 3 * 4 + 2 + 4))
+    lib.check_status()
+    if args.json:
+        json.dump({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}, "tokens": T, "rows": rows}, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -20,9 +20,10 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+@pytest.mark.parametrize("impl", ["1cta", "2cta"])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
-@pytest.mark.parametrize("shape", [(256, 512, 128), (384, 320, 192), (1000, 136, 72), (4096, 1024, 4096)])
-def test_gemm_layouts(a_mn, b_mn, shape):
+@pytest.mark.parametrize("shape", [(256, 512, 128), (384, 320, 192), (1000, 136, 72), (4096, 1024, 4096), (2048, 6144, 4096)])
+def test_gemm_layouts(a_mn, b_mn, shape, impl):
     from open_instruct_b200.ops import fused
 
     M, N, K = shape
@@ -32,12 +33,12 @@ def test_gemm_layouts(a_mn, b_mn, shape):
     ref = a.float() @ b.float().t()
     a_in = a.t().contiguous() if a_mn else a
     b_in = b.t().contiguous() if b_mn else b
-    out = fused.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    out = fused.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn, impl=impl)
     assert _rel(out, ref) < 5e-3
-    out32 = fused.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32)
+    out32 = fused.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32, impl=impl)
     assert _rel(out32, ref) < 1e-4
     acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
-    fused.gemm(a_in, b_in, acc, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32_ACC)
+    fused.gemm(a_in, b_in, acc, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32_ACC, impl=impl)
     assert _rel(acc, ref + 1) < 1e-4
 
 
