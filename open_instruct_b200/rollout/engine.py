@@ -1,0 +1,444 @@
+"""Rollout engine: continuous batching over a paged KV cache, in process (no HTTP hop).
+
+Stands where the reference wraps vLLM (``open_instruct/vllm_utils.py:553-843``, ``:1188-1313``): requests
+arrive as token ids with a sampling config, ``n`` samples per prompt share the prompt's KV blocks,
+every generated token comes back with its log-prob under the *processed* distribution
+(temperature / top-p applied - the reference asks vLLM for ``logprobs_mode="processed_logprobs"``,
+``vllm_utils.py:1284``), finished requests carry finish reasons and token statistics.
+
+Scheduling and block management are native (``ops/csrc/host/host_runtime.cpp``); the model math runs
+on this package's kernels: packed varlen attention for prefill, ``b200_paged_decode`` for decode
+steps, ``b200_kv_write`` to fill cache blocks, ``b200_sample`` (Philox Gumbel-max) for sampling.
+``ops="ref"`` keeps everything in PyTorch (CPU-testable; same cache layout and scheduler).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from ..data_types import GenerationResult, RequestInfo, SamplingConfig, TokenStatistics
+from ..models import LlamaModel, ModelSpec
+from ..ops import lib, ref
+
+KV_BLOCK = 64
+
+
+class _Host:
+    """ctypes view of the native scheduler / block manager."""
+
+    def __init__(self, num_blocks: int, max_running: int):
+        h = lib.load_host()
+        i64, i32, p = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+        h.b200_engine_create.restype = p
+        h.b200_engine_create.argtypes = [i32, i32, i32]
+        h.b200_engine_destroy.argtypes = [p]
+        h.b200_engine_add.argtypes = [p, i64, i64, i32, i32]
+        h.b200_engine_finish.argtypes = [p, i64]
+        h.b200_engine_advance.argtypes = [p, i64, i32]
+        h.b200_engine_free_blocks.argtypes = [p]
+        h.b200_engine_preemptions.argtypes = [p]
+        h.b200_engine_preemptions.restype = i64
+        PI64, PI32 = ctypes.POINTER(i64), ctypes.POINTER(i32)
+        h.b200_engine_schedule.argtypes = [p, PI64, PI32, PI64, PI32, PI64, PI32, i32]
+        h.b200_engine_blocks.argtypes = [p, i64, PI32, i32, PI32]
+        h.b200_engine_counts.argtypes = [p, PI32, PI32]
+        self.h = h
+        self.e = h.b200_engine_create(num_blocks, KV_BLOCK, max_running)
+        self.cap = max(1024, max_running * 2)
+        self._pre = (i64 * self.cap)()
+        self._dec = (i64 * self.cap)()
+        self._pmt = (i64 * self.cap)()
+        self._blk = (i32 * 65536)()
+
+    def add(self, sid, group, prompt_len, max_len):
+        rc = self.h.b200_engine_add(self.e, sid, group, prompt_len, max_len)
+        if rc:
+            raise ValueError(f"cannot queue sequence {sid} (code {rc}): prompt+response does not fit the KV cache")
+
+    def schedule(self):
+        a, b, c = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+        self.h.b200_engine_schedule(self.e, self._pre, ctypes.byref(a), self._dec, ctypes.byref(b), self._pmt, ctypes.byref(c), self.cap)
+        return list(self._pre[: a.value]), list(self._dec[: b.value]), list(self._pmt[: c.value])
+
+    def blocks(self, sid):
+        shared = ctypes.c_int(0)
+        n = self.h.b200_engine_blocks(self.e, sid, self._blk, 65536, ctypes.byref(shared))
+        return list(self._blk[:n]), shared.value
+
+    def advance(self, sid, n=1):
+        return self.h.b200_engine_advance(self.e, sid, n)
+
+    def finish(self, sid):
+        self.h.b200_engine_finish(self.e, sid)
+
+    def free_blocks(self):
+        return self.h.b200_engine_free_blocks(self.e)
+
+    def counts(self):
+        w, r = ctypes.c_int(0), ctypes.c_int(0)
+        self.h.b200_engine_counts(self.e, ctypes.byref(w), ctypes.byref(r))
+        return w.value, r.value
+
+    def preemptions(self):
+        return int(self.h.b200_engine_preemptions(self.e))
+
+    def __del__(self):
+        try:
+            self.h.b200_engine_destroy(self.e)
+        except Exception:  # noqa: BLE001
+            pass
+
+
+@dataclass
+class _Sequence:
+    sid: int
+    request: "_Request"
+    sample_idx: int
+    tokens: list[int]  # prompt + generated
+    prompt_len: int
+    logprobs: list[float] = field(default_factory=list)
+    finish_reason: str | None = None
+    seed: int = 0
+    last_token: int = 0
+
+
+@dataclass
+class _Request:
+    rid: int
+    prompt: list[int]
+    sampling: SamplingConfig
+    meta: dict
+    seqs: list[_Sequence] = field(default_factory=list)
+    start_time: float = 0.0
+    done: int = 0
+
+
+class RolloutEngine:
+    """One engine = one GPU (or CPU with ``ops='ref'``) holding a bf16 copy of the weights."""
+
+    def __init__(self, spec: ModelSpec, device="cuda", ops: str = "auto", num_blocks: int | None = None,
+                 gpu_memory_utilization: float = 0.85, max_running: int = 256, max_model_len: int = 8192, seed: int = 0,
+                 flat: torch.Tensor | None = None, eos_token_ids: list[int] | None = None, tokenizer=None):
+        self.spec = spec
+        self.device = torch.device(device)
+        if ops == "auto":
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and lib.available()) else "ref"
+        self.ops = ops
+        dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, seed=seed, flat=flat)
+        if ops == "ref":
+            self.model.flat.requires_grad_(False)
+        self.dtype = dtype
+        self.max_model_len = max_model_len
+        self.tokenizer = tokenizer
+        self.eos = set(eos_token_ids if eos_token_ids is not None else ([spec.eos_token_id] if spec.eos_token_id is not None else []))
+        per_block = 2 * spec.num_layers * spec.num_kv_heads * KV_BLOCK * spec.head_dim * (2 if dtype == torch.bfloat16 else 4)
+        if num_blocks is None:
+            if self.device.type == "cuda":
+                free, total = torch.cuda.mem_get_info(self.device)
+                num_blocks = max(16, int((free - (1 - gpu_memory_utilization) * total) // per_block))
+            else:
+                num_blocks = 256
+        self.num_blocks = num_blocks
+        shape = (spec.num_layers, num_blocks, spec.num_kv_heads, KV_BLOCK, spec.head_dim)
+        self.k_cache = torch.zeros(shape, dtype=dtype, device=self.device)
+        self.v_cache = torch.zeros(shape, dtype=dtype, device=self.device)
+        self.host = _Host(num_blocks, max_running)
+        self.max_running = max_running
+        self._next_sid = 0
+        self._next_rid = 0
+        self.seqs: dict[int, _Sequence] = {}
+        self.requests: dict[int, _Request] = {}
+        self.base_seed = seed
+        self.model_step = 0
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
+
+    # ------------------------------------------------------------------ public API
+    def kv_cache_max_concurrency(self, seq_len: int) -> int:
+        """How many sequences of ``seq_len`` tokens fit at once (cf. ``get_kv_cache_info``, ``vllm_utils.py:826-843``)."""
+        return self.num_blocks // max(1, -(-seq_len // KV_BLOCK))
+
+    def add_request(self, prompt: list[int], sampling: SamplingConfig, **meta) -> int:
+        rid = self._next_rid
+        self._next_rid += 1
+        if len(prompt) + sampling.max_tokens > self.max_model_len:
+            raise ValueError(f"prompt ({len(prompt)}) + max_tokens ({sampling.max_tokens}) exceeds max_model_len {self.max_model_len}")
+        req = _Request(rid, list(prompt), sampling, meta, start_time=time.perf_counter())
+        base = sampling.seed if sampling.seed is not None else self.base_seed * 1000003 + rid
+        for j in range(sampling.n):
+            sid = self._next_sid
+            self._next_sid += 1
+            seq = _Sequence(sid, req, j, list(prompt), len(prompt), seed=base + j)
+            req.seqs.append(seq)
+            self.seqs[sid] = seq
+            self.host.add(sid, rid, len(prompt), len(prompt) + sampling.max_tokens)
+        self.requests[rid] = req
+        return rid
+
+    def has_unfinished(self) -> bool:
+        return bool(self.requests)
+
+    def num_active(self) -> int:
+        w, r = self.host.counts()
+        return w + r
+
+    def update_weights(self, flat: torch.Tensor, model_step: int | None = None) -> None:
+        """Replace the weights (same flat layout) between steps; cached KV of running sequences stays."""
+        with torch.no_grad():
+            self.model.flat[: flat.numel()].copy_(flat.to(self.model.flat.dtype), non_blocking=True)
+        if model_step is not None:
+            self.model_step = model_step
+
+    @torch.no_grad()
+    def step(self) -> list[GenerationResult]:
+        """One scheduling + model step.  Returns the requests that completed in it."""
+        prefill_ids, decode_ids, preempted = self.host.schedule()
+        for sid in preempted:  # recompute later from prompt + generated-so-far
+            pass
+        finished: list[GenerationResult] = []
+        if decode_ids:
+            self._decode([self.seqs[s] for s in decode_ids])
+        if prefill_ids:
+            self._prefill([self.seqs[s] for s in prefill_ids])
+        self.stats["steps"] += 1
+        for sid in list(decode_ids) + list(prefill_ids):
+            seq = self.seqs.get(sid)
+            if seq is None or seq.finish_reason is None:
+                continue
+            self.host.finish(sid)
+            del self.seqs[sid]
+            req = seq.request
+            req.done += 1
+            if req.done == len(req.seqs):
+                finished.append(self._finalize(req))
+                del self.requests[req.rid]
+        return finished
+
+    def generate(self, prompts: list[list[int]], sampling: SamplingConfig) -> list[GenerationResult]:
+        rids = [self.add_request(p, sampling) for p in prompts]
+        out: dict[int, GenerationResult] = {}
+        while self.has_unfinished():
+            for res in self.step():
+                out[res.index] = res
+        return [out[r] for r in rids]
+
+    # ------------------------------------------------------------------ bookkeeping
+    def _finalize(self, req: _Request) -> GenerationResult:
+        responses = [s.tokens[s.prompt_len:] for s in req.seqs]
+        now = time.perf_counter()
+        n = len(req.seqs)
+        info = RequestInfo(num_calls=[0] * n, timeouts=[0] * n, tool_errors=[""] * n, tool_outputs=[""] * n,
+                           tool_runtimes=[0.0] * n, tool_calleds=[False] * n, rollout_states=[{} for _ in range(n)])
+        return GenerationResult(
+            responses=responses, finish_reasons=[s.finish_reason for s in req.seqs], masks=[[1] * len(r) for r in responses],
+            request_info=info, index=req.rid, prompt_id=req.meta.get("prompt_id"), epoch_number=req.meta.get("epoch_number"),
+            token_statistics=TokenStatistics(len(req.prompt), sum(len(r) for r in responses), now - req.start_time, req.start_time),
+            start_time=req.start_time, logprobs=[s.logprobs for s in req.seqs], model_step=self.model_step,
+            is_eval=req.meta.get("is_eval", False), queries=[list(req.prompt)] * n, ground_truth=req.meta.get("ground_truth"),
+            dataset=req.meta.get("dataset"), raw_query=req.meta.get("raw_query"))
+
+    def _accept(self, seq: _Sequence, token: int, logprob: float) -> None:
+        seq.tokens.append(token)
+        seq.logprobs.append(logprob)
+        seq.last_token = token
+        self.host.advance(seq.sid, 1)
+        sp = seq.request.sampling
+        n_gen = len(seq.tokens) - seq.prompt_len
+        if token in self.eos and n_gen >= sp.min_tokens:
+            seq.finish_reason = "stop"
+        elif sp.stop and self.tokenizer is not None and n_gen >= sp.min_tokens:
+            tail = self.tokenizer.decode(seq.tokens[max(seq.prompt_len, len(seq.tokens) - 16):])
+            if any(s in tail for s in sp.stop):
+                seq.finish_reason = "stop"
+        if seq.finish_reason is None and n_gen >= sp.max_tokens:
+            seq.finish_reason = "length"
+
+    def _sampling_tensors(self, seqs: list[_Sequence]):
+        dev = self.device
+        temp = torch.tensor([s.request.sampling.temperature for s in seqs], dtype=torch.float32, device=dev)
+        top_p = torch.tensor([s.request.sampling.top_p for s in seqs], dtype=torch.float32, device=dev)
+        seeds = torch.tensor([s.seed for s in seqs], dtype=torch.int64, device=dev)
+        ctr = torch.tensor([len(s.tokens) - s.prompt_len for s in seqs], dtype=torch.int32, device=dev)
+        return temp, top_p, seeds, ctr
+
+    def _sample(self, logits: torch.Tensor, seqs: list[_Sequence]):
+        temp, top_p, seeds, ctr = self._sampling_tensors(seqs)
+        if self.ops == "fused":
+            from ..ops.lib import call, ptr, stream_ptr
+
+            B, V = logits.shape
+            toks = torch.empty(B, dtype=torch.int64, device=self.device)
+            lps = torch.empty(B, dtype=torch.float32, device=self.device)
+            call("b200_sample", ptr(logits), logits.stride(0), B, V, ptr(temp), ptr(top_p), ptr(seeds), ptr(ctr), ptr(toks), ptr(lps), stream_ptr())
+            return toks.tolist(), lps.tolist()
+        from .sampler import sample_ref
+
+        return sample_ref(logits, temp, top_p, seeds, ctr)
+
+    # ------------------------------------------------------------------ model math
+    def _slots_for(self, seq: _Sequence, start: int, end: int) -> list[int]:
+        blocks, _ = self.host.blocks(seq.sid)
+        return [blocks[t // KV_BLOCK] * KV_BLOCK + t % KV_BLOCK for t in range(start, end)]
+
+    def _layer_stack(self, ids: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, attn_fn) -> torch.Tensor:
+        """Embedding -> decoder layers -> final norm for a flat batch of tokens.  ``slots`` may hold
+        several destination maps back to back (length a multiple of the token count)."""
+        s, p = self.spec, self.model.p
+        T = ids.numel()
+        if self.ops == "fused":
+            from ..ops import fused as f
+            from ..ops.lib import call, ptr, stream_ptr
+
+            pos32 = pos.to(torch.int32)
+            impl = "2cta" if T > 128 else "1cta"
+            stream, delta = f.embedding_fwd(p["embed"], ids), None
+            for i in range(s.num_layers):
+                n1, h_in, _ = f.rmsnorm_fwd(delta if delta is not None else stream, p[f"l{i}.attn_norm"], s.rms_norm_eps,
+                                            res=stream if delta is not None else None)
+                qkv = f.gemm(n1, p[f"l{i}.wqkv"], impl=impl)
+                f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+                call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
+                     s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
+                attn = attn_fn(i, qkv)
+                o = f.gemm(attn, p[f"l{i}.wo"], impl=impl)
+                n2, h_mid, _ = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=h_in)
+                act = f.swiglu_fwd(f.gemm(n2, p[f"l{i}.w_gate_up"], impl=impl))
+                delta = f.gemm(act, p[f"l{i}.w_down"], impl=impl)
+                stream = h_mid
+            nf, _, _ = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
+            return nf
+        x = p["embed"][ids]
+        for i in range(s.num_layers):
+            n1 = ref.rmsnorm(x, p[f"l{i}.attn_norm"], s.rms_norm_eps)
+            qkv = ref.rope(ref.linear(n1, p[f"l{i}.wqkv"]), pos, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            heads = qkv.view(T, s.num_heads + 2 * s.num_kv_heads, s.head_dim)
+            k_new, v_new = heads[:, s.num_heads : s.num_heads + s.num_kv_heads], heads[:, s.num_heads + s.num_kv_heads :]
+            for rep in range(slots.numel() // T):
+                sl = slots[rep * T : (rep + 1) * T]
+                ok = sl >= 0
+                blk, off = sl[ok] // KV_BLOCK, sl[ok] % KV_BLOCK
+                self.k_cache[i][blk, :, off] = k_new[ok]
+                self.v_cache[i][blk, :, off] = v_new[ok]
+            attn = attn_fn(i, qkv)
+            x = x + ref.linear(attn, p[f"l{i}.wo"])
+            n2 = ref.rmsnorm(x, p[f"l{i}.mlp_norm"], s.rms_norm_eps)
+            x = x + ref.linear(ref.swiglu(ref.linear(n2, p[f"l{i}.w_gate_up"])), p[f"l{i}.w_down"])
+        return ref.rmsnorm(x, p["final_norm"], s.rms_norm_eps)
+
+    def _logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        w = self.model.lm_head_weight()
+        if self.ops == "fused":
+            from ..ops import fused as f
+
+            return f.gemm(hidden.contiguous(), w, impl="2cta" if hidden.shape[0] > 128 else "1cta")
+        return ref.linear(hidden, w)
+
+    def _prefill(self, seqs: list[_Sequence]) -> None:
+        """Prompt pass for newly admitted sequences.  Samples of one request that start from the same
+        tokens run through the model ONCE; the others reuse the result (their private tail block gets
+        its own copy of the K/V rows, their first token is sampled from the same logits row)."""
+        s = self.spec
+        groups: dict[tuple, list[_Sequence]] = {}
+        for q in seqs:
+            groups.setdefault((q.request.rid, len(q.tokens), len(q.tokens) == q.prompt_len), []).append(q)
+        reps, members = [], []
+        for (rid, n, fresh), qs in groups.items():
+            if fresh:
+                reps.append(qs[0])
+                members.append(qs)
+            else:  # resumed after preemption: each has its own history
+                for q in qs:
+                    reps.append(q)
+                    members.append([q])
+        ids = torch.tensor([t for q in reps for t in q.tokens], dtype=torch.long)
+        lens = [len(q.tokens) for q in reps]
+        T = int(ids.numel())
+        pos = torch.cat([torch.arange(n) for n in lens])
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        n_var = max(len(m) for m in members)
+        slot_rows = []
+        for v in range(n_var):
+            row = []
+            for q, ms, n in zip(reps, members, lens):
+                if v < len(ms):
+                    full = (ms[v].prompt_len // KV_BLOCK) * KV_BLOCK if (v > 0) else 0
+                    sl = self._slots_for(ms[v], 0, n)
+                    row += [-1] * min(full, n) + sl[min(full, n):]  # shared full blocks were written by variant 0
+                else:
+                    row += [-1] * n
+            slot_rows.append(row)
+        dev = self.device
+        ids_d, pos_d, cu_d = ids.to(dev), pos.to(dev), cu.to(dev)
+        slots = torch.tensor([x for r in slot_rows for x in r], dtype=torch.long, device=dev)
+        scale = s.head_dim ** -0.5
+        if self.ops == "fused":
+            from ..ops import fused as f
+
+            attn_fn = lambda i, qkv: f.attn_fwd(qkv, cu_d, s.num_heads, s.num_kv_heads, s.head_dim, scale)[0]
+        else:
+            attn_fn = lambda i, qkv: ref.attention_varlen(qkv, cu_d, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+        hidden = self._layer_stack(ids_d, pos_d, slots, attn_fn)
+        last = cu_d[1:].long() - 1
+        logits = self._logits(hidden[last])
+        self.stats["prefill_tokens"] += T
+        flat_members = [m for ms in members for m in ms]
+        rows = torch.tensor([ri for ri, ms in enumerate(members) for _ in ms], device=dev)
+        toks, lps = self._sample(logits[rows].contiguous(), flat_members)
+        for q, t, lp in zip(flat_members, toks, lps):
+            self._accept(q, int(t), float(lp))
+
+    def _decode(self, seqs: list[_Sequence]) -> None:
+        """One token for every running sequence."""
+        s = self.spec
+        dev = self.device
+        B = len(seqs)
+        ids = torch.tensor([q.last_token for q in seqs], dtype=torch.long, device=dev)
+        ctx_list = [len(q.tokens) for q in seqs]  # the new token sits at position len-1
+        pos = torch.tensor([n - 1 for n in ctx_list], dtype=torch.long, device=dev)
+        tables = [self.host.blocks(q.sid)[0] for q in seqs]
+        max_blocks = max(len(t) for t in tables)
+        bt = torch.zeros(B, max_blocks, dtype=torch.int32)
+        for i, t in enumerate(tables):
+            bt[i, : len(t)] = torch.tensor(t, dtype=torch.int32)
+        bt = bt.to(dev)
+        slots = torch.tensor([tables[i][(n - 1) // KV_BLOCK] * KV_BLOCK + (n - 1) % KV_BLOCK for i, n in enumerate(ctx_list)],
+                             dtype=torch.long, device=dev)
+        ctx = torch.tensor(ctx_list, dtype=torch.int32, device=dev)
+        scale = s.head_dim ** -0.5
+        if self.ops == "fused":
+            from ..ops.lib import call, ptr, stream_ptr
+
+            max_ctx = max(ctx_list)
+            splits = 1 if B * s.num_kv_heads >= 148 else max(1, min(8, (148 // max(1, B * s.num_kv_heads)), -(-max_ctx // (4 * KV_BLOCK))))
+            part_o = torch.empty(B * s.num_heads * splits * s.head_dim, dtype=torch.float32, device=dev) if splits > 1 else None
+            part_ml = torch.empty(B * s.num_heads * splits * 2, dtype=torch.float32, device=dev) if splits > 1 else None
+
+            def attn_fn(i, qkv):
+                out = torch.empty(B, s.num_heads * s.head_dim, dtype=qkv.dtype, device=dev)
+                call("b200_paged_decode", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(bt), max_blocks, ptr(ctx), B,
+                     s.num_heads, s.num_kv_heads, s.head_dim, scale, splits, ptr(out), ptr(part_o), ptr(part_ml), stream_ptr())
+                return out
+        else:
+            g = s.num_heads // s.num_kv_heads
+
+            def attn_fn(i, qkv):
+                q = qkv.view(B, s.num_heads + 2 * s.num_kv_heads, s.head_dim)[:, : s.num_heads].float()
+                outs = []
+                for b in range(B):
+                    blk = bt[b, : -(-ctx_list[b] // KV_BLOCK)].long()
+                    k = self.k_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, : ctx_list[b]].float()
+                    v = self.v_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, : ctx_list[b]].float()
+                    k, v = k.repeat_interleave(g, 0), v.repeat_interleave(g, 0)
+                    p = torch.softmax((q[b][:, None, :] @ k.transpose(1, 2)) * scale, -1)
+                    outs.append((p @ v).squeeze(1).reshape(-1))
+                return torch.stack(outs).to(qkv.dtype)
+        hidden = self._layer_stack(ids, pos, slots, attn_fn)
+        logits = self._logits(hidden)
+        self.stats["decode_tokens"] += B
+        toks, lps = self._sample(logits, seqs)
+        for q, t, lp in zip(seqs, toks, lps):
+            self._accept(q, int(t), float(lp))
