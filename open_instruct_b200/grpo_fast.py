@@ -1,0 +1,564 @@
+"""RLVR / GRPO entry point (the ``grpo_fast`` API).
+
+    python -m open_instruct_b200.grpo_fast config.yaml [--flag value ...]
+
+Process topology follows the reference (``open_instruct/grpo_fast.py:1245-1432``, ``:1796-2052``): learner
+workers (one per GPU, sharded optimizer among them), rollout-engine workers, one data-preparation
+worker, an actor manager, three queues (prompts, results, eval results); the driver loop steps the
+learners, triggers the weight sync and logs.  Differences: the engines are this package's
+``RolloutEngine`` (called in process, no HTTP server); weights reach the engines by direct stores
+into their parameter buffers (CUDA IPC mapping + one multi-destination copy kernel over NVLink, or
+a plain copy when learner and engine share a process) instead of 291 NCCL broadcasts.
+
+``--single_gpu_mode`` (or a machine without several GPUs) runs learner, engine and data
+preparation as threads of one process on one device.
+
+The learner step implements the reference semantics (``grpo_fast.py:586-765``): per packed micro-batch,
+new log-probs at ``temperature``; old log-probs = detached new ones on the first pass (or precomputed
+with several mini-batches, or the engine's); rho correction; DAPO / CISPO loss (+ beta * KL to the
+reference policy when loaded); token-normalised over the accumulation group with the denominator
+all-reduced over data-parallel ranks.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import json
+import logging
+import math
+import os
+import threading
+import time
+from dataclasses import asdict
+
+import numpy as np
+import torch
+
+from .ckpt.hf_io import load_hf_checkpoint, save_hf_checkpoint
+from .ckpt.train_state import load_train_state, save_train_state
+from .config.argparser import ArgumentParserPlus
+from .config.schemas import ModelConfig
+from .data.tokenize import TokenizerConfig
+from .data_types import CollatedBatchData, GenerationResult, PromptRequest, ShutdownSentinel
+from .ground_truth_utils import RewardConfig, build_all_verifiers
+from .grpo_utils import (
+    GRPOExperimentConfig,
+    calculate_token_counts,
+    compute_grpo_loss,
+    compute_rho_correction,
+    compute_vllm_local_debug_metrics,
+    mask_logprobs,
+    masked_mean,
+    resolve_old_logprob,
+)
+from .learner import Learner, LearnerConfig
+from .models import get_spec
+from .parallel import dist as pdist
+from .streaming import DataPreparation, StreamingDataLoaderConfig, VLLMConfig
+from .utils.common import INVALID_LOGPROB, Tracker, set_seed, setup_logger
+from .utils.model_dims import ModelDims
+
+logger = setup_logger(__name__)
+WEIGHT_SYNC_TIMEOUT_S = 120
+
+
+# ======================================================================================= learner step
+def _packed_batch(data: CollatedBatchData, i: int, device) -> dict:
+    qr = data.query_responses[i].to(device, non_blocking=True)
+    labels = torch.full_like(qr, -100)
+    labels[:-1] = qr[1:]
+    cu = data.cu_seqlens[i].to(device, non_blocking=True)
+    labels[cu[1:].long() - 1] = -100  # the last token of a document has no target
+    return {"input_ids": qr, "position_ids": data.position_ids[i].to(device, non_blocking=True), "cu_seq_lens_q": cu,
+            "labels_shifted": labels}
+
+
+def forward_for_logprobs(learner: Learner, batch: dict, temperature: float, want_entropy: bool = False):
+    """Per-token log-prob of the NEXT token at ``temperature`` (position t scores token t+1), shifted so
+    that entry t is the log-prob OF token t; invalid entries hold ``INVALID_LOGPROB``."""
+    lp, ent = learner.token_logprobs(batch, temperature, want_entropy)
+    valid = batch["labels_shifted"] >= 0
+    lp = torch.where(valid, lp, torch.full_like(lp, INVALID_LOGPROB))
+    out = torch.full_like(lp, INVALID_LOGPROB)
+    out[1:] = lp[:-1]
+    e = None
+    if ent is not None:
+        e = torch.zeros_like(ent)
+        e[1:] = ent[:-1]
+    return out, e
+
+
+def grpo_train_step(learner: Learner, data: CollatedBatchData, args: GRPOExperimentConfig, ref_learner: Learner | None = None,
+                    group=None) -> dict:
+    """All epochs / mini-batches of one training step on this rank's packed micro-batches."""
+    dev = learner.device
+    n = len(data)
+    if n == 0:
+        return {}
+    accumulation_steps = max(1, math.ceil(n / args.num_mini_batches - 0.5))
+    usable = (n // accumulation_steps) * accumulation_steps
+    batches = [_packed_batch(data, i, dev) for i in range(usable)]
+    resp_masks = [data.response_masks[i].to(dev) for i in range(usable)]
+    resp_bool = [m > 0 for m in resp_masks]
+    advantages = [data.advantages[i].to(dev) for i in range(usable)]
+    vllm_lp = [mask_logprobs(data.vllm_logprobs[i].to(dev), resp_bool[i]) for i in range(usable)]
+    ref_lp = [None] * usable
+    if ref_learner is not None:
+        with torch.no_grad():
+            for i in range(usable):
+                ref_lp[i], _ = forward_for_logprobs(ref_learner, batches[i], args.temperature)
+    old_cache: list = [None] * usable
+    if args.num_mini_batches > 1:
+        with torch.no_grad():
+            for i in range(usable):
+                old_cache[i] = vllm_lp[i] if args.use_vllm_logprobs else forward_for_logprobs(learner, batches[i], args.temperature)[0]
+    if args.loss_denominator == "token":
+        denoms = calculate_token_counts(accumulation_steps, resp_bool, dev, group)
+    else:
+        denoms = {s: float(args.loss_denominator) for s in range(0, usable, accumulation_steps)}
+    world = pdist.world_size(group)
+    stats = {k: [] for k in ("pg", "kl", "loss", "clipfrac", "ratio", "entropy", "lpdiff")}
+    rho_stats: dict[str, list] = {}
+    grad_norms = []
+    for epoch in range(args.num_epochs):
+        for i in range(usable):
+            new_lp, ent = forward_for_logprobs(learner, batches[i], args.temperature, args.record_entropy)
+            mask = resp_bool[i]
+            new_lp = torch.where(mask, new_lp, torch.full_like(new_lp, INVALID_LOGPROB))
+            old = resolve_old_logprob(old_cache, i, epoch, args.num_mini_batches, args.use_vllm_logprobs, vllm_lp[i], new_lp)
+            ratio = torch.exp(new_lp - old)
+            rho = compute_rho_correction(old, vllm_lp[i], mask, advantages[i], args, segment_ids=resp_masks[i])
+            pg, clipfrac, kl = compute_grpo_loss(new_lp, ratio, advantages[i], ref_lp[i], args, rho.weights)
+            group_start = (i // accumulation_steps) * accumulation_steps
+            denom = max(denoms[group_start], 1.0)
+            # summed over the group's tokens on ALL ranks / global token count; the optimizer averages over
+            # ranks, hence the factor world (same convention as the reference with DeepSpeed)
+            loss = masked_mean(pg + args.beta * kl, mask, None, denom) * world
+            learner.backward(loss)
+            with torch.no_grad():
+                stats["pg"].append(masked_mean(pg, mask))
+                stats["kl"].append(masked_mean(kl, mask))
+                stats["loss"].append(masked_mean(pg + args.beta * kl, mask))
+                stats["clipfrac"].append(masked_mean(clipfrac, mask))
+                stats["ratio"].append(masked_mean(ratio, mask))
+                if ent is not None:
+                    stats["entropy"].append(masked_mean(ent, mask))
+                if epoch == 0:
+                    stats["lpdiff"].append(compute_vllm_local_debug_metrics(new_lp.detach(), data.vllm_logprobs[i].to(dev), mask))
+                for k, v in rho.metrics.items():
+                    rho_stats.setdefault(k, []).append(masked_mean(v, mask))
+            if (i + 1) % accumulation_steps == 0:
+                # the loss already carries 1/denominator and the factor world: undo only the rank average
+                grad_norms.append(learner.optimizer_step(grad_scale=1.0 / world))
+    mean = lambda xs: float(torch.stack(xs).mean()) if xs else 0.0
+    out = {"loss/policy_avg": mean(stats["pg"]), "loss/kl_avg": mean(stats["kl"]), "loss/total_avg": mean(stats["loss"]),
+           "policy/clipfrac_avg": mean(stats["clipfrac"]), "val/ratio": mean(stats["ratio"]),
+           "val/ratio_var": float(torch.stack(stats["ratio"]).var()) if len(stats["ratio"]) > 1 else 0.0,
+           "optim/grad_norm": mean([g.reshape(()) for g in grad_norms]), "lr": learner.lr(max(0, learner.global_step - 1)),
+           "num_response_tokens": float(sum(int(m.sum()) for m in resp_bool))}
+    if stats["entropy"]:
+        out["policy/entropy_avg"] = mean(stats["entropy"])
+    for k, v in rho_stats.items():
+        out[k] = mean(v)
+    if stats["lpdiff"]:
+        for k in stats["lpdiff"][0]:
+            out[k] = float(np.mean([d[k] for d in stats["lpdiff"]]))
+    return out
+
+
+# ======================================================================================= engine worker
+class EngineWorker:
+    """Rollout engine + its request loop (the role of ``LLMRayActor``, ``open_instruct/vllm_utils.py:553-843``).
+
+    A background thread pulls ``PromptRequest``s while the engine has room, steps the engine, computes
+    rewards for finished requests and pushes ``GenerationResult``s to the results queue (eval requests
+    go to the eval queue)."""
+
+    def __init__(self, spec, prompt_queue, results_queue, eval_queue, reward_config: RewardConfig | None, tokenizer=None,
+                 device="cuda", ops: str = "auto", seed: int = 0, max_model_len: int = 8192, num_blocks: int | None = None,
+                 gpu_memory_utilization: float = 0.85, flat: torch.Tensor | None = None, inflight_updates: bool = True,
+                 max_running: int = 256):
+        from .rollout.engine import RolloutEngine
+
+        self.engine = RolloutEngine(spec, device=device, ops=ops, seed=seed, max_model_len=max_model_len, num_blocks=num_blocks,
+                                    gpu_memory_utilization=gpu_memory_utilization, flat=flat, tokenizer=tokenizer,
+                                    max_running=max_running)
+        self.prompt_q, self.results_q, self.eval_q = prompt_queue, results_queue, eval_queue
+        self.reward_fn = reward_config.build() if reward_config is not None else None
+        self.tokenizer = tokenizer
+        self.inflight_updates = inflight_updates
+        self.should_stop = threading.Event()
+        self.shutdown_flag = threading.Event()
+        self.lock = threading.Lock()  # engine state is touched by the loop thread and by update_weights
+        self.error: BaseException | None = None
+        self.pending: dict[int, PromptRequest] = {}
+        self.thread = threading.Thread(target=self._loop, name="engine-loop", daemon=True)
+        self.thread.start()
+
+    def ready(self) -> bool:
+        return True
+
+    def get_kv_cache_info(self, seq_len: int) -> int:
+        return self.engine.kv_cache_max_concurrency(seq_len)
+
+    def set_should_stop(self, flag: bool) -> None:
+        (self.should_stop.set if flag else self.should_stop.clear)()
+
+    def check_background_threads(self) -> None:
+        if self.error is not None:
+            raise RuntimeError(f"engine loop died: {self.error!r}")
+        if not self.thread.is_alive() and not self.shutdown_flag.is_set():
+            raise RuntimeError("engine loop is not running")
+
+    def update_weights(self, flat: torch.Tensor | None, model_step: int) -> None:
+        """In-process sync: copy ``flat`` into the engine's buffer (None: weights were already written
+        into the buffer by a peer through its IPC mapping; only the version changes)."""
+        with self.lock:
+            if flat is not None:
+                self.engine.update_weights(flat, model_step)
+            else:
+                self.engine.model_step = model_step
+
+    def weight_buffer_ipc(self):
+        """Picklable description of the parameter buffer for a CUDA-IPC mapping in another process."""
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        fn, a = reduce_tensor(self.engine.model.flat.detach())
+        return fn, a
+
+    def _score(self, res: GenerationResult, req: PromptRequest) -> None:
+        decoded = self.tokenizer.batch_decode(res.responses, skip_special_tokens=True) if self.tokenizer is not None else \
+            [" ".join(map(str, r)) for r in res.responses]
+        res.decoded_responses = decoded
+        n = len(res.responses)
+        if self.reward_fn is None:
+            res.reward_scores, res.reward_metrics = [0.0] * n, {}
+            return
+        scores, metrics = asyncio.run(self.reward_fn(res.responses, decoded, [req.ground_truth] * n, [req.dataset] * n,
+                                                     res.finish_reasons, res.request_info, [req.raw_query] * n))
+        res.reward_scores, res.reward_metrics = [float(s) for s in scores], metrics
+
+    def _loop(self) -> None:
+        try:
+            while not self.shutdown_flag.is_set():
+                admitted = False
+                while self.engine.num_active() < self.engine.max_running and not self.should_stop.is_set():
+                    try:
+                        req = self.prompt_q.get(timeout=0.0 if self.engine.has_unfinished() else 0.05) if hasattr(self.prompt_q, "get") else None
+                    except Exception:  # noqa: BLE001 - empty
+                        break
+                    if req is None or isinstance(req, ShutdownSentinel):
+                        if isinstance(req, ShutdownSentinel):
+                            self.shutdown_flag.set()
+                        break
+                    with self.lock:
+                        rid = self.engine.add_request(req.prompt, req.generation_config, prompt_id=req.prompt_id, is_eval=req.is_eval,
+                                                      ground_truth=req.ground_truth, dataset=req.dataset, raw_query=req.raw_query,
+                                                      epoch_number=req.epoch_number)
+                    self.pending[rid] = req
+                    admitted = True
+                if self.should_stop.is_set() and not self.inflight_updates:
+                    time.sleep(0.005)  # paused for a weight update
+                    continue
+                if not self.engine.has_unfinished():
+                    if not admitted:
+                        time.sleep(0.005)
+                    continue
+                with self.lock:
+                    finished = self.engine.step()
+                for res in finished:
+                    req = self.pending.pop(res.index)
+                    res.index = req.index
+                    self._score(res, req)
+                    (self.eval_q if req.is_eval and self.eval_q is not None else self.results_q).put(res)
+        except BaseException as e:  # noqa: BLE001
+            self.error = e
+            logger.exception("engine loop failed")
+
+    def shutdown(self) -> None:
+        self.shutdown_flag.set()
+        self.thread.join(timeout=10)
+
+
+# ======================================================================================= learner worker
+class LearnerWorker:
+    """One learner rank (the role of ``PolicyTrainerRayProcess``, ``open_instruct/grpo_fast.py:253-912``)."""
+
+    def __init__(self, rank: int, world: int, master_addr: str, master_port: int, spec, args: GRPOExperimentConfig,
+                 model_config: ModelConfig, num_training_steps: int, device: str | None = None):
+        os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "MASTER_ADDR": master_addr, "MASTER_PORT": str(master_port),
+                           "LOCAL_RANK": "0"})
+        self.rank, self.world = rank, world
+        _, _, dev = pdist.init_distributed(timeout_s=args.backend_timeout * 60)
+        self.device = torch.device(device) if device else dev
+        set_seed(args.seed + rank)
+        self.args, self.spec = args, spec
+        warm = args.warm_up_steps or int(num_training_steps * args.warmup_ratio)
+        cfg = LearnerConfig(ops=args.ops, comm=args.comm_backend, learning_rate=args.learning_rate, weight_decay=args.weight_decay,
+                            max_grad_norm=args.max_grad_norm, lr_scheduler_type=args.lr_scheduler_type, warmup_steps=warm,
+                            total_steps=max(1, num_training_steps * args.num_epochs * args.num_mini_batches),
+                            gradient_checkpointing=model_config.gradient_checkpointing, seed=args.seed)
+        self.learner = Learner(spec, cfg, device=self.device)
+        src = model_config.model_name_or_path
+        if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
+            load_hf_checkpoint(src, self.learner.model.flat.detach(), spec, strict=False)
+            self.learner.opt.master.copy_(self.learner.model.flat.detach()[self.learner.opt.lo:self.learner.opt.hi].float())
+        self.ref: Learner | None = None
+        if args.load_ref_policy and args.beta != 0.0:
+            # frozen copy of the initial policy; only its forward is used
+            self.ref = Learner(spec, LearnerConfig(ops=args.ops, comm="nccl" if world > 1 else "none", seed=args.seed), device=self.device,
+                               flat_init=self.learner.model.flat.detach().clone())
+        self.training_step = 0
+        self._engine_views: list[torch.Tensor] = []
+
+    def ready(self) -> bool:
+        return True
+
+    def flat_weights(self) -> torch.Tensor:
+        return self.learner.model.flat.detach()
+
+    def step(self, data: CollatedBatchData) -> dict:
+        t0 = time.perf_counter()
+        out = grpo_train_step(self.learner, data, self.args, self.ref)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        out["time/training"] = time.perf_counter() - t0
+        self.training_step += 1
+        if self.ref is not None and self.args.ref_policy_update_freq and self.training_step % self.args.ref_policy_update_freq == 0:
+            self.update_ref_policy()
+        return out
+
+    def update_ref_policy(self) -> None:
+        """Polyak update ref <- alpha * policy + (1 - alpha) * ref on the flat buffers."""
+        with torch.no_grad():
+            self.ref.model.flat.detach().lerp_(self.learner.model.flat.detach(), self.args.alpha)
+
+    # ---- weight sync into engines living in other processes (CUDA IPC + multi-destination copy kernel)
+    def connect_engines(self, ipc_descs: list) -> int:
+        self._engine_views = [fn(*a) for fn, a in ipc_descs]
+        return len(self._engine_views)
+
+    def push_weights(self) -> float:
+        """Copy this rank's 1/world slice of the bf16 working copy into every engine's buffer."""
+        from .parallel.weight_sync import push_slice
+
+        t0 = time.perf_counter()
+        n = self.learner.model.layout.total
+        per = -(-n // self.world)
+        lo, hi = self.rank * per, min(n, (self.rank + 1) * per)
+        push_slice(self.learner.model.flat.detach(), self._engine_views, lo, hi)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        pdist.barrier()
+        return time.perf_counter() - t0
+
+    def save_model(self, output_dir: str, tokenizer_path: str | None = None) -> None:
+        if self.rank == 0:
+            tok = None
+            if tokenizer_path:
+                from transformers import AutoTokenizer
+
+                tok = AutoTokenizer.from_pretrained(tokenizer_path)
+            save_hf_checkpoint(self.learner.model.flat, self.spec, output_dir, tokenizer=tok)
+            with open(os.path.join(output_dir, ".checkpoint_complete"), "w") as fh:
+                fh.write("ok")
+        pdist.barrier()
+
+    def save_checkpoint_state(self, ckpt_dir: str, client_state: dict) -> None:
+        d = os.path.join(ckpt_dir, f"step_{client_state['training_step']}")
+        save_train_state(d, self.learner.opt, client_state)
+        if self.ref is not None and self.rank == 0:
+            torch.save(self.ref.model.flat.detach().cpu(), os.path.join(d, "ref_policy.pt"))
+
+    def load_checkpoint_state(self, ckpt_dir: str) -> dict | None:
+        from .utils.common import get_last_checkpoint
+
+        d = get_last_checkpoint(ckpt_dir)
+        if d is None:
+            return None
+        st = load_train_state(d, self.learner.opt)
+        self.training_step = st.get("training_step", 0)
+        self.learner.global_step = st.get("optimizer_steps", self.training_step)
+        p = os.path.join(d, "ref_policy.pt")
+        if self.ref is not None and os.path.exists(p):
+            self.ref.model.flat.detach().copy_(torch.load(p, map_location=self.device))
+        return st
+
+    def shutdown(self) -> None:
+        pdist.destroy()
+
+
+# ======================================================================================= driver
+def setup_runtime_variables(args: GRPOExperimentConfig, streaming: StreamingDataLoaderConfig) -> GRPOExperimentConfig:
+    """Derived quantities (``open_instruct/grpo_fast.py:1014-1049``)."""
+    args.world_size = sum(args.num_learners_per_node)
+    per_step = streaming.num_unique_prompts_rollout * streaming.num_samples_per_prompt_rollout
+    args.num_training_steps = args.num_training_steps or max(1, args.total_episodes // per_step)
+    if args.run_name is None:
+        args.run_name = f"{args.exp_name}__{args.seed}__{int(time.time())}"
+    return args
+
+
+def validate_configs(args: GRPOExperimentConfig, streaming: StreamingDataLoaderConfig, vllm: VLLMConfig) -> None:
+    if streaming.num_unique_prompts_rollout * streaming.num_samples_per_prompt_rollout < args.world_size:
+        raise ValueError("fewer rollouts per step than learner ranks")
+    if vllm.vllm_tensor_parallel_size not in (1, 2, 4, 8):
+        raise ValueError("vllm_tensor_parallel_size must be 1, 2, 4 or 8")
+    if args.single_gpu_mode and (args.world_size != 1 or vllm.vllm_num_engines != 1):
+        raise ValueError("single_gpu_mode runs exactly one learner and one engine")
+
+
+def load_prompt_dataset(streaming: StreamingDataLoaderConfig, tc: TokenizerConfig, eval_split: bool = False):
+    from .data.mixer import get_cached_dataset_tulu
+
+    mix = streaming.dataset_mixer_eval_list if eval_split else streaming.dataset_mixer_list
+    splits = streaming.dataset_mixer_eval_list_splits if eval_split else streaming.dataset_mixer_list_splits
+    if not mix:
+        return None
+    override = None
+    if streaming.system_prompt_override_file:
+        override = open(streaming.system_prompt_override_file).read().strip()
+    targs = [{}, {"max_prompt_token_length": streaming.max_prompt_token_length}][: len(streaming.dataset_transform_fn)]
+    return get_cached_dataset_tulu(mix, splits, tc, streaming.dataset_transform_fn, targs,
+                                   dataset_cache_mode=streaming.dataset_cache_mode,
+                                   dataset_config_hash=streaming.dataset_config_eval_hash if eval_split else streaming.dataset_config_hash,
+                                   dataset_local_cache_dir=streaming.dataset_local_cache_dir, dataset_skip_cache=streaming.dataset_skip_cache,
+                                   system_prompt_override=override)
+
+
+def _weighted_average(per_rank: list[dict]) -> dict:
+    """Token-weighted mean of the learners' metrics (``open_instruct/grpo_fast.py:1562-1595``)."""
+    per_rank = [m for m in per_rank if m]
+    if not per_rank:
+        return {}
+    w = np.array([max(m.get("num_response_tokens", 1.0), 1.0) for m in per_rank])
+    out = {}
+    for k in per_rank[0]:
+        vals = np.array([m.get(k, 0.0) for m in per_rank], dtype=np.float64)
+        out[k] = float(vals.sum()) if k == "num_response_tokens" else float(vals.max()) if k.startswith("time/") else float((vals * w).sum() / w.sum())
+    return out
+
+
+def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelConfig, streaming: StreamingDataLoaderConfig,
+         vllm: VLLMConfig, tools_config=None) -> dict:
+    from .actor_manager import ActorManager
+    from .actors import ray_compat as ray
+    from .parallel.weight_sync import sync_in_process
+
+    args = setup_runtime_variables(args, streaming)
+    validate_configs(args, streaming, vllm)
+    set_seed(args.seed)
+    if tc.tokenizer_name_or_path is None:
+        tc.tokenizer_name_or_path = model_config.model_name_or_path
+    tokenizer = tc.tokenizer
+    dataset = load_prompt_dataset(streaming, tc)
+    eval_dataset = load_prompt_dataset(streaming, tc, eval_split=True)
+    if args.cache_dataset_only:
+        return {"cached": len(dataset)}
+    spec = get_spec(model_config.config_name or model_config.model_name_or_path)
+    if len(tokenizer) > spec.vocab_size:
+        spec = spec.replace(vocab_size=(len(tokenizer) + 7) // 8 * 8)
+    spec = spec.replace(pad_token_id=tokenizer.pad_token_id, eos_token_id=tokenizer.eos_token_id, bos_token_id=tokenizer.bos_token_id)
+    reward_cfg = RewardConfig(apply_r1_style_format_reward=streaming.apply_r1_style_format_reward,
+                              r1_style_format_reward=streaming.r1_style_format_reward,
+                              apply_verifiable_reward=streaming.apply_verifiable_reward, verification_reward=streaming.verification_reward,
+                              non_stop_penalty=streaming.non_stop_penalty, non_stop_penalty_value=streaming.non_stop_penalty_value,
+                              additive_format_reward=streaming.additive_format_reward, reward_aggregator=streaming.reward_aggregator,
+                              verifier_functions=build_all_verifiers(args, streaming))
+    single = args.single_gpu_mode or not torch.cuda.is_available() or torch.cuda.device_count() < 2
+    max_len = streaming.max_prompt_token_length + max(streaming.response_length, streaming.eval_response_length or 0)
+    tracker = Tracker(args.output_dir, args.run_name, {**asdict(args), **asdict(streaming), **asdict(vllm)},
+                      report_to=("wandb", "tensorboard") if args.with_tracking else ("jsonl",), wandb_project=args.wandb_project_name,
+                      wandb_entity=args.wandb_entity)
+    dims = ModelDims.from_spec(spec)
+    per_step = streaming.num_unique_prompts_rollout * streaming.num_samples_per_prompt_rollout
+    qsize = (streaming.async_steps + 1) * streaming.num_unique_prompts_rollout
+    last: dict = {}
+
+    if single:
+        prompt_q, results_q, eval_q = ray.Queue(local=True), ray.Queue(maxsize=qsize, local=True), ray.Queue(local=True)
+        device = "cuda:0" if torch.cuda.is_available() else "cpu"
+        learner = LearnerWorker.__new__(LearnerWorker)
+        LearnerWorker.__init__(learner, 0, 1, "127.0.0.1", 29512, spec, args, model_config, args.num_training_steps, device=device)
+        engine = EngineWorker(spec, prompt_q, results_q, eval_q, reward_cfg, tokenizer, device=device, ops=args.ops, seed=args.seed,
+                              max_model_len=max_len, num_blocks=None if torch.cuda.is_available() else 512,
+                              gpu_memory_utilization=0.25 if torch.cuda.is_available() else 0.9,
+                              flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates)
+        learners, engines = [learner], [engine]
+        call = lambda obj, m, *a: getattr(obj, m)(*a)
+    else:
+        raise NotImplementedError("multi-process GRPO is launched through open_instruct_b200.grpo_launch")
+
+    manager = ActorManager({"prompts": prompt_q, "results": results_q, "eval": eval_q}, enable_dashboard=args.enable_queue_dashboard and not single,
+                           port=args.queue_dashboard_port)
+    manager.set_kv_cache_max_concurrency(engines[0].get_kv_cache_info(max_len))
+    prep = DataPreparation(dataset, streaming, prompt_q, results_q, tokenizer, args.world_size, args.per_device_train_batch_size,
+                           args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p)
+    resume_step = 0
+    if args.checkpoint_state_dir and os.path.isdir(args.checkpoint_state_dir):
+        st = learners[0].load_checkpoint_state(args.checkpoint_state_dir)
+        if st:
+            resume_step = st["training_step"]
+            prep.set_state(st["data_prep_actor_state"])
+            prep.next_step = resume_step + 1
+            prep.trainer_step = resume_step
+            prep.model_step = resume_step
+            sync_in_process(learners[0].flat_weights(), engines, resume_step, learners[0].learner.model.layout.total)
+    prep.start()
+    total_tokens, t_run = 0, time.time()
+    try:
+        for step in range(resume_step + 1, args.num_training_steps + 1):
+            t_step = time.perf_counter()
+            for e in engines:
+                e.check_background_threads()
+            data, prep_metrics = prep.get_data(0, step)
+            t_wait = time.perf_counter() - t_step
+            metrics = _weighted_average([call(l, "step", data) for l in learners])
+            manager.report_training_step_time(metrics.get("time/training", 0.0))
+            # ---- weight sync (every step)
+            manager.set_should_stop(True)
+            for e in engines:
+                e.set_should_stop(True)
+            t_sync = sync_in_process(learners[0].flat_weights(), engines, step, learners[0].learner.model.layout.total)
+            if t_sync > WEIGHT_SYNC_TIMEOUT_S:
+                raise TimeoutError("weight sync exceeded its time limit")
+            for e in engines:
+                e.set_should_stop(False)
+            manager.set_should_stop(False)
+            prep.set_model_step(step)
+            tokens = prep_metrics.get("val/total_response_tokens", 0) + prep_metrics.get("val/total_prompt_tokens", 0)
+            total_tokens += tokens
+            dt = time.perf_counter() - t_step
+            last = {**prep_metrics, **metrics, "training_step": step, "episode": step * per_step, "time/total": dt,
+                    "time/weight_sync": t_sync, "time/trainer_waiting_for_data": t_wait,
+                    "learner_tokens_per_second_step": tokens / max(metrics.get("time/training", dt), 1e-9),
+                    "learner_tokens_per_second_overall": total_tokens / max(time.time() - t_run, 1e-9),
+                    "learner_mfu": dims.approximate_learner_utilization(tokens, prep_metrics.get("val/sequence_lengths", 1.0) +
+                                                                        streaming.max_prompt_token_length, metrics.get("time/training", dt),
+                                                                        args.world_size) if torch.cuda.is_available() else 0.0}
+            tracker.log(last, step)
+            logger.info("step %d: score %.3f loss %.4f len %.1f sync %.3fs", step, last.get("scores", 0.0), last.get("loss/total_avg", 0.0),
+                        last.get("val/sequence_lengths", 0.0), t_sync)
+            if args.save_freq > 0 and step % args.save_freq == 0:
+                call(learners[0], "save_model", os.path.join(f"{args.output_dir}_checkpoints", f"step_{step}"), tc.tokenizer_name_or_path)
+            if args.checkpoint_state_dir and args.checkpoint_state_freq > 0 and step % args.checkpoint_state_freq == 0:
+                client = {"training_step": step, "optimizer_steps": learners[0].learner.global_step, "episode": step * per_step,
+                          "num_total_tokens": total_tokens, "data_prep_actor_state": prep.get_state()}
+                call(learners[0], "save_checkpoint_state", args.checkpoint_state_dir, client)
+        call(learners[0], "save_model", args.output_dir, tc.tokenizer_name_or_path)
+    finally:
+        prep.shutdown()
+        for e in engines:
+            e.shutdown()
+        manager.shutdown()
+        tracker.close()
+    last["num_training_steps"] = args.num_training_steps
+    return last
+
+
+if __name__ == "__main__":
+    from .environments.tools.utils import EnvsConfig
+
+    parser = ArgumentParserPlus((GRPOExperimentConfig, TokenizerConfig, ModelConfig, StreamingDataLoaderConfig, VLLMConfig, EnvsConfig))
+    parser.set_defaults(exp_name="grpo", warmup_ratio=0.0, max_grad_norm=1.0, per_device_train_batch_size=1)
+    main(*parser.parse())

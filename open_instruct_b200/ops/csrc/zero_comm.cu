@@ -260,3 +260,51 @@ extern "C" int b200_zero_adamw_allgather(float* master, float* m, float* v, cons
                                                               bc2);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------ learner -> engine weight push
+// One read of the source slice, one 16-byte store per destination: dst_r[off + i] = src[off + i] for
+// every destination r (peer buffers mapped through CUDA IPC or symmetric memory).  With `src_f32`
+// the source is the fp32 master copy and the cast to bf16 happens in flight.
+namespace b200 {
+template <bool F32>
+__global__ void __launch_bounds__(256)
+multi_push_kernel(const void* __restrict__ src, PeerPtrs dsts, int n_dst, long long off, long long n) {
+  const long long nv = n / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 pk;
+    if (F32) {
+      const float4 a = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + off)[i * 2];
+      const float4 b = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + off)[i * 2 + 1];
+      pk.x = pack_bf16x2(a.x, a.y); pk.y = pack_bf16x2(a.z, a.w);
+      pk.z = pack_bf16x2(b.x, b.y); pk.w = pack_bf16x2(b.z, b.w);
+    } else {
+      pk = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + off)[i];
+    }
+#pragma unroll 1
+    for (int r = 0; r < n_dst; ++r)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dsts.p[r]) + off)[i] = pk;
+  }
+  // tail (n not a multiple of 8)
+  if (blockIdx.x == 0) {
+    for (long long i = nv * 8 + threadIdx.x; i < n; i += blockDim.x) {
+      const __nv_bfloat16 v = F32 ? __float2bfloat16(reinterpret_cast<const float*>(src)[off + i])
+                                  : reinterpret_cast<const __nv_bfloat16*>(src)[off + i];
+      for (int r = 0; r < n_dst; ++r) reinterpret_cast<__nv_bfloat16*>(dsts.p[r])[off + i] = v;
+    }
+  }
+  __threadfence_system();
+}
+}  // namespace b200
+
+// src: bf16 (src_f32 = 0) or fp32 (src_f32 = 1) buffer; copies elements [off, off + n) to the same
+// offsets of up to 8 destination bf16 buffers.  `off` must be a multiple of 8.
+extern "C" int b200_multi_push(const void* src, const void* const* dst_ptrs, int n_dst, long long off, long long n, int src_f32,
+                               void* stream) {
+  if (n <= 0 || n_dst <= 0) return 0;
+  if (n_dst > MAX_PEERS || off % 8) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (src_f32) multi_push_kernel<true><<<148 * 8, 256, 0, st>>>(src, make_ptrs(dst_ptrs, n_dst), n_dst, off, n);
+  else multi_push_kernel<false><<<148 * 8, 256, 0, st>>>(src, make_ptrs(dst_ptrs, n_dst), n_dst, off, n);
+  return static_cast<int>(cudaGetLastError());
+}
