@@ -48,6 +48,17 @@ _gpu_next = 0
 _pool = cf.ThreadPoolExecutor(max_workers=64, thread_name_prefix="actor-call")
 
 
+def _send(conn, obj) -> None:
+    """Plain pickle by value.  (``Connection.send`` would use multiprocessing's ForkingPickler, for which
+    torch registers shared-memory / file-descriptor passing of tensors - a second channel between the
+    processes that we neither need nor want for small control messages.)"""
+    conn.send_bytes(pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL))
+
+
+def _recv(conn):
+    return pickle.loads(conn.recv_bytes())
+
+
 class ActorError(RuntimeError):
     """An exception raised inside an actor method, re-raised in the caller with the remote traceback."""
 
@@ -80,12 +91,12 @@ def _serve(cls, args, kwargs, address, ready, max_concurrency, env):
         try:
             while not stop.is_set():
                 try:
-                    msg = conn.recv()
+                    msg = _recv(conn)
                 except (EOFError, OSError):
                     return
                 if msg[0] == "stop":
                     stop.set()
-                    conn.send(("ok", None))
+                    _send(conn, ("ok", None))
                     return
                 _, method, a, kw = msg
                 try:
@@ -93,9 +104,9 @@ def _serve(cls, args, kwargs, address, ready, max_concurrency, env):
                 except BaseException as e:  # noqa: BLE001
                     res = ("error", f"{type(e).__name__}: {e}\n{traceback.format_exc()}")
                 try:
-                    conn.send(res)
+                    _send(conn, res)
                 except Exception as e:  # noqa: BLE001 - unpicklable result
-                    conn.send(("error", f"cannot send result of {method}: {e}"))
+                    _send(conn, ("error", f"cannot send result of {method}: {e}"))
         finally:
             conn.close()
 
@@ -147,8 +158,8 @@ class ActorHandle:
     def _call(self, method, args, kwargs):
         try:
             c = self._conn()
-            c.send(("call", method, args, kwargs))
-            status, val = c.recv()
+            _send(c, ("call", method, args, kwargs))
+            status, val = _recv(c)
         except (EOFError, OSError, ConnectionError) as e:
             self._local.conn = None
             raise ActorError(f"actor {self._name or self._address} is not reachable: {e}") from e
@@ -173,13 +184,17 @@ class ActorClass:
         global _gpu_next
         env = dict(self._opts.get("env", {}))
         n_gpu = self._opts.get("num_gpus", 0)
-        if n_gpu and "CUDA_VISIBLE_DEVICES" not in env:
+        if n_gpu and "CUDA_VISIBLE_DEVICES" not in env and "B200_GPU_IDS" not in env:
             with _gpu_lock:
                 ids = list(range(_gpu_next, _gpu_next + int(max(1, n_gpu))))
                 _gpu_next += int(max(1, n_gpu)) if n_gpu >= 1 else 0
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            pool = visible.split(",") if visible else None
-            env["CUDA_VISIBLE_DEVICES"] = ",".join(pool[i] if pool else str(i) for i in ids)
+            if self._opts.get("mask_gpus", False):
+                visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+                pool = visible.split(",") if visible else None
+                env["CUDA_VISIBLE_DEVICES"] = ",".join(pool[i] if pool else str(i) for i in ids)
+            else:
+                # every GPU stays visible (CUDA IPC and peer mappings need that); the actor picks its own
+                env["B200_GPU_IDS"] = ",".join(str(i) for i in ids)
         address = os.path.join(tempfile.gettempdir(), f"oib200-{uuid.uuid4().hex[:12]}.sock")
         ctx = mp.get_context("spawn")
         ready = ctx.Queue()
@@ -236,8 +251,8 @@ def get_actor(name: str) -> ActorHandle:
 def kill(handle: ActorHandle) -> None:
     try:
         c = Client(handle._address, family="AF_UNIX", authkey=_AUTH)
-        c.send(("stop",))
-        c.recv()
+        _send(c, ("stop",))
+        _recv(c)
         c.close()
     except Exception:  # noqa: BLE001
         pass

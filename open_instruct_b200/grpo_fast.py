@@ -180,6 +180,17 @@ class EngineWorker:
                  max_running: int = 256):
         from .rollout.engine import RolloutEngine
 
+        if isinstance(tokenizer, TokenizerConfig):  # built in the worker's own process
+            tokenizer = tokenizer.tokenizer
+        if device == "auto":
+            ids = os.environ.get("B200_GPU_IDS")
+            device = f"cuda:{ids.split(',')[0]}" if ids and torch.cuda.is_available() else ("cuda:0" if torch.cuda.is_available() else "cpu")
+        if str(device).startswith("cuda"):
+            torch.cuda.set_device(torch.device(device))
+
+        if flat is not None:
+            want = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+            flat = flat.detach().to(device=device, dtype=want).clone()
         self.engine = RolloutEngine(spec, device=device, ops=ops, seed=seed, max_model_len=max_model_len, num_blocks=num_blocks,
                                     gpu_memory_utilization=gpu_memory_utilization, flat=flat, tokenizer=tokenizer,
                                     max_running=max_running)
@@ -210,7 +221,7 @@ class EngineWorker:
         if not self.thread.is_alive() and not self.shutdown_flag.is_set():
             raise RuntimeError("engine loop is not running")
 
-    def update_weights(self, flat: torch.Tensor | None, model_step: int) -> None:
+    def update_weights(self, flat, model_step: int) -> None:
         """In-process sync: copy ``flat`` into the engine's buffer (None: weights were already written
         into the buffer by a peer through its IPC mapping; only the version changes)."""
         with self.lock:
@@ -286,10 +297,14 @@ class LearnerWorker:
 
     def __init__(self, rank: int, world: int, master_addr: str, master_port: int, spec, args: GRPOExperimentConfig,
                  model_config: ModelConfig, num_training_steps: int, device: str | None = None):
+        gpu = (os.environ.get("B200_GPU_IDS") or "0").split(",")[0]
+        if device is not None and str(device).startswith("cuda:"):
+            gpu = str(device).split(":")[1]
         os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "MASTER_ADDR": master_addr, "MASTER_PORT": str(master_port),
-                           "LOCAL_RANK": "0"})
+                           "LOCAL_RANK": gpu})
         self.rank, self.world = rank, world
-        _, _, dev = pdist.init_distributed(timeout_s=args.backend_timeout * 60)
+        _, _, dev = pdist.init_distributed(backend=None if torch.cuda.is_available() and device != "cpu" else "gloo",
+                                           timeout_s=args.backend_timeout * 60)
         self.device = torch.device(device) if device else dev
         set_seed(args.seed + rank)
         self.args, self.spec = args, spec
@@ -314,8 +329,14 @@ class LearnerWorker:
     def ready(self) -> bool:
         return True
 
+    def optimizer_steps(self) -> int:
+        return self.learner.global_step
+
     def flat_weights(self) -> torch.Tensor:
         return self.learner.model.flat.detach()
+
+    def flat_weights_cpu(self) -> torch.Tensor:
+        return self.learner.model.flat.detach().to("cpu", copy=True)
 
     def step(self, data: CollatedBatchData) -> dict:
         t0 = time.perf_counter()
@@ -426,6 +447,12 @@ def load_prompt_dataset(streaming: StreamingDataLoaderConfig, tc: TokenizerConfi
                                    system_prompt_override=override)
 
 
+def ParamLayoutTotal(spec) -> int:
+    from .models.spec import ParamLayout
+
+    return ParamLayout(spec).total
+
+
 def _weighted_average(per_rank: list[dict]) -> dict:
     """Token-weighted mean of the learners' metrics (``open_instruct/grpo_fast.py:1562-1595``)."""
     per_rank = [m for m in per_rank if m]
@@ -465,7 +492,8 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
                               non_stop_penalty=streaming.non_stop_penalty, non_stop_penalty_value=streaming.non_stop_penalty_value,
                               additive_format_reward=streaming.additive_format_reward, reward_aggregator=streaming.reward_aggregator,
                               verifier_functions=build_all_verifiers(args, streaming))
-    single = args.single_gpu_mode or not torch.cuda.is_available() or torch.cuda.device_count() < 2
+    few_gpus = not torch.cuda.is_available() or torch.cuda.device_count() < 2
+    single = args.single_gpu_mode or (args.world_size == 1 and vllm.vllm_num_engines == 1 and few_gpus)
     max_len = streaming.max_prompt_token_length + max(streaming.response_length, streaming.eval_response_length or 0)
     tracker = Tracker(args.output_dir, args.run_name, {**asdict(args), **asdict(streaming), **asdict(vllm)},
                       report_to=("wandb", "tensorboard") if args.with_tracking else ("jsonl",), wandb_project=args.wandb_project_name,
@@ -485,45 +513,88 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
                               gpu_memory_utilization=0.25 if torch.cuda.is_available() else 0.9,
                               flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates)
         learners, engines = [learner], [engine]
-        call = lambda obj, m, *a: getattr(obj, m)(*a)
+        single_objs = True
     else:
-        raise NotImplementedError("multi-process GRPO is launched through open_instruct_b200.grpo_launch")
+        import dataclasses
+
+        cuda = torch.cuda.is_available()
+        prompt_q, results_q, eval_q = ray.Queue(), ray.Queue(maxsize=qsize), ray.Queue()
+        tc_plain = dataclasses.replace(tc)  # without the cached tokenizer object
+        port = 29600 + (os.getpid() % 200)
+        LW, EW = ray.remote(LearnerWorker), ray.remote(EngineWorker)
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=args.world_size) as ex:  # ranks must start together: they rendezvous in __init__
+            futs = [ex.submit(LW.options(num_gpus=1 if cuda else 0, max_concurrency=4).remote, r, args.world_size, "127.0.0.1", port,
+                              spec, args, model_config, args.num_training_steps, None if cuda else "cpu")
+                    for r in range(args.world_size)]
+            learners = [f.result() for f in futs]
+        init_flat = ray.get(learners[0].flat_weights_cpu.remote())
+        engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
+            spec, prompt_q, results_q, eval_q, reward_cfg, tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len,
+            None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates)
+            for i in range(vllm.vllm_num_engines)]
+        ray.get([e.ready.remote() for e in engines] + [l.ready.remote() for l in learners])
+        if cuda:
+            descs = ray.get([e.weight_buffer_ipc.remote() for e in engines])
+            ray.get([l.connect_engines.remote(descs) for l in learners])
+        single_objs = False
+
+    def call(obj, method, *a):
+        return getattr(obj, method)(*a) if single_objs else ray.get(getattr(obj, method).remote(*a))
+
+    def call_all(objs, method, *a, per_obj=None):
+        if single_objs:
+            return [getattr(o, method)(*(per_obj[i] if per_obj else a)) for i, o in enumerate(objs)]
+        return ray.get([getattr(o, method).remote(*(per_obj[i] if per_obj else a)) for i, o in enumerate(objs)])
+
+    total_params = ParamLayoutTotal(spec)
+
+    def weight_sync(step: int) -> float:
+        t0 = time.perf_counter()
+        if single_objs:
+            return sync_in_process(learners[0].flat_weights(), engines, step, total_params)
+        if torch.cuda.is_available():
+            call_all(learners, "push_weights")
+            call_all(engines, "update_weights", None, step)
+        else:
+            flat = call(learners[0], "flat_weights_cpu")
+            call_all(engines, "update_weights", flat, step)
+        return time.perf_counter() - t0
 
     manager = ActorManager({"prompts": prompt_q, "results": results_q, "eval": eval_q}, enable_dashboard=args.enable_queue_dashboard and not single,
                            port=args.queue_dashboard_port)
-    manager.set_kv_cache_max_concurrency(engines[0].get_kv_cache_info(max_len))
+    manager.set_kv_cache_max_concurrency(call(engines[0], "get_kv_cache_info", max_len))
     prep = DataPreparation(dataset, streaming, prompt_q, results_q, tokenizer, args.world_size, args.per_device_train_batch_size,
                            args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p)
     resume_step = 0
     if args.checkpoint_state_dir and os.path.isdir(args.checkpoint_state_dir):
-        st = learners[0].load_checkpoint_state(args.checkpoint_state_dir)
+        st = call_all(learners, "load_checkpoint_state", args.checkpoint_state_dir)[0]
         if st:
             resume_step = st["training_step"]
             prep.set_state(st["data_prep_actor_state"])
             prep.next_step = resume_step + 1
             prep.trainer_step = resume_step
             prep.model_step = resume_step
-            sync_in_process(learners[0].flat_weights(), engines, resume_step, learners[0].learner.model.layout.total)
+            weight_sync(resume_step)
     prep.start()
     total_tokens, t_run = 0, time.time()
     try:
         for step in range(resume_step + 1, args.num_training_steps + 1):
             t_step = time.perf_counter()
-            for e in engines:
-                e.check_background_threads()
-            data, prep_metrics = prep.get_data(0, step)
+            call_all(engines, "check_background_threads")
+            per_rank = [prep.get_data(r, step) for r in range(args.world_size)]
+            prep_metrics = per_rank[0][1]
             t_wait = time.perf_counter() - t_step
-            metrics = _weighted_average([call(l, "step", data) for l in learners])
+            metrics = _weighted_average(call_all(learners, "step", per_obj=[(d,) for d, _ in per_rank]))
             manager.report_training_step_time(metrics.get("time/training", 0.0))
             # ---- weight sync (every step)
             manager.set_should_stop(True)
-            for e in engines:
-                e.set_should_stop(True)
-            t_sync = sync_in_process(learners[0].flat_weights(), engines, step, learners[0].learner.model.layout.total)
+            call_all(engines, "set_should_stop", True)
+            t_sync = weight_sync(step)
             if t_sync > WEIGHT_SYNC_TIMEOUT_S:
                 raise TimeoutError("weight sync exceeded its time limit")
-            for e in engines:
-                e.set_should_stop(False)
+            call_all(engines, "set_should_stop", False)
             manager.set_should_stop(False)
             prep.set_model_step(step)
             tokens = prep_metrics.get("val/total_response_tokens", 0) + prep_metrics.get("val/total_prompt_tokens", 0)
@@ -540,16 +611,22 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
             logger.info("step %d: score %.3f loss %.4f len %.1f sync %.3fs", step, last.get("scores", 0.0), last.get("loss/total_avg", 0.0),
                         last.get("val/sequence_lengths", 0.0), t_sync)
             if args.save_freq > 0 and step % args.save_freq == 0:
-                call(learners[0], "save_model", os.path.join(f"{args.output_dir}_checkpoints", f"step_{step}"), tc.tokenizer_name_or_path)
+                call_all(learners, "save_model", os.path.join(f"{args.output_dir}_checkpoints", f"step_{step}"), tc.tokenizer_name_or_path)
             if args.checkpoint_state_dir and args.checkpoint_state_freq > 0 and step % args.checkpoint_state_freq == 0:
-                client = {"training_step": step, "optimizer_steps": learners[0].learner.global_step, "episode": step * per_step,
+                client = {"training_step": step, "optimizer_steps": call(learners[0], "optimizer_steps"), "episode": step * per_step,
                           "num_total_tokens": total_tokens, "data_prep_actor_state": prep.get_state()}
-                call(learners[0], "save_checkpoint_state", args.checkpoint_state_dir, client)
-        call(learners[0], "save_model", args.output_dir, tc.tokenizer_name_or_path)
+                call_all(learners, "save_checkpoint_state", args.checkpoint_state_dir, client)
+        call_all(learners, "save_model", args.output_dir, tc.tokenizer_name_or_path)
     finally:
         prep.shutdown()
-        for e in engines:
-            e.shutdown()
+        if single_objs:
+            for e in engines:
+                e.shutdown()
+        else:
+            for h in list(engines) + list(learners):
+                ray.kill(h)
+            for q in (prompt_q, results_q, eval_q):
+                q.shutdown()
         manager.shutdown()
         tracker.close()
     last["num_training_steps"] = args.num_training_steps

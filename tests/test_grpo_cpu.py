@@ -66,3 +66,30 @@ def test_grpo_train_step_moves_policy_toward_advantage():
         grpo_train_step(learner, data, args)
     after = seq_logp(r[0]), seq_logp(r[1])
     assert after[0] > before[0] and after[1] < before[1]
+
+
+def test_grpo_multi_process_actors(tmp_path):
+    """Two learner processes (gloo) + one engine process + cross-process queues, CPU."""
+    from open_instruct_b200.actors import ray_compat as ray
+    from open_instruct_b200.config.schemas import ModelConfig
+    from open_instruct_b200.data.tokenize import TokenizerConfig
+    from open_instruct_b200.grpo_fast import main
+    from open_instruct_b200.grpo_utils import GRPOExperimentConfig
+    from open_instruct_b200.streaming import StreamingDataLoaderConfig, VLLMConfig
+    import open_instruct_b200.grpo_fast as gf
+
+    tmp = str(tmp_path)
+    tok = make_tokenizer(os.path.join(tmp, "tok"))
+    data = make_rlvr_jsonl(os.path.join(tmp, "rl.jsonl"), n=12)
+    args = GRPOExperimentConfig(total_episodes=2 * 4 * 4, learning_rate=1e-3, beta=0.0, load_ref_policy=False, output_dir=os.path.join(tmp, "out"),
+                                num_learners_per_node=[2], ops="ref", seed=3, save_freq=-1, lr_scheduler_type="constant")
+    streaming = StreamingDataLoaderConfig(max_prompt_token_length=64, response_length=8, pack_length=128, async_steps=1,
+                                          num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=4, dataset_mixer_list=[data, "1.0"],
+                                          dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False)
+    try:
+        out = main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path="tiny"),
+                   streaming, VLLMConfig())
+    finally:
+        ray.shutdown()
+    assert out["training_step"] == 2
+    assert os.path.exists(os.path.join(args.output_dir, "model.safetensors"))
