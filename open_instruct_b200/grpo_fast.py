@@ -177,7 +177,7 @@ class EngineWorker:
     def __init__(self, spec, prompt_queue, results_queue, eval_queue, reward_config: RewardConfig | None, tokenizer=None,
                  device="cuda", ops: str = "auto", seed: int = 0, max_model_len: int = 8192, num_blocks: int | None = None,
                  gpu_memory_utilization: float = 0.85, flat: torch.Tensor | None = None, inflight_updates: bool = True,
-                 max_running: int = 256):
+                 max_running: int = 256, envs_config=None):
         from .rollout.engine import RolloutEngine
 
         if isinstance(tokenizer, TokenizerConfig):  # built in the worker's own process
@@ -203,6 +203,23 @@ class EngineWorker:
         self.lock = threading.Lock()  # engine state is touched by the loop thread and by update_weights
         self.error: BaseException | None = None
         self.pending: dict[int, PromptRequest] = {}
+        # multi-turn tool / environment rollouts: engine request id -> (group key, sample index)
+        self.tool_runner = None
+        self.sessions: dict[int, tuple[int, int]] = {}
+        self.groups: dict[int, dict] = {}
+        self._group_ids = 0
+        if envs_config is not None and envs_config.enabled:
+            from .environments.base import TextRLEnvironment
+            from .environments.tools.parsers import create_tool_parser
+            from .environments.tools.tools import TOOL_REGISTRY, build_pools
+            from .rollout.tool_session import ToolRunner
+
+            pools = build_pools(envs_config, default_pool_size=max(8, max_running))
+            text_env = next((n for n in envs_config.envs if isinstance(TOOL_REGISTRY[n], type) and issubclass(TOOL_REGISTRY[n], TextRLEnvironment)), None)
+            names = [d["function"]["name"] for p in pools.values() for d in p.tool_definitions()] or list(pools)
+            parser = create_tool_parser(envs_config.tool_parser_type, names)
+            self.tool_runner = ToolRunner(pools, parser, tokenizer, envs_config.max_steps, envs_config.max_tool_calls, text_env)
+            self.engine.tokenizer = tokenizer
         self.thread = threading.Thread(target=self._loop, name="engine-loop", daemon=True)
         self.thread.start()
 
@@ -262,6 +279,10 @@ class EngineWorker:
                         if isinstance(req, ShutdownSentinel):
                             self.shutdown_flag.set()
                         break
+                    if self.tool_runner is not None:
+                        self._start_tool_group(req)
+                        admitted = True
+                        continue
                     with self.lock:
                         rid = self.engine.add_request(req.prompt, req.generation_config, prompt_id=req.prompt_id, is_eval=req.is_eval,
                                                       ground_truth=req.ground_truth, dataset=req.dataset, raw_query=req.raw_query,
@@ -278,6 +299,9 @@ class EngineWorker:
                 with self.lock:
                     finished = self.engine.step()
                 for res in finished:
+                    if res.index in self.sessions:
+                        self._advance_tool_session(res)
+                        continue
                     req = self.pending.pop(res.index)
                     res.index = req.index
                     self._score(res, req)
@@ -286,9 +310,69 @@ class EngineWorker:
             self.error = e
             logger.exception("engine loop failed")
 
+    # ------------------------------------------------------------------ multi-turn groups
+    def _task_for(self, req: PromptRequest) -> dict | None:
+        cfg = req.env_config
+        if cfg is None:
+            return None
+        entries = getattr(cfg, "env_configs", None) or []
+        return dict(entries[0].kwargs) if entries else None
+
+    def _submit_turn(self, gid: int, j: int) -> None:
+        g = self.groups[gid]
+        prompt, cfg = g["sessions"][j].next_request()
+        with self.lock:
+            rid = self.engine.add_request(prompt, cfg)
+        self.sessions[rid] = (gid, j)
+
+    def _start_tool_group(self, req: PromptRequest) -> None:
+        gid = self._group_ids
+        self._group_ids += 1
+        n = req.generation_config.n
+        base = req.generation_config.seed if req.generation_config.seed is not None else self.engine.base_seed * 1000003 + gid
+        task = self._task_for(req)
+        sessions = [self.tool_runner.new_session(req.prompt, req.generation_config, base + j, task) for j in range(n)]
+        self.groups[gid] = {"req": req, "sessions": sessions, "open": n, "start": time.perf_counter(), "task": task}
+        for j in range(n):
+            self._submit_turn(gid, j)
+
+    def _advance_tool_session(self, res: GenerationResult) -> None:
+        gid, j = self.sessions.pop(res.index)
+        g = self.groups[gid]
+        s = g["sessions"][j]
+        again = self.tool_runner.on_turn(s, res.responses[0], res.logprobs[0], res.finish_reasons[0], g["task"])
+        if again:
+            self._submit_turn(gid, j)
+            return
+        self.tool_runner.close_session(s)
+        g["open"] -= 1
+        if g["open"] > 0:
+            return
+        from .data_types import RequestInfo, TokenStatistics
+
+        req, ss = g["req"], g["sessions"]
+        info = RequestInfo(num_calls=[x.num_calls for x in ss], timeouts=[int(x.timeout) for x in ss], tool_errors=[x.tool_error for x in ss],
+                           tool_outputs=[x.tool_output for x in ss], tool_runtimes=[x.tool_runtime for x in ss],
+                           tool_calleds=[x.tool_called for x in ss], tool_call_stats=[x.call_stats for x in ss],
+                           rollout_states=[x.state.to_dict() for x in ss])
+        now = time.perf_counter()
+        out = GenerationResult(responses=[x.tokens for x in ss], finish_reasons=[x.finish_reason or "stop" for x in ss],
+                               masks=[x.masks for x in ss], request_info=info, index=req.index, prompt_id=req.prompt_id,
+                               epoch_number=req.epoch_number,
+                               token_statistics=TokenStatistics(len(req.prompt), sum(len(x.tokens) for x in ss), now - g["start"], g["start"]),
+                               start_time=g["start"], logprobs=[x.logprobs for x in ss], model_step=self.engine.model_step,
+                               is_eval=req.is_eval, queries=[list(x.prompt) for x in ss], ground_truth=req.ground_truth,
+                               dataset=req.dataset, raw_query=req.raw_query)
+        del self.groups[gid]
+        self._score(out, req)
+        (self.eval_q if req.is_eval and self.eval_q is not None else self.results_q).put(out)
+
     def shutdown(self) -> None:
         self.shutdown_flag.set()
         self.thread.join(timeout=10)
+        if self.tool_runner is not None:
+            for p in self.tool_runner.pools.values():
+                p.close()
 
 
 # ======================================================================================= learner worker
@@ -511,7 +595,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
         engine = EngineWorker(spec, prompt_q, results_q, eval_q, reward_cfg, tokenizer, device=device, ops=args.ops, seed=args.seed,
                               max_model_len=max_len, num_blocks=None if torch.cuda.is_available() else 512,
                               gpu_memory_utilization=0.25 if torch.cuda.is_available() else 0.9,
-                              flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates)
+                              flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates, envs_config=tools_config)
         learners, engines = [learner], [engine]
         single_objs = True
     else:
@@ -532,7 +616,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
         init_flat = ray.get(learners[0].flat_weights_cpu.remote())
         engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
             spec, prompt_q, results_q, eval_q, reward_cfg, tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len,
-            None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates)
+            None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates, 256, tools_config)
             for i in range(vllm.vllm_num_engines)]
         ray.get([e.ready.remote() for e in engines] + [l.ready.remote() for l in learners])
         if cuda:

@@ -93,3 +93,30 @@ def test_grpo_multi_process_actors(tmp_path):
         ray.shutdown()
     assert out["training_step"] == 2
     assert os.path.exists(os.path.join(args.output_dir, "model.safetensors"))
+
+
+def test_engine_worker_runs_tool_sessions(tmp_path):
+    """An engine worker with a counter environment: every sample is a multi-turn session."""
+    import queue
+    import time
+
+    from transformers import AutoTokenizer
+
+    from open_instruct_b200.data_types import PromptRequest, SamplingConfig
+    from open_instruct_b200.environments.tools.utils import EnvsConfig
+    from open_instruct_b200.grpo_fast import EngineWorker
+    from open_instruct_b200.models import get_spec
+
+    tok = AutoTokenizer.from_pretrained(make_tokenizer(os.path.join(str(tmp_path), "tok")))
+    pq, rq = queue.Queue(), queue.Queue()
+    w = EngineWorker(get_spec("tiny"), pq, rq, None, None, tok, device="cpu", ops="ref", num_blocks=256,
+                     envs_config=EnvsConfig(envs=["counter"], tool_parser_type="vllm_hermes", max_steps=2))
+    try:
+        pq.put(PromptRequest(prompt=[5, 6, 7], generation_config=SamplingConfig(max_tokens=24, n=2, seed=1), index=3, prompt_id="0_3"))
+        res = rq.get(timeout=120)
+        assert res.index == 3 and len(res.responses) == 2
+        assert all(len(r) == len(m) == len(l) for r, m, l in zip(res.responses, res.masks, res.logprobs))
+        assert len(res.request_info.rollout_states) == 2 and res.reward_scores == [0.0, 0.0]
+        w.check_background_threads()
+    finally:
+        w.shutdown()
