@@ -165,11 +165,12 @@ class ArgumentParserPlus(argparse.ArgumentParser):
         ns = self.parse_args(args)
         return self._build(ns)
 
-    def parse_dict(self, cfg: dict, overrides=None):
+    def parse_dict(self, cfg: dict, overrides=None, allow_extra_keys: bool = False):
         """Build the dataclasses from a mapping (config file) plus CLI-style overrides."""
         unknown = [k for k in cfg if k not in self._fields]
-        if unknown:
+        if unknown and not allow_extra_keys:
             raise ValueError(f"unknown config keys: {sorted(unknown)}")
+        cfg = {k: v for k, v in cfg.items() if k in self._fields}
         argv = []
         for k, v in cfg.items():
             tp = self._hints[k]
@@ -186,18 +187,18 @@ class ArgumentParserPlus(argparse.ArgumentParser):
                 argv += [f"--{k}", str(v)]
         return self.parse_args_into_dataclasses(argv + list(overrides or []))
 
-    def parse_yaml_and_args(self, path: str, overrides=None):
+    def parse_yaml_and_args(self, path: str, overrides=None, allow_extra_keys: bool = False):
         import yaml
 
         with open(path) as fh:
             cfg = json.load(fh) if path.endswith(".json") else (yaml.safe_load(fh) or {})
-        return self.parse_dict(cfg, overrides)
+        return self.parse_dict(cfg, overrides, allow_extra_keys)
 
-    def parse(self, argv=None):
+    def parse(self, argv=None, allow_extra_keys: bool = False):
         """`script.py config.yaml [--k v ...]` or plain CLI.  Returns one dataclass or a tuple."""
         argv = list(sys.argv[1:] if argv is None else argv)
         if argv and not argv[0].startswith("-") and argv[0].rsplit(".", 1)[-1] in ("yaml", "yml", "json"):
-            out = self.parse_yaml_and_args(argv[0], argv[1:])
+            out = self.parse_yaml_and_args(argv[0], argv[1:], allow_extra_keys)
         else:
             out = self.parse_args_into_dataclasses(argv)
         return out[0] if len(out) == 1 else out

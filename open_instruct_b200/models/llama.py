@@ -185,13 +185,18 @@ class LlamaModel:
         return _fused().gemm(h, self.lm_head_weight())
 
     # ------------------------------------------------------------------ ref path
+    def _ref_params(self) -> dict:
+        """Parameter tensors of the autograd path: views of the flat leaf, or differentiable overrides
+        installed by an adapter (``param_override``)."""
+        return self.param_override if getattr(self, "param_override", None) is not None else self.layout.views(self.flat)
+
     def lm_head_weight_ref(self) -> torch.Tensor:
-        v = self.layout.views(self.flat)
+        v = self._ref_params()
         return v["embed"] if self.spec.tie_word_embeddings or "lm_head" not in v else v["lm_head"]
 
     def _ref_hidden(self, input_ids, position_ids, cu_seqlens) -> torch.Tensor:
         s = self.spec
-        v = self.layout.views(self.flat)  # autograd views of the single leaf
+        v = self._ref_params()  # autograd views of the single leaf
         x = v["embed"][input_ids]
         for i in range(s.num_layers):
             x = self._ref_layer(x, v, i, position_ids, cu_seqlens)

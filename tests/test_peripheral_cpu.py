@@ -1,0 +1,157 @@
+"""CPU tests for offline tooling: code execution, numpy shards, model merging, LoRA, legacy mixer."""
+
+import gzip
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from open_instruct_b200.models.spec import get_spec
+
+
+def test_code_exec_assert_and_stdio():
+    from open_instruct_b200.code_utils.code_utils import get_successful_tests_fast, get_successful_tests_stdio
+
+    prog = "def add(a, b):\n    return a + b\n"
+    res, times = get_successful_tests_fast(prog, ["assert add(1, 2) == 3", "assert add(1, 2) == 4", "import time; time.sleep(5)"], 1.0)
+    assert res == [1, 0, 0] and len(times) == 3
+    res, _ = get_successful_tests_stdio("print(int(input()) * 2)", [{"input": "4\n", "output": "8"}, {"input": "4\n", "output": "9"}], 1.0)
+    assert res == [1, 0]
+    # the guard makes destructive calls unusable inside the child, and the parent is untouched
+    res, _ = get_successful_tests_fast("import os\nos.remove('x')", ["assert True"], 1.0)
+    assert res == [0] and os.remove is not None
+    assert get_successful_tests_fast("import subprocess", ["assert True"], 1.0)[0] == [0]
+
+
+def test_code_api_routes():
+    from fastapi.testclient import TestClient
+
+    from open_instruct_b200.code_utils.api import app
+
+    try:
+        c = TestClient(app)
+    except Exception as e:  # httpx missing
+        pytest.skip(str(e))
+    assert c.get("/health").json() == {"status": "healthy"}
+    r = c.post("/test_program", json={"program": "x = 1", "tests": ["assert x == 1", "assert x == 2"], "max_execution_time": 1.0}).json()
+    assert r["results"] == [1, 0]
+
+
+def test_shard_writer_resume_and_reader(tmp_path):
+    from open_instruct_b200.data.numpy_dataset_conversion import NumpyPackedFSLDataset, ShardWriter, select_token_dtype
+
+    assert select_token_dtype(256) is np.uint8 and select_token_dtype(257) is np.uint16 and select_token_dtype(70000) is np.uint32
+    rng = np.random.default_rng(0)
+    docs = [rng.integers(0, 1000, size=int(n)) for n in rng.integers(3, 40, size=30)]
+    w = ShardWriter(tmp_path, 1000, sync_every=1)
+    for d in docs[:10]:
+        w.append(d, np.where(np.arange(len(d)) < 2, -100, d))
+    w.sync()
+    for f in w.fh.values():
+        f.close()
+    # simulate a crash in the middle of a sample: data written, commit record cut in half
+    with open(tmp_path / "_tokens.partial.bin", "ab") as f:
+        f.write(b"\x01\x02\x03\x04\x05\x06")
+    with open(tmp_path / "_boundaries.partial.bin", "ab") as f:
+        f.write(b"\x00" * 7)
+    w = ShardWriter(tmp_path, 1000, resume=True)
+    assert w.num_samples == 10 and w.position == sum(len(d) for d in docs[:10])
+    for d in docs[10:]:
+        w.append(d, np.where(np.arange(len(d)) < 2, -100, d))
+    chunks = w.finalize(max_shard_gb=200 * 2 / 1024**3)  # 200 tokens of uint16 per shard
+    total = sum(len(d) for d in docs)
+    assert chunks[-1][1] == total and len(chunks) == -(-total // 200)
+    flat = np.concatenate(docs)
+    got = np.concatenate([np.memmap(tmp_path / f"token_ids_part_{i:04d}.npy", mode="r", dtype=np.uint16) for i in range(len(chunks))])
+    assert np.array_equal(got, flat)
+    with gzip.open(tmp_path / "token_ids_part_0000.csv.gz", "rt") as f:
+        first = [tuple(map(int, ln.split(","))) for ln in f]
+    assert first[0] == (0, len(docs[0])) and first[-1][1] == 200
+    ds = NumpyPackedFSLDataset(tmp_path, 64, 1000)
+    assert len(ds) == sum((e - s) // 64 for s, e in chunks)
+    win = ds[1]
+    assert np.array_equal(win.input_ids, flat[64:128]) and win.cu_seqlens[0] == 0 and win.cu_seqlens[-1] == 64
+    assert not win.label_mask[win.cu_seqlens[1]:win.cu_seqlens[1] + 2].any()
+
+
+def _tiny_ckpt(path, seed):
+    from open_instruct_b200.ckpt.hf_io import save_hf_checkpoint
+    from open_instruct_b200.models.llama import LlamaModel
+
+    m = LlamaModel(get_spec("tiny"), seed=seed)
+    save_hf_checkpoint(m.flat, m.spec, str(path), dtype=torch.float32)
+    return m
+
+
+def test_merge_models(tmp_path):
+    from safetensors.torch import load_file
+
+    from open_instruct_b200.ckpt.merge_models import merge_models
+
+    a, b = _tiny_ckpt(tmp_path / "a", 1), _tiny_ckpt(tmp_path / "b", 2)
+    merge_models([str(tmp_path / "a"), str(tmp_path / "b")], str(tmp_path / "m"), [1.0, 3.0], dtype="float32")
+    sd = load_file(str(tmp_path / "m" / "model.safetensors"))
+    exp = 0.25 * a.p["l0.wo"] + 0.75 * b.p["l0.wo"]
+    assert torch.allclose(sd["model.layers.0.self_attn.o_proj.weight"], exp.detach(), atol=1e-6)
+    assert (tmp_path / "m" / "config.json").exists()
+    with pytest.raises(ValueError):
+        merge_models([str(tmp_path / "a")], str(tmp_path / "x"), [1.0, 2.0])
+
+
+def test_lora_ref_grads_match_merged_contraction(tmp_path):
+    from safetensors.torch import load_file
+
+    from open_instruct_b200.models.llama import LlamaModel
+    from open_instruct_b200.models.lora import LoRAAdapters, merge_lora_checkpoint
+
+    spec = get_spec("tiny")
+    m = _tiny_ckpt(tmp_path / "base", 3)
+    lora = LoRAAdapters(spec, m.layout, rank=4, alpha=8.0, seed=1)
+    with torch.no_grad():
+        for k in lora.B:
+            lora.B[k].normal_(0, 0.05)
+    base = m.flat.detach().clone()
+    ids = torch.randint(0, spec.vocab_size, (24,))
+    pos = torch.cat([torch.arange(10), torch.arange(14)])
+    cu = torch.tensor([0, 10, 24], dtype=torch.int32)
+    labels = torch.roll(ids, -1)
+    # (1) autograd through the adapters
+    lora.apply_ref(m, base)
+    loss = -m.token_logprobs(ids, pos, cu, labels)[0].mean()
+    loss.backward()
+    g_auto = lora.flat.grad.clone()
+    # (2) merged weights -> dL/dW_eff -> contraction (what the fused path does)
+    m2 = LlamaModel(spec, flat=base.clone())
+    lora.merge_into(m2, base)
+    m2.flat.requires_grad_(True)
+    m2.p = m2.layout.views(m2.flat)
+    loss2 = -m2.token_logprobs(ids, pos, cu, labels)[0].mean()
+    loss2.backward()
+    assert abs(loss.item() - loss2.item()) < 1e-5
+    m2.main_grad = m2.flat.grad.float()
+    g_merged = lora.pull_grads(m2)
+    assert torch.allclose(g_auto, g_merged, atol=1e-5, rtol=1e-4)
+    # (3) adapter files fold into the checkpoint
+    lora.save(str(tmp_path / "adapter"))
+    n = merge_lora_checkpoint(str(tmp_path / "base"), str(tmp_path / "adapter"), str(tmp_path / "merged"), dtype=torch.float32)
+    assert n == len(lora.slots)
+    sd = load_file(str(tmp_path / "merged" / "model.safetensors"))
+    k = "model.layers.1.mlp.up_proj.weight"
+    assert torch.allclose(sd[k], m2.layout.views(m2.flat.detach())["l1.w_gate_up"][spec.intermediate_size:], atol=1e-6)
+
+
+def test_legacy_get_datasets(tmp_path):
+    from open_instruct_b200.data.legacy_mix import get_datasets
+
+    a, b = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    a.write_text("\n".join(json.dumps({"messages": [{"role": "user", "content": f"q{i}"}, {"role": "assistant", "content": "a"}]}) for i in range(10)))
+    b.write_text("\n".join(json.dumps({"instruction": f"do {i}", "input": "", "output": "ok"}) for i in range(8)))
+    out = get_datasets({str(a): 0.5, str(b): 1.0}, splits=["train"], columns_to_keep=["messages"], add_source_col=True, keep_ids=True)
+    assert len(out["train"]) == 5 + 8 and set(out["train"].column_names) == {"messages", "id", "source"}
+    assert out["train"][12]["messages"][1]["content"] == "ok"
+    out = get_datasets([str(a), "3", str(b), "2"], splits=["train"], columns_to_keep=["messages"])
+    assert len(out["train"]) == 5
+    with pytest.raises(NotImplementedError):
+        get_datasets({str(a): 0.5, str(b): 3}, splits=["train"])
