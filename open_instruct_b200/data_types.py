@@ -133,5 +133,36 @@ class CollatedBatchData:
         return CollatedBatchData(**{k: pm(v) for k, v in self.__dict__.items()})
 
 
+@dataclass
+class Batch:
+    """Column-wise container of prompts with list-like indexing: ``b[3]``, ``b[2:5]``, ``b[[1, 4]]`` all give a
+    ``Batch`` (cf. ``open_instruct/model_utils.py:118-174``).  Optional columns stay ``None``."""
+
+    queries: list
+    ground_truths: list
+    datasets: list
+    raw_queries: list | None = None
+    decoded_responses: list | None = None
+    indices: list | None = None
+    scores: list | None = None
+    active_tools: list | None = None
+    model_steps: list = field(default_factory=list)
+
+    def __len__(self) -> int:
+        return len(self.queries)
+
+    def __getitem__(self, key) -> "Batch":
+        if isinstance(key, slice):
+            pick = lambda col: col[key]
+        elif isinstance(key, int):
+            pick = lambda col: [col[key]]
+        else:
+            pick = lambda col: [col[i] for i in key]
+        cols = {}
+        for name, col in self.__dict__.items():
+            cols[name] = None if col is None else (pick(col) if (col or name != "model_steps") else [])
+        return Batch(**cols)
+
+
 class ShutdownSentinel:
     """Put on a queue to tell its consumer to stop."""

@@ -308,3 +308,21 @@ extern "C" int b200_multi_push(const void* src, const void* const* dst_ptrs, int
   else multi_push_kernel<false><<<148 * 8, 256, 0, st>>>(src, make_ptrs(dst_ptrs, n_dst), n_dst, off, n);
   return static_cast<int>(cudaGetLastError());
 }
+
+// Lets kernels running on `dev` dereference pointers into `peer`'s memory (needed before a kernel writes through a
+// CUDA-IPC mapping of another GPU's buffer; copies issued by the runtime enable it on their own, raw kernels do not).
+// Returns 0 on success or if access was already enabled, 1 if the two devices cannot reach each other, else the CUDA error.
+extern "C" int b200_enable_peer_access(int dev, int peer) {
+  if (dev == peer) return 0;
+  int can = 0;
+  cudaError_t e = cudaDeviceCanAccessPeer(&can, dev, peer);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (!can) return 1;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(dev);
+  e = cudaDeviceEnablePeerAccess(peer, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+  cudaSetDevice(prev);
+  return static_cast<int>(e);
+}

@@ -24,12 +24,30 @@ _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
 lib._SIGNATURES["b200_multi_push"] = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), _I, _L, _L, _I, _P]
 
 
+_peer_ok: set[tuple[int, int]] = set()
+
+
+def ensure_peer_access(dev: int, peer: int) -> None:
+    """Kernels on ``dev`` may then store into ``peer``'s memory.  Idempotent; raises if the GPUs are not connected."""
+    if dev == peer or (dev, peer) in _peer_ok:
+        return
+    so = lib.load_ops()
+    so.b200_enable_peer_access.argtypes = [_I, _I]
+    so.b200_enable_peer_access.restype = _I
+    rc = so.b200_enable_peer_access(dev, peer)
+    if rc:
+        raise lib.KernelError(f"cannot enable peer access from GPU {dev} to GPU {peer} (code {rc})")
+    _peer_ok.add((dev, peer))
+
+
 def push_slice(src: torch.Tensor, dsts: list[torch.Tensor], lo: int, hi: int) -> None:
     """``dst[lo:hi] = bf16(src[lo:hi])`` for every destination (CUDA: one kernel for all of them)."""
     if hi <= lo or not dsts:
         return
     if src.is_cuda and all(d.is_cuda and d.dtype == torch.bfloat16 for d in dsts) and lo % 8 == 0 and len(dsts) <= 8:
         so = lib.load_ops()
+        for d in dsts:
+            ensure_peer_access(src.device.index, d.device.index)
         fn = so.b200_multi_push
         fn.argtypes = [_P, ctypes.POINTER(ctypes.c_void_p), _I, _L, _L, _I, _P]
         fn.restype = _I

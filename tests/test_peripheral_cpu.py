@@ -155,3 +155,47 @@ def test_legacy_get_datasets(tmp_path):
     assert len(out["train"]) == 5
     with pytest.raises(NotImplementedError):
         get_datasets({str(a): 0.5, str(b): 3}, splits=["train"])
+
+
+def _completions():
+    rows = []
+    for p in range(3):
+        for c in range(2):
+            rows.append({"messages": [{"role": "user", "content": f"q{p}"}, {"role": "assistant", "content": f"a{p}{c}"}],
+                         "model_completion": f"a{p}{c}", "reference_completion": f"ref{p}"})
+    return rows
+
+
+def test_rejection_sampling_select_and_vote():
+    from open_instruct_b200.rejection_sampling.rejection_sampling import majority_vote, select
+
+    length = lambda convs: [float(len(c[-1]["content"])) + (0.5 if c[-1]["content"].endswith("1") else 0.0) for c in convs]
+    neg = lambda convs: [-x for x in length(convs)]
+    table, per = select(_completions(), {"len": length, "len2": length, "neg": neg}, num_completions=2)
+    # reference ("refP", 4 chars) is the longest, "aP0" the shortest
+    assert [c[-1]["content"] for c in table["chosen"]] == ["ref0", "ref1", "ref2"]
+    assert [c[-1]["content"] for c in table["rejected"]] == ["a00", "a10", "a20"]
+    assert len(per["messages"]) == 9 and set(table["chosen_score"][0]) == {"len", "len2", "neg"}
+    table, per = select(_completions(), {"len": length}, num_completions=2, include_reference=False)
+    assert [c[-1]["content"] for c in table["chosen"]] == ["a01", "a11", "a21"] and len(per["messages"]) == 6
+    v = majority_vote({"a": torch.tensor([1, 2]), "b": torch.tensor([1, 3]), "c": torch.tensor([0, 3])})
+    assert v.tolist() == [1, 3]
+
+
+def test_synthetic_preferences_with_fake_judge(tmp_path):
+    from open_instruct_b200.rejection_sampling import synthetic_preference_dataset as spd
+
+    src = tmp_path / "c.jsonl"
+    src.write_text("\n".join(json.dumps(r) for r in _completions()))
+
+    async def judge(messages):
+        # prefers whichever shown response is the reference answer, else response 0
+        text = messages[0]["content"]
+        r1 = text.split("Response 1:")[1]
+        return "Comparison: ok\nPreferred: " + ("1" if "'ref" in r1 else "0")
+
+    out = spd.main(spd.Args(input_filename=str(src), save_filename=str(tmp_path / "o.jsonl"), num_completions=2), judge=judge)
+    assert len(out["chosen"]) == 9  # 3 prompts x C(3, 2)
+    for ch, rj in zip(out["chosen"], out["rejected"]):
+        assert not rj[-1]["content"].startswith("ref") and ch[:-1] == rj[:-1]
+    assert sum(c[-1]["content"].startswith("ref") for c in out["chosen"]) == 6
