@@ -87,8 +87,17 @@ def _serve(cls, args, kwargs, address, ready, max_concurrency, env):
     pool = cf.ThreadPoolExecutor(max_workers=max_concurrency)
     stop = threading.Event()
 
+    def bind_device():
+        # CUDA's current device is a per-thread setting: give every serving thread the actor's GPU
+        dev = getattr(obj, "device", None) or getattr(getattr(obj, "engine", None), "device", None)
+        if dev is not None and str(dev).startswith("cuda"):
+            import torch
+
+            torch.cuda.set_device(torch.device(str(dev)))
+
     def handle(conn):
         try:
+            bind_device()
             while not stop.is_set():
                 try:
                     msg = _recv(conn)

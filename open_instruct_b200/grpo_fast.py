@@ -249,10 +249,9 @@ class EngineWorker:
 
     def weight_buffer_ipc(self):
         """Picklable description of the parameter buffer for a CUDA-IPC mapping in another process."""
-        from torch.multiprocessing.reductions import reduce_tensor
+        from .parallel.weight_sync import export_buffer
 
-        fn, a = reduce_tensor(self.engine.model.flat.detach())
-        return fn, a
+        return export_buffer(self.engine.model.flat.detach())
 
     def _score(self, res: GenerationResult, req: PromptRequest) -> None:
         decoded = self.tokenizer.batch_decode(res.responses, skip_special_tokens=True) if self.tokenizer is not None else \
@@ -268,6 +267,8 @@ class EngineWorker:
 
     def _loop(self) -> None:
         try:
+            if self.engine.device.type == "cuda":
+                torch.cuda.set_device(self.engine.device)  # the current device is per thread; raw kernel launches follow it
             while not self.shutdown_flag.is_set():
                 admitted = False
                 while self.engine.num_active() < self.engine.max_running and not self.should_stop.is_set():
@@ -440,7 +441,9 @@ class LearnerWorker:
 
     # ---- weight sync into engines living in other processes (CUDA IPC + multi-destination copy kernel)
     def connect_engines(self, ipc_descs: list) -> int:
-        self._engine_views = [fn(*a) for fn, a in ipc_descs]
+        from .parallel.weight_sync import import_buffer
+
+        self._engine_views = [import_buffer(d, self.device.index) for d in ipc_descs]
         return len(self._engine_views)
 
     def push_weights(self) -> float:

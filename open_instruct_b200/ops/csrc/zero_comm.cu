@@ -326,3 +326,57 @@ extern "C" int b200_enable_peer_access(int dev, int peer) {
   cudaSetDevice(prev);
   return static_cast<int>(e);
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Cross-process buffer sharing for the weight push.  The exporting process describes the allocation that contains
+// `ptr` (64-byte IPC handle + byte offset of `ptr` inside it); the importing process opens the handle WITH ITS OWN
+// COMPUTE DEVICE CURRENT, so the mapping is created in the address space of the device whose kernels will store
+// through it (an IPC mapping belongs to the context that opened it; peer access to the exporting GPU is switched on
+// by the open itself via the lazy-peer-access flag).
+// ---------------------------------------------------------------------------------------------------------------
+typedef CUresult (*GetAddressRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+extern "C" int b200_ipc_export(const void* ptr, unsigned char* handle_out, long long* offset_out, long long* size_out) {
+  static GetAddressRangeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return -1;
+    fn = reinterpret_cast<GetAddressRangeFn>(p);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (fn(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS) return -2;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle_out, &h, 64);
+  *offset_out = static_cast<long long>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  *size_out = static_cast<long long>(size);
+  return 0;
+}
+
+// Opens the handle with device `dev` current; *base_out is the mapped base of the exporter's allocation.
+extern "C" int b200_ipc_open(int dev, const unsigned char* handle, void** base_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(dev);
+  cudaError_t e = cudaIpcOpenMemHandle(base_out, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) cudaGetLastError();
+  cudaSetDevice(prev);
+  return static_cast<int>(e);
+}
+
+extern "C" int b200_ipc_close(int dev, void* base) {
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(dev);
+  cudaError_t e = cudaIpcCloseMemHandle(base);
+  if (e != cudaSuccess) cudaGetLastError();
+  cudaSetDevice(prev);
+  return static_cast<int>(e);
+}

@@ -199,3 +199,63 @@ def test_synthetic_preferences_with_fake_judge(tmp_path):
     for ch, rj in zip(out["chosen"], out["rejected"]):
         assert not rj[-1]["content"].startswith("ref") and ch[:-1] == rj[:-1]
     assert sum(c[-1]["content"].startswith("ref") for c in out["chosen"]) == 6
+
+
+def test_launcher_spec():
+    import argparse
+
+    from open_instruct_b200 import launch
+
+    own, cmd = launch.split_command(["--num_gpus", "4", "--", "python", "-m", "open_instruct_b200.finetune", "r.yaml", "--with_tracking",
+                                     "--wandb_entity", "x", "--learning_rate", "1e-5"])
+    assert own == ["--num_gpus", "4"] and launch.training_module(cmd) == "open_instruct_b200.finetune"
+    c = launch.caching_command(cmd)
+    assert c[-1] == "--cache_dataset_only" and "--with_tracking" not in c and "x" not in c and "1e-5" in c
+    opts = argparse.Namespace(num_gpus=4, num_nodes=2, node_rank=1, master_addr="10.0.0.1", master_port=1234, env=["A=b"], no_auto_dataset_cache=False,
+                              auto_output_dir_path="/out", description="")
+    spec = launch.build_spec(opts, cmd)
+    assert [s["name"] for s in spec["steps"]] == ["cache_dataset", "train"] and spec["env"]["A"] == "b"
+    train = spec["steps"][1]["command"]
+    assert train[1:3] == ["-m", "torch.distributed.run"] and "--nproc-per-node=4" in train and "--node-rank=1" in train
+    assert "--output_dir" in train and train[train.index("--output_dir") + 1].startswith("/out/finetune_")
+    spec = launch.build_spec(opts, ["python", "-m", "open_instruct_b200.grpo_fast", "--output_dir", "o"])
+    assert spec["steps"][1]["command"][1:3] == ["-m", "open_instruct_b200.grpo_fast"]
+
+
+def test_resource_plan():
+    from open_instruct_b200.grpo_fast_resource_plan import build_plan, check_or_raise
+
+    plan = build_plan([6], False, 2, 1)
+    assert plan.min_gpus == 8 and plan.min_cpus == 60 + 2 + 2 + 1
+    assert plan.shortfalls({"GPU": 8, "CPU": 100}) == []
+    assert "learner group requires GPU=6" in plan.shortfalls({"GPU": 4, "CPU": 100})[0]
+    assert "full topology requires at least GPU=8" in plan.shortfalls({"GPU": 7, "CPU": 100})[0]
+    with pytest.raises(RuntimeError):
+        check_or_raise(plan, {"GPU": 7, "CPU": 100})
+    assert len(check_or_raise(plan, {"GPU": 8, "CPU": 10})) == 1
+    assert build_plan([1], True, 1, 1).min_gpus == 1
+
+
+def test_finetune_numpy_end_to_end(tmp_path):
+    from open_instruct_b200 import finetune_numpy as fn
+    from open_instruct_b200.data.numpy_dataset_conversion import NumpyPackedFSLDataset, ShardWriter
+
+    spec = get_spec("tiny")
+    rng = np.random.default_rng(1)
+    w = ShardWriter(tmp_path / "data", spec.vocab_size)
+    for _ in range(40):
+        d = rng.integers(1, spec.vocab_size, size=int(rng.integers(5, 30)))
+        w.append(d, np.where(np.arange(len(d)) < 2, -100, d))
+    w.finalize()
+    ds = NumpyPackedFSLDataset(tmp_path / "data", 32, spec.vocab_size)
+    b = fn.window_to_batch([ds[0], ds[1]])
+    cu = b["cu_seq_lens_q"]
+    assert cu[-1] == 64 and 32 in cu.tolist() and (b["position_ids"][cu[:-1].long()] == 0).all()
+    assert (b["labels_shifted"][cu[1:].long() - 1] == -100).all()
+    args = fn.Args(model_name_or_path="tiny", dataset_path=str(tmp_path / "data"), sequence_length=32, global_batch_size=128,
+                   rank_microbatch_size=64, max_train_steps=3, save_folder=str(tmp_path / "out"), save_interval=2, learning_rate=1e-3)
+    m = fn.main(args)
+    assert m["completed_steps"] == 3 and np.isfinite(m["train_loss"])
+    assert (tmp_path / "out" / "hf" / "config.json").exists() and (tmp_path / "out" / "step_2").exists()
+    args.max_train_steps = 4
+    assert fn.main(args)["completed_steps"] == 4  # resumed from step_2, ran 2 more
