@@ -15,36 +15,9 @@
 // No TMA is used here: all remote traffic is ordinary ld/st (or multimem) from this GPU's SMs.
 // Every wait is bounded and reports through the status word instead of hanging.
 #include "common.cuh"
+#include "peer.cuh"
 
 namespace b200 {
-
-constexpr int MAX_PEERS = 8;
-struct PeerPtrs {
-  void* p[MAX_PEERS];
-};
-
-// signal-pad slots (uint32 index from the pad base); torch's own channels live below 1024
-constexpr int PAD_BARRIER = 1024;       // [+rank]
-constexpr int PAD_SCALAR_FLAG = 1040;   // [+rank]
-constexpr int PAD_SCALAR_VAL = 1056;    // [+parity*8 + rank] (float bits)
-
-__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-  return v;
-}
-// wait until *addr has reached `epoch` (wrap-safe); false when the time limit ran out
-__device__ __forceinline__ bool wait_epoch(const uint32_t* addr, uint32_t epoch, long long limit_cycles) {
-  const long long t0 = clock64();
-  while (static_cast<int32_t>(ld_acquire_sys(addr) - epoch) < 0) {
-    if (clock64() - t0 > limit_cycles) return false;
-    __nanosleep(64);
-  }
-  return true;
-}
 
 // One thread per peer: publish my arrival in the peer's pad, then wait for the peer's in mine.
 __global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, long long limit_cycles,
@@ -194,11 +167,6 @@ zero_adamw_allgather_kernel(float* __restrict__ master, float* __restrict__ m, f
   }
 }
 
-static PeerPtrs make_ptrs(const void* const* host, int world) {
-  PeerPtrs pp;
-  for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < world ? const_cast<void*>(host[i]) : nullptr;
-  return pp;
-}
 
 }  // namespace b200
 

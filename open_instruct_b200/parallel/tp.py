@@ -1,0 +1,110 @@
+"""Tensor parallelism for the rollout engine: weight sharding and the fused all-reduce + residual + RMSNorm.
+
+Megatron-style split of a decoder layer over ``tp`` GPUs (what vLLM does for ``--vllm_tensor_parallel_size``,
+``open_instruct/vllm_utils.py:1234-1270``): q/k/v and gate/up are column-parallel (each rank keeps ``heads / tp``
+heads and ``intermediate / tp`` channels), o_proj and down_proj are row-parallel, so each of the two produces a
+partial ``[T, hidden]`` that must be summed over ranks.  Embedding, norms and lm_head are replicated.  Because a
+rank's shard is itself a valid model layout with fewer heads and a narrower MLP, the engine runs its ordinary layer
+stack on ``local_spec`` and only swaps the "add residual + norm" step for ``TPContext.reduce_norm``, which sums the
+partials out of the peers' symmetric buffers inside the same kernel (``ops/csrc/tp_comm.cu``).
+
+All ranks of a TP group run the same schedule on the same requests (SPMD): the reduced activations are bitwise
+identical on every rank, and so are the sampled tokens.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..models.spec import ModelSpec, ParamLayout
+from ..ops import lib
+from ..ops.lib import ptr, status_word, stream_ptr
+from .symm import _ptr_array
+
+_P, _I, _F, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_uint
+_PP = ctypes.POINTER(ctypes.c_void_p)
+lib._SIGNATURES["b200_tp_allreduce_norm"] = [_PP, _PP, _I, _I, _U, _P, _P, _P, _P, _I, _I, _F, _I, _P, _P]
+
+
+def local_spec(spec: ModelSpec, tp: int) -> ModelSpec:
+    if spec.num_heads % tp or spec.num_kv_heads % tp or spec.intermediate_size % tp:
+        raise ValueError(f"heads {spec.num_heads}/{spec.num_kv_heads} and intermediate size {spec.intermediate_size} must divide by tp={tp}")
+    return spec.replace(num_heads=spec.num_heads // tp, num_kv_heads=spec.num_kv_heads // tp, intermediate_size=spec.intermediate_size // tp)
+
+
+@torch.no_grad()
+def shard_flat(full_flat: torch.Tensor, spec: ModelSpec, rank: int, tp: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """This rank's shard of a full flat parameter buffer, laid out as ``ParamLayout(local_spec(spec, tp))``."""
+    ls = local_spec(spec, tp)
+    full, loc = ParamLayout(spec), ParamLayout(ls)
+    if out is None:
+        out = torch.empty(loc.total, dtype=full_flat.dtype, device=full_flat.device)
+    fv, lv = full.views(full_flat), loc.views(out)
+    hq, hk, f, d = ls.num_heads * ls.head_dim, ls.num_kv_heads * ls.head_dim, ls.intermediate_size, spec.head_dim
+    for name, dst in lv.items():
+        src = fv[name]
+        leaf = name.split(".", 1)[-1]
+        if leaf in ("wqkv", "bqkv"):
+            q0, k0, v0 = 0, spec.q_dim, spec.q_dim + spec.kv_dim
+            dst.copy_(torch.cat([src[q0 + rank * hq: q0 + (rank + 1) * hq], src[k0 + rank * hk: k0 + (rank + 1) * hk],
+                                 src[v0 + rank * hk: v0 + (rank + 1) * hk]], 0))
+        elif leaf == "wo":
+            dst.copy_(src[:, rank * hq:(rank + 1) * hq])
+        elif leaf == "w_gate_up":
+            F = spec.intermediate_size
+            dst.copy_(torch.cat([src[rank * f:(rank + 1) * f], src[F + rank * f: F + (rank + 1) * f]], 0))
+        elif leaf == "w_down":
+            dst.copy_(src[:, rank * f:(rank + 1) * f])
+        else:
+            dst.copy_(src)
+    return out
+
+
+class TPContext:
+    """Two symmetric ``[max_tokens, hidden]`` bf16 buffers for the row-parallel outputs + the fused reduction."""
+
+    def __init__(self, hidden: int, max_tokens: int, device, group=None, peer_timeout_ms: int = 20000):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.device, self.hidden, self.max_tokens = torch.device(device), hidden, max_tokens
+        self.peer_timeout_ms = peer_timeout_ms
+        self.bufs, self._ptrs = [], []
+        for _ in range(2):
+            b = symm_mem.empty(max_tokens * hidden, dtype=torch.bfloat16, device=self.device)
+            b.zero_()
+            h = symm_mem.rendezvous(b, self.group)
+            self.bufs.append(b)
+            self._ptrs.append([int(p) for p in h.buffer_ptrs])
+            self._pads = _ptr_array(h.signal_pad_ptrs)
+            self._h = h
+        self._next, self._epoch = 0, 0
+        fn = lib.load_ops().b200_tp_allreduce_norm
+        fn.argtypes, fn.restype = lib._SIGNATURES["b200_tp_allreduce_norm"], ctypes.c_int
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def out_buffer(self, tokens: int) -> torch.Tensor:
+        """The symmetric buffer the next row-parallel GEMM must write its ``[tokens, hidden]`` partial into."""
+        if tokens > self.max_tokens:
+            raise ValueError(f"{tokens} tokens exceed the tensor-parallel exchange buffer ({self.max_tokens})")
+        return self.bufs[self._next][: tokens * self.hidden].view(tokens, self.hidden)
+
+    def reduce_norm(self, partial: torch.Tensor, weight: torch.Tensor | None, eps: float, res: torch.Tensor | None = None):
+        """``h = res + sum_ranks partial``; ``y = rmsnorm(h) * weight``.  Returns ``(y, h)`` (``y`` is None without a weight)."""
+        T, D = partial.shape
+        buf = self.bufs[self._next]
+        if partial.data_ptr() != buf.data_ptr():
+            raise ValueError("the partial must live in the buffer handed out by out_buffer()")
+        h = torch.empty(T, D, dtype=torch.bfloat16, device=self.device)
+        y = torch.empty_like(h) if weight is not None else None
+        self._epoch += 1
+        lib.call("b200_tp_allreduce_norm", _ptr_array(self._ptrs[self._next]), self._pads, self.rank, self.world, self._epoch,
+                 ptr(res) if res is not None else None, ptr(weight) if weight is not None else None, ptr(h), ptr(y) if y is not None else None,
+                 T, D, eps, self.peer_timeout_ms, ptr(status_word(self.device)), stream_ptr())
+        self._next ^= 1
+        return y, h

@@ -122,7 +122,9 @@ class RolloutEngine:
 
     def __init__(self, spec: ModelSpec, device="cuda", ops: str = "auto", num_blocks: int | None = None,
                  gpu_memory_utilization: float = 0.85, max_running: int = 256, max_model_len: int = 8192, seed: int = 0,
-                 flat: torch.Tensor | None = None, eos_token_ids: list[int] | None = None, tokenizer=None):
+                 flat: torch.Tensor | None = None, eos_token_ids: list[int] | None = None, tokenizer=None, tp=None):
+        # ``tp``: a ``parallel.tp.TPContext``; ``spec`` and ``flat`` are then this rank's shard (``local_spec`` / ``shard_flat``)
+        self.tp = tp
         self.spec = spec
         self.device = torch.device(device)
         if ops == "auto":
@@ -296,20 +298,29 @@ class RolloutEngine:
             pos32 = pos.to(torch.int32)
             impl = "2cta" if T > 128 else "1cta"
             stream, delta = f.embedding_fwd(p["embed"], ids), None
+            tp = self.tp
+
+            def add_norm(partial, w, res):
+                """(normed, new residual stream): local fused add+norm, or the cross-rank reduction fused with it."""
+                if tp is None or res is None:
+                    y, h, _ = f.rmsnorm_fwd(partial, w, s.rms_norm_eps, res=res)
+                    return y, h
+                return tp.reduce_norm(partial, w, s.rms_norm_eps, res=res)
+
+            row_out = (lambda: tp.out_buffer(T)) if tp is not None else (lambda: None)
             for i in range(s.num_layers):
-                n1, h_in, _ = f.rmsnorm_fwd(delta if delta is not None else stream, p[f"l{i}.attn_norm"], s.rms_norm_eps,
-                                            res=stream if delta is not None else None)
+                n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
                 qkv = f.gemm(n1, p[f"l{i}.wqkv"], impl=impl)
                 f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
                 call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
                      s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
                 attn = attn_fn(i, qkv)
-                o = f.gemm(attn, p[f"l{i}.wo"], impl=impl)
-                n2, h_mid, _ = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=h_in)
+                o = f.gemm(attn, p[f"l{i}.wo"], row_out(), impl=impl)
+                n2, h_mid = add_norm(o, p[f"l{i}.mlp_norm"], h_in)
                 act = f.swiglu_fwd(f.gemm(n2, p[f"l{i}.w_gate_up"], impl=impl))
-                delta = f.gemm(act, p[f"l{i}.w_down"], impl=impl)
+                delta = f.gemm(act, p[f"l{i}.w_down"], row_out(), impl=impl)
                 stream = h_mid
-            nf, _, _ = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
+            nf, _ = add_norm(delta, p["final_norm"], stream)
             return nf
         x = p["embed"][ids]
         for i in range(s.num_layers):

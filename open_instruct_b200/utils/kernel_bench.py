@@ -60,6 +60,7 @@ def main():
     ap.add_argument("--json", default="")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--impl", default=None, help="GEMM kernel: 1cta | 2cta (default: library default)")
+    ap.add_argument("--shapes", default="", help="GEMM: comma-separated subset of qkv,o,gate_up,down,lm_head")
     ap.add_argument("--doc_len", type=int, default=0, help="attention: document length (0 = one document of --tokens)")
     args = ap.parse_args()
     from open_instruct_b200.ops import fused, lib
@@ -84,7 +85,10 @@ def main():
     if not only or "gemm" in only:
         shapes = {"qkv": (T, (Hq + 2 * Hkv) * Dh, D), "o": (T, D, Hq * Dh), "gate_up": (T, 2 * F, D), "down": (T, D, F),
                   "lm_head": (T, V, D)}
+        pick = set(filter(None, args.shapes.split(",")))
         for name, (M, N, K) in shapes.items():
+            if pick and name not in pick:
+                continue
             x, w, dy = bf(M, K), bf(N, K), bf(M, N)
             fl = 2.0 * M * N * K
             rec(f"gemm_fwd_{name}", time_op(lambda: fused.gemm(x, w, impl=args.impl), args.iters), fl)

@@ -1,0 +1,39 @@
+"""Tensor-parallel sharding: the per-rank shards, run as the engine runs them (sum of partials after the two
+row-parallel projections), reproduce the unsharded model."""
+
+import torch
+
+from open_instruct_b200.models.llama import LlamaModel
+from open_instruct_b200.models.spec import get_spec
+from open_instruct_b200.ops import ref
+from open_instruct_b200.parallel.tp import local_spec, shard_flat
+
+
+def test_sharded_layers_sum_to_full_model():
+    spec = get_spec("tiny")
+    m = LlamaModel(spec, seed=0)
+    full = m.flat.detach()
+    ids = torch.randint(0, spec.vocab_size, (12,))
+    pos = torch.cat([torch.arange(5), torch.arange(7)])
+    cu = torch.tensor([0, 5, 12], dtype=torch.int32)
+    want = m.hidden_states(ids, pos, cu).detach()
+    for tp in (2, spec.num_kv_heads):
+        ls = local_spec(spec, tp)
+        shards = [LlamaModel(ls, flat=shard_flat(full, spec, r, tp)) for r in range(tp)]
+        views = [s.layout.views(s.flat.detach()) for s in shards]
+        x = views[0]["embed"][ids]
+        for i in range(spec.num_layers):
+            parts = []
+            for s, p in zip(shards, views):
+                n1 = ref.rmsnorm(x, p[f"l{i}.attn_norm"], spec.rms_norm_eps)
+                qkv = ref.rope(ref.linear(n1, p[f"l{i}.wqkv"]), pos, s.inv_freq, ls.num_heads, ls.num_kv_heads, ls.head_dim)
+                a = ref.attention_varlen(qkv, cu, ls.num_heads, ls.num_kv_heads, ls.head_dim)
+                parts.append(ref.linear(a, p[f"l{i}.wo"]))
+            x = x + sum(parts)
+            parts = []
+            for p in views:
+                n2 = ref.rmsnorm(x, p[f"l{i}.mlp_norm"], spec.rms_norm_eps)
+                parts.append(ref.linear(ref.swiglu(ref.linear(n2, p[f"l{i}.w_gate_up"])), p[f"l{i}.w_down"]))
+            x = x + sum(parts)
+        got = ref.rmsnorm(x, views[0]["final_norm"], spec.rms_norm_eps)
+        assert torch.allclose(got, want, atol=2e-5, rtol=1e-4), (tp, (got - want).abs().max())
