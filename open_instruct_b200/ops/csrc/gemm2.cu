@@ -97,7 +97,8 @@ struct Sched {
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-             void* __restrict__ Cout, int M, int N, int K, long long ldc, int* __restrict__ status) {
+             void* __restrict__ Cout, int M, int N, int K, long long ldc, int* __restrict__ status,
+             const long long* __restrict__ scatter, int row_off) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -254,7 +255,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         tmem_ld_wait();
         if (row < M) {
           if (OUT == OUT_BF16) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<long long>(row) * ldc + col;
+            // column scatter: every 128-column block has its own destination base (possibly in a peer GPU's memory),
+            // rows shift by row_off; used to fuse the sequence -> head exchange into the projection
+            __nv_bfloat16* crow =
+                scatter ? reinterpret_cast<__nv_bfloat16*>(scatter[col >> 7]) + static_cast<long long>(row + row_off) * ldc + (col & 127)
+                        : reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<long long>(row) * ldc + col;
             if (col + 32 <= N) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -316,7 +321,7 @@ static int max_pairs_cache = 0;
 
 template <bool A_MN, bool B_MN, int OUT>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc,
-                  int* status, cudaStream_t stream, int max_ctas) {
+                  int* status, cudaStream_t stream, int max_ctas, const long long* scatter = nullptr, int row_off = 0) {
   auto kern = gemm2_kernel<A_MN, B_MN, OUT>;
   static bool configured = false;
   if (!configured) {
@@ -345,7 +350,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, 
   int pairs = tiles < max_pairs_cache ? tiles : max_pairs_cache;
   if (max_ctas > 1 && pairs > max_ctas / 2) pairs = max_ctas / 2;
   cfg.gridDim = dim3(2 * pairs);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, status, scatter, row_off);
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
@@ -380,4 +385,28 @@ extern "C" int b200_gemm2_bf16(const void* A, const void* B, void* C, int M, int
   if (a_mn && !b_mn) { B200_DISPATCH2(true, false) }
   B200_DISPATCH2(true, true)
 #undef B200_DISPATCH2
+}
+
+// C is not one matrix: column block j (128 wide) of the bf16 result goes to `scatter[j]` (device table of base
+// addresses, local or peer memory) at row `row + row_off`, leading dimension `ld_dst`.  N % 128 == 0.
+extern "C" int b200_gemm2_bf16_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                       int a_mn, int b_mn, const long long* scatter, int row_off, long long ld_dst,
+                                       int* status, void* stream) {
+  using namespace b200;
+  using namespace b200::g2;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (N % 128 || scatter == nullptr) return -3;
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2, true);
+  else r = make_tmap_2d(&ta, A, K, M, lda, BK, 64, 2, true);
+  if (r) return 10000 + r;
+  if (!b_mn) r = make_tmap_2d(&tb, B, N, K, ldb, BNH, BK, 2, true);
+  else r = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2, true);
+  if (r) return 20000 + r;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return g2::launch<false, false, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
+  if (!a_mn && b_mn) return g2::launch<false, true, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
+  if (a_mn && !b_mn) return g2::launch<true, false, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
+  return g2::launch<true, true, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
 }

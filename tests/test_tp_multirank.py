@@ -1,0 +1,20 @@
+"""Tensor-parallel rollout on two GPUs (fused all-reduce + residual + norm kernel, sharded engine)."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.gpu
+def test_tp2_engine_and_fused_allreduce():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", os.path.join(ROOT, "tests", "_tp_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+    assert res.returncode == 0 and "TP_WORKER_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
