@@ -125,6 +125,7 @@ class FlatArguments:
     packing: bool = field(default=False, metadata={"help": "Fill micro-batches up to max_seq_length tokens (padding-free either way)"})
     verbose: bool = False
     sequence_parallel_size: int = field(default=1, metadata={"help": "Ulysses sequence-parallel degree"})
+    offload_optimizer: bool = field(default=False, metadata={"help": "keep fp32 master weights and Adam moments in pinned host memory"})
     # engine selection (not in the reference: there the back end is fixed by the launcher config)
     ops: Literal["auto", "fused", "ref"] = "auto"
     comm_backend: Literal["auto", "fused", "nccl"] = "auto"
@@ -212,7 +213,12 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                                                 pad_token_id=tokenizer.pad_token_id or 0)
     if args.packing:
         collator.max_seq_length = args.max_seq_length  # loader packs to this token budget; collator pads the row up to it
-    loader = HFDataLoader(dataset, batch_size=per_rank * world, seed=args.seed, dp_rank=rank, dp_world_size=world,
+    sp = args.sequence_parallel_size
+    if sp > 1:
+        if sp != world or not args.packing or args.max_seq_length % sp:
+            raise ValueError("sequence_parallel_size must equal the number of ranks, with --packing and max_seq_length divisible by it")
+    dp_rank, dp_world = rank // sp, world // sp  # the ranks of one sequence-parallel group read the same micro-batches
+    loader = HFDataLoader(dataset, batch_size=per_rank * dp_world, seed=args.seed, dp_rank=dp_rank, dp_world_size=dp_world,
                           collator=collator, drop_last=True)
     steps_per_epoch = math.ceil(len(loader) / args.gradient_accumulation_steps)
     max_steps = args.max_train_steps or args.num_train_epochs * steps_per_epoch
@@ -221,7 +227,9 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
     cfg = LearnerConfig(ops=args.ops, comm=args.comm_backend, learning_rate=args.learning_rate, weight_decay=args.weight_decay,
                         max_grad_norm=args.clip_grad_norm if args.clip_grad_norm > 0 else None,
                         lr_scheduler_type=args.lr_scheduler_type, warmup_steps=warmup, total_steps=max_steps,
-                        final_lr_ratio=args.final_lr_ratio, gradient_checkpointing=args.gradient_checkpointing, seed=args.seed)
+                        final_lr_ratio=args.final_lr_ratio, gradient_checkpointing=args.gradient_checkpointing, seed=args.seed,
+                        sequence_parallel_size=sp, sp_max_tokens=args.max_seq_length * max(1, per_rank) if sp > 1 else 0,
+                        offload_optimizer=args.offload_optimizer)
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):

@@ -37,6 +37,9 @@ class LearnerConfig:
     gradient_checkpointing: bool = False
     seed: int = 0
     dtype: torch.dtype | None = None
+    offload_optimizer: bool = False   # fp32 master / moments in pinned host memory, streamed through the GPU per step
+    sequence_parallel_size: int = 1   # Ulysses: every packed micro-batch is split over this many ranks (== world size)
+    sp_max_tokens: int = 8192         # largest packed micro-batch (all ranks together) the exchange buffers hold
 
 
 class Learner:
@@ -82,9 +85,24 @@ class Learner:
         self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, lr=cfg.learning_rate,
                                  betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay,
                                  max_grad_norm=cfg.max_grad_norm, group=group, comm=comm, symm=self.symm,
-                                 use_kernels=(ops == "fused"))
+                                 use_kernels=(ops == "fused"), offload=cfg.offload_optimizer)
         self.global_step = 0
         self._accum = 0
+        self.sp = 1
+        if cfg.sequence_parallel_size > 1:
+            if ops != "fused" or cfg.sequence_parallel_size != self.world:
+                raise NotImplementedError("sequence parallelism runs on the fused path with sequence_parallel_size == world size")
+            from .parallel.ulysses import UlyssesContext
+
+            self.sp = cfg.sequence_parallel_size
+            self.model.sp = UlyssesContext(spec, cfg.sp_max_tokens, self.device, group)
+
+    def local_slice(self, t: torch.Tensor) -> torch.Tensor:
+        """This rank's chunk of a per-token tensor of the packed micro-batch (identity without sequence parallelism)."""
+        if self.sp == 1:
+            return t
+        lo, hi = self.model.sp.local_tokens(t.shape[-1])
+        return t[..., lo:hi]
 
     # ------------------------------------------------------------------ pieces
     def lr(self, step: int | None = None) -> float:
@@ -130,10 +148,13 @@ class Learner:
         ``mean``: mean CE over this micro-batch's target tokens (HF default, ``finetune.py:822-826``);
         ``sum`` : summed CE; the caller normalises by the global token count at the step.
         """
-        logp, _ = self.token_logprobs(batch)
-        n = (batch["labels_shifted"] != IGNORE).sum()
+        logp, _ = self.token_logprobs(batch)  # sequence parallel: log-probs of this rank's chunk only
+        n = (batch["labels_shifted"] != IGNORE).sum()  # target tokens of the whole micro-batch (every SP rank sees all labels)
         total = -logp.sum()
-        loss = total / n.clamp(min=1) if reduce_loss == "mean" else total
+        # "mean": the sp ranks' partial sums add up in the gradient exchange, which then divides by the world size
+        loss = total * self.sp / n.clamp(min=1) if reduce_loss == "mean" else total
+        if self.sp > 1:
+            n = self.local_slice(batch["labels_shifted"] != IGNORE).sum()
         self.backward(loss)
         return loss.detach(), n
 

@@ -46,6 +46,7 @@ class _LayerStash:
     h_mid: torch.Tensor  # residual stream after attention
     rstd2: torch.Tensor
     gate_up: torch.Tensor
+    attn_tok: torch.Tensor | None = None  # sequence parallel: attention output for MY tokens, all heads
 
 
 class LlamaModel:
@@ -83,6 +84,7 @@ class LlamaModel:
                 raise ValueError("flat buffer is smaller than the layout")
             self.flat = flat
         self.p = self.layout.views(self.flat)
+        self.sp = None  # parallel.ulysses.UlyssesContext when the sequence is split over ranks (fused path)
         self.main_grad: torch.Tensor | None = None  # fp32 flat gradient (fused path)
         self.g: dict[str, torch.Tensor] = {}
         self.inv_freq = ref.rope_inv_freq(spec.head_dim, spec.rope_theta, spec.rope_scaling, device=self.device)
@@ -230,16 +232,18 @@ class LlamaModel:
         cu = cu_seqlens.to(torch.int32)
         scale = s.head_dim ** -0.5
         stash: list[_LayerStash] = []
+        if self.sp is not None:
+            # sequence parallel: this rank embeds and projects its contiguous chunk of the packed tokens
+            lo, hi = self.sp.local_tokens(input_ids.numel())
+            input_ids = input_ids[lo:hi]
         stream = f.embedding_fwd(p["embed"], input_ids)
         delta = None  # pending residual contribution, added inside the next RMSNorm
         for i in range(s.num_layers):
             n1, h_in, rstd1 = f.rmsnorm_fwd(delta if delta is not None else stream, p[f"l{i}.attn_norm"], s.rms_norm_eps,
                                             res=stream if delta is not None else None)
-            qkv = f.gemm(n1, p[f"l{i}.wqkv"])
+            qkv, attn, lse, attn_tok = self._attention_block(i, n1, pos, cu)
             del n1
-            f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
-            attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
-            o = f.gemm(attn, p[f"l{i}.wo"])
+            o = f.gemm(attn_tok if attn_tok is not None else attn, p[f"l{i}.wo"])
             n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=h_in)
             del o
             gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
@@ -252,25 +256,40 @@ class LlamaModel:
                 if self.gradient_checkpointing:
                     stash.append(_LayerStash(h_in, None, None, None, None, None, None, None))
                 else:
-                    stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up))
+                    stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok))
         nf, h_last, rstd_f = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
         state = None
         if keep:
             state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu}
         return nf, state
 
+    def _attention_block(self, i: int, n1, pos, cu):
+        """QKV projection, RoPE and attention of layer ``i``.  Returns ``(qkv, attn, lse, attn_tok)``; with sequence
+        parallelism ``qkv``/``attn`` cover all tokens for this rank's heads and ``attn_tok`` this rank's tokens for all
+        heads (else ``attn_tok`` is None)."""
+        f = _fused()
+        s, p, sp = self.spec, self.p, self.sp
+        scale = s.head_dim ** -0.5
+        if sp is None:
+            qkv = f.gemm(n1, p[f"l{i}.wqkv"])
+            f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+            return qkv, attn, lse, None
+        qkv = sp.qkv_project(i, n1, p[f"l{i}.wqkv"], pos.numel())
+        f.rope_(qkv, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim)
+        attn, lse = f.attn_fwd(qkv, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
+        return qkv, attn, lse, sp.attn_exchange(i, attn)
+
     def _recompute_layer(self, i: int, st: _LayerStash, pos, cu) -> _LayerStash:
         """Gradient checkpointing: rebuild a layer's activations from its input stream."""
         f = _fused()
         s, p = self.spec, self.p
         n1, _, rstd1 = f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)
-        qkv = f.gemm(n1, p[f"l{i}.wqkv"])
-        f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
-        attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, s.head_dim ** -0.5)
-        o = f.gemm(attn, p[f"l{i}.wo"])
+        qkv, attn, lse, attn_tok = self._attention_block(i, n1, pos, cu)
+        o = f.gemm(attn_tok if attn_tok is not None else attn, p[f"l{i}.wo"])
         n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=st.h_in)
         gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
-        return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up)
+        return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok)
 
     def _fused_backward_hidden(self, state: dict, d_nf: torch.Tensor) -> None:
         """Backward from d(final-norm hidden) to the embedding; accumulates into ``main_grad``."""
@@ -304,11 +323,18 @@ class LlamaModel:
             d_mid = f.rmsnorm_bwd(st.h_mid, p[f"l{i}.mlp_norm"], st.rstd2, d_n2, d_stream, g[f"l{i}.mlp_norm"])
             del d_n2, d_stream
             # ---- attention: h_mid = h_in + wo(attn(rope(wqkv(norm(h_in)))))
-            f.gemm(d_mid, st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
-            d_attn = f.gemm(d_mid, p[f"l{i}.wo"], b_mn=True)
-            dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
-            del d_attn
-            f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True)
+            sp = self.sp
+            f.gemm(d_mid, st.attn_tok if sp is not None else st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            if sp is None:
+                d_attn = f.gemm(d_mid, p[f"l{i}.wo"], b_mn=True)
+                dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+                del d_attn
+                f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True)
+            else:
+                d_attn = sp.d_attn_project(d_mid, p[f"l{i}.wo"], pos.numel())
+                dqkv_heads = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
+                f.rope_(dqkv_heads, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim, backward=True)
+                dqkv = sp.dqkv_exchange(dqkv_heads)
             n1, _, _ = f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)
             f.gemm(dqkv, n1, g[f"l{i}.wqkv"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
             del n1
@@ -344,6 +370,9 @@ class _FusedLogprobFn(torch.autograd.Function):
         f = _fused()
         needs_grad = keep
         nf, ctx.state = model._fused_forward_hidden(input_ids, position_ids, cu_seqlens, keep=needs_grad)
+        if model.sp is not None:  # log-probs of this rank's chunk of the tokens
+            lo, hi = model.sp.local_tokens(labels.numel())
+            labels = labels[lo:hi].contiguous()
         w = model.lm_head_weight()
         logits = f.gemm(nf, w)
         logp, lse, ent = f.logprob_fwd(logits, labels, temperature, want_entropy)

@@ -57,7 +57,13 @@ class ZeroOptimizer:
 
     def __init__(self, flat: torch.Tensor, total: int, decay_end: int, *, lr: float = 1e-5,
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, max_grad_norm: float | None = None,
-                 group=None, comm: str = "auto", use_kernels: bool | None = None, symm=None):
+                 group=None, comm: str = "auto", use_kernels: bool | None = None, symm=None, offload: bool = False,
+                 offload_chunk: int = 1 << 26):
+        # ``offload``: fp32 master / m / v shards live in pinned host memory and stream through two device staging
+        # sets per optimizer step (H2D on one side stream, D2H on another, AdamW on the main stream) - the 12 bytes
+        # per parameter leave the GPU, the price is 24 bytes per parameter over PCIe per step
+        # (cf. DeepSpeed ``offload_optimizer``, ``open_instruct/dpo_tune_cache.py:76-114``).
+        self.offload, self.offload_chunk = offload, offload_chunk
         self.flat = flat
         self.total = total
         self.decay_end = decay_end
@@ -82,10 +88,18 @@ class ZeroOptimizer:
         self.device = flat.device
         self.use_kernels = (flat.is_cuda and flat.dtype == torch.bfloat16) if use_kernels is None else use_kernels
         with torch.no_grad():
-            self.master = flat.detach()[self.lo:self.hi].to(torch.float32, copy=True)
-        self.m = torch.zeros_like(self.master)
-        self.v = torch.zeros_like(self.master)
-        self.grad_shard = torch.zeros_like(self.master) if self.world > 1 else None
+            if offload:
+                pin = flat.is_cuda
+                self.master = torch.empty(self.shard, dtype=torch.float32, pin_memory=pin)
+                self.master.copy_(flat.detach()[self.lo:self.hi])
+                self.m = torch.zeros(self.shard, dtype=torch.float32, pin_memory=pin)
+                self.v = torch.zeros(self.shard, dtype=torch.float32, pin_memory=pin)
+            else:
+                self.master = flat.detach()[self.lo:self.hi].to(torch.float32, copy=True)
+                self.m = torch.zeros_like(self.master)
+                self.v = torch.zeros_like(self.master)
+        self.grad_shard = torch.zeros(self.shard, dtype=torch.float32, device=flat.device) if self.world > 1 else None
+        self._stage = None
         self.step_count = 0
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._gscale = torch.ones(1, dtype=torch.float32, device=self.device)
@@ -151,7 +165,9 @@ class ZeroOptimizer:
         # ---- AdamW on the shard (+ bf16 refresh of my slice of the working copy)
         b1, b2 = self.betas
         my_flat = self.flat[self.lo:self.hi]
-        for (a, b, wd) in self._segments():
+        if self.offload:
+            self._step_offloaded(gs, my_flat, lr, fused_comm)
+        for (a, b, wd) in ([] if self.offload else self._segments()):
             if self.use_kernels:
                 from ..ops import fused
 
@@ -178,6 +194,60 @@ class ZeroOptimizer:
                 dist.all_gather(parts, my_flat.contiguous(), group=self.group)
                 self.flat.copy_(torch.cat(parts))
         return norm
+
+    def _adamw_piece(self, M, m, v, g, out16, goff: int, lr: float, wd: float, fused_comm: bool) -> None:
+        b1, b2 = self.betas
+        if self.use_kernels:
+            from ..ops import fused
+
+            if fused_comm:
+                self.symm.adamw_allgather(M, m, v, g, goff, gscale=self._gscale, lr=lr, beta1=b1, beta2=b2, eps=self.eps, wd=wd,
+                                          step=self.step_count)
+            else:
+                fused.adamw(M, m, v, g, out16, lr=lr, beta1=b1, beta2=b2, eps=self.eps, wd=wd, step=self.step_count,
+                            gscale=self._gscale, zero_grad=True)
+        else:
+            ref.adamw_step(M, m, v, g, lr, b1, b2, self.eps, wd, self.step_count, gscale=self._gscale)
+            out16.copy_(M.to(out16.dtype))
+
+    def _step_offloaded(self, gs: torch.Tensor, my_flat: torch.Tensor, lr: float, fused_comm: bool) -> None:
+        """AdamW over host-resident state, chunk by chunk through two staging sets."""
+        CH = self.offload_chunk
+        pieces = [(c0, min(b, c0 + CH), wd) for (a, b, wd) in self._segments() for c0 in range(a, b, CH)]
+        if not self.flat.is_cuda:
+            for c0, c1, wd in pieces:  # host-only run (tests): same arithmetic, no streams
+                self._adamw_piece(self.master[c0:c1], self.m[c0:c1], self.v[c0:c1], gs[c0:c1], my_flat[c0:c1], self.lo + c0, lr, wd, fused_comm)
+            return
+        dev = self.device
+        if self._stage is None:
+            n = min(CH, self.shard)
+            self._stage = [[torch.empty(n, dtype=torch.float32, device=dev) for _ in range(3)] for _ in range(2)]
+            self._h2d, self._d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+            self._ev_in = [torch.cuda.Event() for _ in range(2)]
+            self._ev_comp = [torch.cuda.Event() for _ in range(2)]
+            self._ev_out = [torch.cuda.Event() for _ in range(2)]
+        main = torch.cuda.current_stream(dev)
+        host = (self.master, self.m, self.v)
+        for i, (c0, c1, wd) in enumerate(pieces):
+            k, n = i & 1, c1 - c0
+            st = self._stage[k]
+            with torch.cuda.stream(self._h2d):
+                if i >= 2:
+                    self._h2d.wait_event(self._ev_out[k])  # the chunk that used this set two rounds ago is back on the host
+                else:
+                    self._h2d.wait_stream(main)
+                for d, h in zip(st, host):
+                    d[:n].copy_(h[c0:c1], non_blocking=True)
+                self._ev_in[k].record(self._h2d)
+            main.wait_event(self._ev_in[k])
+            self._adamw_piece(st[0][:n], st[1][:n], st[2][:n], gs[c0:c1], my_flat[c0:c1], self.lo + c0, lr, wd, fused_comm)
+            self._ev_comp[k].record(main)
+            with torch.cuda.stream(self._d2h):
+                self._d2h.wait_event(self._ev_comp[k])
+                for d, h in zip(st, host):
+                    h[c0:c1].copy_(d[:n], non_blocking=True)
+                self._ev_out[k].record(self._d2h)
+        main.wait_stream(self._d2h)  # host state is complete before the step returns (checkpointing reads it)
 
     # ------------------------------------------------------------------ checkpointing
     def state_dict(self) -> dict:

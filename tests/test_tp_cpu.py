@@ -37,3 +37,21 @@ def test_sharded_layers_sum_to_full_model():
             x = x + sum(parts)
         got = ref.rmsnorm(x, views[0]["final_norm"], spec.rms_norm_eps)
         assert torch.allclose(got, want, atol=2e-5, rtol=1e-4), (tp, (got - want).abs().max())
+
+
+def test_offloaded_optimizer_matches_resident():
+    from open_instruct_b200.parallel.zero import ZeroOptimizer, padded_numel
+
+    torch.manual_seed(0)
+    total, decay_end = 1000, 800
+    n = padded_numel(total, 1)
+    flat_a = torch.randn(n)
+    flat_b = flat_a.clone()
+    a = ZeroOptimizer(flat_a, total, decay_end, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, comm="none")
+    b = ZeroOptimizer(flat_b, total, decay_end, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, comm="none", offload=True, offload_chunk=96)
+    for _ in range(3):
+        g = torch.randn(n)
+        na = a.step(g.clone(), grad_scale=0.5)
+        nb = b.step(g.clone(), grad_scale=0.5)
+        assert torch.allclose(na, nb)
+    assert torch.equal(flat_a, flat_b) and torch.equal(a.m, b.m) and torch.equal(a.v, b.v)
