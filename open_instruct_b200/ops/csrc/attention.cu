@@ -5,9 +5,10 @@
 // lse [Hq, T] fp32 (natural log of the softmax denominator of scale*QK^T).
 //
 // Forward: one CTA per (128-query tile, q head).  Warp 0 streams K/V tiles with TMA, warp 1
-// issues S = Q K^T (double-buffered in TMEM) and O_blk = P V, warps 2-5 own one query row per
-// thread: online softmax straight out of TMEM, P written to swizzled shared memory as bf16, the
-// running output kept in registers.
+// issues S = Q K^T (double-buffered in TMEM) and O += P V (accumulated in TMEM), warps 2-5 own one
+// query row per thread: the score row is read from TMEM once into registers, the softmax maximum
+// follows the row maximum lazily (O is rescaled in TMEM only when it moved by more than 2^8), P is
+// written to swizzled shared memory as bf16 while the previous P V still runs.
 //
 // Backward: one CTA per (128-key tile, kv head); it walks every query tile at or after its key
 // tile for each q head of the GQA group.  Scores are computed transposed (S^T = K Q^T) so each
@@ -23,6 +24,7 @@ constexpr int TK = 128;   // key tile
 constexpr int SUB = 128 * 64 * 2;  // bytes of one [128 x 64] bf16 swizzled sub-tile (16 KB)
 constexpr int TILE = 2 * SUB;      // [128 x 128] bf16 tile (32 KB)
 constexpr int ATT_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter, 64 columns each)
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ bool find_tile(const int* __restrict__ cu, int B, int slot, int& start, int& end,
@@ -165,7 +167,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restric
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sm.v[s]);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(T_O, desc_kmajor(p_addr, k), desc_mnmajor(v_addr, k), idesc_o, k != 0);
+        // O accumulates in TMEM over all key tiles; the softmax warps rescale it in place when a row maximum moves
+        for (int k = 0; k < 8; ++k) umma_ss(T_O, desc_kmajor(p_addr, k), desc_mnmajor(v_addr, k), idesc_o, (j | k) != 0);
         umma_commit(&sm.v_empty[s]);
         umma_commit(&sm.o_full);
       }
@@ -175,79 +178,81 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restric
     const int r = lane_grp * 32 + lane;          // query row inside the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(lane_grp * 32) << 16;
     const float c = scale * LOG2E;
+    // `m` is the maximum the exponentials are taken against.  It follows the true row maximum lazily: it moves only
+    // when the row maximum has grown by more than 2^8 since, so the running output in TMEM is rescaled rarely and the
+    // weights stay below 2^8 (exact in the end: O and l use the same m).
     float m = -INFINITY, l = 0.f;
-    float o_acc[DH];
-#pragma unroll
-    for (int i = 0; i < DH; ++i) o_acc[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      if (j > 0) {
-        ok = warp_wait(&sm.o_full, (j - 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t t[32];
-          tmem_ld32(T_O + lane_off + cc * 32, t);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[cc * 32 + i] += __uint_as_float(t[i]);
-        }
-        tc_fence_before();
-      }
       const int s = j & 1;
       ok = warp_wait(&sm.s_full[s], (j >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const bool diag = (j == n_kv - 1);
       const uint32_t ts = T_S0 + s * 128 + lane_off;
-      float mx = -INFINITY;
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld32(ts + cc * 32, sv[cc]);
+      tmem_ld_wait();
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
-        uint32_t t[32];
-        tmem_ld32(ts + cc * 32, t);
-        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(t[i]);
-          if (!diag || cc * 32 + i <= r) mx = fmaxf(mx, v);
+          float v = __uint_as_float(sv[cc][i]);
+          if (diag && cc * 32 + i > r) {
+            v = -INFINITY;  // causal mask: contributes exp2(-inf) = 0 below
+            sv[cc][i] = __float_as_uint(v);
+          }
+          mx4[i & 3] = fmaxf(mx4[i & 3], v);
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float alpha = exp2f((m - m_new) * c);
-      l *= alpha;
-      if (alpha != 1.f) {
-#pragma unroll
-        for (int i = 0; i < DH; ++i) o_acc[i] *= alpha;
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float alpha = 1.f;
+      const bool grow = (mx - m) * c > 8.f;
+      if (grow) {
+        alpha = ex2_approx((m - mx) * c);
+        m = mx;
+        l *= alpha;
       }
-      m = m_new;
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, grow);
       const float mc = m * c;
-      float rs = 0.f;
+      uint32_t pk[64];
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
-        uint32_t t[32];
-        tmem_ld32(ts + cc * 32, t);
-        tmem_ld_wait();
 #pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          float p[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int col = cc * 32 + g8 * 8 + i;
-            float v = exp2f(fmaf(__uint_as_float(t[g8 * 8 + i]), c, -mc));
-            if (diag && col > r) v = 0.f;
-            p[i] = v;
-            rs += v;
-          }
-          uint4 pk;
-          pk.x = pack_bf16x2(p[0], p[1]);
-          pk.y = pack_bf16x2(p[2], p[3]);
-          pk.z = pack_bf16x2(p[4], p[5]);
-          pk.w = pack_bf16x2(p[6], p[7]);
-          *reinterpret_cast<uint4*>(sm.p + swz_off(r, cc * 32 + g8 * 8)) = pk;
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[cc][i]), c, -mc));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[cc][i + 1]), c, -mc));
+          rs4[(i >> 1) & 3] += p0 + p1;
+          pk[cc * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
         }
       }
-      l += rs;
+      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      // the P buffer and the O accumulator are free once P V of the previous tile has completed
+      if (j > 0) {
+        ok = warp_wait(&sm.o_full, (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      if (rescale) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t t[32];
+          tmem_ld32(T_O + lane_off + cc * 32, t);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+          tmem_st32(T_O + lane_off + cc * 32, t);
+        }
+        tmem_st_wait();
+      }
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        const uint4 v4 = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+        *reinterpret_cast<uint4*>(sm.p + swz_off(r, q * 8)) = v4;
+      }
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
@@ -267,13 +272,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restric
           __nv_bfloat16* dst = out + static_cast<long long>(tok) * (Hq * DH) + h * DH + cc * 32;
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
-            uint4 pk;
-            const int b = cc * 32 + g8 * 8;
-            pk.x = pack_bf16x2((o_acc[b + 0] + __uint_as_float(t[g8 * 8 + 0])) * inv_l, (o_acc[b + 1] + __uint_as_float(t[g8 * 8 + 1])) * inv_l);
-            pk.y = pack_bf16x2((o_acc[b + 2] + __uint_as_float(t[g8 * 8 + 2])) * inv_l, (o_acc[b + 3] + __uint_as_float(t[g8 * 8 + 3])) * inv_l);
-            pk.z = pack_bf16x2((o_acc[b + 4] + __uint_as_float(t[g8 * 8 + 4])) * inv_l, (o_acc[b + 5] + __uint_as_float(t[g8 * 8 + 5])) * inv_l);
-            pk.w = pack_bf16x2((o_acc[b + 6] + __uint_as_float(t[g8 * 8 + 6])) * inv_l, (o_acc[b + 7] + __uint_as_float(t[g8 * 8 + 7])) * inv_l);
-            reinterpret_cast<uint4*>(dst)[g8] = pk;
+            uint4 v4;
+            v4.x = pack_bf16x2(__uint_as_float(t[g8 * 8 + 0]) * inv_l, __uint_as_float(t[g8 * 8 + 1]) * inv_l);
+            v4.y = pack_bf16x2(__uint_as_float(t[g8 * 8 + 2]) * inv_l, __uint_as_float(t[g8 * 8 + 3]) * inv_l);
+            v4.z = pack_bf16x2(__uint_as_float(t[g8 * 8 + 4]) * inv_l, __uint_as_float(t[g8 * 8 + 5]) * inv_l);
+            v4.w = pack_bf16x2(__uint_as_float(t[g8 * 8 + 6]) * inv_l, __uint_as_float(t[g8 * 8 + 7]) * inv_l);
+            reinterpret_cast<uint4*>(dst)[g8] = v4;
           }
         }
       }
@@ -356,7 +360,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
                 const int* __restrict__ cu, int B, int Hq, int Hkv, const float* __restrict__ lse,
                 const float* __restrict__ delta, float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int T,
@@ -378,9 +382,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     mbar_init(&sm.qdo_full, 1);
     mbar_init(&sm.qdo_empty, 1);
     mbar_init(&sm.sdp_full, 1);
-    mbar_init(&sm.pds_full, 128);
+    mbar_init(&sm.pds_full, 256);
     mbar_init(&sm.dq_full, 1);
-    mbar_init(&sm.dq_done, 4);
+    mbar_init(&sm.dq_done, 8);
     mbar_init(&sm.ld_full, 128);
     sm.abort_flag = 0;
     fence_barrier_init();
@@ -449,6 +453,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     }
   } else {
     const int lane_grp = warp & 3;
+    const int half = (warp - 2) >> 2;    // which 64 of the 128 columns this warp handles (same TMEM lanes as its twin)
     const int r = lane_grp * 32 + lane;  // key row for S^T / dK / dV; query row for the dQ tile
     const int tid = r;
     const uint32_t lane_off = static_cast<uint32_t>(lane_grp * 32) << 16;
@@ -460,7 +465,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       const int qt = kvb + it % n_q;
       const int q0 = doc_start + qt * TQ;
       const bool diag = (qt == kvb);
-      {
+      if (half == 0) {
         const int tq = q0 + tid;
         const bool v = tq < doc_end;
         // every thread finished reading the previous iteration's values before pds_full
@@ -474,19 +479,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       ok = warp_wait(&sm.sdp_full, it & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(T_ST + lane_off + cc * 32, s);
-        tmem_ld32(T_DPT + lane_off + cc * 32, dp);
-        tmem_ld_wait();
+      uint32_t s2[2][32], dp2[2][32];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        tmem_ld32(T_ST + lane_off + (half * 2 + u) * 32, s2[u]);
+        tmem_ld32(T_DPT + lane_off + (half * 2 + u) * 32, dp2[u]);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int cc = half * 2 + u;
+        const uint32_t(&s)[32] = s2[u];
+        const uint32_t(&dp)[32] = dp2[u];
 #pragma unroll
         for (int g8 = 0; g8 < 4; ++g8) {
           float p[8], ds[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int qc = cc * 32 + g8 * 8 + i;  // query column
-            float pv = exp2f(fmaf(__uint_as_float(s[g8 * 8 + i]), c, -sm.lse2[qc]));
+            float pv = ex2_approx(fmaf(__uint_as_float(s[g8 * 8 + i]), c, -sm.lse2[qc]));
             if (diag && r > qc) pv = 0.f;  // key after query
             p[i] = pv;
             ds[i] = pv * (__uint_as_float(dp[g8 * 8 + i]) - sm.delta[qc]) * scale;
@@ -512,7 +523,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         const bool v = tq < doc_end;
         float* dst = dq_acc + static_cast<long long>(tq) * (Hq * DH) + h * DH;
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int cc = half * 2; cc < half * 2 + 2; ++cc) {
           uint32_t t[32];
           tmem_ld32(T_ST + lane_off + cc * 32, t);
           tmem_ld_wait();
@@ -533,8 +544,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tc_fence_after();
       const bool v = key < doc_end;
       const long long row = static_cast<long long>(Hq + 2 * Hkv) * DH;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = half;  // first column half of the warps writes dK, the second dV
         const uint32_t tbase = (which == 0 ? T_DK : T_DV) + lane_off;
         __nv_bfloat16* dst = dqkv + static_cast<long long>(key) * row + (which == 0 ? kcol : vcol);
 #pragma unroll 1
@@ -637,7 +648,7 @@ extern "C" int b200_attn_bwd(const void* qkv, const void* out, const void* d_out
     cfg = true;
   }
   dim3 grid(max_tiles, Hkv);
-  attn_bwd_kernel<<<grid, ATT_THREADS, smem, st>>>(tq, tdo, cu_seqlens, B, Hq, Hkv, lse, delta, dq_acc,
+  attn_bwd_kernel<<<grid, BWD_THREADS, smem, st>>>(tq, tdo, cu_seqlens, B, Hq, Hkv, lse, delta, dq_acc,
                                                    reinterpret_cast<__nv_bfloat16*>(dqkv), T, scale, status);
   attn_dq_convert_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), T, Hq, Hkv);
   return static_cast<int>(cudaGetLastError());
