@@ -84,7 +84,9 @@ def _serve(cls, args, kwargs, address, ready, max_concurrency, env):
         return
     listener = Listener(address, family="AF_UNIX", authkey=_AUTH)
     ready.put(("ok", None))
-    pool = cf.ThreadPoolExecutor(max_workers=max_concurrency)
+    # one thread per client connection (connections are long-lived: every calling thread keeps its own); at most
+    # ``max_concurrency`` method bodies run at a time
+    running = threading.BoundedSemaphore(max(1, max_concurrency))
     stop = threading.Event()
 
     def bind_device():
@@ -109,7 +111,8 @@ def _serve(cls, args, kwargs, address, ready, max_concurrency, env):
                     return
                 _, method, a, kw = msg
                 try:
-                    res = ("ok", getattr(obj, method)(*a, **kw))
+                    with running:
+                        res = ("ok", getattr(obj, method)(*a, **kw))
                 except BaseException as e:  # noqa: BLE001
                     res = ("error", f"{type(e).__name__}: {e}\n{traceback.format_exc()}")
                 try:
@@ -127,7 +130,7 @@ def _serve(cls, args, kwargs, address, ready, max_concurrency, env):
             continue
         except Exception:  # noqa: BLE001
             continue
-        pool.submit(handle, conn)
+        threading.Thread(target=handle, args=(conn,), daemon=True, name="actor-conn").start()
     listener.close()
     if hasattr(obj, "shutdown"):
         try:
@@ -261,7 +264,8 @@ def kill(handle: ActorHandle) -> None:
     try:
         c = Client(handle._address, family="AF_UNIX", authkey=_AUTH)
         _send(c, ("stop",))
-        _recv(c)
+        if c.poll(5.0):
+            _recv(c)
         c.close()
     except Exception:  # noqa: BLE001
         pass

@@ -32,7 +32,7 @@ def test_actor_calls_and_errors():
         C = ray.remote(Counter)
         a = C.options(name="ctr").remote(5)
         assert ray.get(a.add.remote(3)) == 8
-        assert ray.get([a.add.remote(1), a.add.remote(1)])[-1] == 10
+        assert max(ray.get([a.add.remote(1), a.add.remote(1)])) == 10  # concurrent calls may finish in either order
         assert ray.get(ray.get_actor("ctr").add.remote(0)) == 10
         t0 = time.time()
         refs = [a.slow.remote(0.3) for _ in range(4)]  # threaded actor: calls overlap
