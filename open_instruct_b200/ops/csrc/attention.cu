@@ -13,7 +13,7 @@
 // Backward: one CTA per (128-key tile, kv head); it walks every query tile at or after its key
 // tile for each q head of the GQA group.  Scores are computed transposed (S^T = K Q^T) so each
 // thread owns one key row; dK and dV accumulate in TMEM across the whole walk, dQ tiles are
-// staged in shared memory and added to an fp32 scratch by TMA reduce, converted once at the end.
+// reduced into an fp32 scratch with vector red.global and converted once at the end.
 #include "common.cuh"
 
 namespace b200 {
@@ -312,7 +312,7 @@ struct BwdSmem {
   uint8_t dst[TILE];
   float lse2[128];
   float delta[128];
-  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_full, dq_full, dq_done, ld_full, stg_full, stg_free;
+  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_full, dq_full, dq_done, ld_full;
   uint32_t tmem_ptr;
   int abort_flag;
 };
@@ -362,7 +362,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_dq, const int* __restrict__ cu, int B, int Hq, int Hkv, const float* __restrict__ lse,
+                const int* __restrict__ cu, int B, int Hq, int Hkv, const float* __restrict__ lse,
                 const float* __restrict__ delta, float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int T,
                 float scale, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -386,8 +386,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     mbar_init(&sm.dq_full, 1);
     mbar_init(&sm.dq_done, 8);
     mbar_init(&sm.ld_full, 128);
-    mbar_init(&sm.stg_full, 256);
-    mbar_init(&sm.stg_free, 1);
     sm.abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -412,19 +410,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tma_load_2d(sm.k + SUB, &tm_qkv, &sm.kv_full, kcol + 64, k0);
       tma_load_2d(sm.v, &tm_qkv, &sm.kv_full, vcol, k0);
       tma_load_2d(sm.v + SUB, &tm_qkv, &sm.kv_full, vcol + 64, k0);
-      // dQ tile of iteration `i`: staged as fp32 in shared memory by the compute warps (four [128 x 32] boxes, 128-byte
-      // swizzle), added to the global accumulator by the copy engine instead of 4096 vector atomics from the SM
-      auto reduce_dq = [&](int i) -> bool {
-        if (!mbar_wait(&sm.stg_full, i & 1, abort_flag)) { atomicCAS(status, 0, ST_TIMEOUT_FULL); return false; }
-        const int hh = kvh * G + i / n_q;
-        const int qq = doc_start + (kvb + i % n_q) * TQ;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) tma_reduce_add_2d(&tm_dq, sm.pt + b * (128 * 128), hh * DH + b * 32, qq);
-        tma_store_commit();
-        tma_store_wait_read<0>();  // the staging area (= P^T / dS^T buffers) may be overwritten again
-        mbar_arrive(&sm.stg_free);
-        return true;
-      };
       for (int it = 0; it < iters; ++it) {
         const int h = kvh * G + it / n_q;
         const int q0 = doc_start + (kvb + it % n_q) * TQ;
@@ -434,10 +419,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         tma_load_2d(sm.q + SUB, &tm_qkv, &sm.qdo_full, h * DH + 64, q0);
         tma_load_2d(sm.d_o, &tm_do, &sm.qdo_full, h * DH, q0);
         tma_load_2d(sm.d_o + SUB, &tm_do, &sm.qdo_full, h * DH + 64, q0);
-        if (it > 0 && !reduce_dq(it - 1)) break;
       }
-      if (iters > 0) reduce_dq(iters - 1);
-      tma_store_wait<0>();  // every reduction has landed before the CTA retires
     }
   } else if (warp == 1) {
     if (elect_one()) {
@@ -496,10 +478,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       if (!ok) break;
       ok = warp_wait(&sm.sdp_full, it & 1, abort_flag);
       if (!ok) break;
-      if (it > 0) {  // the previous dQ tile has left the staging area that P^T / dS^T are about to overwrite
-        ok = warp_wait(&sm.stg_free, (it - 1) & 1, abort_flag);
-        if (!ok) break;
-      }
       tc_fence_after();
       uint32_t s2[2][32], dp2[2][32];
 #pragma unroll
@@ -542,28 +520,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tc_fence_after();
       {
         const int tq = q0 + r;
-        const bool v = tq < doc_end;  // rows past the document end belong to other documents: they add zero
-        uint32_t t2[2][32];
+        const bool v = tq < doc_end;
+        float* dst = dq_acc + static_cast<long long>(tq) * (Hq * DH) + h * DH;
+#pragma unroll 1
+        for (int cc = half * 2; cc < half * 2 + 2; ++cc) {
+          uint32_t t[32];
+          tmem_ld32(T_ST + lane_off + cc * 32, t);
+          tmem_ld_wait();
+          if (v) {
 #pragma unroll
-        for (int u = 0; u < 2; ++u) tmem_ld32(T_ST + lane_off + (half * 2 + u) * 32, t2[u]);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.dq_done);  // S^T columns are free for the next iteration's MMA
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          uint8_t* box = sm.pt + (half * 2 + u) * (128 * 128) + r * 128;
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            uint4 q4 = make_uint4(t2[u][4 * k], t2[u][4 * k + 1], t2[u][4 * k + 2], t2[u][4 * k + 3]);
-            if (!v) q4 = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(box + ((k ^ (r & 7)) << 4)) = q4;
+            for (int i = 0; i < 8; ++i)
+              red_add_v4(dst + cc * 32 + i * 4, __uint_as_float(t[4 * i]), __uint_as_float(t[4 * i + 1]),
+                         __uint_as_float(t[4 * i + 2]), __uint_as_float(t[4 * i + 3]));
           }
         }
-        fence_proxy_async();
-        mbar_arrive(&sm.stg_full);
       }
-
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.dq_done);
     }
     if (ok) {
       // the last dq_full wait covers every MMA issued before it, including all dK/dV updates
@@ -666,9 +640,6 @@ extern "C" int b200_attn_bwd(const void* qkv, const void* out, const void* d_out
   if (r) return 10000 + r;
   r = attn_tmap(&tdo, d_out, T, static_cast<long long>(Hq) * DH);
   if (r) return 20000 + r;
-  CUtensorMap tdq;  // fp32 accumulator [T, Hq*128], boxes of 128 rows x 32 columns (128 bytes), 128-byte swizzle
-  r = make_tmap_2d(&tdq, dq_acc, static_cast<uint64_t>(T), static_cast<uint64_t>(Hq) * DH, static_cast<uint64_t>(Hq) * DH, 128, 32, 4, true);
-  if (r) return 30000 + r;
   const int smem = sizeof(BwdSmem) + 1024;
   static bool cfg = false;
   if (!cfg) {
@@ -677,7 +648,7 @@ extern "C" int b200_attn_bwd(const void* qkv, const void* out, const void* d_out
     cfg = true;
   }
   dim3 grid(max_tiles, Hkv);
-  attn_bwd_kernel<<<grid, BWD_THREADS, smem, st>>>(tq, tdo, tdq, cu_seqlens, B, Hq, Hkv, lse, delta, dq_acc,
+  attn_bwd_kernel<<<grid, BWD_THREADS, smem, st>>>(tq, tdo, cu_seqlens, B, Hq, Hkv, lse, delta, dq_acc,
                                                    reinterpret_cast<__nv_bfloat16*>(dqkv), T, scale, status);
   attn_dq_convert_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), T, Hq, Hkv);
   return static_cast<int>(cudaGetLastError());
