@@ -259,3 +259,33 @@ def test_finetune_numpy_end_to_end(tmp_path):
     assert (tmp_path / "out" / "hf" / "config.json").exists() and (tmp_path / "out" / "step_2").exists()
     args.max_train_steps = 4
     assert fn.main(args)["completed_steps"] == 4  # resumed from step_2, ran 2 more
+
+
+def test_distill_compression_roundtrip_and_sampler(tmp_path):
+    from open_instruct_b200.distill.compression import QuantizationConfig, compress_logprobs, decompress_logprobs, pack_bits, unpack_bits
+    from open_instruct_b200.distill.sample_logits import Args, ParquetShardWriter, process_dataset
+    from open_instruct_b200.models.llama import LlamaModel
+
+    ids = torch.randint(0, 128256, (5, 7, 64))
+    assert torch.equal(unpack_bits(pack_bits(ids, 17), 17, 64), ids)
+    assert pack_bits(ids, 17).shape[-1] == 64 * 17 // 8
+    cfg = QuantizationConfig(k=64, exact_k=8, vocab_size=128256)
+    logits = torch.randn(40, 1000) * 3
+    lp = torch.log_softmax(logits, -1).topk(64, -1).values
+    comp = compress_logprobs(lp, cfg)
+    assert comp.dtype == torch.uint8 and comp.shape == (40, cfg.logprob_bytes()) and cfg.logprob_bytes() < 64 * 2 // 2
+    back = decompress_logprobs(comp, cfg)
+    assert torch.allclose(back[:, :8], lp[:, :8], atol=5e-3)
+    assert (back - lp).abs().max() < 0.25 and (back - lp).abs().mean() < 0.03
+    # teacher sampling end to end on the tiny model
+    spec = get_spec("tiny")
+    m = LlamaModel(spec, seed=0)
+    rows = [{"input_ids": torch.randint(1, spec.vocab_size, (n,)).tolist()} for n in (9, 17, 5)]
+    qc = QuantizationConfig(k=16, exact_k=4, residual_bins=[], polynomial_degree=2, vocab_size=spec.vocab_size)
+    n = process_dataset(m, rows, qc, Args(top_k=16, max_batch_tokens=20), ParquetShardWriter(str(tmp_path / "t"), 2))
+    import pyarrow.parquet as pq
+
+    files = sorted((tmp_path / "t").glob("*.parquet"))
+    assert n == 3 and len(files) == 2
+    t = pq.read_table(files[0]).to_pylist()
+    assert t[0]["num_positions"] == 9 and len(t[0]["compressed_logprobs"]) == 9 * qc.logprob_bytes()
