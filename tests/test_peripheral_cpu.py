@@ -289,3 +289,49 @@ def test_distill_compression_roundtrip_and_sampler(tmp_path):
     assert n == 3 and len(files) == 2
     t = pq.read_table(files[0]).to_pylist()
     assert t[0]["num_positions"] == 9 and len(t[0]["compressed_logprobs"]) == 9 * qc.logprob_bytes()
+
+
+def test_decontamination_and_oai_generate(tmp_path):
+    import asyncio
+
+    from open_instruct_b200.decontamination.search import find_contamination
+    from open_instruct_b200.experimental import oai_generate as og
+
+    leak = "what is the capital of the country whose flag is a red circle on white background answer tokyo"
+    train = [{"messages": [{"role": "user", "content": "hello there"}, {"role": "assistant", "content": "hi"}]},
+             {"messages": [{"role": "user", "content": "Quiz: " + leak.upper()}, {"role": "assistant", "content": "Tokyo"}]}]
+    ev = [{"text": leak}, {"text": "a completely unrelated question about prime numbers and their distribution over the integers today"}]
+    rep = find_contamination(train, ev, ["messages"], ["text"], n=8, threshold=0.5)
+    assert rep["eval_contaminated"] == 1 and rep["train_contaminated"] == [1]
+    assert find_contamination(train, ev, ["messages"], ["text"], mode="exact")["eval_contaminated"] == 0
+
+    calls = []
+
+    async def post(url, payload, headers):
+        calls.append(payload)
+        if len(calls) == 1:
+            raise RuntimeError("transient")
+        return {"choices": [{"message": {"content": "ok:" + payload["messages"][0]["content"]}}], "usage": {"total_tokens": 3}}
+
+    rows = [{"custom_id": "a", "body": {"messages": [{"role": "user", "content": "x"}]}}, {"custom_id": "b", "body": {"messages": [{"role": "user", "content": "y"}]}}]
+    out = asyncio.run(og.run_chat(rows, og.Args(max_parallel_requests=1), post=post))
+    assert [o["response"] for o in out] == ["ok:x", "ok:y"] and len(calls) == 3
+
+    state = {"polls": 0}
+
+    def http(method, url, **kw):
+        if url.endswith("/files"):
+            state["lines"] = kw["files"]["file"][1].decode().splitlines()
+            return {"id": "file-1"}
+        if url.endswith("/batches"):
+            return {"id": "b1", "status": "validating"}
+        if url.endswith("/batches/b1"):
+            state["polls"] += 1
+            return {"id": "b1", "status": "completed", "output_file_id": "file-2"}
+        if url.endswith("/content"):
+            return "\n".join(json.dumps({"custom_id": json.loads(l)["custom_id"], "response": {"body": {"choices": [{"message": {"content": "r"}}]}}})
+                             for l in state["lines"]).encode()
+        raise AssertionError(url)
+
+    out = og.run_batch(rows, og.Args(poll_seconds=0.0), http=http)
+    assert [o["response"] for o in out] == ["r", "r"] and state["polls"] == 1
