@@ -41,20 +41,20 @@ struct TileSched {
   }
 };
 
-template <bool A_MN, bool B_MN, int OUT>
+template <bool A_MN, bool B_MN, int OUT, int BN_T = BN, int STAGES_T = STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Cout, int M, int N, int K, long long ldc, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
-  uint64_t* full = bars;                 // [STAGES]
-  uint64_t* empty = bars + STAGES;       // [STAGES]
-  uint64_t* tfull = bars + 2 * STAGES;   // [2]
-  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint8_t* sB = smem + STAGES_T * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES_T * (A_STAGE_BYTES + (BN_T * BK * 2)));
+  uint64_t* full = bars;                 // [STAGES_T]
+  uint64_t* empty = bars + STAGES_T;       // [STAGES_T]
+  uint64_t* tfull = bars + 2 * STAGES_T;   // [2]
+  uint64_t* tempty = bars + 2 * STAGES_T + 2;  // [2]
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES_T + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -62,12 +62,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   TileSched sched;
   sched.num_m = (M + BM - 1) / BM;
-  sched.num_n = (N + BN - 1) / BN;
+  sched.num_n = (N + BN_T - 1) / BN_T;
   sched.total = sched.num_m * sched.num_n;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) {
+    for (int i = 0; i < STAGES_T; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
@@ -98,18 +98,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
         int m_blk, n_blk;
         sched.get(t, m_blk, n_blk);
-        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        const int m0 = m_blk * BM, n0 = n_blk * BN_T;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+          const int s = it % STAGES_T;
+          const uint32_t ph = (it / STAGES_T) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
             atomicCAS(status, 0, ST_TIMEOUT_EMPTY);
             ok = false;
             break;
           }
-          mbar_expect_tx(&full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          mbar_expect_tx(&full[s], A_STAGE_BYTES + (BN_T * BK * 2));
           uint8_t* a_dst = sA + s * A_STAGE_BYTES;
-          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * (BN_T * BK * 2);
           const int k0 = kb * BK;
           if (!A_MN) {
             tma_load_2d(a_dst, &tma_a, &full[s], k0, m0);
@@ -121,7 +121,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             tma_load_2d(b_dst, &tma_b, &full[s], k0, n0);
           } else {
 #pragma unroll
-            for (int b = 0; b < BN / 64; ++b) tma_load_2d(b_dst + b * (BK * 128), &tma_b, &full[s], n0 + b * 64, k0);
+            for (int b = 0; b < BN_T / 64; ++b) tma_load_2d(b_dst + b * (BK * 128), &tma_b, &full[s], n0 + b * 64, k0);
           }
         }
       }
@@ -129,7 +129,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN_T, A_MN, B_MN);
       uint32_t it = 0;
       uint32_t tile_i = 0;
       bool ok = true;
@@ -141,10 +141,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * BN_T;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+          const int s = it % STAGES_T;
+          const uint32_t ph = (it / STAGES_T) & 1;
           if (!mbar_wait(&full[s], ph, abort_flag)) {
             atomicCAS(status, 0, ST_TIMEOUT_FULL);
             ok = false;
@@ -152,7 +152,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * (BN_T * BK * 2));
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
             // K-major: advance 16 elements (32 B) inside the 128 B swizzle row;
@@ -185,10 +185,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_after();
       const int row = m_blk * BM + lane_grp * 32 + lane;
-      const int n0 = n_blk * BN;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * BN;
+      const int n0 = n_blk * BN_T;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * BN_T;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < BN_T / 32; ++c) {
         const int col = n0 + c * 32;
         if (col >= N) break;  // uniform across the warp
         uint32_t r[32];
@@ -294,20 +294,21 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <bool A_MN, bool B_MN, int OUT>
+template <bool A_MN, bool B_MN, int OUT, int BN_T = BN, int STAGES_T = STAGES>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc,
                   int* status, cudaStream_t stream, int max_ctas) {
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT, BN_T, STAGES_T>;
+  constexpr int smem = STAGES_T * (A_STAGE_BYTES + BN_T * BK * 2) + 1024 /*align*/ + 256 /*barriers*/;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN_T - 1) / BN_T);
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, C, M, N, K, ldc, status);
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, C, M, N, K, ldc, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -345,4 +346,19 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if (a_mn && !b_mn) { B200_DISPATCH(true, false) }
   B200_DISPATCH(true, true)
 #undef B200_DISPATCH
+}
+
+// Narrow-tile variant for small M (decode): C[M,N] = A[M,K] * B[N,K]^T, bf16 out, 128 x 64 tiles and an 8-stage ring.
+// With few rows the GEMM is a stream over the weights; 64-wide column tiles give 4x as many CTAs as the 256-wide
+// kernel, so all SMs pull on HBM (M = 256, N = 4096: 128 CTAs instead of 32).
+extern "C" int b200_gemm_bf16_skinny(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldc, int* status, void* stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2, true);
+  if (r) return 10000 + r;
+  r = make_tmap_2d(&tb, B, N, K, ldb, 64, BK, 2, true);
+  if (r) return 20000 + r;
+  return launch<false, false, OUT_BF16, 64, 8>(ta, tb, C, M, N, K, ldc, status, reinterpret_cast<cudaStream_t>(stream), 0);
 }

@@ -14,6 +14,8 @@ steps, ``b200_kv_write`` to fill cache blocks, ``b200_sample`` (Philox Gumbel-ma
 
 from __future__ import annotations
 
+import os
+
 import ctypes
 import time
 from dataclasses import dataclass, field
@@ -158,6 +160,11 @@ class RolloutEngine:
         self.base_seed = seed
         self.model_step = 0
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
+        # captured decode steps, keyed by (batch size, padded block-table width, kv splits)
+        self.use_cuda_graphs = os.environ.get("B200_DECODE_GRAPHS", "1") == "1" and tp is None
+        self._graphs: dict = {}
+        self._graph_seen: dict = {}
+        self._graph_pool = None
 
     # ------------------------------------------------------------------ public API
     def kv_cache_max_concurrency(self, seq_len: int) -> int:
@@ -296,7 +303,10 @@ class RolloutEngine:
             from ..ops.lib import call, ptr, stream_ptr
 
             pos32 = pos.to(torch.int32)
-            impl = "2cta" if T > 128 else "1cta"
+            impl = "2cta"
+            # few rows and a 4096-wide output: the 256-wide tiles leave most SMs idle, the 64-wide kernel streams the weights
+            # from four times as many CTAs (measured at M = 256: o_proj 34 -> 21 us, down_proj 81 -> 54 us)
+            impl_narrow = "skinny" if T <= 256 else "2cta"
             stream, delta = f.embedding_fwd(p["embed"], ids), None
             tp = self.tp
 
@@ -315,10 +325,10 @@ class RolloutEngine:
                 call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
                      s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
                 attn = attn_fn(i, qkv)
-                o = f.gemm(attn, p[f"l{i}.wo"], row_out(), impl=impl)
+                o = f.gemm(attn, p[f"l{i}.wo"], row_out(), impl=impl_narrow)
                 n2, h_mid = add_norm(o, p[f"l{i}.mlp_norm"], h_in)
                 act = f.swiglu_fwd(f.gemm(n2, p[f"l{i}.w_gate_up"], impl=impl))
-                delta = f.gemm(act, p[f"l{i}.w_down"], row_out(), impl=impl)
+                delta = f.gemm(act, p[f"l{i}.w_down"], row_out(), impl=impl_narrow)
                 stream = h_mid
             nf, _ = add_norm(delta, p["final_norm"], stream)
             return nf
@@ -345,7 +355,7 @@ class RolloutEngine:
         if self.ops == "fused":
             from ..ops import fused as f
 
-            return f.gemm(hidden.contiguous(), w, impl="2cta" if hidden.shape[0] > 128 else "1cta")
+            return f.gemm(hidden.contiguous(), w, impl="2cta")
         return ref.linear(hidden, w)
 
     def _prefill(self, seqs: list[_Sequence]) -> None:
@@ -402,11 +412,97 @@ class RolloutEngine:
         for q, t, lp in zip(flat_members, toks, lps):
             self._accept(q, int(t), float(lp))
 
+    # ---- fused decode step: everything between "inputs on the device" and "sampled tokens" is one replayable unit
+    def _decode_device(self, buf: dict, B: int, max_blocks: int, splits: int):
+        """Layer stack + lm_head + sampling for ``B`` sequences, reading only the device tensors in ``buf``."""
+        from ..ops.lib import call, ptr, stream_ptr
+
+        s, dev = self.spec, self.device
+        scale = s.head_dim ** -0.5
+        part_o = torch.empty(B * s.num_heads * splits * s.head_dim, dtype=torch.float32, device=dev) if splits > 1 else None
+        part_ml = torch.empty(B * s.num_heads * splits * 2, dtype=torch.float32, device=dev) if splits > 1 else None
+
+        def attn_fn(i, qkv):
+            out = torch.empty(B, s.num_heads * s.head_dim, dtype=qkv.dtype, device=dev)
+            call("b200_paged_decode", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(buf["bt"]), max_blocks, ptr(buf["ctx"]), B,
+                 s.num_heads, s.num_kv_heads, s.head_dim, scale, splits, ptr(out), ptr(part_o), ptr(part_ml), stream_ptr())
+            return out
+
+        hidden = self._layer_stack(buf["ids"], buf["pos"], buf["slots"], attn_fn)
+        logits = self._logits(hidden)
+        V = logits.shape[1]
+        toks = torch.empty(B, dtype=torch.int64, device=dev)
+        lps = torch.empty(B, dtype=torch.float32, device=dev)
+        call("b200_sample", ptr(logits), logits.stride(0), B, V, ptr(buf["temp"]), ptr(buf["top_p"]), ptr(buf["seeds"]), ptr(buf["ctr"]),
+             ptr(toks), ptr(lps), stream_ptr())
+        return toks, lps
+
+    def _decode_fused(self, seqs: list[_Sequence]):
+        """Host side of the fused decode step: pack the step's inputs, then run the device part - replaying a CUDA graph
+        when this (batch size, block-table width) has been seen before.  The launch-bound inner loop (about 400 kernels
+        for a 32-layer model) then costs one graph launch."""
+        import numpy as np
+
+        dev = self.device
+        B = len(seqs)
+        ctx_list = [len(q.tokens) for q in seqs]  # the new token sits at position len-1
+        tables = [self.host.blocks(q.sid)[0] for q in seqs]
+        need = max(len(t) for t in tables)
+        max_blocks = -(-need // 4) * 4  # padded so that one captured graph serves 256 consecutive steps
+        s = self.spec
+        splits = 1 if B * s.num_kv_heads >= 148 else max(1, min(8, 148 // max(1, B * s.num_kv_heads), max_blocks // 4))
+        bt = np.zeros((B, max_blocks), dtype=np.int32)
+        for i, t in enumerate(tables):
+            bt[i, : len(t)] = t
+        host = {
+            "ids": np.fromiter((q.last_token for q in seqs), dtype=np.int64, count=B),
+            "pos": np.fromiter((n - 1 for n in ctx_list), dtype=np.int64, count=B),
+            "slots": np.fromiter((tables[i][(n - 1) // KV_BLOCK] * KV_BLOCK + (n - 1) % KV_BLOCK for i, n in enumerate(ctx_list)), dtype=np.int64, count=B),
+            "ctx": np.asarray(ctx_list, dtype=np.int32),
+            "bt": bt,
+            "temp": np.fromiter((q.request.sampling.temperature for q in seqs), dtype=np.float32, count=B),
+            "top_p": np.fromiter((q.request.sampling.top_p for q in seqs), dtype=np.float32, count=B),
+            "seeds": np.fromiter((q.seed for q in seqs), dtype=np.int64, count=B),
+            "ctr": np.fromiter((len(q.tokens) - q.prompt_len for q in seqs), dtype=np.int32, count=B),
+        }
+        key = (B, max_blocks, splits)
+        entry = self._graphs.get(key)
+        if entry is None:
+            buf = {k: torch.from_numpy(v).to(dev) for k, v in host.items()}
+            seen = self._graph_seen.get(key, 0)
+            self._graph_seen[key] = seen + 1
+            if not self.use_cuda_graphs or seen < 1 or B < 4:
+                toks, lps = self._decode_device(buf, B, max_blocks, splits)  # eager (also the warm-up of this shape)
+                return toks.tolist(), lps.tolist()
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                toks, lps = self._decode_device(buf, B, max_blocks, splits)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            entry = (graph, buf, toks, lps)
+            if len(self._graphs) >= 48:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = entry
+            graph.replay()  # the capture only records; this runs the step
+            return toks.tolist(), lps.tolist()
+        graph, buf, toks, lps = entry
+        for k, v in host.items():
+            buf[k].copy_(torch.from_numpy(v), non_blocking=False)
+        graph.replay()
+        return toks.tolist(), lps.tolist()
+
     def _decode(self, seqs: list[_Sequence]) -> None:
         """One token for every running sequence."""
         s = self.spec
         dev = self.device
         B = len(seqs)
+        if self.ops == "fused":
+            toks, lps = self._decode_fused(seqs)
+            self.stats["decode_tokens"] += B
+            for q, t, lp in zip(seqs, toks, lps):
+                self._accept(q, int(t), float(lp))
+            return
         ids = torch.tensor([q.last_token for q in seqs], dtype=torch.long, device=dev)
         ctx_list = [len(q.tokens) for q in seqs]  # the new token sits at position len-1
         pos = torch.tensor([n - 1 for n in ctx_list], dtype=torch.long, device=dev)
@@ -420,20 +516,7 @@ class RolloutEngine:
                              dtype=torch.long, device=dev)
         ctx = torch.tensor(ctx_list, dtype=torch.int32, device=dev)
         scale = s.head_dim ** -0.5
-        if self.ops == "fused":
-            from ..ops.lib import call, ptr, stream_ptr
-
-            max_ctx = max(ctx_list)
-            splits = 1 if B * s.num_kv_heads >= 148 else max(1, min(8, (148 // max(1, B * s.num_kv_heads)), -(-max_ctx // (4 * KV_BLOCK))))
-            part_o = torch.empty(B * s.num_heads * splits * s.head_dim, dtype=torch.float32, device=dev) if splits > 1 else None
-            part_ml = torch.empty(B * s.num_heads * splits * 2, dtype=torch.float32, device=dev) if splits > 1 else None
-
-            def attn_fn(i, qkv):
-                out = torch.empty(B, s.num_heads * s.head_dim, dtype=qkv.dtype, device=dev)
-                call("b200_paged_decode", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(bt), max_blocks, ptr(ctx), B,
-                     s.num_heads, s.num_kv_heads, s.head_dim, scale, splits, ptr(out), ptr(part_o), ptr(part_ml), stream_ptr())
-                return out
-        else:
+        if True:
             g = s.num_heads // s.num_kv_heads
 
             def attn_fn(i, qkv):

@@ -100,6 +100,14 @@ def main():
                 rec(f"cublas_dgrad_{name}", time_op(lambda: torch.matmul(dy, w), args.iters), fl)
                 rec(f"cublas_wgrad_{name}", time_op(lambda: torch.matmul(dy.t(), x), args.iters), fl)
             del x, w, dy, g
+    if "decode_gemm" in only:
+        # decode-sized GEMMs: a stream over the weights; the roofline is HBM bandwidth
+        for M in (64, 256, 512):
+            for name, (N, K) in {"qkv": ((Hq + 2 * Hkv) * Dh, D), "o": (D, Hq * Dh), "gate_up": (2 * F, D), "down": (D, F)}.items():
+                x, w = bf(M, K), bf(N, K)
+                by = (N * K + M * K + M * N) * 2
+                for impl in ("1cta", "2cta", "skinny"):
+                    rec(f"decode_gemm_{name}_M{M}_{impl}", time_op(lambda: fused.gemm(x, w, impl=impl), args.iters), bytes_=by)
     if not only or "attn" in only:
         L = args.doc_len or T
         lens = [L] * (T // L) + ([T % L] if T % L else [])

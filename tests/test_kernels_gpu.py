@@ -42,6 +42,18 @@ def test_gemm_layouts(a_mn, b_mn, shape, impl):
     assert _rel(acc, ref + 1) < 1e-4
 
 
+@pytest.mark.parametrize("shape", [(1, 512, 128), (37, 200, 72), (256, 4096, 4096), (300, 6144, 1024), (512, 4096, 14336)])
+def test_gemm_skinny(shape):
+    from open_instruct_b200.ops import fused
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    out = fused.gemm(a, b, impl="skinny")
+    assert _rel(out, a.float() @ b.float().t()) < 5e-3
+
+
 def test_gemm_strided_views():
     from open_instruct_b200.ops import fused
 
