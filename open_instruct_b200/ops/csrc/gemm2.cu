@@ -98,7 +98,7 @@ template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
              void* __restrict__ Cout, int M, int N, int K, long long ldc, int* __restrict__ status,
-             const long long* __restrict__ scatter, int row_off) {
+             const long long* __restrict__ scatter, int row_off, const long long* __restrict__ scatter2) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -261,6 +261,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
                 scatter ? reinterpret_cast<__nv_bfloat16*>(scatter[col >> 7]) + static_cast<long long>(row + row_off) * ldc + (col & 127)
                         : reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<long long>(row) * ldc + col;
             if (col + 32 <= N) {
+              // second destination table: the same tile also goes to another buffer (a peer GPU's copy), so that a
+              // tensor-parallel partial result reaches every rank while the following tiles are still being computed
+              __nv_bfloat16* crow2 =
+                  scatter2 ? reinterpret_cast<__nv_bfloat16*>(scatter2[col >> 7]) + static_cast<long long>(row + row_off) * ldc + (col & 127)
+                           : nullptr;
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint4 v;
@@ -269,6 +274,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
                 v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
                 v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
                 reinterpret_cast<uint4*>(crow)[j] = v;
+                if (crow2) reinterpret_cast<uint4*>(crow2)[j] = v;
               }
             } else {
               for (int j = 0; j < 32 && col + j < N; ++j) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
@@ -321,7 +327,8 @@ static int max_pairs_cache = 0;
 
 template <bool A_MN, bool B_MN, int OUT>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc,
-                  int* status, cudaStream_t stream, int max_ctas, const long long* scatter = nullptr, int row_off = 0) {
+                  int* status, cudaStream_t stream, int max_ctas, const long long* scatter = nullptr, int row_off = 0,
+                  const long long* scatter2 = nullptr) {
   auto kern = gemm2_kernel<A_MN, B_MN, OUT>;
   static bool configured = false;
   if (!configured) {
@@ -350,7 +357,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, 
   int pairs = tiles < max_pairs_cache ? tiles : max_pairs_cache;
   if (max_ctas > 1 && pairs > max_ctas / 2) pairs = max_ctas / 2;
   cfg.gridDim = dim3(2 * pairs);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, status, scatter, row_off);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, status, scatter, row_off, scatter2);
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
@@ -389,9 +396,10 @@ extern "C" int b200_gemm2_bf16(const void* A, const void* B, void* C, int M, int
 
 // C is not one matrix: column block j (128 wide) of the bf16 result goes to `scatter[j]` (device table of base
 // addresses, local or peer memory) at row `row + row_off`, leading dimension `ld_dst`.  N % 128 == 0.
+// `scatter2` (optional): a second table of the same shape; every tile is stored to both destinations.
 extern "C" int b200_gemm2_bf16_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                                        int a_mn, int b_mn, const long long* scatter, int row_off, long long ld_dst,
-                                       int* status, void* stream) {
+                                       int* status, void* stream, const long long* scatter2) {
   using namespace b200;
   using namespace b200::g2;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -405,8 +413,8 @@ extern "C" int b200_gemm2_bf16_scatter(const void* A, const void* B, int M, int 
   else r = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2, true);
   if (r) return 20000 + r;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!a_mn && !b_mn) return g2::launch<false, false, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
-  if (!a_mn && b_mn) return g2::launch<false, true, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
-  if (a_mn && !b_mn) return g2::launch<true, false, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
-  return g2::launch<true, true, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off);
+  if (!a_mn && !b_mn) return g2::launch<false, false, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off, scatter2);
+  if (!a_mn && b_mn) return g2::launch<false, true, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off, scatter2);
+  if (a_mn && !b_mn) return g2::launch<true, false, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off, scatter2);
+  return g2::launch<true, true, g2::OUT_BF16>(ta, tb, nullptr, M, N, K, ld_dst, status, st, 0, scatter, row_off, scatter2);
 }

@@ -73,9 +73,13 @@ class TPContext:
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.device, self.hidden, self.max_tokens = torch.device(device), hidden, max_tokens
         self.peer_timeout_ms = peer_timeout_ms
+        # per parity: ``world`` slots of [max_tokens, hidden]; slot r holds rank r's partial.  A rank always writes its own
+        # slot of its own buffer; with the fused push (large T) the GEMM epilogue also stores the tile into the same slot
+        # of every peer's buffer, so that the reduction afterwards reads local memory only.
         self.bufs, self._ptrs = [], []
+        self.slot = max_tokens * hidden
         for _ in range(2):
-            b = symm_mem.empty(max_tokens * hidden, dtype=torch.bfloat16, device=self.device)
+            b = symm_mem.empty(self.world * self.slot, dtype=torch.bfloat16, device=self.device)
             b.zero_()
             h = symm_mem.rendezvous(b, self.group)
             self.bufs.append(b)
@@ -83,6 +87,19 @@ class TPContext:
             self._pads = _ptr_array(h.signal_pad_ptrs)
             self._h = h
         self._next, self._epoch = 0, 0
+        self._pushed = False
+        if hidden % 128:
+            raise ValueError("hidden size must be a multiple of 128")
+        nblk = hidden // 128
+        mine = 2 * self.rank * self.slot  # byte offset of my slot
+        self._tab_local, self._tab_peer = [], []
+        for par in range(2):
+            self._tab_local.append(torch.tensor([self._ptrs[par][self.rank] + mine + 256 * j for j in range(nblk)], dtype=torch.int64, device=self.device))
+            peer = (self.rank + 1) % self.world
+            self._tab_peer.append(torch.tensor([self._ptrs[par][peer] + mine + 256 * j for j in range(nblk)], dtype=torch.int64, device=self.device))
+        lib._SIGNATURES["b200_gemm2_bf16_scatter"] = [_P, _P, _I, _I, _I, ctypes.c_longlong, ctypes.c_longlong, _I, _I, _P, _I, ctypes.c_longlong, _P, _P, _P]
+        fn2 = lib.load_ops().b200_gemm2_bf16_scatter
+        fn2.argtypes, fn2.restype = lib._SIGNATURES["b200_gemm2_bf16_scatter"], ctypes.c_int
         fn = lib.load_ops().b200_tp_allreduce_norm
         fn.argtypes, fn.restype = lib._SIGNATURES["b200_tp_allreduce_norm"], ctypes.c_int
         torch.cuda.synchronize(self.device)
@@ -92,18 +109,38 @@ class TPContext:
         """The symmetric buffer the next row-parallel GEMM must write its ``[tokens, hidden]`` partial into."""
         if tokens > self.max_tokens:
             raise ValueError(f"{tokens} tokens exceed the tensor-parallel exchange buffer ({self.max_tokens})")
-        return self.bufs[self._next][: tokens * self.hidden].view(tokens, self.hidden)
+        a = self.rank * self.slot
+        return self.bufs[self._next][a: a + tokens * self.hidden].view(tokens, self.hidden)
+
+    def row_gemm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Row-parallel projection ``x @ w^T`` whose epilogue stores every output tile into this rank's slot of BOTH GPUs'
+        exchange buffers (two ranks): the NVLink transfer of a tile overlaps the computation of the next ones, and the
+        reduction that follows reads only local memory.  Returns this rank's partial (a view of the local slot)."""
+        if self.world != 2:
+            raise NotImplementedError("the fused push is written for two ranks")
+        T, _ = x.shape
+        out = self.out_buffer(T)
+        par = self._next
+        lib.call("b200_gemm2_bf16_scatter", ptr(x), ptr(w), T, w.shape[0], x.shape[1], x.stride(0), w.stride(0), 0, 0, ptr(self._tab_local[par]),
+                 0, self.hidden, ptr(status_word(self.device)), stream_ptr(), ptr(self._tab_peer[par]))
+        self._pushed = True
+        return out
 
     def reduce_norm(self, partial: torch.Tensor, weight: torch.Tensor | None, eps: float, res: torch.Tensor | None = None):
         """``h = res + sum_ranks partial``; ``y = rmsnorm(h) * weight``.  Returns ``(y, h)`` (``y`` is None without a weight)."""
         T, D = partial.shape
         buf = self.bufs[self._next]
-        if partial.data_ptr() != buf.data_ptr():
+        if partial.data_ptr() != buf.data_ptr() + 2 * self.rank * self.slot:
             raise ValueError("the partial must live in the buffer handed out by out_buffer()")
         h = torch.empty(T, D, dtype=torch.bfloat16, device=self.device)
         y = torch.empty_like(h) if weight is not None else None
         self._epoch += 1
-        lib.call("b200_tp_allreduce_norm", _ptr_array(self._ptrs[self._next]), self._pads, self.rank, self.world, self._epoch,
+        if self._pushed:  # every rank's partial already sits in my buffer: slot r at a local address
+            srcs = [self._ptrs[self._next][self.rank] + 2 * r * self.slot for r in range(self.world)]
+        else:             # read slot r out of rank r's buffer over NVLink
+            srcs = [self._ptrs[self._next][r] + 2 * r * self.slot for r in range(self.world)]
+        self._pushed = False
+        lib.call("b200_tp_allreduce_norm", _ptr_array(srcs), self._pads, self.rank, self.world, self._epoch,
                  ptr(res) if res is not None else None, ptr(weight) if weight is not None else None, ptr(h), ptr(y) if y is not None else None,
                  T, D, eps, self.peer_timeout_ms, ptr(status_word(self.device)), stream_ptr())
         self._next ^= 1

@@ -154,7 +154,7 @@ class UlyssesContext:
         _P, _I, _L, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint
         _PP = ctypes.POINTER(ctypes.c_void_p)
         lib._SIGNATURES.update({
-            "b200_gemm2_bf16_scatter": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _P, _I, _L, _P, _P],
+            "b200_gemm2_bf16_scatter": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _P, _I, _L, _P, _P, _P],
             "b200_a2a_heads": [_P, _L, _PP, _I, _L, _P, _I, _I, _I, _P],
             "b200_symm_barrier": [_PP, _I, _I, _U, _I, _P, _P],
         })
@@ -196,7 +196,7 @@ class UlyssesContext:
         M, K = a.shape
         N = b.shape[1] if b_mn else b.shape[0]
         lib.call("b200_gemm2_bf16_scatter", ptr(a), ptr(b), M, N, K, a.stride(0), b.stride(0), 0, int(b_mn), ptr(table), row_off, ld_dst,
-                 ptr(status_word(self.device)), stream_ptr())
+                 ptr(status_word(self.device)), stream_ptr(), None)
 
     def _a2a(self, src: torch.Tensor, region: str, offset: int, ld_dst: int, cols: torch.Tensor, T: int) -> None:
         from ..ops import lib

@@ -318,6 +318,11 @@ class RolloutEngine:
                 return tp.reduce_norm(partial, w, s.rms_norm_eps, res=res)
 
             row_out = (lambda: tp.out_buffer(T)) if tp is not None else (lambda: None)
+            push = tp is not None and tp.world == 2 and T > 256  # large batches: peer push fused into the GEMM epilogue
+
+            def row_proj(x, w):
+                return tp.row_gemm(x, w) if push else f.gemm(x, w, row_out(), impl=impl_narrow)
+
             for i in range(s.num_layers):
                 n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
                 qkv = f.gemm(n1, p[f"l{i}.wqkv"], impl=impl)
@@ -325,10 +330,10 @@ class RolloutEngine:
                 call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
                      s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
                 attn = attn_fn(i, qkv)
-                o = f.gemm(attn, p[f"l{i}.wo"], row_out(), impl=impl_narrow)
+                o = row_proj(attn, p[f"l{i}.wo"])
                 n2, h_mid = add_norm(o, p[f"l{i}.mlp_norm"], h_in)
                 act = f.swiglu_fwd(f.gemm(n2, p[f"l{i}.w_gate_up"], impl=impl))
-                delta = f.gemm(act, p[f"l{i}.w_down"], row_out(), impl=impl_narrow)
+                delta = row_proj(act, p[f"l{i}.w_down"])
                 stream = h_mid
             nf, _ = add_norm(delta, p["final_norm"], stream)
             return nf

@@ -48,12 +48,29 @@ def main():
         assert torch.equal(h, hb), (B, (h.float() - hb.float()).abs().max())
         assert torch.allclose(y.float(), y_ref, atol=2e-2, rtol=2e-2), (B, (y.float() - y_ref).abs().max())
 
+    # (1b) row-parallel GEMM with the peer push fused into its epilogue, then the purely local reduction
+    for T in (300, 1000):
+        gx = torch.Generator(device=device).manual_seed(100 + rank)
+        x = torch.randn(T, 384, device=device, generator=gx).bfloat16()
+        w = (torch.randn(D, 384, device=device, generator=gx) * 0.05).bfloat16()
+        res = torch.randn(T, D, device=device, generator=torch.Generator(device=device).manual_seed(T)).bfloat16()
+        nw = (torch.rand(D, device=device, generator=torch.Generator(device=device).manual_seed(3)) + 0.5).bfloat16()
+        part = tp.row_gemm(x, w)
+        y, h = tp.reduce_norm(part, nw, 1e-5, res=res)
+        torch.cuda.synchronize()
+        lib.check_status()
+        mine = (x.float() @ w.float().t()).bfloat16()
+        both = [torch.empty_like(mine) for _ in range(2)]
+        dist.all_gather(both, mine)
+        hb = (both[0].float() + both[1].float() + res.float()).bfloat16()
+        assert (h.float() - hb.float()).abs().max() < 0.06, (T, (h.float() - hb.float()).abs().max())
+
     # (2) engine: TP=2 against the unsharded engine
     full = LlamaModel(spec, device=device, dtype=torch.bfloat16, ops="fused", seed=11).flat.detach()
     ref_eng = RolloutEngine(spec, device=device, num_blocks=64, flat=full.clone(), eos_token_ids=[], seed=5)
     ls = local_spec(spec, 2)
     tp_eng = RolloutEngine(ls, device=device, num_blocks=64, flat=shard_flat(full, spec, rank, 2), eos_token_ids=[], seed=5, tp=tp)
-    prompts = [[(7 * i + j) % (spec.vocab_size - 1) + 1 for j in range(20 + 9 * i)] for i in range(3)]
+    prompts = [[(7 * i + j) % (spec.vocab_size - 1) + 1 for j in range(20 + 150 * i)] for i in range(3)]  # 20 + 170 + 320 > 256: pushed path
     cfg = SamplingConfig(temperature=0.01, top_p=1.0, max_tokens=12, n=1, seed=123)
     a = ref_eng.generate(prompts, cfg)
     b = tp_eng.generate(prompts, cfg)
