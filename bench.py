@@ -45,6 +45,10 @@ def parse():
     ap.add_argument("--ops", default="fused", choices=["fused", "ref"])
     ap.add_argument("--gradient_checkpointing", action="store_true")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--task", default="sft", choices=["sft", "dpo"],
+                    help="sft: the headline metric; dpo: DPO train tokens/s with cached reference log-probs (same JSON shape)")
+    ap.add_argument("--pairs_per_gpu", type=int, default=16)
+    ap.add_argument("--pairs_per_micro", type=int, default=2)
     return ap.parse_args()
 
 
@@ -66,11 +70,126 @@ def reference_arm(args) -> None:
         print(json.dumps({"impl": "reference", "unavailable": why[:400]}))
 
 
+def run_dpo(args) -> int:
+    """DPO (length-normalised sigmoid loss, beta 5) on synthetic pairs: shared prompt of 64-512 tokens, independent
+    responses of 64-1024 tokens, max length 2048, reference log-probs from a cache built before the timed region
+    (``dpo_tune_cache`` path).  Tokens/s counts every chosen and rejected token that goes through the model."""
+    import torch
+
+    from open_instruct_b200.data.collate import TensorDataCollatorWithFlatteningDPO, pin, to_device
+    from open_instruct_b200.data.synthetic import dpo_pairs
+    from open_instruct_b200.dpo_utils import DPOConfig, compute_loss, concatenated_forward
+    from open_instruct_b200.learner import Learner, LearnerConfig
+    from open_instruct_b200.models import get_spec
+    from open_instruct_b200.ops import lib
+    from open_instruct_b200.parallel import dist as pdist
+    from open_instruct_b200.utils.clocks import ClockSampler
+
+    rank, world, device = pdist.init_distributed()
+    spec = get_spec(args.model)
+    learner = Learner(spec, LearnerConfig(ops=args.ops, comm=args.comm, learning_rate=5e-7, lr_scheduler_type="linear", warmup_steps=30,
+                                          total_steps=1000, max_grad_norm=1.0, gradient_checkpointing=args.gradient_checkpointing, seed=0),
+                      device=device)
+    dcfg = DPOConfig(loss_type="dpo_norm", beta=5.0)
+    total_steps = args.warmup + 2 * args.steps
+    collate = TensorDataCollatorWithFlatteningDPO()
+    n = args.pairs_per_gpu
+    host, index = [], 0
+    for i in range(total_steps):
+        rows = dpo_pairs(n, spec.vocab_size, seed=7000 * (rank + 1) + i, max_len=2048)
+        for r in rows:
+            r["index"] = index
+            index += 1
+        host.append([pin(collate(rows[j:j + args.pairs_per_micro])) for j in range(0, n, args.pairs_per_micro)])
+    # reference cache: one forward-only pass of the initial policy over every pair (not timed, as in the cached trainer)
+    cache = {"chosen_logps": torch.zeros(index, device=device), "rejected_logps": torch.zeros(index, device=device)}
+    with torch.no_grad():
+        for mbs in host:
+            for mb in mbs:
+                mb = to_device(mb, device)
+                pc, pr, _ = concatenated_forward(learner, mb, average_log_prob=True)
+                cache["chosen_logps"][mb["index"]] = pc
+                cache["rejected_logps"][mb["index"]] = pr
+
+    def step(mbs):
+        ntok = 0
+        for mb in mbs:
+            pc, pr, aux = concatenated_forward(learner, mb, average_log_prob=True)
+            losses, _, _ = compute_loss(dcfg, mb, pc, pr, cache, (aux["chosen_tokens"], aux["rejected_tokens"]))
+            learner.backward(losses.mean())
+            ntok += mb["chosen_input_ids"].numel() + mb["rejected_input_ids"].numel()
+        learner.optimizer_step()
+        return losses.mean().detach(), ntok
+
+    def sync():
+        pdist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step([to_device(mb, device) for mb in host[i]])
+    sync()
+    lib.check_status()
+    staged = [[to_device(mb, device) for mb in host[args.warmup + i]] for i in range(args.steps)]
+    sync()
+    sampler = ClockSampler(device.index or 0).start()
+    l0 = lib.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    tok = 0
+    for i in range(args.steps):
+        loss, nt = step(staged[i])
+        tok += nt
+    e1.record()
+    sync()
+    ms = pdist.max_over_ranks(e0.elapsed_time(e1), device)
+    launches = lib.launch_count - l0
+    clocks = sampler.stop()
+    t = torch.tensor([float(tok)], device=device)
+    pdist.all_reduce_(t)
+    tok_all = float(t.item())
+    del staged
+    sync()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    f0.record()
+    tok2, h2d, lv = 0, 0, 0.0
+    for i in range(args.steps):
+        mbs = [to_device(mb, device, non_blocking=True) for mb in host[args.warmup + args.steps + i]]
+        h2d = sum(v.numel() * v.element_size() for mb in host[args.warmup + args.steps + i] for v in mb.values() if torch.is_tensor(v))
+        loss, nt = step(mbs)
+        lv = float(loss.item())
+        tok2 += nt
+    f1.record()
+    sync()
+    ms2 = pdist.max_over_ranks(max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3), device)
+    t = torch.tensor([float(tok2)], device=device)
+    pdist.all_reduce_(t)
+    lib.check_status()
+    value = tok_all / (ms / 1e3)
+    result = {"metric": "dpo_train_tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+              "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+              "dtype": "bf16", "data": "synthetic preference pairs (shared random prompt 64-512, random responses 64-1024, random-init weights)",
+              "config": {"model": args.model, "global_batch": world * n, "max_len": 2048, "pairs_per_micro_batch": args.pairs_per_micro,
+                         "loss": "dpo_norm beta 5, cached reference log-probs (built before the timed region)",
+                         "parallelism": f"dp{world} zero-sharded optimizer ({learner.comm} comm), resident bf16 params", "ops": learner.ops,
+                         "l2": "per-step working set far exceeds the 126 MB L2; no explicit flush"},
+              "clocks": clocks, "gpu_launches": launches, "loss": float(loss.item()), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+              "e2e": {"value": float(t.item()) / (ms2 / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                      "ms_per_step": ms2 / args.steps, "last_loss": lv}}
+    if rank == 0:
+        print(json.dumps(result))
+    pdist.barrier()
+    pdist.destroy()
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         reference_arm(args)
         return 0
+    if args.task == "dpo":
+        return run_dpo(args)
     import torch
 
     from open_instruct_b200.data.collate import pin, to_device
