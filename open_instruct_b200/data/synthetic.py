@@ -63,3 +63,42 @@ def dpo_pairs(n_pairs: int, vocab: int, seed: int, max_len: int = 2048) -> list[
             row[f"{side}_labels"] = lab
         rows.append(row)
     return rows
+
+
+def make_byte_tokenizer(path: str, vocab_size: int = 320) -> str:
+    """A small byte-level BPE tokenizer written to ``path`` (benchmarks and tests run without network access;
+    random-init models only need token ids below their vocabulary size)."""
+    import os
+
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    from transformers import PreTrainedTokenizerFast
+
+    corpus = ["what is 1234 + 5678 - 90 * 12 ?", "the answer is 0123456789", "user assistant system compute the value of the expression",
+              "<|user|> <|assistant|> <|system|> \n step by step reasoning result"] * 4
+    tok = Tokenizer(models.BPE(unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=vocab_size, special_tokens=["<unk>", "<s>", "</s>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(corpus, trainer)
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<s>", eos_token="</s>", unk_token="<unk>")
+    os.makedirs(path, exist_ok=True)
+    fast.save_pretrained(path)
+    return path
+
+
+def arithmetic_rlvr_jsonl(path: str, n: int, seed: int = 0) -> str:
+    """Seeded synthetic arithmetic prompts: two to four integers in [0, 10^4] joined by + - *; the ground truth is the
+    exact value; verifier ``gsm8k`` (last integer of the response must equal it)."""
+    import json
+    import random
+
+    rng = random.Random(seed)
+    with open(path, "w") as fh:
+        for _ in range(n):
+            k = rng.randint(2, 4)
+            nums = [rng.randint(0, 10**4) for _ in range(k)]
+            ops = [rng.choice("+-*") for _ in range(k - 1)]
+            expr = str(nums[0]) + "".join(f" {o} {v}" for o, v in zip(ops, nums[1:]))
+            fh.write(json.dumps({"messages": [{"role": "user", "content": f"Compute the value of the expression: {expr}. Give the final integer."}],
+                                 "ground_truth": str(eval(expr)), "dataset": "gsm8k"}) + "\n")  # noqa: S307 - digits and + - * only
+    return path

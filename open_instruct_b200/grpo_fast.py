@@ -703,7 +703,8 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
                 client = {"training_step": step, "optimizer_steps": call(learners[0], "optimizer_steps"), "episode": step * per_step,
                           "num_total_tokens": total_tokens, "data_prep_actor_state": prep.get_state()}
                 call_all(learners, "save_checkpoint_state", args.checkpoint_state_dir, client)
-        call_all(learners, "save_model", args.output_dir, tc.tokenizer_name_or_path)
+        if args.save_final_model:
+            call_all(learners, "save_model", args.output_dir, tc.tokenizer_name_or_path)
     finally:
         prep.shutdown()
         if single_objs:
