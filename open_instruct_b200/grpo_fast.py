@@ -167,6 +167,37 @@ def grpo_train_step(learner: Learner, data: CollatedBatchData, args: GRPOExperim
 
 
 # ======================================================================================= engine worker
+class _TPLeader:
+    """Rank 0 of a tensor-parallel engine: forwards every state-changing engine call to the other ranks before running it
+    itself.  Calls are batched: ``add_request`` only records; ``step`` (or ``send``) broadcasts the batch."""
+
+    def __init__(self, engine, group):
+        self._e, self._g, self._cmds = engine, group, []
+
+    def __getattr__(self, name):
+        return getattr(self._e, name)
+
+    def __setattr__(self, name, value):
+        if name.startswith("_"):
+            object.__setattr__(self, name, value)
+        else:
+            setattr(self._e, name, value)
+
+    def add_request(self, prompt, sampling, **meta):
+        self._cmds.append(("add", list(prompt), sampling))
+        return self._e.add_request(prompt, sampling, **meta)
+
+    def send(self, extra: list) -> None:
+        import torch.distributed as dist
+
+        batch, self._cmds = self._cmds + list(extra), []
+        dist.broadcast_object_list([batch], src=0, group=self._g)
+
+    def step(self):
+        self.send([("step",)])
+        return self._e.step()
+
+
 class EngineWorker:
     """Rollout engine + its request loop (the role of ``LLMRayActor``, ``open_instruct/vllm_utils.py:553-843``).
 
@@ -177,9 +208,10 @@ class EngineWorker:
     def __init__(self, spec, prompt_queue, results_queue, eval_queue, reward_config: RewardConfig | None, tokenizer=None,
                  device="cuda", ops: str = "auto", seed: int = 0, max_model_len: int = 8192, num_blocks: int | None = None,
                  gpu_memory_utilization: float = 0.85, flat: torch.Tensor | None = None, inflight_updates: bool = True,
-                 max_running: int = 256, envs_config=None):
+                 max_running: int = 256, envs_config=None, tp_rank: int = 0, tp_size: int = 1, tp_addr: str = "127.0.0.1", tp_port: int = 0):
         from .rollout.engine import RolloutEngine
 
+        self.tp_rank, self.tp_size = tp_rank, tp_size
         if isinstance(tokenizer, TokenizerConfig):  # built in the worker's own process
             tokenizer = tokenizer.tokenizer
         if device == "auto":
@@ -191,9 +223,14 @@ class EngineWorker:
         if flat is not None:
             want = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
             flat = flat.detach().to(device=device, dtype=want).clone()
-        self.engine = RolloutEngine(spec, device=device, ops=ops, seed=seed, max_model_len=max_model_len, num_blocks=num_blocks,
-                                    gpu_memory_utilization=gpu_memory_utilization, flat=flat, tokenizer=tokenizer,
-                                    max_running=max_running)
+        self.full_flat = None  # tensor parallel: staging copy of the whole model that the learners push into
+        if tp_size > 1:
+            self.engine = self._build_tp_engine(spec, device, ops, seed, max_model_len, num_blocks, gpu_memory_utilization, flat, tokenizer,
+                                                max_running, tp_addr, tp_port)
+        else:
+            self.engine = RolloutEngine(spec, device=device, ops=ops, seed=seed, max_model_len=max_model_len, num_blocks=num_blocks,
+                                        gpu_memory_utilization=gpu_memory_utilization, flat=flat, tokenizer=tokenizer,
+                                        max_running=max_running)
         self.prompt_q, self.results_q, self.eval_q = prompt_queue, results_queue, eval_queue
         self.reward_fn = reward_config.build() if reward_config is not None else None
         self.tokenizer = tokenizer
@@ -220,8 +257,70 @@ class EngineWorker:
             parser = create_tool_parser(envs_config.tool_parser_type, names)
             self.tool_runner = ToolRunner(pools, parser, tokenizer, envs_config.max_steps, envs_config.max_tool_calls, text_env)
             self.engine.tokenizer = tokenizer
-        self.thread = threading.Thread(target=self._loop, name="engine-loop", daemon=True)
+        self.thread = threading.Thread(target=self._loop if tp_rank == 0 else self._follow, name="engine-loop", daemon=True)
         self.thread.start()
+
+    # ------------------------------------------------------------------ tensor-parallel engines
+    def _build_tp_engine(self, spec, device, ops, seed, max_model_len, num_blocks, util, flat, tokenizer, max_running, addr, port):
+        """One rank of a tensor-parallel engine: own process group (NCCL for the symmetric-memory set-up, gloo for the
+        command stream), this rank's weight shard, a KV cache for its heads.  Rank 0 drives; the others mirror every
+        engine call it makes (``_TPLeader`` / ``_follow``), so all ranks run the same schedule on the same requests."""
+        import datetime
+
+        import torch.distributed as dist
+
+        from .parallel.tp import TPContext, local_spec, shard_flat
+        from .rollout.engine import KV_BLOCK, RolloutEngine
+
+        dev = torch.device(device)
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl", init_method=f"tcp://{addr}:{port}", rank=self.tp_rank, world_size=self.tp_size,
+                                timeout=datetime.timedelta(seconds=600), device_id=dev)
+        self._tp_cmd_group = dist.new_group(backend="gloo")
+        ls = local_spec(spec, self.tp_size)
+        if flat is None:
+            raise ValueError("a tensor-parallel engine needs the initial weights")
+        self.full_flat = flat
+        self._tp_spec = spec
+        local = shard_flat(flat, spec, self.tp_rank, self.tp_size)
+        tp = TPContext(spec.hidden_size, max(4096, max_model_len), dev)
+        if num_blocks is None:
+            free, total = torch.cuda.mem_get_info(dev)
+            per_block = 2 * ls.num_layers * ls.num_kv_heads * KV_BLOCK * ls.head_dim * 2
+            n = torch.tensor([max(16, int((free - (1 - util) * total) // per_block))], dtype=torch.int64, device=dev)
+            dist.all_reduce(n, op=dist.ReduceOp.MIN)  # every rank must see the same number of KV blocks: same schedule
+            num_blocks = int(n.item())
+        eng = RolloutEngine(ls, device=dev, ops=ops, seed=seed, max_model_len=max_model_len, num_blocks=num_blocks, flat=local, tokenizer=tokenizer,
+                            max_running=max_running, tp=tp)
+        return _TPLeader(eng, self._tp_cmd_group) if self.tp_rank == 0 else eng
+
+    def _reshard(self, model_step: int) -> None:
+        from .parallel.tp import shard_flat
+
+        shard_flat(self.full_flat, self._tp_spec, self.tp_rank, self.tp_size, out=self.engine.model.flat.detach())
+        self.engine.model_step = model_step
+
+    def _follow(self) -> None:
+        """Ranks > 0 of a tensor-parallel engine: apply the leader's command batches in order."""
+        import torch.distributed as dist
+
+        try:
+            if self.engine.device.type == "cuda":
+                torch.cuda.set_device(self.engine.device)
+            while not self.shutdown_flag.is_set():
+                box = [None]
+                dist.broadcast_object_list(box, src=0, group=self._tp_cmd_group)
+                for cmd in box[0]:
+                    if cmd[0] == "add":
+                        self.engine.add_request(cmd[1], cmd[2])
+                    elif cmd[0] == "step":
+                        self.engine.step()
+                    elif cmd[0] == "reshard":
+                        self._reshard(cmd[1])
+                    elif cmd[0] == "stop":
+                        self.shutdown_flag.set()
+        except BaseException as e:  # noqa: BLE001
+            self.error = e
+            logger.exception("tensor-parallel follower failed")
 
     def ready(self) -> bool:
         return True
@@ -241,6 +340,16 @@ class EngineWorker:
     def update_weights(self, flat, model_step: int) -> None:
         """In-process sync: copy ``flat`` into the engine's buffer (None: weights were already written
         into the buffer by a peer through its IPC mapping; only the version changes)."""
+        if self.tp_size > 1:
+            if self.tp_rank == 0:  # followers reshard when the leader's command reaches them, at the same point of the schedule
+                with self.lock:
+                    if flat is not None:
+                        self.full_flat.copy_(flat.to(self.full_flat.dtype))
+                    self.engine.send([("reshard", model_step)])
+                    self._reshard(model_step)
+            elif flat is not None:
+                self.full_flat.copy_(flat.to(self.full_flat.dtype))
+            return
         with self.lock:
             if flat is not None:
                 self.engine.update_weights(flat, model_step)
@@ -251,7 +360,7 @@ class EngineWorker:
         """Picklable description of the parameter buffer for a CUDA-IPC mapping in another process."""
         from .parallel.weight_sync import export_buffer
 
-        return export_buffer(self.engine.model.flat.detach())
+        return export_buffer(self.full_flat if self.tp_size > 1 else self.engine.model.flat.detach())
 
     def _score(self, res: GenerationResult, req: PromptRequest) -> None:
         decoded = self.tokenizer.batch_decode(res.responses, skip_special_tokens=True) if self.tokenizer is not None else \
@@ -369,6 +478,9 @@ class EngineWorker:
         (self.eval_q if req.is_eval and self.eval_q is not None else self.results_q).put(out)
 
     def shutdown(self) -> None:
+        if self.tp_size > 1 and self.tp_rank == 0:
+            with self.lock:
+                self.engine.send([("stop",)])
         self.shutdown_flag.set()
         self.thread.join(timeout=10)
         if self.tool_runner is not None:
@@ -516,6 +628,45 @@ def validate_configs(args: GRPOExperimentConfig, streaming: StreamingDataLoaderC
         raise ValueError("single_gpu_mode runs exactly one learner and one engine")
 
 
+def submit_eval_prompts(eval_dataset, prompt_q, streaming: StreamingDataLoaderConfig, args: GRPOExperimentConfig, step: int, top_p: float = 1.0) -> int:
+    """Queue every evaluation prompt (``is_eval`` requests go to the eval queue when they finish).  ``eval_pass_at_k``
+    samples per prompt at the training temperature (cf. ``open_instruct/grpo_fast.py:1648-1720``)."""
+    from .data_types import PromptRequest, SamplingConfig
+
+    cfg = SamplingConfig(temperature=streaming.temperature if args.eval_pass_at_k > 1 else 0.0, top_p=top_p, max_tokens=streaming.eval_response_length,
+                         n=max(1, args.eval_pass_at_k), stop=streaming.stop_strings or None, seed=args.seed + 7919 * step)
+    for i in range(len(eval_dataset)):
+        row = eval_dataset[i]
+        prompt_q.put(PromptRequest(prompt=list(row["input_ids_prompt"]), generation_config=cfg, index=int(row.get("index", i)), prompt_id=f"eval_{step}_{i}",
+                                   is_eval=True, raw_query=row.get("prompt"), ground_truth=row.get("ground_truth"), dataset=row.get("dataset"),
+                                   training_step=step))
+    return len(eval_dataset)
+
+
+def collect_eval_results(eval_q, expected: int, timeout: float, args: GRPOExperimentConfig, max_possible_score: float) -> tuple[dict, int]:
+    """Drain up to ``expected`` evaluation results (waiting at most ``timeout`` seconds) and reduce them to metrics."""
+    from .grpo_utils import compute_pass_at_k_metrics
+
+    got, deadline = [], time.time() + timeout
+    while len(got) < expected:
+        try:
+            got.append(eval_q.get(timeout=max(0.0, min(1.0, deadline - time.time()))))
+        except Exception:  # noqa: BLE001 - empty
+            if time.time() >= deadline:
+                break
+    if not got:
+        return {}, 0
+    scores = [s for r in got for s in (r.reward_scores or [])]
+    lens = [len(x) for r in got for x in r.responses]
+    stops = [fr == "stop" for r in got for fr in r.finish_reasons]
+    pids = [r.prompt_id for r in got for _ in r.responses]
+    m = {"eval/scores": float(np.mean(scores)) if scores else 0.0, "eval/sequence_lengths": float(np.mean(lens)) if lens else 0.0,
+         "eval/sequence_lengths_max": float(max(lens)) if lens else 0.0, "eval/stop_rate": float(np.mean(stops)) if stops else 0.0,
+         "eval/num_prompts": float(len(got))}
+    m.update(compute_pass_at_k_metrics(scores, pids, max(1, args.eval_pass_at_k), max_possible_score))
+    return m, len(got)
+
+
 def load_prompt_dataset(streaming: StreamingDataLoaderConfig, tc: TokenizerConfig, eval_split: bool = False):
     from .data.mixer import get_cached_dataset_tulu
 
@@ -617,13 +768,27 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
                     for r in range(args.world_size)]
             learners = [f.result() for f in futs]
         init_flat = ray.get(learners[0].flat_weights_cpu.remote())
-        engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
-            spec, prompt_q, results_q, eval_q, reward_cfg, tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len,
-            None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates, 256, tools_config)
-            for i in range(vllm.vllm_num_engines)]
-        ray.get([e.ready.remote() for e in engines] + [l.ready.remote() for l in learners])
+        tp = vllm.vllm_tensor_parallel_size if cuda else 1
+        followers = []
+        if tp == 1:
+            engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
+                spec, prompt_q, results_q, eval_q, reward_cfg, tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len,
+                None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates, 256, tools_config)
+                for i in range(vllm.vllm_num_engines)]
+        else:
+            # every rank of a tensor-parallel engine is its own process on its own GPU; the ranks of one engine rendezvous in
+            # __init__, so they are created together
+            with ThreadPoolExecutor(max_workers=tp * vllm.vllm_num_engines) as ex:
+                futs = [[ex.submit(EW.options(num_gpus=1, max_concurrency=8).remote, spec, prompt_q, results_q, eval_q, reward_cfg if r == 0 else None,
+                                   tc_plain, "auto", args.ops, args.seed + 100 * i, max_len, None, vllm.vllm_gpu_memory_utilization, init_flat,
+                                   streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", port + 50 + i)
+                         for r in range(tp)] for i in range(vllm.vllm_num_engines)]
+                handles = [[f.result() for f in row] for row in futs]
+            engines = [row[0] for row in handles]
+            followers = [h for row in handles for h in row[1:]]
+        ray.get([e.ready.remote() for e in engines + followers] + [l.ready.remote() for l in learners])
         if cuda:
-            descs = ray.get([e.weight_buffer_ipc.remote() for e in engines])
+            descs = ray.get([e.weight_buffer_ipc.remote() for e in engines + followers])
             ray.get([l.connect_engines.remote(descs) for l in learners])
         single_objs = False
 
@@ -665,6 +830,8 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
             prep.model_step = resume_step
             weight_sync(resume_step)
     prep.start()
+    eval_outstanding = 0
+    max_score = streaming.verification_reward + (streaming.r1_style_format_reward if streaming.apply_r1_style_format_reward else 0.0)
     total_tokens, t_run = 0, time.time()
     try:
         for step in range(resume_step + 1, args.num_training_steps + 1):
@@ -694,6 +861,20 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
                     "learner_mfu": dims.approximate_learner_utilization(tokens, prep_metrics.get("val/sequence_lengths", 1.0) +
                                                                         streaming.max_prompt_token_length, metrics.get("time/training", dt),
                                                                         args.world_size) if torch.cuda.is_available() else 0.0}
+            # ---- evaluation: prompts ride along with the training rollouts; results are picked up when they are ready
+            is_last = step == args.num_training_steps
+            if eval_dataset is not None and len(eval_dataset) and args.local_eval_every > 0 and (step % args.local_eval_every == 0 or is_last) \
+                    and eval_outstanding == 0:
+                eval_outstanding = submit_eval_prompts(eval_dataset, prompt_q, streaming, args, step, vllm.vllm_top_p)
+            if eval_outstanding:
+                em, n_got = collect_eval_results(eval_q, eval_outstanding, 600.0 if is_last else 0.0, args, max_score)
+                if n_got >= eval_outstanding or is_last:
+                    last.update(em)
+                    eval_outstanding = 0
+                elif n_got:
+                    # partial drain: put the count back so that the rest is not waited for twice
+                    eval_outstanding -= n_got
+                    last.update({k: v for k, v in em.items() if k == "eval/num_prompts"})
             tracker.log(last, step)
             logger.info("step %d: score %.3f loss %.4f len %.1f sync %.3fs", step, last.get("scores", 0.0), last.get("loss/total_avg", 0.0),
                         last.get("val/sequence_lengths", 0.0), t_sync)
@@ -711,7 +892,12 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
             for e in engines:
                 e.shutdown()
         else:
-            for h in list(engines) + list(learners):
+            for h in list(engines):
+                try:
+                    ray.get(h.shutdown.remote(), timeout=20)  # tensor-parallel leaders release their followers first
+                except Exception:  # noqa: BLE001
+                    pass
+            for h in list(engines) + list(followers) + list(learners):
                 ray.kill(h)
             for q in (prompt_q, results_q, eval_q):
                 q.shutdown()

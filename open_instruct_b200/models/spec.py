@@ -125,6 +125,9 @@ PRESETS: dict[str, ModelSpec] = {
     "tiny": ModelSpec(vocab_size=512, hidden_size=64, intermediate_size=256, num_layers=2, num_heads=4,
                       num_kv_heads=4, head_dim=16, rope_theta=1e4, max_position_embeddings=2048),
     # tiny but with head_dim 128 so the tcgen05 attention path is exercised
+    # tiny, head_dim 128, heads that divide by 2: the smallest model tensor and sequence parallelism can split
+    "tiny128-tp": ModelSpec(vocab_size=512, hidden_size=512, intermediate_size=1024, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
+                            rope_theta=10000.0, max_position_embeddings=4096),
     "tiny128": ModelSpec(vocab_size=512, hidden_size=256, intermediate_size=512, num_layers=2, num_heads=2,
                          num_kv_heads=1, head_dim=128, rope_theta=1e4, max_position_embeddings=4096),
     "llama3.2-1b": ModelSpec(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_layers=16,

@@ -160,6 +160,7 @@ class RolloutEngine:
         self.base_seed = seed
         self.model_step = 0
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
+        self.prefill_token_budget = 16384
         # captured decode steps, keyed by (batch size, padded block-table width, kv splits)
         self.use_cuda_graphs = os.environ.get("B200_DECODE_GRAPHS", "1") == "1" and tp is None
         self._graphs: dict = {}
@@ -380,6 +381,20 @@ class RolloutEngine:
                 for q in qs:
                     reps.append(q)
                     members.append([q])
+        # run the prompts in sub-batches of at most ``prefill_token_budget`` tokens (documents are independent): bounds the
+        # activation memory of a step and, with tensor parallelism, fits the exchange buffers
+        budget = self.prefill_token_budget if self.tp is None else min(self.prefill_token_budget, self.tp.max_tokens)
+        i = 0
+        while i < len(reps):
+            j, tok = i, 0
+            while j < len(reps) and (j == i or tok + len(reps[j].tokens) <= budget):
+                tok += len(reps[j].tokens)
+                j += 1
+            self._prefill_batch(reps[i:j], members[i:j])
+            i = j
+
+    def _prefill_batch(self, reps: list, members: list) -> None:
+        s = self.spec
         ids = torch.tensor([t for q in reps for t in q.tokens], dtype=torch.long)
         lens = [len(q.tokens) for q in reps]
         T = int(ids.numel())

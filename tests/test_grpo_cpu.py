@@ -20,9 +20,12 @@ def test_grpo_single_process(tmp_path):
     data = make_rlvr_jsonl(os.path.join(tmp, "rl.jsonl"), n=12)
     args = GRPOExperimentConfig(total_episodes=3 * 4 * 4, learning_rate=1e-3, beta=0.0, load_ref_policy=False, output_dir=os.path.join(tmp, "out"),
                                 single_gpu_mode=True, ops="ref", seed=3, save_freq=-1, checkpoint_state_freq=2,
-                                checkpoint_state_dir=os.path.join(tmp, "state"), lr_scheduler_type="constant", record_entropy=True)
+                                checkpoint_state_dir=os.path.join(tmp, "state"), lr_scheduler_type="constant", record_entropy=True,
+                                local_eval_every=2, eval_pass_at_k=2)
+    eval_data = make_rlvr_jsonl(os.path.join(tmp, "eval.jsonl"), n=3)
     streaming = StreamingDataLoaderConfig(max_prompt_token_length=64, response_length=12, pack_length=256, async_steps=1,
                                           num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=4, dataset_mixer_list=[data, "1.0"],
+                                          dataset_mixer_eval_list=[eval_data, "1.0"], dataset_mixer_eval_list_splits=["train"],
                                           dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False, temperature=1.0)
     out = main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path="tiny"), streaming,
                VLLMConfig())
@@ -35,6 +38,8 @@ def test_grpo_single_process(tmp_path):
         assert "policy/entropy_avg" in l and l["time/weight_sync"] >= 0
     assert os.path.exists(os.path.join(args.output_dir, "model.safetensors"))
     assert os.path.exists(os.path.join(tmp, "state", "step_2", "COMPLETED"))
+    # evaluation prompts were submitted at step 2 and at the last step; the last step waits for its results
+    assert lines[-1]["eval/num_prompts"] == 3 and "eval/pass_at_2" in lines[-1] and lines[-1]["eval/sequence_lengths"] > 0
 
 
 def test_grpo_train_step_moves_policy_toward_advantage():

@@ -12,7 +12,7 @@ from helpers import make_rlvr_jsonl, make_tokenizer
 pytestmark = pytest.mark.gpu
 
 
-def _run(tmp, single):
+def _run(tmp, single, tp=1, model="tiny128"):
     from open_instruct_b200.actors import ray_compat as ray
     from open_instruct_b200.config.schemas import ModelConfig
     from open_instruct_b200.data.tokenize import TokenizerConfig
@@ -28,8 +28,8 @@ def _run(tmp, single):
                                           num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=4, dataset_mixer_list=[data, "1.0"],
                                           dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False)
     try:
-        out = main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path="tiny128"),
-                   streaming, VLLMConfig(vllm_gpu_memory_utilization=0.3))
+        out = main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path=model),
+                   streaming, VLLMConfig(vllm_gpu_memory_utilization=0.3, vllm_tensor_parallel_size=tp))
     finally:
         ray.shutdown()
     lines = [json.loads(l) for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
@@ -48,4 +48,13 @@ def test_grpo_learner_and_engine_processes_ipc_push(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     lines = _run(str(tmp_path), single=False)
+    assert all(l["time/weight_sync"] < 30 for l in lines)
+
+
+def test_grpo_tensor_parallel_engine(tmp_path):
+    """One learner + one rollout engine split over two GPUs (three processes, three GPUs)."""
+    if torch.cuda.device_count() < 3:
+        pytest.skip("needs 3 GPUs")
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    lines = _run(str(tmp_path), single=False, tp=2, model="tiny128-tp")
     assert all(l["time/weight_sync"] < 30 for l in lines)
