@@ -356,6 +356,17 @@ class EngineWorker:
             else:
                 self.engine.model_step = model_step
 
+    def weights_checksum(self, expect_step: int | None = None) -> tuple[float, int, int]:
+        """(sum of the weights this rank computes with, tp rank, tp size) - compared with the learner's after a sync.
+        A tensor-parallel follower applies the reshard when the leader's command reaches it: wait (bounded) for that."""
+        deadline = time.time() + 10.0
+        while expect_step is not None and self.engine.model_step != expect_step and time.time() < deadline:
+            time.sleep(0.002)
+        with self.lock:
+            w = self.engine.model.flat.detach()
+            n = self.engine.model.layout.total
+            return float(w[:n].double().sum().item()), self.tp_rank, self.tp_size
+
     def weight_buffer_ipc(self):
         """Picklable description of the parameter buffer for a CUDA-IPC mapping in another process."""
         from .parallel.weight_sync import export_buffer
@@ -531,6 +542,15 @@ class LearnerWorker:
 
     def flat_weights(self) -> torch.Tensor:
         return self.learner.model.flat.detach()
+
+    def weights_checksum(self, tp_rank: int = 0, tp_size: int = 1) -> float:
+        """Sum of the bf16 working weights, or of the shard a tensor-parallel engine rank holds of them."""
+        w = self.learner.model.flat.detach()
+        if tp_size > 1:
+            from .parallel.tp import shard_flat
+
+            return float(shard_flat(w[: self.learner.model.layout.total].contiguous(), self.spec, tp_rank, tp_size).double().sum().item())
+        return float(w[: self.learner.model.layout.total].double().sum().item())
 
     def flat_weights_cpu(self) -> torch.Tensor:
         return self.learner.model.flat.detach().to("cpu", copy=True)
@@ -730,6 +750,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
                               non_stop_penalty=streaming.non_stop_penalty, non_stop_penalty_value=streaming.non_stop_penalty_value,
                               additive_format_reward=streaming.additive_format_reward, reward_aggregator=streaming.reward_aggregator,
                               verifier_functions=build_all_verifiers(args, streaming))
+    followers: list = []
     few_gpus = not torch.cuda.is_available() or torch.cuda.device_count() < 2
     single = args.single_gpu_mode or (args.world_size == 1 and vllm.vllm_num_engines == 1 and few_gpus)
     max_len = streaming.max_prompt_token_length + max(streaming.response_length, streaming.eval_response_length or 0)
@@ -848,6 +869,12 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
             t_sync = weight_sync(step)
             if t_sync > WEIGHT_SYNC_TIMEOUT_S:
                 raise TimeoutError("weight sync exceeded its time limit")
+            sync_err = None
+            if args.verify_weight_sync and not single_objs:
+                sync_err = 0.0
+                for h in list(engines) + list(followers):
+                    got, r, n = call(h, "weights_checksum", step)
+                    sync_err = max(sync_err, abs(got - call(learners[0], "weights_checksum", r, n)))
             call_all(engines, "set_should_stop", False)
             manager.set_should_stop(False)
             prep.set_model_step(step)
@@ -856,6 +883,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
             dt = time.perf_counter() - t_step
             last = {**prep_metrics, **metrics, "training_step": step, "episode": step * per_step, "time/total": dt,
                     "time/weight_sync": t_sync, "time/trainer_waiting_for_data": t_wait,
+                    **({"debug/weight_sync_checksum_diff": sync_err} if sync_err is not None else {}),
                     "learner_tokens_per_second_step": tokens / max(metrics.get("time/training", dt), 1e-9),
                     "learner_tokens_per_second_overall": total_tokens / max(time.time() - t_run, 1e-9),
                     "learner_mfu": dims.approximate_learner_utilization(tokens, prep_metrics.get("val/sequence_lengths", 1.0) +

@@ -47,6 +47,7 @@ class GRPOExperimentConfig(ExperimentConfig):
     num_training_steps: int | None = None
     local_eval_every: int = 100
     save_freq: int = 200
+    verify_weight_sync: bool = False  # debug: after every sync compare weight checksums of the learner and every engine rank
     save_final_model: bool = True  # benchmarks switch the final Hugging Face export off
     backend_timeout: int = 120
     model_dtype: str = "bfloat16"

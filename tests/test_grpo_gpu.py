@@ -12,7 +12,7 @@ from helpers import make_rlvr_jsonl, make_tokenizer
 pytestmark = pytest.mark.gpu
 
 
-def _run(tmp, single, tp=1, model="tiny128"):
+def _run(tmp, single, tp=1, model="tiny128", verify=False):
     from open_instruct_b200.actors import ray_compat as ray
     from open_instruct_b200.config.schemas import ModelConfig
     from open_instruct_b200.data.tokenize import TokenizerConfig
@@ -23,7 +23,7 @@ def _run(tmp, single, tp=1, model="tiny128"):
     tok = make_tokenizer(os.path.join(tmp, "tok"))
     data = make_rlvr_jsonl(os.path.join(tmp, "rl.jsonl"), n=12)
     args = GRPOExperimentConfig(total_episodes=3 * 4 * 4, learning_rate=1e-4, beta=0.0, load_ref_policy=False, output_dir=os.path.join(tmp, "out"),
-                                single_gpu_mode=single, ops="fused", seed=3, save_freq=-1, lr_scheduler_type="constant")
+                                single_gpu_mode=single, ops="fused", seed=3, save_freq=-1, lr_scheduler_type="constant", verify_weight_sync=verify)
     streaming = StreamingDataLoaderConfig(max_prompt_token_length=64, response_length=16, pack_length=256, async_steps=1,
                                           num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=4, dataset_mixer_list=[data, "1.0"],
                                           dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False)
@@ -36,7 +36,10 @@ def _run(tmp, single, tp=1, model="tiny128"):
     assert out["training_step"] == 3 and len(lines) == 3
     # the engine and the learner run the same weights through the same kernels: their log-probs agree
     assert lines[0]["debug/vllm_vs_local_logprob_diff_mean"] < 0.05
-    assert lines[-1]["debug/vllm_vs_local_logprob_diff_mean"] < 0.05  # still true after two weight syncs
+    if verify:  # the engines compute with exactly the learner's weights after every sync
+        assert all(l["debug/weight_sync_checksum_diff"] == 0.0 for l in lines)
+    else:
+        assert lines[-1]["debug/vllm_vs_local_logprob_diff_mean"] < 0.05  # still true after two weight syncs
     return lines
 
 
@@ -47,7 +50,7 @@ def test_grpo_single_gpu_mode(tmp_path):
 def test_grpo_learner_and_engine_processes_ipc_push(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    lines = _run(str(tmp_path), single=False)
+    lines = _run(str(tmp_path), single=False, verify=True)
     assert all(l["time/weight_sync"] < 30 for l in lines)
 
 
@@ -56,5 +59,5 @@ def test_grpo_tensor_parallel_engine(tmp_path):
     if torch.cuda.device_count() < 3:
         pytest.skip("needs 3 GPUs")
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    lines = _run(str(tmp_path), single=False, tp=2, model="tiny128-tp")
+    lines = _run(str(tmp_path), single=False, tp=2, model="tiny128-tp", verify=True)
     assert all(l["time/weight_sync"] < 30 for l in lines)
