@@ -164,6 +164,9 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
         loader.load_state_dict(st["loader"])
 
     # ------------------------------------------------------------------ phase B: training
+    from .utils.common import StepProfiler
+
+    profiler = StepProfiler(args.profiling, args.output_dir, rank)
     metrics = MetricsTracker(device=device)
     t_start, tokens_seen, last = time.time(), 0, {}
     for epoch in range(start_epoch, args.num_epochs):
@@ -203,6 +206,7 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
                     cu = mb[f"{k}_cu_seq_lens_q"]
                     lengths += (cu[1:] - cu[:-1]).tolist()
             norm = learner.optimizer_step()
+            profiler.step()
             completed += 1
             if completed % args.logging_steps == 0:
                 metrics.reduce_(average=True)
@@ -229,6 +233,7 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
     pdist.barrier()
     if is_main:
         save_hf_checkpoint(learner.model.flat, spec, args.output_dir, tokenizer=tokenizer)
+    profiler.close()
     tracker.close()
     pdist.barrier()
     last["completed_steps"] = completed

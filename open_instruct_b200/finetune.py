@@ -125,6 +125,7 @@ class FlatArguments:
     packing: bool = field(default=False, metadata={"help": "Fill micro-batches up to max_seq_length tokens (padding-free either way)"})
     verbose: bool = False
     sequence_parallel_size: int = field(default=1, metadata={"help": "Ulysses sequence-parallel degree"})
+    profiling: bool = field(default=False, metadata={"help": "torch.profiler trace of a few steps into <output_dir>/profiler"})
     offload_optimizer: bool = field(default=False, metadata={"help": "keep fp32 master weights and Adam moments in pinned host memory"})
     # engine selection (not in the reference: there the back end is fixed by the launcher config)
     ops: Literal["auto", "fused", "ref"] = "auto"
@@ -258,6 +259,9 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
             clean_last_n_checkpoints(args.output_dir, args.keep_last_n_checkpoints)
 
     # ------------------------------------------------------------------ loop
+    from .utils.common import StepProfiler
+
+    profiler = StepProfiler(args.profiling, args.output_dir, rank)
     total_tokens = torch.zeros((), dtype=torch.long, device=device)
     pred_tokens = torch.zeros((), dtype=torch.long, device=device)
     loss_acc = torch.zeros((), device=device)
@@ -274,6 +278,7 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                 break
             mbs = [to_device(mb, device) for mb in mbs]
             out = learner.sft_step(mbs, args.reduce_loss)
+            profiler.step()
             completed += 1
             loss_acc += out["loss"].detach()
             pred_tokens += out["target_tokens"]
@@ -303,6 +308,7 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
         if completed >= max_steps:
             break
 
+    profiler.close()
     # ------------------------------------------------------------------ final export
     pdist.barrier()
     if is_main:

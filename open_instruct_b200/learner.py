@@ -19,6 +19,7 @@ from .data.collate import IGNORE
 from .models import LlamaModel, ModelSpec
 from .parallel import dist as pdist
 from .parallel.zero import ZeroOptimizer, lr_at, padded_numel
+from .utils.common import nvtx_range
 
 
 @dataclass
@@ -111,11 +112,13 @@ class Learner:
                      c.lr_scheduler_type, c.final_lr_ratio)
 
     def token_logprobs(self, batch: dict, temperature: float = 1.0, want_entropy: bool = False):
-        return self.model.token_logprobs(batch["input_ids"], batch["position_ids"], batch["cu_seq_lens_q"],
-                                         batch["labels_shifted"], temperature, want_entropy)
+        with nvtx_range("forward"):
+            return self.model.token_logprobs(batch["input_ids"], batch["position_ids"], batch["cu_seq_lens_q"],
+                                             batch["labels_shifted"], temperature, want_entropy)
 
     def backward(self, loss: torch.Tensor) -> None:
-        loss.backward()
+        with nvtx_range("backward"):
+            loss.backward()
         self._accum += 1
 
     def optimizer_step(self, grad_scale: float | None = None) -> torch.Tensor:
@@ -128,7 +131,8 @@ class Learner:
             raise RuntimeError("optimizer_step called without any backward")
         if grad.numel() < self.opt.flat.numel():  # ref path: autograd grad has the padded size already
             raise RuntimeError("gradient buffer smaller than the parameter buffer")
-        norm = self.opt.step(grad, lr=self.lr(), grad_scale=grad_scale)
+        with nvtx_range("optimizer_step"):
+            norm = self.opt.step(grad, lr=self.lr(), grad_scale=grad_scale)
         if self.ops == "fused":
             if self.world > 1 or self.comm != "none":
                 self.model.main_grad.zero_()

@@ -274,3 +274,53 @@ def warn_if_low_disk_space(path: str, threshold: float = 0.9) -> bool:
                                             100 * usage.used / usage.total, usage.total / 2**30, path)
         return True
     return False
+
+
+class nvtx_range(ContextDecorator):
+    """NVTX range around a phase of the step (visible in Nsight timelines); a no-op without CUDA or when
+    ``B200_NVTX=0``."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.on = os.environ.get("B200_NVTX", "1") == "1"
+
+    def __enter__(self):
+        import torch
+
+        self.on = self.on and torch.cuda.is_available()
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            import torch
+
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
+class StepProfiler:
+    """``--profiling``: torch.profiler over a few training steps (skip 5, wait 1, warm up 2, record 3, with memory), the
+    schedule the reference's profiler callback uses (``open_instruct/dpo.py:87-90``).  Call ``step()`` once per
+    optimizer step; the Chrome trace lands in ``<output_dir>/profiler``."""
+
+    def __init__(self, enabled: bool, output_dir: str, rank: int = 0):
+        self.prof = None
+        if enabled:
+            import torch
+            from torch.profiler import ProfilerActivity, profile, schedule, tensorboard_trace_handler
+
+            acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+            self.prof = profile(activities=acts, schedule=schedule(skip_first=5, wait=1, warmup=2, active=3, repeat=1), profile_memory=True,
+                                on_trace_ready=tensorboard_trace_handler(os.path.join(output_dir, "profiler"), worker_name=f"rank{rank}"))
+            self.prof.__enter__()
+
+    def step(self) -> None:
+        if self.prof is not None:
+            self.prof.step()
+
+    def close(self) -> None:
+        if self.prof is not None:
+            self.prof.__exit__(None, None, None)
+            self.prof = None
