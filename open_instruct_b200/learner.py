@@ -52,8 +52,8 @@ class Learner:
         self.device = torch.device(device)
         ops = cfg.ops
         if ops == "auto":
-            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.qk_norm
-                              and not spec.attention_bias and torch.cuda.get_device_capability(self.device)[0] == 10) else "ref"
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128
+                              and torch.cuda.get_device_capability(self.device)[0] == 10) else "ref"
         self.ops = ops
         dtype = cfg.dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
         comm = cfg.comm

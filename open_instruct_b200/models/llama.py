@@ -47,6 +47,7 @@ class _LayerStash:
     rstd2: torch.Tensor
     gate_up: torch.Tensor
     attn_tok: torch.Tensor | None = None  # sequence parallel: attention output for MY tokens, all heads
+    qk: tuple | None = None                # per-head q/k RMSNorm: (q_pre, rstd_q, k_pre, rstd_k)
 
 
 class LlamaModel:
@@ -69,8 +70,6 @@ class LlamaModel:
                 raise ValueError("the fused path runs bf16 on CUDA")
             if spec.head_dim != 128:
                 raise NotImplementedError("fused attention is built for head_dim 128")
-            if spec.qk_norm or spec.attention_bias:
-                raise NotImplementedError("qk_norm / attention_bias run on ops='ref' only")
             from ..ops import lib
 
             if not lib.available():
@@ -84,6 +83,7 @@ class LlamaModel:
                 raise ValueError("flat buffer is smaller than the layout")
             self.flat = flat
         self.p = self.layout.views(self.flat)
+        self._last_qk = None
         self.sp = None  # parallel.ulysses.UlyssesContext when the sequence is split over ranks (fused path)
         self.main_grad: torch.Tensor | None = None  # fp32 flat gradient (fused path)
         self.g: dict[str, torch.Tensor] = {}
@@ -256,7 +256,7 @@ class LlamaModel:
                 if self.gradient_checkpointing:
                     stash.append(_LayerStash(h_in, None, None, None, None, None, None, None))
                 else:
-                    stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok))
+                    stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk))
         nf, h_last, rstd_f = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
         state = None
         if keep:
@@ -272,13 +272,48 @@ class LlamaModel:
         scale = s.head_dim ** -0.5
         if sp is None:
             qkv = f.gemm(n1, p[f"l{i}.wqkv"])
+            self._last_qk = self.qkv_bias_and_norm_(qkv, i)
             f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
             attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
             return qkv, attn, lse, None
+        if s.qk_norm or s.attention_bias:
+            raise NotImplementedError("sequence parallelism with qk_norm / attention_bias is not built")
         qkv = sp.qkv_project(i, n1, p[f"l{i}.wqkv"], pos.numel())
         f.rope_(qkv, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim)
         attn, lse = f.attn_fwd(qkv, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
         return qkv, attn, lse, sp.attn_exchange(i, attn)
+
+    def qkv_bias_and_norm_(self, qkv: torch.Tensor, i: int):
+        """Qwen2-style q/k/v bias and Qwen3 / OLMo-2 style per-head RMSNorm of q and k, in place on the fused projection
+        output (before RoPE).  Returns what the backward needs (``None`` when the model has neither)."""
+        f = _fused()
+        s, p = self.spec, self.p
+        if s.attention_bias:
+            qkv.add_(p[f"l{i}.bqkv"])
+        if not s.qk_norm:
+            return None
+        T = qkv.shape[0]
+        out = []
+        for lo, heads, name in ((0, s.num_heads, "q_norm"), (s.q_dim, s.num_kv_heads, "k_norm")):
+            pre = qkv[:, lo:lo + heads * s.head_dim].contiguous().view(T * heads, s.head_dim)
+            y, _, rstd = f.rmsnorm_fwd(pre, p[f"l{i}.{name}"], s.rms_norm_eps)
+            qkv[:, lo:lo + heads * s.head_dim].copy_(y.view(T, heads * s.head_dim))
+            out += [pre, rstd]
+        return tuple(out)
+
+    def _qkv_bias_and_norm_bwd_(self, dqkv: torch.Tensor, i: int, qk) -> None:
+        """Backward of ``qkv_bias_and_norm_`` in place on ``dqkv`` (after the RoPE backward); accumulates the norm and
+        bias gradients."""
+        f = _fused()
+        s, g, p = self.spec, self.g, self.p
+        T = dqkv.shape[0]
+        if qk is not None:
+            for (lo, heads, name), pre, rstd in (((0, s.num_heads, "q_norm"), qk[0], qk[1]), ((s.q_dim, s.num_kv_heads, "k_norm"), qk[2], qk[3])):
+                dy = dqkv[:, lo:lo + heads * s.head_dim].contiguous().view(T * heads, s.head_dim)
+                dx = f.rmsnorm_bwd(pre, p[f"l{i}.{name}"], rstd, dy, None, g[f"l{i}.{name}"])
+                dqkv[:, lo:lo + heads * s.head_dim].copy_(dx.view(T, heads * s.head_dim))
+        if s.attention_bias:
+            g[f"l{i}.bqkv"].add_(dqkv.float().sum(0))
 
     def _recompute_layer(self, i: int, st: _LayerStash, pos, cu) -> _LayerStash:
         """Gradient checkpointing: rebuild a layer's activations from its input stream."""
@@ -289,7 +324,7 @@ class LlamaModel:
         o = f.gemm(attn_tok if attn_tok is not None else attn, p[f"l{i}.wo"])
         n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=st.h_in)
         gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
-        return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok)
+        return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk)
 
     def _fused_backward_hidden(self, state: dict, d_nf: torch.Tensor) -> None:
         """Backward from d(final-norm hidden) to the embedding; accumulates into ``main_grad``."""
@@ -330,6 +365,7 @@ class LlamaModel:
                 dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
                 del d_attn
                 f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True)
+                self._qkv_bias_and_norm_bwd_(dqkv, i, st.qk)
             else:
                 d_attn = sp.d_attn_project(d_mid, p[f"l{i}.wo"], pos.numel())
                 dqkv_heads = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)

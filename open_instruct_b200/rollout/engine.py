@@ -319,7 +319,9 @@ class RolloutEngine:
                 return tp.reduce_norm(partial, w, s.rms_norm_eps, res=res)
 
             row_out = (lambda: tp.out_buffer(T)) if tp is not None else (lambda: None)
-            push = tp is not None and tp.world == 2 and T > 256  # large batches: peer push fused into the GEMM epilogue
+            # peer push fused into the GEMM epilogue: built and tested, but measured 2.4x slower than "plain GEMM + pulling
+            # reduction" at T = 4096 (row-per-thread epilogue stores reach the peer as 16-byte writes), so it is opt-in
+            push = tp is not None and tp.world == 2 and T > 256 and os.environ.get("B200_TP_PUSH", "0") == "1"
 
             def row_proj(x, w):
                 return tp.row_gemm(x, w) if push else f.gemm(x, w, row_out(), impl=impl_narrow)
@@ -327,6 +329,7 @@ class RolloutEngine:
             for i in range(s.num_layers):
                 n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
                 qkv = f.gemm(n1, p[f"l{i}.wqkv"], impl=impl)
+                self.model.qkv_bias_and_norm_(qkv, i)
                 f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
                 call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
                      s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())

@@ -65,7 +65,8 @@ def main():
         hb = (both[0].float() + both[1].float() + res.float()).bfloat16()
         assert (h.float() - hb.float()).abs().max() < 0.06, (T, (h.float() - hb.float()).abs().max())
 
-    # (2) engine: TP=2 against the unsharded engine
+    # (2) engine: TP=2 against the unsharded engine (prefill through the fused peer push as well as the default pull)
+    os.environ["B200_TP_PUSH"] = "1"
     full = LlamaModel(spec, device=device, dtype=torch.bfloat16, ops="fused", seed=11).flat.detach()
     ref_eng = RolloutEngine(spec, device=device, num_blocks=64, flat=full.clone(), eos_token_ids=[], seed=5)
     ls = local_spec(spec, 2)

@@ -19,13 +19,23 @@ def _batch(lens, vocab, device):
     return ids, pos, cu, labels
 
 
+@pytest.mark.parametrize("variant", ["llama", "qwen2_bias", "qwen3_qknorm"])
 @pytest.mark.parametrize("ckpt", [False, True])
-def test_fused_matches_ref(ckpt):
+def test_fused_matches_ref(ckpt, variant):
     from open_instruct_b200.models import LlamaModel, get_spec
     from open_instruct_b200.ops import lib
 
     spec = get_spec("tiny128")
+    if variant == "qwen2_bias":
+        spec = spec.replace(attention_bias=True, model_type="qwen2")
+    elif variant == "qwen3_qknorm":
+        spec = spec.replace(qk_norm=True, model_type="qwen3")
     fused = LlamaModel(spec, device="cuda", dtype=torch.bfloat16, ops="fused", seed=3, gradient_checkpointing=ckpt)
+    if variant != "llama":  # biases start at zero and norm weights at one: move them so that their gradients are exercised
+        with torch.no_grad():
+            for name, v in fused.p.items():
+                if name.endswith(("bqkv", "q_norm", "k_norm")):
+                    v.add_(torch.randn_like(v.float()).mul_(0.1).to(v.dtype))
     refm = LlamaModel(spec, device="cuda", dtype=torch.float32, ops="ref", flat=fused.flat.float().clone())
     ids, pos, cu, labels = _batch([200, 57, 300], spec.vocab_size, "cuda")
     lp_f, ent_f = fused.token_logprobs(ids, pos, cu, labels, want_entropy=True)
