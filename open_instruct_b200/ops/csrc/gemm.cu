@@ -351,14 +351,18 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int 
 // Narrow-tile variant for small M (decode): C[M,N] = A[M,K] * B[N,K]^T, bf16 out, 128 x 64 tiles and an 8-stage ring.
 // With few rows the GEMM is a stream over the weights; 64-wide column tiles give 4x as many CTAs as the 256-wide
 // kernel, so all SMs pull on HBM (M = 256, N = 4096: 128 CTAs instead of 32).
+// `bn`: 64 (8-stage ring) or 128 (6-stage ring; half of every stage is weights instead of a third).
 extern "C" int b200_gemm_bf16_skinny(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                                     long long ldb, long long ldc, int* status, void* stream) {
+                                     long long ldb, long long ldc, int* status, void* stream, int bn) {
   using namespace b200;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (bn != 64 && bn != 128) return -4;
   CUtensorMap ta, tb;
   int r = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2, true);
   if (r) return 10000 + r;
-  r = make_tmap_2d(&tb, B, N, K, ldb, 64, BK, 2, true);
+  r = make_tmap_2d(&tb, B, N, K, ldb, bn, BK, 2, true);
   if (r) return 20000 + r;
-  return launch<false, false, OUT_BF16, 64, 8>(ta, tb, C, M, N, K, ldc, status, reinterpret_cast<cudaStream_t>(stream), 0);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<false, false, OUT_BF16, 64, 8>(ta, tb, C, M, N, K, ldc, status, st, 0);
+  return launch<false, false, OUT_BF16, 128, 6>(ta, tb, C, M, N, K, ldc, status, st, 0);
 }

@@ -65,11 +65,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a
     if ldc % 8 and N >= 8:
         raise ValueError("gemm output row stride must be a multiple of 8 elements")
     impl = impl or GEMM_IMPL
-    if impl == "skinny":
+    if impl in ("skinny", "skinny128"):
         # 128 x 64 tiles: for small M, where the GEMM is a stream over the weights and needs many CTAs pulling on HBM
         if a_mn or b_mn or out_mode != OUT_BF16:
             raise ValueError("the skinny GEMM covers the forward layout with bf16 output only")
-        call("b200_gemm_bf16_skinny", ptr(a), ptr(b), ptr(out), M, N, K, lda, ldb, ldc, ptr(status_word(a.device)), stream_ptr())
+        call("b200_gemm_bf16_skinny", ptr(a), ptr(b), ptr(out), M, N, K, lda, ldb, ldc, ptr(status_word(a.device)), stream_ptr(),
+             64 if impl == "skinny" else 128)
         return out
     call("b200_gemm2_bf16" if impl == "2cta" else "b200_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, lda, ldb, ldc,
          int(a_mn), int(b_mn), out_mode,

@@ -106,7 +106,7 @@ def main():
             for name, (N, K) in {"qkv": ((Hq + 2 * Hkv) * Dh, D), "o": (D, Hq * Dh), "gate_up": (2 * F, D), "down": (D, F)}.items():
                 x, w = bf(M, K), bf(N, K)
                 by = (N * K + M * K + M * N) * 2
-                for impl in ("1cta", "2cta", "skinny"):
+                for impl in ("1cta", "2cta", "skinny", "skinny128"):
                     rec(f"decode_gemm_{name}_M{M}_{impl}", time_op(lambda: fused.gemm(x, w, impl=impl), args.iters), bytes_=by)
     if not only or "attn" in only:
         L = args.doc_len or T

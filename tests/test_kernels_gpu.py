@@ -43,14 +43,15 @@ def test_gemm_layouts(a_mn, b_mn, shape, impl):
 
 
 @pytest.mark.parametrize("shape", [(1, 512, 128), (37, 200, 72), (256, 4096, 4096), (300, 6144, 1024), (512, 4096, 14336)])
-def test_gemm_skinny(shape):
+@pytest.mark.parametrize("impl", ["skinny", "skinny128"])
+def test_gemm_skinny(shape, impl):
     from open_instruct_b200.ops import fused
 
     M, N, K = shape
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
     b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
-    out = fused.gemm(a, b, impl="skinny")
+    out = fused.gemm(a, b, impl=impl)
     assert _rel(out, a.float() @ b.float().t()) < 5e-3
 
 
