@@ -240,6 +240,14 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                       report_to=args.report_to if args.with_tracking else ("jsonl",), wandb_project=args.wandb_project_name,
                       wandb_entity=args.wandb_entity, enabled=is_main)
 
+    lora = None
+    if args.use_lora:
+        from .models.lora import LoRATrainer
+
+        lora = LoRATrainer(learner, rank=args.lora_rank, alpha=args.lora_alpha, dropout=args.lora_dropout, lr=args.learning_rate,
+                           weight_decay=args.weight_decay)
+        logger.info("LoRA: %d trainable parameters (rank %d) on a frozen base", lora.adapters.num_parameters(), args.lora_rank)
+
     # ------------------------------------------------------------------ resume
     completed, start_epoch = 0, 0
     ckpt = get_last_checkpoint_path(args.output_dir, args.resume_from_checkpoint)
@@ -277,7 +285,7 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
             if not mbs:
                 break
             mbs = [to_device(mb, device) for mb in mbs]
-            out = learner.sft_step(mbs, args.reduce_loss)
+            out = lora.step(mbs, learner.lr(completed)) if lora is not None else learner.sft_step(mbs, args.reduce_loss)
             profiler.step()
             completed += 1
             loss_acc += out["loss"].detach()
@@ -312,7 +320,9 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
     # ------------------------------------------------------------------ final export
     pdist.barrier()
     if is_main:
-        save_hf_checkpoint(learner.model.flat, spec, args.output_dir, tokenizer=tokenizer)
+        save_hf_checkpoint(learner.model.flat, spec, args.output_dir, tokenizer=tokenizer)  # with LoRA: the merged model
+        if lora is not None:
+            lora.save(os.path.join(args.output_dir, "adapter"), args.model_name_or_path or "")
         if args.clean_checkpoints_at_end:
             clean_last_n_checkpoints(args.output_dir, 0)
     tracker.close()

@@ -200,3 +200,54 @@ def main(argv=None) -> None:
 
 if __name__ == "__main__":
     main()
+
+
+class LoRATrainer:
+    """Adapter training around a ``Learner``: the base weights stay frozen, AdamW runs on the adapters only.
+
+    Both paths produce ``dL/dW_eff`` for the whole model first (autograd on the ref path, the fused engine's ``main_grad``
+    on the GPU path) and contract it into adapter gradients (``pull_grads``); adapter gradients are summed over ranks, the
+    adapters are updated identically everywhere, and the merged weights are written back into the working buffer."""
+
+    def __init__(self, learner, rank: int = 64, alpha: float = 16.0, dropout: float = 0.0, lr: float = 1e-4, weight_decay: float = 0.0):
+        self.learner = learner
+        m = learner.model
+        self.adapters = LoRAAdapters(m.spec, m.layout, rank, alpha, dropout, device=m.device, dtype=torch.float32, seed=learner.cfg.seed)
+        self.base = m.flat.detach().clone()
+        self.opt = torch.optim.AdamW([self.adapters.flat], lr=lr, weight_decay=weight_decay)
+
+    def step(self, micro_batches: list[dict], lr: float | None = None) -> dict:
+        """One optimizer step on the adapters over packed SFT micro-batches (token-mean loss)."""
+        from ..data.collate import IGNORE
+        from ..parallel import dist as pdist
+
+        L, m = self.learner, self.learner.model
+        m.zero_grad()
+        losses, ntok = [], 0
+        for mb in micro_batches:
+            logp, _ = L.token_logprobs(mb)
+            n = (mb["labels_shifted"] != IGNORE).sum().clamp(min=1)
+            loss = -logp.sum() / n
+            loss.backward()
+            losses.append(loss.detach())
+            ntok += int(n)
+        if m.ops == "ref":
+            m.main_grad = m.flat.grad.float()
+        self.adapters.grad = None
+        g = self.adapters.pull_grads(m).div_(len(micro_batches) * L.world)
+        pdist.all_reduce_(g, group=L.group)
+        self.adapters.flat.grad = g.to(self.adapters.flat.dtype)
+        if lr is not None:
+            for grp in self.opt.param_groups:
+                grp["lr"] = lr
+        self.opt.step()
+        self.opt.zero_grad(set_to_none=True)
+        if m.ops == "ref":
+            m.main_grad = None
+        m.zero_grad()
+        with torch.no_grad():
+            self.adapters.merge_into(m, self.base)
+        return {"loss": torch.stack(losses).mean(), "grad_norm": g.norm(), "target_tokens": ntok}
+
+    def save(self, out_dir: str, base_model_name_or_path: str = "") -> None:
+        self.adapters.save(out_dir, base_model_name_or_path)

@@ -73,3 +73,23 @@ def test_resume_is_bitwise_identical(tmp_path):
     resumed = load_file(os.path.join(b.output_dir, "model.safetensors"))
     for k in full:
         assert torch.equal(full[k], resumed[k]), k
+
+
+def test_lora_finetune_trains_adapters_only(tmp_path):
+    from safetensors.torch import load_file
+
+    from open_instruct_b200.finetune import main
+    from open_instruct_b200.models import LlamaModel, get_spec
+
+    args, tc = _args(str(tmp_path), use_lora=True, lora_rank=4, lora_alpha=8.0, lora_dropout=0.0, learning_rate=5e-3, num_train_epochs=3)
+    out = main(args, tc)
+    lines = [json.loads(l) for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
+    assert lines[-1]["train_loss"] < lines[0]["train_loss"] and out["completed_steps"] == 15
+    ad = load_file(os.path.join(args.output_dir, "adapter", "adapter_model.safetensors"))
+    assert any(k.endswith("lora_B.weight") and v.abs().sum() > 0 for k, v in ad.items())
+    # embeddings have no adapter: the exported (merged) model keeps the base embedding exactly
+    merged = load_file(os.path.join(args.output_dir, "model.safetensors"))
+    spec = get_spec("tiny").replace(vocab_size=merged["model.embed_tokens.weight"].shape[0])
+    base = LlamaModel(spec, seed=0)
+    assert torch.allclose(merged["model.embed_tokens.weight"].float(), base.p["embed"].detach().to(torch.bfloat16).float(), atol=1e-6)
+    assert not torch.allclose(merged["model.layers.0.self_attn.q_proj.weight"].float(), base.p["l0.wqkv"][: spec.q_dim].detach().to(torch.bfloat16).float())
