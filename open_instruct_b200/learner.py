@@ -145,6 +145,38 @@ class Learner:
         self.global_step += 1
         return norm
 
+    # ------------------------------------------------------------------ residency (colocated learner + engine)
+    def offload_to_cpu(self) -> int:
+        """Move what only the optimizer step needs (fp32 master weights, moments, gradient shard, gradient accumulator) to
+        pinned host memory, e.g. while a colocated rollout engine generates (cf. ``RayProcess.offload_to_cpu``,
+        ``open_instruct/utils.py:1600-1648``).  Returns the bytes freed on the GPU.  A no-op for buffers that are in
+        symmetric memory (they must stay mapped) or already on the host."""
+        moved = 0
+        self._parked = {}
+        for name in ("master", "m", "v", "grad_shard"):
+            t = getattr(self.opt, name, None)
+            if t is not None and t.is_cuda:
+                host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                host.copy_(t)
+                self._parked[name] = host
+                setattr(self.opt, name, host)  # keeps the attribute valid (state_dict works while parked)
+                moved += t.numel() * t.element_size()
+        if self.symm is None and self.model.main_grad is not None and self.model.main_grad.is_cuda and self._accum == 0:
+            moved += self.model.main_grad.numel() * 4
+            self.model.main_grad = None
+            self.model.g = {}
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            torch.cuda.empty_cache()
+        return moved
+
+    def backload_to_gpu(self) -> None:
+        for name, host in getattr(self, "_parked", {}).items():
+            setattr(self.opt, name, host.to(self.device, non_blocking=True))
+        self._parked = {}
+        if self.ops == "fused" and self.symm is None:
+            self.model.ensure_main_grad()
+
     # ------------------------------------------------------------------ SFT
     def sft_micro_step(self, batch: dict, reduce_loss: str = "mean") -> tuple[torch.Tensor, torch.Tensor]:
         """Forward + backward of one packed micro-batch.  Returns (loss, number of target tokens).

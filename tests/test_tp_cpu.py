@@ -55,3 +55,33 @@ def test_offloaded_optimizer_matches_resident():
         nb = b.step(g.clone(), grad_scale=0.5)
         assert torch.allclose(na, nb)
     assert torch.equal(flat_a, flat_b) and torch.equal(a.m, b.m) and torch.equal(a.v, b.v)
+
+
+def test_context_window_checker():
+    from open_instruct_b200.context_window_checker import (check_context_window_limit, truncate_messages_to_fit_context,
+                                                            truncate_str_for_prompt_template, will_exceed_context_window)
+
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "x" * 3000}, {"role": "user", "content": "tail"}]
+    assert will_exceed_context_window(msgs, 100, "no-such-model", max_context_length=600)
+    cut = truncate_messages_to_fit_context(msgs, 100, "no-such-model", max_context_length=600)
+    assert cut[0]["role"] == "system" and len(cut) == 2 and len(cut[1]["content"]) < 3000
+    assert check_context_window_limit(cut, 100, "no-such-model", max_context_length=600)
+    s = truncate_str_for_prompt_template("y" * 5000, "Grade this: {output}\nScore:", 50, "no-such-model", max_context_length=400)
+    assert 0 < len(s) < 5000
+
+
+def test_learner_offload_roundtrip():
+    from open_instruct_b200.data.synthetic import sft_step_batches
+    from open_instruct_b200.learner import Learner, LearnerConfig
+    from open_instruct_b200.models.spec import get_spec
+
+    spec = get_spec("tiny")
+    a = Learner(spec, LearnerConfig(ops="ref", comm="none", learning_rate=1e-3, total_steps=10, seed=2), device="cpu")
+    b = Learner(spec, LearnerConfig(ops="ref", comm="none", learning_rate=1e-3, total_steps=10, seed=2), device="cpu")
+    for s in range(3):
+        mbs = sft_step_batches(2, 64, spec.vocab_size, seed=s)
+        a.sft_step(mbs)
+        b.offload_to_cpu()   # on CPU nothing moves, but the calls must be harmless between steps
+        b.backload_to_gpu()
+        b.sft_step(mbs)
+    assert torch.equal(a.model.flat.detach(), b.model.flat.detach())
