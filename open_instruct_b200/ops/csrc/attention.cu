@@ -522,22 +522,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         const int tq = q0 + r;
         const bool v = tq < doc_end;
         float* dst = dq_acc + static_cast<long long>(tq) * (Hq * DH) + h * DH;
-#pragma unroll 1
-        for (int cc = half * 2; cc < half * 2 + 2; ++cc) {
-          uint32_t t[32];
-          tmem_ld32(T_ST + lane_off + cc * 32, t);
-          tmem_ld_wait();
-          if (v) {
+        // read this thread's 64 dQ values into registers, hand the TMEM columns back to the MMA warp at once (the next
+        // iteration's S^T can start), then issue the reductions
+        uint32_t t2[2][32];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) tmem_ld32(T_ST + lane_off + (half * 2 + u) * 32, t2[u]);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.dq_done);
+        if (v) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              red_add_v4(dst + cc * 32 + i * 4, __uint_as_float(t[4 * i]), __uint_as_float(t[4 * i + 1]),
-                         __uint_as_float(t[4 * i + 2]), __uint_as_float(t[4 * i + 3]));
+              red_add_v4(dst + (half * 2 + u) * 32 + i * 4, __uint_as_float(t2[u][4 * i]), __uint_as_float(t2[u][4 * i + 1]),
+                         __uint_as_float(t2[u][4 * i + 2]), __uint_as_float(t2[u][4 * i + 3]));
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.dq_done);
     }
     if (ok) {
       // the last dq_full wait covers every MMA issued before it, including all dK/dV updates

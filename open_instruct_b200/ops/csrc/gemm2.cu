@@ -29,7 +29,8 @@ constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_BYTES = BNH * BK * 2;  // 16 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
-constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int STAGING_BYTES = 4 * 32 * 256;  // scatter epilogue: per epilogue warp 32 rows x 128 bf16 columns
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256 + STAGING_BYTES;
 
 enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
 
@@ -110,6 +111,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   uint64_t* tempty = bars + 2 * STAGES + 2;    // [2]       used in the leader only (8 arrivals)
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();  // 0 = leader
@@ -246,6 +248,51 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const int row = m_blk * 2 * BM + cta * BM + lane_grp * 32 + lane;
       const int n0 = n_blk * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * BN;
+      if (OUT == OUT_BF16 && scatter != nullptr) {
+        // Scatter epilogue (destinations may be peer GPUs).  One TMEM lane per thread means a thread holds one ROW; stored
+        // directly, every 16-byte store of a warp would land in a different row - fine for local L2, wasteful over NVLink.
+        // So each warp transposes through shared memory: 32 rows x 128 columns are staged (16-byte chunks XOR-swizzled by
+        // row against bank conflicts) and written back two rows per instruction, 256 contiguous bytes per row.
+        uint8_t* stg = staging + lane_grp * (32 * 256);
+        const int row0 = m_blk * 2 * BM + cta * BM + lane_grp * 32;
+#pragma unroll 1
+        for (int hb = 0; hb < BN / 128; ++hb) {
+          const int col0 = n0 + hb * 128;
+          if (col0 >= N) break;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld32(taddr + hb * 128 + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              const int chunk = c * 4 + j;  // 16-byte chunk of this thread's 256-byte row
+              *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = v;
+            }
+          }
+          __syncwarp();
+          __nv_bfloat16* d1 = reinterpret_cast<__nv_bfloat16*>(scatter[col0 >> 7]);
+          __nv_bfloat16* d2 = scatter2 ? reinterpret_cast<__nv_bfloat16*>(scatter2[col0 >> 7]) : nullptr;
+          const int sub = lane >> 4, chunk = lane & 15;
+#pragma unroll 4
+          for (int i = 0; i < 32; i += 2) {
+            const int rr = i + sub;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((chunk ^ (rr & 15)) << 4));
+            const int grow = row0 + rr;
+            if (grow < M) {
+              const long long off = static_cast<long long>(grow + row_off) * ldc + chunk * 8;
+              *reinterpret_cast<uint4*>(d1 + off) = v;
+              if (d2) *reinterpret_cast<uint4*>(d2 + off) = v;
+            }
+          }
+          __syncwarp();
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col = n0 + c * 32;
