@@ -92,3 +92,91 @@ class RubricBuffer:
 
     def dumps(self) -> str:
         return json.dumps(self.state_dict())
+
+
+_EVOLVE_PROMPT = ("You maintain grading rubrics for the question below. Here are several sampled answers. Propose rubric items that "
+                  "separate good answers from bad ones and are NOT already covered by the existing rubrics: 'positive' items describe "
+                  "what strong answers do, 'negative' items describe failure patterns.\n\n[Question]\n{query}\n\n[Existing rubrics]\n{existing}\n\n"
+                  "[Answers]\n{answers}\n\nRespond in JSON: {{\"positive_rubrics\": [{{\"description\": \"...\", \"title\": \"...\"}}], "
+                  "\"negative_rubrics\": [{{\"description\": \"...\", \"title\": \"...\"}}]}}")
+
+
+def extract_json_from_response(text: str) -> dict | None:
+    """First JSON object in a model reply (code fences tolerated)."""
+    import re
+
+    m = re.search(r"\{.*\}", text.replace("```json", "").replace("```", ""), re.S)
+    if not m:
+        return None
+    try:
+        out = json.loads(m.group(0))
+        return out if isinstance(out, dict) else None
+    except json.JSONDecodeError:
+        return None
+
+
+class RubricManager:
+    """One evolving-rubric step per training step (the role of ``open_instruct/rubrics/evolving_rubric_step.py:26-160``):
+    for every prompt group, show the judge a few sampled answers and the current rubrics, parse its proposals, add them to
+    the buffer as adaptive items (positive weight +1, negative weight -1), cap the active adaptive items, and return
+    (metrics, ground-truth overrides keyed by dataset index).  ``ask`` is an async callable ``messages -> str``."""
+
+    def __init__(self, ask, max_active_rubrics: int = 5, answers_shown: int = 4, answer_length_limit_in_words: int | None = 400,
+                 cache_dir: str | None = None):
+        self.ask, self.answers_shown, self.word_limit, self.cache_dir = ask, answers_shown, answer_length_limit_in_words, cache_dir
+        self.buffer = RubricBuffer(max_active_adaptive=max_active_rubrics)
+
+    def initialize(self, prompt_id: str, ground_truth: dict) -> None:
+        if prompt_id not in self.buffer.items:
+            self.buffer.add_persistent(prompt_id, [r["description"] for r in ground_truth.get("rubrics", []) if r.get("weight", 1.0) >= 0])
+            neg = [r for r in ground_truth.get("rubrics", []) if r.get("weight", 1.0) < 0]
+            self.buffer.items[prompt_id].extend(RubricItem(r["description"], float(r["weight"]), False) for r in neg)
+
+    async def _propose(self, query: str, prompt_id: str, answers: list[str]) -> list[dict] | None:
+        shown = answers[: self.answers_shown]
+        if self.word_limit:
+            shown = [" ".join(a.split()[: self.word_limit]) for a in shown]
+        existing = "\n".join(f"- {i.description}" for i in self.buffer.items.get(prompt_id, [])) or "(none)"
+        body = _EVOLVE_PROMPT.format(query=query, existing=existing, answers="\n\n".join(f"[Answer {k + 1}]\n{a}" for k, a in enumerate(shown)))
+        try:
+            parsed = extract_json_from_response(await self.ask([{"role": "user", "content": body}]))
+        except Exception:  # noqa: BLE001 - transport error counts as an invalid proposal
+            parsed = None
+        if parsed is None:
+            return None
+        out = [{"description": r["description"], "weight": 1.0} for r in parsed.get("positive_rubrics", []) if r.get("description")]
+        out += [{"description": r["description"], "weight": -1.0} for r in parsed.get("negative_rubrics", []) if r.get("description")]
+        return out
+
+    def step(self, decoded_responses: list[str], ground_truths: list[dict], indices: list[int], num_samples: int, training_step: int = 0):
+        groups = [(indices[g] if indices else g // num_samples, ground_truths[g], decoded_responses[g:g + num_samples])
+                  for g in range(0, len(decoded_responses), num_samples)]
+        for idx, gt, _ in groups:
+            self.initialize(str(idx), gt)
+
+        async def run():
+            return await asyncio.gather(*(self._propose(gt.get("query", ""), str(idx), answers) for idx, gt, answers in groups))
+
+        proposals = asyncio.run(run())
+        overrides, n_new, valid = {}, 0, 0
+        for (idx, gt, _), prop in zip(groups, proposals):
+            if prop is not None:
+                valid += 1
+                before = len(self.buffer.items[str(idx)])
+                self.buffer.add_adaptive(str(idx), prop)
+                n_new += max(0, len(self.buffer.items[str(idx)]) - before)
+            overrides[idx] = {**gt, **self.buffer.spec_for(str(idx), gt.get("query", ""))}
+        n = max(1, len(groups))
+        active = [sum(1 for i in self.buffer.items[str(idx)] if i.adaptive) for idx, _, _ in groups]
+        metrics = {"evolving_rubrics/valid_rate": valid / n, "evolving_rubrics/avg_new_rubrics": n_new / n,
+                   "evolving_rubrics/avg_active_buffer": sum(active) / n, "evolving_rubrics/num_overrides": len(overrides),
+                   "evolving_rubrics/skipped": len(groups) - valid}
+        if self.cache_dir:
+            import os
+
+            os.makedirs(self.cache_dir, exist_ok=True)
+            tmp = os.path.join(self.cache_dir, f".step_{training_step}.json.tmp")
+            with open(tmp, "w") as f:
+                json.dump({"step": training_step, "buffer": self.buffer.state_dict(), "proposals": proposals}, f)
+            os.replace(tmp, os.path.join(self.cache_dir, f"step_{training_step}.json"))
+        return metrics, overrides

@@ -85,3 +85,30 @@ def test_learner_offload_roundtrip():
         b.backload_to_gpu()
         b.sft_step(mbs)
     assert torch.equal(a.model.flat.detach(), b.model.flat.detach())
+
+
+def test_evolving_rubric_step(tmp_path):
+    import json
+
+    from open_instruct_b200.rubrics import RubricManager
+
+    calls = []
+
+    async def ask(messages):
+        calls.append(messages[0]["content"])
+        if "q-bad" in messages[0]["content"]:
+            return "sorry, no json here"
+        return "```json\n" + json.dumps({"positive_rubrics": [{"description": "cites a source", "title": "t"}],
+                                         "negative_rubrics": [{"description": "rambles", "title": "t"}]}) + "\n```"
+
+    mgr = RubricManager(ask, max_active_rubrics=2, cache_dir=str(tmp_path))
+    gts = [{"query": "q-good", "rubrics": [{"description": "is correct", "weight": 1.0}]}] * 2 + [{"query": "q-bad", "rubrics": []}] * 2
+    metrics, over = mgr.step(["a1", "a2", "b1", "b2"], gts, indices=[7, 7, 9, 9], num_samples=2, training_step=3)
+    assert metrics["evolving_rubrics/valid_rate"] == 0.5 and metrics["evolving_rubrics/avg_new_rubrics"] == 1.0
+    descs = [r["description"] for r in over[7]["rubrics"]]
+    assert descs == ["is correct", "cites a source", "rambles"] and [r["weight"] for r in over[7]["rubrics"]] == [1.0, 1.0, -1.0]
+    assert over[9]["rubrics"] == [] and (tmp_path / "step_3.json").exists()
+    # a second step proposes the same items again: nothing new, cap holds
+    metrics, over = mgr.step(["a1", "a2", "b1", "b2"], gts, indices=[7, 7, 9, 9], num_samples=2, training_step=4)
+    assert metrics["evolving_rubrics/avg_new_rubrics"] == 0.0 and len(over[7]["rubrics"]) == 3
+    assert "is correct" in calls[-2] or "is correct" in calls[-1]  # existing rubrics are shown to the judge
