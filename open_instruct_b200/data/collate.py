@@ -82,12 +82,23 @@ class TensorDataCollatorWithFlattening:
     max_seq_length: int | None = None
     pad_token_id: int = 0
     return_batch_dim: bool = False
+    native: bool = False  # pack with the C++ host runtime (``data/native_pack.py``) when no padding is requested
 
     def __call__(self, features: list[dict]) -> dict:
         has_labels = "labels" in features[0]
-        batch = flatten_examples([f["input_ids"] for f in features],
-                                 [f["labels"] for f in features] if has_labels else None,
-                                 pad_to=self.max_seq_length, pad_token_id=self.pad_token_id)
+        batch = None
+        if self.native and self.max_seq_length is None and all(len(f["input_ids"]) > 0 for f in features):
+            from . import native_pack
+
+            if native_pack.available():
+                batch = native_pack.pack_examples([f["input_ids"] for f in features], [f["labels"] for f in features] if has_labels else None,
+                                                  budget=1 << 30)[0]
+                lens = (batch["cu_seq_lens_q"][1:] - batch["cu_seq_lens_q"][:-1]).long()
+                batch["seq_idx"] = torch.repeat_interleave(torch.arange(lens.numel(), dtype=torch.int32), lens)
+        if batch is None:
+            batch = flatten_examples([f["input_ids"] for f in features],
+                                     [f["labels"] for f in features] if has_labels else None,
+                                     pad_to=self.max_seq_length, pad_token_id=self.pad_token_id)
         if "index" in features[0]:
             batch["index"] = torch.tensor([int(f["index"]) for f in features], dtype=torch.long)
         if not self.return_position_ids:

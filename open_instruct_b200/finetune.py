@@ -211,7 +211,7 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
     spec = spec.replace(pad_token_id=tokenizer.pad_token_id, eos_token_id=tokenizer.eos_token_id, bos_token_id=tokenizer.bos_token_id)
     per_rank = args.per_device_train_batch_size
     collator = TensorDataCollatorWithFlattening(max_seq_length=args.max_seq_length if args.packing else None,
-                                                pad_token_id=tokenizer.pad_token_id or 0)
+                                                pad_token_id=tokenizer.pad_token_id or 0, native=True)
     if args.packing:
         collator.max_seq_length = args.max_seq_length  # loader packs to this token budget; collator pads the row up to it
     sp = args.sequence_parallel_size

@@ -209,3 +209,36 @@ def test_attention_varlen(lens):
 
 def test_attention_gqa_llama_heads():
     _attn_case([700, 324], 32, 8)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 128), (300, 1024, 192), (4096, 6144, 512)])
+def test_gemm_scatter_epilogue_local(shape):
+    """Column-scatter epilogue (shared-memory transpose, two destination tables) with every destination on this GPU:
+    128-column block j goes to buffer j % 2 at column block j // 2, rows shifted by 5; a second table mirrors it."""
+    import ctypes
+
+    from open_instruct_b200.ops import fused, lib
+    from open_instruct_b200.ops.lib import ptr, status_word, stream_ptr
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    ref = fused.gemm(a, b)
+    nb, off = N // 128, 5
+    half = (nb + 1) // 2 * 128
+    bufs = [torch.zeros(M + off, half, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    mk = lambda pair: torch.tensor([pair[j % 2].data_ptr() + 2 * (j // 2) * 128 for j in range(nb)], dtype=torch.int64, device="cuda")
+    t1, t2 = mk(bufs[:2]), mk(bufs[2:])
+    P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    lib._SIGNATURES["b200_gemm2_bf16_scatter"] = [P, P, I, I, I, L, L, I, I, P, I, L, P, P, P]
+    fn = lib.load_ops().b200_gemm2_bf16_scatter
+    fn.argtypes, fn.restype = lib._SIGNATURES["b200_gemm2_bf16_scatter"], ctypes.c_int
+    lib.call("b200_gemm2_bf16_scatter", ptr(a), ptr(b), M, N, K, a.stride(0), b.stride(0), 0, 0, ptr(t1), off, half, ptr(status_word(a.device)),
+             stream_ptr(), ptr(t2))
+    torch.cuda.synchronize()
+    for pair in (bufs[:2], bufs[2:]):
+        for j in range(nb):
+            got = pair[j % 2][off:, (j // 2) * 128:(j // 2 + 1) * 128]
+            assert torch.equal(got, ref[:, j * 128:(j + 1) * 128]), (shape, j)
+        assert all(buf[:off].abs().sum() == 0 for buf in pair)

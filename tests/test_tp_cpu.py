@@ -112,3 +112,28 @@ def test_evolving_rubric_step(tmp_path):
     metrics, over = mgr.step(["a1", "a2", "b1", "b2"], gts, indices=[7, 7, 9, 9], num_samples=2, training_step=4)
     assert metrics["evolving_rubrics/avg_new_rubrics"] == 0.0 and len(over[7]["rubrics"]) == 3
     assert "is correct" in calls[-2] or "is correct" in calls[-1]  # existing rubrics are shown to the judge
+
+
+def test_native_packer_matches_python_collator():
+    from open_instruct_b200.data import native_pack
+    from open_instruct_b200.data.collate import flatten_examples
+
+    if not native_pack.available():
+        import pytest
+
+        pytest.skip("host library not built")
+    g = torch.Generator().manual_seed(0)
+    ids = [torch.randint(0, 1000, (int(n),), generator=g).tolist() for n in torch.randint(1, 50, (40,), generator=g)]
+    labs = [[-100 if j < 2 else t for j, t in enumerate(x)] for x in ids]
+    rows = native_pack.pack_examples(ids, labs, budget=128, max_per_row=6)
+    plan = native_pack.pack_plan([len(x) for x in ids], 128, 6)
+    assert len(rows) == plan[-1] + 1
+    k = 0
+    for r in rows:
+        n_docs = r["cu_seq_lens_q"].numel() - 1
+        ref = flatten_examples(ids[k:k + n_docs], labs[k:k + n_docs])
+        for key in ("input_ids", "labels", "labels_shifted", "position_ids", "cu_seq_lens_q"):
+            assert torch.equal(r[key], ref[key]), key
+        assert r["input_ids"].numel() <= 128 or n_docs == 1
+        k += n_docs
+    assert k == len(ids)
