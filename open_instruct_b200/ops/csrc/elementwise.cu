@@ -60,20 +60,33 @@ __device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
 // ------------------------------------------------------------------ RMSNorm forward
 // h = x (+ res);  y = h * rsqrt(mean(h^2) + eps) * w.  Writes h back to `h_out` when a
 // residual is given (the new residual stream), rstd[row] for the backward.
-__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+// X32: x is an fp32 accumulator (split-K GEMM output) that is consumed here: it is read, zeroed for the next GEMM that adds
+// into it, and rounded to bf16 before the residual is added (what a bf16 GEMM output would have been).
+template <bool X32>
+__global__ void rmsnorm_fwd_kernel(const void* __restrict__ x_any, const __nv_bfloat16* __restrict__ res,
                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
                                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int D, float eps) {
   __shared__ float red[32];
   extern __shared__ __align__(16) uint8_t dyn[];
   float* hbuf = reinterpret_cast<float*>(dyn);  // D floats: keeps h so x is read once
   const long long row = blockIdx.x;
-  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(reinterpret_cast<const __nv_bfloat16*>(x_any) + row * D);
+  float4* x32 = reinterpret_cast<float4*>(const_cast<float*>(reinterpret_cast<const float*>(x_any)) + row * D);
   const bf16x8* rr = res ? reinterpret_cast<const bf16x8*>(res + row * D) : nullptr;
   const int nv = D / 8;
   float ss = 0.f;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     float f[8];
-    unpack8(xr[i], f);
+    if (X32) {
+      const float4 a = x32[2 * i], b = x32[2 * i + 1];
+      x32[2 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      x32[2 * i + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float t[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16(t[j]));
+    } else {
+      unpack8(xr[i], f);
+    }
     if (rr) {
       float g[8];
       unpack8(rr[i], g);
@@ -346,12 +359,26 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* res, const void* w, v
   const int threads = D >= 2048 ? 256 : 128;
   static bool cfg = false;
   if (!cfg) {
-    cudaFuncSetAttribute(rmsnorm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    cudaFuncSetAttribute(rmsnorm_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     cfg = true;
   }
   if (D * 4 > 64 * 1024) return -2;
-  rmsnorm_fwd_kernel<<<T, threads, D * sizeof(float), ST(stream)>>>(CBF(x), CBF(res), CBF(w), BF(h_out), BF(y), rstd,
-                                                                    D, eps);
+  rmsnorm_fwd_kernel<false><<<T, threads, D * sizeof(float), ST(stream)>>>(x, CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Same, with x an fp32 [T, D] accumulator that is consumed (read, then zeroed): the partner of the split-K GEMM.
+extern "C" int b200_rmsnorm_fwd_acc32(float* x32, const void* res, const void* w, void* h_out, void* y, float* rstd, int T, int D,
+                                      float eps, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8 || D * 4 > 64 * 1024) return -1;
+  const int threads = D >= 2048 ? 256 : 128;
+  static bool cfg = false;
+  if (!cfg) {
+    cudaFuncSetAttribute(rmsnorm_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    cfg = true;
+  }
+  rmsnorm_fwd_kernel<true><<<T, threads, D * sizeof(float), ST(stream)>>>(x32, CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -23,7 +23,7 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_SMEM = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 
-enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
+enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_F32_RED = 3 /* atomic fp32 add: split-K partial sums */ };
 
 struct TileSched {
   int num_m, num_n, total;
@@ -44,7 +44,7 @@ struct TileSched {
 template <bool A_MN, bool B_MN, int OUT, int BN_T = BN, int STAGES_T = STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 void* __restrict__ Cout, int M, int N, int K, long long ldc, int* __restrict__ status) {
+                 void* __restrict__ Cout, int M, int N, int K, long long ldc, int* __restrict__ status, int splits) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -63,8 +63,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   TileSched sched;
   sched.num_m = (M + BM - 1) / BM;
   sched.num_n = (N + BN_T - 1) / BN_T;
-  sched.total = sched.num_m * sched.num_n;
+  const int tiles = sched.num_m * sched.num_n;
+  sched.total = tiles * splits;  // work item t: output tile t / splits, K slice t % splits (split-K: partial sums are added atomically)
   const int num_kb = (K + BK - 1) / BK;
+  const int kb_per = (num_kb + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES_T; ++i) {
@@ -97,9 +99,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
         int m_blk, n_blk;
-        sched.get(t, m_blk, n_blk);
+        sched.get(t / splits, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN_T;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (t % splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES_T;
           const uint32_t ph = (it / STAGES_T) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
@@ -142,7 +145,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN_T;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (t % splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES_T;
           const uint32_t ph = (it / STAGES_T) & 1;
           if (!mbar_wait(&full[s], ph, abort_flag)) {
@@ -161,7 +165,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                      : umma_desc_sw128(a_addr + k * (UK * 2), 16, 1024);
             const uint64_t bd = B_MN ? umma_desc_sw128(b_addr + k * (UK * 128), BK * 128, 1024)
                                      : umma_desc_sw128(b_addr + k * (UK * 2), 16, 1024);
-            umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_ss(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
         }
@@ -174,7 +178,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t tile_i = 0;
     for (int t = blockIdx.x; t < sched.total; t += gridDim.x, ++tile_i) {
       int m_blk, n_blk;
-      sched.get(t, m_blk, n_blk);
+      sched.get(t / splits, m_blk, n_blk);
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       // the decision must be warp-uniform: the TMEM loads below are .sync.aligned
@@ -217,6 +221,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int j = 0; j < 8; ++j) {
                 float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                if (OUT == OUT_F32_RED) {
+                  red_add_v4(crow + 4 * j, v.x, v.y, v.z, v.w);
+                  continue;
+                }
                 if (OUT == OUT_F32_ACC) {
                   const float4 o = reinterpret_cast<float4*>(crow)[j];
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -226,6 +234,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             } else {
               for (int j = 0; j < 32 && col + j < N; ++j) {
                 float v = __uint_as_float(r[j]);
+                if (OUT == OUT_F32_RED) {
+                  atomicAdd(crow + j, v);
+                  continue;
+                }
                 if (OUT == OUT_F32_ACC) v += crow[j];
                 crow[j] = v;
               }
@@ -296,7 +308,7 @@ static int num_sms() {
 
 template <bool A_MN, bool B_MN, int OUT, int BN_T = BN, int STAGES_T = STAGES>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc,
-                  int* status, cudaStream_t stream, int max_ctas) {
+                  int* status, cudaStream_t stream, int max_ctas, int splits = 1) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT, BN_T, STAGES_T>;
   constexpr int smem = STAGES_T * (A_STAGE_BYTES + BN_T * BK * 2) + 1024 /*align*/ + 256 /*barriers*/;
   static bool configured = false;
@@ -305,10 +317,14 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, 
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN_T - 1) / BN_T);
+  const int num_kb = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > num_kb) splits = num_kb;
+  while (splits > 1 && ((num_kb + splits - 1) / splits) * (splits - 1) >= num_kb) --splits;  // no empty K slice
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN_T - 1) / BN_T) * splits;
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, C, M, N, K, ldc, status);
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, C, M, N, K, ldc, status, splits);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -365,4 +381,19 @@ extern "C" int b200_gemm_bf16_skinny(const void* A, const void* B, void* C, int 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<false, false, OUT_BF16, 64, 8>(ta, tb, C, M, N, K, ldc, status, st, 0);
   return launch<false, false, OUT_BF16, 128, 6>(ta, tb, C, M, N, K, ldc, status, st, 0);
+}
+
+// Split-K variant for small M and long K (decode-sized down / o projections): C32[M,N] += A[M,K] * B[N,K]^T with the K
+// range cut into `splits` slices that run on different SMs and add their fp32 partial tiles atomically.  The caller zeroes
+// C32 first (or seeds it with a residual) and converts afterwards.  128 x 128 tiles.
+extern "C" int b200_gemm_bf16_splitk(const void* A, const void* B, float* C32, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldc, int splits, int* status, void* stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2, true);
+  if (r) return 10000 + r;
+  r = make_tmap_2d(&tb, B, N, K, ldb, 128, BK, 2, true);
+  if (r) return 20000 + r;
+  return launch<false, false, OUT_F32_RED, 128, 6>(ta, tb, C32, M, N, K, ldc, status, reinterpret_cast<cudaStream_t>(stream), 0, splits);
 }

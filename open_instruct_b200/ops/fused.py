@@ -78,6 +78,31 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a
     return out
 
 
+def gemm_splitk_(acc32: torch.Tensor, a: torch.Tensor, b: torch.Tensor, splits: int) -> torch.Tensor:
+    """``acc32 += a @ b^T`` (fp32 [M, N], atomically) with the K range cut into ``splits`` slices on different SMs: for small M and
+    long K, where one tile per output block would leave most of the GPU idle.  ``acc32`` must hold zeros (or a seed)."""
+    _check(a, torch.bfloat16, "a")
+    _check(b, torch.bfloat16, "b")
+    _check(acc32, torch.float32, "acc32")
+    M, K = a.shape
+    N = b.shape[0]
+    if tuple(acc32.shape) != (M, N) or b.shape[1] != K or a.stride(0) % 8 or b.stride(0) % 8 or acc32.stride(0) % 4:
+        raise ValueError("split-K GEMM: shape or stride mismatch")
+    call("b200_gemm_bf16_splitk", ptr(a), ptr(b), ptr(acc32), M, N, K, a.stride(0), b.stride(0), acc32.stride(0), splits,
+         ptr(status_word(a.device)), stream_ptr())
+    return acc32
+
+
+def rmsnorm_fwd_acc32_(acc32: torch.Tensor, w: torch.Tensor, eps: float, res: torch.Tensor | None):
+    """RMSNorm of ``bf16(acc32) (+ res)``; ``acc32`` (fp32 [T, D]) is zeroed on the way so that the next split-K GEMM can add
+    into it again.  Returns ``(y, h)``."""
+    T, D = acc32.shape
+    y = torch.empty(T, D, dtype=torch.bfloat16, device=acc32.device)
+    h = torch.empty_like(y)
+    call("b200_rmsnorm_fwd_acc32", ptr(acc32), ptr(res), ptr(w), ptr(h), ptr(y), None, T, D, eps, stream_ptr())
+    return y, h
+
+
 def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, res: torch.Tensor | None = None):
     """Returns (y, h, rstd): h = x (+ res) is the residual stream that was normalised."""
     T, D = x.shape

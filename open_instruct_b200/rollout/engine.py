@@ -161,6 +161,8 @@ class RolloutEngine:
         self.model_step = 0
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
         self.prefill_token_budget = 16384
+        self.decode_splitk = int(os.environ.get("B200_DECODE_SPLITK", "0"))  # K slices for o_proj / down_proj at <= 256 rows
+        self._acc32: dict = {}
         # captured decode steps, keyed by (batch size, padded block-table width, kv splits)
         self.use_cuda_graphs = os.environ.get("B200_DECODE_GRAPHS", "1") == "1" and tp is None
         self._graphs: dict = {}
@@ -290,6 +292,12 @@ class RolloutEngine:
         return sample_ref(logits, temp, top_p, seeds, ctr)
 
     # ------------------------------------------------------------------ model math
+    def _splitk_acc(self, which: int, T: int) -> torch.Tensor:
+        """Persistent zero-initialised fp32 [256, hidden] accumulators (one per projection); the consuming norm re-zeroes them."""
+        if which not in self._acc32:
+            self._acc32[which] = torch.zeros(256, self.spec.hidden_size, dtype=torch.float32, device=self.device)
+        return self._acc32[which][:T]
+
     def _slots_for(self, seq: _Sequence, start: int, end: int) -> list[int]:
         blocks, _ = self.host.blocks(seq.sid)
         return [blocks[t // KV_BLOCK] * KV_BLOCK + t % KV_BLOCK for t in range(start, end)]
@@ -314,6 +322,8 @@ class RolloutEngine:
 
             def add_norm(partial, w, res):
                 """(normed, new residual stream): local fused add+norm, or the cross-rank reduction fused with it."""
+                if partial.dtype == torch.float32:  # split-K accumulator: consumed (and zeroed) by the norm
+                    return f.rmsnorm_fwd_acc32_(partial, w, s.rms_norm_eps, res)
                 if tp is None or res is None:
                     y, h, _ = f.rmsnorm_fwd(partial, w, s.rms_norm_eps, res=res)
                     return y, h
@@ -324,7 +334,11 @@ class RolloutEngine:
             # reduction" at T = 4096 (row-per-thread epilogue stores reach the peer as 16-byte writes), so it is opt-in
             push = tp is not None and tp.world == 2 and T > 256 and os.environ.get("B200_TP_PUSH", "0") == "1"
 
-            def row_proj(x, w):
+            splitk = tp is None and T <= 256 and self.decode_splitk > 1
+
+            def row_proj(x, w, which=0):
+                if splitk:  # few rows, long K: cut K over SMs, partial sums added into a persistent fp32 buffer
+                    return f.gemm_splitk_(self._splitk_acc(which, T), x, w, self.decode_splitk if which else max(2, self.decode_splitk // 2))
                 return tp.row_gemm(x, w) if push else f.gemm(x, w, row_out(), impl=impl_narrow)
 
             for i in range(s.num_layers):
@@ -338,7 +352,7 @@ class RolloutEngine:
                 o = row_proj(attn, p[f"l{i}.wo"])
                 n2, h_mid = add_norm(o, p[f"l{i}.mlp_norm"], h_in)
                 act = f.swiglu_fwd(f.gemm(n2, p[f"l{i}.w_gate_up"], impl=impl))
-                delta = row_proj(act, p[f"l{i}.w_down"])
+                delta = row_proj(act, p[f"l{i}.w_down"], 1)
                 stream = h_mid
             nf, _ = add_norm(delta, p["final_norm"], stream)
             return nf

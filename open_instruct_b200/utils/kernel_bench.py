@@ -108,6 +108,10 @@ def main():
                 by = (N * K + M * K + M * N) * 2
                 for impl in ("1cta", "2cta", "skinny", "skinny128"):
                     rec(f"decode_gemm_{name}_M{M}_{impl}", time_op(lambda: fused.gemm(x, w, impl=impl), args.iters), bytes_=by)
+                if name in ("o", "down"):
+                    acc = torch.zeros(M, N, device="cuda")
+                    for sk in (2, 4, 8):
+                        rec(f"decode_gemm_{name}_M{M}_splitk{sk}", time_op(lambda: fused.gemm_splitk_(acc, x, w, sk), args.iters), bytes_=by)
     if not only or "attn" in only:
         L = args.doc_len or T
         lens = [L] * (T // L) + ([T % L] if T % L else [])

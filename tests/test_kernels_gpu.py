@@ -242,3 +242,24 @@ def test_gemm_scatter_epilogue_local(shape):
             got = pair[j % 2][off:, (j // 2) * 128:(j // 2 + 1) * 128]
             assert torch.equal(got, ref[:, j * 128:(j + 1) * 128]), (shape, j)
         assert all(buf[:off].abs().sum() == 0 for buf in pair)
+
+
+@pytest.mark.parametrize("shape,splits", [((256, 4096, 14336), 8), ((64, 512, 4096), 4), ((37, 200, 1000), 3), ((256, 4096, 4096), 1)])
+def test_gemm_splitk_and_consuming_norm(shape, splits):
+    from open_instruct_b200.ops import fused
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    acc = torch.zeros(M, N, device="cuda")
+    fused.gemm_splitk_(acc, a, b, splits)
+    ref = a.float() @ b.float().t()
+    assert _rel(acc, ref) < 1e-3
+    if N % 8 == 0:
+        res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+        w = (torch.rand(N, device="cuda", generator=g) + 0.5).bfloat16()
+        y, h = fused.rmsnorm_fwd_acc32_(acc, w, 1e-5, res)
+        y2, h2, _ = fused.rmsnorm_fwd(ref.bfloat16(), w, 1e-5, res=res)
+        assert acc.abs().max().item() == 0.0  # consumed: ready for the next accumulation
+        assert (h.float() - h2.float()).abs().max().item() < 0.07 and _rel(y, y2) < 2e-2
