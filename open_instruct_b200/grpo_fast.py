@@ -731,6 +731,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
     from .parallel.weight_sync import sync_in_process
 
     args = setup_runtime_variables(args, streaming)
+    args.temperature = streaming.temperature
     validate_configs(args, streaming, vllm)
     set_seed(args.seed)
     if tc.tokenizer_name_or_path is None:

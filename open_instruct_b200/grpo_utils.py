@@ -72,7 +72,8 @@ class GRPOExperimentConfig(ExperimentConfig):
     loss_fn: GRPOLossType = GRPOLossType.dapo
     record_entropy: bool = False
     use_vllm_logprobs: bool = False
-    temperature: float = 1.0
+    # the sampling temperature lives in StreamingDataLoaderConfig; main() copies it here for the learner's log-prob passes
+    temperature: float = field(default=1.0, init=False)
     # process topology
     single_gpu_mode: bool = False
     num_learners_per_node: list[int] = field(default_factory=lambda: [1])
@@ -99,7 +100,6 @@ class GRPOExperimentConfig(ExperimentConfig):
     hf_repo_revision: str | None = None
     hf_repo_url: str | None = None
     output_dir: str = "output"
-    save_traces: bool = False
     cache_dataset_only: bool = False
     keep_last_n_checkpoints: int = 3
     checkpoint_state_freq: int = 200

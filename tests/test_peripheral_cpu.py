@@ -335,3 +335,33 @@ def test_decontamination_and_oai_generate(tmp_path):
 
     out = og.run_batch(rows, og.Args(poll_seconds=0.0), http=http)
     assert [o["response"] for o in out] == ["r", "r"] and state["polls"] == 1
+
+
+def test_recipes_parse():
+    from open_instruct_b200.config.argparser import ArgumentParserPlus
+    from open_instruct_b200.config.schemas import ModelConfig
+    from open_instruct_b200.data.tokenize import TokenizerConfig
+    from open_instruct_b200.dpo_utils import DPOExperimentConfig
+    from open_instruct_b200.finetune import FlatArguments
+    from open_instruct_b200.grpo_utils import GRPOExperimentConfig
+    from open_instruct_b200.streaming import StreamingDataLoaderConfig, VLLMConfig
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "train_configs")
+    a, _ = ArgumentParserPlus((FlatArguments, TokenizerConfig)).parse([os.path.join(root, "tulu3_sft_8b.yaml"), "--learning_rate", "1e-5"])
+    assert a.learning_rate == 1e-5 and a.gradient_accumulation_steps == 16 and a.packing
+    d, _ = ArgumentParserPlus((DPOExperimentConfig, TokenizerConfig)).parse([os.path.join(root, "tulu3_dpo_8b.yaml")])
+    assert str(getattr(d.loss_type, "value", d.loss_type)) == "dpo_norm" and d.beta == 5.0
+    g = ArgumentParserPlus((GRPOExperimentConfig, TokenizerConfig, ModelConfig, StreamingDataLoaderConfig, VLLMConfig)).parse(
+        [os.path.join(root, "tulu3_grpo_8b.yaml")])
+    assert g[0].num_learners_per_node == [6] and g[3].num_samples_per_prompt_rollout == 16 and g[4].vllm_num_engines == 2
+
+
+@pytest.mark.parametrize("module", ["finetune", "dpo_tune_cache", "reward_modeling", "grpo_fast", "finetune_numpy"])
+def test_entry_point_help(module):
+    """Every trainer builds its command line (no duplicate fields across its config dataclasses)."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-m", f"open_instruct_b200.{module}", "--help"], capture_output=True, text=True, timeout=180, cwd=root)
+    assert res.returncode == 0 and "--" in res.stdout, res.stderr[-1500:]
