@@ -161,7 +161,7 @@ class RolloutEngine:
         self.model_step = 0
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
         self.prefill_token_budget = 16384
-        self.decode_splitk = int(os.environ.get("B200_DECODE_SPLITK", "0"))  # K slices for o_proj / down_proj at <= 256 rows
+        self.decode_splitk = os.environ.get("B200_DECODE_SPLITK", "1") == "1"  # split-K for o_proj / down_proj at <= 256 rows
         self._acc32: dict = {}
         # captured decode steps, keyed by (batch size, padded block-table width, kv splits)
         self.use_cuda_graphs = os.environ.get("B200_DECODE_GRAPHS", "1") == "1" and tp is None
@@ -334,11 +334,14 @@ class RolloutEngine:
             # reduction" at T = 4096 (row-per-thread epilogue stores reach the peer as 16-byte writes), so it is opt-in
             push = tp is not None and tp.world == 2 and T > 256 and os.environ.get("B200_TP_PUSH", "0") == "1"
 
-            splitk = tp is None and T <= 256 and self.decode_splitk > 1
+            splitk = tp is None and T <= 256 and self.decode_splitk
 
             def row_proj(x, w, which=0):
-                if splitk:  # few rows, long K: cut K over SMs, partial sums added into a persistent fp32 buffer
-                    return f.gemm_splitk_(self._splitk_acc(which, T), x, w, self.decode_splitk if which else max(2, self.decode_splitk // 2))
+                # few rows, long K: cut K over SMs, fp32 partial sums added into a persistent buffer that the following norm
+                # consumes.  Measured (8B shapes): down_proj 54 -> 38 us at 64 rows (4 slices), 54 -> 49 us at 256 rows (2 slices);
+                # o_proj 22 -> 17 us at 64 rows, no gain at 256 rows (stays on the narrow-tile kernel)
+                if splitk and (which == 1 or T <= 128):
+                    return f.gemm_splitk_(self._splitk_acc(which, T), x, w, 4 if T <= 128 else 2)
                 return tp.row_gemm(x, w) if push else f.gemm(x, w, row_out(), impl=impl_narrow)
 
             for i in range(s.num_layers):
