@@ -248,11 +248,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const int row = m_blk * 2 * BM + cta * BM + lane_grp * 32 + lane;
       const int n0 = n_blk * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * BN;
-      if (OUT == OUT_BF16 && scatter != nullptr) {
-        // Scatter epilogue (destinations may be peer GPUs).  One TMEM lane per thread means a thread holds one ROW; stored
-        // directly, every 16-byte store of a warp would land in a different row - fine for local L2, wasteful over NVLink.
-        // So each warp transposes through shared memory: 32 rows x 128 columns are staged (16-byte chunks XOR-swizzled by
-        // row against bank conflicts) and written back two rows per instruction, 256 contiguous bytes per row.
+      if (OUT == OUT_BF16 && (scatter != nullptr || (N & 127) == 0)) {
+        // Coalescing epilogue (also the scatter epilogue, whose destinations may be peer GPUs).  One TMEM lane per thread means
+        // a thread holds one ROW; stored directly, every 16-byte store of a warp lands in a different row - tolerable for local
+        // L2, wasteful over NVLink (measured 2.4x on a peer push).  So each warp transposes through shared memory: 32 rows x 128
+        // columns are staged (16-byte chunks XOR-swizzled by row against bank conflicts) and written back two rows per
+        // instruction, 256 contiguous bytes per row.  Used for every bf16 output whose width is a multiple of 128.
         uint8_t* stg = staging + lane_grp * (32 * 256);
         const int row0 = m_blk * 2 * BM + cta * BM + lane_grp * 32;
 #pragma unroll 1
@@ -276,7 +277,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             }
           }
           __syncwarp();
-          __nv_bfloat16* d1 = reinterpret_cast<__nv_bfloat16*>(scatter[col0 >> 7]);
+          __nv_bfloat16* d1 = scatter ? reinterpret_cast<__nv_bfloat16*>(scatter[col0 >> 7]) : reinterpret_cast<__nv_bfloat16*>(Cout) + col0;
           __nv_bfloat16* d2 = scatter2 ? reinterpret_cast<__nv_bfloat16*>(scatter2[col0 >> 7]) : nullptr;
           const int sub = lane >> 4, chunk = lane & 15;
 #pragma unroll 4
