@@ -519,25 +519,44 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         const int tq = q0 + r;
         const bool v = tq < doc_end;
         float* dst = dq_acc + static_cast<long long>(tq) * (Hq * DH) + h * DH;
-        // read this thread's 64 dQ values into registers, hand the TMEM columns back to the MMA warp at once (the next
-        // iteration's S^T can start), then issue the reductions
+        // dQ tile -> global accumulator.  A thread holds 64 columns of ONE query row; reduced directly, each 16-byte
+        // reduction of a warp would hit a different row (half-used 32-byte sectors at the L2 atomic units).  Each warp
+        // therefore transposes its 32 x 64 fp32 block through its own 8 KB slice of the P^T / dS^T buffers (free between
+        // the MMAs that read them and the next iteration's writes, which wait for every warp's dq_done below) and issues
+        // reductions that cover 256 contiguous bytes of a row.
         uint32_t t2[2][32];
 #pragma unroll
         for (int u = 0; u < 2; ++u) tmem_ld32(T_ST + lane_off + (half * 2 + u) * 32, t2[u]);
         tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.dq_done);
-        if (v) {
+        uint8_t* stg = sm.pt + (warp - 2) * (32 * 256);
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < 2; ++u) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              red_add_v4(dst + (half * 2 + u) * 32 + i * 4, __uint_as_float(t2[u][4 * i]), __uint_as_float(t2[u][4 * i + 1]),
-                         __uint_as_float(t2[u][4 * i + 2]), __uint_as_float(t2[u][4 * i + 3]));
+          for (int j = 0; j < 8; ++j) {
+            const int chunk = u * 8 + j;
+            uint4 q4 = make_uint4(t2[u][4 * j], t2[u][4 * j + 1], t2[u][4 * j + 2], t2[u][4 * j + 3]);
+            if (!v) q4 = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = q4;
           }
         }
+        __syncwarp();
+        const int sub = lane >> 4, chunk = lane & 15;
+        const int q_row0 = q0 + lane_grp * 32;
+        float* base = dq_acc + static_cast<long long>(h) * DH + half * 64 + chunk * 4;
+#pragma unroll 4
+        for (int i = 0; i < 32; i += 2) {
+          const int rr = i + sub;
+          const int tok = q_row0 + rr;
+          const uint4 u4 = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((chunk ^ (rr & 15)) << 4));
+          if (tok < doc_end)
+            red_add_v4(base + static_cast<long long>(tok) * (Hq * DH), __uint_as_float(u4.x), __uint_as_float(u4.y), __uint_as_float(u4.z),
+                       __uint_as_float(u4.w));
+        }
+        (void)dst;
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.dq_done);
     }
     if (ok) {
       // the last dq_full wait covers every MMA issued before it, including all dK/dV updates

@@ -253,7 +253,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         // a thread holds one ROW; stored directly, every 16-byte store of a warp lands in a different row - tolerable for local
         // L2, wasteful over NVLink (measured 2.4x on a peer push).  So each warp transposes through shared memory: 32 rows x 128
         // columns are staged (16-byte chunks XOR-swizzled by row against bank conflicts) and written back two rows per
-        // instruction, 256 contiguous bytes per row.  Used for every bf16 output whose width is a multiple of 128.
+        // instruction, 256 contiguous bytes per row.  Used for every bf16 output whose width is a multiple of 128.  (The fp32
+        // outputs keep the row-per-thread form: a thread already moves whole 128-byte lines there, and the transposed
+        // read-modify-write measured 30 % slower because its loads are no longer all in flight at once.)
         uint8_t* stg = staging + lane_grp * (32 * 256);
         const int row0 = m_blk * 2 * BM + cta * BM + lane_grp * 32;
 #pragma unroll 1
