@@ -30,6 +30,7 @@ def main() -> int:
     ap.add_argument("--async_steps", type=int, default=1)
     ap.add_argument("--single_gpu_mode", action="store_true")
     ap.add_argument("--ops", default="fused")
+    ap.add_argument("--engine_tp", type=int, default=1, help="tensor-parallel size of every rollout engine (one process and GPU per rank)")
     a = ap.parse_args()
 
     from open_instruct_b200.actors import ray_compat as ray
@@ -53,18 +54,18 @@ def main() -> int:
                                           filter_zero_std_samples=False)
     try:
         grpo_main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path=a.model), streaming,
-                  VLLMConfig(vllm_num_engines=a.engines, vllm_gpu_memory_utilization=0.85))
+                  VLLMConfig(vllm_num_engines=a.engines, vllm_gpu_memory_utilization=0.85, vllm_tensor_parallel_size=a.engine_tp))
     finally:
         ray.shutdown()
     lines = [json.loads(line) for line in open(os.path.join(args.output_dir, "metrics.jsonl"))]
     steady = lines[1:] or lines
     med = lambda k: statistics.median(float(x.get(k, 0.0)) for x in steady)
-    out = {"metric": "grpo_step_seconds", "value": med("time/total"), "unit": "s", "higher_is_better": False, "n_gpus": a.learners + a.engines,
+    out = {"metric": "grpo_step_seconds", "value": med("time/total"), "unit": "s", "higher_is_better": False, "n_gpus": a.learners + a.engines * a.engine_tp,
            "steps": len(steady), "warmup": 1, "first_step_s": float(lines[0].get("time/total", 0.0)), "learner_step_s": med("time/training"),
            "weight_sync_s": med("time/weight_sync"), "waiting_for_rollouts_s": med("time/trainer_waiting_for_data"),
            "response_tokens_per_step": med("val/total_response_tokens"), "mean_response_length": med("val/sequence_lengths"),
            "dtype": "bf16", "data": "synthetic arithmetic prompts, random-init weights",
-           "config": {"model": a.model, "learners": a.learners, "engines": a.engines, "engine_tp": 1, "prompts_per_step": a.prompts,
+           "config": {"model": a.model, "learners": a.learners, "engines": a.engines, "engine_tp": a.engine_tp, "prompts_per_step": a.prompts,
                       "samples_per_prompt": a.samples, "max_response": a.response_length, "async_steps": a.async_steps,
                       "weight_sync": "every step, multi-destination push kernel through CUDA-IPC mappings"}}
     print(json.dumps(out))
