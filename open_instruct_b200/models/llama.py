@@ -88,6 +88,7 @@ class LlamaModel:
             self.flat = flat
         self.p = self.layout.views(self.flat)
         self._last_qk = None
+        self._rope_tab = None
         # keep the RMSNorm outputs and the SwiGLU activation for the backward pass instead of recomputing them
         # (5.8 GB per 4096-token micro-batch at 8B; about 2.5 % of the step): on by default, off under checkpointing
         self.keep_cheap_activations = os.environ.get("B200_RECOMPUTE_CHEAP", "0") != "1"
@@ -239,6 +240,7 @@ class LlamaModel:
         cu = cu_seqlens.to(torch.int32)
         scale = s.head_dim ** -0.5
         stash: list[_LayerStash] = []
+        self._rope_tab = f.rope_table(pos, self.inv_freq, s.head_dim)  # cos/sin once per packed batch, for every layer and the backward
         if self.sp is not None:
             # sequence parallel: this rank embeds and projects its contiguous chunk of the packed tokens
             lo, hi = self.sp.local_tokens(input_ids.numel())
@@ -268,7 +270,7 @@ class LlamaModel:
         nf, h_last, rstd_f = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
         state = None
         if keep:
-            state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu}
+            state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu, "rope_tab": self._rope_tab}
         return nf, state
 
     def _attention_block(self, i: int, n1, pos, cu):
@@ -281,13 +283,13 @@ class LlamaModel:
         if sp is None:
             qkv = f.gemm(n1, p[f"l{i}.wqkv"])
             self._last_qk = self.qkv_bias_and_norm_(qkv, i)
-            f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, table=self._rope_tab)
             attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
             return qkv, attn, lse, None
         if s.qk_norm or s.attention_bias:
             raise NotImplementedError("sequence parallelism with qk_norm / attention_bias is not built")
         qkv = sp.qkv_project(i, n1, p[f"l{i}.wqkv"], pos.numel())
-        f.rope_(qkv, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim)
+        f.rope_(qkv, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim, table=self._rope_tab)
         attn, lse = f.attn_fwd(qkv, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
         return qkv, attn, lse, sp.attn_exchange(i, attn)
 
@@ -342,6 +344,7 @@ class LlamaModel:
         g = self.g
         h_last, rstd_f = state["final"]
         stash, pos, cu = state["stash"], state["pos"], state["cu"]
+        self._rope_tab = state["rope_tab"]
         # final norm: h_last = stream + delta ; both get the same gradient
         d_stream = f.rmsnorm_bwd(h_last, p["final_norm"], rstd_f, d_nf, None, g["final_norm"])
         del d_nf
@@ -374,12 +377,12 @@ class LlamaModel:
                 d_attn = f.gemm(d_mid, p[f"l{i}.wo"], b_mn=True)
                 dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
                 del d_attn
-                f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True)
+                f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True, table=self._rope_tab)
                 self._qkv_bias_and_norm_bwd_(dqkv, i, st.qk)
             else:
                 d_attn = sp.d_attn_project(d_mid, p[f"l{i}.wo"], pos.numel())
                 dqkv_heads = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
-                f.rope_(dqkv_heads, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim, backward=True)
+                f.rope_(dqkv_heads, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim, backward=True, table=self._rope_tab)
                 dqkv = sp.dqkv_exchange(dqkv_heads)
             n1 = st.n1 if st.n1 is not None else f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)[0]
             st.n1 = None

@@ -210,6 +210,50 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restri
   }
 }
 
+// Rotation table for one packed batch: tab[t][i] = (cos, sin)(pos[t] * inv_freq[i]).  Computed once per micro-batch and
+// reused by every layer's forward and backward rotation (sincosf is by far the most expensive part of the rotation).
+__global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float2* __restrict__ tab, long long T,
+                                  int half) {
+  const long long total = T * half;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float s, c;
+    sincosf(static_cast<float>(pos[idx / half]) * inv_freq[idx % half], &s, &c);
+    tab[idx] = make_float2(c, s);
+  }
+}
+
+// Rotation from the table: one thread rotates 8 (lo, hi) pairs of one head with 16-byte accesses.  Dh % 16 == 0.
+__global__ void rope_apply_kernel(__nv_bfloat16* __restrict__ qkv, const float2* __restrict__ tab, long long T, int Hq, int Hkv, int Dh,
+                                  float sign) {
+  const int half = Dh / 2, nchunk = half / 8, heads = Hq + Hkv;
+  const long long row_stride = static_cast<long long>(Hq + 2 * Hkv) * Dh;
+  const long long total = T * heads * nchunk;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx % nchunk);
+    const long long th = idx / nchunk;
+    const int hd = static_cast<int>(th % heads);
+    const long long t = th / heads;
+    __nv_bfloat16* base = qkv + t * row_stride + static_cast<long long>(hd) * Dh + c * 8;
+    float lo[8], hi[8], ol[8], oh[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(base), lo);
+    unpack8(*reinterpret_cast<const bf16x8*>(base + half), hi);
+    const float4* tv = reinterpret_cast<const float4*>(tab + t * half + c * 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 cs = tv[j];  // (cos, sin) of pairs 2j and 2j + 1
+      const float s0 = cs.y * sign, s1 = cs.w * sign;
+      ol[2 * j] = lo[2 * j] * cs.x - hi[2 * j] * s0;
+      oh[2 * j] = hi[2 * j] * cs.x + lo[2 * j] * s0;
+      ol[2 * j + 1] = lo[2 * j + 1] * cs.z - hi[2 * j + 1] * s1;
+      oh[2 * j + 1] = hi[2 * j + 1] * cs.z + lo[2 * j + 1] * s1;
+    }
+    *reinterpret_cast<bf16x8*>(base) = pack8(ol);
+    *reinterpret_cast<bf16x8*>(base + half) = pack8(oh);
+  }
+}
+
 // ------------------------------------------------------------------ SwiGLU
 // gate_up [T, 2F] (gate | up) -> act [T, F] = silu(gate) * up
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long T,
@@ -304,20 +348,47 @@ __global__ void sumsq_final_kernel(const float* __restrict__ partial, int P, flo
 // ------------------------------------------------------------------ AdamW on an fp32 shard
 // g = grad * gscale[0] (device scalar: clip coefficient / accumulation divisor);
 // decoupled weight decay; writes the refreshed bf16 working copy; optionally zeroes the grad.
-__global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                             float* __restrict__ grad, __nv_bfloat16* __restrict__ param_bf16, long long n,
-                             const float* __restrict__ gscale, float lr, float beta1, float beta2, float eps, float wd,
-                             float bc1, float bc2, int zero_grad) {
+__device__ __forceinline__ float adamw_one(float& p, float& mi, float& vi, float g, float lr, float beta1, float beta2, float eps, float wd,
+                                           float bc1, float bc2) {
+  mi = beta1 * mi + (1.f - beta1) * g;
+  vi = beta2 * vi + (1.f - beta2) * g * g;
+  p *= (1.f - lr * wd);
+  p -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+  return p;
+}
+
+// VEC: every pointer is 16-byte aligned (8 for the bf16 copy): four elements per thread and iteration, 16-byte accesses.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, float* __restrict__ grad,
+             __nv_bfloat16* __restrict__ param_bf16, long long n, const float* __restrict__ gscale, float lr, float beta1, float beta2,
+             float eps, float wd, float bc1, float bc2, int zero_grad) {
   const float gs = gscale ? gscale[0] : 1.f;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float g = grad[i] * gs;
-    float p = master[i];
-    const float mi = beta1 * m[i] + (1.f - beta1) * g;
-    const float vi = beta2 * v[i] + (1.f - beta2) * g * g;
-    p *= (1.f - lr * wd);
-    const float denom = sqrtf(vi / bc2) + eps;
-    p -= lr * (mi / bc1) / denom;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  long long done = 0;
+  if (VEC) {
+    const long long nv = n / 4;
+    for (long long i = tid; i < nv; i += nthreads) {
+      const float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+      float4 p4 = reinterpret_cast<const float4*>(master)[i];
+      float4 m4 = reinterpret_cast<const float4*>(m)[i];
+      float4 v4 = reinterpret_cast<const float4*>(v)[i];
+      adamw_one(p4.x, m4.x, v4.x, g4.x * gs, lr, beta1, beta2, eps, wd, bc1, bc2);
+      adamw_one(p4.y, m4.y, v4.y, g4.y * gs, lr, beta1, beta2, eps, wd, bc1, bc2);
+      adamw_one(p4.z, m4.z, v4.z, g4.z * gs, lr, beta1, beta2, eps, wd, bc1, bc2);
+      adamw_one(p4.w, m4.w, v4.w, g4.w * gs, lr, beta1, beta2, eps, wd, bc1, bc2);
+      reinterpret_cast<float4*>(m)[i] = m4;
+      reinterpret_cast<float4*>(v)[i] = v4;
+      reinterpret_cast<float4*>(master)[i] = p4;
+      if (param_bf16) reinterpret_cast<uint2*>(param_bf16)[i] = make_uint2(pack_bf16x2(p4.x, p4.y), pack_bf16x2(p4.z, p4.w));
+      if (zero_grad) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    done = nv * 4;
+  }
+  for (long long i = done + tid; i < n; i += nthreads) {
+    float p = master[i], mi = m[i], vi = v[i];
+    adamw_one(p, mi, vi, grad[i] * gs, lr, beta1, beta2, eps, wd, bc1, bc2);
     m[i] = mi;
     v[i] = vi;
     master[i] = p;
@@ -383,7 +454,8 @@ extern "C" int b200_rmsnorm_fwd_acc32(float* x32, const void* res, const void* w
 }
 
 // number of partial rows the backward needs in its scratch buffer ([ctas, D] floats)
-extern "C" int b200_rmsnorm_bwd_ctas(int T) { return T < 296 ? T : 296; }
+// four CTAs per SM: one CTA walks its rows one at a time (two block reductions per row), so rows in flight = CTAs
+extern "C" int b200_rmsnorm_bwd_ctas(int T) { return T < 592 ? T : 592; }
 
 extern "C" int b200_rmsnorm_bwd(const void* h, const void* w, const float* rstd, const void* dy, const void* dres,
                                 void* dx, float* dw_partial, float* dw_out, int T, int D, void* stream) {
@@ -409,6 +481,23 @@ extern "C" int b200_rope(void* qkv, const int* pos, const float* inv_freq, int T
   const long long total = static_cast<long long>(T) * (Hq + Hkv) * (Dh / 4);
   rope_kernel<<<grid_for(total, 256), 256, 0, ST(stream)>>>(BF(qkv), pos, inv_freq, T, Hq, Hkv, Dh,
                                                             backward ? -1.f : 1.f);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// table [T, Dh/2] float2 (cos, sin)
+extern "C" int b200_rope_table(const int* pos, const float* inv_freq, void* table, int T, int Dh, void* stream) {
+  if (T <= 0) return 0;
+  const long long total = static_cast<long long>(T) * (Dh / 2);
+  rope_table_kernel<<<grid_for(total, 256), 256, 0, ST(stream)>>>(pos, inv_freq, reinterpret_cast<float2*>(table), T, Dh / 2);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int b200_rope_apply(void* qkv, const void* table, int T, int Hq, int Hkv, int Dh, int backward, void* stream) {
+  if (T <= 0) return 0;
+  if (Dh % 16) return -1;
+  const long long total = static_cast<long long>(T) * (Hq + Hkv) * (Dh / 16);
+  rope_apply_kernel<<<grid_for(total, 256), 256, 0, ST(stream)>>>(BF(qkv), reinterpret_cast<const float2*>(table), T, Hq, Hkv, Dh,
+                                                                 backward ? -1.f : 1.f);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -458,8 +547,14 @@ extern "C" int b200_adamw(float* master, float* m, float* v, float* grad, void* 
   if (n <= 0) return 0;
   const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
   const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
-  adamw_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, ST(stream)>>>(master, m, v, grad, BF(param_bf16), n, gscale, lr,
-                                                                 beta1, beta2, eps, wd, bc1, bc2, zero_grad);
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                         reinterpret_cast<uintptr_t>(grad) | (reinterpret_cast<uintptr_t>(param_bf16) << 1);
+  if ((bits & 15) == 0)
+    adamw_kernel<true><<<grid_for(n / 4 + 1, 256, 148 * 8), 256, 0, ST(stream)>>>(master, m, v, grad, BF(param_bf16), n, gscale, lr, beta1, beta2,
+                                                                                   eps, wd, bc1, bc2, zero_grad);
+  else
+    adamw_kernel<false><<<grid_for(n, 256, 148 * 8), 256, 0, ST(stream)>>>(master, m, v, grad, BF(param_bf16), n, gscale, lr, beta1, beta2, eps,
+                                                                            wd, bc1, bc2, zero_grad);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -512,7 +607,7 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* h, const void* w, const floa
     g_partials_addr[dev] = p;
   }
   float* partials = g_partials_addr[dev];
-  const int ctas = b200_rmsnorm_bwd_ctas(T);  // <= NOALLOC_MAX_CTAS
+  const int ctas = T < NOALLOC_MAX_CTAS ? T : NOALLOC_MAX_CTAS;
   // every CTA overwrites its whole [D] row of the partials, so nothing left by an earlier call is read
   rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx),
                                                                    partials, T, D);

@@ -125,9 +125,23 @@ def rmsnorm_bwd(h: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor, dy: torch.
     return dx
 
 
+def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """(cos, sin) of every (token, frequency) pair, fp32 [T, head_dim / 2, 2]: computed once per packed batch and shared by all
+    layers and by the backward rotation."""
+    if pos.dtype != torch.int32:
+        raise TypeError("rope positions must be int32")
+    tab = torch.empty(pos.numel(), head_dim // 2, 2, dtype=torch.float32, device=pos.device)
+    call("b200_rope_table", ptr(pos), ptr(inv_freq), ptr(tab), pos.numel(), head_dim, stream_ptr())
+    return tab
+
+
 def rope_(qkv: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-          backward: bool = False) -> torch.Tensor:
-    """In-place rotary embedding of the q and k heads of fused qkv; ``pos`` int32 [T]."""
+          backward: bool = False, table: torch.Tensor | None = None) -> torch.Tensor:
+    """In-place rotary embedding of the q and k heads of fused qkv; ``pos`` int32 [T].  With ``table`` (from ``rope_table``)
+    the rotation reads precomputed cos/sin instead of evaluating them per head."""
+    if table is not None and head_dim % 16 == 0:
+        call("b200_rope_apply", ptr(qkv), ptr(table), qkv.shape[0], n_q, n_kv, head_dim, int(backward), stream_ptr())
+        return qkv
     if pos.dtype != torch.int32:
         raise TypeError("rope positions must be int32")
     call("b200_rope", ptr(qkv), ptr(pos), ptr(inv_freq), qkv.shape[0], n_q, n_kv, head_dim, int(backward), stream_ptr())

@@ -30,6 +30,8 @@ _SIGNATURES = {
     "b200_gemm2_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, I],
     "b200_gemm_bf16_skinny": [P, P, P, I, I, I, L, L, L, P, P, I],
     "b200_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "b200_rope_table": [P, P, P, I, I, P],
+    "b200_rope_apply": [P, P, I, I, I, I, I, P],
     "b200_rmsnorm_fwd_acc32": [P, P, P, P, P, P, I, I, F, P],
     "b200_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, P, P],
     "b200_rmsnorm_bwd_ctas": [I],

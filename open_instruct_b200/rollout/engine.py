@@ -312,6 +312,7 @@ class RolloutEngine:
             from ..ops.lib import call, ptr, stream_ptr
 
             pos32 = pos.to(torch.int32)
+            rope_tab = f.rope_table(pos32, self.model.inv_freq, s.head_dim)
             impl = "2cta"
             # few rows and a 4096-wide output: the 256-wide tiles leave most SMs idle, the 64-wide kernel streams the weights
             # from four times as many CTAs (measured at M = 256: o_proj 34 -> 21 us, down_proj 81 -> 54 us)
@@ -348,7 +349,7 @@ class RolloutEngine:
                 n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
                 qkv = f.gemm(n1, p[f"l{i}.wqkv"], impl=impl_qkv)
                 self.model.qkv_bias_and_norm_(qkv, i)
-                f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+                f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, table=rope_tab)
                 call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
                      s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
                 attn = attn_fn(i, qkv)

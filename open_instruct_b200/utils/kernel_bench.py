@@ -137,6 +137,8 @@ def main():
         pos = torch.arange(T, device="cuda", dtype=torch.int32)
         inv = torch.rand(Dh // 2, device="cuda")
         rec("rope", time_op(lambda: fused.rope_(qkv, pos, inv, Hq, Hkv, Dh), args.iters), bytes_=T * (Hq + Hkv) * Dh * 2 * 2)
+        tab = fused.rope_table(pos, inv, Dh)
+        rec("rope_from_table", time_op(lambda: fused.rope_(qkv, pos, inv, Hq, Hkv, Dh, table=tab), args.iters), bytes_=T * (Hq + Hkv) * Dh * 2 * 2)
         logits = bf(T, V)
         labels = torch.randint(0, V, (T,), device="cuda")
         rec("logprob_fwd", time_op(lambda: fused.logprob_fwd(logits, labels), args.iters), bytes_=T * V * 2)

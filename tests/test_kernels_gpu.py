@@ -105,6 +105,13 @@ def test_rope_roundtrip_and_ref():
     back = fused.rope_(got.clone(), pos, inv, Hq, Hkv, Dh, backward=True)
     assert _rel(back, qkv) < 8e-3
     assert torch.equal(got[:, (Hq + Hkv) * Dh:], qkv[:, (Hq + Hkv) * Dh:])
+    # same rotation from the precomputed cos/sin table (what the model uses)
+    tab = fused.rope_table(pos, inv, Dh)
+    got_t = fused.rope_(qkv.clone(), pos, inv, Hq, Hkv, Dh, table=tab)
+    assert _rel(got_t, expect) < 4e-3 and (got_t.float() - got.float()).abs().max().item() < 0.04
+    back_t = fused.rope_(got_t.clone(), pos, inv, Hq, Hkv, Dh, backward=True, table=tab)
+    assert _rel(back_t, qkv) < 8e-3
+    assert torch.equal(got_t[:, (Hq + Hkv) * Dh:], qkv[:, (Hq + Hkv) * Dh:])
 
 
 def test_swiglu():
