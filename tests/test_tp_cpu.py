@@ -137,3 +137,27 @@ def test_native_packer_matches_python_collator():
         assert r["input_ids"].numel() <= 128 or n_docs == 1
         k += n_docs
     assert k == len(ids)
+
+
+def test_model_dims_utilisation_stays_physical():
+    """Logged-run shapes (Qwen2.5-7B on 8 single-GPU H100 engines, 32 prompts x 16 samples, ~440-546 response tokens in
+    11-15 s): the analytic MFU / MBU must stay at or below 100 % - the failure mode this fixture was recorded for."""
+    import random
+
+    from open_instruct_b200.utils.model_dims import ModelDims
+
+    dims = ModelDims(num_layers=28, hidden_size=3584, intermediate_size=18944, vocab_size=152064, num_attn_heads=28, head_dim=128, num_kv_heads=4,
+                     device_name="h100")
+    rng = random.Random(0)
+    for gen_time, mean_resp in ((13.86, 440), (15.40, 502), (11.02, 546)):
+        prompts = [rng.randint(60, 320) for _ in range(32)]
+        resp = [max(1, int(rng.gauss(mean_resp, 150))) for _ in range(32 * 16)]
+        u = dims.calculate_actor_utilization(prompts, resp, gen_time, 16, 8, 1)
+        assert 0 < u["mfu"] <= 100 and 0 < u["mbu"] <= 100, u
+    # training: 6 * params FLOPs per token dominates; 512 sequences of 600 tokens in 4 s on 16 GPUs is far below peak
+    learner = dims.calculate_learner_utilization([100] * 32, [500] * 512, 4.0, 16, 16)
+    assert 0 < learner["mfu"] <= 100
+    # B200 denominators exist and are larger than H100's
+    b = ModelDims(num_layers=28, hidden_size=3584, intermediate_size=18944, vocab_size=152064, num_attn_heads=28, head_dim=128, num_kv_heads=4,
+                  device_name="b200")
+    assert b.device_flops > dims.device_flops and b.device_memory_bandwidth > dims.device_memory_bandwidth
