@@ -24,8 +24,11 @@ def _paragraphs(text: str, sep: str = r"\n\s*\n") -> list[str]:
     return [p for p in re.split(sep, text.strip()) if p.strip()]
 
 
-def _compare(n: int, relation: str | None, target: int) -> bool:
+def _compare(n: int, relation: str | None, target: int, slack: int | None = None) -> bool:
+    """``slack`` is the tolerance of the "around" quantifier (a tenth of the target, at least one, by default)."""
     rel = (relation or "at least").lower()
+    if rel == "around":
+        return abs(n - target) <= (max(round(0.1 * target), 1) if slack is None else slack)
     if rel in ("at least", ">=", "more than or equal"):
         return n >= target
     if rel in ("at most", "<=", "less than or equal"):
@@ -36,7 +39,7 @@ def _compare(n: int, relation: str | None, target: int) -> bool:
         return n > target
     if rel in ("exactly", "==", "equal"):
         return n == target
-    raise ValueError(f"unknown relation {relation}")
+    return False  # an unknown quantifier satisfies nothing
 
 
 # ------------------------------------------------------------------ single-constraint functions
@@ -72,12 +75,11 @@ def verify_paragraph_count(text: str, N: int) -> bool:
 
 
 def validate_word_constraint(text: str, N: int, quantifier: str) -> bool:
-    return _compare(len(text.strip().split()), {"around": "exactly"}.get(quantifier, quantifier), N) if quantifier != "around" \
-        else abs(len(text.strip().split()) - N) <= max(1, round(0.1 * N))
+    return _compare(len(text.strip().split()), quantifier, N)
 
 
 def verify_sentence_constraint(text: str, N: int, quantifier: str) -> bool:
-    return _compare(len(_sentences(text)), quantifier, N)
+    return _compare(len(_sentences(text)), quantifier, N, slack=1)
 
 
 def validate_paragraphs(text: str, N: int, first_word: str, i: int) -> bool:

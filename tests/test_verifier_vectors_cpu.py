@@ -40,3 +40,38 @@ def test_f1(pred, label, want):
 @pytest.mark.parametrize("pred,label,want", GSM)
 def test_gsm8k_signed_numbers(pred, label, want):
     assert gtu.GSM8KVerifier()([], pred, label).score == want
+
+
+# ------------------------------------------------------------------ instruction-following constraint functions
+@pytest.mark.parametrize("text,n,quant,want", [
+    ("AAA BBB CCC DDD EEE", 5, "around", True),
+    ("AAA BBB CCC DDD", 5, "around", True),
+    ("AAA BBB CCC DDD EEE FFF", 5, "around", True),
+    ("AAA BBB", 5, "around", False),
+    ("AAA BBB CCC", 2, "at least", True),
+    ("AAA BBB CCC DDD", 2, "at most", False),
+    ("AAA BBB", 2, "no such quantifier", False),
+])
+def test_capital_word_frequency(text, n, quant, want):
+    from open_instruct_b200 import if_functions
+    assert if_functions.validate_frequency_capital_words(text, n, quant) is want
+
+
+@pytest.mark.parametrize("text,options,want", [
+    ("I believe the answer is B", ["A", "B", "C", "D"], True),
+    ("I choose red", ["red", "blue"], True),
+    ("I choose green", ["red", "blue"], False),
+    ("red", ["red", "blue"], True),
+])
+def test_validate_choice(text, options, want):
+    from open_instruct_b200 import if_functions
+    assert if_functions.validate_choice(text, options) is want
+
+
+def test_around_tolerances():
+    from open_instruct_b200 import if_functions
+    words = " ".join(["w"] * 112)
+    assert if_functions.validate_word_constraint(words, 100, "around") is False
+    assert if_functions.validate_word_constraint(" ".join(["w"] * 91), 100, "around") is True
+    assert if_functions.verify_sentence_constraint("One. Two. Three.", 4, "around") is True
+    assert if_functions.verify_sentence_constraint("One. Two.", 4, "around") is False
