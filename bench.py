@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--ops", default="fused", choices=["fused", "ref"])
     ap.add_argument("--gradient_checkpointing", action="store_true")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--shard_parameters", action="store_true",
+                    help="sft: ZeRO-3 style gather-on-use parameter sharding instead of the resident bf16 copy (for models that do not fit)")
     ap.add_argument("--task", default="sft", choices=["sft", "dpo"],
                     help="sft: the headline metric; dpo: DPO train tokens/s with cached reference log-probs (same JSON shape)")
     ap.add_argument("--pairs_per_gpu", type=int, default=16)
@@ -171,7 +173,8 @@ def run_dpo(args) -> int:
               "dtype": "bf16", "data": "synthetic preference pairs (shared random prompt 64-512, random responses 64-1024, random-init weights)",
               "config": {"model": args.model, "global_batch": world * n, "max_len": 2048, "pairs_per_micro_batch": args.pairs_per_micro,
                          "loss": "dpo_norm beta 5, cached reference log-probs (built before the timed region)",
-                         "parallelism": f"dp{world} zero-sharded optimizer ({learner.comm} comm), resident bf16 params", "ops": learner.ops,
+                         "parallelism": (f"dp{world} zero-sharded optimizer ({learner.comm} comm), resident bf16 params" if learner.z3 is None else
+                            f"dp{world} parameters, gradients and optimizer sharded, layers gathered on use ({learner.z3.comm} transport)"), "ops": learner.ops,
                          "l2": "per-step working set far exceeds the 126 MB L2; no explicit flush"},
               "clocks": clocks, "gpu_launches": launches, "loss": float(loss.item()), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
               "e2e": {"value": float(t.item()) / (ms2 / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
@@ -207,7 +210,7 @@ def main():
     total_steps = args.warmup + 2 * args.steps
     cfg = LearnerConfig(ops=args.ops, comm=args.comm, learning_rate=5e-6, lr_scheduler_type="linear",
                         warmup_steps=max(1, int(0.03 * 1000)), total_steps=1000, max_grad_norm=1.0,
-                        gradient_checkpointing=args.gradient_checkpointing, seed=0)
+                        gradient_checkpointing=args.gradient_checkpointing, seed=0, shard_parameters=args.shard_parameters)
     learner = Learner(spec, cfg, device=device)
 
     def host_step(i):
@@ -287,7 +290,8 @@ def main():
             "global_batch": world * args.packs_per_gpu,
             "seq_len": args.seq_len,
             "micro_batch_tokens": args.seq_len * args.packs_per_micro,
-            "parallelism": f"dp{world} zero-sharded optimizer ({learner.comm} comm), resident bf16 params",
+            "parallelism": (f"dp{world} zero-sharded optimizer ({learner.comm} comm), resident bf16 params" if learner.z3 is None else
+                            f"dp{world} parameters, gradients and optimizer sharded, layers gathered on use ({learner.z3.comm} transport)"),
             "ops": learner.ops,
             "optimizer": "AdamW fp32 master+moments, fp32 grad accumulation, clip 1.0, inside timed region",
             "gradient_checkpointing": bool(args.gradient_checkpointing),

@@ -72,8 +72,8 @@ def load_train_state(ckpt_dir: str, optimizer, group=None, restore_rng: bool = T
     else:
         sd = reshard_optimizer(ckpt_dir, rank, world, optimizer.shard, optimizer.master.device)
     optimizer.load_state_dict(sd)
-    # every rank refreshed only its own slice of the working copy: exchange them
-    if world > 1:
+    # every rank refreshed only its own slice of the working copy: exchange them (parameter-sharded state keeps slices only)
+    if world > 1 and not getattr(optimizer, "is_param_sharded", False):
         mine = optimizer.flat[optimizer.lo:optimizer.hi].contiguous()
         if optimizer.flat.is_cuda:
             torch.distributed.all_gather_into_tensor(optimizer.flat, mine, group=group)

@@ -119,12 +119,12 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
     cfg = LearnerConfig(ops=args.ops, comm=args.comm_backend, learning_rate=args.learning_rate, weight_decay=args.weight_decay,
                         max_grad_norm=args.max_grad_norm, lr_scheduler_type=args.lr_scheduler_type,
                         warmup_steps=int(max_steps * args.warmup_ratio), total_steps=max_steps,
-                        gradient_checkpointing=args.activation_memory_budget < 1 or args.gradient_checkpointing, seed=args.seed)
+                        gradient_checkpointing=args.activation_memory_budget < 1 or args.gradient_checkpointing, seed=args.seed,
+                        offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters)
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
-        load_hf_checkpoint(src, learner.model.flat.detach(), spec, strict=False)
-        learner.opt.master.copy_(learner.model.flat.detach()[learner.opt.lo:learner.opt.hi].float())
+        learner.load_hf(src)
     dims = ModelDims.from_spec(spec)
     if is_main and args.zero_stage is not None:
         logger.info("placement: %s", build_deepspeed_config(args.zero_stage, args.offload_optimizer, args.offload_param,
@@ -231,8 +231,9 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
         if completed >= max_steps:
             break
     pdist.barrier()
+    full_weights = learner.full_flat()  # a gather when the parameters are sharded: every rank takes part
     if is_main:
-        save_hf_checkpoint(learner.model.flat, spec, args.output_dir, tokenizer=tokenizer)
+        save_hf_checkpoint(full_weights, spec, args.output_dir, tokenizer=tokenizer)
     profiler.close()
     tracker.close()
     pdist.barrier()

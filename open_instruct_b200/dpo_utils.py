@@ -112,6 +112,7 @@ class DPOExperimentConfig(ExperimentConfig, ModelConfig, DPOConfig, DPOTrainingC
     hf_metadata_dataset: str | None = None
     zero_stage: int | None = None
     offload_optimizer: bool = False
+    shard_parameters: bool | None = None  # gather-on-use parameter sharding; None = only when the model does not fit resident
     offload_param: bool = False
     zero_hpz_partition_size: int = 8
     ops: str = "auto"

@@ -126,6 +126,7 @@ class FlatArguments:
     verbose: bool = False
     sequence_parallel_size: int = field(default=1, metadata={"help": "Ulysses sequence-parallel degree"})
     profiling: bool = field(default=False, metadata={"help": "torch.profiler trace of a few steps into <output_dir>/profiler"})
+    shard_parameters: bool | None = field(default=None, metadata={"help": "ZeRO-3 parameter sharding: gather each layer on use. Default: only when the resident design does not fit the GPU"})
     offload_optimizer: bool = field(default=False, metadata={"help": "keep fp32 master weights and Adam moments in pinned host memory"})
     # engine selection (not in the reference: there the back end is fixed by the launcher config)
     ops: Literal["auto", "fused", "ref"] = "auto"
@@ -230,12 +231,11 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                         lr_scheduler_type=args.lr_scheduler_type, warmup_steps=warmup, total_steps=max_steps,
                         final_lr_ratio=args.final_lr_ratio, gradient_checkpointing=args.gradient_checkpointing, seed=args.seed,
                         sequence_parallel_size=sp, sp_max_tokens=args.max_seq_length * max(1, per_rank) if sp > 1 else 0,
-                        offload_optimizer=args.offload_optimizer)
+                        offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters)
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
-        load_hf_checkpoint(src, learner.model.flat.detach(), spec, strict=False)
-        learner.opt.master.copy_(learner.model.flat.detach()[learner.opt.lo:learner.opt.hi].float())
+        learner.load_hf(src)
     tracker = Tracker(args.output_dir, args.exp_name, {**asdict(args), **{f"tc_{k}": v for k, v in asdict(tc).items()}},
                       report_to=args.report_to if args.with_tracking else ("jsonl",), wandb_project=args.wandb_project_name,
                       wandb_entity=args.wandb_entity, enabled=is_main)
@@ -319,8 +319,9 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
     profiler.close()
     # ------------------------------------------------------------------ final export
     pdist.barrier()
+    full_weights = learner.full_flat()  # a gather when the parameters are sharded: every rank takes part
     if is_main:
-        save_hf_checkpoint(learner.model.flat, spec, args.output_dir, tokenizer=tokenizer)  # with LoRA: the merged model
+        save_hf_checkpoint(full_weights, spec, args.output_dir, tokenizer=tokenizer)  # with LoRA: the merged model
         if lora is not None:
             lora.save(os.path.join(args.output_dir, "adapter"), args.model_name_or_path or "")
         if args.clean_checkpoints_at_end:

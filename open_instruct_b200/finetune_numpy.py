@@ -105,8 +105,7 @@ def main(args: Args) -> dict:
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
-        load_hf_checkpoint(src, learner.model.flat.detach(), spec, strict=False)
-        learner.opt.master.copy_(learner.model.flat.detach()[learner.opt.lo:learner.opt.hi].float())
+        learner.load_hf(src)
     tracker = Tracker(args.save_folder, args.exp_name, asdict(args), report_to=("jsonl",), enabled=rank == 0)
     step = 0
     ckpt = get_last_checkpoint_path(args.save_folder, None)
@@ -136,8 +135,9 @@ def main(args: Args) -> dict:
             if rank == 0:
                 clean_last_n_checkpoints(args.save_folder, args.keep_last_n_checkpoints)
     pdist.barrier()
+    full_weights = learner.full_flat()  # a gather when the parameters are sharded: every rank takes part
     if rank == 0:
-        save_hf_checkpoint(learner.model.flat, spec, os.path.join(args.save_folder, "hf"))
+        save_hf_checkpoint(full_weights, spec, os.path.join(args.save_folder, "hf"))
     tracker.close()
     pdist.barrier()
     metrics["completed_steps"] = step

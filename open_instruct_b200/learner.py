@@ -41,6 +41,15 @@ class LearnerConfig:
     offload_optimizer: bool = False   # fp32 master / moments in pinned host memory, streamed through the GPU per step
     sequence_parallel_size: int = 1   # Ulysses: every packed micro-batch is split over this many ranks (== world size)
     sp_max_tokens: int = 8192         # largest packed micro-batch (all ranks together) the exchange buffers hold
+    # Parameter sharding (ZeRO stage 3): None = only when the resident design does not fit this GPU (``needs_sharding``)
+    shard_parameters: bool | None = None
+
+
+def needs_sharding(total_params: int, world: int, hbm_bytes: int, offload_optimizer: bool = False) -> bool:
+    """True when bf16 parameters + the fp32 gradient accumulator resident on every GPU, plus this rank's share of the fp32
+    master weights and Adam moments, would take more than 70 % of the GPU's memory (the rest is for activations)."""
+    resident = 6 * total_params + (0 if offload_optimizer else 12 * total_params // max(world, 1)) + 4 * total_params // max(world, 1)
+    return resident > 0.7 * hbm_bytes
 
 
 class Learner:
@@ -65,6 +74,33 @@ class Learner:
         layout = ParamLayout(spec)
         n = padded_numel(layout.total, self.world)
         self.symm = None
+        self.z3 = None
+        shard = cfg.shard_parameters
+        if shard is None:
+            shard = (ops == "fused" and self.world > 1 and
+                     needs_sharding(layout.total, self.world, torch.cuda.get_device_properties(self.device).total_memory, cfg.offload_optimizer))
+        if shard:
+            if ops != "fused":
+                raise NotImplementedError("parameter sharding runs on the fused (CUDA) path")
+            if cfg.sequence_parallel_size > 1:
+                raise NotImplementedError("parameter sharding together with sequence parallelism is not built")
+            from .parallel.zero3 import Zero3State
+
+            self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, sharded=True,
+                                    gradient_checkpointing=cfg.gradient_checkpointing)
+            self.z3 = Zero3State(layout, self.device, dtype, group, comm="peer" if comm == "fused" else "nccl", lr=cfg.learning_rate,
+                                 betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
+                                 use_kernels=True, offload=cfg.offload_optimizer)
+            if flat_init is not None:
+                self.z3.load_full(flat_init)
+            else:
+                self.z3.init_random(cfg.seed)
+            self.z3.attach(self.model)
+            self.opt = self.z3  # same checkpoint interface (state_dict / load_state_dict / master)
+            self.global_step = 0
+            self._accum = 0
+            self.sp = 1
+            return
         if comm == "fused":
             from .parallel.symm import SymmetricState
 
@@ -126,6 +162,12 @@ class Learner:
         the mean over everything accumulated since the last step, DeepSpeed's convention."""
         if grad_scale is None:
             grad_scale = 1.0 / (max(self._accum, 1) * self.world)
+        if self.z3 is not None:
+            with nvtx_range("optimizer_step"):
+                norm = self.z3.step(lr=self.lr(), grad_scale=grad_scale)
+            self._accum = 0
+            self.global_step += 1
+            return norm
         grad = self.model.grad_flat()
         if grad is None:
             raise RuntimeError("optimizer_step called without any backward")
@@ -145,6 +187,38 @@ class Learner:
         self.global_step += 1
         return norm
 
+    # ------------------------------------------------------------------ whole-model views (loading, saving, weight sync)
+    @torch.no_grad()
+    def load_full_weights(self, flat: torch.Tensor) -> None:
+        """Install a complete flat parameter vector (global layout, any device) as the working copy and the fp32 master."""
+        if self.z3 is not None:
+            self.z3.load_full(flat)
+            return
+        w = self.model.flat.detach()
+        w[: flat.numel()].copy_(flat.to(w.dtype))
+        self.opt.master.copy_(w[self.opt.lo:self.opt.hi].float())
+
+    def load_hf(self, path: str, strict: bool = False) -> None:
+        """Load a Hugging Face checkpoint folder.  With sharded parameters the tensors are staged in host memory and every
+        rank keeps its slices only."""
+        from .ckpt.hf_io import load_hf_checkpoint
+
+        if self.z3 is None:
+            load_hf_checkpoint(path, self.model.flat.detach(), self.spec, strict=strict)
+            self.opt.master.copy_(self.model.flat.detach()[self.opt.lo:self.opt.hi].float())
+            return
+        stage = torch.zeros(self.model.layout.total, dtype=self.z3.dtype)
+        load_hf_checkpoint(path, stage, self.spec, strict=strict)
+        self.load_full_weights(stage)
+
+    @torch.no_grad()
+    def full_flat(self, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The complete bf16 parameter vector in the global layout: the resident working copy, or a gather of the shards
+        (a collective: every rank calls it)."""
+        if self.z3 is None:
+            return self.model.flat.detach()
+        return self.z3.gather_full(out)
+
     # ------------------------------------------------------------------ residency (colocated learner + engine)
     def offload_to_cpu(self) -> int:
         """Move what only the optimizer step needs (fp32 master weights, moments, gradient shard, gradient accumulator) to
@@ -153,15 +227,16 @@ class Learner:
         symmetric memory (they must stay mapped) or already on the host."""
         moved = 0
         self._parked = {}
+        opt = self.z3.opt if self.z3 is not None else self.opt
         for name in ("master", "m", "v", "grad_shard"):
-            t = getattr(self.opt, name, None)
+            t = getattr(opt, name, None)
             if t is not None and t.is_cuda:
                 host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
                 host.copy_(t)
                 self._parked[name] = host
-                setattr(self.opt, name, host)  # keeps the attribute valid (state_dict works while parked)
+                setattr(opt, name, host)  # keeps the attribute valid (state_dict works while parked)
                 moved += t.numel() * t.element_size()
-        if self.symm is None and self.model.main_grad is not None and self.model.main_grad.is_cuda and self._accum == 0:
+        if self.z3 is None and self.symm is None and self.model.main_grad is not None and self.model.main_grad.is_cuda and self._accum == 0:
             moved += self.model.main_grad.numel() * 4
             self.model.main_grad = None
             self.model.g = {}
@@ -172,9 +247,9 @@ class Learner:
 
     def backload_to_gpu(self) -> None:
         for name, host in getattr(self, "_parked", {}).items():
-            setattr(self.opt, name, host.to(self.device, non_blocking=True))
+            setattr(self.z3.opt if self.z3 is not None else self.opt, name, host.to(self.device, non_blocking=True))
         self._parked = {}
-        if self.ops == "fused" and self.symm is None:
+        if self.ops == "fused" and self.symm is None and self.z3 is None:
             self.model.ensure_main_grad()
 
     # ------------------------------------------------------------------ SFT

@@ -59,7 +59,7 @@ class LlamaModel:
 
     def __init__(self, spec: ModelSpec, device="cpu", dtype=torch.float32, ops: str = "ref", seed: int = 0,
                  init: str = "normal", with_lm_head: bool = True, flat: torch.Tensor | None = None,
-                 gradient_checkpointing: bool = False):
+                 gradient_checkpointing: bool = False, sharded: bool = False):
         if ops not in ("ref", "fused"):
             raise ValueError("ops must be 'ref' or 'fused'")
         self.spec = spec
@@ -78,7 +78,13 @@ class LlamaModel:
 
             if not lib.available():
                 raise RuntimeError("ops='fused' needs a B200 (sm_100) device and libb200ops.so")
-        if flat is None:
+        self.zero3 = None  # parallel.zero3.Zero3State when the parameters are sharded over the ranks (fused path)
+        if sharded:
+            # no resident flat buffer: ``Zero3State.attach`` points ``p`` / ``g`` at its gather workspaces
+            if ops != "fused":
+                raise NotImplementedError("parameter sharding runs on the fused path")
+            self.flat, self.p = None, {}
+        elif flat is None:
             flat = torch.empty(self.layout.total, dtype=dtype, device=self.device)
             self.flat = flat
             self.init_weights(seed, init)
@@ -86,7 +92,8 @@ class LlamaModel:
             if flat.numel() < self.layout.total:
                 raise ValueError("flat buffer is smaller than the layout")
             self.flat = flat
-        self.p = self.layout.views(self.flat)
+        if not sharded:
+            self.p = self.layout.views(self.flat)
         self._last_qk = None
         self._rope_tab = None
         # keep the RMSNorm outputs and the SwiGLU activation for the backward pass instead of recomputing them
@@ -132,6 +139,8 @@ class LlamaModel:
         return self.p["embed"] if self.spec.tie_word_embeddings or "lm_head" not in self.p else self.p["lm_head"]
 
     def ensure_main_grad(self) -> torch.Tensor:
+        if self.zero3 is not None:
+            return None  # gradients live in the sharded state's workspaces
         if self.main_grad is None:
             self.main_grad = torch.zeros(self.flat.numel(), dtype=torch.float32, device=self.device)
             self.g = self.layout.views(self.main_grad)
@@ -192,6 +201,8 @@ class LlamaModel:
         if self.ops == "ref":
             return ref.linear(self._ref_hidden(input_ids, position_ids, cu_seqlens), self.lm_head_weight_ref())
         h, _ = self._fused_forward_hidden(input_ids, position_ids, cu_seqlens, keep=False)
+        if self.zero3 is not None:
+            self.zero3.head()
         return _fused().gemm(h, self.lm_head_weight())
 
     # ------------------------------------------------------------------ ref path
@@ -212,9 +223,10 @@ class LlamaModel:
             x = self._ref_layer(x, v, i, position_ids, cu_seqlens)
         return ref.rmsnorm(x, v["final_norm"], s.rms_norm_eps)
 
-    def _ref_layer(self, x, v, i, position_ids, cu_seqlens):
+    def ref_qkv(self, n1, v, i):
+        """QKV projection of the PyTorch path with the family's extras: Qwen2-style bias, Qwen3 / OLMo-2 per-head RMSNorm of
+        q and k (before RoPE)."""
         s = self.spec
-        n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
         qkv = ref.linear(n1, v[f"l{i}.wqkv"])
         if s.attention_bias:
             qkv = qkv + v[f"l{i}.bqkv"]
@@ -224,6 +236,12 @@ class LlamaModel:
             q = ref.rmsnorm(heads[:, : s.num_heads], v[f"l{i}.q_norm"], s.rms_norm_eps)
             k = ref.rmsnorm(heads[:, s.num_heads : s.num_heads + s.num_kv_heads], v[f"l{i}.k_norm"], s.rms_norm_eps)
             qkv = torch.cat([q, k, heads[:, s.num_heads + s.num_kv_heads :]], dim=1).reshape(T, -1)
+        return qkv
+
+    def _ref_layer(self, x, v, i, position_ids, cu_seqlens):
+        s = self.spec
+        n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
+        qkv = self.ref_qkv(n1, v, i)
         qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
         attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim)
         x = x + ref.linear(attn, v[f"l{i}.wo"])
@@ -245,9 +263,14 @@ class LlamaModel:
             # sequence parallel: this rank embeds and projects its contiguous chunk of the packed tokens
             lo, hi = self.sp.local_tokens(input_ids.numel())
             input_ids = input_ids[lo:hi]
+        z = self.zero3
+        if z is not None:
+            z.fwd_begin()
         stream = f.embedding_fwd(p["embed"], input_ids)
         delta = None  # pending residual contribution, added inside the next RMSNorm
         for i in range(s.num_layers):
+            if z is not None:
+                z.layer_fwd(i)  # layer i's parameters are in their workspace; the next layer's gather is under way
             n1, h_in, rstd1 = f.rmsnorm_fwd(delta if delta is not None else stream, p[f"l{i}.attn_norm"], s.rms_norm_eps,
                                             res=stream if delta is not None else None)
             qkv, attn, lse, attn_tok = self._attention_block(i, n1, pos, cu)
@@ -349,7 +372,10 @@ class LlamaModel:
         d_stream = f.rmsnorm_bwd(h_last, p["final_norm"], rstd_f, d_nf, None, g["final_norm"])
         del d_nf
         scale = s.head_dim ** -0.5
+        z = self.zero3
         for i in reversed(range(s.num_layers)):
+            if z is not None:
+                z.layer_bwd(i)
             st = stash[i]
             if st.qkv is None:
                 st = self._recompute_layer(i, st, pos, cu)
@@ -392,6 +418,8 @@ class LlamaModel:
             del dqkv
             d_stream = f.rmsnorm_bwd(st.h_in, p[f"l{i}.attn_norm"], st.rstd1, d_n1, d_mid, g[f"l{i}.attn_norm"])
             del d_n1, d_mid
+            if z is not None:
+                z.layer_bwd_done(i)  # this layer's weight gradients go to their owners while the next layer runs
         f.embedding_bwd(g["embed"], state["ids"], d_stream)
         state.clear()
 
@@ -423,6 +451,8 @@ class _FusedLogprobFn(torch.autograd.Function):
         if model.sp is not None:  # log-probs of this rank's chunk of the tokens
             lo, hi = model.sp.local_tokens(labels.numel())
             labels = labels[lo:hi].contiguous()
+        if model.zero3 is not None:
+            model.zero3.head()
         w = model.lm_head_weight()
         logits = f.gemm(nf, w)
         logp, lse, ent = f.logprob_fwd(logits, labels, temperature, want_entropy)

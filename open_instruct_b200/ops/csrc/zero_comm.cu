@@ -191,6 +191,58 @@ extern "C" int b200_symm_allreduce_scalar(const void* const* pad_ptrs, int rank,
   return static_cast<int>(cudaGetLastError());
 }
 
+// Parameter sharding (gather on use).  out[r * n + i] = shard_r[soff + i] for every rank r: each GPU PULLS the peers'
+// slices with 16-byte loads (its own slice is an ordinary local copy).  Parameters only change in the optimizer step,
+// which is fenced by barriers on both sides, so the gather itself needs no handshake.  n % 8 == 0, soff % 8 == 0 (bf16).
+__global__ void __launch_bounds__(256)
+allgather_pull_kernel(PeerPtrs shards, int world, long long soff, long long n, __nv_bfloat16* __restrict__ out) {
+  const long long nv = n / 8;
+  const long long total = nv * world;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / nv);
+    const long long j = i - r * nv;
+    const uint4 v = ld_volatile_u4(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.p[r]) + soff) + j);
+    reinterpret_cast<uint4*>(out)[i] = v;
+  }
+}
+
+// acc[i] += sum_r ws_r[lo + i]: the per-layer gradient reduction of the parameter-sharded learner (the owner reads its
+// slice of every rank's layer workspace, fixed rank order).  n % 4 == 0, lo % 4 == 0.
+__global__ void __launch_bounds__(256)
+reduce_scatter_add_kernel(PeerPtrs ws, int world, long long lo, long long n, float* __restrict__ acc) {
+  const long long nv = n / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 a = reinterpret_cast<float4*>(acc)[i];
+#pragma unroll 1
+    for (int r = 0; r < world; ++r) {
+      const uint4 u = ld_volatile_u4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ws.p[r]) + lo) + i);
+      a.x += __uint_as_float(u.x); a.y += __uint_as_float(u.y); a.z += __uint_as_float(u.z); a.w += __uint_as_float(u.w);
+    }
+    reinterpret_cast<float4*>(acc)[i] = a;
+  }
+}
+
+extern "C" int b200_allgather_pull(const void* const* shard_ptrs, int world, long long soff, long long n, void* out,
+                                   int ctas, void* stream) {
+  if (world > MAX_PEERS || n % 8 || soff % 8) return -1;
+  if (n == 0) return 0;
+  // a modest grid: the gather runs beside the layer's GEMMs on another stream and must not take the SMs from them
+  allgather_pull_kernel<<<ctas > 0 ? ctas : 32, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_ptrs(shard_ptrs, world), world, soff, n, reinterpret_cast<__nv_bfloat16*>(out));
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int b200_reduce_scatter_add(const void* const* ws_ptrs, int world, long long lo, long long n, float* acc,
+                                       int ctas, void* stream) {
+  if (world > MAX_PEERS || n % 4 || lo % 4) return -1;
+  if (n == 0) return 0;
+  reduce_scatter_add_kernel<<<ctas > 0 ? ctas : 32, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_ptrs(ws_ptrs, world), world, lo, n, acc);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // out_shard[n] = sum over ranks of grads_r[lo .. lo+n); sumsq[0] = |out_shard|^2 (overwritten).
 extern "C" int b200_zero_reduce_scatter(const void* const* grad_ptrs, const void* mc_grads, int rank, int world,
                                         long long lo, long long n, float* out_shard, float* sumsq, int use_multimem,

@@ -132,20 +132,25 @@ class ZeroOptimizer:
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()
-    def step(self, grad: torch.Tensor, lr: float | None = None, grad_scale: float = 1.0) -> torch.Tensor:
+    def step(self, grad: torch.Tensor, lr: float | None = None, grad_scale: float = 1.0,
+             norm_sq: torch.Tensor | None = None) -> torch.Tensor:
         """One optimizer step from the accumulated flat gradient.
 
         ``grad_scale`` multiplies the summed gradient before clipping (1 / accumulation steps,
         1 / world for mean-reduced losses).  Returns the global gradient norm (device scalar,
         after ``grad_scale``, before clipping).  The caller zeroes its gradient buffer afterwards
         (``zero_grad`` below does it for the shard it owns; the full buffer is the model's).
+        ``norm_sq`` (device scalar) replaces the squared gradient norm computed here: a caller that runs this
+        optimizer over rank-local buffers (parameter sharding) supplies the global value.
         """
         lr = self.lr if lr is None else lr
         self.step_count += 1
         fused_comm = self.comm == "fused" and self.world > 1
         gs = self._reduce_scatter(grad, grad_scale)
         # ---- global grad norm (of the summed gradient times grad_scale)
-        if fused_comm:
+        if norm_sq is not None:
+            self._norm_sq.copy_(norm_sq)
+        elif fused_comm:
             pass  # the reduce-scatter kernel already accumulated this rank's sum of squares
         elif self.use_kernels:
             from ..ops import fused
@@ -153,7 +158,7 @@ class ZeroOptimizer:
             fused.sumsq(gs, self._norm_sq)
         else:
             self._norm_sq.copy_(gs.double().pow(2).sum().float().reshape(1))
-        if self.world > 1 and not fused_comm:
+        if self.world > 1 and not fused_comm and norm_sq is None:
             dist.all_reduce(self._norm_sq, op=dist.ReduceOp.SUM, group=self.group)
         norm = self._norm_sq.sqrt() * grad_scale
         self.last_grad_norm = norm

@@ -206,8 +206,7 @@ def main(args: Args, tc: TokenizerConfig, model_config: ModelConfig) -> dict:
     learner = Learner(spec, cfg, device=device)
     src = model_config.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
-        load_hf_checkpoint(src, learner.model.flat.detach(), spec, strict=False)
-        learner.opt.master.copy_(learner.model.flat.detach()[learner.opt.lo:learner.opt.hi].float())
+        learner.load_hf(src)
     head = RewardHead(spec.hidden_size, device, args.learning_rate, args.eps, args.seed)
     loader = HFDataLoader(train, batch_size=args.micro_batch_size, seed=args.seed, dp_rank=rank, dp_world_size=world,
                           collator=pack_preference_batch, automatic_reshuffle=True)
@@ -249,8 +248,9 @@ def main(args: Args, tc: TokenizerConfig, model_config: ModelConfig) -> dict:
         if is_main:
             logger.info("step %d loss %.4f acc %.3f", step, last["train/rm/loss"], last["train/rm/accuracy"])
     pdist.barrier()
+    full_weights = learner.full_flat()  # a gather when the parameters are sharded: every rank takes part
     if is_main:
-        save_hf_checkpoint(learner.model.flat, spec, args.output_dir, tokenizer=tokenizer,
+        save_hf_checkpoint(full_weights, spec, args.output_dir, tokenizer=tokenizer,
                            extra_config={"architectures": ["LlamaForSequenceClassification"], "num_labels": 1})
         from safetensors.torch import save_file
 

@@ -363,7 +363,7 @@ class RolloutEngine:
         x = p["embed"][ids]
         for i in range(s.num_layers):
             n1 = ref.rmsnorm(x, p[f"l{i}.attn_norm"], s.rms_norm_eps)
-            qkv = ref.rope(ref.linear(n1, p[f"l{i}.wqkv"]), pos, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            qkv = ref.rope(self.model.ref_qkv(n1, p, i), pos, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
             heads = qkv.view(T, s.num_heads + 2 * s.num_kv_heads, s.head_dim)
             k_new, v_new = heads[:, s.num_heads : s.num_heads + s.num_kv_heads], heads[:, s.num_heads + s.num_kv_heads :]
             for rep in range(slots.numel() // T):

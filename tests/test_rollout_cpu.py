@@ -3,18 +3,28 @@
 import torch
 
 
-def _engine(**kw):
+import pytest
+
+
+def _engine(spec_kw=None, **kw):
     from open_instruct_b200.models import get_spec
     from open_instruct_b200.rollout.engine import RolloutEngine
 
-    spec = get_spec("tiny").replace(eos_token_id=3)
-    return RolloutEngine(spec, device="cpu", ops="ref", seed=1, **kw), spec
+    spec = get_spec("tiny").replace(eos_token_id=3, **(spec_kw or {}))
+    eng = RolloutEngine(spec, device="cpu", ops="ref", seed=1, **kw)
+    if spec_kw:  # biases start at zero and q/k norm weights at one: move them so that leaving them out would show
+        with torch.no_grad():
+            for name, v in eng.model.layout.views(eng.model.flat).items():
+                if name.endswith(("bqkv", "q_norm", "k_norm")):
+                    v.add_(0.3 * torch.randn(v.shape, generator=torch.Generator().manual_seed(5)))
+    return eng, spec
 
 
-def test_greedy_matches_full_forward():
+@pytest.mark.parametrize("family", [None, {"attention_bias": True, "model_type": "qwen2"}, {"qk_norm": True, "model_type": "qwen3"}])
+def test_greedy_matches_full_forward(family):
     from open_instruct_b200.data_types import SamplingConfig
 
-    eng, spec = _engine(num_blocks=64)
+    eng, spec = _engine(family, num_blocks=64)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(4, spec.vocab_size, (n,), generator=g).tolist() for n in (5, 70, 130)]
     res = eng.generate(prompts, SamplingConfig(temperature=0.0, max_tokens=12, n=1))

@@ -1,0 +1,37 @@
+"""Parameter sharding (ZeRO stage 3): the unit plan, and two gloo ranks against a resident single-process optimizer."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+
+from open_instruct_b200.models import get_spec
+from open_instruct_b200.models.spec import ParamLayout
+from open_instruct_b200.parallel.zero3 import plan_units
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_unit_plan_covers_the_decay_region():
+    spec = get_spec("llama3.1-8b")
+    layout = ParamLayout(spec)
+    for world in (1, 2, 8):
+        units, n_shard = plan_units(layout, world)
+        assert [u.name for u in units] == ["embed"] + [f"l{i}" for i in range(32)] + ["lm_head"]
+        assert units[0].start == 0 and units[-1].start + units[-1].size == layout.decay_end
+        for a, b in zip(units, units[1:]):
+            assert a.start + a.size == b.start and a.soff + a.shard == b.soff
+        assert all(u.shard % 128 == 0 and u.shard * world >= u.size for u in units)
+        assert n_shard * world < layout.decay_end + 34 * 128 * world  # padding only
+        layer = units[1]
+        assert layer.size == 218_103_808 and not layer.pinned and units[0].pinned and units[-1].pinned
+
+
+@pytest.mark.parametrize("world,tied", [(2, "0"), (3, "1")])
+def test_sharded_state_matches_resident_optimizer(world, tied):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29670 + world), os.path.join(HERE, "_zero3_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env={**os.environ, "TIED": tied})
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count("ZERO3_OK") == world
