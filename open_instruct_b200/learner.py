@@ -43,6 +43,9 @@ class LearnerConfig:
     sp_max_tokens: int = 8192         # largest packed micro-batch (all ranks together) the exchange buffers hold
     # Parameter sharding (ZeRO stage 3): None = only when the resident design does not fit this GPU (``needs_sharding``)
     shard_parameters: bool | None = None
+    # Hybrid sharding: parameters are split over groups of this many consecutive ranks and replicated across the groups
+    # (gradient shards summed between the groups once per step).  None = one shard group spanning all ranks.
+    shard_degree: int | None = None
 
 
 def needs_sharding(total_params: int, world: int, hbm_bytes: int, offload_optimizer: bool = False) -> bool:
@@ -88,7 +91,10 @@ class Learner:
 
             self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, sharded=True,
                                     gradient_checkpointing=cfg.gradient_checkpointing)
-            self.z3 = Zero3State(layout, self.device, dtype, group, comm="peer" if comm == "fused" else "nccl", lr=cfg.learning_rate,
+            shard_group, replica_group = group, None
+            if cfg.shard_degree and cfg.shard_degree != self.world:
+                shard_group, replica_group = pdist.hsdp_groups(cfg.shard_degree)
+            self.z3 = Zero3State(layout, self.device, dtype, shard_group, replica_group=replica_group, comm="peer" if comm == "fused" else "nccl", lr=cfg.learning_rate,
                                  betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
                                  use_kernels=True, offload=cfg.offload_optimizer)
             if flat_init is not None:

@@ -95,6 +95,28 @@ def broadcast_object(obj, src: int = 0, group=None):
     return box[0]
 
 
+def hsdp_groups(shard_degree: int):
+    """Split the default group into shard groups of ``shard_degree`` consecutive ranks and replica groups of the ranks
+    that hold the same slice (hybrid sharding: ``DataParallelType.hsdp`` with ``shard_degree`` / ``num_replicas`` in the
+    reference's olmo-core path, ``open_instruct/dpo.py:270-277``).  Returns ``(shard_group, replica_group)`` of this rank;
+    every rank must call it (``new_group`` is collective)."""
+    world, me = world_size(), rank()
+    if shard_degree <= 0 or world % shard_degree:
+        raise ValueError(f"shard_degree {shard_degree} must divide the world size {world}")
+    shard_group = replica_group = None
+    for s0 in range(0, world, shard_degree):
+        ranks = list(range(s0, s0 + shard_degree))
+        g = dist.new_group(ranks)
+        if me in ranks:
+            shard_group = g
+    for r0 in range(shard_degree):
+        ranks = list(range(r0, world, shard_degree))
+        g = dist.new_group(ranks)
+        if me in ranks:
+            replica_group = g
+    return shard_group, replica_group
+
+
 def destroy() -> None:
     if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()

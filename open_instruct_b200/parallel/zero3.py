@@ -71,8 +71,12 @@ class Zero3State:
 
     def __init__(self, layout, device, dtype, group=None, comm: str = "auto", lr: float = 1e-5, betas=(0.9, 0.999),
                  eps: float = 1e-8, weight_decay: float = 0.0, max_grad_norm: float | None = None, use_kernels: bool | None = None,
-                 offload: bool = False, peer_timeout_ms: int = 20000):
+                 offload: bool = False, peer_timeout_ms: int = 20000, replica_group=None):
+        # ``group`` is the SHARD group (its ranks split every unit); ``replica_group`` holds the ranks of other shard
+        # groups that own the same slices (hybrid sharding): their gradient shards are summed once per optimizer step.
         self.layout, self.device, self.dtype, self.group = layout, torch.device(device), dtype, group
+        self.replica_group = replica_group
+        self.replicas = pdist.world_size(replica_group) if replica_group is not None else 1
         self.world, self.rank = pdist.world_size(group), pdist.rank(group)
         cuda = self.device.type == "cuda"
         if comm == "auto":
@@ -327,6 +331,8 @@ class Zero3State:
         tail = self.grad_local[self.n_shard:self.n_local]
         if self.world > 1:
             dist.all_reduce(tail, op=dist.ReduceOp.SUM, group=self.group)
+        if self.replicas > 1:  # the other shard groups' contributions to my slices (and to the tail), once per step
+            dist.all_reduce(self.grad_local[:self.n_local], op=dist.ReduceOp.SUM, group=self.replica_group)
         sharded = self.grad_local[:self.n_shard]
         if self.opt.use_kernels:
             from ..ops import fused

@@ -36,7 +36,13 @@ def main():
         full[e.offset + e.numel:(e.offset + e.numel + 127) // 128 * 128] = 0
     hyper = dict(lr=1e-2, weight_decay=0.1, max_grad_norm=0.5)
 
-    z = Zero3State(layout, device, torch.float32, use_kernels=False, **hyper)
+    shard_degree = int(os.environ.get("SHARD_DEGREE", "0"))
+    groups = {}
+    if shard_degree:  # hybrid: shard groups of ``shard_degree`` ranks, replicated world / shard_degree times
+        sg, rg = pdist.hsdp_groups(shard_degree)
+        groups = dict(group=sg, replica_group=rg)
+    z = Zero3State(layout, device, torch.float32, use_kernels=False, **hyper, **groups)
+    assert z.world == (shard_degree or world)
     z.load_full(full)
     model = types.SimpleNamespace()
     z.attach(model)

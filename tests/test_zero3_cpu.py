@@ -28,10 +28,10 @@ def test_unit_plan_covers_the_decay_region():
         assert layer.size == 218_103_808 and not layer.pinned and units[0].pinned and units[-1].pinned
 
 
-@pytest.mark.parametrize("world,tied", [(2, "0"), (3, "1")])
-def test_sharded_state_matches_resident_optimizer(world, tied):
+@pytest.mark.parametrize("world,tied,shard_degree", [(2, "0", "0"), (3, "1", "0"), (4, "0", "2")])
+def test_sharded_state_matches_resident_optimizer(world, tied, shard_degree):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(29670 + world), os.path.join(HERE, "_zero3_worker.py")]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env={**os.environ, "TIED": tied})
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env={**os.environ, "TIED": tied, "SHARD_DEGREE": shard_degree})
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("ZERO3_OK") == world
