@@ -373,6 +373,9 @@ class LlamaModel:
         del d_nf
         scale = s.head_dim ** -0.5
         z = self.zero3
+        # sharded parameters: a layer's gradient workspace is written once per micro-batch and reduced right away, so the
+        # weight-gradient GEMMs overwrite it (no zeroing pass, no read in the epilogue); otherwise they accumulate
+        wgrad_mode = f.OUT_F32 if z is not None else f.OUT_F32_ACC
         for i in reversed(range(s.num_layers)):
             if z is not None:
                 z.layer_bwd(i)
@@ -383,14 +386,14 @@ class LlamaModel:
             # ---- MLP: out = h_mid + down(swiglu(gate_up(norm(h_mid))))
             act = st.act if st.act is not None else f.swiglu_fwd(st.gate_up)
             st.act = None
-            f.gemm(d_stream, act, g[f"l{i}.w_down"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            f.gemm(d_stream, act, g[f"l{i}.w_down"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
             d_act = f.gemm(d_stream, p[f"l{i}.w_down"], b_mn=True)
             del act
             dgu = f.swiglu_bwd_(st.gate_up, d_act)
             del d_act
             n2 = st.n2 if st.n2 is not None else f.rmsnorm_fwd(st.h_mid, p[f"l{i}.mlp_norm"], s.rms_norm_eps)[0]
             st.n2 = None
-            f.gemm(dgu, n2, g[f"l{i}.w_gate_up"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            f.gemm(dgu, n2, g[f"l{i}.w_gate_up"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
             del n2
             d_n2 = f.gemm(dgu, p[f"l{i}.w_gate_up"], b_mn=True)
             del dgu
@@ -398,7 +401,7 @@ class LlamaModel:
             del d_n2, d_stream
             # ---- attention: h_mid = h_in + wo(attn(rope(wqkv(norm(h_in)))))
             sp = self.sp
-            f.gemm(d_mid, st.attn_tok if sp is not None else st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            f.gemm(d_mid, st.attn_tok if sp is not None else st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
             if sp is None:
                 d_attn = f.gemm(d_mid, p[f"l{i}.wo"], b_mn=True)
                 dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
@@ -412,7 +415,7 @@ class LlamaModel:
                 dqkv = sp.dqkv_exchange(dqkv_heads)
             n1 = st.n1 if st.n1 is not None else f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)[0]
             st.n1 = None
-            f.gemm(dqkv, n1, g[f"l{i}.wqkv"], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            f.gemm(dqkv, n1, g[f"l{i}.wqkv"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
             del n1
             d_n1 = f.gemm(dqkv, p[f"l{i}.wqkv"], b_mn=True)
             del dqkv

@@ -196,14 +196,28 @@ extern "C" int b200_symm_allreduce_scalar(const void* const* pad_ptrs, int rank,
 // which is fenced by barriers on both sides, so the gather itself needs no handshake.  n % 8 == 0, soff % 8 == 0 (bf16).
 __global__ void __launch_bounds__(256)
 allgather_pull_kernel(PeerPtrs shards, int world, long long soff, long long n, __nv_bfloat16* __restrict__ out) {
+  // 8 independent 16-byte loads per thread per round: a peer load takes a few microseconds over NVLink, so the
+  // bandwidth is (bytes in flight) / latency and one load per thread would leave the link idle
+  constexpr int U = 8;
   const long long nv = n / 8;
   const long long total = nv * world;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / nv);
-    const long long j = i - r * nv;
-    const uint4 v = ld_volatile_u4(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.p[r]) + soff) + j);
-    reinterpret_cast<uint4*>(out)[i] = v;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int r = static_cast<int>(i / nv);
+        const long long j = i - r * nv;
+        v[u] = ld_volatile_u4(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.p[r]) + soff) + j);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) reinterpret_cast<uint4*>(out)[i] = v[u];
+    }
   }
 }
 
@@ -211,17 +225,54 @@ allgather_pull_kernel(PeerPtrs shards, int world, long long soff, long long n, _
 // slice of every rank's layer workspace, fixed rank order).  n % 4 == 0, lo % 4 == 0.
 __global__ void __launch_bounds__(256)
 reduce_scatter_add_kernel(PeerPtrs ws, int world, long long lo, long long n, float* __restrict__ acc) {
+  constexpr int U = 4;
   const long long nv = n / 4;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float4 a = reinterpret_cast<float4*>(acc)[i];
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nv; i0 += stride * U) {
+    float4 a[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      a[u] = i < nv ? reinterpret_cast<const float4*>(acc)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 #pragma unroll 1
     for (int r = 0; r < world; ++r) {
-      const uint4 u = ld_volatile_u4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ws.p[r]) + lo) + i);
-      a.x += __uint_as_float(u.x); a.y += __uint_as_float(u.y); a.z += __uint_as_float(u.z); a.w += __uint_as_float(u.w);
+      uint4 x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nv) x[u] = ld_volatile_u4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ws.p[r]) + lo) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nv) {
+          a[u].x += __uint_as_float(x[u].x); a[u].y += __uint_as_float(x[u].y);
+          a[u].z += __uint_as_float(x[u].z); a[u].w += __uint_as_float(x[u].w);
+        }
+      }
     }
-    reinterpret_cast<float4*>(acc)[i] = a;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nv) reinterpret_cast<float4*>(acc)[i] = a[u];
+    }
   }
+}
+
+// The same gather by the copy engines: one peer-to-peer copy per rank, no SM involved, so the layer's GEMMs keep the
+// whole GPU.  `elem` = bytes per element.
+extern "C" int b200_allgather_copy(const void* const* shard_ptrs, int world, long long soff, long long n, int elem,
+                                   void* out, void* stream) {
+  if (world > MAX_PEERS) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  for (int r = 0; r < world; ++r) {
+    const char* src = reinterpret_cast<const char*>(shard_ptrs[r]) + soff * elem;
+    cudaError_t e = cudaMemcpyAsync(reinterpret_cast<char*>(out) + static_cast<long long>(r) * n * elem, src,
+                                    static_cast<size_t>(n) * elem, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return 0;
 }
 
 extern "C" int b200_allgather_pull(const void* const* shard_ptrs, int world, long long soff, long long n, void* out,

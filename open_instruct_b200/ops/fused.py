@@ -14,9 +14,11 @@ from .lib import call, ptr, status_word, stream_ptr
 
 import os
 
-OUT_BF16, OUT_F32, OUT_F32_ACC = 0, 1, 2
+OUT_BF16, OUT_F32, OUT_F32_ACC, OUT_F32_RED = 0, 1, 2, 3  # RED: accumulate with red.global.add (CTA-pair kernel only)
 # "2cta": tcgen05 cta_group::2 kernel on CTA pairs (256x256 tiles); "1cta": one CTA per 128x256 tile
 GEMM_IMPL = os.environ.get("B200_GEMM_IMPL", "2cta")
+# fp32 accumulation of the CTA-pair GEMM through 16-byte `red.global.add` instead of load + add + store
+WGRAD_RED = os.environ.get("B200_WGRAD_RED", "0") == "1"
 
 
 def _check(t: torch.Tensor, dtype, name: str):
@@ -54,7 +56,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a
         raise ValueError("gemm row strides must be multiples of 8 elements (TMA 16-byte rule)")
     odt = torch.bfloat16 if out_mode == OUT_BF16 else torch.float32
     if out is None:
-        if out_mode == OUT_F32_ACC:
+        if out_mode in (OUT_F32_ACC, OUT_F32_RED):
             raise ValueError("accumulate mode needs an output tensor")
         out = torch.empty(M, N, dtype=odt, device=a.device)
     else:
@@ -65,6 +67,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a
     if ldc % 8 and N >= 8:
         raise ValueError("gemm output row stride must be a multiple of 8 elements")
     impl = impl or GEMM_IMPL
+    if out_mode == OUT_F32_RED and impl != "2cta":
+        raise ValueError("OUT_F32_RED is a mode of the CTA-pair kernel")
     if impl in ("skinny", "skinny128"):
         # 128 x 64 tiles: for small M, where the GEMM is a stream over the weights and needs many CTAs pulling on HBM
         if a_mn or b_mn or out_mode != OUT_BF16:
@@ -73,7 +77,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, a
              64 if impl == "skinny" else 128)
         return out
     call("b200_gemm2_bf16" if impl == "2cta" else "b200_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, lda, ldb, ldc,
-         int(a_mn), int(b_mn), out_mode,
+         int(a_mn), int(b_mn), 3 if (out_mode == OUT_F32_ACC and WGRAD_RED and impl == "2cta") else out_mode,
          ptr(status_word(a.device)), stream_ptr(), max_ctas)
     return out
 

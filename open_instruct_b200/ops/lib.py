@@ -143,7 +143,7 @@ def check_status(sync: bool = True) -> None:
 
 
 # kernels launched per library call (for launch accounting in benchmarks)
-_KERNELS_PER_CALL = {"b200_attn_bwd": 3, "b200_rmsnorm_bwd": 2, "b200_sumsq": 2}
+_KERNELS_PER_CALL = {"b200_attn_bwd": 3, "b200_rmsnorm_bwd": 2, "b200_sumsq": 2, "b200_allgather_copy": 0}
 launch_count = 0
 
 

@@ -293,16 +293,11 @@ class Zero3State:
     def layer_bwd(self, i: int) -> None:
         self._want(i, i - 1)
         k = i & 1
-        # the reduction that last read this gradient workspace has finished.  With peer reads the OTHER ranks' reductions
-        # of that workspace must have finished too: the barrier that opens the following reduction (of the other
-        # workspace) says so, hence the wait on that one.
-        kk = k if self.peer is None else k ^ 1
-        if self._ev_r[kk] is not None:
-            self._main().wait_event(self._ev_r[kk])
+        # the reduction that last read this gradient workspace has finished - on every rank: the peer transport closes each
+        # reduction with a barrier.  The weight-gradient GEMMs then overwrite the workspace (no zeroing needed).
         if self._ev_r[k] is not None:
             self._main().wait_event(self._ev_r[k])
             self._ev_r[k] = None
-        self.gws[k].zero_()
 
     def layer_bwd_done(self, i: int) -> None:
         k, u = i & 1, self.layers[i]

@@ -27,6 +27,7 @@ _PP = ctypes.POINTER(ctypes.c_void_p)
 lib._SIGNATURES.update({
     "b200_allgather_pull": [_PP, _I, _L, _L, _P, _I, _P],
     "b200_reduce_scatter_add": [_PP, _I, _L, _L, _P, _I, _P],
+    "b200_allgather_copy": [_PP, _I, _L, _L, _I, _P, _P],
 })
 
 
@@ -53,10 +54,12 @@ class PeerComm:
         self._handles = hs
         self._epoch = 0
         # CTAs of the two transport kernels: they run beside the layer's GEMMs, so they get a slice of the SMs only
-        self.gather_ctas = int(os.environ.get("B200_Z3_GATHER_CTAS", "32"))
-        self.reduce_ctas = int(os.environ.get("B200_Z3_REDUCE_CTAS", "32"))
+        # the gather goes through the copy engines by default ("ce": no SM taken from the GEMMs); "sm" = the pull kernel
+        self.gather_mode = os.environ.get("B200_Z3_GATHER", "ce")
+        self.gather_ctas = int(os.environ.get("B200_Z3_GATHER_CTAS", "64"))
+        self.reduce_ctas = int(os.environ.get("B200_Z3_REDUCE_CTAS", "16"))  # has a whole layer's backward to finish
         lib.load_ops()
-        for name in ("b200_symm_barrier", "b200_allgather_pull", "b200_reduce_scatter_add"):
+        for name in ("b200_symm_barrier", "b200_allgather_pull", "b200_reduce_scatter_add", "b200_allgather_copy"):
             fn = getattr(lib.load_ops(), name)
             fn.argtypes = lib._SIGNATURES[name]
             fn.restype = ctypes.c_int
@@ -70,8 +73,12 @@ class PeerComm:
                  ptr(status_word(self.device)), stream_ptr())
 
     def all_gather(self, out: torch.Tensor, soff: int, n: int) -> None:
-        lib.call("b200_allgather_pull", self._shard_ptrs, self.world, soff, n, ptr(out), self.gather_ctas, stream_ptr())
+        if self.gather_mode == "ce":
+            lib.call("b200_allgather_copy", self._shard_ptrs, self.world, soff, n, 2, ptr(out), stream_ptr())
+        else:
+            lib.call("b200_allgather_pull", self._shard_ptrs, self.world, soff, n, ptr(out), self.gather_ctas, stream_ptr())
 
     def reduce_scatter_add(self, slot: int, n: int, acc: torch.Tensor) -> None:
-        self.barrier()
+        self.barrier()  # every rank has finished writing this workspace
         lib.call("b200_reduce_scatter_add", self._ws_ptrs[slot], self.world, self.rank * n, n, ptr(acc), self.reduce_ctas, stream_ptr())
+        self.barrier()  # every rank has finished reading it: whoever waits on this stream may overwrite its copy

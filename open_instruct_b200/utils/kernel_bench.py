@@ -95,6 +95,8 @@ def main():
             rec(f"gemm_dgrad_{name}", time_op(lambda: fused.gemm(dy, w, b_mn=True, impl=args.impl), args.iters), fl)
             g = torch.zeros(N, K, device="cuda")
             rec(f"gemm_wgrad_{name}", time_op(lambda: fused.gemm(dy, x, g, a_mn=True, b_mn=True, out_mode=fused.OUT_F32_ACC, impl=args.impl), args.iters), fl)
+            if args.impl in (None, "2cta"):
+                rec(f"gemm_wgrad_red_{name}", time_op(lambda: fused.gemm(dy, x, g, a_mn=True, b_mn=True, out_mode=fused.OUT_F32_RED, impl=args.impl), args.iters), fl)
             if args.cublas:
                 rec(f"cublas_fwd_{name}", time_op(lambda: torch.matmul(x, w.t()), args.iters), fl)
                 rec(f"cublas_dgrad_{name}", time_op(lambda: torch.matmul(dy, w), args.iters), fl)

@@ -72,7 +72,11 @@ def main():
                 z.layer_bwd(i)
                 for leaf in ("wqkv", "wo", "w_gate_up", "w_down", "attn_norm", "mlp_norm"):
                     assert close(model.p[f"l{i}.{leaf}"], rv[f"l{i}.{leaf}"]), (step, mb, i, leaf, "bwd")
-                    model.g[f"l{i}.{leaf}"] += synthetic_grad(model.p[f"l{i}.{leaf}"], rank, mb)
+                    gr = synthetic_grad(model.p[f"l{i}.{leaf}"], rank, mb)
+                    if leaf.endswith("norm"):
+                        model.g[f"l{i}.{leaf}"] += gr      # replicated tail: accumulates until the step
+                    else:
+                        model.g[f"l{i}.{leaf}"].copy_(gr)  # layer workspace: overwritten per micro-batch, reduced right away
                 z.layer_bwd_done(i)
             model.g["embed"] += 0.5 * synthetic_grad(model.p["embed"], rank, mb)
             for r in range(world):  # what every rank contributed

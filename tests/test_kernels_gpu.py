@@ -40,6 +40,10 @@ def test_gemm_layouts(a_mn, b_mn, shape, impl):
     acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
     fused.gemm(a_in, b_in, acc, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32_ACC, impl=impl)
     assert _rel(acc, ref + 1) < 1e-4
+    if impl == "2cta":  # the same accumulation through red.global.add
+        acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+        fused.gemm(a_in, b_in, acc, a_mn=a_mn, b_mn=b_mn, out_mode=fused.OUT_F32_RED, impl=impl)
+        assert _rel(acc, ref + 1) < 1e-4
 
 
 @pytest.mark.parametrize("shape", [(1, 512, 128), (37, 200, 72), (256, 4096, 4096), (300, 6144, 1024), (512, 4096, 14336)])
