@@ -241,6 +241,8 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                       wandb_entity=args.wandb_entity, enabled=is_main)
 
     lora = None
+    if args.use_lora and learner.z3 is not None:
+        raise NotImplementedError("LoRA adapters need the resident parameter copy; run with shard_parameters false")
     if args.use_lora:
         from .models.lora import LoRATrainer
 

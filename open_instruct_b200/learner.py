@@ -51,7 +51,8 @@ class LearnerConfig:
 def needs_sharding(total_params: int, world: int, hbm_bytes: int, offload_optimizer: bool = False) -> bool:
     """True when bf16 parameters + the fp32 gradient accumulator resident on every GPU, plus this rank's share of the fp32
     master weights and Adam moments, would take more than 70 % of the GPU's memory (the rest is for activations)."""
-    resident = 6 * total_params + (0 if offload_optimizer else 12 * total_params // max(world, 1)) + 4 * total_params // max(world, 1)
+    world = max(world, 1)
+    resident = 6 * total_params + (0 if offload_optimizer else 12 * total_params // world) + (4 * total_params // world if world > 1 else 0)
     return resident > 0.7 * hbm_bytes
 
 

@@ -139,6 +139,12 @@ PRESETS: dict[str, ModelSpec] = {
     "qwen2.5-7b": ModelSpec(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_layers=28, num_heads=28,
                             num_kv_heads=4, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, attention_bias=True,
                             model_type="qwen2", max_position_embeddings=32768),
+    "qwen2.5-14b": ModelSpec(vocab_size=152064, hidden_size=5120, intermediate_size=13824, num_layers=48, num_heads=40,
+                             num_kv_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, attention_bias=True,
+                             model_type="qwen2", max_position_embeddings=32768),
+    "qwen2.5-32b": ModelSpec(vocab_size=152064, hidden_size=5120, intermediate_size=27648, num_layers=64, num_heads=40,
+                             num_kv_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, attention_bias=True,
+                             model_type="qwen2", max_position_embeddings=32768),
     "qwen3-0.6b": ModelSpec(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_layers=28, num_heads=16,
                             num_kv_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True,
                             model_type="qwen3", tie_word_embeddings=True, max_position_embeddings=40960),

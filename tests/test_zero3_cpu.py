@@ -35,3 +35,13 @@ def test_sharded_state_matches_resident_optimizer(world, tied, shard_degree):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env={**os.environ, "TIED": tied, "SHARD_DEGREE": shard_degree})
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("ZERO3_OK") == world
+
+
+def test_sharding_policy():
+    from open_instruct_b200.learner import needs_sharding
+
+    hbm = 192 * 10**9
+    total = {n: ParamLayout(get_spec(n)).total for n in ("llama3.1-8b", "qwen2.5-14b", "llama3.1-70b")}
+    assert not any(needs_sharding(total["llama3.1-8b"], w, hbm) for w in (2, 4, 8))   # the headline config stays resident
+    assert needs_sharding(total["qwen2.5-14b"], 2, hbm) and not needs_sharding(total["qwen2.5-14b"], 8, hbm)
+    assert all(needs_sharding(total["llama3.1-70b"], w, hbm, offload_optimizer=True) for w in (2, 4, 8))
