@@ -144,14 +144,25 @@ class GRPOExperimentConfig(ExperimentConfig):
 
 # ---------------------------------------------------------------------------------- small helpers
 def masked_mean(values: torch.Tensor, mask: torch.Tensor, axis: int | None = None, denominator: float | None = None) -> torch.Tensor:
-    """Mean of ``values`` where ``mask``; 0 for an empty mask (``open_instruct/rl_utils.py:426-448``).
-    With ``denominator`` the masked SUM is divided by it instead (token-normalised losses)."""
+    """Mean of ``values`` where ``mask`` (``open_instruct/rl_utils.py:426-448``).
+
+    ``values`` may carry leading dimensions the mask does not have (e.g. four KL estimators stacked over one mask): the
+    result keeps them.  ``axis=None``: one mean over all masked elements.  ``axis=k``: a masked mean along mask dimension
+    ``k`` for every row, then the plain mean of those (sample-level averaging).  An empty mask (or empty row) gives 0, not
+    NaN.  With ``denominator`` the masked SUM is divided by it instead (token-normalised losses)."""
     m = mask.to(values.dtype)
-    num = (values * m).sum(axis) if axis is not None else (values * m).sum()
+    extra = values.ndim - m.ndim
+    if axis is None:
+        dims = tuple(range(extra, values.ndim))
+    else:
+        dims = axis + extra if axis >= 0 else axis
+    num = (values * m).sum(dim=dims)
     if denominator is not None:
-        return num / denominator
-    den = m.sum(axis) if axis is not None else m.sum()
-    return num / den.clamp(min=1)
+        res = num / denominator if denominator > 0 else torch.zeros_like(num)
+    else:
+        den = m.sum(dim=axis) if axis is not None else m.sum()
+        res = torch.where(den > 0, num / den.clamp(min=1e-30), torch.zeros_like(num))
+    return res.flatten(extra).mean(-1) if res.ndim > extra else res
 
 
 def estimate_kl(ref_logprobs_diff: torch.Tensor, ratio: torch.Tensor) -> torch.Tensor:
