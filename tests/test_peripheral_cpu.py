@@ -365,3 +365,73 @@ def test_entry_point_help(module):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, "-m", f"open_instruct_b200.{module}", "--help"], capture_output=True, text=True, timeout=180, cwd=root)
     assert res.returncode == 0 and "--" in res.stdout, res.stderr[-1500:]
+
+
+def test_human_eval_app_and_metrics(tmp_path):
+    from fastapi.testclient import TestClient
+
+    from open_instruct_b200.human_eval.app import create_app, export_records
+    from open_instruct_b200.human_eval.metrics import comparison_results
+
+    inst = [{"id": f"q{i}", "prompt": f"prompt {i}", "completions": [{"model": "m1", "completion": f"a{i}"}, {"model": "m2", "completion": f"b{i}"}]}
+            for i in range(3)]
+    db = str(tmp_path / "he.sqlite3")
+    c = TestClient(create_app(inst, db, seed=0))
+    assert c.get("/summary").status_code == 401
+    assert c.post("/signup", json={"username": "ann", "password": "pw"}).status_code == 200
+    assert c.post("/signup", json={"username": "ann", "password": "x"}).status_code == 409
+    assert c.post("/login", json={"username": "ann", "password": "bad"}).status_code == 401
+    out = c.get("/api/model-outputs/1").json()
+    assert out["prompt"] == "prompt 1" and {x["model"] for x in out["completions"]} == {"m1", "m2"}
+    assert "error" in c.get("/api/model-outputs/9").json()
+    assert "Instance 2" in c.get("/instances/2").text
+
+    def judge(i, a, b, pref, acc_a="yes", acc_b="no"):
+        r = c.post("/api/submit-evaluation", json={"index": i, "prompt": inst[i]["prompt"], "model_a": a, "model_b": b, "completion_a": "x",
+                                                   "completion_b": "y", "completion_a_is_acceptable": acc_a, "completion_b_is_acceptable": acc_b,
+                                                   "preference": pref})
+        assert r.status_code == 200
+
+    judge(0, "m1", "m2", "a-is-better")
+    judge(0, "m2", "m1", "b-is-slightly-better", "no", "yes")   # second annotation of q0, sides swapped: m1 again
+    judge(1, "m1", "m2", "tie")
+    judge(1, "m1", "m2", "b-is-better")                         # tie vs preference: half an agreement
+    judge(2, "m2", "m1", "a-is-better", "yes", "yes")
+    assert c.post("/api/submit-feedback", json={"index": 2, "prompt": "p", "model_a": "m1", "model_b": "m2", "completion_a": "x",
+                                                "completion_b": "y", "instance_quality": "bad", "comment": "unclear"}).status_code == 200
+    s = c.get("/summary").json()
+    assert s["user_contributions"] == {"ann": 5, "all": 5} and s["progress"]["missing_indices"] == []
+    res = s["results"]["m1_vs_m2"]
+    cmp_ = res["comparison_results"]
+    assert cmp_["m1_wins"] == pytest.approx(1 / 3) and cmp_["m2_wins"] == pytest.approx(2 / 3)
+    assert cmp_["agreement"] == {"num_instances_with_multiple_annotations": 2, "comparison_agreement": 0.5, "relaxed_comparison_agreement": 0.75}
+    assert res["acceptance_results"]["m1"] == pytest.approx(1.0) and res["acceptance_results"]["m2"] == pytest.approx(1 / 3)
+    assert res["feedback_records"] == {"bad": [2]}
+    assert comparison_results([], "m1", "m2")["m1_wins"] == 0
+    assert export_records(db, str(tmp_path / "out.jsonl")) == 6 and export_records(db, str(tmp_path / "out.csv")) == 6
+
+
+def test_dataset_builders(tmp_path):
+    from open_instruct_b200.data import builders
+    from open_instruct_b200.data.synthetic import make_byte_tokenizer
+    from transformers import AutoTokenizer
+
+    rows = [{"question": "2+2?", "answer": "It is 4.\n#### 4"}, {"question": "big?", "answer": "a lot\n#### 1,234.5"}]
+    assert builders.qa_to_messages(rows)[0]["messages"][1] == {"role": "assistant", "content": "It is 4.\n#### 4"}
+    rl = builders.gsm8k_to_rlvr(rows)
+    assert [r["ground_truth"] for r in rl] == ["4", "1234.5"] and rl[0]["dataset"] == "gsm8k" and len(rl[0]["messages"]) == 1
+    c = builders.counter_env_samples(12)
+    assert c[10]["ground_truth"] == "1" and c[9]["env_config"] == {"env_configs": [{"env_name": "counter", "target": "10"}]}
+    g = builders.guess_number_env_samples(3, nothink=True)
+    assert g[2]["env_config"]["env_configs"][0] == {"env_name": "guess_number", "number": "3"} and g[0]["messages"][1]["content"].endswith("/nothink")
+    tok = AutoTokenizer.from_pretrained(make_byte_tokenizer(str(tmp_path / "tok")))
+    data = [{"id": f"r{i}", "messages": [{"role": "system", "content": "s"}, {"role": "user", "content": "u" * (10 * (i + 1))},
+                                         {"role": "assistant", "content": "a" * 5}]} for i in range(4)]
+    st = builders.messages_statistics(data, tok)
+    assert st["num_instances"] == 4 and st["turns_summary"]["mean"] == 2.0 and st["assistant_response_lengths_summary"]["max"] == 5.0
+    assert st["total_lengths_summary"]["max"] == 45.0 and st["top_100_longest_instances"][0] == "r3"
+    assert st["num_instances_with_total_length_gt_512"] == 0
+    h = builders.token_length_histogram([{"text": "x" * n} for n in (3, 9, 17)], tok, "text", bucket=8)
+    assert h["counts"] == [1, 1, 1] and h["edges"] == [0, 8, 16, 24]
+    builders.main(["env", "--kind", "counter", "--num", "5", "--out", str(tmp_path / "c.jsonl")])
+    assert len(builders.read_jsonl(str(tmp_path / "c.jsonl"))) == 5

@@ -90,3 +90,15 @@ def test_masked_mean_vectors():
     assert torch.allclose(got, torch.tensor([2.75, 27.5, 275.0, 2750.0]))
     got = rl_utils.masked_mean(stacked, m)
     assert torch.allclose(got, torch.tensor([7 / 3, 70 / 3, 700 / 3, 7000 / 3]))
+
+
+def test_packed_batch_logps_vectors():
+    """The per-sequence aggregation of ``open_instruct/test_dpo_utils.py`` (average: a fully masked row gives 0, not NaN),
+    restated for packed rows with shifted labels."""
+    from open_instruct_b200.data.collate import get_batch_logps
+
+    lp = torch.tensor([-1.0, -2, -3, -4, -1, -2, -3, -4, -1, -2, -3, -4])
+    shifted = torch.tensor([1, 2, 3, -100, -100, -100, -100, -100, 1, 2, -100, -100])
+    cu = torch.tensor([0, 4, 8, 12])
+    assert get_batch_logps(lp, shifted, cu, True).tolist() == [-2.0, 0.0, -1.5]
+    assert get_batch_logps(lp, shifted, cu, False).tolist() == [-6.0, 0.0, -3.0]
