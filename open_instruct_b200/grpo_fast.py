@@ -520,17 +520,21 @@ class LearnerWorker:
         cfg = LearnerConfig(ops=args.ops, comm=args.comm_backend, learning_rate=args.learning_rate, weight_decay=args.weight_decay,
                             max_grad_norm=args.max_grad_norm, lr_scheduler_type=args.lr_scheduler_type, warmup_steps=warm,
                             total_steps=max(1, num_training_steps * args.num_epochs * args.num_mini_batches),
-                            gradient_checkpointing=model_config.gradient_checkpointing, seed=args.seed)
+                            gradient_checkpointing=model_config.gradient_checkpointing, seed=args.seed,
+                            offload_optimizer=args.deepspeed_offload_optimizer, shard_parameters=args.shard_parameters)
         self.learner = Learner(spec, cfg, device=self.device)
         src = model_config.model_name_or_path
         if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
-            load_hf_checkpoint(src, self.learner.model.flat.detach(), spec, strict=False)
-            self.learner.opt.master.copy_(self.learner.model.flat.detach()[self.learner.opt.lo:self.learner.opt.hi].float())
+            self.learner.load_hf(src)
         self.ref: Learner | None = None
         if args.load_ref_policy and args.beta != 0.0:
-            # frozen copy of the initial policy; only its forward is used
-            self.ref = Learner(spec, LearnerConfig(ops=args.ops, comm="nccl" if world > 1 else "none", seed=args.seed), device=self.device,
-                               flat_init=self.learner.model.flat.detach().clone())
+            # frozen copy of the initial policy; only its forward is used (sharded like the policy when that is sharded:
+            # the full weights are then staged through host memory once)
+            sharded = self.learner.z3 is not None
+            init = self.learner.full_flat(torch.empty(self.learner.model.layout.total, dtype=torch.bfloat16)) if sharded \
+                else self.learner.model.flat.detach().clone()
+            self.ref = Learner(spec, LearnerConfig(ops=args.ops, comm="nccl" if world > 1 else "none", seed=args.seed,
+                                                   shard_parameters=sharded), device=self.device, flat_init=init)
         self.training_step = 0
         self._engine_views: list[torch.Tensor] = []
 
@@ -541,11 +545,11 @@ class LearnerWorker:
         return self.learner.global_step
 
     def flat_weights(self) -> torch.Tensor:
-        return self.learner.model.flat.detach()
+        return self.learner.full_flat()
 
     def weights_checksum(self, tp_rank: int = 0, tp_size: int = 1) -> float:
         """Sum of the bf16 working weights, or of the shard a tensor-parallel engine rank holds of them."""
-        w = self.learner.model.flat.detach()
+        w = self.learner.full_flat()
         if tp_size > 1:
             from .parallel.tp import shard_flat
 
@@ -553,7 +557,7 @@ class LearnerWorker:
         return float(w[: self.learner.model.layout.total].double().sum().item())
 
     def flat_weights_cpu(self) -> torch.Tensor:
-        return self.learner.model.flat.detach().to("cpu", copy=True)
+        return self.learner.full_flat().to("cpu", copy=True)
 
     def step(self, data: CollatedBatchData) -> dict:
         t0 = time.perf_counter()
@@ -569,7 +573,11 @@ class LearnerWorker:
     def update_ref_policy(self) -> None:
         """Polyak update ref <- alpha * policy + (1 - alpha) * ref on the flat buffers."""
         with torch.no_grad():
-            self.ref.model.flat.detach().lerp_(self.learner.model.flat.detach(), self.args.alpha)
+            if self.learner.z3 is not None:  # both are sharded the same way: the update is local to every rank's slices
+                self.ref.z3.local16.lerp_(self.learner.z3.local16, self.args.alpha)
+                self.ref.z3._after_weights_changed()
+            else:
+                self.ref.model.flat.detach().lerp_(self.learner.model.flat.detach(), self.args.alpha)
 
     # ---- weight sync into engines living in other processes (CUDA IPC + multi-destination copy kernel)
     def connect_engines(self, ipc_descs: list) -> int:
@@ -584,22 +592,33 @@ class LearnerWorker:
 
         t0 = time.perf_counter()
         n = self.learner.model.layout.total
-        per = -(-n // self.world)
-        lo, hi = self.rank * per, min(n, (self.rank + 1) * per)
-        push_slice(self.learner.model.flat.detach(), self._engine_views, lo, hi)
+        z = self.learner.z3
+        if z is not None:
+            # sharded parameters: every rank pushes the slices it owns, unit by unit, straight from its shard buffer
+            # (no gather); rank 0 adds the replicated tail
+            for u in z.units:
+                a, b = z._my_slice(u)
+                push_slice(z.local16, self._engine_views, a, b, src_offset=u.soff)
+            if self.rank == 0:
+                push_slice(z.local16, self._engine_views, z.layout.decay_end, n, src_offset=z.n_shard)
+        else:
+            per = -(-n // self.world)
+            lo, hi = self.rank * per, min(n, (self.rank + 1) * per)
+            push_slice(self.learner.model.flat.detach(), self._engine_views, lo, hi)
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         pdist.barrier()
         return time.perf_counter() - t0
 
     def save_model(self, output_dir: str, tokenizer_path: str | None = None) -> None:
+        full = self.learner.full_flat()  # a gather when the parameters are sharded: every rank takes part
         if self.rank == 0:
             tok = None
             if tokenizer_path:
                 from transformers import AutoTokenizer
 
                 tok = AutoTokenizer.from_pretrained(tokenizer_path)
-            save_hf_checkpoint(self.learner.model.flat, self.spec, output_dir, tokenizer=tok)
+            save_hf_checkpoint(full, self.spec, output_dir, tokenizer=tok)
             with open(os.path.join(output_dir, ".checkpoint_complete"), "w") as fh:
                 fh.write("ok")
         pdist.barrier()
@@ -607,8 +626,10 @@ class LearnerWorker:
     def save_checkpoint_state(self, ckpt_dir: str, client_state: dict) -> None:
         d = os.path.join(ckpt_dir, f"step_{client_state['training_step']}")
         save_train_state(d, self.learner.opt, client_state)
-        if self.ref is not None and self.rank == 0:
-            torch.save(self.ref.model.flat.detach().cpu(), os.path.join(d, "ref_policy.pt"))
+        if self.ref is not None:
+            ref_full = self.ref.full_flat()
+            if self.rank == 0:
+                torch.save(ref_full.detach().cpu(), os.path.join(d, "ref_policy.pt"))
 
     def load_checkpoint_state(self, ckpt_dir: str) -> dict | None:
         from .utils.common import get_last_checkpoint
@@ -621,7 +642,7 @@ class LearnerWorker:
         self.learner.global_step = st.get("optimizer_steps", self.training_step)
         p = os.path.join(d, "ref_policy.pt")
         if self.ref is not None and os.path.exists(p):
-            self.ref.model.flat.detach().copy_(torch.load(p, map_location=self.device))
+            self.ref.load_full_weights(torch.load(p, map_location="cpu" if self.ref.z3 is not None else self.device))
         return st
 
     def shutdown(self) -> None:

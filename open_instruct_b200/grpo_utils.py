@@ -83,6 +83,7 @@ class GRPOExperimentConfig(ExperimentConfig):
     deepspeed_zpg: int = 8
     deepspeed_offload_param: bool = False
     deepspeed_offload_optimizer: bool = False
+    shard_parameters: bool | None = None  # gather-on-use parameter sharding of the learner; None = only when the model does not fit resident
     deepspeed_checkpoint_load_universal: bool = False
     gather_whole_model: bool = True
     fsdp_shard_degree: int | None = None

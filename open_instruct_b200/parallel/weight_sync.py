@@ -92,10 +92,15 @@ def ensure_peer_access(dev: int, peer: int) -> None:
     _peer_ok.add((dev, peer))
 
 
-def push_slice(src: torch.Tensor, dsts: list[torch.Tensor], lo: int, hi: int) -> None:
-    """``dst[lo:hi] = bf16(src[lo:hi])`` for every destination (CUDA: one kernel for all of them)."""
+def push_slice(src: torch.Tensor, dsts: list[torch.Tensor], lo: int, hi: int, src_offset: int | None = None) -> None:
+    """``dst[lo:hi] = bf16(src[lo:hi])`` for every destination (CUDA: one kernel for all of them).  With ``src_offset`` the
+    source range starts there instead of at ``lo`` (a rank that holds only its slice of the parameters pushes it to its
+    place in the engines' full buffers)."""
     if hi <= lo or not dsts:
         return
+    so_ = lo if src_offset is None else src_offset
+    if so_ % 8:
+        raise ValueError("source offset must be a multiple of 8 elements")
     if any(isinstance(d, PeerBuffer) for d in dsts) and not (src.is_cuda and lo % 8 == 0 and len(dsts) <= 8):
         raise ValueError("buffers of other processes can only be written by the push kernel (CUDA source, offset multiple of 8, <= 8 engines)")
     if src.is_cuda and all(d.is_cuda and d.dtype == torch.bfloat16 for d in dsts) and lo % 8 == 0 and len(dsts) <= 8:
@@ -115,14 +120,15 @@ def push_slice(src: torch.Tensor, dsts: list[torch.Tensor], lo: int, hi: int) ->
         for i, d in enumerate(dsts):
             arr[i] = d.data_ptr()
         with torch.cuda.device(src.device):  # the launch goes to the source GPU whatever this thread's current device is
-            rc = fn(ptr(src), arr, len(dsts), lo, hi - lo, int(src.dtype == torch.float32), stream_ptr())
+            # the kernel indexes source and destinations with the same offset: shift the source base instead
+            rc = fn(ptr(src) + (so_ - lo) * src.element_size(), arr, len(dsts), lo, hi - lo, int(src.dtype == torch.float32), stream_ptr())
         lib.launch_count += 1
         if rc:
             raise lib.KernelError(f"b200_multi_push failed with code {rc}")
         return
     with torch.no_grad():
         for d in dsts:
-            d[lo:hi].copy_(src[lo:hi].to(d.dtype), non_blocking=True)
+            d[lo:hi].copy_(src[so_:so_ + hi - lo].to(d.dtype), non_blocking=True)
 
 
 def sync_in_process(learner_flat: torch.Tensor, engines: list, model_step: int, total: int) -> float:
