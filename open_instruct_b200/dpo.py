@@ -2,8 +2,9 @@
 
 The reference has two DPO entry points that share one config dataclass: ``dpo_tune_cache.py`` (accelerate + DeepSpeed) and
 ``dpo.py`` (olmo-core FSDP/HSDP + TP, ``open_instruct/dpo.py:141-342``).  Here one sharded-optimizer runtime serves both
-names; the olmo-core-only switches (``tensor_parallel_degree``, ``shard_degree``, ``num_replicas``) are accepted by the
-config and have no effect, because parameters are resident on every GPU and the optimizer is always sharded over all ranks.
+names.  ``tensor_parallel_degree`` splits every layer over groups of that many ranks (``parallel/tp.py:TrainTP``), with
+data parallelism across the groups; ``fsdp_shard_degree`` sets the size of the parameter-sharding groups when the
+parameters are sharded (``parallel/zero3.py``), replicas across them.
 """
 
 from .dpo_tune_cache import main  # noqa: F401

@@ -111,16 +111,22 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
     collator = TensorDataCollatorWithFlatteningDPO(max_seq_length=None, pad_token_id=tokenizer.pad_token_id or 0)
     if args.packing:
         collator.max_seq_length = args.max_seq_length
-    loader = HFDataLoader(dataset, batch_size=args.per_device_train_batch_size * world,
-                          seed=args.data_loader_seed if args.data_loader_seed is not None else args.seed, dp_rank=rank,
-                          dp_world_size=world, collator=collator, drop_last=True)
+    # the ranks of one tensor-parallel group work on the same micro-batches: data is sharded over the groups
+    tp = max(1, args.tensor_parallel_degree)
+    if world % tp:
+        raise ValueError(f"tensor_parallel_degree {tp} must divide the number of ranks {world}")
+    data_rank, data_world = rank // tp, world // tp
+    loader = HFDataLoader(dataset, batch_size=args.per_device_train_batch_size * data_world,
+                          seed=args.data_loader_seed if args.data_loader_seed is not None else args.seed, dp_rank=data_rank,
+                          dp_world_size=data_world, collator=collator, drop_last=True)
     steps_per_epoch = math.ceil(len(loader) / args.gradient_accumulation_steps)
     max_steps = args.max_train_steps or args.num_epochs * steps_per_epoch
     cfg = LearnerConfig(ops=args.ops, comm=args.comm_backend, learning_rate=args.learning_rate, weight_decay=args.weight_decay,
                         max_grad_norm=args.max_grad_norm, lr_scheduler_type=args.lr_scheduler_type,
                         warmup_steps=int(max_steps * args.warmup_ratio), total_steps=max_steps,
                         gradient_checkpointing=args.activation_memory_budget < 1 or args.gradient_checkpointing, seed=args.seed,
-                        offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters)
+                        offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters,
+                        tensor_parallel_degree=args.tensor_parallel_degree, shard_degree=args.fsdp_shard_degree)
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
@@ -142,8 +148,8 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
             dcs_hash = compute_config_hash(dcs, tc)
         cache_hash = compute_reference_cache_hash(args, dcs_hash)
         cache_path = os.path.join(REFERENCE_LOGPROBS_CACHE_PATH, f"{cache_hash}.pt")
-        cache_loader = HFDataLoader(dataset, batch_size=args.per_device_train_batch_size * world, seed=args.seed, dp_rank=rank,
-                                    dp_world_size=world, collator=collator, drop_last=False)
+        cache_loader = HFDataLoader(dataset, batch_size=args.per_device_train_batch_size * data_world, seed=args.seed, dp_rank=data_rank,
+                                    dp_world_size=data_world, collator=collator, drop_last=False)
         t0 = time.time()
         reference_cache = build_reference_logprobs_cache(learner, cache_loader, average, forward_fn, len(dataset), device,
                                                          cache_path, is_main)
@@ -212,7 +218,7 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
                 metrics.reduce_(average=True)
                 vals = metrics.get_metrics_list()
                 step_time = time.time() - step_t0
-                tokens_step = vals.pop("token_count") * world
+                tokens_step = vals.pop("token_count") * data_world
                 tokens_seen += tokens_step
                 last = {**vals, "learning_rate": learner.lr(completed - 1), "grad_norm": float(norm), "epoch": epoch,
                         "training_step": completed, "perf/tokens_per_second_step": tokens_step / max(step_time, 1e-9),

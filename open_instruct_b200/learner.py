@@ -46,6 +46,9 @@ class LearnerConfig:
     # Hybrid sharding: parameters are split over groups of this many consecutive ranks and replicated across the groups
     # (gradient shards summed between the groups once per step).  None = one shard group spanning all ranks.
     shard_degree: int | None = None
+    # Tensor parallelism of the training engine: groups of this many consecutive ranks split every layer (heads and MLP
+    # channels); data parallelism and the optimizer sharding run across the groups.
+    tensor_parallel_degree: int = 1
 
 
 def needs_sharding(total_params: int, world: int, hbm_bytes: int, offload_optimizer: bool = False) -> bool:
@@ -58,6 +61,16 @@ def needs_sharding(total_params: int, world: int, hbm_bytes: int, offload_optimi
 
 class Learner:
     def __init__(self, spec: ModelSpec, cfg: LearnerConfig, device=None, group=None, flat_init: torch.Tensor | None = None):
+        self.full_spec = spec
+        self.tp = None
+        if cfg.tensor_parallel_degree > 1:
+            from .parallel.tp import TrainTP, local_spec
+
+            if group is not None:
+                raise ValueError("tensor parallelism builds its own groups from the default group")
+            tp_group, group = pdist.tp_groups(cfg.tensor_parallel_degree)   # group: data-parallel ranks of my shard
+            self.tp = TrainTP(tp_group)
+            spec = local_spec(spec, cfg.tensor_parallel_degree)              # the model of this rank
         self.spec, self.cfg, self.group = spec, cfg, group
         self.rank, self.world = pdist.rank(group), pdist.world_size(group)
         if device is None:
@@ -72,6 +85,11 @@ class Learner:
         comm = cfg.comm
         if comm == "auto":
             comm = "none" if self.world == 1 else ("fused" if ops == "fused" else "nccl")
+        if self.tp is not None:
+            comm = "none" if self.world == 1 else "nccl"   # the data-parallel exchange of a TP shard goes through NCCL
+            if cfg.shard_parameters or cfg.sequence_parallel_size > 1:
+                raise NotImplementedError("tensor parallelism together with parameter sharding or sequence parallelism is not built")
+            flat_init = self._tp_shard_of(flat_init, dtype, cfg.seed)
         self.comm = comm
         from .models.spec import ParamLayout
 
@@ -81,7 +99,7 @@ class Learner:
         self.z3 = None
         shard = cfg.shard_parameters
         if shard is None:
-            shard = (ops == "fused" and self.world > 1 and
+            shard = (ops == "fused" and self.world > 1 and self.tp is None and
                      needs_sharding(layout.total, self.world, torch.cuda.get_device_properties(self.device).total_memory, cfg.offload_optimizer))
         if shard:
             if ops != "fused":
@@ -126,10 +144,13 @@ class Learner:
                 torch.distributed.broadcast(self.model.flat.detach(), src=0, group=group)
         if self.symm is not None:
             self.model.bind_main_grad(self.symm.grads)
+        self.model.tp = self.tp
         self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, lr=cfg.learning_rate,
                                  betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay,
                                  max_grad_norm=cfg.max_grad_norm, group=group, comm=comm, symm=self.symm,
-                                 use_kernels=(ops == "fused"), offload=cfg.offload_optimizer)
+                                 use_kernels=(ops == "fused"), offload=cfg.offload_optimizer,
+                                 norm_weights=self.tp.norm_weights(layout) if self.tp is not None else None,
+                                 norm_extra_group=self.tp.group if self.tp is not None else None)
         self.global_step = 0
         self._accum = 0
         self.sp = 1
@@ -178,6 +199,8 @@ class Learner:
         grad = self.model.grad_flat()
         if grad is None:
             raise RuntimeError("optimizer_step called without any backward")
+        if self.tp is not None:
+            self.tp.sync_replicated_grads(self.model.layout.views(grad), self.spec)
         if grad.numel() < self.opt.flat.numel():  # ref path: autograd grad has the padded size already
             raise RuntimeError("gradient buffer smaller than the parameter buffer")
         with nvtx_range("optimizer_step"):
@@ -195,9 +218,22 @@ class Learner:
         return norm
 
     # ------------------------------------------------------------------ whole-model views (loading, saving, weight sync)
+    def _tp_shard_of(self, full: torch.Tensor | None, dtype, seed: int) -> torch.Tensor:
+        """This rank's tensor-parallel shard of ``full`` (or of a fresh random initialisation drawn with ``seed``, identical
+        on every rank)."""
+        from .models.spec import ParamLayout
+        from .parallel.tp import shard_flat
+
+        if full is None:
+            full = LlamaModel(self.full_spec, device=self.device, dtype=dtype, ops="ref", seed=seed).flat.detach()
+        total = ParamLayout(self.full_spec).total
+        return shard_flat(full[:total].to(self.device), self.full_spec, self.tp.rank, self.tp.world)
+
     @torch.no_grad()
     def load_full_weights(self, flat: torch.Tensor) -> None:
         """Install a complete flat parameter vector (global layout, any device) as the working copy and the fp32 master."""
+        if self.tp is not None:
+            flat = self._tp_shard_of(flat, self.model.flat.dtype, 0)
         if self.z3 is not None:
             self.z3.load_full(flat)
             return
@@ -210,18 +246,27 @@ class Learner:
         rank keeps its slices only."""
         from .ckpt.hf_io import load_hf_checkpoint
 
-        if self.z3 is None:
+        if self.z3 is None and self.tp is None:
             load_hf_checkpoint(path, self.model.flat.detach(), self.spec, strict=strict)
             self.opt.master.copy_(self.model.flat.detach()[self.opt.lo:self.opt.hi].float())
             return
-        stage = torch.zeros(self.model.layout.total, dtype=self.z3.dtype)
-        load_hf_checkpoint(path, stage, self.spec, strict=strict)
+        from .models.spec import ParamLayout
+
+        stage = torch.zeros(ParamLayout(self.full_spec).total, dtype=self.z3.dtype if self.z3 is not None else self.model.flat.dtype)
+        load_hf_checkpoint(path, stage, self.full_spec, strict=strict)
         self.load_full_weights(stage)
 
     @torch.no_grad()
     def full_flat(self, out: torch.Tensor | None = None) -> torch.Tensor:
         """The complete bf16 parameter vector in the global layout: the resident working copy, or a gather of the shards
         (a collective: every rank calls it)."""
+        if self.tp is not None:
+            from .parallel.tp import unshard_flat
+
+            mine = self.model.flat.detach()[: self.model.layout.total].contiguous()
+            parts = [torch.empty_like(mine) for _ in range(self.tp.world)]
+            torch.distributed.all_gather(parts, mine, group=self.tp.group)
+            return unshard_flat(parts, self.full_spec, out)
         if self.z3 is None:
             return self.model.flat.detach()
         return self.z3.gather_full(out)

@@ -99,6 +99,7 @@ class LlamaModel:
         # keep the RMSNorm outputs and the SwiGLU activation for the backward pass instead of recomputing them
         # (5.8 GB per 4096-token micro-batch at 8B; about 2.5 % of the step): on by default, off under checkpointing
         self.keep_cheap_activations = os.environ.get("B200_RECOMPUTE_CHEAP", "0") != "1"
+        self.tp = None  # parallel.tp.TrainTP when the layers are split over a tensor-parallel group (spec is then the LOCAL spec)
         self.sp = None  # parallel.ulysses.UlyssesContext when the sequence is split over ranks (fused path)
         self.main_grad: torch.Tensor | None = None  # fp32 flat gradient (fused path)
         self.g: dict[str, torch.Tensor] = {}
@@ -240,14 +241,21 @@ class LlamaModel:
 
     def _ref_layer(self, x, v, i, position_ids, cu_seqlens):
         s = self.spec
+        tp = self.tp
         n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
+        if tp is not None:
+            n1 = tp.enter(n1)
         qkv = self.ref_qkv(n1, v, i)
         qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
         attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim)
-        x = x + ref.linear(attn, v[f"l{i}.wo"])
+        o = ref.linear(attn, v[f"l{i}.wo"])
+        x = x + (tp.sum_partials(o) if tp is not None else o)
         n2 = ref.rmsnorm(x, v[f"l{i}.mlp_norm"], s.rms_norm_eps)
+        if tp is not None:
+            n2 = tp.enter(n2)
         act = ref.swiglu(ref.linear(n2, v[f"l{i}.w_gate_up"]))
-        return x + ref.linear(act, v[f"l{i}.w_down"])
+        d = ref.linear(act, v[f"l{i}.w_down"])
+        return x + (tp.sum_partials(d) if tp is not None else d)
 
     # ------------------------------------------------------------------ fused path
     def _fused_forward_hidden(self, input_ids, position_ids, cu_seqlens, keep: bool):
@@ -275,11 +283,15 @@ class LlamaModel:
                                             res=stream if delta is not None else None)
             qkv, attn, lse, attn_tok = self._attention_block(i, n1, pos, cu)
             o = f.gemm(attn_tok if attn_tok is not None else attn, p[f"l{i}.wo"])
+            if self.tp is not None:
+                self.tp.all_reduce_(o)      # row-parallel projection: sum of the ranks' partials
             n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=h_in)
             del o
             gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
             act = f.swiglu_fwd(gate_up)
             delta = f.gemm(act, p[f"l{i}.w_down"])
+            if self.tp is not None:
+                self.tp.all_reduce_(delta)
             keep_cheap = keep and self.keep_cheap_activations and not self.gradient_checkpointing
             if not keep_cheap:
                 n1 = n2 = act = None
@@ -355,6 +367,8 @@ class LlamaModel:
         n1, _, rstd1 = f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)
         qkv, attn, lse, attn_tok = self._attention_block(i, n1, pos, cu)
         o = f.gemm(attn_tok if attn_tok is not None else attn, p[f"l{i}.wo"])
+        if self.tp is not None:
+            self.tp.all_reduce_(o)
         n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=st.h_in)
         gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
         return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk)
@@ -396,6 +410,8 @@ class LlamaModel:
             f.gemm(dgu, n2, g[f"l{i}.w_gate_up"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
             del n2
             d_n2 = f.gemm(dgu, p[f"l{i}.w_gate_up"], b_mn=True)
+            if self.tp is not None:
+                self.tp.all_reduce_(d_n2)   # column-parallel projection: the input gradient is a sum over the ranks
             del dgu
             d_mid = f.rmsnorm_bwd(st.h_mid, p[f"l{i}.mlp_norm"], st.rstd2, d_n2, d_stream, g[f"l{i}.mlp_norm"])
             del d_n2, d_stream
@@ -418,6 +434,8 @@ class LlamaModel:
             f.gemm(dqkv, n1, g[f"l{i}.wqkv"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
             del n1
             d_n1 = f.gemm(dqkv, p[f"l{i}.wqkv"], b_mn=True)
+            if self.tp is not None:
+                self.tp.all_reduce_(d_n1)
             del dqkv
             d_stream = f.rmsnorm_bwd(st.h_in, p[f"l{i}.attn_norm"], st.rstd1, d_n1, d_mid, g[f"l{i}.attn_norm"])
             del d_n1, d_mid

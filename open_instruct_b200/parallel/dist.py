@@ -95,6 +95,12 @@ def broadcast_object(obj, src: int = 0, group=None):
     return box[0]
 
 
+def tp_groups(tp: int):
+    """Tensor-parallel groups of ``tp`` consecutive ranks and the data-parallel groups across them (ranks with the same
+    position inside their TP group).  Returns ``(tp_group, dp_group)`` of this rank; collective."""
+    return hsdp_groups(tp)
+
+
 def hsdp_groups(shard_degree: int):
     """Split the default group into shard groups of ``shard_degree`` consecutive ranks and replica groups of the ranks
     that hold the same slice (hybrid sharding: ``DataParallelType.hsdp`` with ``shard_degree`` / ``num_replicas`` in the

@@ -63,6 +63,104 @@ def shard_flat(full_flat: torch.Tensor, spec: ModelSpec, rank: int, tp: int, out
     return out
 
 
+@torch.no_grad()
+def unshard_flat(shards: list[torch.Tensor], spec: ModelSpec, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Inverse of ``shard_flat``: the full flat buffer from the ``tp`` rank shards (replicated entries come from shard 0)."""
+    tp = len(shards)
+    ls = local_spec(spec, tp)
+    full, loc = ParamLayout(spec), ParamLayout(ls)
+    if out is None:
+        out = torch.zeros(full.total, dtype=shards[0].dtype, device=shards[0].device)
+    fv = full.views(out)
+    lvs = [loc.views(s) for s in shards]
+    hq, hk, f = ls.num_heads * ls.head_dim, ls.num_kv_heads * ls.head_dim, ls.intermediate_size
+    for name, dst in fv.items():
+        leaf = name.split(".", 1)[-1]
+        parts = [lv[name] for lv in lvs]
+        if leaf in ("wqkv", "bqkv"):
+            dst.copy_(torch.cat([p[:hq] for p in parts] + [p[hq:hq + hk] for p in parts] + [p[hq + hk:] for p in parts], 0))
+        elif leaf in ("wo", "w_down"):
+            dst.copy_(torch.cat(parts, 1))
+        elif leaf == "w_gate_up":
+            dst.copy_(torch.cat([p[:f] for p in parts] + [p[f:] for p in parts], 0))
+        else:
+            dst.copy_(parts[0])
+    return out
+
+
+class _SumOverTP(torch.autograd.Function):
+    """Forward: sum of the ranks' partial outputs (after a row-parallel projection).  Backward: identity - the upstream
+    gradient is the same on every rank."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        y = x.clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _CopyToTP(torch.autograd.Function):
+    """Forward: identity (a replicated activation enters a column-parallel projection).  Backward: the ranks' partial input
+    gradients are summed."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class TrainTP:
+    """Tensor parallelism of the TRAINING engine (what olmo-core's ``tensor_parallel_degree`` gives the reference's DPO
+    trainer, ``open_instruct/dpo_utils.py:129-130``, ``open_instruct/dpo.py:295-299``).  The model runs ``local_spec`` on this
+    rank's shard; the two row-parallel outputs of a layer are summed over the group in the forward, the two
+    column-parallel input gradients in the backward.  Replicated parameters (embedding, norms, output head) see
+    identical inputs and gradients on every rank; the q/k norm weights, whose gradient is a sum over heads, are the one
+    exception and are summed at the optimizer step (``sync_replicated_grads``)."""
+
+    def __init__(self, group):
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:   # fused path: explicit, in place
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def sum_partials(self, x):    # autograd path
+        return _SumOverTP.apply(x, self.group)
+
+    def enter(self, x):
+        return _CopyToTP.apply(x, self.group)
+
+    def norm_weights(self, layout: ParamLayout) -> list[tuple[int, int, float]]:
+        """Ranges of the local flat layout with their weight in the global gradient norm: 1 for entries split over the group,
+        1 / tp for replicated ones (every rank holds the same gradient).  Adjacent entries of equal weight are merged."""
+        out: list[list] = []
+        for name, e in layout.entries.items():
+            leaf = name.split(".", 1)[-1]
+            w = 1.0 if leaf in ("wqkv", "wo", "w_gate_up", "w_down", "bqkv") else 1.0 / self.world
+            if out and out[-1][2] == w:
+                out[-1][1] = e.offset + e.numel
+            else:
+                out.append([e.offset, e.offset + e.numel, w])
+        return [tuple(x) for x in out]
+
+    def sync_replicated_grads(self, grads: dict, spec: ModelSpec) -> None:
+        if spec.qk_norm:
+            for name, g in grads.items():
+                if name.endswith(("q_norm", "k_norm")):
+                    dist.all_reduce(g, group=self.group)
+
+
 class TPContext:
     """Two symmetric ``[max_tokens, hidden]`` bf16 buffers for the row-parallel outputs + the fused reduction."""
 

@@ -58,7 +58,11 @@ class ZeroOptimizer:
     def __init__(self, flat: torch.Tensor, total: int, decay_end: int, *, lr: float = 1e-5,
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, max_grad_norm: float | None = None,
                  group=None, comm: str = "auto", use_kernels: bool | None = None, symm=None, offload: bool = False,
-                 offload_chunk: int = 1 << 26):
+                 offload_chunk: int = 1 << 26, norm_weights: list | None = None, norm_extra_group=None):
+        # ``norm_weights``: (start, end, weight) ranges of the flat buffer for the gradient norm, with ``norm_extra_group`` a
+        # second group the squared norm is summed over.  Tensor parallelism uses it: the flat buffer is one rank's shard, the
+        # norm must cover all shards (summed over the TP group) but count replicated entries once (weight 1 / tp).
+        self.norm_weights, self.norm_extra_group = norm_weights, norm_extra_group
         # ``offload``: fp32 master / m / v shards live in pinned host memory and stream through two device staging
         # sets per optimizer step (H2D on one side stream, D2H on another, AdamW on the main stream) - the 12 bytes
         # per parameter leave the GPU, the price is 24 bytes per parameter over PCIe per step
@@ -150,6 +154,22 @@ class ZeroOptimizer:
         # ---- global grad norm (of the summed gradient times grad_scale)
         if norm_sq is not None:
             self._norm_sq.copy_(norm_sq)
+        elif self.norm_weights is not None:
+            self._norm_sq.zero_()
+            part = torch.zeros_like(self._norm_sq)
+            for (a, b, w) in self.norm_weights:
+                a2, b2 = max(a, self.lo) - self.lo, min(b, self.hi) - self.lo
+                if b2 <= a2:
+                    continue
+                if self.use_kernels and a2 % 4 == 0:
+                    from ..ops import fused
+
+                    fused.sumsq(gs[a2:b2], part)
+                else:
+                    part.copy_(gs[a2:b2].double().pow(2).sum().float().reshape(1))
+                self._norm_sq.add_(part, alpha=w)
+            if self.norm_extra_group is not None:
+                dist.all_reduce(self._norm_sq, op=dist.ReduceOp.SUM, group=self.norm_extra_group)
         elif fused_comm:
             pass  # the reduce-scatter kernel already accumulated this rank's sum of squares
         elif self.use_kernels:

@@ -161,3 +161,23 @@ def test_model_dims_utilisation_stays_physical():
     b = ModelDims(num_layers=28, hidden_size=3584, intermediate_size=18944, vocab_size=152064, num_attn_heads=28, head_dim=128, num_kv_heads=4,
                   device_name="b200")
     assert b.device_flops > dims.device_flops and b.device_memory_bandwidth > dims.device_memory_bandwidth
+
+
+def _run_tp_train(world, family, port):
+    import os
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "_tp_train_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "FAMILY": family})
+    assert res.returncode == 0 and res.stdout.count("TP_TRAIN_OK") == world, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+def test_training_tensor_parallel_matches_unsharded():
+    _run_tp_train(2, "llama", 29691)
+
+
+def test_training_tensor_parallel_with_data_parallel_and_qk_norm():
+    _run_tp_train(4, "qwen3", 29692)
