@@ -126,6 +126,7 @@ class FlatArguments:
     verbose: bool = False
     sequence_parallel_size: int = field(default=1, metadata={"help": "Ulysses sequence-parallel degree"})
     profiling: bool = field(default=False, metadata={"help": "torch.profiler trace of a few steps into <output_dir>/profiler"})
+    tensor_parallel_degree: int = field(default=1, metadata={"help": "split every layer over groups of this many GPUs (data parallel across the groups)"})
     shard_parameters: bool | None = field(default=None, metadata={"help": "ZeRO-3 parameter sharding: gather each layer on use. Default: only when the resident design does not fit the GPU"})
     offload_optimizer: bool = field(default=False, metadata={"help": "keep fp32 master weights and Adam moments in pinned host memory"})
     # engine selection (not in the reference: there the back end is fixed by the launcher config)
@@ -219,7 +220,11 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
     if sp > 1:
         if sp != world or not args.packing or args.max_seq_length % sp:
             raise ValueError("sequence_parallel_size must equal the number of ranks, with --packing and max_seq_length divisible by it")
-    dp_rank, dp_world = rank // sp, world // sp  # the ranks of one sequence-parallel group read the same micro-batches
+    tp = max(1, args.tensor_parallel_degree)
+    if tp > 1 and (sp > 1 or world % tp):
+        raise ValueError("tensor_parallel_degree must divide the number of ranks and excludes sequence parallelism")
+    grp = sp * tp  # (one of them is 1)
+    dp_rank, dp_world = rank // grp, world // grp  # the ranks of one sequence- or tensor-parallel group read the same micro-batches
     loader = HFDataLoader(dataset, batch_size=per_rank * dp_world, seed=args.seed, dp_rank=dp_rank, dp_world_size=dp_world,
                           collator=collator, drop_last=True)
     steps_per_epoch = math.ceil(len(loader) / args.gradient_accumulation_steps)
@@ -231,7 +236,8 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                         lr_scheduler_type=args.lr_scheduler_type, warmup_steps=warmup, total_steps=max_steps,
                         final_lr_ratio=args.final_lr_ratio, gradient_checkpointing=args.gradient_checkpointing, seed=args.seed,
                         sequence_parallel_size=sp, sp_max_tokens=args.max_seq_length * max(1, per_rank) if sp > 1 else 0,
-                        offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters)
+                        offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters,
+                        tensor_parallel_degree=tp)
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):

@@ -89,9 +89,14 @@ struct Sched {
   // L2 (about 40 MB of its 126 are budgeted for them), while B is streamed once per sweep: the more row tiles a sweep
   // holds, the fewer times B comes from DRAM (gate/up forward at 4096 tokens: 4 sweeps -> 1, 1.08 GB -> 0.3 GB read).
   int group;
-  __device__ __forceinline__ void set_group(int K) {
+  __device__ __forceinline__ void set_group(int K, int N) {
     const long long bytes_per_row_tile = 2LL * BM * K * 2;
-    const long long gmax = (40LL << 20) / bytes_per_row_tile;
+    const long long b_bytes = 2LL * N * K;
+    // a B operand that fits in L2 stays there too: the sweep's A rows get what is left of about 56 MB
+    long long budget = 40LL << 20;
+    if (b_bytes <= (48LL << 20)) budget = (56LL << 20) - b_bytes;
+    if (budget < (8LL << 20)) budget = 8LL << 20;
+    const long long gmax = budget / bytes_per_row_tile;
     group = static_cast<int>(gmax < 4 ? 4 : (gmax > 64 ? 64 : gmax));
   }
   __device__ __forceinline__ void get(int t, int& m_blk, int& n_blk) const {
@@ -133,7 +138,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   sched.num_m = (M + 2 * BM - 1) / (2 * BM);
   sched.num_n = (N + BN - 1) / BN;
   sched.total = sched.num_m * sched.num_n;
-  sched.set_group(K);
+  sched.set_group(K, N);
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
