@@ -167,6 +167,82 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ h, const __
   for (int i = threadIdx.x; i < D; i += blockDim.x) dw_partial[static_cast<long long>(blockIdx.x) * D + i] = dwacc[i];
 }
 
+// The same backward for D = 2048 * VPT: every thread keeps its VPT 16-byte vectors of h and dy in registers (one read
+// of each row, no second pass), its weight-gradient partial sums too, and issues the NEXT row's loads before the block
+// reduction of the current one, so that the memory latency overlaps the reduction instead of adding to it.
+template <int VPT>
+__global__ void __launch_bounds__(256, VPT <= 2 ? 2 : 1)
+rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ w,
+                       const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw_partial, int T) {
+  constexpr int D = 2048 * VPT;
+  __shared__ float red[32];
+  float wf[VPT][8], dwr[VPT][8];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    unpack8(reinterpret_cast<const bf16x8*>(w)[threadIdx.x + v * 256], wf[v]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwr[v][j] = 0.f;
+  }
+  bf16x8 hv[VPT], dv[VPT], rv[VPT], hn[VPT], dn[VPT], rn[VPT];
+  long long row = blockIdx.x;
+  if (row < T) {
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      hv[v] = reinterpret_cast<const bf16x8*>(h + row * D)[threadIdx.x + v * 256];
+      dv[v] = reinterpret_cast<const bf16x8*>(dy + row * D)[threadIdx.x + v * 256];
+      if (dres) rv[v] = reinterpret_cast<const bf16x8*>(dres + row * D)[threadIdx.x + v * 256];
+    }
+  }
+  for (; row < T; row += gridDim.x) {
+    const long long nrow = row + gridDim.x;
+    if (nrow < T) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        hn[v] = reinterpret_cast<const bf16x8*>(h + nrow * D)[threadIdx.x + v * 256];
+        dn[v] = reinterpret_cast<const bf16x8*>(dy + nrow * D)[threadIdx.x + v * 256];
+        if (dres) rn[v] = reinterpret_cast<const bf16x8*>(dres + nrow * D)[threadIdx.x + v * 256];
+      }
+    }
+    const float r = rstd[row];
+    float hf[VPT][8], df[VPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      unpack8(hv[v], hf[v]);
+      unpack8(dv[v], df[v]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += df[v][j] * wf[v][j] * hf[v][j] * r;
+    }
+    const float mean_gx = block_sum(dot, red) / D;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float o[8], rf[8];
+      if (dres) unpack8(rv[v], rf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = hf[v][j] * r;
+        o[j] = r * (df[v][j] * wf[v][j] - xhat * mean_gx);
+        if (dres) o[j] += rf[j];
+        dwr[v][j] += df[v][j] * xhat;
+      }
+      reinterpret_cast<bf16x8*>(dx + row * D)[threadIdx.x + v * 256] = pack8(o);
+    }
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      hv[v] = hn[v];
+      dv[v] = dn[v];
+      rv[v] = rn[v];
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPT; ++v)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      dw_partial[static_cast<long long>(blockIdx.x) * D + (threadIdx.x + v * 256) * 8 + j] = dwr[v][j];
+}
+
 // dw_out[d] += sum_p partial[p][d]   (fp32 main-grad accumulate)
 __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw_out, int P, int D) {
   const int d = blockIdx.x * blockDim.x + threadIdx.x;
@@ -466,10 +542,22 @@ extern "C" int b200_rmsnorm_bwd(const void* h, const void* w, const float* rstd,
     cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     cfg = true;
   }
-  const int ctas = b200_rmsnorm_bwd_ctas(T);
-  // blockDim * 8 must cover whole vectors consistently: thread i owns vectors i, i+blockDim, ...
-  rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx),
-                                                                   dw_partial, T, D);
+  int ctas = b200_rmsnorm_bwd_ctas(T);
+  if (D == 2048 || D == 4096 || D == 8192) {
+    // two resident CTAs per SM (one at D = 8192), each with the next row's loads in flight
+    const int cap = D == 8192 ? 148 : 296;
+    if (ctas > cap) ctas = cap;
+    if (D == 2048)
+      rmsnorm_bwd_reg_kernel<1><<<ctas, 256, 0, ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
+    else if (D == 4096)
+      rmsnorm_bwd_reg_kernel<2><<<ctas, 256, 0, ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
+    else
+      rmsnorm_bwd_reg_kernel<4><<<ctas, 256, 0, ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
+  } else {
+    // blockDim * 8 must cover whole vectors consistently: thread i owns vectors i, i+blockDim, ...
+    rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx),
+                                                                     dw_partial, T, D);
+  }
   if (dw_out) rmsnorm_dw_reduce_kernel<<<(D + 255) / 256, 256, 0, ST(stream)>>>(dw_partial, dw_out, ctas, D);
   return static_cast<int>(cudaGetLastError());
 }

@@ -256,6 +256,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       sched.get(t, m_blk, n_blk);
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
+      if (OUT == OUT_F32_ACC) {
+        // the accumulate epilogue reads the old gradient tile, which never sits in L2 (the gradient buffer is streamed once
+        // per micro-batch): ask L2 for this thread's row now, while the tile's MMAs are still running
+        const int prow = m_blk * 2 * BM + cta * BM + lane_grp * 32 + lane;
+        if (prow < M) {
+          const char* pc = reinterpret_cast<const char*>(reinterpret_cast<const float*>(Cout) + static_cast<long long>(prow) * ldc + n_blk * BN);
+          const int ncols = min(BN, N - n_blk * BN);
+#pragma unroll
+          for (int b = 0; b < BN * 4; b += 128)
+            if (b < ncols * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + b));
+        }
+      }
       const bool ready = __all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag));
       if (!ready) {
         if (lane == 0) atomicCAS(status, 0, ST_TIMEOUT_TMEM_FULL);

@@ -69,7 +69,7 @@ def test_gemm_strided_views():
     assert _rel(out, a.float() @ w.float().t()) < 5e-3
 
 
-@pytest.mark.parametrize("T,D", [(7, 64), (300, 4096), (1024, 8192)])
+@pytest.mark.parametrize("T,D", [(7, 64), (300, 4096), (1024, 8192), (5, 2048), (700, 2048), (1500, 4096), (333, 5120)])
 def test_rmsnorm(T, D):
     from open_instruct_b200.ops import fused, ref
 
