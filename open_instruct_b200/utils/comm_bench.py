@@ -1,7 +1,7 @@
 """Device-timed micro-benchmark of the fused compute + collective kernels (run under torchrun, one rank per GPU).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29720 \
-        -m open_instruct_b200.utils.comm_bench --params 8.03e9 --json gpurun_out/comm_bench.json
+        -m open_instruct_b200.utils.comm_bench --params 8.03e9 --json comm_bench.json
 
 For each kernel: CUDA-event time on the launching stream (max over ranks, after warm-up, inputs far larger than L2), the
 bytes each GPU must move over NVLink, and the fraction of the link roofline (bytes / 770 GB/s measured peer-copy rate per
