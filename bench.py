@@ -210,7 +210,7 @@ def main():
     total_steps = args.warmup + 2 * args.steps
     cfg = LearnerConfig(ops=args.ops, comm=args.comm, learning_rate=5e-6, lr_scheduler_type="linear",
                         warmup_steps=max(1, int(0.03 * 1000)), total_steps=1000, max_grad_norm=1.0,
-                        gradient_checkpointing=args.gradient_checkpointing, seed=0, shard_parameters=args.shard_parameters)
+                        gradient_checkpointing=args.gradient_checkpointing, seed=0, shard_parameters=True if args.shard_parameters else None)
     learner = Learner(spec, cfg, device=device)
 
     def host_step(i):

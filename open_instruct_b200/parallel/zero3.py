@@ -111,7 +111,9 @@ class Zero3State:
         self.resident: list[int | None] = [None, None]   # which layer each parameter workspace holds
         self.pinned_fresh = False
         self.gather_count = 0   # layer gathers issued (tests check the prefetch / reuse logic with it)
-        self.cs = torch.cuda.Stream(self.device) if cuda else None
+        # two communication streams: the gather of the next layer must not queue behind a gradient reduction
+        self.cs = torch.cuda.Stream(self.device) if cuda else None   # gathers
+        self.rs = torch.cuda.Stream(self.device) if cuda else None   # reductions
         self._ev_g = [torch.cuda.Event() for _ in range(2)] if cuda else None       # gather into slot k finished
         self._ev_r = [None, None]                                                  # reduce out of grad slot k finished
         self._ev_pin: dict[str, torch.cuda.Event] = {}
@@ -304,11 +306,11 @@ class Zero3State:
         if self.cs is None:
             self._reduce_scatter_add(self.gws[k], u, slot=k)
             return
-        self.cs.wait_stream(self._main())
-        with torch.cuda.stream(self.cs):
+        self.rs.wait_stream(self._main())
+        with torch.cuda.stream(self.rs):
             self._reduce_scatter_add(self.gws[k], u, slot=k)
             self._ev_r[k] = torch.cuda.Event()
-            self._ev_r[k].record(self.cs)
+            self._ev_r[k].record(self.rs)
 
     # ------------------------------------------------------------------ optimizer step
     @torch.no_grad()
@@ -316,6 +318,7 @@ class Zero3State:
         """Reduce what is still local (pinned units, tail), global norm, clip, AdamW on the shards."""
         if self.cs is not None:
             self._main().wait_stream(self.cs)
+            self._main().wait_stream(self.rs)
             self._ev_r = [None, None]
         if self.peer is not None:
             self.peer.barrier()  # every rank's layer reductions have read my workspaces; pinned gradients are complete

@@ -57,7 +57,7 @@ class PeerComm:
         # the gather goes through the copy engines by default ("ce": no SM taken from the GEMMs); "sm" = the pull kernel
         self.gather_mode = os.environ.get("B200_Z3_GATHER", "ce")
         self.gather_ctas = int(os.environ.get("B200_Z3_GATHER_CTAS", "64"))
-        self.reduce_ctas = int(os.environ.get("B200_Z3_REDUCE_CTAS", "16"))  # has a whole layer's backward to finish
+        self.reduce_ctas = int(os.environ.get("B200_Z3_REDUCE_CTAS", "64"))
         lib.load_ops()
         for name in ("b200_symm_barrier", "b200_allgather_pull", "b200_reduce_scatter_add", "b200_allgather_copy"):
             fn = getattr(lib.load_ops(), name)
