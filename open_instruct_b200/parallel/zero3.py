@@ -161,6 +161,14 @@ class Zero3State:
 
     def _make_optimizer(self) -> None:
         a = self._opt_args
+        if self.opt is not None:
+            # new weights into the existing state (no second set of fp32 buffers, not even for a moment)
+            with torch.no_grad():
+                self.opt.master.copy_(self.local16[:self.opt.master.numel()])
+                self.opt.m.zero_()
+                self.opt.v.zero_()
+            self.opt.step_count = 0
+            return
         self.opt = ZeroOptimizer(self.local16, self.n_local, self.n_shard, lr=a["lr"], betas=a["betas"], eps=a["eps"],
                                  weight_decay=a["weight_decay"], max_grad_norm=a["max_grad_norm"], group=pdist.SOLO, comm="none",
                                  use_kernels=a["use_kernels"], offload=a["offload"])
