@@ -233,6 +233,20 @@ def main():
 
     # ---------------- phase A: device-resident inputs
     staged = [[to_device(mb, device) for mb in host[args.warmup + i]] for i in range(args.steps)]
+    # device time of the optimizer step alone (gradient exchange + clip + AdamW + bf16 refresh): events around the call,
+    # read after the timed region
+    opt_events = []
+    plain_optimizer_step = learner.optimizer_step
+
+    def timed_optimizer_step(*a, **k):
+        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        ev[0].record()
+        r = plain_optimizer_step(*a, **k)
+        ev[1].record()
+        opt_events.append(ev)
+        return r
+
+    learner.optimizer_step = timed_optimizer_step
     sync()
     sampler = ClockSampler(device.index or 0).start()
     launches0 = lib.launch_count
@@ -244,6 +258,8 @@ def main():
     sync()
     ms_dev = pdist.max_over_ranks(e0.elapsed_time(e1), device)
     launches = lib.launch_count - launches0
+    learner.optimizer_step = plain_optimizer_step
+    opt_ms = pdist.max_over_ranks(sum(a.elapsed_time(b) for a, b in opt_events) / max(1, len(opt_events)), device)
     clocks = sampler.stop()
     del staged
 
@@ -278,6 +294,7 @@ def main():
         "steps": args.steps,
         "warmup": args.warmup,
         "ms_per_step": ms_dev / args.steps,
+        "optimizer_step_ms": opt_ms,  # exchange + clip + AdamW + refresh; its growth with N is the exposed communication
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world),
