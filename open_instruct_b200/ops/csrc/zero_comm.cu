@@ -223,8 +223,12 @@ allgather_pull_kernel(PeerPtrs shards, int world, long long soff, long long n, _
 
 // acc[i] += sum_r ws_r[lo + i]: the per-layer gradient reduction of the parameter-sharded learner (the owner reads its
 // slice of every rank's layer workspace, fixed rank order).  n % 4 == 0, lo % 4 == 0.
+// MULTIMEM: one `multimem.ld_reduce` through the NVSwitch returns the sum over all ranks (the switch adds), so the owner
+// pulls n floats over NVLink instead of world * n.
+template <bool MULTIMEM>
 __global__ void __launch_bounds__(256)
-reduce_scatter_add_kernel(PeerPtrs ws, int world, long long lo, long long n, float* __restrict__ acc) {
+reduce_scatter_add_kernel(PeerPtrs ws, const float* __restrict__ mc_ws, int world, long long lo, long long n,
+                          float* __restrict__ acc) {
   constexpr int U = 4;
   const long long nv = n / 4;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -235,6 +239,16 @@ reduce_scatter_add_kernel(PeerPtrs ws, int world, long long lo, long long n, flo
       const long long i = i0 + u * stride;
       a[u] = i < nv ? reinterpret_cast<const float4*>(acc)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    if (MULTIMEM) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nv) {
+          const float4 x = multimem_ld_reduce_f32x4(mc_ws + lo + i * 4);
+          a[u].x += x.x; a[u].y += x.y; a[u].z += x.z; a[u].w += x.w;
+        }
+      }
+    } else
 #pragma unroll 1
     for (int r = 0; r < world; ++r) {
       uint4 x[U];
@@ -285,12 +299,16 @@ extern "C" int b200_allgather_pull(const void* const* shard_ptrs, int world, lon
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int b200_reduce_scatter_add(const void* const* ws_ptrs, int world, long long lo, long long n, float* acc,
-                                       int ctas, void* stream) {
+extern "C" int b200_reduce_scatter_add(const void* const* ws_ptrs, const void* mc_ws, int world, long long lo, long long n,
+                                       float* acc, int ctas, void* stream) {
   if (world > MAX_PEERS || n % 4 || lo % 4) return -1;
   if (n == 0) return 0;
-  reduce_scatter_add_kernel<<<ctas > 0 ? ctas : 32, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      make_ptrs(ws_ptrs, world), world, lo, n, acc);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (mc_ws)
+    reduce_scatter_add_kernel<true><<<ctas > 0 ? ctas : 32, 256, 0, st>>>(make_ptrs(ws_ptrs, world),
+                                                                           reinterpret_cast<const float*>(mc_ws), world, lo, n, acc);
+  else
+    reduce_scatter_add_kernel<false><<<ctas > 0 ? ctas : 32, 256, 0, st>>>(make_ptrs(ws_ptrs, world), nullptr, world, lo, n, acc);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -26,7 +26,7 @@ _PP = ctypes.POINTER(ctypes.c_void_p)
 
 lib._SIGNATURES.update({
     "b200_allgather_pull": [_PP, _I, _L, _L, _P, _I, _P],
-    "b200_reduce_scatter_add": [_PP, _I, _L, _L, _P, _I, _P],
+    "b200_reduce_scatter_add": [_PP, _P, _I, _L, _L, _P, _I, _P],
     "b200_allgather_copy": [_PP, _I, _L, _L, _I, _P, _P],
 })
 
@@ -47,10 +47,16 @@ class PeerComm:
         hs = symm_mem.rendezvous(self.shards, self.group)
         self._shard_ptrs = _ptr_array(hs.buffer_ptrs)
         self._pads = _ptr_array(hs.signal_pad_ptrs)
-        self._ws_ptrs = []
+        self._ws_ptrs, self._ws_mc = [], []
+        # B200_MULTIMEM=1: the reduction reads through the workspaces' multicast address (the NVSwitch adds the ranks'
+        # values); off by default, like the optimizer-step kernels' multimem variants
+        want_mc = os.environ.get("B200_MULTIMEM", "0") == "1"
         for w in self.grad_ws:
             w.zero_()
-            self._ws_ptrs.append(_ptr_array(symm_mem.rendezvous(w, self.group).buffer_ptrs))
+            hw = symm_mem.rendezvous(w, self.group)
+            self._ws_ptrs.append(_ptr_array(hw.buffer_ptrs))
+            self._ws_mc.append(int(hw.multicast_ptr or 0) if want_mc else 0)
+        self.use_multimem = all(self._ws_mc)
         self._handles = hs
         self._epoch = 0
         # CTAs of the two transport kernels: they run beside the layer's GEMMs, so they get a slice of the SMs only
@@ -80,5 +86,6 @@ class PeerComm:
 
     def reduce_scatter_add(self, slot: int, n: int, acc: torch.Tensor) -> None:
         self.barrier()  # every rank has finished writing this workspace
-        lib.call("b200_reduce_scatter_add", self._ws_ptrs[slot], self.world, self.rank * n, n, ptr(acc), self.reduce_ctas, stream_ptr())
+        lib.call("b200_reduce_scatter_add", self._ws_ptrs[slot], self._ws_mc[slot] if self.use_multimem else None, self.world,
+                 self.rank * n, n, ptr(acc), self.reduce_ctas, stream_ptr())
         self.barrier()  # every rank has finished reading it: whoever waits on this stream may overwrite its copy

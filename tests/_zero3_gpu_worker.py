@@ -47,9 +47,11 @@ def main():
         if world > 1:
             variants["z3_peer"] = dict(comm="fused", shard_parameters=True)      # gather by the copy engines
             variants["z3_peer_sm"] = dict(comm="fused", shard_parameters=True)   # gather by the pull kernel
+            variants["z3_peer_mm"] = dict(comm="fused", shard_parameters=True)   # reduction by multimem.ld_reduce (if the fabric offers it)
         out = {}
         for name, v in variants.items():
             os.environ["B200_Z3_GATHER"] = "sm" if name == "z3_peer_sm" else "ce"
+            os.environ["B200_MULTIMEM"] = "1" if name == "z3_peer_mm" else "0"
             L = Learner(spec, LearnerConfig(**kw, **v), device=device, flat_init=init.to(device))
             assert (L.z3 is not None) == v["shard_parameters"]
             if name.startswith("z3_peer"):
