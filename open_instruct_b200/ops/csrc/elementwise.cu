@@ -529,6 +529,28 @@ extern "C" int b200_rmsnorm_fwd_acc32(float* x32, const void* res, const void* w
   return static_cast<int>(cudaGetLastError());
 }
 
+// Shared by both entry points: picks the register-resident kernel where D allows it, launches it with at most `max_ctas`
+// CTAs (`dw_partial` has that many rows of D floats) and reduces the partial rows into `dw_out`.
+static void launch_rmsnorm_bwd(const void* h, const void* w, const float* rstd, const void* dy, const void* dres, void* dx,
+                               float* dw_partial, float* dw_out, int T, int D, int max_ctas, cudaStream_t st) {
+  int ctas = T < max_ctas ? T : max_ctas;
+  if (D == 2048 || D == 4096 || D == 8192) {
+    // two resident CTAs per SM (one at D = 8192), each with the next row's loads in flight
+    const int cap = D == 8192 ? 148 : 296;
+    if (ctas > cap) ctas = cap;
+    if (D == 2048)
+      rmsnorm_bwd_reg_kernel<1><<<ctas, 256, 0, st>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
+    else if (D == 4096)
+      rmsnorm_bwd_reg_kernel<2><<<ctas, 256, 0, st>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
+    else
+      rmsnorm_bwd_reg_kernel<4><<<ctas, 256, 0, st>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
+  } else {
+    // blockDim * 8 must cover whole vectors consistently: thread i owns vectors i, i+blockDim, ...
+    rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), st>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T, D);
+  }
+  if (dw_out) rmsnorm_dw_reduce_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_partial, dw_out, ctas, D);
+}
+
 // number of partial rows the backward needs in its scratch buffer ([ctas, D] floats)
 // four CTAs per SM: one CTA walks its rows one at a time (two block reductions per row), so rows in flight = CTAs
 extern "C" int b200_rmsnorm_bwd_ctas(int T) { return T < 592 ? T : 592; }
@@ -542,23 +564,7 @@ extern "C" int b200_rmsnorm_bwd(const void* h, const void* w, const float* rstd,
     cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     cfg = true;
   }
-  int ctas = b200_rmsnorm_bwd_ctas(T);
-  if (D == 2048 || D == 4096 || D == 8192) {
-    // two resident CTAs per SM (one at D = 8192), each with the next row's loads in flight
-    const int cap = D == 8192 ? 148 : 296;
-    if (ctas > cap) ctas = cap;
-    if (D == 2048)
-      rmsnorm_bwd_reg_kernel<1><<<ctas, 256, 0, ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
-    else if (D == 4096)
-      rmsnorm_bwd_reg_kernel<2><<<ctas, 256, 0, ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
-    else
-      rmsnorm_bwd_reg_kernel<4><<<ctas, 256, 0, ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T);
-  } else {
-    // blockDim * 8 must cover whole vectors consistently: thread i owns vectors i, i+blockDim, ...
-    rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx),
-                                                                     dw_partial, T, D);
-  }
-  if (dw_out) rmsnorm_dw_reduce_kernel<<<(D + 255) / 256, 256, 0, ST(stream)>>>(dw_partial, dw_out, ctas, D);
+  launch_rmsnorm_bwd(h, w, rstd, dy, dres, dx, dw_partial, dw_out, T, D, b200_rmsnorm_bwd_ctas(T), ST(stream));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -695,10 +701,7 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* h, const void* w, const floa
     g_partials_addr[dev] = p;
   }
   float* partials = g_partials_addr[dev];
-  const int ctas = T < NOALLOC_MAX_CTAS ? T : NOALLOC_MAX_CTAS;
   // every CTA overwrites its whole [D] row of the partials, so nothing left by an earlier call is read
-  rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), ST(stream)>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx),
-                                                                   partials, T, D);
-  if (dw_out) rmsnorm_dw_reduce_kernel<<<(D + 255) / 256, 256, 0, ST(stream)>>>(partials, dw_out, ctas, D);
+  launch_rmsnorm_bwd(h, w, rstd, dy, dres, dx, partials, dw_out, T, D, NOALLOC_MAX_CTAS, ST(stream));
   return static_cast<int>(cudaGetLastError());
 }
