@@ -243,13 +243,25 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16*
       dw_partial[static_cast<long long>(blockIdx.x) * D + (threadIdx.x + v * 256) * 8 + j] = dwr[v][j];
 }
 
-// dw_out[d] += sum_p partial[p][d]   (fp32 main-grad accumulate)
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw_out, int P, int D) {
-  const int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= D) return;
+// dw_out[d] += sum_p partial[p][d]   (fp32 main-grad accumulate).  A CTA of 32 x 8 threads owns 32 columns: the eight
+// thread rows walk interleaved partial rows (128-byte coalesced loads), then add up through shared memory in a fixed
+// order.  (One thread per column walking all P rows took 23 us for P = 296: a chain of dependent-latency loads.)
+__global__ void __launch_bounds__(256)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw_out, int P, int D) {
+  __shared__ float red[8][32];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int d = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[static_cast<long long>(p) * D + d];
-  dw_out[d] += s;
+  if (d < D)
+    for (int p = ty; p < P; p += 8) s += partial[static_cast<long long>(p) * D + d];
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && d < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][tx];
+    dw_out[d] += t;
+  }
 }
 
 // ------------------------------------------------------------------ RoPE
@@ -548,7 +560,7 @@ static void launch_rmsnorm_bwd(const void* h, const void* w, const float* rstd, 
     // blockDim * 8 must cover whole vectors consistently: thread i owns vectors i, i+blockDim, ...
     rmsnorm_bwd_kernel<<<ctas, 256, D * sizeof(float), st>>>(CBF(h), CBF(w), rstd, CBF(dy), CBF(dres), BF(dx), dw_partial, T, D);
   }
-  if (dw_out) rmsnorm_dw_reduce_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_partial, dw_out, ctas, D);
+  if (dw_out) rmsnorm_dw_reduce_kernel<<<(D + 31) / 32, 256, 0, st>>>(dw_partial, dw_out, ctas, D);
 }
 
 // number of partial rows the backward needs in its scratch buffer ([ctas, D] floats)
