@@ -36,7 +36,13 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "hf_stack"],
+                    help="ours: this framework; reference: the unmodified reference (prints 'unavailable' where it cannot run); "
+                         "hf_stack: transformers + FlashAttention-2 + liger + torch fused AdamW / FSDP2 over NCCL, the libraries the "
+                         "reference trainer drives, without its accelerate/DeepSpeed wrapper (a same-box anchor, not the reference arm)")
+    ap.add_argument("--hf_attn", default=None, help="hf_stack: attention implementation (default flash_attention_2 on CUDA)")
+    ap.add_argument("--hf_grad_accum", default="fp32", choices=["fp32", "bf16"], help="hf_stack, one GPU: gradient accumulation dtype")
+    ap.add_argument("--no_liger", action="store_true", help="hf_stack: plain transformers modules")
     ap.add_argument("--model", default="llama3.1-8b")
     ap.add_argument("--seq_len", type=int, default=4096)
     ap.add_argument("--packs_per_gpu", type=int, default=16)
@@ -58,7 +64,7 @@ def reference_arm(args) -> None:
     """The unmodified reference cannot run here: its trainers import accelerate, deepspeed, ray
     and beaker at module load and none of them is installed or in the offline wheelhouse."""
     why = ("reference finetune.py needs accelerate+deepspeed (+ray, peft, beaker-py, olmo-core) which are not "
-           "installed and not in /opt/wheelhouse; pip --no-deps install of the reference yields no importable module")
+           "installed and not in the offline wheel folder; pip --no-deps install of the reference yields no importable module")
     try:
         sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref"))
         import importlib
@@ -191,6 +197,10 @@ def main():
     if args.impl == "reference":
         reference_arm(args)
         return 0
+    if args.impl == "hf_stack":
+        from open_instruct_b200.utils.hf_stack_bench import run as run_hf_stack
+
+        return run_hf_stack(args)
     if args.task == "dpo":
         return run_dpo(args)
     import torch

@@ -195,6 +195,7 @@ class Learner:
                 norm = self.z3.step(lr=self.lr(), grad_scale=grad_scale)
             self._accum = 0
             self.global_step += 1
+            self._check_kernel_status()
             return norm
         grad = self.model.grad_flat()
         if grad is None:
@@ -215,7 +216,19 @@ class Learner:
             self.model.flat.grad = None
         self._accum = 0
         self.global_step += 1
+        self._check_kernel_status()
         return norm
+
+    def _check_kernel_status(self) -> None:
+        """Every optimizer step ends by reading the status word of the bounded device waits, so that a peer that never
+        arrived (the reduce-scatter then summed unfinished buffers) raises here - before the next step runs and before a
+        checkpoint of the diverged state can be written.  Ranks that wait on peers read it now (one small device
+        synchronisation per optimizer step); a single rank only has its own pipeline waits and uses the non-blocking form."""
+        if self.ops != "fused":
+            return
+        from .ops import lib
+
+        lib.check_status(sync=self.world > 1 or self.sp > 1 or self.tp is not None)
 
     # ------------------------------------------------------------------ whole-model views (loading, saving, weight sync)
     def _tp_shard_of(self, full: torch.Tensor | None, dtype, seed: int) -> torch.Tensor:

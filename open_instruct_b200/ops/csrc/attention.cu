@@ -623,11 +623,10 @@ extern "C" int b200_attn_fwd(const void* qkv, const int* cu_seqlens, void* out, 
   int r = attn_tmap(&tm, qkv, T, static_cast<long long>(Hq + 2 * Hkv) * DH);
   if (r) return 10000 + r;
   const int smem = sizeof(FwdSmem) + 1024;
-  static bool cfg = false;
-  if (!cfg) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static std::atomic<unsigned long long> cfg{0};
+  {
+    cudaError_t e = opt_in_shared_memory(attn_fwd_kernel, smem, cfg);
     if (e != cudaSuccess) return static_cast<int>(e);
-    cfg = true;
   }
   dim3 grid(max_tiles, Hq);
   attn_fwd_kernel<<<grid, ATT_THREADS, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
@@ -660,11 +659,10 @@ extern "C" int b200_attn_bwd(const void* qkv, const void* out, const void* d_out
   r = attn_tmap(&tdo, d_out, T, static_cast<long long>(Hq) * DH);
   if (r) return 20000 + r;
   const int smem = sizeof(BwdSmem) + 1024;
-  static bool cfg = false;
-  if (!cfg) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static std::atomic<unsigned long long> cfg{0};
+  {
+    cudaError_t e = opt_in_shared_memory(attn_bwd_kernel, smem, cfg);
     if (e != cudaSuccess) return static_cast<int>(e);
-    cfg = true;
   }
   dim3 grid(max_tiles, Hkv);
   attn_bwd_kernel<<<grid, BWD_THREADS, smem, st>>>(tq, tdo, cu_seqlens, B, Hq, Hkv, lse, delta, dq_acc,

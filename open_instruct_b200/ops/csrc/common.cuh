@@ -239,8 +239,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }  // namespace b200
 
 // ---------------------------------------------------------------- host side
+#include <atomic>
 #include <cstdio>
 namespace b200 {
+// Kernel function attributes (the opt-in to more than 48 KB of dynamic shared memory) are kept per DEVICE, not per
+// process: a kernel launched on a second GPU of the same process needs its own opt-in.  `done` is a per-call-site
+// bit mask of the devices that already have it (devices above 63 simply repeat the cheap call).
+template <typename Kernel>
+inline cudaError_t opt_in_shared_memory(Kernel kern, int bytes, std::atomic<unsigned long long>& done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && ((done.load(std::memory_order_relaxed) >> dev) & 1ull)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && dev < 64) done.fetch_or(1ull << dev, std::memory_order_relaxed);
+  return e;
+}
 // cuTensorMapEncodeTiled resolved at run time so the library has no link-time libcuda dependency.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -516,10 +516,10 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* res, const void* w, v
   if (T <= 0) return 0;
   if (D % 8) return -1;
   const int threads = D >= 2048 ? 256 : 128;
-  static bool cfg = false;
-  if (!cfg) {
-    cudaFuncSetAttribute(rmsnorm_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    cfg = true;
+  static std::atomic<unsigned long long> cfg{0};
+  {
+    cudaError_t e = opt_in_shared_memory(rmsnorm_fwd_kernel<false>, 64 * 1024, cfg);
+    if (e != cudaSuccess) return static_cast<int>(e);
   }
   if (D * 4 > 64 * 1024) return -2;
   rmsnorm_fwd_kernel<false><<<T, threads, D * sizeof(float), ST(stream)>>>(x, CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps);
@@ -532,10 +532,10 @@ extern "C" int b200_rmsnorm_fwd_acc32(float* x32, const void* res, const void* w
   if (T <= 0) return 0;
   if (D % 8 || D * 4 > 64 * 1024) return -1;
   const int threads = D >= 2048 ? 256 : 128;
-  static bool cfg = false;
-  if (!cfg) {
-    cudaFuncSetAttribute(rmsnorm_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    cfg = true;
+  static std::atomic<unsigned long long> cfg{0};
+  {
+    cudaError_t e = opt_in_shared_memory(rmsnorm_fwd_kernel<true>, 64 * 1024, cfg);
+    if (e != cudaSuccess) return static_cast<int>(e);
   }
   rmsnorm_fwd_kernel<true><<<T, threads, D * sizeof(float), ST(stream)>>>(x32, CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps);
   return static_cast<int>(cudaGetLastError());
@@ -571,10 +571,10 @@ extern "C" int b200_rmsnorm_bwd(const void* h, const void* w, const float* rstd,
                                 void* dx, float* dw_partial, float* dw_out, int T, int D, void* stream) {
   if (T <= 0) return 0;
   if (D % 8 || D * 4 > 64 * 1024) return -1;
-  static bool cfg = false;
-  if (!cfg) {
-    cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    cfg = true;
+  static std::atomic<unsigned long long> cfg{0};
+  {
+    cudaError_t e = opt_in_shared_memory(rmsnorm_bwd_kernel, 64 * 1024, cfg);
+    if (e != cudaSuccess) return static_cast<int>(e);
   }
   launch_rmsnorm_bwd(h, w, rstd, dy, dres, dx, dw_partial, dw_out, T, D, b200_rmsnorm_bwd_ctas(T), ST(stream));
   return static_cast<int>(cudaGetLastError());

@@ -311,11 +311,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, 
                   int* status, cudaStream_t stream, int max_ctas, int splits = 1) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT, BN_T, STAGES_T>;
   constexpr int smem = STAGES_T * (A_STAGE_BYTES + BN_T * BK * 2) + 1024 /*align*/ + 256 /*barriers*/;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static std::atomic<unsigned long long> configured{0};
+  {
+    cudaError_t e = opt_in_shared_memory(kern, smem, configured);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   const int num_kb = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;

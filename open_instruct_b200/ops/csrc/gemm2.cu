@@ -417,11 +417,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, 
                   int* status, cudaStream_t stream, int max_ctas, const long long* scatter = nullptr, int row_off = 0,
                   const long long* scatter2 = nullptr) {
   auto kern = gemm2_kernel<A_MN, B_MN, OUT>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  static std::atomic<unsigned long long> configured{0};
+  {
+    cudaError_t e = opt_in_shared_memory(kern, SMEM, configured);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];

@@ -20,13 +20,15 @@
 namespace b200 {
 
 // One thread per peer: publish my arrival in the peer's pad, then wait for the peer's in mine.
+// `slot`: first pad word of the flag row used (PAD_BARRIER, or PAD_BARRIER_SIDE for barriers issued on a second stream:
+// the wait is "flag >= epoch", so two streams must not share a row).
 __global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, long long limit_cycles,
-                                    int* __restrict__ status) {
+                                    int* __restrict__ status, int slot) {
   const int peer = threadIdx.x;
   if (peer >= world) return;
   __threadfence_system();
-  st_release_sys(reinterpret_cast<uint32_t*>(pads.p[peer]) + PAD_BARRIER + rank, epoch);
-  if (!wait_epoch(reinterpret_cast<const uint32_t*>(pads.p[rank]) + PAD_BARRIER + peer, epoch, limit_cycles))
+  st_release_sys(reinterpret_cast<uint32_t*>(pads.p[peer]) + slot + rank, epoch);
+  if (!wait_epoch(reinterpret_cast<const uint32_t*>(pads.p[rank]) + slot + peer, epoch, limit_cycles))
     atomicCAS(status, 0, ST_TIMEOUT_PEER);
 }
 
@@ -78,29 +80,62 @@ __device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
 }
 
 // out[i] = sum_r grads_r[lo + i],  i in [0, n);  sumsq += sum out[i]^2.   n % 4 == 0.
+// P2P variant: a peer load takes a few microseconds over NVLink, so the achieved rate is (bytes in flight) / latency.
+// Every thread therefore issues the loads of ALL ranks for U vectors (up to 16 independent 16-byte loads) before the
+// first add; the adds then run in fixed rank order, which keeps the sum bitwise identical from run to run.
+// MULTIMEM variant: one `multimem.ld_reduce` returns the sum over all ranks (the NVSwitch adds), so the owner's ingress
+// carries n floats instead of world * n.
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(256)
-zero_reduce_scatter_kernel(PeerPtrs grads, const float* __restrict__ mc_grads, int rank, int world, long long lo,
+zero_reduce_scatter_kernel(PeerPtrs grads, const float* __restrict__ mc_grads, int world, long long lo,
                            long long n, float* __restrict__ out, float* __restrict__ sumsq) {
   __shared__ float red[8];
+  constexpr int U = 2;
   float ss = 0.f;
   const long long nv = n / 4;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float4 acc;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nv; i0 += stride * U) {
     if (MULTIMEM) {
-      acc = multimem_ld_reduce_f32x4(mc_grads + lo + i * 4);
+      float4 a[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nv) a[u] = multimem_ld_reduce_f32x4(mc_grads + lo + i * 4);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nv) {
+          reinterpret_cast<float4*>(out)[i] = a[u];
+          ss += a[u].x * a[u].x + a[u].y * a[u].y + a[u].z * a[u].z + a[u].w * a[u].w;
+        }
+      }
     } else {
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      // fixed rank order keeps the sum bitwise identical from run to run
-#pragma unroll 1
-      for (int r = 0; r < world; ++r) {
-        const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      uint4 x[U][MAX_PEERS];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+#pragma unroll
+        for (int r = 0; r < MAX_PEERS; ++r)
+          if (r < world && i < nv)
+            x[u][r] = ld_volatile_u4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nv) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int r = 0; r < MAX_PEERS; ++r)
+            if (r < world) {
+              acc.x += __uint_as_float(x[u][r].x); acc.y += __uint_as_float(x[u][r].y);
+              acc.z += __uint_as_float(x[u][r].z); acc.w += __uint_as_float(x[u][r].w);
+            }
+          reinterpret_cast<float4*>(out)[i] = acc;
+          ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+        }
       }
     }
-    reinterpret_cast<float4*>(out)[i] = acc;
-    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -178,7 +213,18 @@ extern "C" int b200_symm_barrier(const void* const* pad_ptrs, int rank, int worl
   if (world > MAX_PEERS) return -1;
   const long long cycles = static_cast<long long>(limit_ms) * 1900000LL;
   symm_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_ptrs(pad_ptrs, world), rank, world,
-                                                                         epoch, cycles, status);
+                                                                         epoch, cycles, status, PAD_BARRIER);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The same barrier on its own flag row, for a second stream that runs beside the one using `b200_symm_barrier`
+// (the gradient exchange that overlaps the backward pass).  Epochs of the two rows count independently.
+extern "C" int b200_symm_barrier_side(const void* const* pad_ptrs, int rank, int world, unsigned epoch, int limit_ms,
+                                      int* status, void* stream) {
+  if (world > MAX_PEERS) return -1;
+  const long long cycles = static_cast<long long>(limit_ms) * 1900000LL;
+  symm_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_ptrs(pad_ptrs, world), rank, world,
+                                                                         epoch, cycles, status, PAD_BARRIER_SIDE);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -312,22 +358,30 @@ extern "C" int b200_reduce_scatter_add(const void* const* ws_ptrs, const void* m
   return static_cast<int>(cudaGetLastError());
 }
 
+// out[0 .. n) = sum over ranks of grads_r[lo .. lo+n); sumsq[0] += |out|^2 (the caller zeroes it once per step).
+// `ctas` <= 0: a grid that fills the GPU; a smaller grid leaves SMs to kernels running beside it on another stream.
+extern "C" int b200_zero_reduce_range(const void* const* grad_ptrs, const void* mc_grads, int world, long long lo,
+                                      long long n, float* out, float* sumsq, int use_multimem, int ctas, void* stream) {
+  if (world > MAX_PEERS || n % 4 || lo % 4) return -1;
+  if (n == 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = ctas > 0 ? ctas : 148 * 4;
+  if (use_multimem && mc_grads)
+    zero_reduce_scatter_kernel<true><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world),
+                                                            reinterpret_cast<const float*>(mc_grads), world, lo, n, out, sumsq);
+  else
+    zero_reduce_scatter_kernel<false><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world), nullptr, world, lo, n, out, sumsq);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // out_shard[n] = sum over ranks of grads_r[lo .. lo+n); sumsq[0] = |out_shard|^2 (overwritten).
 extern "C" int b200_zero_reduce_scatter(const void* const* grad_ptrs, const void* mc_grads, int rank, int world,
                                         long long lo, long long n, float* out_shard, float* sumsq, int use_multimem,
                                         void* stream) {
-  if (world > MAX_PEERS || n % 4) return -1;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  cudaMemsetAsync(sumsq, 0, sizeof(float), st);
-  const int grid = 148 * 8;
-  if (use_multimem && mc_grads)
-    zero_reduce_scatter_kernel<true><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world),
-                                                            reinterpret_cast<const float*>(mc_grads), rank, world, lo, n,
-                                                            out_shard, sumsq);
-  else
-    zero_reduce_scatter_kernel<false><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world), nullptr, rank, world, lo, n,
-                                                             out_shard, sumsq);
-  return static_cast<int>(cudaGetLastError());
+  (void)rank;
+  cudaError_t e = cudaMemsetAsync(sumsq, 0, sizeof(float), reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return b200_zero_reduce_range(grad_ptrs, mc_grads, world, lo, n, out_shard, sumsq, use_multimem, 0, stream);
 }
 
 extern "C" int b200_zero_adamw_allgather(float* master, float* m, float* v, const float* grad,

@@ -133,10 +133,31 @@ def status_word(device=None) -> torch.Tensor:
     return t
 
 
+_status_host = {}
+
+
 def check_status(sync: bool = True) -> None:
-    """Raise ``KernelError`` when any kernel recorded a timed-out wait (synchronises the device)."""
+    """Raise ``KernelError`` when any kernel recorded a timed-out wait.
+
+    ``sync=True`` reads the status word now (synchronises the device).  ``sync=False`` never blocks: it looks at the copy
+    of the word that the PREVIOUS non-blocking call queued (raising if that copy has arrived and is non-zero) and queues
+    a fresh copy into pinned host memory behind the work submitted so far, so a failure surfaces one call later."""
     for key, t in _status.items():
-        code = int(t.item()) if sync else 0
+        if sync:
+            code = int(t.item())
+        else:
+            slot = _status_host.get(key)
+            if slot is None:
+                slot = _status_host[key] = [torch.zeros(1, dtype=torch.int32, pin_memory=True), torch.cuda.Event(), False]
+            host, ev, pending = slot
+            code = 0
+            if pending and ev.query():
+                code = int(host[0])
+            if not pending or ev.query():
+                with torch.cuda.device(t.device):
+                    host.copy_(t, non_blocking=True)
+                    ev.record(torch.cuda.current_stream(t.device))
+                slot[2] = True
         if code:
             t.zero_()
             raise KernelError(f"kernel on cuda:{key} gave up a bounded wait (status {code})")

@@ -17,7 +17,7 @@ Everything that moves data is done by this package's own kernels
 ``use_multimem=True`` switches the two data kernels to ``multimem.ld_reduce`` / ``multimem.st`` through
 the NVSwitch when the allocation has a multicast address.  Waits on peers are bounded
 (``peer_timeout_ms``): a rank whose peer never arrives gets ``ST_TIMEOUT_PEER`` in the status word and
-an exception at the next ``lib.check_status()`` instead of a hung GPU.
+an exception at the end of that optimizer step (``Learner.optimizer_step`` reads the status word) instead of a hung GPU.
 """
 
 from __future__ import annotations

@@ -4,7 +4,10 @@
 
 Reports achieved TFLOP/s or GB/s per kernel and the fraction of the measured peaks found in
 ``MEASURED_PEAKS.json`` at the repository root (copy bandwidth and cuBLAS bf16 GEMM throughput).
-With ``--cublas`` the same GEMM shapes are also timed through ``torch.matmul`` for comparison.
+With ``--cublas`` the same GEMM shapes are also timed through ``torch.matmul`` for comparison.  With ``--library`` every
+kernel family is also timed through the library the reference's trainer reaches for the same op on the same inputs
+(``torch.matmul`` = cuBLAS, ``flash_attn_varlen_func`` = FlashAttention-2, liger fused-linear-cross-entropy, ATen
+``_fused_adamw_``), each row named ``lib_*``; a library that does not import is reported and skipped.
 """
 
 from __future__ import annotations
@@ -62,7 +65,10 @@ def main():
     ap.add_argument("--impl", default=None, help="GEMM kernel: 1cta | 2cta (default: library default)")
     ap.add_argument("--shapes", default="", help="GEMM: comma-separated subset of qkv,o,gate_up,down,lm_head")
     ap.add_argument("--doc_len", type=int, default=0, help="attention: document length (0 = one document of --tokens)")
+    ap.add_argument("--pack", default="", help="attention: 'loguniform' = documents with log-uniform lengths in [128, 4096] as in the SFT bench")
+    ap.add_argument("--library", action="store_true", help="also time the library kernel for each family (implies --cublas)")
     args = ap.parse_args()
+    args.cublas = args.cublas or args.library
     from open_instruct_b200.ops import fused, lib
 
     hbm, tf, src = _peaks()
@@ -117,6 +123,15 @@ def main():
     if not only or "attn" in only:
         L = args.doc_len or T
         lens = [L] * (T // L) + ([T % L] if T % L else [])
+        if args.pack == "loguniform":
+            from open_instruct_b200.data.synthetic import sft_pack
+
+            gen, lens = torch.Generator().manual_seed(0), []
+            while sum(lens) < T:
+                cu_h = sft_pack(4096, 1000, gen)["cu_seq_lens_q"].tolist()
+                lens += [b - a for a, b in zip(cu_h[:-1], cu_h[1:])]
+            lens, L = lens[: max(1, len(lens))], "loguniform"
+            T = sum(lens)
         cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
         qkv = bf(T, (Hq + 2 * Hkv) * Dh)
         scale = Dh ** -0.5
@@ -125,6 +140,24 @@ def main():
         fl = sum(4.0 * l * l * Dh * Hq / 2 for l in lens)  # causal: half of the full score matrix
         rec(f"attn_fwd_L{L}", time_op(lambda: fused.attn_fwd(qkv, cu, Hq, Hkv, Dh, scale), args.iters), fl)
         rec(f"attn_bwd_L{L}", time_op(lambda: fused.attn_bwd(qkv, out, d_out, lse, cu, Hq, Hkv, Dh, scale), args.iters), 2.5 * fl)
+        if args.library:
+            try:
+                from flash_attn import flash_attn_varlen_func
+
+                q = qkv[:, : Hq * Dh].reshape(T, Hq, Dh).contiguous().requires_grad_(True)
+                k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].reshape(T, Hkv, Dh).contiguous().requires_grad_(True)
+                v = qkv[:, (Hq + Hkv) * Dh:].reshape(T, Hkv, Dh).contiguous().requires_grad_(True)
+                mx = max(lens)
+                fa = lambda: flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, softmax_scale=scale, causal=True)
+                with torch.no_grad():
+                    rec(f"lib_flash_attn2_fwd_L{L}", time_op(fa, args.iters), fl)
+                o = fa()
+                do = d_out.view(T, Hq, Dh)
+                rec(f"lib_flash_attn2_bwd_L{L}", time_op(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True), args.iters), 2.5 * fl)
+                del o, q, k, v
+            except Exception as e:  # noqa: BLE001
+                print({"kernel": "lib_flash_attn2", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}, flush=True)
+        T = args.tokens
     if not only or "elementwise" in only:
         x, r, w = bf(T, D), bf(T, D), bf(D)
         rec("rmsnorm_fwd_res", time_op(lambda: fused.rmsnorm_fwd(x, w, 1e-5, res=r), args.iters), bytes_=T * D * 2 * 4)
@@ -147,11 +180,55 @@ def main():
         lp, lse, _ = fused.logprob_fwd(logits, labels)
         g = torch.ones(T, device="cuda")
         rec("logprob_bwd", time_op(lambda: fused.logprob_bwd_(logits, labels, lse, g), args.iters), bytes_=T * V * 2 * 2)
+        if args.library:
+            # lm_head GEMM + log-softmax + label gather, forward and backward, against liger's fused-linear-CE
+            h = bf(T, D).requires_grad_(True)
+            w = (bf(V, D) * 0.02).requires_grad_(True)
+            lab2 = labels.clone()
+
+            def ours_head():
+                lg = fused.gemm(h.detach(), w.detach())
+                lp2, lse2, _ = fused.logprob_fwd(lg, lab2)
+                dl = fused.logprob_bwd_(lg, lab2, lse2, g)
+                gw = torch.empty(V, D, device="cuda")
+                fused.gemm(dl, h.detach(), gw, a_mn=True, b_mn=True, out_mode=fused.OUT_F32)
+                return fused.gemm(dl, w.detach(), b_mn=True)
+
+            fl_head = 3 * 2.0 * T * V * D
+            rec("lm_head_logprob_fwd_bwd", time_op(ours_head, args.iters), fl_head)
+            try:
+                from liger_kernel.transformers.functional import liger_fused_linear_cross_entropy
+
+                def liger_head():
+                    loss = liger_fused_linear_cross_entropy(h, w, lab2)
+                    return torch.autograd.grad(loss, (h, w))
+
+                rec("lib_liger_flce_fwd_bwd", time_op(liger_head, args.iters), fl_head)
+            except Exception as e:  # noqa: BLE001
+                print({"kernel": "lib_liger_flce", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}, flush=True)
+
+            def torch_head():
+                lg = torch.matmul(h, w.t()).float()
+                loss = torch.nn.functional.cross_entropy(lg, lab2)
+                return torch.autograd.grad(loss, (h, w))
+
+            rec("lib_torch_linear_ce_fwd_bwd", time_op(torch_head, args.iters), fl_head)
+            del h, w
+        del logits
         n = 1 << 28
         ma, m_, v_, gr = (torch.zeros(n, device="cuda") for _ in range(4))
         p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
         rec("adamw", time_op(lambda: fused.adamw(ma, m_, v_, gr, p16, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, step=1), args.iters),
             bytes_=n * (4 * 4 + 3 * 4 + 2 + 4))
+        if args.library:
+            st = torch.tensor(1.0, device="cuda")
+
+            def torch_adamw():
+                torch._fused_adamw_([ma], [gr], [m_], [v_], [], [st], lr=1e-3, beta1=0.9, beta2=0.999, weight_decay=0.0, eps=1e-8,
+                                    amsgrad=False, maximize=False)
+                p16.copy_(ma)  # the bf16 working copy the trainer refreshes after the fp32 update
+
+            rec("lib_torch_fused_adamw_plus_bf16_copy", time_op(torch_adamw, args.iters), bytes_=n * (4 * 4 + 3 * 4 + 2 + 4))
     lib.check_status()
     if args.json:
         json.dump({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}, "tokens": T, "rows": rows}, open(args.json, "w"), indent=1)
