@@ -121,10 +121,10 @@ def run_dpo(args) -> int:
 
     def step(mbs):
         ntok = 0
-        for mb in mbs:
+        for k, mb in enumerate(mbs):
             pc, pr, aux = concatenated_forward(learner, mb, average_log_prob=True)
             losses, _, _ = compute_loss(dcfg, mb, pc, pr, cache, (aux["chosen_tokens"], aux["rejected_tokens"]))
-            learner.backward(losses.mean())
+            learner.backward(losses.mean(), last=(k == len(mbs) - 1))
             ntok += mb["chosen_input_ids"].numel() + mb["rejected_input_ids"].numel()
         learner.optimizer_step()
         return losses.mean().detach(), ntok

@@ -45,7 +45,9 @@ def set_rng_state(st: dict) -> None:
             pass
 
 
-def save_train_state(ckpt_dir: str, optimizer, trainer_state: dict, group=None) -> None:
+def save_train_state(ckpt_dir: str, optimizer, trainer_state: dict, group=None, before_complete=None) -> None:
+    """``before_complete(ckpt_dir)`` runs on rank 0 after the regular files and before the ``COMPLETED`` marker: state
+    that lives beside the optimizer (LoRA adapters and their moments) is written there, so a marked directory is whole."""
     rank, world = pdist.rank(group), pdist.world_size(group)
     os.makedirs(ckpt_dir, exist_ok=True)
     sd = optimizer.state_dict()
@@ -57,6 +59,8 @@ def save_train_state(ckpt_dir: str, optimizer, trainer_state: dict, group=None) 
         with open(tmp, "w") as fh:
             json.dump(trainer_state, fh, indent=2, default=str)
         os.replace(tmp, os.path.join(ckpt_dir, "trainer_state.json"))
+        if before_complete is not None:
+            before_complete(ckpt_dir)
     pdist.barrier(group)
     if rank == 0:
         with open(os.path.join(ckpt_dir, "COMPLETED"), "w") as fh:

@@ -190,13 +190,13 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
                 break
             step_t0 = time.time()
             lengths = []
-            for mb in mbs:
+            for k, mb in enumerate(mbs):
                 mb = to_device(mb, device)
                 pc, pr, aux = forward_fn(learner, mb, average_log_prob=average)
                 losses, c_rew, r_rew = compute_loss(args, mb, pc, pr, reference_cache,
                                                     (aux["chosen_tokens"], aux["rejected_tokens"]))
                 loss = losses.mean()
-                learner.backward(loss)
+                learner.backward(loss, last=(k == len(mbs) - 1))
                 metrics.add("train_loss", loss.detach() / len(mbs))
                 metrics.add("logps/chosen", pc.detach().mean() / len(mbs))
                 metrics.add("logps/rejected", pr.detach().mean() / len(mbs))

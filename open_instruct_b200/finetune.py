@@ -218,8 +218,8 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
         collator.max_seq_length = args.max_seq_length  # loader packs to this token budget; collator pads the row up to it
     sp = args.sequence_parallel_size
     if sp > 1:
-        if sp != world or not args.packing or args.max_seq_length % sp:
-            raise ValueError("sequence_parallel_size must equal the number of ranks, with --packing and max_seq_length divisible by it")
+        if world % sp or not args.packing or args.max_seq_length % sp:
+            raise ValueError("sequence_parallel_size must divide the number of ranks, with --packing and max_seq_length divisible by it")
     tp = max(1, args.tensor_parallel_degree)
     if tp > 1 and (sp > 1 or world % tp):
         raise ValueError("tensor_parallel_degree must divide the number of ranks and excludes sequence parallelism")
@@ -261,6 +261,8 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
     ckpt = get_last_checkpoint_path(args.output_dir, args.resume_from_checkpoint)
     if ckpt and is_checkpoint_folder(ckpt):
         st = load_train_state(ckpt, learner.opt)
+        if lora is not None:
+            lora.load_state(ckpt)  # adapters + their AdamW moments; raises when the checkpoint has none
         completed, start_epoch = st["completed_steps"], st["epoch"]
         learner.global_step = completed
         loader.load_state_dict(st["loader"])
@@ -270,7 +272,8 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
 
     def save_ckpt(tag: str, epoch: int):
         d = os.path.join(args.output_dir, tag)
-        save_train_state(d, learner.opt, {"completed_steps": completed, "epoch": epoch, "loader": loader.state_dict()})
+        save_train_state(d, learner.opt, {"completed_steps": completed, "epoch": epoch, "loader": loader.state_dict()},
+                         before_complete=lora.save_state if lora is not None else None)
         if is_main:
             clean_last_n_checkpoints(args.output_dir, args.keep_last_n_checkpoints)
 

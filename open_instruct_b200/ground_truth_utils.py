@@ -198,9 +198,18 @@ class IFEvalVerifier(VerifierFunction):
     def __call__(self, tokenized_prediction, prediction, label, query=None, rollout_state=None):
         from .if_functions import check_instruction
 
-        spec = json.loads(label) if isinstance(label, str) else label
+        spec = label
+        if isinstance(spec, str):
+            try:
+                spec = json.loads(spec)
+            except ValueError:  # datasets store the label as a Python literal (``open_instruct/ground_truth_utils.py:332``)
+                import ast
+
+                spec = ast.literal_eval(spec)
         if isinstance(spec, list):
             spec = spec[0]
+        if isinstance(spec, str):
+            spec = json.loads(spec)
         ids, kws = spec.get("instruction_id", []), spec.get("kwargs", [])
         answer = remove_thinking_section(prediction)
         if not ids or not answer:

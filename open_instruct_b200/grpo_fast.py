@@ -63,14 +63,31 @@ WEIGHT_SYNC_TIMEOUT_S = 120
 
 
 # ======================================================================================= learner step
-def _packed_batch(data: CollatedBatchData, i: int, device) -> dict:
+def _packed_batch(data: CollatedBatchData, i: int, device, pad_multiple: int = 1, pad_token_id: int = 0) -> dict:
+    """Model inputs of packed micro-batch ``i``.  ``pad_multiple`` > 1 (sequence parallelism) appends one fully masked
+    document so that the token count divides evenly over the ranks of the group."""
     qr = data.query_responses[i].to(device, non_blocking=True)
+    pos = data.position_ids[i].to(device, non_blocking=True)
+    cu = data.cu_seqlens[i].to(device, non_blocking=True)
+    T = qr.numel()
     labels = torch.full_like(qr, -100)
     labels[:-1] = qr[1:]
-    cu = data.cu_seqlens[i].to(device, non_blocking=True)
     labels[cu[1:].long() - 1] = -100  # the last token of a document has no target
-    return {"input_ids": qr, "position_ids": data.position_ids[i].to(device, non_blocking=True), "cu_seq_lens_q": cu,
-            "labels_shifted": labels}
+    extra = (-T) % pad_multiple
+    if extra:
+        qr = torch.cat([qr, qr.new_full((extra,), pad_token_id)])
+        pos = torch.cat([pos, torch.arange(extra, device=device, dtype=pos.dtype)])
+        labels = torch.cat([labels, labels.new_full((extra,), -100)])
+        cu = torch.cat([cu, cu.new_tensor([T + extra])])
+    return {"input_ids": qr, "position_ids": pos, "cu_seq_lens_q": cu, "labels_shifted": labels}
+
+
+def _to_label_space(x: torch.Tensor, fill, total: int) -> torch.Tensor:
+    """``y[t] = x[t + 1]``: a per-token quantity moved to the position that PREDICTS the token (where the model's
+    log-prob of it lives), padded with ``fill`` up to ``total`` entries."""
+    y = x.new_full((total,), fill)
+    y[: x.numel() - 1] = x[1:]
+    return y
 
 
 def forward_for_logprobs(learner: Learner, batch: dict, temperature: float, want_entropy: bool = False):
@@ -97,21 +114,44 @@ def grpo_train_step(learner: Learner, data: CollatedBatchData, args: GRPOExperim
         return {}
     accumulation_steps = max(1, math.ceil(n / args.num_mini_batches - 0.5))
     usable = (n // accumulation_steps) * accumulation_steps
-    batches = [_packed_batch(data, i, dev) for i in range(usable)]
-    resp_masks = [data.response_masks[i].to(dev) for i in range(usable)]
+    # Sequence parallelism: every rank of a group sees the same packs and computes log-probs for its chunk of the positions.
+    # The per-token quantities are therefore kept in LABEL space (entry t belongs to the token at t + 1, scored at position
+    # t) instead of being shifted after the forward pass, which would need the neighbour's last entry; then each is cut to
+    # this rank's chunk.  Response tokens never open a document, so no response entry is lost by the shift.
+    sp = getattr(learner, "sp", 1)
+    label_space = sp > 1 or getattr(args, "_force_label_space", False)
+    if label_space and (args.rho_mask_sequence_level or args.rho_mask_tv_divergence):
+        raise NotImplementedError("sequence-level rho masking needs whole sequences on one rank: not available with sequence parallelism")
+    batches = [_packed_batch(data, i, dev, pad_multiple=sp) for i in range(usable)]
+
+    def per_token(col, i, fill):
+        t = col[i].to(dev)
+        if not label_space:
+            return t
+        return learner.local_slice(_to_label_space(t, fill, batches[i]["input_ids"].numel()))
+
+    def logprobs_of(lrn, i, want_entropy=False):
+        if not label_space:
+            return forward_for_logprobs(lrn, batches[i], args.temperature, want_entropy)
+        lp, ent = lrn.token_logprobs(batches[i], args.temperature, want_entropy)
+        valid = learner.local_slice(batches[i]["labels_shifted"] >= 0)
+        return torch.where(valid, lp, torch.full_like(lp, INVALID_LOGPROB)), ent
+
+    resp_masks = [per_token(data.response_masks, i, 0) for i in range(usable)]
     resp_bool = [m > 0 for m in resp_masks]
-    advantages = [data.advantages[i].to(dev) for i in range(usable)]
-    vllm_lp = [mask_logprobs(data.vllm_logprobs[i].to(dev), resp_bool[i]) for i in range(usable)]
+    advantages = [per_token(data.advantages, i, 0.0) for i in range(usable)]
+    vllm_raw = [per_token(data.vllm_logprobs, i, float("nan")) for i in range(usable)]
+    vllm_lp = [mask_logprobs(vllm_raw[i], resp_bool[i]) for i in range(usable)]
     ref_lp = [None] * usable
     if ref_learner is not None:
         with torch.no_grad():
             for i in range(usable):
-                ref_lp[i], _ = forward_for_logprobs(ref_learner, batches[i], args.temperature)
+                ref_lp[i], _ = logprobs_of(ref_learner, i)
     old_cache: list = [None] * usable
     if args.num_mini_batches > 1:
         with torch.no_grad():
             for i in range(usable):
-                old_cache[i] = vllm_lp[i] if args.use_vllm_logprobs else forward_for_logprobs(learner, batches[i], args.temperature)[0]
+                old_cache[i] = vllm_lp[i] if args.use_vllm_logprobs else logprobs_of(learner, i)[0]
     if args.loss_denominator == "token":
         denoms = calculate_token_counts(accumulation_steps, resp_bool, dev, group)
     else:
@@ -122,7 +162,7 @@ def grpo_train_step(learner: Learner, data: CollatedBatchData, args: GRPOExperim
     grad_norms = []
     for epoch in range(args.num_epochs):
         for i in range(usable):
-            new_lp, ent = forward_for_logprobs(learner, batches[i], args.temperature, args.record_entropy)
+            new_lp, ent = logprobs_of(learner, i, args.record_entropy)
             mask = resp_bool[i]
             new_lp = torch.where(mask, new_lp, torch.full_like(new_lp, INVALID_LOGPROB))
             old = resolve_old_logprob(old_cache, i, epoch, args.num_mini_batches, args.use_vllm_logprobs, vllm_lp[i], new_lp)
@@ -134,7 +174,7 @@ def grpo_train_step(learner: Learner, data: CollatedBatchData, args: GRPOExperim
             # summed over the group's tokens on ALL ranks / global token count; the optimizer averages over
             # ranks, hence the factor world (same convention as the reference with DeepSpeed)
             loss = masked_mean(pg + args.beta * kl, mask, None, denom) * world
-            learner.backward(loss)
+            learner.backward(loss, last=(i + 1) % accumulation_steps == 0)
             with torch.no_grad():
                 stats["pg"].append(masked_mean(pg, mask))
                 stats["kl"].append(masked_mean(kl, mask))
@@ -144,7 +184,7 @@ def grpo_train_step(learner: Learner, data: CollatedBatchData, args: GRPOExperim
                 if ent is not None:
                     stats["entropy"].append(masked_mean(ent, mask))
                 if epoch == 0:
-                    stats["lpdiff"].append(compute_vllm_local_debug_metrics(new_lp.detach(), data.vllm_logprobs[i].to(dev), mask))
+                    stats["lpdiff"].append(compute_vllm_local_debug_metrics(new_lp.detach(), vllm_raw[i], mask))
                 for k, v in rho.metrics.items():
                     rho_stats.setdefault(k, []).append(masked_mean(v, mask))
             if (i + 1) % accumulation_steps == 0:
@@ -337,24 +377,76 @@ class EngineWorker:
         if not self.thread.is_alive() and not self.shutdown_flag.is_set():
             raise RuntimeError("engine loop is not running")
 
+    # ---- control surface of the reference's engine actor (``open_instruct/vllm_utils.py:781-843``)
+    def sleep(self) -> None:
+        """Pause generation between engine steps and keep everything resident (the reference's ``sleep(level=0,
+        mode="keep")``): returns once the step that was running has finished; no new step starts until ``wake_up``."""
+        self.should_stop.set()
+        self._paused = True
+        with self.lock:  # the loop holds the lock while it steps: taking it once means that step is over
+            pass
+
+    def wake_up(self) -> None:
+        self._paused = False
+        self.should_stop.clear()
+
+    def reset_prefix_cache(self) -> bool:
+        """Forget every cached prompt prefix (KV blocks shared between requests), as after a weight update: KV computed
+        with older weights must not be reused for new requests."""
+        with self.lock:
+            eng = self.engine._e if isinstance(self.engine, _TPLeader) else self.engine
+            return bool(eng.reset_prefix_cache())
+
+    def set_model_step(self, model_step: int) -> None:
+        """Stamp the policy version that new results report (staleness accounting in the data-preparation actor)."""
+        with self.lock:
+            (self.engine._e if isinstance(self.engine, _TPLeader) else self.engine).model_step = int(model_step)
+
+    def begin_weight_update(self) -> None:
+        """First half of a weight update whose data arrives from OUTSIDE this process (a learner storing through its
+        CUDA-IPC mapping of the parameter buffer): waits for the engine step that is running and keeps the next one from
+        starting until ``update_weights`` (or ``abort_weight_update``) ends the update, so no forward pass ever runs on
+        half-old, half-new weights.  Requests in flight keep their KV cache (``inflight_updates`` semantics) and continue
+        with the new weights at their next step; the reference likewise applies updates between engine steps."""
+        self.lock.acquire()
+        self._update_open = True
+
+    def abort_weight_update(self) -> None:
+        if getattr(self, "_update_open", False):
+            self._update_open = False
+            self.lock.release()
+
     def update_weights(self, flat, model_step: int) -> None:
         """In-process sync: copy ``flat`` into the engine's buffer (None: weights were already written
         into the buffer by a peer through its IPC mapping; only the version changes)."""
+        if getattr(self, "_update_open", False):  # opened by begin_weight_update: the lock is already held
+            try:
+                self._apply_update(flat, model_step)
+            finally:
+                self._update_open = False
+                self.lock.release()
+            return
+        if self.tp_size > 1 and self.tp_rank != 0:
+            self._apply_update(flat, model_step)
+            return
+        with self.lock:
+            self._apply_update(flat, model_step)
+
+    def _apply_update(self, flat, model_step: int) -> None:
+        """The update itself; the caller holds ``self.lock`` (tensor-parallel followers have no loop to exclude)."""
         if self.tp_size > 1:
             if self.tp_rank == 0:  # followers reshard when the leader's command reaches them, at the same point of the schedule
-                with self.lock:
-                    if flat is not None:
-                        self.full_flat.copy_(flat.to(self.full_flat.dtype))
-                    self.engine.send([("reshard", model_step)])
-                    self._reshard(model_step)
+                if flat is not None:
+                    self.full_flat.copy_(flat.to(self.full_flat.dtype))
+                self.engine.send([("reshard", model_step)])
+                self._reshard(model_step)
             elif flat is not None:
                 self.full_flat.copy_(flat.to(self.full_flat.dtype))
             return
-        with self.lock:
-            if flat is not None:
-                self.engine.update_weights(flat, model_step)
-            else:
-                self.engine.model_step = model_step
+        if flat is not None:
+            self.engine.update_weights(flat, model_step)
+        else:
+            self.engine.model_step = model_step
 
     def weights_checksum(self, expect_step: int | None = None) -> tuple[float, int, int]:
         """(sum of the weights this rank computes with, tp rank, tp size) - compared with the learner's after a sync.
@@ -410,8 +502,8 @@ class EngineWorker:
                                                       epoch_number=req.epoch_number)
                     self.pending[rid] = req
                     admitted = True
-                if self.should_stop.is_set() and not self.inflight_updates:
-                    time.sleep(0.005)  # paused for a weight update
+                if self.should_stop.is_set() and (not self.inflight_updates or getattr(self, "_paused", False)):
+                    time.sleep(0.005)  # paused for a weight update, or put to sleep
                     continue
                 if not self.engine.has_unfinished():
                     if not admitted:
@@ -521,7 +613,9 @@ class LearnerWorker:
                             max_grad_norm=args.max_grad_norm, lr_scheduler_type=args.lr_scheduler_type, warmup_steps=warm,
                             total_steps=max(1, num_training_steps * args.num_epochs * args.num_mini_batches),
                             gradient_checkpointing=model_config.gradient_checkpointing, seed=args.seed,
-                            offload_optimizer=args.deepspeed_offload_optimizer, shard_parameters=args.shard_parameters)
+                            offload_optimizer=args.deepspeed_offload_optimizer, shard_parameters=args.shard_parameters,
+                            sequence_parallel_size=max(1, args.sequence_parallel_size),
+                            sp_max_tokens=-(-getattr(args, "sp_max_tokens", 0) // max(1, args.sequence_parallel_size)) * max(1, args.sequence_parallel_size))
         self.learner = Learner(spec, cfg, device=self.device)
         src = model_config.model_name_or_path
         if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
@@ -667,6 +761,11 @@ def validate_configs(args: GRPOExperimentConfig, streaming: StreamingDataLoaderC
         raise ValueError("vllm_tensor_parallel_size must be 1, 2, 4 or 8")
     if args.single_gpu_mode and (args.world_size != 1 or vllm.vllm_num_engines != 1):
         raise ValueError("single_gpu_mode runs exactly one learner and one engine")
+    sp = max(1, args.sequence_parallel_size)
+    if args.world_size % sp:
+        raise ValueError(f"sequence_parallel_size {sp} must divide the number of learner ranks {args.world_size}")
+    if sp > 1 and streaming.num_unique_prompts_rollout * streaming.num_samples_per_prompt_rollout < args.world_size // sp:
+        raise ValueError("fewer rollouts per step than data-parallel learner groups")
 
 
 def submit_eval_prompts(eval_dataset, prompt_q, streaming: StreamingDataLoaderConfig, args: GRPOExperimentConfig, step: int, top_p: float = 1.0) -> int:
@@ -753,6 +852,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
 
     args = setup_runtime_variables(args, streaming)
     args.temperature = streaming.temperature
+    args.sp_max_tokens = streaming.pack_length * max(1, args.per_device_train_batch_size)  # largest packed micro-batch
     validate_configs(args, streaming, vllm)
     set_seed(args.seed)
     if tc.tokenizer_name_or_path is None:
@@ -788,7 +888,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
         prompt_q, results_q, eval_q = ray.Queue(local=True), ray.Queue(maxsize=qsize, local=True), ray.Queue(local=True)
         device = "cuda:0" if torch.cuda.is_available() else "cpu"
         learner = LearnerWorker.__new__(LearnerWorker)
-        LearnerWorker.__init__(learner, 0, 1, "127.0.0.1", 29512, spec, args, model_config, args.num_training_steps, device=device)
+        LearnerWorker.__init__(learner, 0, 1, "127.0.0.1", pdist.find_free_port(), spec, args, model_config, args.num_training_steps, device=device)
         engine = EngineWorker(spec, prompt_q, results_q, eval_q, reward_cfg, tokenizer, device=device, ops=args.ops, seed=args.seed,
                               max_model_len=max_len, num_blocks=None if torch.cuda.is_available() else 512,
                               gpu_memory_utilization=0.25 if torch.cuda.is_available() else 0.9,
@@ -801,7 +901,7 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
         cuda = torch.cuda.is_available()
         prompt_q, results_q, eval_q = ray.Queue(), ray.Queue(maxsize=qsize), ray.Queue()
         tc_plain = dataclasses.replace(tc)  # without the cached tokenizer object
-        port = 29600 + (os.getpid() % 200)
+        port = pdist.find_free_port()
         LW, EW = ray.remote(LearnerWorker), ray.remote(EngineWorker)
         from concurrent.futures import ThreadPoolExecutor
 
@@ -821,10 +921,11 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
         else:
             # every rank of a tensor-parallel engine is its own process on its own GPU; the ranks of one engine rendezvous in
             # __init__, so they are created together
+            tp_ports = [pdist.find_free_port() for _ in range(vllm.vllm_num_engines)]  # one rendezvous per engine
             with ThreadPoolExecutor(max_workers=tp * vllm.vllm_num_engines) as ex:
                 futs = [[ex.submit(EW.options(num_gpus=1, max_concurrency=8).remote, spec, prompt_q, results_q, eval_q, reward_cfg if r == 0 else None,
                                    tc_plain, "auto", args.ops, args.seed + 100 * i, max_len, None, vllm.vllm_gpu_memory_utilization, init_flat,
-                                   streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", port + 50 + i)
+                                   streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", tp_ports[i])
                          for r in range(tp)] for i in range(vllm.vllm_num_engines)]
                 handles = [[f.result() for f in row] for row in futs]
             engines = [row[0] for row in handles]
@@ -850,7 +951,14 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
         if single_objs:
             return sync_in_process(learners[0].flat_weights(), engines, step, total_params)
         if torch.cuda.is_available():
-            call_all(learners, "push_weights")
+            # the learners store straight into the engines' parameter buffers: every engine first finishes the step it is
+            # in and holds the next one back until the new version is complete
+            call_all(engines, "begin_weight_update")
+            try:
+                call_all(learners, "push_weights")
+            except BaseException:
+                call_all(engines, "abort_weight_update")
+                raise
             call_all(engines, "update_weights", None, step)
         else:
             flat = call(learners[0], "flat_weights_cpu")
@@ -860,7 +968,8 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
     manager = ActorManager({"prompts": prompt_q, "results": results_q, "eval": eval_q}, enable_dashboard=args.enable_queue_dashboard and not single,
                            port=args.queue_dashboard_port)
     manager.set_kv_cache_max_concurrency(call(engines[0], "get_kv_cache_info", max_len))
-    prep = DataPreparation(dataset, streaming, prompt_q, results_q, tokenizer, args.world_size, args.per_device_train_batch_size,
+    sp = max(1, args.sequence_parallel_size)  # the ranks of one sequence-parallel group train on the same packs
+    prep = DataPreparation(dataset, streaming, prompt_q, results_q, tokenizer, args.world_size // sp, args.per_device_train_batch_size,
                            args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p)
     resume_step = 0
     if args.checkpoint_state_dir and os.path.isdir(args.checkpoint_state_dir):
@@ -880,7 +989,8 @@ def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelCon
         for step in range(resume_step + 1, args.num_training_steps + 1):
             t_step = time.perf_counter()
             call_all(engines, "check_background_threads")
-            per_rank = [prep.get_data(r, step) for r in range(args.world_size)]
+            per_group = [prep.get_data(g, step) for g in range(args.world_size // sp)]
+            per_rank = [per_group[r // sp] for r in range(args.world_size)]
             prep_metrics = per_rank[0][1]
             t_wait = time.perf_counter() - t_step
             metrics = _weighted_average(call_all(learners, "step", per_obj=[(d,) for d, _ in per_rank]))

@@ -132,8 +132,10 @@ class GRPOExperimentConfig(ExperimentConfig):
                 raise ValueError(f"loss_denominator must be 'token' or a positive number, got {self.loss_denominator!r}") from None
         if self.num_mini_batches < 1 or self.num_epochs < 1:
             raise ValueError("num_mini_batches and num_epochs must be >= 1")
-        if self.sequence_parallel_size > 1 and self.deepspeed_stage != 3:
-            raise ValueError("sequence parallelism requires sharded parameters (deepspeed_stage 3)")
+        if self.sequence_parallel_size < 1:
+            raise ValueError("sequence_parallel_size must be >= 1")
+        # (the reference needs deepspeed_stage 3 for sequence parallelism, ``open_instruct/grpo_utils.py:275-276``; here it
+        # works with resident and with sharded parameters alike)
         if self.use_vllm_logprobs and self.use_rho_correction:
             # rho == 1 by construction when the engine's log-probs ARE the old log-probs
             self.use_rho_correction = False

@@ -39,7 +39,7 @@ class LearnerConfig:
     seed: int = 0
     dtype: torch.dtype | None = None
     offload_optimizer: bool = False   # fp32 master / moments in pinned host memory, streamed through the GPU per step
-    sequence_parallel_size: int = 1   # Ulysses: every packed micro-batch is split over this many ranks (== world size)
+    sequence_parallel_size: int = 1   # Ulysses: every packed micro-batch is split over groups of this many consecutive ranks
     sp_max_tokens: int = 8192         # largest packed micro-batch (all ranks together) the exchange buffers hold
     # Parameter sharding (ZeRO stage 3): None = only when the resident design does not fit this GPU (``needs_sharding``)
     shard_parameters: bool | None = None
@@ -104,8 +104,6 @@ class Learner:
         if shard:
             if ops != "fused":
                 raise NotImplementedError("parameter sharding runs on the fused (CUDA) path")
-            if cfg.sequence_parallel_size > 1:
-                raise NotImplementedError("parameter sharding together with sequence parallelism is not built")
             from .parallel.zero3 import Zero3State
 
             self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, sharded=True,
@@ -125,6 +123,7 @@ class Learner:
             self.global_step = 0
             self._accum = 0
             self.sp = 1
+            self._setup_sequence_parallel(spec, cfg, group)
             return
         if comm == "fused":
             from .parallel.symm import SymmetricState
@@ -154,13 +153,32 @@ class Learner:
         self.global_step = 0
         self._accum = 0
         self.sp = 1
-        if cfg.sequence_parallel_size > 1:
-            if ops != "fused" or cfg.sequence_parallel_size != self.world:
-                raise NotImplementedError("sequence parallelism runs on the fused path with sequence_parallel_size == world size")
-            from .parallel.ulysses import UlyssesContext
+        self._setup_sequence_parallel(spec, cfg, group)
 
-            self.sp = cfg.sequence_parallel_size
-            self.model.sp = UlyssesContext(spec, cfg.sp_max_tokens, self.device, group)
+    def _setup_sequence_parallel(self, spec, cfg, group) -> None:
+        """Ulysses groups of ``sequence_parallel_size`` CONSECUTIVE ranks inside the data-parallel world (the reference's
+        layout, ``open_instruct/grpo_fast.py:484-495``): the ranks of a group work on the same packed micro-batches, each on
+        its chunk of the tokens; gradients are exchanged over the whole world as before (the partial sums of a group's ranks
+        add up to the micro-batch's gradient), optimizer states and - with ``shard_parameters`` - parameters stay sharded
+        over all ranks."""
+        sp = cfg.sequence_parallel_size
+        self.sp_group = None
+        if sp <= 1:
+            return
+        if self.ops != "fused":
+            raise NotImplementedError("sequence parallelism runs on the fused (CUDA) path")
+        if self.world % sp:
+            raise ValueError(f"sequence_parallel_size {sp} must divide the number of ranks {self.world}")
+        if group is not None and sp != self.world:
+            raise ValueError("sequence-parallel groups inside a custom process group are not supported")
+        from .parallel.ulysses import UlyssesContext
+
+        sp_group = group
+        if sp != self.world:
+            sp_group, _ = pdist.hsdp_groups(sp)  # consecutive ranks; collective: every rank builds every group
+        self.sp = sp
+        self.sp_group = sp_group
+        self.model.sp = UlyssesContext(spec, cfg.sp_max_tokens, self.device, sp_group)
 
     def local_slice(self, t: torch.Tensor) -> torch.Tensor:
         """This rank's chunk of a per-token tensor of the packed micro-batch (identity without sequence parallelism)."""
@@ -180,9 +198,18 @@ class Learner:
             return self.model.token_logprobs(batch["input_ids"], batch["position_ids"], batch["cu_seq_lens_q"],
                                              batch["labels_shifted"], temperature, want_entropy)
 
-    def backward(self, loss: torch.Tensor) -> None:
-        with nvtx_range("backward"):
-            loss.backward()
+    def backward(self, loss: torch.Tensor, last: bool = False) -> None:
+        """Backward of one micro-batch.  ``last=True`` says that no further micro-batch follows before
+        ``optimizer_step``: every layer's gradients are then final as soon as this backward has passed the layer, and the
+        sharded optimizer starts exchanging them under the rest of the backward pass (the overlap DeepSpeed's
+        ``overlap_comm`` gives the reference, ``open_instruct/utils.py:1431-1460``).  Every rank must pass the same value."""
+        hook = getattr(self.opt, "grads_ready", None) if (last and self.z3 is None and self.ops == "fused") else None
+        self.model.grad_ready_hook = hook
+        try:
+            with nvtx_range("backward"):
+                loss.backward()
+        finally:
+            self.model.grad_ready_hook = None
         self._accum += 1
 
     def optimizer_step(self, grad_scale: float | None = None) -> torch.Tensor:
@@ -318,7 +345,7 @@ class Learner:
             self.model.ensure_main_grad()
 
     # ------------------------------------------------------------------ SFT
-    def sft_micro_step(self, batch: dict, reduce_loss: str = "mean") -> tuple[torch.Tensor, torch.Tensor]:
+    def sft_micro_step(self, batch: dict, reduce_loss: str = "mean", last: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
         """Forward + backward of one packed micro-batch.  Returns (loss, number of target tokens).
 
         ``mean``: mean CE over this micro-batch's target tokens (HF default, ``finetune.py:822-826``);
@@ -331,14 +358,14 @@ class Learner:
         loss = total * self.sp / n.clamp(min=1) if reduce_loss == "mean" else total
         if self.sp > 1:
             n = self.local_slice(batch["labels_shifted"] != IGNORE).sum()
-        self.backward(loss)
+        self.backward(loss, last=last)
         return loss.detach(), n
 
     def sft_step(self, micro_batches: list[dict], reduce_loss: str = "mean") -> dict:
         """One optimizer step over a list of packed micro-batches already on the device."""
         losses, toks = [], []
-        for mb in micro_batches:
-            loss, n = self.sft_micro_step(mb, reduce_loss)
+        for k, mb in enumerate(micro_batches):
+            loss, n = self.sft_micro_step(mb, reduce_loss, last=(k == len(micro_batches) - 1))
             losses.append(loss)
             toks.append(n)
         loss_t = torch.stack(losses)

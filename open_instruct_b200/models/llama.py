@@ -101,6 +101,9 @@ class LlamaModel:
         self.keep_cheap_activations = os.environ.get("B200_RECOMPUTE_CHEAP", "0") != "1"
         self.tp = None  # parallel.tp.TrainTP when the layers are split over a tensor-parallel group (spec is then the LOCAL spec)
         self.sp = None  # parallel.ulysses.UlyssesContext when the sequence is split over ranks (fused path)
+        # called with (lo, hi) once the flat gradient range [lo, hi) is final for this optimizer step; the learner sets it
+        # for the LAST micro-batch's backward only, so that the gradient exchange can start under the backward pass
+        self.grad_ready_hook = None
         self.main_grad: torch.Tensor | None = None  # fp32 flat gradient (fused path)
         self.g: dict[str, torch.Tensor] = {}
         self.inv_freq = ref.rope_inv_freq(spec.head_dim, spec.rope_theta, spec.rope_scaling, device=self.device)
@@ -160,6 +163,21 @@ class LlamaModel:
         self.p = self.layout.views(flat)
         if self.ops == "ref":
             self.flat.requires_grad_(True)
+
+    def logit_workspace(self, rows: int, vocab: int) -> torch.Tensor:
+        """One reused bf16 ``[rows, vocab]`` buffer for the chunked lm_head (allocated on first use)."""
+        ws = getattr(self, "_logit_ws", None)
+        if ws is None or ws.shape[0] < rows or ws.shape[1] != vocab:
+            ws = self._logit_ws = torch.empty(rows, vocab, dtype=torch.bfloat16, device=self.device)
+        return ws
+
+    def layer_grad_range(self, i: int) -> tuple[int, int]:
+        """Flat-buffer range of layer ``i``'s matrices (wqkv, wo, w_gate_up, w_down are adjacent in the layout)."""
+        e = self.layout.entries
+        lo = e[f"l{i}.wqkv"].offset
+        if i + 1 < self.spec.num_layers:
+            return lo, e[f"l{i + 1}.wqkv"].offset
+        return lo, (e["lm_head"].offset if "lm_head" in e else self.layout.decay_end)
 
     def grad_flat(self) -> torch.Tensor | None:
         """Flat gradient: fp32 ``main_grad`` (fused) or autograd's ``flat.grad`` (ref)."""
@@ -321,43 +339,50 @@ class LlamaModel:
             f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, table=self._rope_tab)
             attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
             return qkv, attn, lse, None
-        if s.qk_norm or s.attention_bias:
-            raise NotImplementedError("sequence parallelism with qk_norm / attention_bias is not built")
         qkv = sp.qkv_project(i, n1, p[f"l{i}.wqkv"], pos.numel())
+        # after the exchange a row is [q | k | v] of THIS rank's heads: same structure, fewer heads
+        self._last_qk = self.qkv_bias_and_norm_(qkv, i, sp.hq_l, sp.hk_l, cols=sp.local_cols_index)
         f.rope_(qkv, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim, table=self._rope_tab)
         attn, lse = f.attn_fwd(qkv, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
         return qkv, attn, lse, sp.attn_exchange(i, attn)
 
-    def qkv_bias_and_norm_(self, qkv: torch.Tensor, i: int):
+    def qkv_bias_and_norm_(self, qkv: torch.Tensor, i: int, hq: int | None = None, hk: int | None = None, cols: torch.Tensor | None = None):
         """Qwen2-style q/k/v bias and Qwen3 / OLMo-2 style per-head RMSNorm of q and k, in place on the fused projection
-        output (before RoPE).  Returns what the backward needs (``None`` when the model has neither)."""
+        output (before RoPE).  Returns what the backward needs (``None`` when the model has neither).  ``hq`` / ``hk``:
+        query / key heads in a row of ``qkv`` (sequence parallelism: this rank's heads only, ``cols`` then indexes their
+        columns in the full fused width for the bias)."""
         f = _fused()
         s, p = self.spec, self.p
+        hq = s.num_heads if hq is None else hq
+        hk = s.num_kv_heads if hk is None else hk
         if s.attention_bias:
-            qkv.add_(p[f"l{i}.bqkv"])
+            qkv.add_(p[f"l{i}.bqkv"] if cols is None else p[f"l{i}.bqkv"][cols])
         if not s.qk_norm:
             return None
         T = qkv.shape[0]
         out = []
-        for lo, heads, name in ((0, s.num_heads, "q_norm"), (s.q_dim, s.num_kv_heads, "k_norm")):
+        for lo, heads, name in ((0, hq, "q_norm"), (hq * s.head_dim, hk, "k_norm")):
             pre = qkv[:, lo:lo + heads * s.head_dim].contiguous().view(T * heads, s.head_dim)
             y, _, rstd = f.rmsnorm_fwd(pre, p[f"l{i}.{name}"], s.rms_norm_eps)
             qkv[:, lo:lo + heads * s.head_dim].copy_(y.view(T, heads * s.head_dim))
             out += [pre, rstd]
         return tuple(out)
 
-    def _qkv_bias_and_norm_bwd_(self, dqkv: torch.Tensor, i: int, qk) -> None:
+    def _qkv_bias_and_norm_bwd_(self, dqkv: torch.Tensor, i: int, qk, hq: int | None = None, hk: int | None = None, bias: bool = True) -> None:
         """Backward of ``qkv_bias_and_norm_`` in place on ``dqkv`` (after the RoPE backward); accumulates the norm and
-        bias gradients."""
+        bias gradients.  ``bias=False``: the caller adds the bias gradient itself (sequence parallelism does it after the
+        exchange, on full-width rows)."""
         f = _fused()
         s, g, p = self.spec, self.g, self.p
+        hq = s.num_heads if hq is None else hq
+        hk = s.num_kv_heads if hk is None else hk
         T = dqkv.shape[0]
         if qk is not None:
-            for (lo, heads, name), pre, rstd in (((0, s.num_heads, "q_norm"), qk[0], qk[1]), ((s.q_dim, s.num_kv_heads, "k_norm"), qk[2], qk[3])):
+            for (lo, heads, name), pre, rstd in (((0, hq, "q_norm"), qk[0], qk[1]), ((hq * s.head_dim, hk, "k_norm"), qk[2], qk[3])):
                 dy = dqkv[:, lo:lo + heads * s.head_dim].contiguous().view(T * heads, s.head_dim)
                 dx = f.rmsnorm_bwd(pre, p[f"l{i}.{name}"], rstd, dy, None, g[f"l{i}.{name}"])
                 dqkv[:, lo:lo + heads * s.head_dim].copy_(dx.view(T, heads * s.head_dim))
-        if s.attention_bias:
+        if s.attention_bias and bias:
             g[f"l{i}.bqkv"].add_(dqkv.float().sum(0))
 
     def _recompute_layer(self, i: int, st: _LayerStash, pos, cu) -> _LayerStash:
@@ -428,7 +453,10 @@ class LlamaModel:
                 d_attn = sp.d_attn_project(d_mid, p[f"l{i}.wo"], pos.numel())
                 dqkv_heads = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
                 f.rope_(dqkv_heads, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim, backward=True, table=self._rope_tab)
+                self._qkv_bias_and_norm_bwd_(dqkv_heads, i, st.qk, sp.hq_l, sp.hk_l, bias=False)
                 dqkv = sp.dqkv_exchange(dqkv_heads)
+                if s.attention_bias:  # my tokens, every head: this rank's share of the bias gradient
+                    g[f"l{i}.bqkv"].add_(dqkv.float().sum(0))
             n1 = st.n1 if st.n1 is not None else f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)[0]
             st.n1 = None
             f.gemm(dqkv, n1, g[f"l{i}.wqkv"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
@@ -441,6 +469,8 @@ class LlamaModel:
             del d_n1, d_mid
             if z is not None:
                 z.layer_bwd_done(i)  # this layer's weight gradients go to their owners while the next layer runs
+            elif self.grad_ready_hook is not None:
+                self.grad_ready_hook(*self.layer_grad_range(i))
         f.embedding_bwd(g["embed"], state["ids"], d_stream)
         state.clear()
 
@@ -460,8 +490,18 @@ class _FusedHiddenFn(torch.autograd.Function):
         return None, None, None, None, None, None
 
 
+# Rows of the lm_head GEMM's output that exist at one time.  A micro-batch of at most this many tokens keeps its bf16
+# logits for the backward pass (no recomputation); a longer one is processed in chunks of this many tokens through one
+# reused [chunk, V] workspace and recomputes each chunk's logits in the backward, so the head's memory does not grow
+# with the number of tokens (a 35,840-token GRPO pack at V = 128,256 would otherwise hold 9 GB of logits).
+LOGIT_CHUNK_TOKENS = int(os.environ.get("B200_LOGIT_CHUNK", "8192"))
+
+
 class _FusedLogprobFn(torch.autograd.Function):
-    """lm_head GEMM + streaming log-softmax; backward rewrites the bf16 logits in place."""
+    """lm_head GEMM + streaming log-softmax (log-prob of the label, log-sum-exp, entropy) over token chunks; the backward
+    rewrites each chunk's bf16 logits in place into their gradient and feeds the head's dgrad / wgrad GEMMs from it.
+    Stands where the reference uses liger's fused-linear-cross-entropy (``open_instruct/finetune.py:571-587``) and its
+    ``[T, V]``-free ``log_softmax_and_gather`` helper (``open_instruct/model_utils.py:587-600``)."""
 
     @staticmethod
     def forward(ctx, model: LlamaModel, input_ids, position_ids, cu_seqlens, labels, temperature, want_entropy, keep,
@@ -475,12 +515,26 @@ class _FusedLogprobFn(torch.autograd.Function):
         if model.zero3 is not None:
             model.zero3.head()
         w = model.lm_head_weight()
-        logits = f.gemm(nf, w)
-        logp, lse, ent = f.logprob_fwd(logits, labels, temperature, want_entropy)
-        ctx.model = model
-        ctx.temperature = temperature
+        T, C = nf.shape[0], max(128, LOGIT_CHUNK_TOKENS)
+        ctx.model, ctx.temperature, ctx.chunk = model, temperature, C
+        if T <= C:
+            logits = f.gemm(nf, w)
+            logp, lse, ent = f.logprob_fwd(logits, labels, temperature, want_entropy)
+        else:
+            logits = None
+            ws = model.logit_workspace(C, w.shape[0])
+            logp = torch.empty(T, dtype=torch.float32, device=nf.device)
+            lse = torch.empty_like(logp)
+            ent = torch.empty_like(logp) if want_entropy else None
+            for t0 in range(0, T, C):
+                t1 = min(T, t0 + C)
+                lg = f.gemm(nf[t0:t1], w, ws[: t1 - t0])
+                lp_c, lse_c, ent_c = f.logprob_fwd(lg, labels[t0:t1], temperature, want_entropy)
+                logp[t0:t1], lse[t0:t1] = lp_c, lse_c
+                if want_entropy:
+                    ent[t0:t1] = ent_c
         if needs_grad:
-            ctx.save_for_backward(nf, logits, lse, labels)
+            ctx.save_for_backward(nf, logits if logits is not None else lse.new_zeros(0), lse, labels)
         if ent is None:
             ent = torch.zeros(0, device=logp.device)
         ctx.mark_non_differentiable(ent)
@@ -492,10 +546,26 @@ class _FusedLogprobFn(torch.autograd.Function):
         model = ctx.model
         nf, logits, lse, labels = ctx.saved_tensors
         model.ensure_main_grad()
-        d_logits = f.logprob_bwd_(logits, labels, lse, d_logp.contiguous().float(), ctx.temperature)
         head = "embed" if (model.spec.tie_word_embeddings or "lm_head" not in model.p) else "lm_head"
-        f.gemm(d_logits, nf, model.g[head], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
-        d_nf = f.gemm(d_logits, model.lm_head_weight(), b_mn=True)
-        del d_logits, logits
+        w = model.lm_head_weight()
+        d_logp = d_logp.contiguous().float()
+        T, C = nf.shape[0], ctx.chunk
+        if logits.numel():
+            d_logits = f.logprob_bwd_(logits, labels, lse, d_logp, ctx.temperature)
+            f.gemm(d_logits, nf, model.g[head], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+            d_nf = f.gemm(d_logits, w, b_mn=True)
+            del d_logits, logits
+        else:
+            ws = model.logit_workspace(C, w.shape[0])
+            d_nf = torch.empty_like(nf)
+            for t0 in range(0, T, C):
+                t1 = min(T, t0 + C)
+                lg = f.gemm(nf[t0:t1], w, ws[: t1 - t0])  # recomputed: the forward kept no logits
+                f.logprob_bwd_(lg, labels[t0:t1], lse[t0:t1], d_logp[t0:t1], ctx.temperature)
+                f.gemm(lg, nf[t0:t1], model.g[head], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+                f.gemm(lg, w, d_nf[t0:t1], b_mn=True)
+        if head == "lm_head" and model.grad_ready_hook is not None and model.zero3 is None:
+            e = model.layout.entries["lm_head"]
+            model.grad_ready_hook(e.offset, model.layout.decay_end)
         model._fused_backward_hidden(ctx.state, d_nf)
         return None, None, None, None, None, None, None, None, None

@@ -251,3 +251,34 @@ class LoRATrainer:
 
     def save(self, out_dir: str, base_model_name_or_path: str = "") -> None:
         self.adapters.save(out_dir, base_model_name_or_path)
+
+    # ---- training-state checkpoints (adapters are replicated: rank 0 writes, every rank reads)
+    def state_dict(self) -> dict:
+        return {"adapters": self.adapters.flat.detach().cpu().clone(), "optimizer": self.opt.state_dict(),
+                "rank": self.adapters.rank if hasattr(self.adapters, "rank") else None}
+
+    def load_state_dict(self, sd: dict) -> None:
+        """Restore adapter weights and their AdamW moments, then rebuild the merged working weights from the frozen base."""
+        if sd["adapters"].numel() != self.adapters.flat.numel():
+            raise ValueError("checkpointed LoRA adapters have a different size (rank or target modules changed)")
+        with torch.no_grad():
+            self.adapters.flat.copy_(sd["adapters"].to(self.adapters.flat.device, self.adapters.flat.dtype))
+        self.opt.load_state_dict(sd["optimizer"])
+        with torch.no_grad():
+            self.adapters.merge_into(self.learner.model, self.base)
+
+    def save_state(self, ckpt_dir: str) -> None:
+        import os
+
+        tmp = os.path.join(ckpt_dir, "lora_state.pt.tmp")
+        torch.save(self.state_dict(), tmp)
+        os.replace(tmp, os.path.join(ckpt_dir, "lora_state.pt"))
+
+    def load_state(self, ckpt_dir: str) -> None:
+        import os
+
+        path = os.path.join(ckpt_dir, "lora_state.pt")
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{ckpt_dir} holds no LoRA adapter state: resuming would restart the adapters from their "
+                                    "initialisation; remove the checkpoint or resume without use_lora")
+        self.load_state_dict(torch.load(path, map_location="cpu", weights_only=False))

@@ -85,12 +85,13 @@ __device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
 // first add; the adds then run in fixed rank order, which keeps the sum bitwise identical from run to run.
 // MULTIMEM variant: one `multimem.ld_reduce` returns the sum over all ranks (the NVSwitch adds), so the owner's ingress
 // carries n floats instead of world * n.
-template <bool MULTIMEM>
+// U: vectors per thread per round; the launcher picks it so that U * world is about 16 loads in flight per thread
+// whatever the number of ranks (with two ranks and U = 2 a small grid reached only a fifth of the link rate).
+template <bool MULTIMEM, int U, int W>
 __global__ void __launch_bounds__(256)
 zero_reduce_scatter_kernel(PeerPtrs grads, const float* __restrict__ mc_grads, int world, long long lo,
                            long long n, float* __restrict__ out, float* __restrict__ sumsq) {
   __shared__ float red[8];
-  constexpr int U = 2;
   float ss = 0.f;
   const long long nv = n / 4;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -111,12 +112,12 @@ zero_reduce_scatter_kernel(PeerPtrs grads, const float* __restrict__ mc_grads, i
         }
       }
     } else {
-      uint4 x[U][MAX_PEERS];
+      uint4 x[U][W];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + u * stride;
 #pragma unroll
-        for (int r = 0; r < MAX_PEERS; ++r)
+        for (int r = 0; r < W; ++r)
           if (r < world && i < nv)
             x[u][r] = ld_volatile_u4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo) + i);
       }
@@ -126,7 +127,7 @@ zero_reduce_scatter_kernel(PeerPtrs grads, const float* __restrict__ mc_grads, i
         if (i < nv) {
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int r = 0; r < MAX_PEERS; ++r)
+          for (int r = 0; r < W; ++r)
             if (r < world) {
               acc.x += __uint_as_float(x[u][r].x); acc.y += __uint_as_float(x[u][r].y);
               acc.z += __uint_as_float(x[u][r].z); acc.w += __uint_as_float(x[u][r].w);
@@ -366,11 +367,15 @@ extern "C" int b200_zero_reduce_range(const void* const* grad_ptrs, const void* 
   if (n == 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = ctas > 0 ? ctas : 148 * 4;
+  const PeerPtrs pp = make_ptrs(grad_ptrs, world);
   if (use_multimem && mc_grads)
-    zero_reduce_scatter_kernel<true><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world),
-                                                            reinterpret_cast<const float*>(mc_grads), world, lo, n, out, sumsq);
+    zero_reduce_scatter_kernel<true, 8, 1><<<grid, 256, 0, st>>>(pp, reinterpret_cast<const float*>(mc_grads), world, lo, n, out, sumsq);
+  else if (world <= 2)
+    zero_reduce_scatter_kernel<false, 8, 2><<<grid, 256, 0, st>>>(pp, nullptr, world, lo, n, out, sumsq);
+  else if (world <= 4)
+    zero_reduce_scatter_kernel<false, 4, 4><<<grid, 256, 0, st>>>(pp, nullptr, world, lo, n, out, sumsq);
   else
-    zero_reduce_scatter_kernel<false><<<grid, 256, 0, st>>>(make_ptrs(grad_ptrs, world), nullptr, world, lo, n, out, sumsq);
+    zero_reduce_scatter_kernel<false, 2, 8><<<grid, 256, 0, st>>>(pp, nullptr, world, lo, n, out, sumsq);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -172,6 +172,9 @@ def call(name: str, *args) -> None:
     global launch_count
     lib = load_ops()
     launch_count += _KERNELS_PER_CALL.get(name, 1)
-    rc = getattr(lib, name)(*args)
+    fn = getattr(lib, name)
+    if fn.argtypes is None and name in _SIGNATURES:  # registered by a module imported after the library was loaded
+        fn.argtypes, fn.restype = _SIGNATURES[name], c_int
+    rc = fn(*args)
     if rc != 0:
         raise KernelError(f"{name} failed with code {rc}")

@@ -14,6 +14,16 @@ import torch
 import torch.distributed as dist
 
 
+def find_free_port(host: str = "127.0.0.1") -> int:
+    """A TCP port that is free right now (bind to port 0, read the number back).  Rendezvous ports are picked this way
+    instead of from fixed numbers, which collide on machines shared with other jobs."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind((host, 0))
+        return int(s.getsockname()[1])
+
+
 def env_rank() -> int:
     return int(os.environ.get("RANK", "0"))
 

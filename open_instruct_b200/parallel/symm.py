@@ -13,6 +13,13 @@ Everything that moves data is done by this package's own kernels
   peer's working copy from inside the optimizer kernel.  (DeepSpeed: optimizer step, bf16 copy,
   then NCCL all-gather.)
 * ``finish_step``          barrier: all stores have landed.
+* ``reduce_ready_range``   the overlapped form of the reduce-scatter: while the LAST micro-batch's backward is still
+  running, every range of the gradient buffer that has received its final contribution (one decoder layer at a time)
+  is reduced by its owner on a side stream - an event from the compute stream, a device barrier on the side stream's own
+  flag row (all ranks have finished that range), then the same reduce kernel on a small grid that shares the SMs with
+  the backward GEMMs.  ``reduce_scatter_grad`` afterwards only reduces what is left (embedding, norm weights).  This
+  is the schedule DeepSpeed's ``overlap_comm`` gives the reference (``open_instruct/utils.py:1431-1460``), with the
+  gradients still crossing NVLink once per optimizer step instead of once per micro-batch.
 
 ``use_multimem=True`` switches the two data kernels to ``multimem.ld_reduce`` / ``multimem.st`` through
 the NVSwitch when the allocation has a multicast address.  Waits on peers are bounded
@@ -37,9 +44,25 @@ _PP = ctypes.POINTER(ctypes.c_void_p)
 lib._SIGNATURES.update({
     "b200_symm_barrier": [_PP, _I, _I, _U, _I, _P, _P],
     "b200_symm_allreduce_scalar": [_PP, _I, _I, _U, _P, _P, _I, _P, _P],
+    "b200_symm_barrier_side": [_PP, _I, _I, _U, _I, _P, _P],
     "b200_zero_reduce_scatter": [_PP, _P, _I, _I, _L, _L, _P, _P, _I, _P],
+    "b200_zero_reduce_range": [_PP, _P, _I, _L, _L, _P, _P, _I, _I, _P],
     "b200_zero_adamw_allgather": [_P, _P, _P, _P, _PP, _P, _I, _L, _L, _P, _F, _F, _F, _F, _F, _I, _I, _P],
 })
+
+
+def unreduced_ranges(lo: int, hi: int, done: list[tuple[int, int]]) -> list[tuple[int, int]]:
+    """The parts of ``[lo, hi)`` that none of the (possibly overlapping, unordered) ranges in ``done`` covers."""
+    out, pos = [], lo
+    for a, b in sorted(done):
+        if a > pos:
+            out.append((pos, min(a, hi)))
+        pos = max(pos, b)
+        if pos >= hi:
+            break
+    if pos < hi:
+        out.append((pos, hi))
+    return [(a, b) for a, b in out if a < b]
 
 
 def _ptr_array(ptrs) -> ctypes.Array:
@@ -79,8 +102,15 @@ class SymmetricState:
             use_multimem = os.environ.get("B200_MULTIMEM", "0") == "1"
         self.use_multimem = bool(use_multimem and self._mc_params and self._mc_grads)
         self._barrier_epoch = 0
+        self._side_epoch = 0
         self._scalar_epoch = 0
         self._local_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        # overlapped exchange: a high-priority side stream, the ranges of MY slice already reduced in this step, and the
+        # number of CTAs the side-stream reduce may take from the backward pass
+        self.side_stream = torch.cuda.Stream(self.device, priority=-1)
+        self._reduced: list[tuple[int, int]] = []
+        self._sq_zeroed = False
+        self.overlap_ctas = int(os.environ.get("B200_OVERLAP_CTAS", "48"))
         lib.load_ops()
         for name, sig in lib._SIGNATURES.items():
             fn = getattr(lib.load_ops(), name, None)
@@ -104,12 +134,47 @@ class SymmetricState:
                  self.peer_timeout_ms, ptr(status_word(self.device)), stream_ptr())
 
     # ------------------------------------------------------------------ optimizer-step collectives
-    def reduce_scatter_grad(self, out_shard: torch.Tensor, norm_sq: torch.Tensor) -> torch.Tensor:
-        """``out_shard`` = sum over ranks of my slice of ``grads``; ``norm_sq`` = global |sum grad|^2."""
-        self.barrier()  # every rank's backward has finished writing its gradient buffer
+    def _reduce_range(self, a: int, b: int, out_shard: torch.Tensor, ctas: int) -> None:
+        """Sum ``grads[a:b]`` (global element offsets inside my slice) over the ranks into ``out_shard``."""
         lo = self.rank * self.shard
-        lib.call("b200_zero_reduce_scatter", self._grad_ptrs, self._mc_grads or None, self.rank, self.world, lo,
-                 self.shard, ptr(out_shard), ptr(self._local_sq), int(self.use_multimem), stream_ptr())
+        lib.call("b200_zero_reduce_range", self._grad_ptrs, self._mc_grads or None, self.world, a, b - a,
+                 out_shard[a - lo:].data_ptr(), ptr(self._local_sq), int(self.use_multimem), ctas, stream_ptr())
+
+    def reduce_ready_range(self, lo: int, hi: int, out_shard: torch.Tensor) -> None:
+        """Every rank calls this, in the same order, once ``grads[lo:hi]`` has received its last contribution of the
+        step on the current stream.  The owner of each part of the range reduces it on the side stream, beside whatever
+        the current stream runs next."""
+        main = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        with torch.cuda.stream(self.side_stream):
+            self.side_stream.wait_event(ev)
+            if not self._sq_zeroed:
+                self._local_sq.zero_()
+                self._sq_zeroed = True
+            self._side_epoch += 1
+            lib.call("b200_symm_barrier_side", self._pads, self.rank, self.world, self._side_epoch, self.peer_timeout_ms,
+                     ptr(status_word(self.device)), stream_ptr())
+            my_lo = self.rank * self.shard
+            a, b = max(lo, my_lo), min(hi, my_lo + self.shard)
+            a, b = (a + 3) // 4 * 4, b // 4 * 4
+            if a < b:
+                self._reduce_range(a, b, out_shard, self.overlap_ctas)
+                self._reduced.append((a, b))
+
+    def reduce_scatter_grad(self, out_shard: torch.Tensor, norm_sq: torch.Tensor) -> torch.Tensor:
+        """``out_shard`` = sum over ranks of my slice of ``grads``; ``norm_sq`` = global |sum grad|^2.  Ranges that
+        ``reduce_ready_range`` already reduced in this step are skipped."""
+        main = torch.cuda.current_stream(self.device)
+        if self._reduced or self._sq_zeroed:
+            main.wait_stream(self.side_stream)
+        if not self._sq_zeroed:
+            self._local_sq.zero_()
+        self.barrier()  # every rank's backward has finished writing its gradient buffer
+        my_lo = self.rank * self.shard
+        for a, b in unreduced_ranges(my_lo, my_lo + self.shard, self._reduced):
+            self._reduce_range(a, b, out_shard, 0)
+        self._reduced, self._sq_zeroed = [], False
         # also the point after which every rank has finished READING the peers' gradients
         self.allreduce_scalar(self._local_sq, norm_sq)
         return out_shard

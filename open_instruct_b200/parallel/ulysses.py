@@ -151,6 +151,8 @@ class UlyssesContext:
         cols += [k0 + (self.rank * self.hk_l + b) * d for b in range(self.hk_l)]
         cols += [v0 + (self.rank * self.hk_l + b) * d for b in range(self.hk_l)]
         self.dqkv_cols = torch.tensor(cols, dtype=torch.int32, device=self.device)
+        # full-width column index of every element of a local [q | k | v] row (for per-column parameters such as the bias)
+        self.local_cols_index = (self.dqkv_cols.long()[:, None] + torch.arange(d, device=self.device)[None, :]).reshape(-1)
         _P, _I, _L, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint
         _PP = ctypes.POINTER(ctypes.c_void_p)
         lib._SIGNATURES.update({

@@ -22,7 +22,7 @@ from ..ops import lib
 from ..ops.lib import ptr, stream_ptr
 
 _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-lib._SIGNATURES["b200_multi_push"] = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), _I, _L, _L, _I, _P]
+lib._SIGNATURES["b200_multi_push"] = [_P, ctypes.POINTER(ctypes.c_void_p), _I, _L, _L, _I, _P]
 
 
 class PeerBuffer:

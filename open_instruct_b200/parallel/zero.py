@@ -28,6 +28,7 @@ Three communication back ends share this state machine:
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -104,6 +105,8 @@ class ZeroOptimizer:
                 self.v = torch.zeros_like(self.master)
         self.grad_shard = torch.zeros(self.shard, dtype=torch.float32, device=flat.device) if self.world > 1 else None
         self._stage = None
+        # start reducing a layer's gradients as soon as the last micro-batch's backward has produced them
+        self.overlap = os.environ.get("B200_OVERLAP_GRADS", "1") != "0"
         self.step_count = 0
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._gscale = torch.ones(1, dtype=torch.float32, device=self.device)
@@ -133,6 +136,13 @@ class ZeroOptimizer:
             dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)
             self.grad_shard.copy_(g[self.lo:self.hi])
         return self.grad_shard
+
+    def grads_ready(self, lo: int, hi: int) -> None:
+        """The flat gradient range ``[lo, hi)`` has received its last contribution of this optimizer step (called by the
+        model during the final micro-batch's backward, in the same order on every rank).  With the fused back end the
+        owner starts reducing it right away on a side stream; the other back ends exchange everything in ``step``."""
+        if self.comm == "fused" and self.world > 1 and self.overlap:
+            self.symm.reduce_ready_range(lo, hi, self.grad_shard)
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()

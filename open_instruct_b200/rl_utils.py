@@ -54,10 +54,11 @@ def reset_position_ids(attention_mask: torch.Tensor) -> torch.Tensor:
 def pack_sequences(queries: list[list[int]], responses: list[list[int]], masks: list[list[int]], pack_length: int,
                    pad_token_id: int, vllm_logprobs: list[list[float]], min_num_batches: int = 1,
                    mask_tool_use: bool = False) -> PackedSequences:
-    if any(pad_token_id in q for q in queries):
-        raise ValueError("queries must not contain the pad token")
     n = len(queries)
+    # pad tokens are stripped from queries as from responses (``open_instruct/rl_utils.py:294``): an already padded prompt,
+    # or a tokenizer whose pad id equals eos, packs fine instead of stopping the data-preparation thread
     q_arr = [np.asarray(q, dtype=np.int64) for q in queries]
+    q_arr = [q[q != pad_token_id] for q in q_arr]
     r_arr, m_arr, lp_arr = [], [], []
     for i in range(n):
         r = np.asarray(responses[i], dtype=np.int64)

@@ -198,6 +198,13 @@ class RolloutEngine:
         w, r = self.host.counts()
         return w + r
 
+    def reset_prefix_cache(self) -> bool:
+        """Drop KV blocks that are kept only so that a LATER request can reuse them.  This engine shares a prompt's blocks
+        among the ``n`` samples of one request and frees them with the request, so nothing outlives a request and there
+        is nothing stale to drop after a weight update; the call exists for the reference's control surface
+        (``open_instruct/vllm_utils.py:791-793``) and reports success."""
+        return True
+
     def update_weights(self, flat: torch.Tensor, model_step: int | None = None) -> None:
         """Replace the weights (same flat layout) between steps; cached KV of running sequences stays."""
         with torch.no_grad():

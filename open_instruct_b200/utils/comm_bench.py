@@ -74,18 +74,23 @@ def main() -> None:
         shard = n // world
         st.grads.normal_()
         out, nsq = torch.empty(shard, device=device), torch.zeros(1, device=device)
-        # each owner pulls (world - 1) remote slices of 4-byte elements
-        rec("zero_reduce_scatter", timed(lambda: st.reduce_scatter_grad(out, nsq)), link_bytes=(world - 1) * shard * 4,
-            hbm_bytes=world * shard * 4 + shard * 4)
-        master, m, v = out.clone(), torch.zeros_like(out), torch.zeros_like(out)
+        master, m, v = torch.randn(shard, device=device), torch.zeros(shard, device=device), torch.zeros(shard, device=device)
         gs = torch.ones(1, device=device)
 
         def adam():
             st.adamw_allgather(master, m, v, out, rank * shard, gscale=gs, lr=1e-6, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, step=1)
             st.finish_step()
 
-        # each owner pushes its bf16 shard to (world - 1) peers; locally it streams 16 B read + 12 B written per element
-        rec("zero_adamw_allgather", timed(adam), link_bytes=(world - 1) * shard * 2, hbm_bytes=shard * 30)
+        variants = [("p2p", False)] + ([("multimem", True)] if (st._mc_grads and st._mc_params) else [])
+        for tag, mm in variants:
+            st.use_multimem = mm
+            # P2P: each owner pulls (world - 1) remote slices of 4-byte elements; multimem: the switch adds, the owner's ingress
+            # carries one slice, every peer's egress still carries its copy of that slice
+            rec(f"zero_reduce_scatter[{tag}]", timed(lambda: st.reduce_scatter_grad(out, nsq)), link_bytes=(world - 1) * shard * 4,
+                hbm_bytes=world * shard * 4 + shard * 4, note="link bytes = egress per GPU (the bound for both variants)")
+            # each owner pushes its bf16 shard to (world - 1) peers; locally it streams 16 B read + 12 B written per element
+            rec(f"zero_adamw_allgather[{tag}]", timed(adam), link_bytes=(world - 1) * shard * 2, hbm_bytes=shard * 30)
+        st.use_multimem = False
         g32 = st.grads
         rs_out = torch.empty(shard, device=device)
         rec("nccl_reduce_scatter", timed(lambda: dist.reduce_scatter_tensor(rs_out, g32)), link_bytes=(world - 1) * shard * 4)

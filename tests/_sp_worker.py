@@ -22,9 +22,18 @@ from open_instruct_b200.parallel.ulysses import UlyssesContext  # noqa: E402
 
 def main():
     rank, world, device = pdist.init_distributed()
-    spec = get_spec("tiny128").replace(num_heads=4, num_kv_heads=2, hidden_size=512, intermediate_size=1024, num_layers=3)
-    for ckpt in (False, True):
+    base = get_spec("tiny128").replace(num_heads=4, num_kv_heads=2, hidden_size=512, intermediate_size=1024, num_layers=3)
+    # plain Llama blocks with and without activation checkpointing, then the families with extras on the fused projection:
+    # Qwen2-style q/k/v bias and Qwen3 / OLMo-2 style per-head q/k RMSNorm (applied to this rank's heads after the exchange)
+    for ckpt, spec in ((False, base), (True, base), (False, base.replace(attention_bias=True, model_type="qwen2")),
+                       (True, base.replace(qk_norm=True, model_type="qwen3"))):
         full = LlamaModel(spec, device=device, dtype=torch.bfloat16, ops="fused", seed=3, gradient_checkpointing=ckpt)
+        if spec.attention_bias or spec.qk_norm:
+            with torch.no_grad():  # biases start at zero and norm weights at one: move them so that they matter
+                gen = torch.Generator(device=device).manual_seed(11)
+                for name, v in full.p.items():
+                    if name.endswith(("bqkv", "q_norm", "k_norm")):
+                        v.add_((torch.randn(v.shape, device=device, generator=gen) * 0.1).to(v.dtype))
         spm = LlamaModel(spec, device=device, dtype=torch.bfloat16, ops="fused", flat=full.flat, gradient_checkpointing=ckpt)
         spm.sp = UlyssesContext(spec, 1024, device)
         g = torch.Generator().manual_seed(5)
@@ -55,7 +64,8 @@ def main():
         den = g_full.norm().item()
         assert num / den < 2e-2, f"gradient mismatch: relative error {num / den}"
         # per-entry check on the attention weights, where the exchanges matter
-        for name in ("l0.wqkv", "l1.wo", "l2.w_down", "embed"):
+        extra = (["l1.bqkv"] if spec.attention_bias else []) + (["l0.q_norm", "l2.k_norm"] if spec.qk_norm else [])
+        for name in ["l0.wqkv", "l1.wo", "l2.w_down", "embed"] + extra:
             a, b = full.layout.view(g_sp, name), full.layout.view(g_full, name)
             rel = ((a - b).norm() / b.norm().clamp(min=1e-12)).item()
             assert rel < 3e-2, (name, rel)

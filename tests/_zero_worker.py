@@ -72,6 +72,31 @@ def main():
         n = single.model.layout.total
         err = (single.model.flat.detach()[:n] - flats[names[0]][0][:n]).abs().max().item()
         assert err < 1e-5, f"multi-rank vs single-process: {err}"
+    if cuda and "fused" in names and world == 2:
+        # A peer that never arrives: rank 0 runs one device barrier with a 50 ms limit while rank 1 skips that call.  The
+        # kernel must return by itself, leave ST_TIMEOUT_PEER in the status word, and the host check must raise; nothing
+        # hangs or faults, and the context stays usable.
+        from open_instruct_b200.ops import lib
+        from open_instruct_b200.parallel.symm import SymmetricState
+
+        st = SymmetricState(4096, device, peer_timeout_ms=50)
+        st.barrier()  # both ranks: a normal barrier passes
+        torch.cuda.synchronize()
+        lib.check_status()
+        if rank == 0:
+            st.barrier()
+            torch.cuda.synchronize()
+            assert int(lib.status_word(device).item()) == 5, "expected ST_TIMEOUT_PEER"
+            try:
+                lib.check_status()
+                raise AssertionError("check_status did not raise after a timed-out peer wait")
+            except lib.KernelError:
+                pass
+            assert int(lib.status_word(device).item()) == 0  # cleared by the raise; the context is still usable
+            x = torch.ones(8, device=device)
+            assert float((x * 2).sum().item()) == 16.0
+        else:
+            st._barrier_epoch += 1  # keep the epoch counters of the two ranks aligned
     pdist.barrier()
     if rank == 0:
         print("ZERO_WORKER_OK", {k: v[1] for k, v in flats.items()})

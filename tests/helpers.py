@@ -4,6 +4,15 @@ import json
 import os
 
 
+def free_port() -> int:
+    """A rendezvous port that is free right now (fixed port numbers collide on shared machines)."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return int(s.getsockname()[1])
+
+
 def make_tokenizer(path: str, vocab_size: int = 300):
     from tokenizers import Tokenizer, models, pre_tokenizers, trainers, decoders
     from transformers import PreTrainedTokenizerFast

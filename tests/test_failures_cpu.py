@@ -7,13 +7,15 @@ import sys
 import time
 
 import pytest
+
+from helpers import free_port
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_rank_leaving_between_steps_is_detected():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29655",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(ROOT, "tests", "_failure_worker.py"), "leave"]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=120)
     out = res.stdout + res.stderr

@@ -39,15 +39,22 @@ def test_sft_trains_and_exports(tmp_path):
     assert os.path.exists(os.path.join(args.output_dir, "tokenizer.json"))
 
 
-def test_resume_is_bitwise_identical(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("extra", [{}, dict(use_lora=True, lora_rank=4, lora_alpha=8.0, lora_dropout=0.0, learning_rate=5e-3)],
+                         ids=["full", "lora"])
+def test_resume_is_bitwise_identical(tmp_path, extra):
+    """With LoRA the checkpoint must carry the adapters and their AdamW moments: a resume that restarted them from their
+    initialisation would still finish, with different weights."""
     from open_instruct_b200.finetune import main
     from safetensors.torch import load_file
 
-    a, tc = _args(str(tmp_path / "a"), checkpointing_steps="4")
+    a, tc = _args(str(tmp_path / "a"), checkpointing_steps="4", **extra)
     main(a, tc)
     full = load_file(os.path.join(a.output_dir, "model.safetensors"))
     # interrupted run: stop after 4 steps, then resume in a fresh call
-    b, tc_b = _args(str(tmp_path / "b"), checkpointing_steps="4")
+    b, tc_b = _args(str(tmp_path / "b"), checkpointing_steps="4", **extra)
     b1 = type(b)(**{**b.__dict__, "max_train_steps": None})
     import open_instruct_b200.finetune as ft
 
@@ -69,6 +76,8 @@ def test_resume_is_bitwise_identical(tmp_path):
     finally:
         ft._micro_batches = orig
     assert os.path.exists(os.path.join(b.output_dir, "step_4", "COMPLETED"))
+    if extra:
+        assert os.path.exists(os.path.join(b.output_dir, "step_4", "lora_state.pt"))
     main(b, tc_b)
     resumed = load_file(os.path.join(b.output_dir, "model.safetensors"))
     for k in full:

@@ -73,6 +73,40 @@ def test_grpo_train_step_moves_policy_toward_advantage():
     assert after[0] > before[0] and after[1] < before[1]
 
 
+def test_grpo_train_step_label_space_matches_token_space():
+    """Sequence parallelism keeps per-token quantities at the position that predicts the token (so that a rank never needs
+    its neighbour's log-prob) instead of shifting the log-probs after the forward pass.  On one rank both forms must give
+    the same metrics and the same parameter update, with rho correction, several mini-batches and two epochs."""
+    from open_instruct_b200.data_types import CollatedBatchData
+    from open_instruct_b200.grpo_fast import grpo_train_step
+    from open_instruct_b200.grpo_utils import GRPOExperimentConfig
+    from open_instruct_b200.learner import Learner, LearnerConfig
+    from open_instruct_b200.models import get_spec
+    from open_instruct_b200.rl_utils import pack_sequences
+
+    spec = get_spec("tiny")
+    g = torch.Generator().manual_seed(0)
+    q = [torch.randint(1, 100, (int(n),), generator=g).tolist() for n in (5, 9, 4, 7)]
+    r = [torch.randint(1, 100, (int(n),), generator=g).tolist() for n in (6, 3, 8, 5)]
+    lp = [(-torch.rand(len(x), generator=g) * 3).tolist() for x in r]
+    p = pack_sequences(q, r, [[1] * len(x) for x in r], 24, 0, lp)
+    adv = torch.tensor([0.0, 1.0, -0.5, 0.7, -1.2])
+    p.advantages = [adv[m.long()] for m in p.response_masks]
+    data = CollatedBatchData(p.query_responses, p.attention_masks, p.position_ids, p.advantages, p.response_masks, p.vllm_logprobs, p.cu_seqlens)
+    outs = []
+    for force in (False, True):
+        learner = Learner(spec, LearnerConfig(ops="ref", learning_rate=5e-3, lr_scheduler_type="constant", seed=3))
+        args = GRPOExperimentConfig(beta=0.0, load_ref_policy=False, use_rho_correction=True, num_mini_batches=2, num_epochs=2, record_entropy=True)
+        args._force_label_space = force
+        m = grpo_train_step(learner, data, args)
+        outs.append((m, learner.model.flat.detach().clone()))
+    (m0, w0), (m1, w1) = outs
+    assert torch.allclose(w0, w1, atol=1e-7), (w0 - w1).abs().max()
+    for k in ("loss/policy_avg", "policy/clipfrac_avg", "val/ratio", "optim/grad_norm", "policy/entropy_avg", "num_response_tokens",
+              "debug/vllm_vs_local_logprob_diff_mean"):
+        assert abs(m0[k] - m1[k]) < 1e-5 * max(1.0, abs(m0[k])), (k, m0[k], m1[k])
+
+
 def test_grpo_multi_process_actors(tmp_path):
     """Two learner processes (gloo) + one engine process + cross-process queues, CPU."""
     from open_instruct_b200.actors import ray_compat as ray

@@ -21,6 +21,18 @@ def test_pack_sequences_mask_tool_use(mask_tool_use, want0, want1):
     assert packed.query_responses[0].tolist() == [1, 2, 3, 10, 11, 12] and packed.query_responses[1].tolist() == [4, 5, 20, 21]
 
 
+def test_pack_sequences_strips_pad_tokens_from_queries_and_responses():
+    """A left-padded prompt (or pad == eos inside a prompt) is packed without its pad tokens, as in the reference
+    (``open_instruct/rl_utils.py:294``); log-probs and masks of padded response positions go with them."""
+    packed = rl_utils.pack_sequences(queries=[[0, 0, 1, 2, 3], [4, 0, 5]], responses=[[10, 0, 12], [20, 21]], masks=[[1, 1, 1], [1, 1]],
+                                     pack_length=16, pad_token_id=0, vllm_logprobs=[[-0.1, -0.2, -0.3], [-0.4, -0.5]])
+    assert packed.query_responses[0].tolist() == [1, 2, 3, 10, 12, 4, 5, 20, 21]
+    assert packed.position_ids[0].tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 3]
+    lp = packed.vllm_logprobs[0]
+    assert torch.isnan(lp[:3]).all() and lp[3:5].tolist() == pytest.approx([-0.1, -0.3]) and lp[7:].tolist() == pytest.approx([-0.4, -0.5])
+    assert packed.cu_seqlens[0].tolist() == [0, 5, 9]
+
+
 def _three_samples():
     queries = [list(range(100, 112)), list(range(200, 214)), list(range(300, 314))]
     responses = [list(range(400, 407)), [500], [600]]

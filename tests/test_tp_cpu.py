@@ -3,6 +3,7 @@ row-parallel projections), reproduce the unsharded model."""
 
 import torch
 
+from helpers import free_port
 from open_instruct_b200.models.llama import LlamaModel
 from open_instruct_b200.models.spec import get_spec
 from open_instruct_b200.ops import ref
@@ -176,8 +177,8 @@ def _run_tp_train(world, family, port):
 
 
 def test_training_tensor_parallel_matches_unsharded():
-    _run_tp_train(2, "llama", 29691)
+    _run_tp_train(2, "llama", free_port())
 
 
 def test_training_tensor_parallel_with_data_parallel_and_qk_norm():
-    _run_tp_train(4, "qwen3", 29692)
+    _run_tp_train(4, "qwen3", free_port())

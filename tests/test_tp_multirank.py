@@ -5,6 +5,8 @@ import subprocess
 import sys
 
 import pytest
+
+from helpers import free_port
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -15,7 +17,7 @@ def test_tp2_engine_and_fused_allreduce():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29631", os.path.join(ROOT, "tests", "_tp_worker.py")]
+           "--master-port", str(free_port()), os.path.join(ROOT, "tests", "_tp_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert res.returncode == 0 and "TP_WORKER_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
 
@@ -25,7 +27,7 @@ def test_ulysses_sequence_parallel_matches_single_gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29633", os.path.join(ROOT, "tests", "_sp_worker.py")]
+           "--master-port", str(free_port()), os.path.join(ROOT, "tests", "_sp_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert res.returncode == 0 and "SP_WORKER_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
 
@@ -35,6 +37,6 @@ def test_training_tensor_parallel_fused_path():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29635", os.path.join(ROOT, "tests", "_tp_train_gpu_worker.py")]
+           "--master-port", str(free_port()), os.path.join(ROOT, "tests", "_tp_train_gpu_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert res.returncode == 0 and res.stdout.count("TP_TRAIN_GPU_OK") == 2, res.stdout[-3000:] + res.stderr[-3000:]

@@ -6,6 +6,8 @@ import sys
 
 import pytest
 
+from helpers import free_port
+
 from open_instruct_b200.models import get_spec
 from open_instruct_b200.models.spec import ParamLayout
 from open_instruct_b200.parallel.zero3 import plan_units
@@ -31,7 +33,7 @@ def test_unit_plan_covers_the_decay_region():
 @pytest.mark.parametrize("world,tied,shard_degree", [(2, "0", "0"), (3, "1", "0"), (4, "0", "2")])
 def test_sharded_state_matches_resident_optimizer(world, tied, shard_degree):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29670 + world), os.path.join(HERE, "_zero3_worker.py")]
+           "--master-port", str(free_port()), os.path.join(HERE, "_zero3_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env={**os.environ, "TIED": tied, "SHARD_DEGREE": shard_degree})
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("ZERO3_OK") == world

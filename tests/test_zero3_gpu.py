@@ -6,6 +6,8 @@ import subprocess
 import sys
 
 import pytest
+
+from helpers import free_port
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -24,6 +26,6 @@ def test_sharded_learner_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29637", WORKER]
+           "--master-port", str(free_port()), WORKER]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert res.returncode == 0 and res.stdout.count("ZERO3_GPU_OK") == 2, res.stdout[-3000:] + res.stderr[-3000:]

@@ -6,6 +6,8 @@ import subprocess
 import sys
 
 import pytest
+
+from helpers import free_port
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -22,11 +24,11 @@ def _launch(nproc, extra, port, env=None):
 
 @pytest.mark.parametrize("world", [2, 3])
 def test_gloo_ranks_match_single_process(world):
-    _launch(world, ["--device", "cpu", "--comms", "nccl"], 29600 + world)
+    _launch(world, ["--device", "cpu", "--comms", "nccl"], free_port())
 
 
 @pytest.mark.gpu
 def test_fused_comm_matches_nccl_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    _launch(2, ["--device", "cuda", "--comms", "nccl,fused"], 29611, env={"NCCL_NVLS_ENABLE": "0"})
+    _launch(2, ["--device", "cuda", "--comms", "nccl,fused"], free_port(), env={"NCCL_NVLS_ENABLE": "0"})
