@@ -70,6 +70,54 @@ def measure_weight_sync(engine, learner_flat: torch.Tensor) -> float:
     return ev0.elapsed_time(ev1) / 1e3
 
 
+def run_vllm(a) -> dict:
+    """The same batches through ``vllm.LLM.generate`` offline (TP 1, in-process engine core, random weights of the same
+    architecture): the library the reference's rollout actors wrap (``open_instruct/vllm_utils.py:1188-1313``), measured
+    on the same box as a bar for this package's engine.  None of this package's kernels run here."""
+    import tempfile
+
+    os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
+    os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
+    import vllm
+
+    spec = get_spec(a.model)
+    d = tempfile.mkdtemp(prefix="b200_vllm_cfg_")
+    cfg = spec.to_hf_config()
+    cfg.update({"max_position_embeddings": max(4096, a.prompt_length + a.response_length + 16), "rope_scaling": None,
+                "bos_token_id": 1, "eos_token_id": 2, "pad_token_id": 0})
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    llm = vllm.LLM(model=d, load_format="dummy", skip_tokenizer_init=True, dtype="bfloat16", tensor_parallel_size=1,
+                   gpu_memory_utilization=a.gpu_memory_utilization, max_model_len=a.prompt_length + a.response_length + 16,
+                   seed=a.seed, enable_prefix_caching=True, max_num_seqs=a.max_running, logprobs_mode="processed_logprobs")
+    sp = vllm.SamplingParams(n=a.num_samples_per_prompt_rollout, temperature=a.temperature, top_p=a.top_p, max_tokens=a.response_length,
+                             min_tokens=a.response_length, ignore_eos=True, logprobs=0, detokenize=False, seed=a.seed)
+    dims = ModelDims.from_spec(spec)
+    results = []
+    for b in range(a.num_batches):
+        prompts = synthetic_prompts(a.num_unique_prompts_rollout, a.prompt_length, spec.vocab_size, a.seed + b)
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        t0 = time.perf_counter()
+        outs = llm.generate([{"prompt_token_ids": p} for p in prompts], sp, use_tqdm=False)
+        ev1.record()
+        torch.cuda.synchronize()
+        seconds = max(ev0.elapsed_time(ev1) / 1e3, time.perf_counter() - t0)
+        resp = [len(c.token_ids) for o in outs for c in o.outputs]
+        r = {"generation_time": seconds, "num_new_tokens": sum(resp), "tokens_per_second": sum(resp) / seconds, "weight_sync_time": 0.0,
+             "finish_reasons": dict(collections.Counter(c.finish_reason for o in outs for c in o.outputs)), "batch": b, "warmup": b == 0}
+        r.update(dims.calculate_actor_utilization([len(p) for p in prompts], resp, seconds, a.num_samples_per_prompt_rollout, 1, 1))
+        print(json.dumps(r))
+        if b > 0:
+            results.append(r)
+    summary = aggregate(results) if results else {}
+    summary.update({"impl": f"vllm {vllm.__version__}", "model": a.model, "batch_size": a.num_unique_prompts_rollout,
+                    "samples_per_prompt": a.num_samples_per_prompt_rollout, "response_length": a.response_length, "prompt_length": a.prompt_length})
+    print(json.dumps({"summary": summary}))
+    return summary
+
+
 def aggregate(results: list[dict]) -> dict:
     t = sum(r["generation_time"] for r in results)
     n = sum(r["num_new_tokens"] for r in results)
@@ -97,7 +145,11 @@ def main(argv=None) -> dict:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--csv", default="")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--impl", default="ours", choices=["ours", "vllm"],
+                    help="vllm: the same batches through vllm.LLM.generate (library bar on the same box; not this package's engine)")
     a = ap.parse_args(argv)
+    if a.impl == "vllm":
+        return run_vllm(a)
 
     from .rollout.engine import RolloutEngine
 

@@ -34,10 +34,53 @@ class ModelConfig:
     rope_scaling_old_context_len: int = 8192
     dtype: str = "bfloat16"
     gradient_checkpointing: bool = False
+    use_cache: bool | None = None
     use_peft: bool = False
     lora_r: int = 16
     lora_alpha: int = 32
     lora_dropout: float = 0.05
+    lora_target_modules: list[str] | None = None
+    lora_modules_to_save: list[str] | None = None
+    lora_task_type: str = "CAUSAL_LM"
+    # quantised base weights (bitsandbytes in the reference, ``open_instruct/model_utils.py:209-216``): accepted on the
+    # command line so that recipes parse, refused at start-up when switched on - this framework trains bf16 + fp32 master
+    load_in_8bit: bool = False
+    load_in_4bit: bool = False
+    bnb_4bit_quant_type: str | None = "nf4"
+    use_bnb_nested_quant: bool = False
+
+    def __post_init__(self):
+        check_model_config(self)
+
+
+def check_model_config(cfg) -> None:
+    """Refuse switches that would otherwise parse and do nothing."""
+    if getattr(cfg, "load_in_8bit", False) or getattr(cfg, "load_in_4bit", False) or getattr(cfg, "use_bnb_nested_quant", False):
+        raise ValueError("load_in_8bit / load_in_4bit / use_bnb_nested_quant: quantised base weights are not available in this "
+                         "framework (no bitsandbytes); train bf16 with fp32 master weights, optionally with use_lora")
+    if getattr(cfg, "gradient_checkpointing", False) and getattr(cfg, "use_cache", None):
+        cfg.use_cache = False  # a KV cache is incompatible with activation checkpointing (``open_instruct/model_utils.py:222-226``)
+    mods = getattr(cfg, "lora_target_modules", None)
+    if mods:
+        known = {"q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj", "all-linear"}
+        bad = [m for m in mods if m not in known]
+        if bad:
+            raise ValueError(f"lora_target_modules {bad}: adapters are built for {sorted(known)}")
+
+
+def check_context_parallel(cp_degree, cp_strategy: str, world: int | None = None) -> int:
+    """Sequence-parallel degree that realises a context-parallel request (``open_instruct/olmo_core_utils.py:151-181``).
+    ``ulysses`` is what ``parallel/ulysses.py`` implements (heads are exchanged for sequence around attention); the ring
+    strategies ``llama3`` (all-gather K/V) and ``zig_zag`` are refused with a pointer to it: inside one NVSwitch domain the
+    head exchange moves less data than a K/V ring, and no ring kernel is built."""
+    if not cp_degree or cp_degree <= 1:
+        return 1
+    if cp_strategy != "ulysses":
+        raise ValueError(f"cp_strategy {cp_strategy!r} (ring attention) is not built; use cp_strategy ulysses "
+                         f"(heads must divide by cp_degree {cp_degree})")
+    if world is not None and world % cp_degree:
+        raise ValueError(f"cp_degree {cp_degree} must divide the number of ranks {world}")
+    return int(cp_degree)
 
 
 @dataclass

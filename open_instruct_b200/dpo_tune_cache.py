@@ -68,7 +68,12 @@ def build_deepspeed_config(zero_stage: int, offload_optimizer: bool = False, off
     }
 
 
-def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
+def prepare(args: DPOExperimentConfig, tc: TokenizerConfig):
+    """Everything both DPO drivers share: process group, cached preference dataset, model + sharded learner, data loader and
+    the reference log-prob cache (phase A).  Returns a namespace; ``done`` holds the result when the flags asked for an early
+    exit (``cache_dataset_only`` / ``cache_logprobs_only``)."""
+    from types import SimpleNamespace
+
     rank, world, device = pdist.init_distributed(timeout_s=args.timeout)
     set_seed(args.seed)
     is_main = rank == 0
@@ -93,7 +98,7 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
     if not is_main:
         dataset = _load()
     if args.cache_dataset_only:
-        return {"cached": len(dataset)}
+        return SimpleNamespace(done={"cached": len(dataset)})
     if args.max_train_samples is not None:
         dataset = dataset.select(range(min(args.max_train_samples, len(dataset))))
     if "index" in dataset.column_names:
@@ -154,8 +159,20 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
         reference_cache = build_reference_logprobs_cache(learner, cache_loader, average, forward_fn, len(dataset), device,
                                                          cache_path, is_main)
         logger.info("reference cache ready in %.1fs (%s)", time.time() - t0, cache_path)
-    if args.cache_logprobs_only:
-        return {"cache_built": True}
+    done = {"cache_built": True} if args.cache_logprobs_only else None
+    return SimpleNamespace(done=done, rank=rank, world=world, device=device, is_main=is_main, dataset=dataset, tokenizer=tokenizer, spec=spec,
+                           loader=loader, learner=learner, dims=dims, lt=lt, average=average, forward_fn=forward_fn, reference_cache=reference_cache,
+                           data_world=data_world, steps_per_epoch=steps_per_epoch, max_steps=max_steps)
+
+
+def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
+    p = prepare(args, tc)
+    if p.done is not None:
+        return p.done
+    rank, world, device, is_main, tokenizer, spec = p.rank, p.world, p.device, p.is_main, p.tokenizer, p.spec
+    loader, learner, dims, lt, average, forward_fn = p.loader, p.learner, p.dims, p.lt, p.average, p.forward_fn
+    reference_cache, data_world, max_steps = p.reference_cache, p.data_world, p.max_steps
+
 
     # ------------------------------------------------------------------ resume
     tracker = Tracker(args.output_dir, args.run_name or args.exp_name, asdict(args),

@@ -142,6 +142,14 @@ class DPOExperimentConfig(ExperimentConfig, ModelConfig, DPOConfig, DPOTrainingC
                 raise ValueError("offload_param can only be used with zero_stage 3")
         if self.use_qlora or self.use_8bit_optimizer:
             raise ValueError("quantised training paths are not part of this framework")
+        from .config.schemas import check_context_parallel, check_model_config
+
+        check_model_config(self)
+        if check_context_parallel(self.cp_degree, self.cp_strategy) > 1:
+            raise ValueError("cp_degree > 1: the preference trainer sums log-probs per sequence on one rank and has no context-parallel "
+                             "path; use tensor_parallel_degree or shard_parameters for long pairs (SFT and GRPO support sequence parallelism)")
+        if self.load_balancing_loss:
+            raise ValueError("load_balancing_loss applies to mixture-of-experts models (OLMoE); the model families built here are dense")
 
 
 # ---------------------------------------------------------------------------------- losses

@@ -147,6 +147,8 @@ class FlatArguments:
             self.additional_model_arguments = json.loads(self.additional_model_arguments)
         if self.sequence_parallel_size < 1:
             raise ValueError("sequence_parallel_size must be >= 1")
+        if self.load_balancing_loss:
+            raise ValueError("load_balancing_loss applies to mixture-of-experts models (OLMoE); the model families built here are dense")
 
 
 def build_spec(args: FlatArguments):

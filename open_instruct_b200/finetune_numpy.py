@@ -55,6 +55,12 @@ class Args:
     gradient_checkpointing: bool = False
     logging_steps: int = 1
     exp_name: str = "sft_numpy"
+    # parallelism switches of the reference's entry point (``open_instruct/olmo_core_finetune.py:208-218``,
+    # ``open_instruct/olmo_core_utils.py:151-181``)
+    cp_degree: int | None = None           # context parallelism: every packed micro-batch is split over this many consecutive ranks
+    cp_strategy: str = "ulysses"           # "ulysses" (built: heads <-> sequence exchange); "llama3" / "zig_zag" rings are refused
+    shard_parameters: bool | None = None   # FSDP-style parameter sharding (None: only when the model does not fit resident)
+    fsdp_shard_degree: int | None = None   # HSDP: shard over groups of this many ranks, replicate across the groups
 
 
 def window_to_batch(windows) -> dict:
@@ -87,12 +93,19 @@ def main(args: Args) -> dict:
     set_seed(args.seed)
     spec = get_spec(args.model_name_or_path)
     L = args.sequence_length
-    if args.rank_microbatch_size % L or args.global_batch_size % (args.rank_microbatch_size * world):
-        raise ValueError("rank_microbatch_size must be a multiple of sequence_length, and global_batch_size of rank_microbatch_size x world size")
+    from .config.schemas import check_context_parallel
+
+    cp = check_context_parallel(args.cp_degree, args.cp_strategy, world)
+    dp_world, dp_rank = world // cp, rank // cp  # the ranks of one context-parallel group read the same windows
+    if args.rank_microbatch_size % L or args.global_batch_size % (args.rank_microbatch_size * dp_world):
+        raise ValueError("rank_microbatch_size must be a multiple of sequence_length, and global_batch_size of rank_microbatch_size x "
+                         "data-parallel size (world size / cp_degree)")
+    if cp > 1 and args.rank_microbatch_size % cp:
+        raise ValueError("rank_microbatch_size must divide by cp_degree")
     ds = NumpyPackedFSLDataset(args.dataset_path, L, args.vocab_size or spec.vocab_size)
     win_per_step = args.global_batch_size // L
     win_per_micro = args.rank_microbatch_size // L
-    micro_per_rank = win_per_step // (win_per_micro * world)
+    micro_per_rank = win_per_step // (win_per_micro * dp_world)
     steps_per_epoch = len(ds) // win_per_step
     if steps_per_epoch == 0:
         raise ValueError(f"dataset has {len(ds)} windows of {L} tokens; one step needs {win_per_step}")
@@ -101,7 +114,9 @@ def main(args: Args) -> dict:
     cfg = LearnerConfig(ops=ops, comm=args.comm_backend if world > 1 else "none", learning_rate=args.learning_rate,
                         weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm, lr_scheduler_type=args.lr_scheduler_type,
                         warmup_steps=int(max_steps * args.warmup_ratio), total_steps=max_steps,
-                        gradient_checkpointing=args.gradient_checkpointing, seed=args.seed)
+                        gradient_checkpointing=args.gradient_checkpointing, seed=args.seed, sequence_parallel_size=cp,
+                        sp_max_tokens=args.rank_microbatch_size if cp > 1 else 0, shard_parameters=args.shard_parameters,
+                        shard_degree=args.fsdp_shard_degree)
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
@@ -118,7 +133,7 @@ def main(args: Args) -> dict:
         epoch, in_epoch = divmod(step, steps_per_epoch)
         order = np.random.default_rng(args.seed + epoch).permutation(len(ds))
         base = in_epoch * win_per_step
-        mine = order[base + rank * micro_per_rank * win_per_micro: base + (rank + 1) * micro_per_rank * win_per_micro]
+        mine = order[base + dp_rank * micro_per_rank * win_per_micro: base + (dp_rank + 1) * micro_per_rank * win_per_micro]
         mbs = []
         for m in range(micro_per_rank):
             b = window_to_batch([ds[int(i)] for i in mine[m * win_per_micro:(m + 1) * win_per_micro]])

@@ -653,19 +653,22 @@ class LearnerWorker:
     def flat_weights_cpu(self) -> torch.Tensor:
         return self.learner.full_flat().to("cpu", copy=True)
 
-    def step(self, data: CollatedBatchData) -> dict:
+    def step(self, data: CollatedBatchData, update_ref: bool = True) -> dict:
+        """``update_ref=False``: the caller runs the reference-policy update itself (as a callback after the step)."""
         t0 = time.perf_counter()
         out = grpo_train_step(self.learner, data, self.args, self.ref)
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         out["time/training"] = time.perf_counter() - t0
         self.training_step += 1
-        if self.ref is not None and self.args.ref_policy_update_freq and self.training_step % self.args.ref_policy_update_freq == 0:
+        if update_ref and self.ref is not None and self.args.ref_policy_update_freq and self.training_step % self.args.ref_policy_update_freq == 0:
             self.update_ref_policy()
         return out
 
     def update_ref_policy(self) -> None:
         """Polyak update ref <- alpha * policy + (1 - alpha) * ref on the flat buffers."""
+        if self.ref is None:
+            return
         with torch.no_grad():
             if self.learner.z3 is not None:  # both are sharded the same way: the update is local to every rank's slices
                 self.ref.z3.local16.lerp_(self.learner.z3.local16, self.args.alpha)
@@ -844,227 +847,302 @@ def _weighted_average(per_rank: list[dict]) -> dict:
     return out
 
 
-def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelConfig, streaming: StreamingDataLoaderConfig,
-         vllm: VLLMConfig, tools_config=None) -> dict:
-    from .actor_manager import ActorManager
-    from .actors import ray_compat as ray
-    from .parallel.weight_sync import sync_in_process
+class GRPORun:
+    """One GRPO run: the actor topology (learner ranks, rollout engines, data preparation, actor manager) and the pieces of
+    a training step as methods, so that two drivers can share them - ``run()`` below is the plain loop of ``grpo_fast``
+    (``open_instruct/grpo_fast.py:1796-2052``); ``open_instruct_b200/grpo.py`` drives the same pieces from a ``Trainer`` with
+    callbacks, the structure of the reference's second entry point (``open_instruct/grpo.py``, ``grpo_callbacks.py``)."""
 
-    args = setup_runtime_variables(args, streaming)
-    args.temperature = streaming.temperature
-    args.sp_max_tokens = streaming.pack_length * max(1, args.per_device_train_batch_size)  # largest packed micro-batch
-    validate_configs(args, streaming, vllm)
-    set_seed(args.seed)
-    if tc.tokenizer_name_or_path is None:
-        tc.tokenizer_name_or_path = model_config.model_name_or_path
-    tokenizer = tc.tokenizer
-    dataset = load_prompt_dataset(streaming, tc)
-    eval_dataset = load_prompt_dataset(streaming, tc, eval_split=True)
-    if args.cache_dataset_only:
-        return {"cached": len(dataset)}
-    spec = get_spec(model_config.config_name or model_config.model_name_or_path)
-    if len(tokenizer) > spec.vocab_size:
-        spec = spec.replace(vocab_size=(len(tokenizer) + 7) // 8 * 8)
-    spec = spec.replace(pad_token_id=tokenizer.pad_token_id, eos_token_id=tokenizer.eos_token_id, bos_token_id=tokenizer.bos_token_id)
-    reward_cfg = RewardConfig(apply_r1_style_format_reward=streaming.apply_r1_style_format_reward,
-                              r1_style_format_reward=streaming.r1_style_format_reward,
-                              apply_verifiable_reward=streaming.apply_verifiable_reward, verification_reward=streaming.verification_reward,
-                              non_stop_penalty=streaming.non_stop_penalty, non_stop_penalty_value=streaming.non_stop_penalty_value,
-                              additive_format_reward=streaming.additive_format_reward, reward_aggregator=streaming.reward_aggregator,
-                              verifier_functions=build_all_verifiers(args, streaming))
-    followers: list = []
-    few_gpus = not torch.cuda.is_available() or torch.cuda.device_count() < 2
-    single = args.single_gpu_mode or (args.world_size == 1 and vllm.vllm_num_engines == 1 and few_gpus)
-    max_len = streaming.max_prompt_token_length + max(streaming.response_length, streaming.eval_response_length or 0)
-    tracker = Tracker(args.output_dir, args.run_name, {**asdict(args), **asdict(streaming), **asdict(vllm)},
-                      report_to=("wandb", "tensorboard") if args.with_tracking else ("jsonl",), wandb_project=args.wandb_project_name,
-                      wandb_entity=args.wandb_entity)
-    dims = ModelDims.from_spec(spec)
-    per_step = streaming.num_unique_prompts_rollout * streaming.num_samples_per_prompt_rollout
-    qsize = (streaming.async_steps + 1) * streaming.num_unique_prompts_rollout
-    last: dict = {}
+    def __init__(self, args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelConfig, streaming: StreamingDataLoaderConfig,
+                 vllm: VLLMConfig, tools_config=None):
+        from .actor_manager import ActorManager
+        from .actors import ray_compat as ray
+        from .parallel.weight_sync import sync_in_process
 
-    if single:
-        prompt_q, results_q, eval_q = ray.Queue(local=True), ray.Queue(maxsize=qsize, local=True), ray.Queue(local=True)
-        device = "cuda:0" if torch.cuda.is_available() else "cpu"
-        learner = LearnerWorker.__new__(LearnerWorker)
-        LearnerWorker.__init__(learner, 0, 1, "127.0.0.1", pdist.find_free_port(), spec, args, model_config, args.num_training_steps, device=device)
-        engine = EngineWorker(spec, prompt_q, results_q, eval_q, reward_cfg, tokenizer, device=device, ops=args.ops, seed=args.seed,
-                              max_model_len=max_len, num_blocks=None if torch.cuda.is_available() else 512,
-                              gpu_memory_utilization=0.25 if torch.cuda.is_available() else 0.9,
-                              flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates, envs_config=tools_config)
-        learners, engines = [learner], [engine]
-        single_objs = True
-    else:
-        import dataclasses
+        args = setup_runtime_variables(args, streaming)
+        args.temperature = streaming.temperature
+        args.sp_max_tokens = streaming.pack_length * max(1, args.per_device_train_batch_size)  # largest packed micro-batch
+        validate_configs(args, streaming, vllm)
+        set_seed(args.seed)
+        if tc.tokenizer_name_or_path is None:
+            tc.tokenizer_name_or_path = model_config.model_name_or_path
+        tokenizer = tc.tokenizer
+        dataset = load_prompt_dataset(streaming, tc)
+        eval_dataset = load_prompt_dataset(streaming, tc, eval_split=True)
+        self.cached_only = None
+        if args.cache_dataset_only:
+            self.cached_only = {"cached": len(dataset)}
+            return
+        spec = get_spec(model_config.config_name or model_config.model_name_or_path)
+        if len(tokenizer) > spec.vocab_size:
+            spec = spec.replace(vocab_size=(len(tokenizer) + 7) // 8 * 8)
+        spec = spec.replace(pad_token_id=tokenizer.pad_token_id, eos_token_id=tokenizer.eos_token_id, bos_token_id=tokenizer.bos_token_id)
+        reward_cfg = RewardConfig(apply_r1_style_format_reward=streaming.apply_r1_style_format_reward,
+                                  r1_style_format_reward=streaming.r1_style_format_reward,
+                                  apply_verifiable_reward=streaming.apply_verifiable_reward, verification_reward=streaming.verification_reward,
+                                  non_stop_penalty=streaming.non_stop_penalty, non_stop_penalty_value=streaming.non_stop_penalty_value,
+                                  additive_format_reward=streaming.additive_format_reward, reward_aggregator=streaming.reward_aggregator,
+                                  verifier_functions=build_all_verifiers(args, streaming))
+        followers: list = []
+        few_gpus = not torch.cuda.is_available() or torch.cuda.device_count() < 2
+        single = args.single_gpu_mode or (args.world_size == 1 and vllm.vllm_num_engines == 1 and few_gpus)
+        max_len = streaming.max_prompt_token_length + max(streaming.response_length, streaming.eval_response_length or 0)
+        tracker = Tracker(args.output_dir, args.run_name, {**asdict(args), **asdict(streaming), **asdict(vllm)},
+                          report_to=("wandb", "tensorboard") if args.with_tracking else ("jsonl",), wandb_project=args.wandb_project_name,
+                          wandb_entity=args.wandb_entity)
+        dims = ModelDims.from_spec(spec)
+        per_step = streaming.num_unique_prompts_rollout * streaming.num_samples_per_prompt_rollout
+        qsize = (streaming.async_steps + 1) * streaming.num_unique_prompts_rollout
+        last: dict = {}
 
-        cuda = torch.cuda.is_available()
-        prompt_q, results_q, eval_q = ray.Queue(), ray.Queue(maxsize=qsize), ray.Queue()
-        tc_plain = dataclasses.replace(tc)  # without the cached tokenizer object
-        port = pdist.find_free_port()
-        LW, EW = ray.remote(LearnerWorker), ray.remote(EngineWorker)
-        from concurrent.futures import ThreadPoolExecutor
-
-        with ThreadPoolExecutor(max_workers=args.world_size) as ex:  # ranks must start together: they rendezvous in __init__
-            futs = [ex.submit(LW.options(num_gpus=1 if cuda else 0, max_concurrency=4).remote, r, args.world_size, "127.0.0.1", port,
-                              spec, args, model_config, args.num_training_steps, None if cuda else "cpu")
-                    for r in range(args.world_size)]
-            learners = [f.result() for f in futs]
-        init_flat = ray.get(learners[0].flat_weights_cpu.remote())
-        tp = vllm.vllm_tensor_parallel_size if cuda else 1
-        followers = []
-        if tp == 1:
-            engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
-                spec, prompt_q, results_q, eval_q, reward_cfg, tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len,
-                None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates, 256, tools_config)
-                for i in range(vllm.vllm_num_engines)]
+        if single:
+            prompt_q, results_q, eval_q = ray.Queue(local=True), ray.Queue(maxsize=qsize, local=True), ray.Queue(local=True)
+            device = "cuda:0" if torch.cuda.is_available() else "cpu"
+            learner = LearnerWorker.__new__(LearnerWorker)
+            LearnerWorker.__init__(learner, 0, 1, "127.0.0.1", pdist.find_free_port(), spec, args, model_config, args.num_training_steps, device=device)
+            engine = EngineWorker(spec, prompt_q, results_q, eval_q, reward_cfg, tokenizer, device=device, ops=args.ops, seed=args.seed,
+                                  max_model_len=max_len, num_blocks=None if torch.cuda.is_available() else 512,
+                                  gpu_memory_utilization=0.25 if torch.cuda.is_available() else 0.9,
+                                  flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates, envs_config=tools_config)
+            learners, engines = [learner], [engine]
+            single_objs = True
         else:
-            # every rank of a tensor-parallel engine is its own process on its own GPU; the ranks of one engine rendezvous in
-            # __init__, so they are created together
-            tp_ports = [pdist.find_free_port() for _ in range(vllm.vllm_num_engines)]  # one rendezvous per engine
-            with ThreadPoolExecutor(max_workers=tp * vllm.vllm_num_engines) as ex:
-                futs = [[ex.submit(EW.options(num_gpus=1, max_concurrency=8).remote, spec, prompt_q, results_q, eval_q, reward_cfg if r == 0 else None,
-                                   tc_plain, "auto", args.ops, args.seed + 100 * i, max_len, None, vllm.vllm_gpu_memory_utilization, init_flat,
-                                   streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", tp_ports[i])
-                         for r in range(tp)] for i in range(vllm.vllm_num_engines)]
-                handles = [[f.result() for f in row] for row in futs]
-            engines = [row[0] for row in handles]
-            followers = [h for row in handles for h in row[1:]]
-        ray.get([e.ready.remote() for e in engines + followers] + [l.ready.remote() for l in learners])
-        if cuda:
-            descs = ray.get([e.weight_buffer_ipc.remote() for e in engines + followers])
-            ray.get([l.connect_engines.remote(descs) for l in learners])
-        single_objs = False
+            import dataclasses
 
-    def call(obj, method, *a):
-        return getattr(obj, method)(*a) if single_objs else ray.get(getattr(obj, method).remote(*a))
+            cuda = torch.cuda.is_available()
+            prompt_q, results_q, eval_q = ray.Queue(), ray.Queue(maxsize=qsize), ray.Queue()
+            tc_plain = dataclasses.replace(tc)  # without the cached tokenizer object
+            port = pdist.find_free_port()
+            LW, EW = ray.remote(LearnerWorker), ray.remote(EngineWorker)
+            from concurrent.futures import ThreadPoolExecutor
 
-    def call_all(objs, method, *a, per_obj=None):
-        if single_objs:
+            with ThreadPoolExecutor(max_workers=args.world_size) as ex:  # ranks must start together: they rendezvous in __init__
+                futs = [ex.submit(LW.options(num_gpus=1 if cuda else 0, max_concurrency=4).remote, r, args.world_size, "127.0.0.1", port,
+                                  spec, args, model_config, args.num_training_steps, None if cuda else "cpu")
+                        for r in range(args.world_size)]
+                learners = [f.result() for f in futs]
+            init_flat = ray.get(learners[0].flat_weights_cpu.remote())
+            tp = vllm.vllm_tensor_parallel_size if cuda else 1
+            followers = []
+            if tp == 1:
+                engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
+                    spec, prompt_q, results_q, eval_q, reward_cfg, tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len,
+                    None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates, 256, tools_config)
+                    for i in range(vllm.vllm_num_engines)]
+            else:
+                # every rank of a tensor-parallel engine is its own process on its own GPU; the ranks of one engine rendezvous in
+                # __init__, so they are created together
+                tp_ports = [pdist.find_free_port() for _ in range(vllm.vllm_num_engines)]  # one rendezvous per engine
+                with ThreadPoolExecutor(max_workers=tp * vllm.vllm_num_engines) as ex:
+                    futs = [[ex.submit(EW.options(num_gpus=1, max_concurrency=8).remote, spec, prompt_q, results_q, eval_q, reward_cfg if r == 0 else None,
+                                       tc_plain, "auto", args.ops, args.seed + 100 * i, max_len, None, vllm.vllm_gpu_memory_utilization, init_flat,
+                                       streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", tp_ports[i])
+                             for r in range(tp)] for i in range(vllm.vllm_num_engines)]
+                    handles = [[f.result() for f in row] for row in futs]
+                engines = [row[0] for row in handles]
+                followers = [h for row in handles for h in row[1:]]
+            ray.get([e.ready.remote() for e in engines + followers] + [l.ready.remote() for l in learners])
+            if cuda:
+                descs = ray.get([e.weight_buffer_ipc.remote() for e in engines + followers])
+                ray.get([l.connect_engines.remote(descs) for l in learners])
+            single_objs = False
+
+        # ---- everything the step methods need
+        self.args, self.tc, self.model_config, self.streaming, self.vllm = args, tc, model_config, streaming, vllm
+        self.ray, self.spec, self.tokenizer, self.dataset, self.eval_dataset = ray, spec, tokenizer, dataset, eval_dataset
+        self.learners, self.engines, self.followers, self.single_objs, self.single = learners, engines, followers, single_objs, single
+        self.prompt_q, self.results_q, self.eval_q = prompt_q, results_q, eval_q
+        self.tracker, self.dims, self.per_step, self.max_len = tracker, dims, per_step, max_len
+        self.total_params = ParamLayoutTotal(spec)
+        self.manager = ActorManager({"prompts": prompt_q, "results": results_q, "eval": eval_q},
+                                    enable_dashboard=args.enable_queue_dashboard and not single, port=args.queue_dashboard_port)
+        self.manager.set_kv_cache_max_concurrency(self.call(engines[0], "get_kv_cache_info", max_len))
+        self.sp = max(1, args.sequence_parallel_size)  # the ranks of one sequence-parallel group train on the same packs
+        self.prep = DataPreparation(dataset, streaming, prompt_q, results_q, tokenizer, args.world_size // self.sp, args.per_device_train_batch_size,
+                                    args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p)
+        self.resume_step, self.eval_outstanding, self.total_tokens, self.t_run = 0, 0, 0, time.time()
+        self.max_score = streaming.verification_reward + (streaming.r1_style_format_reward if streaming.apply_r1_style_format_reward else 0.0)
+        self.last: dict = {}
+        self.ref_update_in_step = True  # False: a callback of the driver updates the reference policy after the step
+        self._closed = False
+
+    # ------------------------------------------------------------------ actor calls
+    def call(self, obj, method, *a):
+        return getattr(obj, method)(*a) if self.single_objs else self.ray.get(getattr(obj, method).remote(*a))
+
+    def call_all(self, objs, method, *a, per_obj=None):
+        if self.single_objs:
             return [getattr(o, method)(*(per_obj[i] if per_obj else a)) for i, o in enumerate(objs)]
-        return ray.get([getattr(o, method).remote(*(per_obj[i] if per_obj else a)) for i, o in enumerate(objs)])
+        return self.ray.get([getattr(o, method).remote(*(per_obj[i] if per_obj else a)) for i, o in enumerate(objs)])
 
-    total_params = ParamLayoutTotal(spec)
+    # ------------------------------------------------------------------ pieces of a step
+    def weight_sync(self, step: int) -> float:
+        from .parallel.weight_sync import sync_in_process
 
-    def weight_sync(step: int) -> float:
         t0 = time.perf_counter()
-        if single_objs:
-            return sync_in_process(learners[0].flat_weights(), engines, step, total_params)
+        if self.single_objs:
+            return sync_in_process(self.learners[0].flat_weights(), self.engines, step, self.total_params)
         if torch.cuda.is_available():
             # the learners store straight into the engines' parameter buffers: every engine first finishes the step it is
             # in and holds the next one back until the new version is complete
-            call_all(engines, "begin_weight_update")
+            self.call_all(self.engines, "begin_weight_update")
             try:
-                call_all(learners, "push_weights")
+                self.call_all(self.learners, "push_weights")
             except BaseException:
-                call_all(engines, "abort_weight_update")
+                self.call_all(self.engines, "abort_weight_update")
                 raise
-            call_all(engines, "update_weights", None, step)
+            self.call_all(self.engines, "update_weights", None, step)
         else:
-            flat = call(learners[0], "flat_weights_cpu")
-            call_all(engines, "update_weights", flat, step)
+            flat = self.call(self.learners[0], "flat_weights_cpu")
+            self.call_all(self.engines, "update_weights", flat, step)
         return time.perf_counter() - t0
 
-    manager = ActorManager({"prompts": prompt_q, "results": results_q, "eval": eval_q}, enable_dashboard=args.enable_queue_dashboard and not single,
-                           port=args.queue_dashboard_port)
-    manager.set_kv_cache_max_concurrency(call(engines[0], "get_kv_cache_info", max_len))
-    sp = max(1, args.sequence_parallel_size)  # the ranks of one sequence-parallel group train on the same packs
-    prep = DataPreparation(dataset, streaming, prompt_q, results_q, tokenizer, args.world_size // sp, args.per_device_train_batch_size,
-                           args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p)
-    resume_step = 0
-    if args.checkpoint_state_dir and os.path.isdir(args.checkpoint_state_dir):
-        st = call_all(learners, "load_checkpoint_state", args.checkpoint_state_dir)[0]
-        if st:
-            resume_step = st["training_step"]
-            prep.set_state(st["data_prep_actor_state"])
-            prep.next_step = resume_step + 1
-            prep.trainer_step = resume_step
-            prep.model_step = resume_step
-            weight_sync(resume_step)
-    prep.start()
-    eval_outstanding = 0
-    max_score = streaming.verification_reward + (streaming.r1_style_format_reward if streaming.apply_r1_style_format_reward else 0.0)
-    total_tokens, t_run = 0, time.time()
-    try:
-        for step in range(resume_step + 1, args.num_training_steps + 1):
-            t_step = time.perf_counter()
-            call_all(engines, "check_background_threads")
-            per_group = [prep.get_data(g, step) for g in range(args.world_size // sp)]
-            per_rank = [per_group[r // sp] for r in range(args.world_size)]
-            prep_metrics = per_rank[0][1]
-            t_wait = time.perf_counter() - t_step
-            metrics = _weighted_average(call_all(learners, "step", per_obj=[(d,) for d, _ in per_rank]))
-            manager.report_training_step_time(metrics.get("time/training", 0.0))
-            # ---- weight sync (every step)
-            manager.set_should_stop(True)
-            call_all(engines, "set_should_stop", True)
-            t_sync = weight_sync(step)
-            if t_sync > WEIGHT_SYNC_TIMEOUT_S:
-                raise TimeoutError("weight sync exceeded its time limit")
-            sync_err = None
-            if args.verify_weight_sync and not single_objs:
-                sync_err = 0.0
-                for h in list(engines) + list(followers):
-                    got, r, n = call(h, "weights_checksum", step)
-                    sync_err = max(sync_err, abs(got - call(learners[0], "weights_checksum", r, n)))
-            call_all(engines, "set_should_stop", False)
-            manager.set_should_stop(False)
-            prep.set_model_step(step)
-            tokens = prep_metrics.get("val/total_response_tokens", 0) + prep_metrics.get("val/total_prompt_tokens", 0)
-            total_tokens += tokens
-            dt = time.perf_counter() - t_step
-            last = {**prep_metrics, **metrics, "training_step": step, "episode": step * per_step, "time/total": dt,
-                    "time/weight_sync": t_sync, "time/trainer_waiting_for_data": t_wait,
-                    **({"debug/weight_sync_checksum_diff": sync_err} if sync_err is not None else {}),
-                    "learner_tokens_per_second_step": tokens / max(metrics.get("time/training", dt), 1e-9),
-                    "learner_tokens_per_second_overall": total_tokens / max(time.time() - t_run, 1e-9),
-                    "learner_mfu": dims.approximate_learner_utilization(tokens, prep_metrics.get("val/sequence_lengths", 1.0) +
-                                                                        streaming.max_prompt_token_length, metrics.get("time/training", dt),
-                                                                        args.world_size) if torch.cuda.is_available() else 0.0}
-            # ---- evaluation: prompts ride along with the training rollouts; results are picked up when they are ready
-            is_last = step == args.num_training_steps
-            if eval_dataset is not None and len(eval_dataset) and args.local_eval_every > 0 and (step % args.local_eval_every == 0 or is_last) \
-                    and eval_outstanding == 0:
-                eval_outstanding = submit_eval_prompts(eval_dataset, prompt_q, streaming, args, step, vllm.vllm_top_p)
-            if eval_outstanding:
-                em, n_got = collect_eval_results(eval_q, eval_outstanding, 600.0 if is_last else 0.0, args, max_score)
-                if n_got >= eval_outstanding or is_last:
-                    last.update(em)
-                    eval_outstanding = 0
-                elif n_got:
-                    # partial drain: put the count back so that the rest is not waited for twice
-                    eval_outstanding -= n_got
-                    last.update({k: v for k, v in em.items() if k == "eval/num_prompts"})
-            tracker.log(last, step)
-            logger.info("step %d: score %.3f loss %.4f len %.1f sync %.3fs", step, last.get("scores", 0.0), last.get("loss/total_avg", 0.0),
-                        last.get("val/sequence_lengths", 0.0), t_sync)
-            if args.save_freq > 0 and step % args.save_freq == 0:
-                call_all(learners, "save_model", os.path.join(f"{args.output_dir}_checkpoints", f"step_{step}"), tc.tokenizer_name_or_path)
-            if args.checkpoint_state_dir and args.checkpoint_state_freq > 0 and step % args.checkpoint_state_freq == 0:
-                client = {"training_step": step, "optimizer_steps": call(learners[0], "optimizer_steps"), "episode": step * per_step,
-                          "num_total_tokens": total_tokens, "data_prep_actor_state": prep.get_state()}
-                call_all(learners, "save_checkpoint_state", args.checkpoint_state_dir, client)
-        if args.save_final_model:
-            call_all(learners, "save_model", args.output_dir, tc.tokenizer_name_or_path)
-    finally:
-        prep.shutdown()
-        if single_objs:
-            for e in engines:
+    def begin(self) -> int:
+        """Resume from ``checkpoint_state_dir`` when it holds a state, start the data-preparation thread; returns the step
+        already completed."""
+        args, prep = self.args, self.prep
+        if args.checkpoint_state_dir and os.path.isdir(args.checkpoint_state_dir):
+            st = self.call_all(self.learners, "load_checkpoint_state", args.checkpoint_state_dir)[0]
+            if st:
+                self.resume_step = st["training_step"]
+                prep.set_state(st["data_prep_actor_state"])
+                prep.next_step = self.resume_step + 1
+                prep.trainer_step = self.resume_step
+                prep.model_step = self.resume_step
+                self.weight_sync(self.resume_step)
+        prep.start()
+        self.t_run = time.time()
+        return self.resume_step
+
+    def train_step(self, step: int) -> dict:
+        """Health check, this step's packed data for every learner rank, one learner step on all ranks."""
+        args = self.args
+        t_step = time.perf_counter()
+        self.call_all(self.engines, "check_background_threads")
+        per_group = [self.prep.get_data(g, step) for g in range(args.world_size // self.sp)]
+        per_rank = [per_group[r // self.sp] for r in range(args.world_size)]
+        prep_metrics = per_rank[0][1]
+        t_wait = time.perf_counter() - t_step
+        metrics = _weighted_average(self.call_all(self.learners, "step", per_obj=[(d, self.ref_update_in_step) for d, _ in per_rank]))
+        self.manager.report_training_step_time(metrics.get("time/training", 0.0))
+        tokens = prep_metrics.get("val/total_response_tokens", 0) + prep_metrics.get("val/total_prompt_tokens", 0)
+        self.total_tokens += tokens
+        self.last = {**prep_metrics, **metrics, "training_step": step, "episode": step * self.per_step, "time/trainer_waiting_for_data": t_wait,
+                     "learner_tokens_per_second_step": tokens / max(metrics.get("time/training", time.perf_counter() - t_step), 1e-9),
+                     "learner_tokens_per_second_overall": self.total_tokens / max(time.time() - self.t_run, 1e-9),
+                     "learner_mfu": self.dims.approximate_learner_utilization(
+                         tokens, prep_metrics.get("val/sequence_lengths", 1.0) + self.streaming.max_prompt_token_length,
+                         metrics.get("time/training", time.perf_counter() - t_step), args.world_size) if torch.cuda.is_available() else 0.0}
+        self._t_step = t_step
+        return self.last
+
+    def sync_step(self, step: int) -> float:
+        """Pause the engines, push the new weights, (optionally) compare checksums, resume."""
+        args = self.args
+        self.manager.set_should_stop(True)
+        self.call_all(self.engines, "set_should_stop", True)
+        t_sync = self.weight_sync(step)
+        if t_sync > WEIGHT_SYNC_TIMEOUT_S:
+            raise TimeoutError("weight sync exceeded its time limit")
+        if args.verify_weight_sync and not self.single_objs:
+            sync_err = 0.0
+            for h in list(self.engines) + list(self.followers):
+                got, r, n = self.call(h, "weights_checksum", step)
+                sync_err = max(sync_err, abs(got - self.call(self.learners[0], "weights_checksum", r, n)))
+            self.last["debug/weight_sync_checksum_diff"] = sync_err
+        self.call_all(self.engines, "set_should_stop", False)
+        self.manager.set_should_stop(False)
+        self.prep.set_model_step(step)
+        self.last["time/weight_sync"] = t_sync
+        return t_sync
+
+    def evaluate(self, step: int) -> None:
+        """Evaluation prompts ride along with the training rollouts; results are picked up when they are ready."""
+        args, streaming = self.args, self.streaming
+        is_last = step == args.num_training_steps
+        eval_due = ((args.eval_on_step_0 and step == 1) or step % args.local_eval_every == 0) if args.local_eval_every > 0 else False
+        if self.eval_dataset is not None and len(self.eval_dataset) and args.local_eval_every > 0 and (eval_due or is_last) \
+                and self.eval_outstanding == 0:
+            self.eval_outstanding = submit_eval_prompts(self.eval_dataset, self.prompt_q, streaming, args, step, self.vllm.vllm_top_p)
+        if self.eval_outstanding:
+            em, n_got = collect_eval_results(self.eval_q, self.eval_outstanding, 600.0 if is_last else 0.0, args, self.max_score)
+            if n_got >= self.eval_outstanding or is_last:
+                self.last.update(em)
+                self.eval_outstanding = 0
+            elif n_got:
+                # partial drain: put the count back so that the rest is not waited for twice
+                self.eval_outstanding -= n_got
+                self.last.update({k: v for k, v in em.items() if k == "eval/num_prompts"})
+
+    def log_step(self, step: int) -> None:
+        self.last["time/total"] = time.perf_counter() - getattr(self, "_t_step", time.perf_counter())
+        self.tracker.log(self.last, step)
+        logger.info("step %d: score %.3f loss %.4f len %.1f sync %.3fs", step, self.last.get("scores", 0.0), self.last.get("loss/total_avg", 0.0),
+                    self.last.get("val/sequence_lengths", 0.0), self.last.get("time/weight_sync", 0.0))
+
+    def save_model(self, step: int | None = None) -> None:
+        out = self.args.output_dir if step is None else os.path.join(f"{self.args.output_dir}_checkpoints", f"step_{step}")
+        self.call_all(self.learners, "save_model", out, self.tc.tokenizer_name_or_path)
+
+    def save_state(self, step: int) -> None:
+        client = {"training_step": step, "optimizer_steps": self.call(self.learners[0], "optimizer_steps"), "episode": step * self.per_step,
+                  "num_total_tokens": self.total_tokens, "data_prep_actor_state": self.prep.get_state()}
+        self.call_all(self.learners, "save_checkpoint_state", self.args.checkpoint_state_dir, client)
+
+    def checkpoint(self, step: int) -> None:
+        args = self.args
+        if args.save_freq > 0 and (step % args.save_freq == 0 or (args.eval_on_step_0 and step == 1)):
+            self.save_model(step)
+        if args.checkpoint_state_dir and args.checkpoint_state_freq > 0 and step % args.checkpoint_state_freq == 0:
+            self.save_state(step)
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        ray = self.ray
+        self.prep.shutdown()
+        if self.single_objs:
+            for e in self.engines:
                 e.shutdown()
         else:
-            for h in list(engines):
+            for h in list(self.engines):
                 try:
                     ray.get(h.shutdown.remote(), timeout=20)  # tensor-parallel leaders release their followers first
                 except Exception:  # noqa: BLE001
                     pass
-            for h in list(engines) + list(followers) + list(learners):
+            for h in list(self.engines) + list(self.followers) + list(self.learners):
                 ray.kill(h)
-            for q in (prompt_q, results_q, eval_q):
+            for q in (self.prompt_q, self.results_q, self.eval_q):
                 q.shutdown()
-        manager.shutdown()
-        tracker.close()
-    last["num_training_steps"] = args.num_training_steps
-    return last
+        self.manager.shutdown()
+        self.tracker.close()
+
+    # ------------------------------------------------------------------ the plain loop
+    def run(self) -> dict:
+        args = self.args
+        try:
+            start = self.begin()
+            for step in range(start + 1, args.num_training_steps + 1):
+                self.train_step(step)
+                self.sync_step(step)
+                self.evaluate(step)
+                self.log_step(step)
+                self.checkpoint(step)
+            if args.save_final_model:
+                self.save_model()
+        finally:
+            self.close()
+        self.last["num_training_steps"] = args.num_training_steps
+        return self.last
+
+
+def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelConfig, streaming: StreamingDataLoaderConfig,
+         vllm: VLLMConfig, tools_config=None) -> dict:
+    run = GRPORun(args, tc, model_config, streaming, vllm, tools_config)
+    if run.cached_only is not None:
+        return run.cached_only
+    return run.run()
 
 
 if __name__ == "__main__":

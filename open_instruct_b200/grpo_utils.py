@@ -46,6 +46,7 @@ class GRPOExperimentConfig(ExperimentConfig):
     world_size: int | None = None
     num_training_steps: int | None = None
     local_eval_every: int = 100
+    eval_on_step_0: bool = False  # also evaluate (and save, with save_freq > 0) at the first training step
     save_freq: int = 200
     verify_weight_sync: bool = False  # debug: after every sync compare weight checksums of the learner and every engine rank
     save_final_model: bool = True  # benchmarks switch the final Hugging Face export off
@@ -132,6 +133,9 @@ class GRPOExperimentConfig(ExperimentConfig):
                 raise ValueError(f"loss_denominator must be 'token' or a positive number, got {self.loss_denominator!r}") from None
         if self.num_mini_batches < 1 or self.num_epochs < 1:
             raise ValueError("num_mini_batches and num_epochs must be >= 1")
+        if self.eval_on_step_0 and self.local_eval_every <= 0:
+            raise ValueError("`eval_on_step_0` requires `local_eval_every` > 0. Set `local_eval_every` to a positive value or "
+                             "disable `eval_on_step_0`.")
         if self.sequence_parallel_size < 1:
             raise ValueError("sequence_parallel_size must be >= 1")
         # (the reference needs deepspeed_stage 3 for sequence parallelism, ``open_instruct/grpo_utils.py:275-276``; here it

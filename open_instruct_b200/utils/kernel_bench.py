@@ -108,6 +108,21 @@ def main():
                 rec(f"cublas_dgrad_{name}", time_op(lambda: torch.matmul(dy, w), args.iters), fl)
                 rec(f"cublas_wgrad_{name}", time_op(lambda: torch.matmul(dy.t(), x), args.iters), fl)
             del x, w, dy, g
+    if "gemm_layouts" in only:
+        # which part of the weight-gradient GEMM costs what: every operand layout x epilogue on one shape (M x N output, K tokens)
+        for name, (M, N) in {"gate_up_wgrad": (2 * F, D), "qkv_wgrad": ((Hq + 2 * Hkv) * Dh, D)}.items():
+            K = T
+            fl = 2.0 * M * N * K
+            a_k, a_m = bf(M, K), bf(K, M)
+            b_k, b_n = bf(N, K), bf(K, N)
+            out16, out32 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16), torch.zeros(M, N, device="cuda")
+            for a_mn in (False, True):
+                for b_mn in (False, True):
+                    for mode, mname, out in ((fused.OUT_BF16, "bf16", out16), (fused.OUT_F32, "f32", out32), (fused.OUT_F32_ACC, "f32acc", out32)):
+                        a, b = (a_m if a_mn else a_k), (b_n if b_mn else b_k)
+                        rec(f"{name}_a{'MN' if a_mn else 'K'}_b{'MN' if b_mn else 'K'}_{mname}",
+                            time_op(lambda: fused.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, out_mode=mode, impl=args.impl), args.iters), fl)
+            del a_k, a_m, b_k, b_n, out16, out32
     if "decode_gemm" in only:
         # decode-sized GEMMs: a stream over the weights; the roofline is HBM bandwidth
         for M in (64, 256, 512):
@@ -116,6 +131,8 @@ def main():
                 by = (N * K + M * K + M * N) * 2
                 for impl in ("1cta", "2cta", "skinny", "skinny128"):
                     rec(f"decode_gemm_{name}_M{M}_{impl}", time_op(lambda: fused.gemm(x, w, impl=impl), args.iters), bytes_=by)
+                if args.cublas:
+                    rec(f"lib_cublas_decode_gemm_{name}_M{M}", time_op(lambda: torch.matmul(x, w.t()), args.iters), bytes_=by)
                 if name in ("o", "down"):
                     acc = torch.zeros(M, N, device="cuda")
                     for sk in (2, 4, 8):
