@@ -53,8 +53,12 @@ def parse():
     ap.add_argument("--skip_e2e", action="store_true")
     ap.add_argument("--shard_parameters", action="store_true",
                     help="sft: ZeRO-3 style gather-on-use parameter sharding instead of the resident bf16 copy (for models that do not fit)")
-    ap.add_argument("--task", default="sft", choices=["sft", "dpo"],
-                    help="sft: the headline metric; dpo: DPO train tokens/s with cached reference log-probs (same JSON shape)")
+    ap.add_argument("--task", default="sft", choices=["sft", "dpo", "grpo"],
+                    help="sft: the headline metric; dpo: DPO train tokens/s with cached reference log-probs (same JSON shape); "
+                         "grpo: RLVR step seconds (learner + rollout-engine processes, weight sync every step)")
+    ap.add_argument("--grpo_response_length", type=int, default=2048)
+    ap.add_argument("--grpo_prompts", type=int, default=64)
+    ap.add_argument("--grpo_samples", type=int, default=8)
     ap.add_argument("--pairs_per_gpu", type=int, default=16)
     ap.add_argument("--pairs_per_micro", type=int, default=2)
     return ap.parse_args()
@@ -192,6 +196,30 @@ def run_dpo(args) -> int:
     return 0
 
 
+def run_grpo(args) -> int:
+    """GRPO step seconds with the GPUs of the node split between learner ranks and rollout engines the way the 8-GPU recipe
+    does (4 learners + 2 engines of tensor-parallel size 2); fewer GPUs keep the learner : engine ratio at 1 : 1.  The GRPO
+    driver starts its own actor processes (one per GPU), so under ``torchrun`` only rank 0 runs it and the others leave."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RUN_ID", "GROUP_RANK", "ROLE_RANK", "LOCAL_WORLD_SIZE",
+              "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS"):
+        os.environ.pop(k, None)  # the actors rendezvous among themselves
+    import bench_grpo
+
+    n = max(1, args.gpus)
+    layout = {1: ["--single_gpu_mode"], 2: ["--learners", "1", "--engines", "1"], 4: ["--learners", "2", "--engines", "2"],
+              8: ["--learners", "4", "--engines", "2", "--engine_tp", "2"]}.get(n)
+    if layout is None:
+        raise SystemExit("--task grpo runs on 1, 2, 4 or 8 GPUs")
+    import torch
+
+    layout = layout + ["--ops", "fused" if torch.cuda.is_available() else "ref"]
+    return bench_grpo.main(layout + ["--steps", str(args.steps + args.warmup), "--warmup", str(args.warmup), "--model", args.model,
+                                     "--prompts", str(args.grpo_prompts), "--samples", str(args.grpo_samples),
+                                     "--response_length", str(args.grpo_response_length), "--pack_length", str(max(4096, args.grpo_response_length + 256))])
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -203,6 +231,8 @@ def main():
         return run_hf_stack(args)
     if args.task == "dpo":
         return run_dpo(args)
+    if args.task == "grpo":
+        return run_grpo(args)
     import torch
 
     from open_instruct_b200.data.collate import pin, to_device

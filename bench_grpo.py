@@ -17,7 +17,7 @@ import statistics
 import tempfile
 
 
-def main() -> int:
+def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--learners", type=int, default=1)
     ap.add_argument("--engines", type=int, default=1)
@@ -31,7 +31,8 @@ def main() -> int:
     ap.add_argument("--single_gpu_mode", action="store_true")
     ap.add_argument("--ops", default="fused")
     ap.add_argument("--engine_tp", type=int, default=1, help="tensor-parallel size of every rollout engine (one process and GPU per rank)")
-    a = ap.parse_args()
+    ap.add_argument("--warmup", type=int, default=1, help="steps left out of the medians (step 1 includes every cold start)")
+    a = ap.parse_args(argv)
 
     from open_instruct_b200.actors import ray_compat as ray
     from open_instruct_b200.config.schemas import ModelConfig
@@ -58,10 +59,10 @@ def main() -> int:
     finally:
         ray.shutdown()
     lines = [json.loads(line) for line in open(os.path.join(args.output_dir, "metrics.jsonl"))]
-    steady = lines[1:] or lines
+    steady = lines[a.warmup:] or lines
     med = lambda k: statistics.median(float(x.get(k, 0.0)) for x in steady)
-    out = {"metric": "grpo_step_seconds", "value": med("time/total"), "unit": "s", "higher_is_better": False, "n_gpus": a.learners + a.engines * a.engine_tp,
-           "steps": len(steady), "warmup": 1, "first_step_s": float(lines[0].get("time/total", 0.0)), "learner_step_s": med("time/training"),
+    out = {"metric": "grpo_step_seconds", "value": med("time/total"), "unit": "s", "higher_is_better": False, "n_gpus": 1 if a.single_gpu_mode else a.learners + a.engines * a.engine_tp,
+           "steps": len(steady), "warmup": a.warmup, "scaling": "strong", "first_step_s": float(lines[0].get("time/total", 0.0)), "learner_step_s": med("time/training"),
            "weight_sync_s": med("time/weight_sync"), "waiting_for_rollouts_s": med("time/trainer_waiting_for_data"),
            "response_tokens_per_step": med("val/total_response_tokens"), "mean_response_length": med("val/sequence_lengths"),
            "dtype": "bf16", "data": "synthetic arithmetic prompts, random-init weights",

@@ -139,6 +139,12 @@ class LlamaModel:
                     v.copy_((torch.randn(v.shape, generator=g, dtype=torch.float32) * std).to(v.dtype))
         # tied output head shares the embedding; nothing else to do
 
+    def vocab_parallel_head(self) -> bool:
+        """True when the log-prob head is computed vocabulary-parallel over a tensor-parallel group (untied head only: a tied
+        embedding also receives the lookup's gradient, which is the same on every rank and must not be summed)."""
+        return (self.tp is not None and getattr(self.tp, "vocab_parallel", False) and self.tp.world > 1
+                and not self.spec.tie_word_embeddings and "lm_head" in self.layout.entries)
+
     def lm_head_weight(self) -> torch.Tensor:
         return self.p["embed"] if self.spec.tie_word_embeddings or "lm_head" not in self.p else self.p["lm_head"]
 
@@ -200,6 +206,10 @@ class LlamaModel:
         """
         if self.ops == "ref":
             h = self._ref_hidden(input_ids, position_ids, cu_seqlens)
+            if self.vocab_parallel_head():
+                v0, v1 = self.tp.vocab_range(self.spec.vocab_size)
+                logits = ref.linear(self.tp.enter(h), self.lm_head_weight_ref()[v0:v1])  # my vocabulary rows; dh is summed over the group
+                return self.tp.vocab_parallel_logprobs(logits, labels, v0, temperature, want_entropy)
             logits = ref.linear(h, self.lm_head_weight_ref())
             return ref.token_logprobs(logits, labels, temperature, with_entropy=want_entropy)
         keep = torch.is_grad_enabled()
@@ -517,7 +527,24 @@ class _FusedLogprobFn(torch.autograd.Function):
         w = model.lm_head_weight()
         T, C = nf.shape[0], max(128, LOGIT_CHUNK_TOKENS)
         ctx.model, ctx.temperature, ctx.chunk = model, temperature, C
-        if T <= C:
+        ctx.vp = None
+        if model.vocab_parallel_head():
+            # tensor-parallel group: every rank multiplies with its rows of the head; [T]-sized partials are exchanged
+            v0, v1 = model.tp.vocab_range(w.shape[0])
+            ctx.vp = (v0, v1)
+            w = w[v0:v1]
+            zl, lse_loc, ez = (torch.empty(T, dtype=torch.float32, device=nf.device) for _ in range(3))
+            logits = None
+            keep_logits = needs_grad and T <= C
+            ws = None if keep_logits else model.logit_workspace(min(C, T), w.shape[0])
+            for t0 in range(0, T, C):
+                t1 = min(T, t0 + C)
+                lg = f.gemm(nf[t0:t1], w) if keep_logits else f.gemm(nf[t0:t1], w, ws[: t1 - t0])
+                zl[t0:t1], lse_loc[t0:t1], ez[t0:t1] = f.logprob_fwd_vp(lg, labels[t0:t1], v0, temperature)
+                if keep_logits:
+                    logits = lg
+            logp, lse, ent = model.tp.combine_logprobs(zl, lse_loc, ez, labels, want_entropy)
+        elif T <= C:
             logits = f.gemm(nf, w)
             logp, lse, ent = f.logprob_fwd(logits, labels, temperature, want_entropy)
         else:
@@ -550,7 +577,21 @@ class _FusedLogprobFn(torch.autograd.Function):
         w = model.lm_head_weight()
         d_logp = d_logp.contiguous().float()
         T, C = nf.shape[0], ctx.chunk
-        if logits.numel():
+        if ctx.vp is not None:
+            v0, v1 = ctx.vp
+            w = w[v0:v1]
+            g_head = model.g[head][v0:v1]
+            d_nf = torch.empty_like(nf)
+            ws = None if logits.numel() else model.logit_workspace(min(C, T), w.shape[0])
+            for t0 in range(0, T, C):
+                t1 = min(T, t0 + C)
+                lg = logits if logits.numel() else f.gemm(nf[t0:t1], w, ws[: t1 - t0])
+                f.logprob_bwd_vp_(lg, labels[t0:t1], lse[t0:t1], d_logp[t0:t1], v0, ctx.temperature)
+                f.gemm(lg, nf[t0:t1], g_head, a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
+                f.gemm(lg, w, d_nf[t0:t1], b_mn=True)
+            del logits
+            model.tp.all_reduce_(d_nf)  # every rank contributed its vocabulary shard's part of d(hidden)
+        elif logits.numel():
             d_logits = f.logprob_bwd_(logits, labels, lse, d_logp, ctx.temperature)
             f.gemm(d_logits, nf, model.g[head], a_mn=True, b_mn=True, out_mode=f.OUT_F32_ACC)
             d_nf = f.gemm(d_logits, w, b_mn=True)

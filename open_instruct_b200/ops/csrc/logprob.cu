@@ -21,14 +21,20 @@ __device__ __forceinline__ void online_merge(float& m, float& s, float& sz, floa
   m = nm;
 }
 
+// VP (vocabulary parallel): `logits` holds the columns [label_offset, label_offset + V) of the full vocabulary.  Rows are
+// skipped only when the GLOBAL label is negative; the outputs are this shard's partial results, combined across the
+// tensor-parallel ranks by the caller: logp <- the label's scaled logit when it lies in this shard (else 0), lse_out <- the
+// log-sum-exp over this shard, ent_out <- sum_i softmax_local(i) * z_i (the shard's mean scaled logit).
+template <bool VP>
 __global__ void __launch_bounds__(512)
 logprob_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                    float* __restrict__ logp, float* __restrict__ lse_out, float* __restrict__ ent_out, int V,
-                   long long ld, float inv_temp) {
+                   long long ld, float inv_temp, long long label_offset) {
   __shared__ float sm[16], ss[16], sz_[16];
   const long long row = blockIdx.x;
-  const long long label = labels[row];
-  if (label < 0 || label >= V) {
+  const long long glabel = labels[row];
+  const long long label = VP ? glabel - label_offset : glabel;
+  if (VP ? (glabel < 0) : (label < 0 || label >= V)) {
     if (threadIdx.x == 0) {
       logp[row] = 0.f;
       if (lse_out) lse_out[row] = 0.f;
@@ -104,23 +110,33 @@ logprob_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __
     }
     if (lane == 0) {
       const float lse = m + logf(s);
-      const float zl = __bfloat162float(r[label]) * inv_temp;
-      logp[row] = zl - lse;
-      if (lse_out) lse_out[row] = lse;
-      if (ent_out) ent_out[row] = lse - sz / s;
+      if (VP) {
+        logp[row] = (label >= 0 && label < V) ? __bfloat162float(r[label]) * inv_temp : 0.f;
+        if (lse_out) lse_out[row] = lse;
+        if (ent_out) ent_out[row] = sz / s;
+      } else {
+        const float zl = __bfloat162float(r[label]) * inv_temp;
+        logp[row] = zl - lse;
+        if (lse_out) lse_out[row] = lse;
+        if (ent_out) ent_out[row] = lse - sz / s;
+      }
     }
   }
 }
 
 // logits[row, v] <- g[row] * (1[v == label] - exp(z_v - lse)) * inv_temp      (bf16, in place)
+// VP: `lse` is the GLOBAL log-sum-exp (over all shards) and the label is global; a label outside this shard just never matches.
+template <bool VP>
 __global__ void __launch_bounds__(512)
 logprob_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
-                   const float* __restrict__ lse, const float* __restrict__ g, int V, long long ld, float inv_temp) {
+                   const float* __restrict__ lse, const float* __restrict__ g, int V, long long ld, float inv_temp,
+                   long long label_offset) {
   const long long row = blockIdx.x;
-  const long long label = labels[row];
+  const long long glabel = labels[row];
+  const long long label = VP ? glabel - label_offset : glabel;
   __nv_bfloat16* r = logits + row * ld;
   const int nv = V / 8;
-  const bool ignore = label < 0 || label >= V;
+  const bool ignore = VP ? (glabel < 0) : (label < 0 || label >= V);
   const float gr = ignore ? 0.f : g[row];
   if (gr == 0.f) {
     bf8 z;
@@ -162,15 +178,35 @@ extern "C" int b200_logprob_fwd(const void* logits, const long long* labels, flo
                                 int T, int V, long long ld, float temperature, void* stream) {
   if (T <= 0) return 0;
   if (ld % 8) return -1;
-  logprob_fwd_kernel<<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(logits), labels, logp, lse, entropy, V, ld, 1.f / temperature);
+  logprob_fwd_kernel<false><<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(logits), labels, logp, lse, entropy, V, ld, 1.f / temperature, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+// Vocabulary-parallel form: `logits` [T, V] are the columns [label_offset, label_offset + V) of the full vocabulary; see the
+// kernel for what the three outputs hold.
+extern "C" int b200_logprob_fwd_vp(const void* logits, const long long* labels, float* label_logit, float* lse_local,
+                                   float* mean_logit_local, int T, int V, long long ld, float temperature,
+                                   long long label_offset, void* stream) {
+  if (T <= 0) return 0;
+  if (ld % 8) return -1;
+  logprob_fwd_kernel<true><<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(logits), labels, label_logit, lse_local, mean_logit_local, V, ld, 1.f / temperature,
+      label_offset);
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int b200_logprob_bwd(void* logits, const long long* labels, const float* lse, const float* g, int T, int V,
                                 long long ld, float temperature, void* stream) {
   if (T <= 0) return 0;
   if (ld % 8) return -1;
-  logprob_bwd_kernel<<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<__nv_bfloat16*>(logits), labels, lse, g, V, ld, 1.f / temperature);
+  logprob_bwd_kernel<false><<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(logits), labels, lse, g, V, ld, 1.f / temperature, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int b200_logprob_bwd_vp(void* logits, const long long* labels, const float* lse_global, const float* g, int T, int V,
+                                   long long ld, float temperature, long long label_offset, void* stream) {
+  if (T <= 0) return 0;
+  if (ld % 8) return -1;
+  logprob_bwd_kernel<true><<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(logits), labels, lse_global, g, V, ld, 1.f / temperature, label_offset);
   return static_cast<int>(cudaGetLastError());
 }

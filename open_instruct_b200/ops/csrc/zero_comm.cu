@@ -457,6 +457,77 @@ extern "C" int b200_multi_push(const void* src, const void* const* dst_ptrs, int
   return static_cast<int>(cudaGetLastError());
 }
 
+// ------------------------------------------------------------------ learner -> tensor-parallel engine weight push
+// The engines' ranks hold SHARDS of every layer in their own flat layout (q/k/v and gate/up rows, o_proj / down_proj columns
+// of their heads and channels; embedding, head and norms whole).  Instead of sending every rank the full model and letting
+// it re-shard (twice the bytes at TP = 2 and one more pass over the engine's memory), the learner's kernel writes every
+// piece straight to its place: the host describes the re-layout once as a table of 2-D copy tiles
+// (``parallel/weight_sync.py:tp_push_plan``), each with a bit mask of the destination buffers that receive it.
+namespace b200 {
+struct PushTile {
+  long long src;         // element offset in the source buffer
+  long long dst;         // element offset in every destination buffer of the mask
+  long long src_stride;  // elements between consecutive rows in the source
+  long long dst_stride;  // ... in the destination
+  int rows, row_len;     // rows x elements per row
+  unsigned mask;         // bit d set: destination d receives this tile
+  int pad_;
+};
+
+template <bool F32>
+__global__ void __launch_bounds__(256)
+tp_push_kernel(const void* __restrict__ src, PeerPtrs dsts, int n_dst, const PushTile* __restrict__ tiles, int n_tiles) {
+  for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const PushTile tl = tiles[t];
+    const bool vec = ((tl.src | tl.dst | tl.src_stride | tl.dst_stride | tl.row_len) & 7) == 0;
+    if (vec) {
+      const int nvr = tl.row_len >> 3;
+      const long long total = static_cast<long long>(tl.rows) * nvr;
+      for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+        const long long r = i / nvr, c = i - r * nvr;
+        const long long so = tl.src + r * tl.src_stride + c * 8, d_o = tl.dst + r * tl.dst_stride + c * 8;
+        uint4 pk;
+        if (F32) {
+          const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + so);
+          const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + so + 4);
+          pk.x = pack_bf16x2(a.x, a.y); pk.y = pack_bf16x2(a.z, a.w);
+          pk.z = pack_bf16x2(b.x, b.y); pk.w = pack_bf16x2(b.z, b.w);
+        } else {
+          pk = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + so);
+        }
+#pragma unroll 1
+        for (int d = 0; d < n_dst; ++d)
+          if (tl.mask >> d & 1u) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dsts.p[d]) + d_o) = pk;
+      }
+    } else {
+      const long long total = static_cast<long long>(tl.rows) * tl.row_len;
+      for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+        const long long r = i / tl.row_len, c = i - r * tl.row_len;
+        const long long so = tl.src + r * tl.src_stride + c, d_o = tl.dst + r * tl.dst_stride + c;
+        const __nv_bfloat16 v = F32 ? __float2bfloat16(reinterpret_cast<const float*>(src)[so]) : reinterpret_cast<const __nv_bfloat16*>(src)[so];
+        for (int d = 0; d < n_dst; ++d)
+          if (tl.mask >> d & 1u) reinterpret_cast<__nv_bfloat16*>(dsts.p[d])[d_o] = v;
+      }
+    }
+  }
+  __threadfence_system();
+}
+}  // namespace b200
+
+// src: bf16 (src_f32 = 0) or fp32 buffer of the learner; dst_ptrs: up to 8 destination bf16 buffers (engine e, rank r at
+// index e * tp + r); tiles: device array of `n_tiles` PushTile records.
+extern "C" int b200_tp_push(const void* src, const void* const* dst_ptrs, int n_dst, const void* tiles, int n_tiles, int src_f32,
+                            void* stream) {
+  if (n_tiles <= 0 || n_dst <= 0) return 0;
+  if (n_dst > MAX_PEERS) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = n_tiles < 148 * 8 ? n_tiles : 148 * 8;
+  const PushTile* tp = reinterpret_cast<const PushTile*>(tiles);
+  if (src_f32) tp_push_kernel<true><<<grid, 256, 0, st>>>(src, make_ptrs(dst_ptrs, n_dst), n_dst, tp, n_tiles);
+  else tp_push_kernel<false><<<grid, 256, 0, st>>>(src, make_ptrs(dst_ptrs, n_dst), n_dst, tp, n_tiles);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // Lets kernels running on `dev` dereference pointers into `peer`'s memory (needed before a kernel writes through a
 // CUDA-IPC mapping of another GPU's buffer; copies issued by the runtime enable it on their own, raw kernels do not).
 // Returns 0 on success or if access was already enabled, 1 if the two devices cannot reach each other, else the CUDA error.

@@ -210,6 +210,25 @@ def logprob_fwd(logits: torch.Tensor, labels: torch.Tensor, temperature: float =
     return lp, lse, ent
 
 
+def logprob_fwd_vp(logits: torch.Tensor, labels: torch.Tensor, label_offset: int, temperature: float = 1.0):
+    """Vocabulary-parallel partials from this rank's logit columns ``[label_offset, label_offset + V_local)``:
+    ``(label_logit, lse_local, mean_logit_local)`` fp32 [T]; rows whose (global) label is negative give zeros."""
+    T, V = logits.shape
+    zl, lse, ez = (torch.empty(T, dtype=torch.float32, device=logits.device) for _ in range(3))
+    call("b200_logprob_fwd_vp", ptr(logits), ptr(labels), ptr(zl), ptr(lse), ptr(ez), T, V, logits.stride(0), temperature, label_offset,
+         stream_ptr())
+    return zl, lse, ez
+
+
+def logprob_bwd_vp_(logits: torch.Tensor, labels: torch.Tensor, lse_global: torch.Tensor, g: torch.Tensor, label_offset: int,
+                    temperature: float = 1.0) -> torch.Tensor:
+    """In-place ``dL/dlogits`` of this rank's logit columns given the GLOBAL log-sum-exp and global labels."""
+    T, V = logits.shape
+    call("b200_logprob_bwd_vp", ptr(logits), ptr(labels), ptr(lse_global), ptr(g), T, V, logits.stride(0), temperature, label_offset,
+         stream_ptr())
+    return logits
+
+
 def logprob_bwd_(logits: torch.Tensor, labels: torch.Tensor, lse: torch.Tensor, g: torch.Tensor,
                  temperature: float = 1.0) -> torch.Tensor:
     """Rewrites ``logits`` in place with dL/dlogits given g = dL/dlogp (fp32 [T])."""

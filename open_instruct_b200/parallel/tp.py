@@ -124,12 +124,62 @@ class TrainTP:
     trainer, ``open_instruct/dpo_utils.py:129-130``, ``open_instruct/dpo.py:295-299``).  The model runs ``local_spec`` on this
     rank's shard; the two row-parallel outputs of a layer are summed over the group in the forward, the two
     column-parallel input gradients in the backward.  Replicated parameters (embedding, norms, output head) see
-    identical inputs and gradients on every rank; the q/k norm weights, whose gradient is a sum over heads, are the one
-    exception and are summed at the optimizer step (``sync_replicated_grads``)."""
+    identical inputs and gradients on every rank; two exceptions are summed at the optimizer step (``sync_replicated_grads``):
+    the q/k norm weights, whose gradient is a sum over heads, and the untied output head, whose log-prob computation is split
+    over the vocabulary (``vocab_parallel``) so that every rank produces the gradient of its own rows."""
 
-    def __init__(self, group):
+    def __init__(self, group, vocab_parallel: bool = True):
         self.group = group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        # the output head's vocabulary is split over the group for the log-prob computation: every rank multiplies the hidden
+        # states with ITS rows of the (replicated) head and the ranks exchange [T]-sized partial results, so no rank holds
+        # [T, V] logits (what the reference's ``DPOLMHead`` does on its local vocabulary shard,
+        # ``open_instruct/olmo_core_train_modules.py:39-85``)
+        self.vocab_parallel = vocab_parallel
+
+    def vocab_range(self, vocab: int) -> tuple[int, int]:
+        """Rows of the output head this rank multiplies with (multiples of 8 rows, the last shard takes what is left)."""
+        per = -(-vocab // self.world)
+        per = (per + 7) // 8 * 8
+        lo = min(vocab, self.rank * per)
+        return lo, min(vocab, lo + per)
+
+    def combine_logprobs(self, label_logit, lse_local, mean_logit_local, labels, want_entropy: bool):
+        """Global ``(logp, lse, entropy | None)`` from the ranks' shard partials ([T] fp32 each; not differentiable - the
+        callers differentiate through the global lse themselves)."""
+        m = lse_local.clone()
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
+        w = torch.exp(lse_local - m)                       # this shard's share of the softmax mass, up to the common factor
+        parts = torch.stack([w, label_logit, w * mean_logit_local])
+        dist.all_reduce(parts, group=self.group)
+        lse = m + torch.log(parts[0])
+        valid = labels >= 0
+        logp = torch.where(valid, parts[1] - lse, torch.zeros_like(lse))
+        ent = torch.where(valid, lse - parts[2] / parts[0], torch.zeros_like(lse)) if want_entropy else None
+        return logp, lse, ent
+
+    def vocab_parallel_logprobs(self, logits_local, labels, v0: int, temperature: float, want_entropy: bool):
+        """Autograd form (PyTorch path): per-token log-probs from this rank's logit columns ``[v0, v0 + V_local)``."""
+        z = logits_local.float() / temperature
+        lse_loc = torch.logsumexp(z, dim=-1)
+        with torch.no_grad():
+            m = lse_loc.detach().clone()
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
+        s = _SumOverTP.apply(torch.exp(lse_loc - m), self.group)
+        lse = m + torch.log(s)
+        local = labels - v0
+        inside = (local >= 0) & (local < z.shape[-1])
+        zl_loc = torch.where(inside, z.gather(-1, local.clamp(0, z.shape[-1] - 1)[:, None]).squeeze(-1), torch.zeros_like(lse_loc))
+        zl = _SumOverTP.apply(zl_loc, self.group)
+        valid = labels >= 0
+        logp = torch.where(valid, zl - lse, torch.zeros_like(lse))
+        ent = None
+        if want_entropy:
+            with torch.no_grad():
+                e = (torch.softmax(z, -1) * z).sum(-1) * torch.exp(lse_loc - lse)
+                dist.all_reduce(e, group=self.group)
+                ent = torch.where(valid, lse - e, torch.zeros_like(lse)).detach()
+        return logp, ent
 
     def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:   # fused path: explicit, in place
         dist.all_reduce(t, group=self.group)
@@ -159,6 +209,9 @@ class TrainTP:
             for name, g in grads.items():
                 if name.endswith(("q_norm", "k_norm")):
                     dist.all_reduce(g, group=self.group)
+        if self.vocab_parallel and "lm_head" in grads:
+            # every rank produced the gradient of its own rows of the head only: the sum is the full gradient everywhere
+            dist.all_reduce(grads["lm_head"], group=self.group)
 
 
 class TPContext:

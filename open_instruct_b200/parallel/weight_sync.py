@@ -131,6 +131,125 @@ def push_slice(src: torch.Tensor, dsts: list[torch.Tensor], lo: int, hi: int, sr
             d[lo:hi].copy_(src[so_:so_ + hi - lo].to(d.dtype), non_blocking=True)
 
 
+# ------------------------------------------------------------------------------------------------ tensor-parallel engines
+lib._SIGNATURES["b200_tp_push"] = [_P, ctypes.POINTER(ctypes.c_void_p), _I, _P, _I, _I, _P]
+TILE_DTYPE = [("src", "<i8"), ("dst", "<i8"), ("src_stride", "<i8"), ("dst_stride", "<i8"), ("rows", "<i4"), ("row_len", "<i4"), ("mask", "<u4"), ("pad", "<i4")]
+
+
+def _tp_pieces(spec, tp: int):
+    """Every piece of the full flat layout with its place in the tensor-parallel ranks' local layouts:
+    ``(src_off, rows, row_len, src_stride, dst_off, dst_stride, rank or -1 for all ranks)`` in elements.  This is the
+    re-layout ``parallel.tp.shard_flat`` performs, written as 2-D copies (what vLLM's ``load_weights`` does per worker in
+    the reference, ``open_instruct/vllm_utils.py:1383-1480``)."""
+    from ..models.spec import ParamLayout
+    from .tp import local_spec
+
+    ls = local_spec(spec, tp)
+    full, loc = ParamLayout(spec), ParamLayout(ls)
+    hq, hk, f = ls.num_heads * ls.head_dim, ls.num_kv_heads * ls.head_dim, ls.intermediate_size
+    for name, e in full.entries.items():
+        le = loc.entries[name]
+        leaf = name.split(".", 1)[-1]
+        C = e.shape[1] if len(e.shape) == 2 else 1  # columns of the full tensor
+        if leaf in ("wqkv", "bqkv"):
+            q0, k0, v0 = 0, spec.q_dim, spec.q_dim + spec.kv_dim
+            for r in range(tp):
+                for g0, n, l0 in ((q0 + r * hq, hq, 0), (k0 + r * hk, hk, hq), (v0 + r * hk, hk, hq + hk)):
+                    yield e.offset + g0 * C, 1, n * C, 0, le.offset + l0 * C, 0, r
+        elif leaf == "w_gate_up":
+            F = spec.intermediate_size
+            for r in range(tp):
+                for g0, l0 in ((r * f, 0), (F + r * f, f)):
+                    yield e.offset + g0 * C, 1, f * C, 0, le.offset + l0 * C, 0, r
+        elif leaf in ("wo", "w_down"):
+            w = hq if leaf == "wo" else f  # columns every rank keeps
+            for r in range(tp):
+                yield e.offset + r * w, e.shape[0], w, C, le.offset, w, r
+        else:
+            yield e.offset, 1, e.numel, 0, le.offset, 0, -1
+
+
+def tp_push_plan(spec, tp: int, lo: int, hi: int, n_engines: int = 1, tile_elems: int = 1 << 16, src_shift: int = 0):
+    """Copy tiles (numpy structured array, ``TILE_DTYPE``) that move the source range ``[lo, hi)`` of the FULL flat layout
+    into the local layouts of ``n_engines`` x ``tp`` engine ranks (destination index ``e * tp + r``).  ``src_shift`` is
+    added to every source offset (a learner that holds only a slice of the parameters pushes from its shard buffer)."""
+    import numpy as np
+
+    all_ranks = (1 << tp) - 1
+    rep = sum(1 << (e * tp) for e in range(n_engines))  # the same rank of every engine
+    out = []
+
+    def emit(src, rows, row_len, ss, dst, ds, mask):
+        if rows <= 0 or row_len <= 0:
+            return
+        if rows == 1:  # contiguous: chop into tiles
+            for o in range(0, row_len, tile_elems):
+                n = min(tile_elems, row_len - o)
+                out.append((src + o + src_shift, dst + o, 0, 0, 1, n, mask, 0))
+        else:
+            per = max(1, tile_elems // row_len)
+            for r0 in range(0, rows, per):
+                n = min(per, rows - r0)
+                out.append((src + r0 * ss + src_shift, dst + r0 * ds, ss, ds, n, row_len, mask, 0))
+
+    for src, rows, row_len, ss, dst, ds, rank in _tp_pieces(spec, tp):
+        mask = (all_ranks if rank < 0 else (1 << rank)) * rep
+        if rows == 1:
+            a, b = max(src, lo), min(src + row_len, hi)
+            emit(a, 1, b - a, 0, dst + (a - src), 0, mask)
+            continue
+        # 2-D piece: rows wholly inside the range go as one strided block, cut rows at either end as single rows
+        end = src + (rows - 1) * ss + row_len
+        if end <= lo or src >= hi:
+            continue
+        first = max(0, -(-(lo - src) // ss)) if lo > src else 0            # first row starting at or after lo
+        last = min(rows, (hi - src - row_len) // ss + 1) if hi < end else rows  # rows ending at or before hi
+        last = max(last, first)
+        if first > 0:  # the row before ``first`` may straddle lo
+            rs = src + (first - 1) * ss
+            a, b = max(rs, lo), min(rs + row_len, hi)
+            emit(a, 1, b - a, 0, dst + (first - 1) * ds + (a - rs), 0, mask)
+        emit(src + first * ss, last - first, row_len, ss, dst + first * ds, ds, mask)
+        if last < rows:  # the row after the block may straddle hi
+            rs = src + last * ss
+            a, b = max(rs, lo), min(rs + row_len, hi)
+            emit(a, 1, b - a, 0, dst + last * ds + (a - rs), 0, mask)
+    return np.array(out, dtype=TILE_DTYPE) if out else np.zeros(0, dtype=TILE_DTYPE)
+
+
+def apply_plan_reference(plan, src: torch.Tensor, dsts: list[torch.Tensor]) -> None:
+    """The copy the push kernel performs, in PyTorch (CPU engines, and the oracle of the kernel's test)."""
+    with torch.no_grad():
+        for t in plan:
+            for d, dst in enumerate(dsts):
+                if not (int(t["mask"]) >> d) & 1:
+                    continue
+                for r in range(int(t["rows"])):
+                    so, do, n = int(t["src"]) + r * int(t["src_stride"]), int(t["dst"]) + r * int(t["dst_stride"]), int(t["row_len"])
+                    dst[do:do + n].copy_(src[so:so + n].to(dst.dtype))
+
+
+def push_tp(src: torch.Tensor, dsts: list, plan_dev: torch.Tensor, n_tiles: int) -> None:
+    """Run the tensor-parallel push kernel: ``plan_dev`` is the tile table (``tp_push_plan``) as a uint8 CUDA tensor."""
+    so = lib.load_ops()
+    for d in dsts:
+        if isinstance(d, PeerBuffer):
+            if d.mapped_for != src.device.index:
+                raise ValueError(f"buffer was mapped for GPU {d.mapped_for} but the push runs on GPU {src.device.index}")
+        else:
+            ensure_peer_access(src.device.index, d.device.index)
+    arr = (ctypes.c_void_p * 8)()
+    for i, d in enumerate(dsts):
+        arr[i] = d.data_ptr()
+    fn = so.b200_tp_push
+    fn.argtypes, fn.restype = lib._SIGNATURES["b200_tp_push"], _I
+    with torch.cuda.device(src.device):
+        rc = fn(ptr(src), arr, len(dsts), ptr(plan_dev), n_tiles, int(src.dtype == torch.float32), stream_ptr())
+    lib.launch_count += 1
+    if rc:
+        raise lib.KernelError(f"b200_tp_push failed with code {rc}")
+
+
 def sync_in_process(learner_flat: torch.Tensor, engines: list, model_step: int, total: int) -> float:
     """Single-process mode: push the whole model into every engine and stamp the new version."""
     t0 = time.perf_counter()

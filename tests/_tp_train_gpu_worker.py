@@ -29,7 +29,11 @@ def batch(spec, device, seed):
 def main():
     rank, world, device = pdist.init_distributed()
     assert world == 2
+    from open_instruct_b200.models import llama
+
     for ckpt in (False, True):
+        # second pass: also push the head through its token-chunked form (512 tokens in chunks of 256, logits recomputed in backward)
+        llama.LOGIT_CHUNK_TOKENS = 256 if ckpt else 8192
         spec = get_spec("tiny128-tp").replace(num_layers=3)
         kw = dict(ops="fused", learning_rate=1e-3, weight_decay=0.1, max_grad_norm=1.0, total_steps=10, lr_scheduler_type="constant", seed=4,
                   gradient_checkpointing=ckpt)
@@ -37,6 +41,12 @@ def main():
         total = ParamLayout(spec).total
         tp = Learner(spec, LearnerConfig(**kw, tensor_parallel_degree=2), device=device, flat_init=oracle.model.flat.detach()[:total].clone())
         assert tp.tp is not None and tp.world == 1 and tp.spec.num_heads == spec.num_heads // 2
+        assert tp.model.vocab_parallel_head()  # the log-prob head is split over the vocabulary: [T]-sized partials are exchanged
+        with torch.no_grad():
+            b0 = batch(spec, device, 99)
+            lp_o, ent_o = oracle.token_logprobs(b0, temperature=0.8, want_entropy=True)
+            lp_t, ent_t = tp.token_logprobs(b0, temperature=0.8, want_entropy=True)
+        assert (lp_o - lp_t).abs().max().item() < 5e-2 and (ent_o - ent_t).abs().max().item() < 5e-2
         for step in range(3):
             mbs = [batch(spec, device, 10 * step + i) for i in range(2)]
             want, got = oracle.sft_step(mbs), tp.sft_step(mbs)

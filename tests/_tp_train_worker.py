@@ -48,6 +48,13 @@ def main():
     assert sharded.tp is not None and sharded.world == dp_world and sharded.rank == dp_rank
     assert sharded.spec.num_heads == spec.num_heads // tp and sharded.full_spec.num_heads == spec.num_heads
     assert torch.equal(sharded.full_flat(), oracle.model.flat.detach()[:total])   # shard -> unshard round trip
+    # the log-prob head runs vocabulary-parallel over the TP group: log-probs and entropy still equal the unsharded model's
+    assert sharded.model.vocab_parallel_head()
+    b0 = batch(spec, 7)
+    with torch.no_grad():
+        lp_o, ent_o = oracle.token_logprobs(b0, temperature=0.7, want_entropy=True)
+        lp_s, ent_s = sharded.token_logprobs(b0, temperature=0.7, want_entropy=True)
+    assert torch.allclose(lp_o, lp_s, atol=1e-5) and torch.allclose(ent_o, ent_s, atol=1e-5)
     for step in range(3):
         want = oracle.sft_step([batch(spec, 100 * step + d) for d in range(dp_world)])
         got = sharded.sft_step([batch(spec, 100 * step + dp_rank)])

@@ -22,7 +22,7 @@ def _rel(a, b):
 
 @pytest.mark.parametrize("impl", ["1cta", "2cta"])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
-@pytest.mark.parametrize("shape", [(256, 512, 128), (384, 320, 192), (1000, 136, 72), (4096, 1024, 4096), (2048, 6144, 4096)])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (384, 320, 192), (1000, 136, 72), (1000, 192, 72), (4096, 1024, 4096), (2048, 6144, 4096)])
 def test_gemm_layouts(a_mn, b_mn, shape, impl):
     from open_instruct_b200.ops import fused
 
