@@ -319,7 +319,7 @@ class EngineWorker:
         ls = local_spec(spec, self.tp_size)
         if flat is None:
             raise ValueError("a tensor-parallel engine needs the initial weights")
-        self.full_flat = flat
+        self.full_flat = None  # a full-size staging copy exists only while a host-supplied update is applied (CPU path)
         self._tp_spec = spec
         local = shard_flat(flat, spec, self.tp_rank, self.tp_size)
         tp = TPContext(spec.hidden_size, max(4096, max_model_len), dev)
@@ -356,6 +356,12 @@ class EngineWorker:
                         self.engine.step()
                     elif cmd[0] == "reshard":
                         self._reshard(cmd[1])
+                    elif cmd[0] == "fence":
+                        if self.engine.device.type == "cuda":
+                            torch.cuda.synchronize(self.engine.device)
+                        dist.barrier(group=self._tp_cmd_group)
+                    elif cmd[0] == "set_step":
+                        self.engine.model_step = cmd[1]
                     elif cmd[0] == "stop":
                         self.shutdown_flag.set()
         except BaseException as e:  # noqa: BLE001
@@ -410,6 +416,15 @@ class EngineWorker:
         with the new weights at their next step; the reference likewise applies updates between engine steps."""
         self.lock.acquire()
         self._update_open = True
+        if self.tp_size > 1 and self.tp_rank == 0:
+            # the followers mirror the leader's steps asynchronously: wait until every rank has finished what it was sent
+            # (their last layers and sampling may still be in flight) before anyone's weights are written
+            import torch.distributed as dist
+
+            self.engine.send([("fence",)])
+            if self.engine._e.device.type == "cuda":
+                torch.cuda.synchronize(self.engine._e.device)
+            dist.barrier(group=self._tp_cmd_group)
 
     def abort_weight_update(self) -> None:
         if getattr(self, "_update_open", False):
@@ -435,13 +450,21 @@ class EngineWorker:
     def _apply_update(self, flat, model_step: int) -> None:
         """The update itself; the caller holds ``self.lock`` (tensor-parallel followers have no loop to exclude)."""
         if self.tp_size > 1:
+            if flat is None:
+                # the learners already wrote this rank's shard in place (between engine steps, behind the fence of
+                # ``begin_weight_update``): only the version stamp changes, on every rank
+                if self.tp_rank == 0:
+                    self.engine.send([("set_step", model_step)])
+                    self.engine._e.model_step = model_step
+                return
+            if self.full_flat is None:
+                self.full_flat = torch.empty(ParamLayoutTotal(self._tp_spec), dtype=self.engine.model.flat.dtype, device=self.engine.device)
             if self.tp_rank == 0:  # followers reshard when the leader's command reaches them, at the same point of the schedule
-                if flat is not None:
-                    self.full_flat.copy_(flat.to(self.full_flat.dtype))
+                self.full_flat[: flat.numel()].copy_(flat.to(self.full_flat.dtype))
                 self.engine.send([("reshard", model_step)])
                 self._reshard(model_step)
-            elif flat is not None:
-                self.full_flat.copy_(flat.to(self.full_flat.dtype))
+            else:
+                self.full_flat[: flat.numel()].copy_(flat.to(self.full_flat.dtype))
             return
         if flat is not None:
             self.engine.update_weights(flat, model_step)
@@ -460,10 +483,15 @@ class EngineWorker:
             return float(w[:n].double().sum().item()), self.tp_rank, self.tp_size
 
     def weight_buffer_ipc(self):
-        """Picklable description of the parameter buffer for a CUDA-IPC mapping in another process."""
+        """Picklable description of the parameter buffer for a CUDA-IPC mapping in another process.  A rank of a
+        tensor-parallel engine exports ITS shard buffer (the learners write every piece straight to its place in it,
+        ``parallel.weight_sync.tp_push_plan``), tagged with its position so that the learner can order the destinations."""
         from .parallel.weight_sync import export_buffer
 
-        return export_buffer(self.full_flat if self.tp_size > 1 else self.engine.model.flat.detach())
+        eng = self.engine._e if isinstance(self.engine, _TPLeader) else self.engine
+        d = export_buffer(eng.model.flat.detach())
+        d.update({"tp_rank": self.tp_rank, "tp_size": self.tp_size})
+        return d
 
     def _score(self, res: GenerationResult, req: PromptRequest) -> None:
         decoded = self.tokenizer.batch_decode(res.responses, skip_special_tokens=True) if self.tokenizer is not None else \
@@ -681,7 +709,30 @@ class LearnerWorker:
         from .parallel.weight_sync import import_buffer
 
         self._engine_views = [import_buffer(d, self.device.index) for d in ipc_descs]
+        # tensor-parallel engines: destinations ordered [engine][rank] (the caller lists leaders first, then followers)
+        self._engine_tp = max([int(d.get("tp_size", 1)) for d in ipc_descs] or [1])
+        if self._engine_tp > 1:
+            leaders = [v for v, d in zip(self._engine_views, ipc_descs) if d.get("tp_rank", 0) == 0]
+            others = [(d["tp_rank"], v) for v, d in zip(self._engine_views, ipc_descs) if d.get("tp_rank", 0) != 0]
+            per_engine = self._engine_tp - 1
+            ordered = []
+            for e, lead in enumerate(leaders):
+                mine = sorted(others[e * per_engine:(e + 1) * per_engine], key=lambda x: x[0])
+                ordered += [lead] + [v for _, v in mine]
+            self._engine_views = ordered
+            self._tp_plans = {}
         return len(self._engine_views)
+
+    def _tp_plan(self, lo: int, hi: int, src_shift: int = 0):
+        """Device copy-tile table for the source range ``[lo, hi)`` of the full layout (built once per range)."""
+        from .parallel.weight_sync import tp_push_plan
+
+        key = (lo, hi, src_shift)
+        if key not in self._tp_plans:
+            plan = tp_push_plan(self.spec, self._engine_tp, lo, hi, n_engines=len(self._engine_views) // self._engine_tp, src_shift=src_shift)
+            dev = torch.from_numpy(plan.view("u1").copy()).to(self.device) if len(plan) else torch.zeros(0, dtype=torch.uint8, device=self.device)
+            self._tp_plans[key] = (dev, len(plan))
+        return self._tp_plans[key]
 
     def push_weights(self) -> float:
         """Copy this rank's 1/world slice of the bf16 working copy into every engine's buffer."""
@@ -690,7 +741,25 @@ class LearnerWorker:
         t0 = time.perf_counter()
         n = self.learner.model.layout.total
         z = self.learner.z3
-        if z is not None:
+        if getattr(self, "_engine_tp", 1) > 1:
+            # tensor-parallel engines: one kernel writes every piece of my slice to its place in every rank's shard layout
+            from .parallel.weight_sync import push_tp
+
+            if z is not None:
+                ranges = [(*z._my_slice(u), u.soff - z._my_slice(u)[0]) for u in z.units]
+                if self.rank == 0:
+                    ranges.append((z.layout.decay_end, n, z.n_shard - z.layout.decay_end))
+                src = z.local16
+            else:
+                per = -(-n // self.world)
+                per = (per + 1023) // 1024 * 1024
+                ranges = [(min(n, self.rank * per), min(n, (self.rank + 1) * per), 0)]
+                src = self.learner.model.flat.detach()
+            for lo, hi, shift in ranges:
+                if hi > lo:
+                    plan, n_tiles = self._tp_plan(lo, hi, shift)
+                    push_tp(src, self._engine_views, plan, n_tiles)
+        elif z is not None:
             # sharded parameters: every rank pushes the slices it owns, unit by unit, straight from its shard buffer
             # (no gather); rank 0 adds the replicated tail
             for u in z.units:

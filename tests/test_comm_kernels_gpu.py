@@ -118,3 +118,33 @@ def test_allgather_pull_and_reduce_scatter_add_virtual_peers(symm_mod):
     want = acc.double() + torch.stack([w[1024:] for w in ws]).double().sum(0)
     lib.call("b200_reduce_scatter_add", _ptrs(ws), None, world, 1024, 4 * 777, acc.data_ptr(), 2, lib.stream_ptr())
     torch.testing.assert_close(acc.double(), want, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("src_f32", [False, True])
+def test_tp_push_writes_every_rank_its_shard(symm_mod, src_f32):
+    """The tensor-parallel weight push (2 engines x TP 2, four destination buffers on this GPU) against ``shard_flat``: every
+    learner slice of the full layout lands in its place of every rank's shard layout, nothing else is touched."""
+    from open_instruct_b200.models.spec import ParamLayout, get_spec
+    from open_instruct_b200.parallel.tp import local_spec, shard_flat
+    from open_instruct_b200.parallel.weight_sync import push_tp, tp_push_plan
+
+    spec = get_spec("tiny128-tp").replace(qk_norm=True, attention_bias=True, model_type="qwen3")
+    tp, engines, world = 2, 2, 3
+    full, loc = ParamLayout(spec), ParamLayout(local_spec(spec, tp))
+    src = torch.randn(full.total, device="cuda")
+    src16 = src.bfloat16()
+    dsts = [torch.full((loc.total + 64,), 9.0, dtype=torch.bfloat16, device="cuda") for _ in range(engines * tp)]
+    per = (-(-full.total // world) + 1023) // 1024 * 1024
+    for r in range(world):
+        lo, hi = min(full.total, r * per), min(full.total, (r + 1) * per)
+        plan = tp_push_plan(spec, tp, lo, hi, n_engines=engines)
+        dev = torch.from_numpy(plan.view("u1").copy()).cuda()
+        push_tp(src if src_f32 else src16, dsts, dev, len(plan))
+    torch.cuda.synchronize()
+    for e in range(engines):
+        for r in range(tp):
+            want = shard_flat(src16, spec, r, tp)
+            got = dsts[e * tp + r]
+            for name, v in loc.views(got[: loc.total]).items():
+                assert torch.equal(v, loc.views(want)[name]), (e, r, name)
+            assert torch.all(got[loc.total:] == 9.0)

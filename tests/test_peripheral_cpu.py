@@ -435,3 +435,41 @@ def test_dataset_builders(tmp_path):
     assert h["counts"] == [1, 1, 1] and h["edges"] == [0, 8, 16, 24]
     builders.main(["env", "--kind", "counter", "--num", "5", "--out", str(tmp_path / "c.jsonl")])
     assert len(builders.read_jsonl(str(tmp_path / "c.jsonl"))) == 5
+
+
+def test_legacy_dataset_processors(tmp_path):
+    """First-generation processors: column contract, prompt masking, length filters (the prompt limit wins for preferences)."""
+    import datasets
+
+    from helpers import make_tokenizer
+    from open_instruct_b200.data import dataset_processor as dp
+    from open_instruct_b200.data.templates import CHAT_TEMPLATES
+    from transformers import AutoTokenizer
+
+    tok = AutoTokenizer.from_pretrained(make_tokenizer(str(tmp_path / "tok")))
+    tok.chat_template = CHAT_TEMPLATES["tulu"]
+    tok.add_special_tokens({"pad_token": "<pad>"})
+    u = lambda t: {"role": "user", "content": t}
+    a = lambda t: {"role": "assistant", "content": t}
+    pref = datasets.Dataset.from_list([{"chosen": [u("say hi"), a("hi there friend")], "rejected": [u("say hi"), a("no")]},
+                                       {"chosen": [u("count to twenty " * 40), a("one two")], "rejected": [u("count to twenty " * 40), a("three")]}])
+    cfg = dp.DatasetConfig(max_prompt_token_length=30, max_token_length=5, num_proc=1)
+    proc = dp.PreferenceDatasetProcessor(tok, cfg)
+    out = proc.tokenize(pref)
+    assert set(dp.TOKENIZED_PREFERENCE_DATASET_KEYS) <= set(out.column_names)
+    assert out[0][dp.INPUT_IDS_CHOSEN_KEY][: len(out[0][dp.INPUT_IDS_PROMPT_KEY])] == out[0][dp.INPUT_IDS_PROMPT_KEY]
+    assert len(proc.filter(out)) == 1  # the prompt limit is the only rule when it is given: row 0 stays although it exceeds max_token_length
+    assert len(dp.PreferenceDatasetProcessor(tok, dp.DatasetConfig(max_token_length=5, num_proc=1)).filter(out)) == 0
+
+    sft = datasets.Dataset.from_list([{"messages": [u("what is 2 plus 2"), a("four")], "ground_truth": "4", "dataset": "gsm8k"},
+                                      {"messages": [u("only a question")], "ground_truth": "", "dataset": "gsm8k"}])
+    p2 = dp.SFTGroundTruthDatasetProcessor(tok, dp.DatasetConfig(train_only_on_prompt=True, num_proc=1))
+    t2 = p2.tokenize(sft)
+    n = len(t2[0][dp.INPUT_IDS_PROMPT_KEY])
+    assert t2[0][dp.LABELS_KEY][:n] == [-100] * n and t2[0][dp.LABELS_KEY][n:] == t2[0][dp.INPUT_IDS_KEY][n:] and t2[0][dp.GROUND_TRUTHS_KEY] == "4"
+    assert len(p2.filter(t2)) == 1 and len(p2.filter(t2, need_contain_labels=False)) == 2  # a lone prompt has no trainable token
+    assert dp.get_num_proc(10, 64, 400) == 1 and dp.get_num_proc(100000, 8, 400) == 8
+    import pytest
+
+    with pytest.raises(ValueError):
+        dp.DatasetConfig(chat_template="no_such_template")

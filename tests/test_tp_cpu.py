@@ -182,3 +182,39 @@ def test_training_tensor_parallel_matches_unsharded():
 
 def test_training_tensor_parallel_with_data_parallel_and_qk_norm():
     _run_tp_train(4, "qwen3", free_port())
+
+
+def test_tp_push_plan_reproduces_shard_flat():
+    """The copy-tile table of the tensor-parallel weight push: whatever slices of the full layout the learner ranks own, applying
+    their tiles gives every engine rank exactly ``shard_flat`` of the full weights (q/k/v and gate/up row blocks, o_proj /
+    down_proj column blocks, replicated entries to all ranks)."""
+    import torch
+
+    from open_instruct_b200.models.spec import ParamLayout, get_spec
+    from open_instruct_b200.parallel.tp import local_spec, shard_flat
+    from open_instruct_b200.parallel.weight_sync import apply_plan_reference, tp_push_plan
+
+    for tp, extra in ((2, {}), (4, {"qk_norm": True, "attention_bias": True})):
+        spec = get_spec("tiny").replace(**extra)
+        full, loc = ParamLayout(spec), ParamLayout(local_spec(spec, tp))
+        src = torch.randn(full.total)
+        for world in (1, 3):
+            per = (-(-full.total // world) + 7) // 8 * 8
+            dsts = [torch.zeros(loc.total) for _ in range(2 * tp)]
+            for r in range(world):
+                apply_plan_reference(tp_push_plan(spec, tp, r * per, min(full.total, (r + 1) * per), n_engines=2, tile_elems=300), src, dsts)
+            for e in range(2):
+                for r in range(tp):
+                    want = loc.views(shard_flat(src, spec, r, tp))
+                    for name, v in loc.views(dsts[e * tp + r]).items():
+                        assert torch.equal(v, want[name]), (tp, world, e, r, name)
+    # a source that is a shard buffer: offsets shift by ``src_shift``
+    spec = get_spec("tiny")
+    full, loc = ParamLayout(spec), ParamLayout(local_spec(spec, 2))
+    src = torch.randn(full.total)
+    lo, hi = 1024, 5000 // 8 * 8
+    dsts = [torch.zeros(loc.total) for _ in range(2)]
+    apply_plan_reference(tp_push_plan(spec, 2, lo, hi, src_shift=100 - lo), torch.cat([torch.zeros(100), src[lo:hi]]), dsts)
+    ref = [torch.zeros(loc.total) for _ in range(2)]
+    apply_plan_reference(tp_push_plan(spec, 2, lo, hi), src, ref)
+    assert all(torch.equal(a, b) for a, b in zip(dsts, ref))
