@@ -101,7 +101,11 @@ int b200_engine_free_blocks(void* h) {
   return static_cast<int>(e->free_list.size());
 }
 
-int64_t b200_engine_preemptions(void* h) { return static_cast<Engine*>(h)->preemptions; }
+int64_t b200_engine_preemptions(void* h) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  return e->preemptions;
+}
 
 // Queue a sequence.  `group` ties the samples of one prompt together for prefix sharing.
 int b200_engine_add(void* h, int64_t seq_id, int64_t group, int prompt_len, int max_len) {
@@ -139,8 +143,9 @@ int b200_engine_finish(void* h, int64_t seq_id) {
 
 // One scheduling step.
 //   1. every running sequence gets room for one more token (a new block when it crosses a block
-//      boundary); if the cache is full the youngest running sequence is preempted: its blocks are
-//      freed and it goes back to the head of the waiting queue to be recomputed.
+//      boundary); if the cache is full the youngest running sequence (possibly the one that asks) is preempted:
+//      its blocks are freed and it goes back to the head of the waiting queue to be recomputed.  A sequence that
+//      was already given its decode slot in this step is never the victim.
 //   2. waiting sequences are admitted in FIFO order while their (prompt + 1 token) blocks fit and
 //      the running set is below max_running.  Full prompt blocks are shared inside a group.
 // Outputs: prefill_ids (sequences admitted this step, needing a prompt pass), decode_ids (sequences
@@ -158,13 +163,15 @@ int b200_engine_schedule(void* h, int64_t* prefill_ids, int* n_prefill, int64_t*
     if (!s.running) continue;  // preempted below
     const int need = e->blocks_needed(s.len + 1) - static_cast<int>(s.blocks.size());
     bool ok = true;
-    for (int k = 0; k < need; ++k) {
+    for (int k = 0; k < need && ok; ++k) {
       int b = e->alloc_block();
       while (b < 0) {
-        // preempt the youngest running sequence that is not this one
+        // The cache is full: the YOUNGEST running sequence gives its blocks back and is recomputed later.  Sequences
+        // are visited oldest first, so the victim is either this sequence itself or one that has not been given its
+        // decode slot yet - a sequence already listed in decode_ids is never taken apart afterwards.
         int64_t victim = -1;
         for (auto rit = order.rbegin(); rit != order.rend(); ++rit) {
-          if (*rit != s.id && e->seqs[*rit].running) { victim = *rit; break; }
+          if (e->seqs[*rit].running) { victim = *rit; break; }
         }
         if (victim < 0) { ok = false; break; }
         Seq& v = e->seqs[victim];
@@ -175,6 +182,7 @@ int b200_engine_schedule(void* h, int64_t* prefill_ids, int* n_prefill, int64_t*
         e->waiting.push_front(victim);
         e->preemptions++;
         if (*n_preempted < cap) preempted_ids[(*n_preempted)++] = victim;
+        if (victim == s.id) { ok = false; break; }  // this sequence was the youngest: it waits, nothing to grow
         b = e->alloc_block();
       }
       if (!ok) break;
