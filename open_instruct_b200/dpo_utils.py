@@ -140,6 +140,9 @@ class DPOExperimentConfig(ExperimentConfig, ModelConfig, DPOConfig, DPOTrainingC
                 raise ValueError(f"zero_stage must be 0, 1, 2, or 3, got {self.zero_stage}")
             if self.offload_param and self.zero_stage != 3:
                 raise ValueError("offload_param can only be used with zero_stage 3")
+        if self.offload_param:
+            raise ValueError("offload_param is not built: with shard_parameters every GPU keeps 1/N of the bf16 weights (17.5 GB for a 70B "
+                             "model on 8 GPUs), which fits; use offload_optimizer to move the 12 bytes/parameter of optimizer state to host memory")
         if self.use_qlora or self.use_8bit_optimizer:
             raise ValueError("quantised training paths are not part of this framework")
         from .config.schemas import check_context_parallel, check_model_config

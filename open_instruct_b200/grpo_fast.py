@@ -1031,6 +1031,10 @@ class GRPORun:
                                     args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p)
         self.resume_step, self.eval_outstanding, self.total_tokens, self.t_run = 0, 0, 0, time.time()
         self.max_score = streaming.verification_reward + (streaming.r1_style_format_reward if streaming.apply_r1_style_format_reward else 0.0)
+        from .utils.notify import ProgressReporter, warn_if_low_disk_space
+
+        self.progress = ProgressReporter(args.num_training_steps)  # a no-op unless a scheduler description sink is configured
+        warn_if_low_disk_space(args.output_dir, send_slack_alerts=getattr(args, "send_slack_alerts", False))
         self.last: dict = {}
         self.ref_update_in_step = True  # False: a callback of the driver updates the reference policy after the step
         self._closed = False
@@ -1146,6 +1150,7 @@ class GRPORun:
     def log_step(self, step: int) -> None:
         self.last["time/total"] = time.perf_counter() - getattr(self, "_t_step", time.perf_counter())
         self.tracker.log(self.last, step)
+        self.progress.update(step)
         logger.info("step %d: score %.3f loss %.4f len %.1f sync %.3fs", step, self.last.get("scores", 0.0), self.last.get("loss/total_avg", 0.0),
                     self.last.get("val/sequence_lengths", 0.0), self.last.get("time/weight_sync", 0.0))
 
@@ -1208,6 +1213,12 @@ class GRPORun:
 
 def main(args: GRPOExperimentConfig, tc: TokenizerConfig, model_config: ModelConfig, streaming: StreamingDataLoaderConfig,
          vllm: VLLMConfig, tools_config=None) -> dict:
+    from .utils.notify import alert_on_failure
+
+    return alert_on_failure(_main)(args, tc, model_config, streaming, vllm, tools_config)
+
+
+def _main(args, tc, model_config, streaming, vllm, tools_config=None) -> dict:
     run = GRPORun(args, tc, model_config, streaming, vllm, tools_config)
     if run.cached_only is not None:
         return run.cached_only

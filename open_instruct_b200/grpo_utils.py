@@ -138,6 +138,9 @@ class GRPOExperimentConfig(ExperimentConfig):
                              "disable `eval_on_step_0`.")
         if self.sequence_parallel_size < 1:
             raise ValueError("sequence_parallel_size must be >= 1")
+        if self.deepspeed_offload_param:
+            raise ValueError("deepspeed_offload_param is not built: with shard_parameters every GPU keeps 1/N of the bf16 weights, which fits "
+                             "in GPU memory; use deepspeed_offload_optimizer to move the optimizer states to host memory")
         # (the reference needs deepspeed_stage 3 for sequence parallelism, ``open_instruct/grpo_utils.py:275-276``; here it
         # works with resident and with sharded parameters alike)
         if self.use_vllm_logprobs and self.use_rho_correction:

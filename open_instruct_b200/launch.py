@@ -12,9 +12,13 @@ What it takes over from the reference's cluster launcher (``mason.py``):
 * *auto output directory* (``mason.py:472-508``): ``--output_dir`` is filled in as
   ``<auto_output_dir_path>/<exp_name>_<timestamp>`` when the command does not set one;
 * *experiment spec*: ``--dry_run`` prints the resolved spec (commands, environment, resources) as JSON instead of
-  running - the input a cluster scheduler would need.
+  running; ``--experiment_spec out.yaml`` writes the same job in the task format of the reference's scheduler
+  (``mason.py:600-690`` builds a Beaker ``ExperimentSpec``): one task per job with image, cluster constraints, priority,
+  preemptibility, GPU count, replicas + leader selection + host networking for several nodes, environment variables and
+  named secrets, mounted datasets, retries.  Writing the file needs no scheduler client; submitting it is the scheduler's
+  own CLI (``beaker experiment create out.yaml``).
 
-Cluster-specific parts of the reference (Beaker secrets, Weka mounts, image builds) have no counterpart here.
+Image builds and site-specific storage mounts of the reference have no counterpart here.
 """
 
 from __future__ import annotations
@@ -28,11 +32,11 @@ import sys
 import time
 
 TRAINING_MODULES = ("open_instruct_b200.finetune", "open_instruct_b200.dpo_tune_cache", "open_instruct_b200.grpo_fast",
-                    "open_instruct_b200.reward_modeling", "open_instruct_b200.finetune_numpy")
+                    "open_instruct_b200.reward_modeling", "open_instruct_b200.finetune_numpy", "open_instruct_b200.dpo", "open_instruct_b200.grpo")
 # arguments that do not change what gets tokenised: dropped from the caching run so it starts fast and never touches a GPU
 CACHE_EXCLUDED_ARGS = {"--with_tracking": False, "--checkpoint_state_freq": True, "--checkpoint_state_dir": True, "--gs_checkpoint_state_dir": True,
                        "--push_to_hub": False, "--try_launch_beaker_eval_jobs": False, "--wandb_entity": True, "--hf_entity": True}
-SINGLE_PROCESS_MODULES = ("open_instruct_b200.grpo_fast",)  # starts its own learner / engine processes
+SINGLE_PROCESS_MODULES = ("open_instruct_b200.grpo_fast", "open_instruct_b200.grpo")  # start their own learner / engine processes
 
 
 def split_command(argv: list[str]) -> tuple[list[str], list[str]]:
@@ -102,6 +106,38 @@ def build_spec(opts, command: list[str]) -> dict:
     return {"steps": steps, "env": env, "resources": {"gpus_per_node": opts.num_gpus, "nodes": opts.num_nodes}, "description": opts.description}
 
 
+def experiment_spec(opts, spec: dict) -> dict:
+    """The job of ``build_spec`` as a scheduler experiment (Beaker v2 field names): the steps become one shell command, the
+    caching step runs on the first replica only."""
+    nodes = opts.num_nodes
+    lines = []
+    for st in spec["steps"]:
+        cmd = " ".join(shlex.quote(c) for c in st["command"])
+        if nodes > 1 and st["name"] == "train":
+            # every replica learns its rank and the leader's address from the scheduler
+            cmd = cmd.replace(f"--node-rank={opts.node_rank}", "--node-rank=$BEAKER_REPLICA_RANK").replace(
+                f"--master-addr {shlex.quote(opts.master_addr)}", "--master-addr $BEAKER_LEADER_REPLICA_HOSTNAME")
+        if st["gpus"] == 0:
+            cmd = f"if [ \"${{BEAKER_REPLICA_RANK:-0}}\" = \"0\" ]; then CUDA_VISIBLE_DEVICES= {cmd}; fi"
+        lines.append(cmd)
+    env = [{"name": k, "value": v} for k, v in sorted(spec["env"].items())]
+    env += [{"name": e.split("=", 1)[1] if "=" in e else e, "secret": e.split("=", 1)[0]} for e in opts.secret]
+    task = {"name": opts.task_name or "train", "image": {"beaker": opts.image} if opts.image else {"docker": "nvcr.io/nvidia/pytorch:latest"},
+            "command": ["/bin/bash", "-c", " && ".join(lines)], "envVars": env,
+            "resources": {"gpuCount": opts.num_gpus, **({"sharedMemory": opts.shared_memory} if opts.shared_memory else {})},
+            "context": {"priority": opts.priority, "preemptible": bool(opts.preemptible)},
+            "constraints": {"cluster": list(opts.cluster)} if opts.cluster else {},
+            "datasets": [{"mountPath": m.split(":", 1)[1], "source": {"beaker": m.split(":", 1)[0]}} for m in opts.mount],
+            "result": {"path": "/output"}}
+    if nodes > 1:
+        task.update({"replicas": nodes, "leaderSelection": True, "hostNetworking": True, "propagateFailure": True, "propagatePreemption": True,
+                     "synchronizedStartTimeout": "48h"})
+    exp = {"version": "v2", "description": spec.get("description") or "", "budget": opts.budget, "tasks": [task]}
+    if opts.max_retries:
+        exp["retry"] = {"allowedTaskRetries": opts.max_retries}
+    return exp
+
+
 def run_spec(spec: dict) -> int:
     env = {**os.environ, **spec["env"]}
     for step in spec["steps"]:
@@ -129,8 +165,27 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--auto_output_dir_path", default="")
     ap.add_argument("--description", default="")
     ap.add_argument("--dry_run", action="store_true")
+    # scheduler experiment file (written, never submitted from here)
+    ap.add_argument("--experiment_spec", default="", help="write the job as a scheduler experiment YAML and exit")
+    ap.add_argument("--cluster", action="append", default=[])
+    ap.add_argument("--image", default="")
+    ap.add_argument("--priority", default="normal", choices=["low", "normal", "high", "urgent"])
+    ap.add_argument("--preemptible", action="store_true")
+    ap.add_argument("--budget", default="")
+    ap.add_argument("--task_name", default="")
+    ap.add_argument("--shared_memory", default="")
+    ap.add_argument("--secret", action="append", default=[], help="SECRET_NAME=ENV_NAME, repeatable")
+    ap.add_argument("--mount", action="append", default=[], help="dataset:/mount/path, repeatable")
+    ap.add_argument("--max_retries", type=int, default=0)
     opts = ap.parse_args(own)
     spec = build_spec(opts, command)
+    if opts.experiment_spec:
+        import yaml
+
+        with open(opts.experiment_spec, "w") as fh:
+            yaml.safe_dump(experiment_spec(opts, spec), fh, sort_keys=False)
+        print(f"[launch] wrote {opts.experiment_spec}")
+        return 0
     if opts.dry_run:
         print(json.dumps(spec, indent=2))
         return 0

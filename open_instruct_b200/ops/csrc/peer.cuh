@@ -14,6 +14,7 @@ struct PeerPtrs {
 constexpr int PAD_BARRIER = 1024;       // [+rank]
 constexpr int PAD_SCALAR_FLAG = 1040;   // [+rank]
 constexpr int PAD_SCALAR_VAL = 1056;    // [+parity*8 + rank] (float bits)
+constexpr int PAD_VEC_FLAG = 1136;      // [+rank]: small-vector all-reduce (metrics)
 constexpr int PAD_BARRIER_SIDE = 1120;  // [+rank]; 1100..1107 is the tensor-parallel flag row (tp_comm.cu)
 
 __device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {

@@ -64,6 +64,43 @@ __global__ void symm_allreduce_scalar_kernel(PeerPtrs pads, int rank, int world,
   }
 }
 
+// out[i] = sum over ranks of in[i], i < n <= SYMM_VEC_MAX: the one small reduction a logging step needs (metric vectors).
+// `bufs.p[r]` is rank r's symmetric exchange buffer of 2 (parity) x MAX_PEERS x SYMM_VEC_MAX floats: every rank stores its
+// vector into its own slot of EVERY peer's buffer, raises its flag there, waits (bounded) for everyone's flag in its own pad
+// and adds the slots of its own buffer in rank order, so the result is bitwise the same on every rank.  One CTA.
+constexpr int SYMM_VEC_MAX = 512;
+__global__ void __launch_bounds__(512)
+symm_allreduce_vec_kernel(PeerPtrs bufs, PeerPtrs pads, int rank, int world, uint32_t epoch, const float* __restrict__ in,
+                          float* __restrict__ out, int n, long long limit_cycles, int* __restrict__ status) {
+  __shared__ int failed;
+  const int par = epoch & 1;
+  if (threadIdx.x == 0) failed = 0;
+  for (int r = 0; r < world; ++r) {
+    float* slot = reinterpret_cast<float*>(bufs.p[r]) + (static_cast<long long>(par) * MAX_PEERS + rank) * SYMM_VEC_MAX;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) reinterpret_cast<volatile float*>(slot)[i] = in[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) {
+    st_release_sys(reinterpret_cast<uint32_t*>(pads.p[threadIdx.x]) + PAD_VEC_FLAG + rank, epoch);
+    if (!wait_epoch(reinterpret_cast<const uint32_t*>(pads.p[rank]) + PAD_VEC_FLAG + threadIdx.x, epoch, limit_cycles)) {
+      atomicCAS(status, 0, ST_TIMEOUT_PEER);
+      failed = 1;
+    }
+  }
+  __syncthreads();
+  const volatile float* mine = reinterpret_cast<const volatile float*>(bufs.p[rank]) + static_cast<long long>(par) * MAX_PEERS * SYMM_VEC_MAX;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float s = 0.f;
+    if (!failed) {
+      for (int r = 0; r < world; ++r) s += mine[r * SYMM_VEC_MAX + i];
+    } else {
+      s = in[i];  // a peer never arrived: the local values stand, the status word tells the host
+    }
+    out[i] = s;
+  }
+}
+
 __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
   float4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -235,6 +272,19 @@ extern "C" int b200_symm_allreduce_scalar(const void* const* pad_ptrs, int rank,
   const long long cycles = static_cast<long long>(limit_ms) * 1900000LL;
   symm_allreduce_scalar_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       make_ptrs(pad_ptrs, world), rank, world, epoch, in, out, cycles, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Floats of the exchange buffer `b200_symm_allreduce_vec` needs per rank (allocate it in symmetric memory, zeroed).
+extern "C" int b200_symm_vec_buffer_floats() { return 2 * MAX_PEERS * SYMM_VEC_MAX; }
+
+extern "C" int b200_symm_allreduce_vec(const void* const* buf_ptrs, const void* const* pad_ptrs, int rank, int world, unsigned epoch,
+                                       const float* in, float* out, int n, int limit_ms, int* status, void* stream) {
+  if (world > MAX_PEERS || n < 0 || n > SYMM_VEC_MAX) return -1;
+  if (n == 0) return 0;
+  const long long cycles = static_cast<long long>(limit_ms) * 1900000LL;
+  symm_allreduce_vec_kernel<<<1, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_ptrs(buf_ptrs, world), make_ptrs(pad_ptrs, world), rank,
+                                                                               world, epoch, in, out, n, cycles, status);
   return static_cast<int>(cudaGetLastError());
 }
 

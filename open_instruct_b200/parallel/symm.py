@@ -47,6 +47,7 @@ lib._SIGNATURES.update({
     "b200_symm_barrier_side": [_PP, _I, _I, _U, _I, _P, _P],
     "b200_zero_reduce_scatter": [_PP, _P, _I, _I, _L, _L, _P, _P, _I, _P],
     "b200_zero_reduce_range": [_PP, _P, _I, _L, _L, _P, _P, _I, _I, _P],
+    "b200_symm_allreduce_vec": [_PP, _PP, _I, _I, _U, _P, _P, _I, _I, _P, _P],
     "b200_zero_adamw_allgather": [_P, _P, _P, _P, _PP, _P, _I, _L, _L, _P, _F, _F, _F, _F, _F, _I, _I, _P],
 })
 
@@ -63,6 +64,18 @@ def unreduced_ranges(lo: int, hi: int, done: list[tuple[int, int]]) -> list[tupl
     if pos < hi:
         out.append((pos, hi))
     return [(a, b) for a, b in out if a < b]
+
+
+_METRICS_STATE = None  # the SymmetricState whose exchange buffer serves metric reductions over the default group
+
+
+def metrics_state(group=None):
+    """The symmetric state to reduce a metric vector over ``group`` with, if one exists for exactly that group."""
+    st = _METRICS_STATE
+    if st is None:
+        return None
+    want = group if group is not None else dist.group.WORLD
+    return st if st.group is want else None
 
 
 def _ptr_array(ptrs) -> ctypes.Array:
@@ -120,6 +133,28 @@ class SymmetricState:
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)  # every rank has mapped every peer before any kernel touches them
         self.shard = n // self.world
+        # exchange buffer of the small-vector all-reduce (metric vectors of a logging step)
+        self._vec_epoch = 0
+        self.vec_buf = symm_mem.empty(2 * 8 * 512, dtype=torch.float32, device=self.device)
+        self.vec_buf.zero_()
+        self._hv = symm_mem.rendezvous(self.vec_buf, self.group)
+        self._vec_ptrs = _ptr_array(self._hv.buffer_ptrs)
+        self._vec_pads = _ptr_array(self._hv.signal_pad_ptrs)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        global _METRICS_STATE
+        _METRICS_STATE = self
+
+    def allreduce_vector_(self, vec: torch.Tensor) -> torch.Tensor:
+        """In-place sum over the ranks of a small fp32 vector (at most 512 entries) in ONE kernel over symmetric memory:
+        no library collective on the logging path.  The parity of the epoch alternates the exchange slots, so a rank that
+        races ahead into the next reduction cannot overwrite values a slower rank is still adding."""
+        if vec.dtype != torch.float32 or not vec.is_cuda or vec.numel() > 512 or not vec.is_contiguous():
+            raise ValueError("allreduce_vector_ takes a contiguous CUDA fp32 vector of at most 512 entries")
+        self._vec_epoch += 1
+        lib.call("b200_symm_allreduce_vec", self._vec_ptrs, self._vec_pads, self.rank, self.world, self._vec_epoch, ptr(vec), ptr(vec),
+                 vec.numel(), self.peer_timeout_ms, ptr(status_word(self.device)), stream_ptr())
+        return vec
 
     # ------------------------------------------------------------------ primitives
     def barrier(self) -> None:

@@ -78,7 +78,15 @@ class MetricsTracker:
     def reduce_(self, group=None, average: bool = True) -> "MetricsTracker":
         from ..parallel import dist as pdist
 
-        pdist.all_reduce_(self.metrics, group=group)
+        st = None
+        if self.metrics.is_cuda and self.metrics.numel() <= 512 and pdist.is_dist():
+            from ..parallel.symm import metrics_state
+
+            st = metrics_state(group)
+        if st is not None:
+            st.allreduce_vector_(self.metrics)   # one kernel over symmetric memory
+        else:
+            pdist.all_reduce_(self.metrics, group=group)
         if average:
             self.metrics /= pdist.world_size(group)
         return self

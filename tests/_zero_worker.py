@@ -80,6 +80,18 @@ def main():
         from open_instruct_b200.parallel.symm import SymmetricState
 
         st = SymmetricState(4096, device, peer_timeout_ms=50)
+        # the small-vector all-reduce of the logging path, three in a row (the exchange slots alternate), against NCCL
+        from open_instruct_b200.utils.common import MetricsTracker
+
+        for k in range(3):
+            v = torch.arange(100, device=device, dtype=torch.float32) * (rank + 1) + k
+            want = v.clone()
+            torch.distributed.all_reduce(want)
+            assert torch.equal(st.allreduce_vector_(v), want)
+        mt = MetricsTracker(device=device)
+        mt["loss"] = float(rank + 1)
+        mt.reduce_(average=True)  # goes through the same kernel (a symmetric state exists for the default group)
+        assert abs(mt.get_metrics_list()["loss"] - 1.5) < 1e-6
         st.barrier()  # both ranks: a normal barrier passes
         torch.cuda.synchronize()
         lib.check_status()

@@ -47,6 +47,8 @@ def test_dpo_and_sft_refuse_switches_they_cannot_honour(tmp_path):
         DPOExperimentConfig(**base, load_balancing_loss=True)
     with pytest.raises(ValueError, match="quantised"):
         DPOExperimentConfig(**base, load_in_4bit=True)
+    with pytest.raises(ValueError, match="offload_param is not built"):
+        DPOExperimentConfig(**base, zero_stage=3, offload_param=True)
     with pytest.raises(ValueError, match="mixture-of-experts"):
         FlatArguments(model_name_or_path="tiny", dataset_mixer_list=["x.jsonl", "1.0"], load_balancing_loss=True)
     with pytest.raises(ValueError):
@@ -62,6 +64,8 @@ def test_grpo_eval_on_step_0_needs_local_eval():
     assert GRPOExperimentConfig(sequence_parallel_size=2, deepspeed_stage=2).sequence_parallel_size == 2
     with pytest.raises(ValueError):
         GRPOExperimentConfig(sequence_parallel_size=0)
+    with pytest.raises(ValueError, match="deepspeed_offload_param is not built"):
+        GRPOExperimentConfig(deepspeed_offload_param=True)
 
 
 def _engine_worker():

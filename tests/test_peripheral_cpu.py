@@ -473,3 +473,118 @@ def test_legacy_dataset_processors(tmp_path):
 
     with pytest.raises(ValueError):
         dp.DatasetConfig(chat_template="no_such_template")
+
+
+def test_notifications_progress_and_tracker_gates(tmp_path, monkeypatch):
+    """Slack alerts, scheduler progress lines, run tags, disk warnings - and the tracker's optional back ends: every one of
+    them works against a fake service and degrades to nothing when its service is missing."""
+    import sys
+    import types
+
+    from open_instruct_b200.utils import notify
+    from open_instruct_b200.utils.common import Tracker
+
+    assert notify.format_eta(59) == "0m" and notify.format_eta(3700) == "1h 1m" and notify.format_eta(90061) == "1d 1h 1m"
+    assert notify.progress_text(0, 40, 5.0) == "[0.0% complete (step 0/40), eta calculating...]"
+    assert notify.progress_text(10, 40, 600.0) == "[25.0% complete (step 10/40), eta 30m]"
+    assert notify.progress_text(40, 40, 7200.0) == "[100.0% complete (step 40/40), finished in 2h 0m]"
+
+    class Sink(notify.DescriptionSink):
+        text = "my run git_commit: old git_branch: old [50% ...]"
+
+        def get(self):
+            return self.text
+
+        def set(self, t):
+            self.text = t
+
+        def url(self):
+            return "https://jobs.example/1"
+
+    monkeypatch.setenv("GIT_COMMIT", "abc123")
+    monkeypatch.setenv("GIT_BRANCH", "main")
+    sink = Sink()
+    rep = notify.ProgressReporter(40, sink, wandb_url="https://wandb.example/run")
+    out = rep.update(10)
+    assert out.startswith("my run git_commit: abc123 git_branch: main https://wandb.example/run [25.0% complete (step 10/40), eta ")
+    assert rep.update(40).count("git_commit:") == 1 and "finished in" in sink.text
+    assert notify.ProgressReporter(40, sink=None).update(1) is None or True  # no scheduler: nothing happens
+
+    sent = []
+
+    class R:
+        ok, status_code, text = True, 200, "ok"
+
+    monkeypatch.delenv("SLACK_WEBHOOK_URL", raising=False)
+    assert notify.send_slack_message("x", post=lambda *a, **k: sent.append((a, k)) or R()) is False and not sent
+    monkeypatch.setenv("SLACK_WEBHOOK_URL", "https://hooks.example/T/B")
+    assert notify.send_slack_message("job died", sink=sink, post=lambda *a, **k: sent.append((a, k)) or R()) is True
+    assert sent[0][0][0] == "https://hooks.example/T/B" and sent[0][1]["json"]["text"] == "job died Check it out: https://jobs.example/1"
+
+    def boom(*a, **k):
+        raise OSError("no network")
+
+    assert notify.send_slack_message("x", post=boom) is False
+
+    class A:
+        send_slack_alerts = True
+
+    calls = []
+    monkeypatch.setattr(notify, "send_slack_message", lambda m, **k: calls.append(m))
+
+    @notify.alert_on_failure
+    def main(args):
+        raise RuntimeError("out of cheese")
+
+    import pytest
+
+    with pytest.raises(RuntimeError):
+        main(A())
+    assert calls and "RuntimeError: out of cheese" in calls[0]
+
+    monkeypatch.setenv("WANDB_TAGS", "a,b")
+    assert notify.get_wandb_tags()[:3] == ["a", "b", "commit: abc123"] and "branch: main" in notify.get_wandb_tags()
+    assert notify.warn_if_low_disk_space("gs://bucket/x") is None
+    assert "Disk usage near capacity" in notify.warn_if_low_disk_space(str(tmp_path / "not" / "yet"), threshold=0.0)
+    assert notify.warn_if_low_disk_space(str(tmp_path), threshold=1.1) is None
+
+    # tracker back ends: a fake wandb module receives init / log / finish; tensorboard writes event files; both are optional
+    logged = []
+    fake = types.SimpleNamespace(init=lambda **k: logged.append(("init", k["project"], k["name"])), log=lambda m, step: logged.append(("log", step, dict(m))),
+                                 finish=lambda: logged.append(("finish",)))
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    t = Tracker(str(tmp_path / "run"), "r1", {"lr": 1.0}, report_to=("wandb", "tensorboard"), wandb_project="proj")
+    t.log({"loss": 0.5, "note": "text"}, 3)
+    t.close()
+    assert logged[0] == ("init", "proj", "r1") and logged[1][:2] == ("log", 3) and logged[-1] == ("finish",)
+    assert os.path.exists(tmp_path / "run" / "metrics.jsonl") and os.path.exists(tmp_path / "run" / "run_config.json")
+    tb = tmp_path / "run" / "tb" / "r1"
+    assert (not tb.exists()) or any(f.name.startswith("events") for f in tb.iterdir())  # written when tensorboard is installed
+    monkeypatch.setitem(sys.modules, "wandb", None)  # import fails: the tracker carries on with the jsonl file alone
+    t2 = Tracker(str(tmp_path / "run2"), "r2", None, report_to=("wandb",))
+    t2.log({"loss": 1.0}, 1)
+    t2.close()
+    assert os.path.exists(tmp_path / "run2" / "metrics.jsonl")
+
+
+def test_launcher_writes_a_scheduler_experiment(tmp_path):
+    import yaml
+
+    from open_instruct_b200 import launch
+
+    out = tmp_path / "exp.yaml"
+    rc = launch.main(["--num_gpus", "8", "--num_nodes", "2", "--cluster", "big-cluster", "--priority", "high", "--preemptible", "--budget", "team/x",
+                      "--image", "me/img", "--secret", "MY_HF_TOKEN=HF_TOKEN", "--mount", "ds123:/data", "--env", "A=b", "--max_retries", "2",
+                      "--experiment_spec", str(out), "--", "python", "-m", "open_instruct_b200.finetune", "recipe.yaml", "--with_tracking"])
+    assert rc == 0
+    exp = yaml.safe_load(open(out))
+    task = exp["tasks"][0]
+    assert exp["version"] == "v2" and exp["budget"] == "team/x" and exp["retry"] == {"allowedTaskRetries": 2}
+    assert task["replicas"] == 2 and task["leaderSelection"] and task["hostNetworking"] and task["resources"]["gpuCount"] == 8
+    assert task["context"] == {"priority": "high", "preemptible": True} and task["constraints"] == {"cluster": ["big-cluster"]}
+    script = task["command"][2]
+    assert "--cache_dataset_only" in script.split(" && ")[0] and "BEAKER_REPLICA_RANK" in script.split(" && ")[0]  # cached once, on replica 0
+    assert "--with_tracking" not in script.split(" && ")[0] and "--with_tracking" in script.split(" && ")[1]
+    assert "--nnodes=2" in script and "--node-rank=$BEAKER_REPLICA_RANK" in script and "--master-addr $BEAKER_LEADER_REPLICA_HOSTNAME" in script
+    assert {"name": "HF_TOKEN", "secret": "MY_HF_TOKEN"} in task["envVars"] and {"name": "A", "value": "b"} in task["envVars"]
+    assert task["datasets"] == [{"mountPath": "/data", "source": {"beaker": "ds123"}}]
