@@ -132,6 +132,7 @@ class FlatArguments:
     # engine selection (not in the reference: there the back end is fixed by the launcher config)
     ops: Literal["auto", "fused", "ref"] = "auto"
     comm_backend: Literal["auto", "fused", "nccl"] = "auto"
+    fsdp_shard_degree: int | None = field(default=None, metadata={"help": "HSDP: shard optimizer state (and parameters) over groups of this many ranks, replicate across the groups"})
     zero_stage: int = field(default=3, metadata={"help": "Kept for recipe compatibility: optimizer states are always sharded, working params resident"})
 
     def __post_init__(self):
@@ -239,7 +240,7 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                         final_lr_ratio=args.final_lr_ratio, gradient_checkpointing=args.gradient_checkpointing, seed=args.seed,
                         sequence_parallel_size=sp, sp_max_tokens=args.max_seq_length * max(1, per_rank) if sp > 1 else 0,
                         offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters,
-                        tensor_parallel_degree=tp)
+                        tensor_parallel_degree=tp, shard_degree=args.fsdp_shard_degree)
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):

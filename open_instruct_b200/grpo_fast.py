@@ -27,6 +27,7 @@ import json
 import logging
 import math
 import os
+import contextlib
 import threading
 import time
 from dataclasses import asdict
@@ -278,6 +279,10 @@ class EngineWorker:
         self.should_stop = threading.Event()
         self.shutdown_flag = threading.Event()
         self.lock = threading.Lock()  # engine state is touched by the loop thread and by update_weights
+        # ``threading.Lock`` is not fair: the loop releases and re-takes it every few milliseconds and a control call could
+        # wait through many engine steps.  Control calls announce themselves here and the loop stands back until they hold it.
+        self._control_waiting = 0
+        self._control_mutex = threading.Lock()
         self.error: BaseException | None = None
         self.pending: dict[int, PromptRequest] = {}
         # multi-turn tool / environment rollouts: engine request id -> (group key, sample index)
@@ -383,13 +388,31 @@ class EngineWorker:
         if not self.thread.is_alive() and not self.shutdown_flag.is_set():
             raise RuntimeError("engine loop is not running")
 
+    def _acquire_for_control(self) -> None:
+        """Take the engine lock ahead of the loop's next step (the step that is running finishes first)."""
+        with self._control_mutex:
+            self._control_waiting += 1
+        try:
+            self.lock.acquire()
+        finally:
+            with self._control_mutex:
+                self._control_waiting -= 1
+
+    @contextlib.contextmanager
+    def _control(self):
+        self._acquire_for_control()
+        try:
+            yield
+        finally:
+            self.lock.release()
+
     # ---- control surface of the reference's engine actor (``open_instruct/vllm_utils.py:781-843``)
     def sleep(self) -> None:
         """Pause generation between engine steps and keep everything resident (the reference's ``sleep(level=0,
         mode="keep")``): returns once the step that was running has finished; no new step starts until ``wake_up``."""
         self.should_stop.set()
         self._paused = True
-        with self.lock:  # the loop holds the lock while it steps: taking it once means that step is over
+        with self._control():  # the loop holds the lock while it steps: taking it once means that step is over
             pass
 
     def wake_up(self) -> None:
@@ -399,13 +422,13 @@ class EngineWorker:
     def reset_prefix_cache(self) -> bool:
         """Forget every cached prompt prefix (KV blocks shared between requests), as after a weight update: KV computed
         with older weights must not be reused for new requests."""
-        with self.lock:
+        with self._control():
             eng = self.engine._e if isinstance(self.engine, _TPLeader) else self.engine
             return bool(eng.reset_prefix_cache())
 
     def set_model_step(self, model_step: int) -> None:
         """Stamp the policy version that new results report (staleness accounting in the data-preparation actor)."""
-        with self.lock:
+        with self._control():
             (self.engine._e if isinstance(self.engine, _TPLeader) else self.engine).model_step = int(model_step)
 
     def begin_weight_update(self) -> None:
@@ -414,7 +437,7 @@ class EngineWorker:
         starting until ``update_weights`` (or ``abort_weight_update``) ends the update, so no forward pass ever runs on
         half-old, half-new weights.  Requests in flight keep their KV cache (``inflight_updates`` semantics) and continue
         with the new weights at their next step; the reference likewise applies updates between engine steps."""
-        self.lock.acquire()
+        self._acquire_for_control()
         self._update_open = True
         if self.tp_size > 1 and self.tp_rank == 0:
             # the followers mirror the leader's steps asynchronously: wait until every rank has finished what it was sent
@@ -444,7 +467,7 @@ class EngineWorker:
         if self.tp_size > 1 and self.tp_rank != 0:
             self._apply_update(flat, model_step)
             return
-        with self.lock:
+        with self._control():
             self._apply_update(flat, model_step)
 
     def _apply_update(self, flat, model_step: int) -> None:
@@ -477,7 +500,7 @@ class EngineWorker:
         deadline = time.time() + 10.0
         while expect_step is not None and self.engine.model_step != expect_step and time.time() < deadline:
             time.sleep(0.002)
-        with self.lock:
+        with self._control():
             w = self.engine.model.flat.detach()
             n = self.engine.model.layout.total
             return float(w[:n].double().sum().item()), self.tp_rank, self.tp_size
@@ -537,6 +560,8 @@ class EngineWorker:
                     if not admitted:
                         time.sleep(0.005)
                     continue
+                while self._control_waiting > 0:  # a control call (weight update, pause, checksum) goes first
+                    time.sleep(0.0002)
                 with self.lock:
                     finished = self.engine.step()
                 for res in finished:
@@ -642,6 +667,7 @@ class LearnerWorker:
                             total_steps=max(1, num_training_steps * args.num_epochs * args.num_mini_batches),
                             gradient_checkpointing=model_config.gradient_checkpointing, seed=args.seed,
                             offload_optimizer=args.deepspeed_offload_optimizer, shard_parameters=args.shard_parameters,
+                            shard_degree=args.fsdp_shard_degree,
                             sequence_parallel_size=max(1, args.sequence_parallel_size),
                             sp_max_tokens=-(-getattr(args, "sp_max_tokens", 0) // max(1, args.sequence_parallel_size)) * max(1, args.sequence_parallel_size))
         self.learner = Learner(spec, cfg, device=self.device)

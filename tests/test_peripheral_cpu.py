@@ -588,3 +588,32 @@ def test_launcher_writes_a_scheduler_experiment(tmp_path):
     assert "--nnodes=2" in script and "--node-rank=$BEAKER_REPLICA_RANK" in script and "--master-addr $BEAKER_LEADER_REPLICA_HOSTNAME" in script
     assert {"name": "HF_TOKEN", "secret": "MY_HF_TOKEN"} in task["envVars"] and {"name": "A", "value": "b"} in task["envVars"]
     assert task["datasets"] == [{"mountPath": "/data", "source": {"beaker": "ds123"}}]
+
+
+def _recipe_files():
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "train_configs")
+    return sorted(os.path.join(root, f) for f in os.listdir(root) if f.endswith(".yaml"))
+
+
+@pytest.mark.parametrize("path", _recipe_files(), ids=os.path.basename)
+def test_every_recipe_parses_with_its_entry_point(path):
+    """Each recipe names its trainer in the first line; all its keys are flags of that trainer and pass its validation."""
+    from open_instruct_b200.config.argparser import ArgumentParserPlus
+    from open_instruct_b200.config.schemas import ModelConfig
+    from open_instruct_b200.data.tokenize import TokenizerConfig
+    from open_instruct_b200.dpo_utils import DPOExperimentConfig
+    from open_instruct_b200.environments.tools.utils import EnvsConfig
+    from open_instruct_b200.finetune import FlatArguments
+    from open_instruct_b200.finetune_numpy import Args as NumpyArgs
+    from open_instruct_b200.grpo_utils import GRPOExperimentConfig
+    from open_instruct_b200.reward_modeling import Args as RMArgs
+    from open_instruct_b200.streaming import StreamingDataLoaderConfig, VLLMConfig
+
+    grpo = (GRPOExperimentConfig, TokenizerConfig, ModelConfig, StreamingDataLoaderConfig, VLLMConfig, EnvsConfig)
+    parsers = {"finetune": (FlatArguments, TokenizerConfig), "dpo_tune_cache": (DPOExperimentConfig, TokenizerConfig), "dpo": (DPOExperimentConfig, TokenizerConfig),
+               "grpo_fast": grpo, "grpo": grpo, "reward_modeling": (RMArgs, TokenizerConfig, ModelConfig), "finetune_numpy": (NumpyArgs,)}
+    first = open(path).readline()
+    assert first.startswith("# entry: "), f"{path} must start with '# entry: <trainer module>'"
+    entry = first.split(":", 1)[1].strip()
+    out = ArgumentParserPlus(parsers[entry]).parse([path])
+    assert out is not None
