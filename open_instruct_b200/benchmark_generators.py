@@ -176,6 +176,11 @@ def main(argv=None) -> dict:
     summary = aggregate(results) if results else {}
     summary.update({"model": a.model, "batch_size": a.num_unique_prompts_rollout, "samples_per_prompt": a.num_samples_per_prompt_rollout,
                     "response_length": a.response_length, "prompt_length": a.prompt_length, "kv_blocks": engine.num_blocks})
+    st = engine.stats
+    if st.get("decode_steps"):  # where a graph-replayed decode step's wall time goes, in ms per step
+        k = 1e3 / st["decode_steps"]
+        summary["decode_step_ms"] = {"host_pack": st["host_pack_s"] * k, "device_wait": st["device_wait_s"] * k, "host_accept": st["host_accept_s"] * k,
+                                     "host_schedule": st["host_sched_s"] * 1e3 / max(1, st["steps"]), "steps": st["decode_steps"]}
     print(json.dumps({"summary": summary}))
     if a.csv:
         new = not os.path.exists(a.csv)

@@ -10,6 +10,8 @@
 // the group are served from the same K/V reads, partial (max, sum, out) triples are merged by a
 // second kernel when the sequence was split.
 #include "common.cuh"
+#include <atomic>
+#include <cstdlib>
 
 namespace b200 {
 
@@ -159,6 +161,214 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* 
       const long long idx = (static_cast<long long>(b) * Hq + kvh * G + g) * splits + sp_i;
       part_o[idx * DEC_DH + tid] = acc[g];
       if (tid == 0) { part_ml[idx * 2] = m[g]; part_ml[idx * 2 + 1] = l[g]; }
+    }
+  }
+}
+
+
+// ------------------------------------------------------------------ paged decode attention, streaming form
+// Same contract as paged_decode_kernel.  Layout of the work: a half-warp reads one 256-byte K (or V) row per load
+// instruction (lane -> 8 of the 128 dims), so every request is a full contiguous row; a thread owns KPT consecutive keys
+// of each 8*KPT-key slice (warp w, half-warp h -> keys (2w+h)*KPT ...).  The K rows of the NEXT slice and the V rows of
+// this one are requested before this slice's scores are computed, so 2*KPT 16-byte loads per thread are in flight
+// while the arithmetic runs.  Every warp keeps its own running (max, sum, output) over the keys it sees: the main loop
+// has no block-wide barrier; the four warps are merged once at the end, exactly like split-KV partials.
+//
+// Scores: each thread forms partial dot products over its 8 dims for NK keys x GP heads (NK * GP = 16) and the 16
+// values are summed over the 16 lanes by recursive halving (15 shuffles): lane i ends up with the complete score of
+// (key i / GP, head i % GP).
+__device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+
+template <int N>
+__device__ __forceinline__ void halve_reduce(float (&v)[16], int l16) {
+  if constexpr (N >= 2) {
+    constexpr int H = N / 2;
+    const bool upper = (l16 & H) != 0;  // mask H: 8, 4, 2, 1 for N = 16, 8, 4, 2
+#pragma unroll
+    for (int j = 0; j < H; ++j) {
+      const float send = upper ? v[j] : v[j + H];
+      const float keep = upper ? v[j + H] : v[j];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, H);
+    }
+    halve_reduce<H>(v, l16);
+  }
+}
+
+template <int G, int KPT, int MINB>
+__global__ void __launch_bounds__(128, MINB)
+paged_decode_stream_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ kc,
+                           const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table, int max_blocks,
+                           const int* __restrict__ ctx, int Hq, int Hkv, float scale, int splits,
+                           __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml) {
+  constexpr int GP = G <= 2 ? 2 : (G <= 4 ? 4 : 8);  // heads padded to a power of two
+  constexpr int NK = 16 / GP;                         // keys per reduction batch
+  static_assert(KPT % NK == 0, "keys per thread must be whole reduction batches");
+  constexpr int NB = KPT / NK;
+  constexpr int KI = 8 * KPT;                         // keys per block iteration (all four warps)
+  static_assert(KV_BLOCK % KI == 0, "an iteration must not straddle pages");
+  constexpr int IPP = KV_BLOCK / KI;
+  __shared__ __align__(16) float sp[4][2 * KPT][GP];
+  __shared__ __align__(16) float sal[4][GP];
+  __shared__ __align__(16) float so[4][G][DEC_DH];
+  __shared__ float sml[4][G][2];
+  const int b = blockIdx.x, kvh = blockIdx.y, sp_i = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, l16 = lane & 15, hw = lane >> 4;
+  const int L = ctx[b];
+  const int nblk = (L + KV_BLOCK - 1) / KV_BLOCK;
+  const int per = (nblk + splits - 1) / splits;
+  const int blk0 = sp_i * per, blk1 = min(nblk, blk0 + per);
+  const int it0 = blk0 * IPP, it1 = blk1 * IPP;
+  const long long row_stride = static_cast<long long>(Hq + 2 * Hkv) * DEC_DH;
+
+  float q[G][8];
+  {
+    const __nv_bfloat16* qrow = qkv + b * row_stride + static_cast<long long>(kvh * G) * DEC_DH + l16 * 8;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const uint4 u = *reinterpret_cast<const uint4*>(qrow + g * DEC_DH);
+      unpack_bf16x8(u, q[g]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[g][e] *= scale;
+    }
+  }
+  float acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  float m_l = -INFINITY, l_l = 0.f;  // running max / partial sum of head (lane % GP) over this warp's keys
+  const int kbase = (warp * 2 + hw) * KPT;
+  const int* bt_row = block_table + static_cast<long long>(b) * max_blocks;
+
+  uint4 k_cur[KPT], k_nxt[KPT], v_cur[KPT];
+  auto load_slice = [&](int it, const __nv_bfloat16* base, uint4 (&r)[KPT]) {
+    const long long blk = bt_row[it / IPP];
+    const __nv_bfloat16* p = base + ((blk * Hkv + kvh) * KV_BLOCK + (it % IPP) * KI + kbase) * DEC_DH + l16 * 8;
+    const int k0 = it * KI + kbase;
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) r[j] = (k0 + j < L) ? ld_stream16(p + j * DEC_DH) : make_uint4(0u, 0u, 0u, 0u);
+  };
+  if (it0 < it1) load_slice(it0, kc, k_cur);
+  for (int it = it0; it < it1; ++it) {
+    load_slice(it, vc, v_cur);
+    if (it + 1 < it1) load_slice(it + 1, kc, k_nxt);
+    const int k0 = it * KI + kbase;
+    float sc[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      float v[16];
+#pragma unroll
+      for (int kk = 0; kk < NK; ++kk) {
+        float kf[8];
+        unpack_bf16x8(k_cur[nb * NK + kk], kf);
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+          float d = 0.f;
+          if (g < G) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) d = fmaf(kf[e], q[g < G ? g : 0][e], d);
+          }
+          v[kk * GP + g] = d;
+        }
+      }
+      halve_reduce<16>(v, l16);
+      const int kpos = k0 + nb * NK + l16 / GP;
+      sc[nb] = (kpos < L && (l16 % GP) < G) ? v[0] : -INFINITY;
+    }
+    float tmax = sc[0];
+#pragma unroll
+    for (int nb = 1; nb < NB; ++nb) tmax = fmaxf(tmax, sc[nb]);
+#pragma unroll
+    for (int o = GP; o < 32; o <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+    const float m_new = fmaxf(m_l, tmax);
+    const float alpha = (m_l == -INFINITY) ? 0.f : __expf(m_l - m_new);
+    float psum = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const float pv = (sc[nb] == -INFINITY) ? 0.f : __expf(sc[nb] - m_new);
+      psum += pv;
+      sp[warp][hw * KPT + nb * NK + l16 / GP][l16 % GP] = pv;
+    }
+    l_l = l_l * alpha + psum;
+    m_l = m_new;
+    if (lane < GP) sal[warp][lane] = alpha;
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float a = sal[warp][g];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= a;
+    }
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) {
+      float vf[8];
+      unpack_bf16x8(v_cur[j], vf);
+      float pj[GP];
+      if constexpr (GP == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(&sp[warp][hw * KPT + j][0]);
+        pj[0] = t.x; pj[1] = t.y;
+      } else {
+#pragma unroll
+        for (int c = 0; c < GP / 4; ++c) {
+          const float4 t = *reinterpret_cast<const float4*>(&sp[warp][hw * KPT + j][4 * c]);
+          pj[4 * c] = t.x; pj[4 * c + 1] = t.y; pj[4 * c + 2] = t.z; pj[4 * c + 3] = t.w;
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj[g], vf[e], acc[g][e]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) k_cur[j] = k_nxt[j];
+  }
+  // merge: the two half-warps, then the four warps (each with its own running maximum)
+#pragma unroll
+  for (int o = GP; o < 32; o <<= 1) l_l += __shfl_xor_sync(0xffffffffu, l_l, o);
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], 16);
+  if (hw == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      *reinterpret_cast<float4*>(&so[warp][g][l16 * 8]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+      *reinterpret_cast<float4*>(&so[warp][g][l16 * 8 + 4]) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+    }
+  }
+  if (lane < GP && lane < G) { sml[warp][lane][0] = m_l; sml[warp][lane][1] = l_l; }
+  __syncthreads();
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[w][g][0]);
+    float o = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sml[w][g][0];
+      const float wt = (mw == -INFINITY) ? 0.f : __expf(mw - M);
+      o += wt * so[w][g][tid];
+      lsum += wt * sml[w][g][1];
+    }
+    if (splits == 1) {
+      out[(static_cast<long long>(b) * Hq + kvh * G + g) * DEC_DH + tid] = __float2bfloat16(lsum > 0.f ? o / lsum : 0.f);
+    } else {
+      const long long idx = (static_cast<long long>(b) * Hq + kvh * G + g) * splits + sp_i;
+      part_o[idx * DEC_DH + tid] = o;
+      if (tid == 0) { part_ml[idx * 2] = M; part_ml[idx * 2 + 1] = lsum; }
     }
   }
 }
@@ -334,6 +544,13 @@ extern "C" int b200_kv_write(const void* qkv, void* k_cache, void* v_cache, cons
   return static_cast<int>(cudaGetLastError());
 }
 
+static std::atomic<int> g_decode_variant{[] { const char* e = getenv("B200_DECODE_ATTN"); return e ? atoi(e) : 0; }()};
+// which decode-attention kernel b200_paged_decode launches (see there)
+extern "C" int b200_paged_decode_variant(int v) {
+  g_decode_variant.store(v);
+  return 0;
+}
+
 // scratch (only read when splits > 1): part_o [B*Hq*splits*128] floats, part_ml [B*Hq*splits*2] floats
 extern "C" int b200_paged_decode(const void* qkv, const void* k_cache, const void* v_cache, const int* block_table,
                                  int max_blocks, const int* ctx, int B, int Hq, int Hkv, int Dh, float scale, int splits,
@@ -344,19 +561,41 @@ extern "C" int b200_paged_decode(const void* qkv, const void* k_cache, const voi
   if (splits < 1) splits = 1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid(B, Hkv, splits);
+  // variant: 0 = streaming kernel (default; 4 keys per thread and iteration at group size 4: 97 us against 104 us with 8 at
+  // 256 sequences of 256-512 tokens), 1 = the block-synchronous kernel (213 us there), 2 = streaming with 8 keys per thread
+  const int variant = g_decode_variant.load(std::memory_order_relaxed);
+#define B200_DECS(GV, KPT, MINB)                                                                                       \
+  paged_decode_stream_kernel<GV, KPT, MINB><<<grid, 128, 0, st>>>(                                                     \
+      reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(k_cache),                    \
+      reinterpret_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks, ctx, Hq, Hkv, scale, splits,           \
+      reinterpret_cast<__nv_bfloat16*>(out), part_o, part_ml)
+  bool launched = variant != 1;
+  if (variant != 1) {
+    switch (G) {
+      case 1: B200_DECS(1, 8, 2); break;
+      case 2: B200_DECS(2, 8, 2); break;
+      case 4: if (variant == 2) B200_DECS(4, 8, 2); else B200_DECS(4, 4, 3); break;
+      case 7: B200_DECS(7, 4, 2); break;
+      case 8: B200_DECS(8, 4, 2); break;
+      default: launched = false;
+    }
+  }
+#undef B200_DECS
 #define B200_DEC(GV)                                                                                                   \
   paged_decode_kernel<GV><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv),                           \
                                                 reinterpret_cast<const __nv_bfloat16*>(k_cache),                        \
                                                 reinterpret_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks, \
                                                 ctx, Hq, Hkv, scale, splits, reinterpret_cast<__nv_bfloat16*>(out), part_o, \
                                                 part_ml)
-  switch (G) {
-    case 1: B200_DEC(1); break;
-    case 2: B200_DEC(2); break;
-    case 4: B200_DEC(4); break;
-    case 7: B200_DEC(7); break;
-    case 8: B200_DEC(8); break;
-    default: return -2;
+  if (!launched) {
+    switch (G) {
+      case 1: B200_DEC(1); break;
+      case 2: B200_DEC(2); break;
+      case 4: B200_DEC(4); break;
+      case 7: B200_DEC(7); break;
+      case 8: B200_DEC(8); break;
+      default: return -2;
+    }
   }
 #undef B200_DEC
   if (splits > 1)

@@ -157,7 +157,15 @@ int b200_engine_schedule(void* h, int64_t* prefill_ids, int* n_prefill, int64_t*
   *n_prefill = *n_decode = *n_preempted = 0;
   // ---- 1. growth of running sequences (oldest first)
   std::vector<int64_t> order = e->running;
-  std::sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return e->seqs[a].arrival < e->seqs[b].arrival; });
+  {
+    // admission order is arrival order except after a preemption: look the arrivals up once, sort only if needed
+    std::vector<std::pair<int64_t, int64_t>> keyed(order.size());
+    for (size_t i = 0; i < order.size(); ++i) keyed[i] = {e->seqs[order[i]].arrival, order[i]};
+    if (!std::is_sorted(keyed.begin(), keyed.end())) {
+      std::sort(keyed.begin(), keyed.end());
+      for (size_t i = 0; i < order.size(); ++i) order[i] = keyed[i].second;
+    }
+  }
   for (size_t i = 0; i < order.size(); ++i) {
     Seq& s = e->seqs[order[i]];
     if (!s.running) continue;  // preempted below
@@ -247,6 +255,55 @@ int b200_engine_blocks(void* h, int64_t seq_id, int* out, int cap, int* shared_p
     *shared_prefix_tokens = shared;
   }
   return n;
+}
+
+// Inputs of one decode step for `n` sequences, written straight into the caller's (pinned) staging arrays: position of
+// the new token, its cache slot, context length, sampled-token counter and the zero-padded block table (row stride =
+// widest table rounded up to `round_to`, returned in *max_blocks).  One call replaces a per-sequence round trip.
+// Returns 0; -1 unknown sequence; -2 table does not fit `bt_cap` ints.
+int b200_engine_pack_decode(void* h, const int64_t* ids, int n, int round_to, int64_t* pos, int64_t* slots, int32_t* ctx,
+                            int32_t* ctr, int32_t* bt, int64_t bt_cap, int* max_blocks) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  std::vector<const Seq*> ss(n);
+  int need = 1;
+  for (int i = 0; i < n; ++i) {
+    auto it = e->seqs.find(ids[i]);
+    if (it == e->seqs.end() || it->second.len < 1) return -1;
+    ss[i] = &it->second;
+    need = std::max(need, static_cast<int>(it->second.blocks.size()));
+  }
+  if (round_to > 1) need = (need + round_to - 1) / round_to * round_to;
+  if (static_cast<int64_t>(n) * need > bt_cap) return -2;
+  *max_blocks = need;
+  const int bs = e->block_size;
+  for (int i = 0; i < n; ++i) {
+    const Seq& s = *ss[i];
+    const int last = s.len - 1;
+    if (last / bs >= static_cast<int>(s.blocks.size())) return -1;
+    pos[i] = last;
+    slots[i] = static_cast<int64_t>(s.blocks[last / bs]) * bs + last % bs;
+    ctx[i] = s.len;
+    ctr[i] = s.len - s.prompt_len;
+    int32_t* row = bt + static_cast<int64_t>(i) * need;
+    const int nb = static_cast<int>(s.blocks.size());
+    for (int k = 0; k < nb; ++k) row[k] = s.blocks[k];
+    for (int k = nb; k < need; ++k) row[k] = 0;
+  }
+  return 0;
+}
+
+// One new token for each of `n` sequences (the batched form of b200_engine_advance).
+int b200_engine_advance_many(void* h, const int64_t* ids, int n) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  for (int i = 0; i < n; ++i) {
+    auto it = e->seqs.find(ids[i]);
+    if (it == e->seqs.end()) return -1;
+    it->second.len += 1;
+    it->second.needs_prefill = false;
+  }
+  return 0;
 }
 
 int b200_engine_counts(void* h, int* waiting, int* running) {

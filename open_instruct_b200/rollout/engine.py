@@ -48,6 +48,8 @@ class _Host:
         h.b200_engine_schedule.argtypes = [p, PI64, PI32, PI64, PI32, PI64, PI32, i32]
         h.b200_engine_blocks.argtypes = [p, i64, PI32, i32, PI32]
         h.b200_engine_counts.argtypes = [p, PI32, PI32]
+        h.b200_engine_pack_decode.argtypes = [p, p, i32, i32, p, p, p, p, p, i64, PI32]
+        h.b200_engine_advance_many.argtypes = [p, p, i32]
         self.h = h
         self.e = h.b200_engine_create(num_blocks, KV_BLOCK, max_running)
         self.cap = max(1024, max_running * 2)
@@ -73,6 +75,22 @@ class _Host:
 
     def advance(self, sid, n=1):
         return self.h.b200_engine_advance(self.e, sid, n)
+
+    def advance_many(self, sids) -> None:
+        """One new token for every sequence of the int64 numpy array ``sids``."""
+        if self.h.b200_engine_advance_many(self.e, sids.ctypes.data, len(sids)):
+            raise KeyError("advance of an unknown sequence")
+
+    def pack_decode(self, sids, pos, slots, ctx, ctr, bt, round_to: int = 4) -> int:
+        """Fill the numpy staging arrays of one decode step natively; returns the block-table row width (-2: ``bt`` too small)."""
+        w = ctypes.c_int(0)
+        rc = self.h.b200_engine_pack_decode(self.e, sids.ctypes.data, len(sids), round_to, pos.ctypes.data, slots.ctypes.data, ctx.ctypes.data,
+                                            ctr.ctypes.data, bt.ctypes.data, bt.size, ctypes.byref(w))
+        if rc == -2:
+            return -2
+        if rc:
+            raise KeyError("decode step names a sequence the scheduler does not hold")
+        return w.value
 
     def finish(self, sid):
         self.h.b200_engine_finish(self.e, sid)
@@ -159,7 +177,9 @@ class RolloutEngine:
         self.requests: dict[int, _Request] = {}
         self.base_seed = seed
         self.model_step = 0
-        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
+        # host_* are wall seconds of the host phases of decode steps (packing inputs, waiting for the device, accepting tokens)
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "host_pack_s": 0.0, "device_wait_s": 0.0, "host_accept_s": 0.0,
+                      "host_sched_s": 0.0, "decode_steps": 0}
         self.prefill_token_budget = 16384
         self.decode_splitk = os.environ.get("B200_DECODE_SPLITK", "1") == "1"  # split-K for o_proj / down_proj at <= 256 rows
         self._acc32: dict = {}
@@ -168,6 +188,8 @@ class RolloutEngine:
         self._graphs: dict = {}
         self._graph_seen: dict = {}
         self._graph_pool = None
+        self._stages: dict = {}  # pinned staging blobs of the decode step, by batch size
+        self._last_sids = None
 
     # ------------------------------------------------------------------ public API
     def kv_cache_max_concurrency(self, seq_len: int) -> int:
@@ -215,9 +237,9 @@ class RolloutEngine:
     @torch.no_grad()
     def step(self) -> list[GenerationResult]:
         """One scheduling + model step.  Returns the requests that completed in it."""
+        t0 = time.perf_counter()
         prefill_ids, decode_ids, preempted = self.host.schedule()
-        for sid in preempted:  # recompute later from prompt + generated-so-far
-            pass
+        self.stats["host_sched_s"] += time.perf_counter() - t0
         finished: list[GenerationResult] = []
         if decode_ids:
             self._decode([self.seqs[s] for s in decode_ids])
@@ -260,11 +282,12 @@ class RolloutEngine:
             is_eval=req.meta.get("is_eval", False), queries=[list(req.prompt)] * n, ground_truth=req.meta.get("ground_truth"),
             dataset=req.meta.get("dataset"), raw_query=req.meta.get("raw_query"))
 
-    def _accept(self, seq: _Sequence, token: int, logprob: float) -> None:
+    def _accept(self, seq: _Sequence, token: int, logprob: float, advance: bool = True) -> None:
         seq.tokens.append(token)
         seq.logprobs.append(logprob)
         seq.last_token = token
-        self.host.advance(seq.sid, 1)
+        if advance:  # the decode step advances all its sequences with one native call
+            self.host.advance(seq.sid, 1)
         sp = seq.request.sampling
         n_gen = len(seq.tokens) - seq.prompt_len
         if token in self.eos and n_gen >= sp.min_tokens:
@@ -480,66 +503,117 @@ class RolloutEngine:
         hidden = self._layer_stack(buf["ids"], buf["pos"], buf["slots"], attn_fn)
         logits = self._logits(hidden)
         V = logits.shape[1]
-        toks = torch.empty(B, dtype=torch.int64, device=dev)
-        lps = torch.empty(B, dtype=torch.float32, device=dev)
         call("b200_sample", ptr(logits), logits.stride(0), B, V, ptr(buf["temp"]), ptr(buf["top_p"]), ptr(buf["seeds"]), ptr(buf["ctr"]),
-             ptr(toks), ptr(lps), stream_ptr())
-        return toks, lps
+             ptr(buf["toks"]), ptr(buf["lps"]), stream_ptr())
 
-    def _decode_fused(self, seqs: list[_Sequence]):
-        """Host side of the fused decode step: pack the step's inputs, then run the device part - replaying a CUDA graph
-        when this (batch size, block-table width) has been seen before.  The launch-bound inner loop (about 400 kernels
-        for a 32-layer model) then costs one graph launch."""
+    _IN_FIELDS = (("ids", "int64"), ("pos", "int64"), ("slots", "int64"), ("seeds", "int64"), ("ctx", "int32"), ("ctr", "int32"),
+                  ("temp", "float32"), ("top_p", "float32"))
+
+    def _stage(self, B: int, width: int):
+        """Pinned host staging for ``B`` sequences: ONE blob holding every per-step input (block table last, room for
+        ``width`` blocks per sequence) and one for the outputs, with numpy views of the fields."""
+        import numpy as np
+
+        st = self._stages.get(B)
+        if st is not None and st["width"] >= width:
+            return st
+        width = max(64, -(-width // 64) * 64)
+        fixed = 48 * B
+        blob = torch.empty(fixed + 4 * B * width, dtype=torch.uint8).pin_memory() if self.device.type == "cuda" else torch.empty(fixed + 4 * B * width, dtype=torch.uint8)
+        out = torch.empty(12 * B, dtype=torch.uint8).pin_memory() if self.device.type == "cuda" else torch.empty(12 * B, dtype=torch.uint8)
+        raw = blob.numpy()
+        views, off = {}, 0
+        for name, dt in self._IN_FIELDS:
+            nbytes = np.dtype(dt).itemsize * B
+            views[name] = raw[off:off + nbytes].view(dt)
+            off += nbytes
+        views["bt"] = raw[off:].view("int32")
+        oraw = out.numpy()
+        st = {"width": width, "blob": blob, "out": out, "np": views, "toks": oraw[: 8 * B].view("int64"), "lps": oraw[8 * B:].view("float32"), "static_key": None}
+        self._stages[B] = st
+        return st
+
+    def _device_buffers(self, B: int, max_blocks: int) -> dict:
+        """Device twin of the staging blob for one (B, block-table width): typed views into one allocation, so a step's
+        inputs arrive with a single copy and its outputs leave with one."""
         import numpy as np
 
         dev = self.device
+        blob = torch.empty(48 * B + 4 * B * max_blocks, dtype=torch.uint8, device=dev)
+        out = torch.empty(12 * B, dtype=torch.uint8, device=dev)
+        buf, off = {"blob": blob, "out": out}, 0
+        for name, dt in self._IN_FIELDS:
+            nbytes = np.dtype(dt).itemsize * B
+            buf[name] = blob[off:off + nbytes].view(getattr(torch, dt))
+            off += nbytes
+        buf["bt"] = blob[off:].view(torch.int32).view(B, max_blocks)
+        buf["toks"] = out[: 8 * B].view(torch.int64)
+        buf["lps"] = out[8 * B:].view(torch.float32)
+        return buf
+
+    def _decode_fused(self, seqs: list[_Sequence]):
+        """Host side of the fused decode step: the scheduler writes positions, cache slots, context lengths and the block
+        table of all sequences into one pinned blob (one native call), one copy takes it to the device, then the device
+        part runs - replaying a CUDA graph when this (batch size, block-table width) has been seen before, so the
+        launch-bound inner loop (about 400 kernels for a 32-layer model) costs one graph launch - and one copy brings the
+        sampled tokens and their log-probs back."""
+        import numpy as np
+
         B = len(seqs)
-        ctx_list = [len(q.tokens) for q in seqs]  # the new token sits at position len-1
-        tables = [self.host.blocks(q.sid)[0] for q in seqs]
-        need = max(len(t) for t in tables)
-        max_blocks = -(-need // 4) * 4  # padded so that one captured graph serves 256 consecutive steps
         s = self.spec
+        sids = np.fromiter((q.sid for q in seqs), dtype=np.int64, count=B)
+        st = self._stage(B, 64)
+        v = st["np"]
+        max_blocks = self.host.pack_decode(sids, v["pos"], v["slots"], v["ctx"], v["ctr"], v["bt"])
+        while max_blocks == -2:  # a longer context than the staging was sized for
+            st = self._stage(B, st["width"] * 2)
+            v = st["np"]
+            max_blocks = self.host.pack_decode(sids, v["pos"], v["slots"], v["ctx"], v["ctr"], v["bt"])
+        v["ids"][:] = np.fromiter((q.last_token for q in seqs), dtype=np.int64, count=B)
+        key_static = sids.tobytes()
+        if st["static_key"] != key_static:  # sampling parameters change only when the set of sequences does
+            v["temp"][:] = np.fromiter((q.request.sampling.temperature for q in seqs), dtype=np.float32, count=B)
+            v["top_p"][:] = np.fromiter((q.request.sampling.top_p for q in seqs), dtype=np.float32, count=B)
+            v["seeds"][:] = np.fromiter((q.seed for q in seqs), dtype=np.int64, count=B)
+            st["static_key"] = key_static
+        self._last_sids = sids
         splits = 1 if B * s.num_kv_heads >= 148 else max(1, min(8, 148 // max(1, B * s.num_kv_heads), max_blocks // 4))
-        bt = np.zeros((B, max_blocks), dtype=np.int32)
-        for i, t in enumerate(tables):
-            bt[i, : len(t)] = t
-        host = {
-            "ids": np.fromiter((q.last_token for q in seqs), dtype=np.int64, count=B),
-            "pos": np.fromiter((n - 1 for n in ctx_list), dtype=np.int64, count=B),
-            "slots": np.fromiter((tables[i][(n - 1) // KV_BLOCK] * KV_BLOCK + (n - 1) % KV_BLOCK for i, n in enumerate(ctx_list)), dtype=np.int64, count=B),
-            "ctx": np.asarray(ctx_list, dtype=np.int32),
-            "bt": bt,
-            "temp": np.fromiter((q.request.sampling.temperature for q in seqs), dtype=np.float32, count=B),
-            "top_p": np.fromiter((q.request.sampling.top_p for q in seqs), dtype=np.float32, count=B),
-            "seeds": np.fromiter((q.seed for q in seqs), dtype=np.int64, count=B),
-            "ctr": np.fromiter((len(q.tokens) - q.prompt_len for q in seqs), dtype=np.int32, count=B),
-        }
+        nbytes = 48 * B + 4 * B * max_blocks
         key = (B, max_blocks, splits)
         entry = self._graphs.get(key)
+        cuda = self.device.type == "cuda"
+
+        def results(buf):
+            st["out"].copy_(buf["out"], non_blocking=True)
+            if cuda:
+                torch.cuda.current_stream(self.device).synchronize()
+            return st["toks"].tolist(), st["lps"].tolist()
+
         if entry is None:
-            buf = {k: torch.from_numpy(v).to(dev) for k, v in host.items()}
+            buf = self._device_buffers(B, max_blocks)
+            buf["blob"].copy_(st["blob"][:nbytes], non_blocking=True)
             seen = self._graph_seen.get(key, 0)
             self._graph_seen[key] = seen + 1
             if not self.use_cuda_graphs or seen < 1 or B < 4:
-                toks, lps = self._decode_device(buf, B, max_blocks, splits)  # eager (also the warm-up of this shape)
-                return toks.tolist(), lps.tolist()
-            torch.cuda.synchronize(dev)
+                self._decode_device(buf, B, max_blocks, splits)  # eager (also the warm-up of this shape)
+                return results(buf)
+            torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                toks, lps = self._decode_device(buf, B, max_blocks, splits)
+                self._decode_device(buf, B, max_blocks, splits)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
-            entry = (graph, buf, toks, lps)
+            entry = (graph, buf)
             if len(self._graphs) >= 48:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = entry
             graph.replay()  # the capture only records; this runs the step
-            return toks.tolist(), lps.tolist()
-        graph, buf, toks, lps = entry
-        for k, v in host.items():
-            buf[k].copy_(torch.from_numpy(v), non_blocking=False)
+            return results(buf)
+        graph, buf = entry
+        buf["blob"].copy_(st["blob"][:nbytes], non_blocking=True)
         graph.replay()
-        return toks.tolist(), lps.tolist()
+        self._t_launched = time.perf_counter()
+        return results(buf)
 
     def _decode(self, seqs: list[_Sequence]) -> None:
         """One token for every running sequence."""
@@ -547,10 +621,19 @@ class RolloutEngine:
         dev = self.device
         B = len(seqs)
         if self.ops == "fused":
+            t0 = time.perf_counter()
+            self._t_launched = None
             toks, lps = self._decode_fused(seqs)
+            t1 = time.perf_counter()
             self.stats["decode_tokens"] += B
+            self.host.advance_many(self._last_sids)
             for q, t, lp in zip(seqs, toks, lps):
-                self._accept(q, int(t), float(lp))
+                self._accept(q, t, lp, advance=False)
+            if self._t_launched is not None:  # graph replay: split the call into packing and waiting for the device
+                self.stats["host_pack_s"] += self._t_launched - t0
+                self.stats["device_wait_s"] += t1 - self._t_launched
+                self.stats["host_accept_s"] += time.perf_counter() - t1
+                self.stats["decode_steps"] += 1
             return
         ids = torch.tensor([q.last_token for q in seqs], dtype=torch.long, device=dev)
         ctx_list = [len(q.tokens) for q in seqs]  # the new token sits at position len-1

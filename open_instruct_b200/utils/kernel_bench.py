@@ -64,6 +64,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--impl", default=None, help="GEMM kernel: 1cta | 2cta (default: library default)")
     ap.add_argument("--shapes", default="", help="GEMM: comma-separated subset of qkv,o,gate_up,down,lm_head")
+    ap.add_argument("--decode_m", default="64,256,512", help="decode_gemm: row counts")
+    ap.add_argument("--decode_impls", default="1cta,2cta,skinny,skinny128", help="decode_gemm: kernels to time")
     ap.add_argument("--doc_len", type=int, default=0, help="attention: document length (0 = one document of --tokens)")
     ap.add_argument("--pack", default="", help="attention: 'loguniform' = documents with log-uniform lengths in [128, 4096] as in the SFT bench")
     ap.add_argument("--library", action="store_true", help="also time the library kernel for each family (implies --cublas)")
@@ -125,18 +127,54 @@ def main():
             del a_k, a_m, b_k, b_n, out16, out32
     if "decode_gemm" in only:
         # decode-sized GEMMs: a stream over the weights; the roofline is HBM bandwidth
-        for M in (64, 256, 512):
+        pick = set(filter(None, args.shapes.split(",")))
+        for M in (int(m) for m in args.decode_m.split(",")):
             for name, (N, K) in {"qkv": ((Hq + 2 * Hkv) * Dh, D), "o": (D, Hq * Dh), "gate_up": (2 * F, D), "down": (D, F)}.items():
+                if pick and name not in pick:
+                    continue
                 x, w = bf(M, K), bf(N, K)
                 by = (N * K + M * K + M * N) * 2
-                for impl in ("1cta", "2cta", "skinny", "skinny128"):
+                for impl in filter(None, args.decode_impls.split(",")):
                     rec(f"decode_gemm_{name}_M{M}_{impl}", time_op(lambda: fused.gemm(x, w, impl=impl), args.iters), bytes_=by)
                 if args.cublas:
                     rec(f"lib_cublas_decode_gemm_{name}_M{M}", time_op(lambda: torch.matmul(x, w.t()), args.iters), bytes_=by)
-                if name in ("o", "down"):
+                if name in ("o", "down") and "splitk" in args.decode_impls + ",splitk" * (args.decode_impls == "1cta,2cta,skinny,skinny128"):
                     acc = torch.zeros(M, N, device="cuda")
                     for sk in (2, 4, 8):
                         rec(f"decode_gemm_{name}_M{M}_splitk{sk}", time_op(lambda: fused.gemm_splitk_(acc, x, w, sk), args.iters), bytes_=by)
+    if "decode_attn" in only:
+        # paged decode attention at the rollout benchmark's shape: 256 sequences (32 prompts x 8 samples that share their
+        # 4 prompt pages), contexts 256 + U[1, 256], 8 KV heads x 4 query heads; the roofline is HBM bandwidth over the
+        # DISTINCT pages read
+        from ..ops.lib import call, ptr, stream_ptr
+
+        Bq, Hq, Hkv, Dh, BLK = 256, 32, 8, 128, 64
+        g = torch.Generator().manual_seed(0)
+        ctxs = (256 + torch.randint(1, 257, (Bq,), generator=g)).tolist()
+        max_blocks = 8
+        nblocks = 32 * 4 + Bq * 4
+        kc = torch.randn(nblocks, Hkv, BLK, Dh, device="cuda").bfloat16()
+        vc = torch.randn(nblocks, Hkv, BLK, Dh, device="cuda").bfloat16()
+        bt = torch.zeros(Bq, max_blocks, dtype=torch.int32)
+        for b in range(Bq):
+            bt[b, :4] = torch.arange(4) + (b // 8) * 4
+            bt[b, 4:] = 128 + b * 4 + torch.arange(4)
+        pages = sum(-(-c // BLK) - 4 for c in ctxs) + 32 * 4
+        by = pages * Hkv * BLK * Dh * 2 * 2
+        bt, ctx = bt.cuda(), torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+        qkv = torch.randn(Bq, (Hq + 2 * Hkv) * Dh, device="cuda").bfloat16()
+        out = torch.empty(Bq, Hq * Dh, device="cuda", dtype=torch.bfloat16)
+        outs = {}
+        for variant, name in ((1, "block_sync"), (2, "stream_kpt8"), (0, "stream_kpt4")):
+            call("b200_paged_decode_variant", variant)
+            fn = lambda: call("b200_paged_decode", ptr(qkv), ptr(kc), ptr(vc), ptr(bt), max_blocks, ptr(ctx), Bq, Hq, Hkv, Dh, Dh ** -0.5, 1,
+                              ptr(out), None, None, stream_ptr())
+            rec(f"decode_attn_{name}_B{Bq}", time_op(fn, args.iters), bytes_=by)
+            outs[name] = out.float().clone()
+        call("b200_paged_decode_variant", 0)
+        for name in ("stream_kpt8", "stream_kpt4"):
+            err = ((outs[name] - outs["block_sync"]).norm() / outs["block_sync"].norm()).item()
+            print({"check": f"decode_attn_{name}_vs_block_sync", "rel_err": err}, flush=True)
     if not only or "attn" in only:
         L = args.doc_len or T
         lens = [L] * (T // L) + ([T % L] if T % L else [])

@@ -79,3 +79,40 @@ def test_sampler_distribution():
     counts = torch.bincount(torch.tensor(toks), minlength=4).float() / 2000
     assert counts[3] == 0  # outside the nucleus
     assert abs(counts[0] - 0.5 / 0.95) < 0.04 and abs(counts[1] - 0.3 / 0.95) < 0.04
+
+
+def test_native_decode_packing_matches_per_sequence_queries():
+    """One native call fills positions, cache slots, context lengths, counters and the padded block table of a decode
+    step exactly as the per-sequence block queries would."""
+    import numpy as np
+
+    from open_instruct_b200.rollout.engine import KV_BLOCK, _Host
+
+    h = _Host(64, 8)
+    prompt_lens = [70, 70, 130, 5]
+    for sid, (g, pl) in enumerate(zip([0, 0, 1, 2], prompt_lens)):
+        h.add(sid, g, pl, pl + 100)
+    pre, dec, _ = h.schedule()
+    assert pre == [0, 1, 2, 3] and not dec
+    for sid in pre:
+        h.advance(sid, 1)
+    for step in range(70):
+        pre, dec, _ = h.schedule()
+        assert not pre and len(dec) == 4
+        sids = np.asarray(dec, dtype=np.int64)
+        B = len(dec)
+        pos, slots = np.zeros(B, np.int64), np.zeros(B, np.int64)
+        ctx, ctr, bt = np.zeros(B, np.int32), np.zeros(B, np.int32), np.full(B * 64, -7, np.int32)
+        w = h.pack_decode(sids, pos, slots, ctx, ctr, bt)
+        tables = [h.blocks(s)[0] for s in dec]
+        assert w == -(-max(len(t) for t in tables) // 4) * 4
+        btm = bt[: B * w].reshape(B, w)
+        for i, (s, t) in enumerate(zip(dec, tables)):
+            n = prompt_lens[s] + 1 + step
+            assert list(btm[i, : len(t)]) == t and (btm[i, len(t):] == 0).all()
+            assert ctx[i] == n and pos[i] == n - 1 and ctr[i] == step + 1
+            assert slots[i] == t[(n - 1) // KV_BLOCK] * KV_BLOCK + (n - 1) % KV_BLOCK
+        h.advance_many(sids)
+    assert h.pack_decode(sids, pos, slots, ctx, ctr, np.zeros(3, np.int32)) == -2  # staging too small: the caller grows it
+    with pytest.raises(KeyError):
+        h.pack_decode(np.asarray([99], np.int64), pos, slots, ctx, ctr, bt)
