@@ -62,10 +62,13 @@ __device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
 // residual is given (the new residual stream), rstd[row] for the backward.
 // X32: x is an fp32 accumulator (split-K GEMM output) that is consumed here: it is read, zeroed for the next GEMM that adds
 // into it, and rounded to bf16 before the residual is added (what a bf16 GEMM output would have been).
+// X32 with nparts > 0: x is `nparts` fp32 planes `part_stride` floats apart (the K slices of a split-K GEMM written with
+// plain stores); they are summed in plane order and nothing is zeroed.
 template <bool X32>
 __global__ void rmsnorm_fwd_kernel(const void* __restrict__ x_any, const __nv_bfloat16* __restrict__ res,
                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
-                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int D, float eps) {
+                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int D, float eps, int nparts = 0,
+                                   long long part_stride = 0) {
   __shared__ float red[32];
   extern __shared__ __align__(16) uint8_t dyn[];
   float* hbuf = reinterpret_cast<float*>(dyn);  // D floats: keeps h so x is read once
@@ -78,9 +81,17 @@ __global__ void rmsnorm_fwd_kernel(const void* __restrict__ x_any, const __nv_bf
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     float f[8];
     if (X32) {
-      const float4 a = x32[2 * i], b = x32[2 * i + 1];
-      x32[2 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      x32[2 * i + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 a = x32[2 * i], b = x32[2 * i + 1];
+      if (nparts == 0) {
+        x32[2 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        x32[2 * i + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      for (int p = 1; p < nparts; ++p) {
+        const float4* xp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x_any) + p * part_stride + row * D);
+        const float4 a2 = xp[2 * i], b2 = xp[2 * i + 1];
+        a.x += a2.x; a.y += a2.y; a.z += a2.z; a.w += a2.w;
+        b.x += b2.x; b.y += b2.y; b.z += b2.z; b.w += b2.w;
+      }
       const float t[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16(t[j]));
@@ -538,6 +549,23 @@ extern "C" int b200_rmsnorm_fwd_acc32(float* x32, const void* res, const void* w
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   rmsnorm_fwd_kernel<true><<<T, threads, D * sizeof(float), ST(stream)>>>(x32, CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Same, with x given as `nparts` fp32 planes [nparts][T][D] (`part_stride` floats apart) that are summed, not zeroed: the
+// partner of the K-split decode GEMM, which writes one plane per K slice with plain stores.
+extern "C" int b200_rmsnorm_fwd_parts(const float* x32, int nparts, long long part_stride, const void* res, const void* w, void* h_out,
+                                      void* y, int T, int D, float eps, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8 || D * 4 > 64 * 1024 || nparts < 1) return -1;
+  const int threads = D >= 2048 ? 256 : 128;
+  static std::atomic<unsigned long long> cfg{0};
+  {
+    cudaError_t e = opt_in_shared_memory(rmsnorm_fwd_kernel<true>, 64 * 1024, cfg);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  rmsnorm_fwd_kernel<true><<<T, threads, D * sizeof(float), ST(stream)>>>(x32, CBF(res), CBF(w), BF(h_out), BF(y), nullptr, D, eps, nparts,
+                                                                          part_stride);
   return static_cast<int>(cudaGetLastError());
 }
 

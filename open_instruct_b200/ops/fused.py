@@ -7,6 +7,8 @@ call fails in Python instead of on the device.
 
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from . import lib
@@ -95,6 +97,96 @@ def gemm_splitk_(acc32: torch.Tensor, a: torch.Tensor, b: torch.Tensor, splits: 
     call("b200_gemm_bf16_splitk", ptr(a), ptr(b), ptr(acc32), M, N, K, a.stride(0), b.stride(0), acc32.stride(0), splits,
          ptr(status_word(a.device)), stream_ptr())
     return acc32
+
+
+# ---------------------------------------------------------------------------------- decode-sized GEMM (M <= 256)
+DECODE_TILES = ((64, 1), (96, 1), (128, 1), (256, 1), (192, 2), (224, 2), (256, 2))  # (columns per MMA, MMAs side by side)
+DECODE_SPLIT_TILES = ((128, 1), (256, 1), (256, 2))                                   # shapes that can write fp32 K-slice planes
+_PAIRS = 74            # CTA pairs of one B200 (148 SMs)
+_SM_BYTES_PER_US = 80e3   # what one busy SM was measured to take in from L2 (about 80 GB/s)
+_HBM_BYTES_PER_US = 6.0e6
+_PLANE_BYTES_PER_US = 4.0e6  # fp32 K-slice planes: written by the GEMM, read by the norm, mostly out of L2
+
+
+def decode_splits(K: int, splits: int) -> int:
+    """K slices really used for a request of ``splits`` (no slice may be empty; 64-wide K blocks)."""
+    nkb = -(-K // 64)
+    splits = max(1, min(splits, nkb))
+    per = -(-nkb // splits)
+    while splits > 1 and per * (splits - 1) >= nkb:
+        splits -= 1
+        per = -(-nkb // splits)
+    return splits
+
+
+@functools.lru_cache(maxsize=None)
+def decode_gemm_plan(N: int, K: int, allow_split: bool, rows: int = 256) -> tuple[int, int, int]:
+    """(columns per MMA, MMAs per tile, K slices) for ``C[rows <= 256, N] = A @ W[N, K]^T``: the combination whose modelled
+    time is lowest.  The model is the one the kernel was shaped by: a launch is one or more waves of 74 CTA pairs, a CTA takes
+    in its 128 rows of A plus half of the tile's weights at a fixed rate, the weights cannot arrive faster than HBM delivers
+    them, and K-slice planes cost a write and a read."""
+    best, best_t = (256, 1, 1), float("inf")
+    a_rows = min(128, max(1, rows))  # rows of A a CTA really loads (rows past M are filled, not fetched)
+    for bns, nsub in DECODE_TILES:
+        bnt = bns * nsub
+        tiles = -(-N // bnt)
+        options = (1, 2, 3, 4, 6, 8) if allow_split and (bns, nsub) in DECODE_SPLIT_TILES else (1,)
+        for want in options:
+            S = decode_splits(K, want)
+            per = -(-(-(-K // 64)) // S)
+            if S != want or (S > 1 and per < 8):  # a slice shorter than the load pipeline only adds planes
+                continue
+            waves = -(-(tiles * S) // _PAIRS)
+            t = waves * (a_rows + bnt // 2) * per * 128 / _SM_BYTES_PER_US
+            t = max(t, N * K * 2 / _HBM_BYTES_PER_US)
+            if S > 1:
+                t += S * rows * N * 4 * 2 / _PLANE_BYTES_PER_US + 0.5 * (S - 1)
+            if t < best_t - 1e-9:
+                best, best_t = (bns, nsub, S), t
+    return best
+
+
+def gemm_decode(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, plan: tuple[int, int, int] | None = None) -> torch.Tensor:
+    """``a[M <= 256, K] @ w[N, K]^T`` on the decode GEMM (one wave of CTA pairs over the weights).  With a plan of one K
+    slice the result is bf16 [M, N]; with S > 1 slices it is fp32 [S, M, N], plane s holding the product over slice s (sum
+    them, e.g. with ``rmsnorm_fwd_parts``)."""
+    _check(a, torch.bfloat16, "a")
+    _check(w, torch.bfloat16, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if M > 256 or N % 16 or w.shape[1] != K or a.stride(-1) != 1 or w.stride(-1) != 1 or a.stride(0) % 8 or w.stride(0) % 8:
+        raise ValueError("decode GEMM: at most 256 rows, N a multiple of 16, K-major operands with 16-byte aligned rows")
+    bns, nsub, S = plan or decode_gemm_plan(N, K, False, M)
+    if S > 1:
+        if decode_splits(K, S) != S:
+            raise ValueError(f"{S} K slices leave one empty at K = {K}")
+        if out is None:
+            out = torch.empty(S, M, N, dtype=torch.float32, device=a.device)
+        elif out.dtype != torch.float32 or tuple(out.shape) != (S, M, N) or not out.is_contiguous():
+            raise ValueError("decode GEMM: K-slice planes must be a contiguous fp32 [S, M, N]")
+        call("b200_gemm_decode", ptr(a), ptr(w), ptr(out), M, N, K, a.stride(0), w.stride(0), N, M * N, bns, nsub, S,
+             ptr(status_word(a.device)), stream_ptr())
+        return out
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    elif out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N) or out.stride(-1) != 1 or out.stride(0) % 8:
+        raise ValueError("decode GEMM: out must be bf16 [M, N] with a 16-byte aligned row stride")
+    call("b200_gemm_decode", ptr(a), ptr(w), ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0), 0, bns, nsub, 1,
+         ptr(status_word(a.device)), stream_ptr())
+    return out
+
+
+def rmsnorm_fwd_parts(parts: torch.Tensor, w: torch.Tensor, eps: float, res: torch.Tensor | None):
+    """RMSNorm of ``bf16(sum over planes of parts) (+ res)`` for fp32 ``parts`` [S, T, D] (the K-slice planes of
+    ``gemm_decode``).  Returns ``(y, h)`` like ``rmsnorm_fwd_acc32_``; nothing is zeroed."""
+    _check(parts, torch.float32, "parts")
+    S, T, D = parts.shape
+    if not parts.is_contiguous():
+        raise ValueError("K-slice planes must be contiguous")
+    y = torch.empty(T, D, dtype=torch.bfloat16, device=parts.device)
+    h = torch.empty_like(y)
+    call("b200_rmsnorm_fwd_parts", ptr(parts), S, T * D, ptr(res), ptr(w), ptr(h), ptr(y), T, D, eps, stream_ptr())
+    return y, h
 
 
 def rmsnorm_fwd_acc32_(acc32: torch.Tensor, w: torch.Tensor, eps: float, res: torch.Tensor | None):

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "b200_rope_apply": [P, P, I, I, I, I, I, P],
     "b200_rmsnorm_fwd_acc32": [P, P, P, P, P, P, I, I, F, P],
     "b200_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, P, P],
+    "b200_gemm_decode": [P, P, P, I, I, I, L, L, L, L, I, I, I, P, P],
+    "b200_rmsnorm_fwd_parts": [P, I, L, P, P, P, P, I, I, F, P],
     "b200_rmsnorm_bwd_ctas": [I],
     "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, P],
     "b200_rope": [P, P, P, I, I, I, I, I, P],

@@ -182,6 +182,8 @@ class RolloutEngine:
                       "host_sched_s": 0.0, "decode_steps": 0}
         self.prefill_token_budget = 16384
         self.decode_splitk = os.environ.get("B200_DECODE_SPLITK", "1") == "1"  # split-K for o_proj / down_proj at <= 256 rows
+        # up to 256 rows: every projection runs on the one-wave decode GEMM (tile width and K slices chosen per weight shape)
+        self.decode_gemm = os.environ.get("B200_DECODE_GEMM", "1") == "1"
         self._acc32: dict = {}
         # captured decode steps, keyed by (batch size, padded block-table width, kv splits)
         self.use_cuda_graphs = os.environ.get("B200_DECODE_GRAPHS", "1") == "1" and tp is None
@@ -351,8 +353,12 @@ class RolloutEngine:
             stream, delta = f.embedding_fwd(p["embed"], ids), None
             tp = self.tp
 
+            dec = tp is None and T <= 256 and self.decode_gemm
+
             def add_norm(partial, w, res):
                 """(normed, new residual stream): local fused add+norm, or the cross-rank reduction fused with it."""
+                if partial.dim() == 3:  # fp32 K-slice planes of the decode GEMM: summed by the norm
+                    return f.rmsnorm_fwd_parts(partial, w, s.rms_norm_eps, res)
                 if partial.dtype == torch.float32:  # split-K accumulator: consumed (and zeroed) by the norm
                     return f.rmsnorm_fwd_acc32_(partial, w, s.rms_norm_eps, res)
                 if tp is None or res is None:
@@ -367,7 +373,12 @@ class RolloutEngine:
 
             splitk = tp is None and T <= 256 and self.decode_splitk
 
+            def col_proj(x, w, wide_impl):
+                return f.gemm_decode(x, w) if dec else f.gemm(x, w, impl=wide_impl)
+
             def row_proj(x, w, which=0):
+                if dec:  # K slices on different CTA pairs where that fills the GPU; the following norm adds them up
+                    return f.gemm_decode(x, w, plan=f.decode_gemm_plan(w.shape[0], w.shape[1], True, T))
                 # few rows, long K: cut K over SMs, fp32 partial sums added into a persistent buffer that the following norm
                 # consumes.  Measured (8B shapes): down_proj 54 -> 38 us at 64 rows (4 slices), 54 -> 49 us at 256 rows (2 slices);
                 # o_proj 22 -> 17 us at 64 rows, no gain at 256 rows (stays on the narrow-tile kernel)
@@ -377,7 +388,7 @@ class RolloutEngine:
 
             for i in range(s.num_layers):
                 n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
-                qkv = f.gemm(n1, p[f"l{i}.wqkv"], impl=impl_qkv)
+                qkv = col_proj(n1, p[f"l{i}.wqkv"], impl_qkv)
                 self.model.qkv_bias_and_norm_(qkv, i)
                 f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, table=rope_tab)
                 call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
@@ -385,7 +396,7 @@ class RolloutEngine:
                 attn = attn_fn(i, qkv)
                 o = row_proj(attn, p[f"l{i}.wo"])
                 n2, h_mid = add_norm(o, p[f"l{i}.mlp_norm"], h_in)
-                act = f.swiglu_fwd(f.gemm(n2, p[f"l{i}.w_gate_up"], impl=impl))
+                act = f.swiglu_fwd(col_proj(n2, p[f"l{i}.w_gate_up"], impl))
                 delta = row_proj(act, p[f"l{i}.w_down"], 1)
                 stream = h_mid
             nf, _ = add_norm(delta, p["final_norm"], stream)
@@ -413,7 +424,10 @@ class RolloutEngine:
         if self.ops == "fused":
             from ..ops import fused as f
 
-            return f.gemm(hidden.contiguous(), w, impl="2cta")
+            hidden = hidden.contiguous()
+            if self.tp is None and self.decode_gemm and hidden.shape[0] <= 256 and w.shape[0] % 16 == 0:
+                return f.gemm_decode(hidden, w)
+            return f.gemm(hidden, w, impl="2cta")
         return ref.linear(hidden, w)
 
     def _prefill(self, seqs: list[_Sequence]) -> None:

@@ -65,7 +65,7 @@ def main():
     ap.add_argument("--impl", default=None, help="GEMM kernel: 1cta | 2cta (default: library default)")
     ap.add_argument("--shapes", default="", help="GEMM: comma-separated subset of qkv,o,gate_up,down,lm_head")
     ap.add_argument("--decode_m", default="64,256,512", help="decode_gemm: row counts")
-    ap.add_argument("--decode_impls", default="1cta,2cta,skinny,skinny128", help="decode_gemm: kernels to time")
+    ap.add_argument("--decode_impls", default="1cta,2cta,skinny,skinny128,decode", help="decode_gemm: kernels to time")
     ap.add_argument("--doc_len", type=int, default=0, help="attention: document length (0 = one document of --tokens)")
     ap.add_argument("--pack", default="", help="attention: 'loguniform' = documents with log-uniform lengths in [128, 4096] as in the SFT bench")
     ap.add_argument("--library", action="store_true", help="also time the library kernel for each family (implies --cublas)")
@@ -134,11 +134,18 @@ def main():
                     continue
                 x, w = bf(M, K), bf(N, K)
                 by = (N * K + M * K + M * N) * 2
-                for impl in filter(None, args.decode_impls.split(",")):
+                if "decode" in args.decode_impls.split(",") and M <= 256:
+                    plan = fused.decode_gemm_plan(N, K, name in ("o", "down"), M)
+                    rec(f"decode_gemm_{name}_M{M}_onewave_{plan[0]}x{plan[1]}_k{plan[2]}", time_op(lambda: fused.gemm_decode(x, w, plan=plan), args.iters), bytes_=by)
+                    if plan[2] > 1:  # with the plane-summing norm that consumes the K slices
+                        g_, r_ = bf(N), bf(M, N)
+                        rec(f"decode_gemm_{name}_M{M}_onewave_plus_norm", time_op(lambda: fused.rmsnorm_fwd_parts(fused.gemm_decode(x, w, plan=plan), g_, 1e-5, r_), args.iters), bytes_=by)
+                        rec(f"decode_gemm_{name}_M{M}_onewave_1slice_plus_norm", time_op(lambda: fused.rmsnorm_fwd(fused.gemm_decode(x, w, plan=fused.decode_gemm_plan(N, K, False, M)), g_, 1e-5, res=r_), args.iters), bytes_=by)
+                for impl in filter(lambda i: i and i != "decode", args.decode_impls.split(",")):
                     rec(f"decode_gemm_{name}_M{M}_{impl}", time_op(lambda: fused.gemm(x, w, impl=impl), args.iters), bytes_=by)
                 if args.cublas:
                     rec(f"lib_cublas_decode_gemm_{name}_M{M}", time_op(lambda: torch.matmul(x, w.t()), args.iters), bytes_=by)
-                if name in ("o", "down") and "splitk" in args.decode_impls + ",splitk" * (args.decode_impls == "1cta,2cta,skinny,skinny128"):
+                if name in ("o", "down") and "splitk" in args.decode_impls + ",splitk" * (args.decode_impls == "1cta,2cta,skinny,skinny128,decode"):
                     acc = torch.zeros(M, N, device="cuda")
                     for sk in (2, 4, 8):
                         rec(f"decode_gemm_{name}_M{M}_splitk{sk}", time_op(lambda: fused.gemm_splitk_(acc, x, w, sk), args.iters), bytes_=by)

@@ -274,3 +274,56 @@ def test_gemm_splitk_and_consuming_norm(shape, splits):
         y2, h2, _ = fused.rmsnorm_fwd(ref.bfloat16(), w, 1e-5, res=res)
         assert acc.abs().max().item() == 0.0  # consumed: ready for the next accumulation
         assert (h.float() - h2.float()).abs().max().item() < 0.07 and _rel(y, y2) < 2e-2
+
+
+@pytest.mark.parametrize("tile", [(64, 1), (96, 1), (128, 1), (256, 1), (192, 2), (224, 2), (256, 2)])
+@pytest.mark.parametrize("M", [1, 100, 256])
+def test_decode_gemm_matches_reference(tile, M):
+    """One-wave decode GEMM, every tile shape, against fp32 PyTorch: N not a multiple of the tile width (edge tiles), K not a
+    multiple of the 64-wide block (zero-filled tail), rows below and at the 256-row limit."""
+    from open_instruct_b200.ops import fused as f
+    from open_instruct_b200.ops import lib
+
+    torch.manual_seed(M + tile[0])
+    N, K = 1072, 1000  # 1072 = 16 * 67: no tile width divides it; K = 1000: 15 full K blocks and a 40-wide tail
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).bfloat16()
+    want = a.float() @ w.float().t()
+    got = f.gemm_decode(a, w, plan=(tile[0], tile[1], 1))
+    lib.check_status()
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (M, N)
+    assert ((got.float() - want).norm() / want.norm()).item() < 5e-3
+
+
+@pytest.mark.parametrize("tile,splits", [((128, 1), 2), ((256, 1), 4), ((256, 2), 3), ((256, 1), 5)])
+def test_decode_gemm_k_slices_and_plane_summing_norm(tile, splits):
+    """K-slice planes: every plane holds its slice's product, their sum is the product, and the plane-summing RMSNorm equals
+    the unfused statement (sum -> bf16 -> + residual -> norm)."""
+    from open_instruct_b200.ops import fused as f
+    from open_instruct_b200.ops import lib, ref
+
+    torch.manual_seed(splits)
+    M, N, K = 200, 512, 1000
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).bfloat16()
+    S = f.decode_splits(K, splits)
+    assert S == (splits if splits != 5 else 4)  # 16 K blocks in 5 slices of 4 would leave the fifth empty: 4 are used
+    parts = f.gemm_decode(a, w, plan=(tile[0], tile[1], S))
+    lib.check_status()
+    assert parts.dtype == torch.float32 and tuple(parts.shape) == (S, M, N)
+    per = -(-(-(-K // 64)) // S) * 64
+    for sidx in range(S):
+        k0, k1 = sidx * per, min(K, (sidx + 1) * per)
+        want = a[:, k0:k1].float() @ w[:, k0:k1].float().t()
+        assert (parts[sidx] - want).abs().max().item() < 2e-3 * max(1.0, want.abs().max().item())
+    total = a.float() @ w.float().t()
+    assert ((parts.sum(0) - total).norm() / total.norm()).item() < 1e-3
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    g = (1 + 0.1 * torch.randn(N, device="cuda")).bfloat16()
+    y, h = f.rmsnorm_fwd_parts(parts, g, 1e-5, res)
+    h_want = (parts.sum(0).bfloat16().float() + res.float()).bfloat16()
+    assert torch.equal(h, h_want)
+    y_want = ref.rmsnorm(h_want.float(), g.float(), 1e-5)
+    assert ((y.float() - y_want).norm() / y_want.norm()).item() < 5e-3
+    y2, h2 = f.rmsnorm_fwd_parts(parts, g, 1e-5, None)
+    assert ((y2.float() - ref.rmsnorm(parts.sum(0).bfloat16().float(), g.float(), 1e-5)).norm() / y2.float().norm()).item() < 5e-3
