@@ -3,7 +3,9 @@
 // With so few rows the product is a stream over the weights, and what limits it is how evenly and how thinly that stream
 // is spread over the SMs: measured on the 8B shapes at M = 256, the general kernels ran with the SMs busy 53-70 % of the
 // time (wave quantisation: 112 tiles on 74 CTA pairs, 96 tiles on 148 SMs) at about 80 GB/s per busy SM, with neither HBM
-// (27-51 %) nor L2 (26-36 %) saturated.  So this kernel is shaped by two rules:
+// (27-51 %) nor L2 (26-36 %) saturated.  (A read-only stream tops out near 3.9 TB/s on this GPU - a library reduction over
+// 2 GiB measures 3.88, a fill 3.91, a copy 6.56 with half the bytes in each direction - so that, not the copy figure, is
+// the ceiling of a weight stream.)  So this kernel is shaped by two rules:
 //   * ONE wave: the caller picks the tile width (BNS columns per MMA, NSUB MMAs side by side, up to 448 columns) and a
 //     K split so that (column tiles x K slices) is at most the number of CTA pairs, every pair getting an equal slice;
 //   * few bytes into each SM: a CTA pair covers all 256 rows (tcgen05.mma.cta_group::2, each CTA loads its own 128 rows of A
@@ -13,8 +15,6 @@
 //
 // Warps: 0 = TMA producer (both CTAs), 1 = MMA issuer (leader CTA), 2-5 = epilogue (TMEM -> registers -> global).
 // Every wait is bounded (mbar_wait) and reports through the status word.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "pair.cuh"
 
@@ -49,7 +49,7 @@ struct Cfg {
 template <int BNS, int NSUB, bool OUT32>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, void* __restrict__ Cout,
-                   int M, int N, int K, long long ldc, long long plane, int n_tiles, int kb_per_split, int issue_group, int* __restrict__ status) {
+                   int M, int N, int K, long long ldc, long long plane, int n_tiles, int kb_per_split, int* __restrict__ status) {
   using C = Cfg<BNS, NSUB>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -92,32 +92,24 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     if (elect_one()) {
       prefetch_tensormap(&tma_a);
       prefetch_tensormap(&tma_b);
-      // K blocks are requested in groups of `issue_group`: the group's stages are waited for first, then all its loads go
-      // out back to back, so that HBM sees issue_group * 128 contiguous bytes of every weight row within a short window
-      // instead of one 128-byte piece per row per pipeline turn
+      // (Requesting several K blocks of a row back to back, to give HBM longer contiguous runs, was measured and changed
+      // nothing: 65.5 us with one block per turn, 67.8 / 68.6 us with groups of 2 / 4 on the gate/up shape.)
       uint32_t it = 0;
-      bool ok = true;
-      for (int kb = kb0; kb < kb1 && ok; kb += issue_group) {
-        const int n = min(issue_group, kb1 - kb);
-        for (int i = 0; i < n && ok; ++i) {
-          const uint32_t iti = it + i;
-          if (!mbar_wait(&empty[iti % C::STAGES], ((iti / C::STAGES) & 1) ^ 1, abort_flag)) {
-            atomicCAS(status, 0, ST_TIMEOUT_EMPTY);
-            ok = false;
-          }
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
+          atomicCAS(status, 0, ST_TIMEOUT_EMPTY);
+          break;
         }
-        if (!ok) break;
-        for (int i = 0; i < n; ++i, ++it) {
-          const int s = it % C::STAGES;
-          const uint32_t leader_full = mapa(smem_u32(&full[s]), 0);
-          if (cta == 0) mbar_expect_tx(&full[s], 2 * C::STAGE_BYTES);
-          uint8_t* st = smem + s * C::STAGE_BYTES;
-          const int k0 = (kb + i) * BK;
-          tma_load_2d_pair(st, &tma_a, leader_full, k0, static_cast<int>(cta) * BM);
+        const uint32_t leader_full = mapa(smem_u32(&full[s]), 0);
+        if (cta == 0) mbar_expect_tx(&full[s], 2 * C::STAGE_BYTES);
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        const int k0 = kb * BK;
+        tma_load_2d_pair(st, &tma_a, leader_full, k0, static_cast<int>(cta) * BM);
 #pragma unroll
-          for (int j = 0; j < NSUB; ++j)
-            tma_load_2d_pair(st + A_BYTES + j * C::B_BYTES, &tma_b, leader_full, k0, n_base + j * BNS + static_cast<int>(cta) * C::B_ROWS);
-        }
+        for (int j = 0; j < NSUB; ++j)
+          tma_load_2d_pair(st + A_BYTES + j * C::B_BYTES, &tma_b, leader_full, k0, n_base + j * BNS + static_cast<int>(cta) * C::B_ROWS);
       }
     }
   } else if (warp == 1) {
@@ -245,9 +237,7 @@ static int launch(const void* A, const void* W, void* Cout, int M, int N, int K,
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  static const int group_env = [] { const char* v = getenv("B200_DECODE_ISSUE_GROUP"); return v ? atoi(v) : 1; }();
-  const int group = group_env < 1 ? 1 : (group_env > C::STAGES / 2 ? (C::STAGES / 2 > 0 ? C::STAGES / 2 : 1) : group_env);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, Cout, M, N, K, ldc, plane, n_tiles, per, group, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, Cout, M, N, K, ldc, plane, n_tiles, per, status);
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(cudaGetLastError());
 }

@@ -125,6 +125,18 @@ def main():
                         rec(f"{name}_a{'MN' if a_mn else 'K'}_b{'MN' if b_mn else 'K'}_{mname}",
                             time_op(lambda: fused.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, out_mode=mode, impl=args.impl), args.iters), fl)
             del a_k, a_m, b_k, b_n, out16, out32
+    if "membw" in only:
+        # what the memory system delivers to plain streaming kernels (library probes, for the rooflines of the decode path):
+        # a copy moves half its bytes in each direction, a reduction only reads
+        n = 1 << 30
+        src, dst = torch.empty(n, device="cuda", dtype=torch.bfloat16), torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        rec("membw_copy_2GiB_read_plus_write", time_op(lambda: dst.copy_(src), args.iters), bytes_=4 * n)
+        rec("membw_read_only_sum_2GiB", time_op(lambda: src.view(torch.int32).sum(), args.iters), bytes_=2 * n)
+        rec("membw_read_only_max_2GiB", time_op(lambda: src.max(), args.iters), bytes_=2 * n)
+        rec("membw_write_only_fill_2GiB", time_op(lambda: dst.zero_(), args.iters), bytes_=2 * n)
+        small = src[: 235 * (1 << 19)]
+        rec("membw_read_only_sum_235MiB", time_op(lambda: small.view(torch.int32).sum(), args.iters), bytes_=2 * small.numel())
+        del src, dst
     if "decode_gemm" in only:
         # decode-sized GEMMs: a stream over the weights; the roofline is HBM bandwidth
         pick = set(filter(None, args.shapes.split(",")))
