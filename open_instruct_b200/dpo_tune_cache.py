@@ -131,7 +131,8 @@ def prepare(args: DPOExperimentConfig, tc: TokenizerConfig):
                         warmup_steps=int(max_steps * args.warmup_ratio), total_steps=max_steps,
                         gradient_checkpointing=args.activation_memory_budget < 1 or args.gradient_checkpointing, seed=args.seed,
                         offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters,
-                        tensor_parallel_degree=args.tensor_parallel_degree, shard_degree=args.fsdp_shard_degree)
+                        tensor_parallel_degree=args.tensor_parallel_degree, shard_degree=args.fsdp_shard_degree,
+                        optimizer_type=args.optimizer_type, optimizer_kwargs=dict(args.optimizer_kwargs or {}))
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):

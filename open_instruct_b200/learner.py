@@ -49,6 +49,8 @@ class LearnerConfig:
     # Tensor parallelism of the training engine: groups of this many consecutive ranks split every layer (heads and MLP
     # channels); data parallelism and the optimizer sharding run across the groups.
     tensor_parallel_degree: int = 1
+    optimizer_type: str = "adamw"     # "adamw" | "muon" (orthogonalised momentum for the decoder layers' matrices, AdamW elsewhere)
+    optimizer_kwargs: dict = field(default_factory=dict)  # Muon: mu, nesterov, ns_steps, adamw_lr_scale
 
 
 def needs_sharding(total_params: int, world: int, hbm_bytes: int, offload_optimizer: bool = False) -> bool:
@@ -97,7 +99,19 @@ class Learner:
         n = padded_numel(layout.total, self.world)
         self.symm = None
         self.z3 = None
+        if cfg.optimizer_type not in ("adamw", "muon"):
+            raise ValueError(f"unknown optimizer_type {cfg.optimizer_type!r}: 'adamw' or 'muon'")
+        muon = cfg.optimizer_type == "muon"
+        if muon:
+            if self.tp is not None or cfg.shard_parameters or cfg.offload_optimizer:
+                raise NotImplementedError("Muon runs with resident parameters and device-resident optimizer states (no tensor "
+                                          "parallelism, parameter sharding or optimizer offload)")
+            if comm == "fused":
+                comm = "nccl" if self.world > 1 else "none"  # momentum is exchanged through torch.distributed
+                self.comm = comm
         shard = cfg.shard_parameters
+        if shard is None and muon:
+            shard = False
         if shard is None:
             shard = (ops == "fused" and self.world > 1 and self.tp is None and
                      needs_sharding(layout.total, self.world, torch.cuda.get_device_properties(self.device).total_memory, cfg.offload_optimizer))
@@ -144,12 +158,19 @@ class Learner:
         if self.symm is not None:
             self.model.bind_main_grad(self.symm.grads)
         self.model.tp = self.tp
-        self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, lr=cfg.learning_rate,
-                                 betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay,
-                                 max_grad_norm=cfg.max_grad_norm, group=group, comm=comm, symm=self.symm,
-                                 use_kernels=(ops == "fused"), offload=cfg.offload_optimizer,
-                                 norm_weights=self.tp.norm_weights(layout) if self.tp is not None else None,
-                                 norm_extra_group=self.tp.group if self.tp is not None else None)
+        if muon:
+            from .parallel.muon import MuonOptimizer, muon_matrices
+
+            self.opt = MuonOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, muon_matrices(layout), lr=cfg.learning_rate,
+                                     betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
+                                     group=group, comm=comm, use_kernels=(ops == "fused"), **dict(cfg.optimizer_kwargs or {}))
+        else:
+            self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, lr=cfg.learning_rate,
+                                     betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay,
+                                     max_grad_norm=cfg.max_grad_norm, group=group, comm=comm, symm=self.symm,
+                                     use_kernels=(ops == "fused"), offload=cfg.offload_optimizer,
+                                     norm_weights=self.tp.norm_weights(layout) if self.tp is not None else None,
+                                     norm_extra_group=self.tp.group if self.tp is not None else None)
         self.global_step = 0
         self._accum = 0
         self.sp = 1
