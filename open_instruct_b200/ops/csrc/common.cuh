@@ -125,6 +125,15 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the stream is
+// still running, once every CTA of the predecessor has called `griddep_launch_dependents()` (or exited).  Whatever it does
+// before `griddep_wait()` must not depend on the predecessor's results (and must not write what the predecessor reads);
+// `griddep_wait()` returns when the predecessor has completed and its writes are visible.  Both are no-ops in a kernel that
+// was launched the ordinary way.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -239,6 +248,32 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }  // namespace b200
 
 // ---------------------------------------------------------------- host side
+#include <cstdlib>
+namespace b200 {
+// false when B200_PDL=0: every launch below then is an ordinary one
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* v = getenv("B200_PDL"); return !v || atoi(v) != 0; }();
+  return on;
+}
+// Launch with programmatic stream serialization: the kernel may start while its predecessor in the stream is still running
+// (see griddep_wait); it MUST call griddep_wait() before it reads anything an earlier kernel wrote or writes anything an
+// earlier kernel reads.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+}  // namespace b200
+
 #include <atomic>
 #include <cstdio>
 namespace b200 {

@@ -43,6 +43,64 @@ __global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bflo
   }
 }
 
+__device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
+
+// Decode step: rotary embedding of the new token's q and k heads (cos/sin from the table) AND the write of its rotated K
+// and its V into the paged cache, in one pass over the fused qkv row (one launch instead of two per layer).
+// One thread handles 8 (lo, hi) pairs of one head; v heads are copied.  slots[t] < 0 skips the cache write.
+__global__ void rope_kv_decode_kernel(__nv_bfloat16* __restrict__ qkv, const float2* __restrict__ tab, __nv_bfloat16* __restrict__ kc,
+                                      __nv_bfloat16* __restrict__ vc, const long long* __restrict__ slots, long long T, int Hq,
+                                      int Hkv) {
+  griddep_launch_dependents();
+  griddep_wait();
+  constexpr int half = DEC_DH / 2, nchunk = half / 8;
+  const int heads = Hq + 2 * Hkv;
+  const long long row_stride = static_cast<long long>(heads) * DEC_DH;
+  const long long total = T * heads * nchunk;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx % nchunk);
+    const long long th = idx / nchunk;
+    const int hd = static_cast<int>(th % heads);
+    const long long t = th / heads;
+    __nv_bfloat16* base = qkv + t * row_stride + static_cast<long long>(hd) * DEC_DH + c * 8;
+    uint4 ulo = *reinterpret_cast<const uint4*>(base), uhi = *reinterpret_cast<const uint4*>(base + half);
+    if (hd < Hq + Hkv) {
+      float lo[8], hi[8];
+      unpack_bf16x8(ulo, lo);
+      unpack_bf16x8(uhi, hi);
+      const float4* tv = reinterpret_cast<const float4*>(tab + t * half + c * 8);
+      float ol[8], oh[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 cs = tv[j];  // (cos, sin) of pairs 2j and 2j + 1
+        ol[2 * j] = lo[2 * j] * cs.x - hi[2 * j] * cs.y;
+        oh[2 * j] = hi[2 * j] * cs.x + lo[2 * j] * cs.y;
+        ol[2 * j + 1] = lo[2 * j + 1] * cs.z - hi[2 * j + 1] * cs.w;
+        oh[2 * j + 1] = hi[2 * j + 1] * cs.z + lo[2 * j + 1] * cs.w;
+      }
+      ulo = make_uint4(pack_bf16x2(ol[0], ol[1]), pack_bf16x2(ol[2], ol[3]), pack_bf16x2(ol[4], ol[5]), pack_bf16x2(ol[6], ol[7]));
+      uhi = make_uint4(pack_bf16x2(oh[0], oh[1]), pack_bf16x2(oh[2], oh[3]), pack_bf16x2(oh[4], oh[5]), pack_bf16x2(oh[6], oh[7]));
+      *reinterpret_cast<uint4*>(base) = ulo;
+      *reinterpret_cast<uint4*>(base + half) = uhi;
+      if (hd < Hq) continue;
+    }
+    const long long slot = slots[t];
+    if (slot < 0) continue;
+    const bool is_v = hd >= Hq + Hkv;
+    const int h = hd - Hq - (is_v ? Hkv : 0);
+    const long long blk = slot / KV_BLOCK, off = slot % KV_BLOCK;
+    __nv_bfloat16* dst = (is_v ? vc : kc) + ((blk * Hkv + h) * KV_BLOCK + off) * DEC_DH + c * 8;
+    *reinterpret_cast<uint4*>(dst) = ulo;
+    *reinterpret_cast<uint4*>(dst + half) = uhi;
+  }
+}
+
 // ------------------------------------------------------------------ paged decode attention
 // q rows come from qkv [B, (Hq+2Hkv)*Dh]; context length of sequence b is ctx[b] (keys 0..ctx-1,
 // the new token's K/V already written).  grid = (B, Hkv, splits), 128 threads.
@@ -177,13 +235,6 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* 
 // Scores: each thread forms partial dot products over its 8 dims for NK keys x GP heads (NK * GP = 16) and the 16
 // values are summed over the 16 lanes by recursive halving (15 shuffles): lane i ends up with the complete score of
 // (key i / GP, head i % GP).
-__device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
-  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
-  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
-  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
-  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
-}
-
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 r;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
@@ -211,6 +262,8 @@ paged_decode_stream_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfl
                            const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table, int max_blocks,
                            const int* __restrict__ ctx, int Hq, int Hkv, float scale, int splits,
                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml) {
+  griddep_launch_dependents();  // the o_proj GEMM that follows may bring its first weight tiles in during this kernel's tail
+  griddep_wait();               // launched with programmatic serialization: q and the new K/V rows are the predecessor's output
   constexpr int GP = G <= 2 ? 2 : (G <= 4 ? 4 : 8);  // heads padded to a power of two
   constexpr int NK = 16 / GP;                         // keys per reduction batch
   static_assert(KPT % NK == 0, "keys per thread must be whole reduction batches");
@@ -428,6 +481,8 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const long long* __restrict__ seeds, const int* __restrict__ counters,
               long long* __restrict__ tokens, float* __restrict__ logprobs) {
+  griddep_launch_dependents();
+  griddep_wait();
   __shared__ float sred[32];
   __shared__ ArgMax samax[32];
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
@@ -551,6 +606,21 @@ extern "C" int b200_paged_decode_variant(int v) {
   return 0;
 }
 
+// qkv [T, (Hq + 2 Hkv) * 128] in place; table [T, 64] float2 (cos, sin); slots [T] cache positions of the tokens (-1: skip)
+extern "C" int b200_rope_kv_decode(void* qkv, const void* table, void* k_cache, void* v_cache, const long long* slots, int T, int Hq,
+                                   int Hkv, int Dh, void* stream) {
+  if (T <= 0) return 0;
+  if (Dh != DEC_DH) return -1;
+  const long long total = static_cast<long long>(T) * (Hq + 2 * Hkv) * (DEC_DH / 16);
+  long long grid = (total + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  cudaError_t le = launch_pdl(rope_kv_decode_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                              reinterpret_cast<__nv_bfloat16*>(qkv), reinterpret_cast<const float2*>(table),
+                              reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), slots,
+                              static_cast<long long>(T), Hq, Hkv);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
+}
+
 // scratch (only read when splits > 1): part_o [B*Hq*splits*128] floats, part_ml [B*Hq*splits*2] floats
 extern "C" int b200_paged_decode(const void* qkv, const void* k_cache, const void* v_cache, const int* block_table,
                                  int max_blocks, const int* ctx, int B, int Hq, int Hkv, int Dh, float scale, int splits,
@@ -565,10 +635,10 @@ extern "C" int b200_paged_decode(const void* qkv, const void* k_cache, const voi
   // 256 sequences of 256-512 tokens), 1 = the block-synchronous kernel (213 us there), 2 = streaming with 8 keys per thread
   const int variant = g_decode_variant.load(std::memory_order_relaxed);
 #define B200_DECS(GV, KPT, MINB)                                                                                       \
-  paged_decode_stream_kernel<GV, KPT, MINB><<<grid, 128, 0, st>>>(                                                     \
-      reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(k_cache),                    \
-      reinterpret_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks, ctx, Hq, Hkv, scale, splits,           \
-      reinterpret_cast<__nv_bfloat16*>(out), part_o, part_ml)
+  launch_pdl(paged_decode_stream_kernel<GV, KPT, MINB>, grid, dim3(128), 0, st,                                        \
+             reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(k_cache),             \
+             reinterpret_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks, ctx, Hq, Hkv, scale, splits,    \
+             reinterpret_cast<__nv_bfloat16*>(out), part_o, part_ml)
   bool launched = variant != 1;
   if (variant != 1) {
     switch (G) {
@@ -606,7 +676,7 @@ extern "C" int b200_paged_decode(const void* qkv, const void* k_cache, const voi
 extern "C" int b200_sample(const void* logits, long long ld, int B, int V, const float* temperature, const float* top_p,
                            const long long* seeds, const int* counters, long long* tokens, float* logprobs, void* stream) {
   if (B <= 0) return 0;
-  sample_kernel<<<B, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, V,
-                                                                       temperature, top_p, seeds, counters, tokens, logprobs);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le = launch_pdl(sample_kernel, dim3(B), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream),
+                              reinterpret_cast<const __nv_bfloat16*>(logits), ld, V, temperature, top_p, seeds, counters, tokens, logprobs);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }

@@ -69,6 +69,8 @@ __global__ void rmsnorm_fwd_kernel(const void* __restrict__ x_any, const __nv_bf
                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
                                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int D, float eps, int nparts = 0,
                                    long long part_stride = 0) {
+  griddep_launch_dependents();  // the decode GEMM that follows may bring its first weight tiles in while this kernel runs
+  griddep_wait();               // launched with programmatic serialization: the input is the predecessor's output
   __shared__ float red[32];
   extern __shared__ __align__(16) uint8_t dyn[];
   float* hbuf = reinterpret_cast<float*>(dyn);  // D floats: keeps h so x is read once
@@ -325,6 +327,8 @@ __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __re
 // Rotation from the table: one thread rotates 8 (lo, hi) pairs of one head with 16-byte accesses.  Dh % 16 == 0.
 __global__ void rope_apply_kernel(__nv_bfloat16* __restrict__ qkv, const float2* __restrict__ tab, long long T, int Hq, int Hkv, int Dh,
                                   float sign) {
+  griddep_launch_dependents();
+  griddep_wait();
   const int half = Dh / 2, nchunk = half / 8, heads = Hq + Hkv;
   const long long row_stride = static_cast<long long>(Hq + 2 * Hkv) * Dh;
   const long long total = T * heads * nchunk;
@@ -357,6 +361,8 @@ __global__ void rope_apply_kernel(__nv_bfloat16* __restrict__ qkv, const float2*
 // gate_up [T, 2F] (gate | up) -> act [T, F] = silu(gate) * up
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long T,
                                   int F) {
+  griddep_launch_dependents();  // see rmsnorm_fwd_kernel
+  griddep_wait();
   const int nv = F / 8;
   const long long total = T * nv;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -533,8 +539,9 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* res, const void* w, v
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   if (D * 4 > 64 * 1024) return -2;
-  rmsnorm_fwd_kernel<false><<<T, threads, D * sizeof(float), ST(stream)>>>(x, CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le = launch_pdl(rmsnorm_fwd_kernel<false>, dim3(T), dim3(threads), D * sizeof(float), ST(stream), x, CBF(res), CBF(w), BF(h_out),
+                              BF(y), rstd, D, eps, 0, 0LL);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }
 
 // Same, with x an fp32 [T, D] accumulator that is consumed (read, then zeroed): the partner of the split-K GEMM.
@@ -548,8 +555,9 @@ extern "C" int b200_rmsnorm_fwd_acc32(float* x32, const void* res, const void* w
     cudaError_t e = opt_in_shared_memory(rmsnorm_fwd_kernel<true>, 64 * 1024, cfg);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  rmsnorm_fwd_kernel<true><<<T, threads, D * sizeof(float), ST(stream)>>>(x32, CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le = launch_pdl(rmsnorm_fwd_kernel<true>, dim3(T), dim3(threads), D * sizeof(float), ST(stream), static_cast<const void*>(x32),
+                              CBF(res), CBF(w), BF(h_out), BF(y), rstd, D, eps, 0, 0LL);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }
 
 // Same, with x given as `nparts` fp32 planes [nparts][T][D] (`part_stride` floats apart) that are summed, not zeroed: the
@@ -564,9 +572,9 @@ extern "C" int b200_rmsnorm_fwd_parts(const float* x32, int nparts, long long pa
     cudaError_t e = opt_in_shared_memory(rmsnorm_fwd_kernel<true>, 64 * 1024, cfg);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  rmsnorm_fwd_kernel<true><<<T, threads, D * sizeof(float), ST(stream)>>>(x32, CBF(res), CBF(w), BF(h_out), BF(y), nullptr, D, eps, nparts,
-                                                                          part_stride);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le = launch_pdl(rmsnorm_fwd_kernel<true>, dim3(T), dim3(threads), D * sizeof(float), ST(stream), static_cast<const void*>(x32),
+                              CBF(res), CBF(w), BF(h_out), BF(y), static_cast<float*>(nullptr), D, eps, nparts, part_stride);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }
 
 // Shared by both entry points: picks the register-resident kernel where D allows it, launches it with at most `max_ctas`
@@ -630,16 +638,16 @@ extern "C" int b200_rope_apply(void* qkv, const void* table, int T, int Hq, int 
   if (T <= 0) return 0;
   if (Dh % 16) return -1;
   const long long total = static_cast<long long>(T) * (Hq + Hkv) * (Dh / 16);
-  rope_apply_kernel<<<grid_for(total, 256), 256, 0, ST(stream)>>>(BF(qkv), reinterpret_cast<const float2*>(table), T, Hq, Hkv, Dh,
-                                                                 backward ? -1.f : 1.f);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le = launch_pdl(rope_apply_kernel, dim3(grid_for(total, 256)), dim3(256), 0, ST(stream), BF(qkv), reinterpret_cast<const float2*>(table),
+                              static_cast<long long>(T), Hq, Hkv, Dh, backward ? -1.f : 1.f);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }
 
 extern "C" int b200_swiglu_fwd(const void* gu, void* act, long long T, int F, void* stream) {
   if (T <= 0) return 0;
   if (F % 8) return -1;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, ST(stream)>>>(CBF(gu), BF(act), T, F);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le = launch_pdl(swiglu_fwd_kernel, dim3(grid_for(T * (F / 8), 256)), dim3(256), 0, ST(stream), CBF(gu), BF(act), T, F);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }
 extern "C" int b200_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long T, int F, void* stream) {
   if (T <= 0) return 0;

@@ -68,6 +68,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   const int kb0 = ks * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
   const int n_base = n_tile * C::BNT;
 
+  griddep_launch_dependents();
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::STAGES; ++i) {
       mbar_init(&full[i], 1);
@@ -94,8 +95,24 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       prefetch_tensormap(&tma_b);
       // (Requesting several K blocks of a row back to back, to give HBM longer contiguous runs, was measured and changed
       // nothing: 65.5 us with one block per turn, 67.8 / 68.6 us with groups of 2 / 4 on the gate/up shape.)
-      uint32_t it = 0;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      //
+      // The weights do not depend on the kernel before this one, the activations do: the B tiles of the first ring turn are
+      // requested right away (under programmatic dependent launch that is while the predecessor still runs), the A tiles
+      // after the grid dependency has resolved.  Both halves of a stage report to the same barrier.
+      const int pre = min(C::STAGES, kb1 - kb0);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t leader_full = mapa(smem_u32(&full[i]), 0);
+        if (cta == 0) mbar_expect_tx(&full[i], 2 * C::STAGE_BYTES);
+        uint8_t* st = smem + i * C::STAGE_BYTES;
+#pragma unroll
+        for (int j = 0; j < NSUB; ++j)
+          tma_load_2d_pair(st + A_BYTES + j * C::B_BYTES, &tma_b, leader_full, (kb0 + i) * BK, n_base + j * BNS + static_cast<int>(cta) * C::B_ROWS);
+      }
+      griddep_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d_pair(smem + i * C::STAGE_BYTES, &tma_a, mapa(smem_u32(&full[i]), 0), (kb0 + i) * BK, static_cast<int>(cta) * BM);
+      uint32_t it = pre;
+      for (int kb = kb0 + pre; kb < kb1; ++kb, ++it) {
         const int s = it % C::STAGES;
         const uint32_t ph = (it / C::STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
@@ -150,6 +167,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int lane_grp = warp & 3;  // the TMEM lane quarter this warp may read
+    griddep_wait();  // stores below must not overtake the predecessor (they could not anyway: the accumulator needs A)
     const bool ready = __all_sync(0xffffffffu, mbar_wait(tfull, 0, abort_flag));
     if (!ready) {
       if (lane == 0) atomicCAS(status, 0, ST_TIMEOUT_TMEM_FULL);
@@ -226,17 +244,21 @@ static int launch(const void* A, const void* W, void* Cout, int M, int N, int K,
   }
   const int n_tiles = (N + C::BNT - 1) / C::BNT;
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: this kernel may start (prologue + first weight tiles) while its predecessor finishes
+  const bool pdl = pdl_enabled();
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(THREADS);
   cfg.gridDim = dim3(2 * n_tiles * splits);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = stream;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, Cout, M, N, K, ldc, plane, n_tiles, per, status);
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(cudaGetLastError());

@@ -55,6 +55,7 @@ _SIGNATURES = {
     "b200_kv_write": [P, P, P, P, I, I, I, I, I, P],
     "b200_paged_decode": [P, P, P, P, I, P, I, I, I, I, F, I, P, P, P, P],
     "b200_paged_decode_variant": [I],
+    "b200_rope_kv_decode": [P, P, P, P, P, I, I, I, I, P],
     "b200_sample": [P, L, I, I, P, P, P, P, P, P, P],
     "b200_attn_fwd": [P, P, P, P, P, I, I, I, I, I, I, F, P],
     "b200_attn_bwd": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P],

@@ -354,6 +354,7 @@ class RolloutEngine:
             tp = self.tp
 
             dec = tp is None and T <= 256 and self.decode_gemm
+            fuse_rope_kv = slots.numel() == T and s.head_dim == 128 and rope_tab is not None
 
             def add_norm(partial, w, res):
                 """(normed, new residual stream): local fused add+norm, or the cross-rank reduction fused with it."""
@@ -390,9 +391,13 @@ class RolloutEngine:
                 n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
                 qkv = col_proj(n1, p[f"l{i}.wqkv"], impl_qkv)
                 self.model.qkv_bias_and_norm_(qkv, i)
-                f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, table=rope_tab)
-                call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
-                     s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
+                if fuse_rope_kv:  # one destination per token (decode, plain prefill): rotation and cache write in one pass
+                    call("b200_rope_kv_decode", ptr(qkv), ptr(rope_tab), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), T,
+                         s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
+                else:
+                    f.rope_(qkv, pos32, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, table=rope_tab)
+                    call("b200_kv_write", ptr(qkv), ptr(self.k_cache[i]), ptr(self.v_cache[i]), ptr(slots), slots.numel(), T,
+                         s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
                 attn = attn_fn(i, qkv)
                 o = row_proj(attn, p[f"l{i}.wo"])
                 n2, h_mid = add_norm(o, p[f"l{i}.mlp_norm"], h_in)

@@ -163,3 +163,27 @@ def test_fused_engine_golden_tokens():
         for a, b in zip(got[name]["logprobs"], want[name]["logprobs"]):
             for x, y in zip(a, b):
                 assert all(abs(p - q) < 2e-2 for p, q in zip(x, y)), name
+
+
+def test_fused_rope_and_kv_write_matches_the_two_kernels():
+    """Rotation + paged-cache write in one pass equals ``rope_`` followed by ``b200_kv_write`` bit for bit, skipped slots included."""
+    from open_instruct_b200.ops import fused as f
+    from open_instruct_b200.ops.lib import call, ptr, stream_ptr
+
+    torch.manual_seed(3)
+    T, Hq, Hkv, Dh, BLK, nblocks = 37, 8, 2, 128, 64, 16
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * Dh, device="cuda").bfloat16()
+    pos = torch.randint(0, 5000, (T,), device="cuda", dtype=torch.int32)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, Dh, 2, device="cuda").float() / Dh)))
+    tab = f.rope_table(pos, inv_freq, Dh)
+    slots = torch.randperm(nblocks * BLK, device="cuda")[:T].long()
+    slots[5] = -1
+    a, b = qkv.clone(), qkv.clone()
+    kc1, vc1 = torch.zeros(nblocks, Hkv, BLK, Dh, device="cuda", dtype=torch.bfloat16), torch.zeros(nblocks, Hkv, BLK, Dh, device="cuda", dtype=torch.bfloat16)
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    f.rope_(a, pos, inv_freq, Hq, Hkv, Dh, table=tab)
+    call("b200_kv_write", ptr(a), ptr(kc1), ptr(vc1), ptr(slots), T, T, Hq, Hkv, Dh, stream_ptr())
+    call("b200_rope_kv_decode", ptr(b), ptr(tab), ptr(kc2), ptr(vc2), ptr(slots), T, Hq, Hkv, Dh, stream_ptr())
+    torch.cuda.synchronize()
+    assert torch.equal(a, b) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert kc1.abs().sum() > 0 and vc1.abs().sum() > 0
