@@ -59,6 +59,7 @@ def parse():
     ap.add_argument("--grpo_response_length", type=int, default=2048)
     ap.add_argument("--grpo_prompts", type=int, default=64)
     ap.add_argument("--grpo_samples", type=int, default=8)
+    ap.add_argument("--grpo_layout", default="", help="--task grpo: learners,engines,engine_tp overriding the default split of --gpus")
     ap.add_argument("--pairs_per_gpu", type=int, default=16)
     ap.add_argument("--pairs_per_micro", type=int, default=2)
     return ap.parse_args()
@@ -210,6 +211,11 @@ def run_grpo(args) -> int:
     n = max(1, args.gpus)
     layout = {1: ["--single_gpu_mode"], 2: ["--learners", "1", "--engines", "1"], 4: ["--learners", "2", "--engines", "2"],
               8: ["--learners", "4", "--engines", "2", "--engine_tp", "2"]}.get(n)
+    if args.grpo_layout:  # "learners,engines,engine_tp", e.g. 2,1,2 = the 8-GPU recipe's shape on 4 GPUs
+        nl, ne, tp = (int(x) for x in args.grpo_layout.split(","))
+        if nl + ne * tp != n:
+            raise SystemExit(f"--grpo_layout {args.grpo_layout} needs {nl + ne * tp} GPUs, --gpus says {n}")
+        layout = ["--learners", str(nl), "--engines", str(ne), "--engine_tp", str(tp)]
     if layout is None:
         raise SystemExit("--task grpo runs on 1, 2, 4 or 8 GPUs")
     import torch

@@ -182,8 +182,34 @@ class TrainTP:
         return logp, ent
 
     def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:   # fused path: explicit, in place
-        dist.all_reduce(t, group=self.group)
+        """Sum ``t`` over the tensor-parallel group, in place.  bf16 ``[tokens, hidden]`` activations on a GPU go through the
+        one-shot kernel the rollout engine uses (every rank stores its partial in a symmetric buffer, exchanges one flag and
+        adds all ranks' slots with 16-byte peer loads in rank order: the same bits on every rank, one kernel instead of a
+        library ring); everything else, and ``B200_TP_FUSED_ALLREDUCE=0``, through ``torch.distributed``."""
+        ctx = self._fused_ctx(t)
+        if ctx is None:
+            dist.all_reduce(t, group=self.group)
+            return t
+        buf = ctx.out_buffer(t.shape[0])
+        buf.copy_(t)
+        ctx.reduce_norm(buf, None, 0.0, res=None, out=t)
         return t
+
+    def _fused_ctx(self, t: torch.Tensor):
+        """The symmetric exchange buffers for ``[<= max_tokens, t.shape[1]]`` tensors, created on first use (a collective:
+        every rank reaches its first all-reduce at the same place), or None where the fused kernel does not apply."""
+        import os
+
+        if (not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or not t.is_contiguous() or self.world < 2 or self.world > 8
+                or t.shape[1] % 128 or t.shape[1] > 8192 or os.environ.get("B200_TP_FUSED_ALLREDUCE", "1") == "0"):
+            return None
+        ctxs = self.__dict__.setdefault("_ctxs", {})
+        D = t.shape[1]
+        if D not in ctxs:
+            max_tokens = int(os.environ.get("B200_TP_MAX_TOKENS", "16384"))
+            ctxs[D] = TPContext(D, max_tokens, t.device, group=self.group)
+        ctx = ctxs[D]
+        return ctx if t.shape[0] <= ctx.max_tokens else None
 
     def sum_partials(self, x):    # autograd path
         return _SumOverTP.apply(x, self.group)
@@ -277,13 +303,15 @@ class TPContext:
         self._pushed = True
         return out
 
-    def reduce_norm(self, partial: torch.Tensor, weight: torch.Tensor | None, eps: float, res: torch.Tensor | None = None):
-        """``h = res + sum_ranks partial``; ``y = rmsnorm(h) * weight``.  Returns ``(y, h)`` (``y`` is None without a weight)."""
+    def reduce_norm(self, partial: torch.Tensor, weight: torch.Tensor | None, eps: float, res: torch.Tensor | None = None,
+                    out: torch.Tensor | None = None):
+        """``h = res + sum_ranks partial``; ``y = rmsnorm(h) * weight``.  Returns ``(y, h)`` (``y`` is None without a weight);
+        ``out`` (bf16 [T, D], contiguous) receives ``h`` instead of a fresh tensor."""
         T, D = partial.shape
         buf = self.bufs[self._next]
         if partial.data_ptr() != buf.data_ptr() + 2 * self.rank * self.slot:
             raise ValueError("the partial must live in the buffer handed out by out_buffer()")
-        h = torch.empty(T, D, dtype=torch.bfloat16, device=self.device)
+        h = out if out is not None else torch.empty(T, D, dtype=torch.bfloat16, device=self.device)
         y = torch.empty_like(h) if weight is not None else None
         self._epoch += 1
         if self._pushed:  # every rank's partial already sits in my buffer: slot r at a local address

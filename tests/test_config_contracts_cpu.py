@@ -93,6 +93,35 @@ def test_engine_control_rpcs():
         w.shutdown()
 
 
+def test_control_calls_go_ahead_of_the_decode_loop():
+    """A weight update is served after the step that is running, not after however many steps the loop manages to start while the
+    caller waits for an unfair lock (measured before the fix: 4 to 20 seconds of engine steps per sync)."""
+    w = _engine_worker()
+    try:
+        steps = []
+
+        def quick_step():
+            steps.append(time.perf_counter())
+            time.sleep(0.002)
+            return []
+
+        w.engine.step = quick_step
+        w.engine.has_unfinished = lambda: True
+        time.sleep(0.1)
+        assert len(steps) > 5  # the loop is spinning
+        worst = 0
+        for _ in range(20):
+            n0 = len(steps)
+            w.begin_weight_update()
+            worst = max(worst, len(steps) - n0)
+            w.abort_weight_update()
+            time.sleep(0.005)
+        assert worst <= 2, worst
+    finally:
+        w.engine.has_unfinished = lambda: False
+        w.shutdown()
+
+
 def test_weight_update_cannot_overlap_an_engine_step():
     """begin_weight_update waits for the running step and holds the next one back until update_weights ends the update."""
     w = _engine_worker()
