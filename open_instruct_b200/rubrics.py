@@ -39,7 +39,8 @@ async def score_rubrics(answer: str, spec: dict, ask) -> tuple[float, list[dict]
     pos = sum(max(0.0, float(r.get("weight", 1.0))) for r in rubrics)
     total = sum(float(r.get("weight", 1.0)) * s for r, s in zip(rubrics, scores))
     final = min(max(total / pos, 0.0), 1.0) if pos > 0 else 0.0
-    return final, [{"description": r["description"], "weight": r.get("weight", 1.0), "score": s} for r, s in zip(rubrics, scores)]
+    return final, [{"description": r["description"], "weight": r.get("weight", 1.0), "score": s, "type": r.get("type", "persistent")}
+                   for r, s in zip(rubrics, scores)]
 
 
 @dataclass
@@ -48,6 +49,11 @@ class RubricItem:
     weight: float = 1.0
     adaptive: bool = False
     history: list[float] = field(default_factory=list)
+    title: str = ""
+
+    @property
+    def kind(self) -> str:
+        return "evolving" if self.adaptive else "persistent"
 
 
 class RubricBuffer:
@@ -55,6 +61,7 @@ class RubricBuffer:
 
     def __init__(self, max_active_adaptive: int = 5, min_std: float = 1e-6):
         self.items: dict[str, list[RubricItem]] = {}
+        self.inactive: dict[str, list[RubricItem]] = {}   # retired adaptive items, kept for inspection and never re-proposed
         self.max_active_adaptive, self.min_std = max_active_adaptive, min_std
 
     def add_persistent(self, prompt_id: str, descriptions: list[str], weight: float = 1.0) -> None:
@@ -62,13 +69,15 @@ class RubricBuffer:
 
     def add_adaptive(self, prompt_id: str, proposals: list[dict]) -> None:
         cur = self.items.setdefault(prompt_id, [])
-        known = {i.description for i in cur}
+        known = {i.description for i in cur} | {i.description for i in self.inactive.get(prompt_id, [])}
         for p in proposals:
             if p["description"] not in known:
-                cur.append(RubricItem(p["description"], float(p.get("weight", 1.0)), True))
+                cur.append(RubricItem(p["description"], float(p.get("weight", 1.0)), True, title=p.get("title", "")))
+                known.add(p["description"])
         adaptive = [i for i in cur if i.adaptive]
         for extra in adaptive[: max(0, len(adaptive) - self.max_active_adaptive)]:
             cur.remove(extra)
+            self.inactive.setdefault(prompt_id, []).append(extra)
 
     def record_group_scores(self, prompt_id: str, per_item_scores: list[list[float]]) -> None:
         """``per_item_scores[k]`` = scores of item k over the samples of one prompt group."""
@@ -80,18 +89,78 @@ class RubricBuffer:
                 retire.append(item)
         for it in retire:
             cur.remove(it)
+            self.inactive.setdefault(prompt_id, []).append(it)
+
+    def filter(self, stats: dict[tuple[str, str], dict], max_active: int | None = None) -> dict[str, int]:
+        """Prune with per-item score statistics gathered over a training step (the reference's ``filter_rubric_buffer``,
+        ``open_instruct/rubrics/metrics.py:79-148``): ``stats[(prompt_id, description)] = {"mean": ..., "std": ...}``.
+        Adaptive items whose scores did not vary at all are retired; if a prompt still has more than ``max_active`` adaptive
+        items, those with the largest spread are kept (items without statistics are not touched).  Returns the counts."""
+        cap = self.max_active_adaptive if max_active is None else max_active
+        zero_std = over_cap = 0
+        for pid, cur in self.items.items():
+            scored = []
+            for it in [i for i in cur if i.adaptive]:
+                st = stats.get((pid, it.description))
+                if st is None:
+                    continue
+                if st["std"] <= self.min_std:
+                    cur.remove(it)
+                    self.inactive.setdefault(pid, []).append(it)
+                    zero_std += 1
+                else:
+                    scored.append((st["std"], it))
+            if sum(1 for i in cur if i.adaptive) > cap:
+                scored.sort(key=lambda t: -t[0])
+                for _, it in scored[cap:]:
+                    cur.remove(it)
+                    self.inactive.setdefault(pid, []).append(it)
+                    over_cap += 1
+        return {"zero_std": zero_std, "over_cap": over_cap}
+
+    def counts(self) -> dict[str, float]:
+        n = max(1, len(self.items))
+        return {"evolving_rubrics/num_active_rubrics": sum(sum(1 for i in v if i.adaptive) for v in self.items.values()) / n,
+                "evolving_rubrics/num_persistent_rubrics": sum(sum(1 for i in v if not i.adaptive) for v in self.items.values()) / n,
+                "evolving_rubrics/num_inactive_rubrics": sum(len(v) for v in self.inactive.values()) / n}
 
     def spec_for(self, prompt_id: str, query: str) -> dict:
-        return {"query": query, "rubrics": [{"description": i.description, "weight": i.weight} for i in self.items.get(prompt_id, [])]}
+        return {"query": query, "rubrics": [{"description": i.description, "weight": i.weight, "type": i.kind} for i in self.items.get(prompt_id, [])]}
 
     def state_dict(self) -> dict:
-        return {k: [vars(i) for i in v] for k, v in self.items.items()}
+        return {"active": {k: [vars(i) for i in v] for k, v in self.items.items()},
+                "inactive": {k: [vars(i) for i in v] for k, v in self.inactive.items()}}
 
     def load_state_dict(self, sd: dict) -> None:
-        self.items = {k: [RubricItem(**i) for i in v] for k, v in sd.items()}
+        if "active" not in sd:  # earlier format: the active items only
+            sd = {"active": sd, "inactive": {}}
+        self.items = {k: [RubricItem(**i) for i in v] for k, v in sd["active"].items()}
+        self.inactive = {k: [RubricItem(**i) for i in v] for k, v in sd["inactive"].items()}
 
     def dumps(self) -> str:
         return json.dumps(self.state_dict())
+
+
+def rubric_reward_metrics(per_response: list[list[dict]]) -> dict[str, float]:
+    """Mean and spread of the weighted item scores, split by item type (``open_instruct/rubrics/metrics.py:19-56``).
+    ``per_response[k]`` is the per-item list that ``score_rubrics`` returns for response k, each entry carrying ``score``,
+    ``weight`` and ``type`` ("evolving" | "persistent"; missing = persistent)."""
+    ev = [d["score"] * d["weight"] for items in per_response for d in items if d.get("type") == "evolving"]
+    ps = [d["score"] * d["weight"] for items in per_response for d in items if d.get("type") != "evolving"]
+    return {"evolving_rubrics/avg_evolving_reward": statistics.fmean(ev) if ev else 0.0,
+            "evolving_rubrics/std_evolving_reward": statistics.pstdev(ev) if ev else 0.0,
+            "evolving_rubrics/avg_persistent_reward": statistics.fmean(ps) if ps else 0.0,
+            "evolving_rubrics/std_persistent_reward": statistics.pstdev(ps) if ps else 0.0}
+
+
+def rubric_key_stats(prompt_ids: list[str], per_response: list[list[dict]]) -> dict[tuple[str, str], dict]:
+    """(prompt id, item description) -> {"mean", "std"} of the item's scores over the responses of a step: the input of
+    ``RubricBuffer.filter``."""
+    acc: dict[tuple[str, str], list[float]] = {}
+    for pid, items in zip(prompt_ids, per_response):
+        for d in items:
+            acc.setdefault((pid, d["description"]), []).append(float(d["score"]))
+    return {k: {"mean": statistics.fmean(v), "std": statistics.pstdev(v) if len(v) > 1 else 0.0} for k, v in acc.items()}
 
 
 _EVOLVE_PROMPT = ("You maintain grading rubrics for the question below. Here are several sampled answers. Propose rubric items that "
@@ -144,8 +213,8 @@ class RubricManager:
             parsed = None
         if parsed is None:
             return None
-        out = [{"description": r["description"], "weight": 1.0} for r in parsed.get("positive_rubrics", []) if r.get("description")]
-        out += [{"description": r["description"], "weight": -1.0} for r in parsed.get("negative_rubrics", []) if r.get("description")]
+        out = [{"description": r["description"], "weight": 1.0, "title": r.get("title", "")} for r in parsed.get("positive_rubrics", []) if r.get("description")]
+        out += [{"description": r["description"], "weight": -1.0, "title": r.get("title", "")} for r in parsed.get("negative_rubrics", []) if r.get("description")]
         return out
 
     def step(self, decoded_responses: list[str], ground_truths: list[dict], indices: list[int], num_samples: int, training_step: int = 0):
@@ -170,7 +239,7 @@ class RubricManager:
         active = [sum(1 for i in self.buffer.items[str(idx)] if i.adaptive) for idx, _, _ in groups]
         metrics = {"evolving_rubrics/valid_rate": valid / n, "evolving_rubrics/avg_new_rubrics": n_new / n,
                    "evolving_rubrics/avg_active_buffer": sum(active) / n, "evolving_rubrics/num_overrides": len(overrides),
-                   "evolving_rubrics/skipped": len(groups) - valid}
+                   "evolving_rubrics/skipped": len(groups) - valid, "evolving_rubrics/num_new_rubrics": n_new / n, **self.buffer.counts()}
         if self.cache_dir:
             import os
 

@@ -15,6 +15,7 @@ The worker runs as a thread in single-process mode and inside an actor otherwise
 from __future__ import annotations
 
 import logging
+import os
 import threading
 import time
 from dataclasses import dataclass, field
@@ -220,8 +221,26 @@ class DataPreparation:
     """
 
     def __init__(self, dataset, config: StreamingDataLoaderConfig, prompt_queue, results_queue, tokenizer, dp_world: int,
-                 per_device_train_batch_size: int, seed: int, num_training_steps: int, eval_queue=None, top_p: float = 1.0):
+                 per_device_train_batch_size: int, seed: int, num_training_steps: int, eval_queue=None, top_p: float = 1.0,
+                 rubric_judge=None):
         self.cfg, self.tok = config, tokenizer
+        # evolving rubrics (``open_instruct/data_loader.py:1366-1370, 1462-1470``): after every step the judge proposes new
+        # rubric items from the step's answers; prompts queued afterwards carry the updated rubric set as their ground truth
+        self.rubric_manager = None
+        self.ground_truth_overrides: dict[int, object] = {}
+        if config.apply_evolving_rubric_reward:
+            from .rubrics import RubricManager
+
+            if rubric_judge is None:
+                from .ground_truth_utils import LMJudgeVerifier, LMJudgeVerifierConfig
+
+                judge = LMJudgeVerifier("quality", LMJudgeVerifierConfig(llm_judge_model=config.llm_judge_model, llm_judge_max_tokens=config.llm_judge_max_tokens,
+                                                                         llm_judge_temperature=config.llm_judge_temperature,
+                                                                         llm_judge_timeout=config.llm_judge_timeout,
+                                                                         llm_judge_base_url=os.environ.get("LLM_JUDGE_BASE_URL")))
+                rubric_judge = judge._ask
+            self.rubric_manager = RubricManager(rubric_judge, max_active_rubrics=config.max_active_rubrics,
+                                                cache_dir=config.cache_evolving_rubric_data_dir)
         self.prompt_q, self.results_q, self.eval_q = prompt_queue, results_queue, eval_queue
         self.dp_world, self.pdbs, self.seed = dp_world, per_device_train_batch_size, seed
         self.num_steps = num_training_steps
@@ -247,8 +266,10 @@ class DataPreparation:
 
     def add_prompt(self) -> None:
         row, epoch = next(self.prompts)
-        req = PromptRequest(prompt=list(row["input_ids_prompt"]), generation_config=self._sampling(), index=int(row.get("index", 0)),
-                            prompt_id=f"{epoch}_{row.get('index', 0)}", raw_query=row.get("prompt"), ground_truth=row.get("ground_truth"),
+        index = int(row.get("index", 0))
+        req = PromptRequest(prompt=list(row["input_ids_prompt"]), generation_config=self._sampling(), index=index,
+                            prompt_id=f"{epoch}_{row.get('index', 0)}", raw_query=row.get("prompt"),
+                            ground_truth=self.ground_truth_overrides.get(index, row.get("ground_truth")),
                             dataset=row.get("dataset"), epoch_number=epoch, training_step=self.model_step)
         self.prompt_q.put(req)
         self.total_prompts += 1
@@ -331,11 +352,40 @@ class DataPreparation:
             for kk, v in (r.reward_metrics or {}).items():
                 m.setdefault(kk, []).append(v)
         m = {kk: (float(np.mean(v)) if isinstance(v, list) else v) for kk, v in m.items()}
+        if self.rubric_manager is not None:
+            m.update(self._evolve_rubrics(results, responses, step))
         with self.lock:
             self.prepared[step] = per_rank
             self.metrics[step] = m
             self.lock.notify_all()
         return True
+
+    def _evolve_rubrics(self, results: list[GenerationResult], responses: list[list[int]], step: int) -> dict:
+        """One evolving-rubric step over this batch's groups; rubric ground truths are JSON specs (``{"query", "rubrics"}``)."""
+        import json
+
+        k = self.cfg.num_samples_per_prompt_rollout
+        decoded, gts, idx, pos = [], [], [], 0
+        for r in results:
+            n = len(r.responses)
+            texts = r.decoded_responses or ([self.tok.decode(x, skip_special_tokens=True) for x in responses[pos:pos + n]] if self.tok is not None else [""] * n)
+            pos += n
+            gt = r.ground_truth[0] if isinstance(r.ground_truth, list) and r.ground_truth else r.ground_truth
+            if isinstance(gt, str):
+                try:
+                    gt = json.loads(gt)
+                except json.JSONDecodeError:
+                    gt = None
+            if not isinstance(gt, dict) or n != k:
+                continue  # not a rubric-scored prompt (mixed datasets), or an incomplete group
+            decoded += list(texts)
+            gts += [gt] * n
+            idx += [int(r.index or 0)] * n
+        if not decoded:
+            return {}
+        metrics, overrides = self.rubric_manager.step(decoded, gts, idx, k, training_step=step)
+        self.ground_truth_overrides.update({i: json.dumps(o) for i, o in overrides.items()})
+        return metrics
 
     # ------------------------------------------------------------------ loop / API
     def _run(self):
@@ -381,12 +431,19 @@ class DataPreparation:
         self.model_step = step
 
     def get_state(self) -> dict:
-        return {"prompts": self.prompts.state_dict(), "next_step": self.next_step, "total_prompts": self.total_prompts}
+        sd = {"prompts": self.prompts.state_dict(), "next_step": self.next_step, "total_prompts": self.total_prompts}
+        if self.rubric_manager is not None:
+            sd["rubric_buffer"] = self.rubric_manager.buffer.state_dict()
+            sd["ground_truth_overrides"] = dict(self.ground_truth_overrides)
+        return sd
 
     def set_state(self, sd: dict):
         self.prompts.load_state_dict(sd["prompts"])
         self.next_step = sd.get("next_step", 1)
         self.total_prompts = sd.get("total_prompts", 0)
+        if self.rubric_manager is not None and "rubric_buffer" in sd:
+            self.rubric_manager.buffer.load_state_dict(sd["rubric_buffer"])
+            self.ground_truth_overrides = {int(k): v for k, v in sd.get("ground_truth_overrides", {}).items()}
 
     def shutdown(self):
         self.stop.set()

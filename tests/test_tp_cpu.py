@@ -115,6 +115,41 @@ def test_evolving_rubric_step(tmp_path):
     assert "is correct" in calls[-2] or "is correct" in calls[-1]  # existing rubrics are shown to the judge
 
 
+def test_rubric_buffer_filter_and_reward_metrics():
+    """Zero-spread adaptive items retire, the cap keeps the items with the largest spread, persistent items stay; reward
+    metrics are split by item type (vectors computed by hand)."""
+    from open_instruct_b200.rubrics import RubricBuffer, rubric_key_stats, rubric_reward_metrics
+
+    buf = RubricBuffer(max_active_adaptive=4)
+    buf.add_persistent("p", ["is correct"])
+    buf.add_adaptive("p", [{"description": d, "weight": w, "title": d[:3]} for d, w in (("cites", 1.0), ("flat", 1.0), ("rambles", -1.0), ("short", 1.0))])
+    per_response = [
+        [{"description": "is correct", "weight": 1.0, "score": 1.0, "type": "persistent"}, {"description": "cites", "weight": 1.0, "score": 1.0, "type": "evolving"},
+         {"description": "flat", "weight": 1.0, "score": 0.5, "type": "evolving"}, {"description": "rambles", "weight": -1.0, "score": 0.0, "type": "evolving"},
+         {"description": "short", "weight": 1.0, "score": 0.4, "type": "evolving"}],
+        [{"description": "is correct", "weight": 1.0, "score": 0.0, "type": "persistent"}, {"description": "cites", "weight": 1.0, "score": 0.0, "type": "evolving"},
+         {"description": "flat", "weight": 1.0, "score": 0.5, "type": "evolving"}, {"description": "rambles", "weight": -1.0, "score": 1.0, "type": "evolving"},
+         {"description": "short", "weight": 1.0, "score": 0.6, "type": "evolving"}],
+    ]
+    m = rubric_reward_metrics(per_response)
+    assert m["evolving_rubrics/avg_persistent_reward"] == 0.5 and m["evolving_rubrics/std_persistent_reward"] == 0.5
+    assert abs(m["evolving_rubrics/avg_evolving_reward"] - (1.0 + 0.5 + 0.0 + 0.4 + 0.0 + 0.5 - 1.0 + 0.6) / 8) < 1e-12
+    stats = rubric_key_stats(["p", "p"], per_response)
+    assert stats[("p", "flat")] == {"mean": 0.5, "std": 0.0} and stats[("p", "cites")]["std"] == 0.5
+    moved = buf.filter(stats, max_active=2)
+    assert moved == {"zero_std": 1, "over_cap": 1}
+    assert [i.description for i in buf.items["p"]] == ["is correct", "cites", "rambles"]      # spread 0.5 each; "short" (0.1) went over the cap
+    assert sorted(i.description for i in buf.inactive["p"]) == ["flat", "short"]
+    buf.add_adaptive("p", [{"description": "flat", "weight": 1.0}])                              # a retired item is not proposed again
+    assert [i.description for i in buf.items["p"]] == ["is correct", "cites", "rambles"]
+    c = buf.counts()
+    assert c["evolving_rubrics/num_active_rubrics"] == 2 and c["evolving_rubrics/num_inactive_rubrics"] == 2
+    sd = buf.state_dict()
+    other = RubricBuffer()
+    other.load_state_dict(sd)
+    assert other.state_dict() == sd and other.spec_for("p", "q")["rubrics"][1]["type"] == "evolving"
+
+
 def test_native_packer_matches_python_collator():
     from open_instruct_b200.data import native_pack
     from open_instruct_b200.data.collate import flatten_examples
@@ -218,3 +253,44 @@ def test_tp_push_plan_reproduces_shard_flat():
     ref = [torch.zeros(loc.total) for _ in range(2)]
     apply_plan_reference(tp_push_plan(spec, 2, lo, hi), src, ref)
     assert all(torch.equal(a, b) for a, b in zip(dsts, ref))
+
+
+def test_evolving_rubrics_reach_the_prompts_of_later_steps(tmp_path):
+    """The data-preparation producer runs one evolving-rubric step per batch and queues later prompts with the updated rubric set
+    as their ground truth; the buffer travels with the producer's checkpoint state."""
+    import json
+    import queue
+
+    from open_instruct_b200.data_types import GenerationResult, RequestInfo
+    from open_instruct_b200.streaming import DataPreparation, StreamingDataLoaderConfig
+
+    async def judge(messages, **kw):
+        return json.dumps({"positive_rubrics": [{"description": "shows its work", "title": "work"}], "negative_rubrics": []})
+
+    gt = json.dumps({"query": "what is 2 + 2?", "rubrics": [{"description": "says 4", "weight": 1.0}]})
+    rows = [{"input_ids_prompt": [5, 6, 7], "index": i, "prompt": "what is 2 + 2?", "ground_truth": gt, "dataset": "rubric"} for i in range(2)]
+    cfg = StreamingDataLoaderConfig(num_unique_prompts_rollout=2, num_samples_per_prompt_rollout=2, async_steps=1, pack_length=64, response_length=8,
+                                    max_prompt_token_length=8, apply_evolving_rubric_reward=True, max_active_rubrics=3,
+                                    cache_evolving_rubric_data_dir=str(tmp_path), filter_zero_std_samples=False)
+    pq, rq = queue.Queue(), queue.Queue()
+    prep = DataPreparation(rows, cfg, pq, rq, tokenizer=None, dp_world=1, per_device_train_batch_size=1, seed=0, num_training_steps=2,
+                           rubric_judge=judge)
+    for i in range(2):
+        rq.put(GenerationResult(responses=[[8, 9], [10]], finish_reasons=["stop", "stop"], masks=[[1, 1], [1]], request_info=RequestInfo(),
+                                index=i, logprobs=[[-0.1, -0.2], [-0.3]], reward_scores=[1.0, 0.0], model_step=0, queries=[[5, 6, 7], [5, 6, 7]],
+                                decoded_responses=["four", "five"], ground_truth=[gt], dataset=["rubric"]))
+    assert prep.build_step(1)
+    m = prep.metrics[1]
+    assert m["evolving_rubrics/valid_rate"] == 1.0 and m["evolving_rubrics/num_new_rubrics"] == 1.0
+    assert set(prep.ground_truth_overrides) == {0, 1}
+    spec = json.loads(prep.ground_truth_overrides[0])
+    assert [r["description"] for r in spec["rubrics"]] == ["says 4", "shows its work"] and spec["rubrics"][1]["type"] == "evolving"
+    while not pq.empty():
+        pq.get()
+    prep.add_prompt()
+    assert json.loads(pq.get().ground_truth)["rubrics"][-1]["description"] == "shows its work"   # later prompts carry the evolved set
+    state = prep.get_state()
+    other = DataPreparation(rows, cfg, queue.Queue(), queue.Queue(), tokenizer=None, dp_world=1, per_device_train_batch_size=1, seed=0,
+                            num_training_steps=2, rubric_judge=judge)
+    other.set_state(json.loads(json.dumps(state)))
+    assert other.ground_truth_overrides == prep.ground_truth_overrides and other.rubric_manager.buffer.state_dict() == prep.rubric_manager.buffer.state_dict()
