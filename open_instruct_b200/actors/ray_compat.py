@@ -19,11 +19,13 @@ GPUs are handed out by the driver through ``CUDA_VISIBLE_DEVICES``.
 
 from __future__ import annotations
 
+import atexit
 import concurrent.futures as cf
 import multiprocessing as mp
 import os
 import pickle
 import queue as _queue
+import sys
 import tempfile
 import threading
 import time
@@ -48,15 +50,120 @@ _gpu_next = 0
 _pool = cf.ThreadPoolExecutor(max_workers=64, thread_name_prefix="actor-call")
 
 
+# ---------------------------------------------------------------------------------- wire format
+# Control messages travel as plain pickles on the socket.  Bulk payloads - the packed batches the data-preparation producer
+# hands to the learner ranks, weight vectors on CPU runs - would be copied through the socket in 64 KB pieces, so tensors
+# and numpy arrays of a message that together exceed ``B200_ACTOR_SHM_MIN_BYTES`` (1 MiB) leave the pickle stream (protocol
+# 5 out-of-band buffers) and go through ONE POSIX shared-memory segment: the sender writes them side by side, the socket
+# carries the segment's name and the layout, the receiver copies them out and unlinks the segment.
+_SHM_MAGIC = b"B2SHM1"
+_SHM_MIN = int(os.environ.get("B200_ACTOR_SHM_MIN_BYTES", str(1 << 20)))
+_shm_sent: list[str] = []   # the last segments this process created: swept at exit in case a receiver died first
+
+
+def _rebuild_tensor(buf, dtype_name: str, shape, pinned: bool):
+    import numpy as np
+    import torch
+
+    a = np.frombuffer(buf, dtype=np.uint8)
+    if not a.flags.writeable:
+        a = a.copy()
+    return torch.from_numpy(a).view(getattr(torch, dtype_name)).view(shape)
+
+
+class _BulkPickler(pickle.Pickler):
+    """Sends dense CPU tensors as out-of-band byte buffers (any dtype, bf16 included; non-contiguous ones are compacted)."""
+
+    def reducer_override(self, obj):
+        torch = sys.modules.get("torch")
+        if torch is not None and isinstance(obj, torch.Tensor) and type(obj) is torch.Tensor and obj.device.type == "cpu" \
+                and obj.layout == torch.strided and not obj.requires_grad and obj.numel() * obj.element_size() >= 4096:
+            flat = obj.detach().contiguous().view(-1).view(torch.uint8)
+            return _rebuild_tensor, (pickle.PickleBuffer(flat.numpy()), str(obj.dtype).replace("torch.", ""), tuple(obj.shape), False)
+        return NotImplemented
+
+
+def _dumps(obj) -> bytes:
+    import io
+
+    bufs: list[pickle.PickleBuffer] = []
+    f = io.BytesIO()
+    _BulkPickler(f, protocol=5, buffer_callback=bufs.append).dump(obj)
+    views = [b.raw() for b in bufs]
+    total = sum(v.nbytes for v in views)
+    if total < _SHM_MIN:
+        if not bufs:
+            return f.getvalue()
+        g = io.BytesIO()   # small payload: keep the buffers in band
+        _BulkPickler(g, protocol=5).dump(obj)
+        return g.getvalue()
+    from multiprocessing import resource_tracker, shared_memory
+
+    layout, off = [], 0
+    for v in views:
+        layout.append((off, v.nbytes))
+        off += -(-v.nbytes // 64) * 64
+    shm = shared_memory.SharedMemory(create=True, size=max(off, 1))
+    try:
+        for (o, n), v in zip(layout, views):
+            shm.buf[o:o + n] = v
+    finally:
+        name = shm.name
+        shm.close()
+    try:  # the receiver unlinks; this process's tracker must not try again at exit
+        resource_tracker.unregister("/" + name.lstrip("/"), "shared_memory")
+    except Exception:  # noqa: BLE001
+        pass
+    _shm_sent.append(name)
+    del _shm_sent[:-256]
+    return _SHM_MAGIC + pickle.dumps((name, layout, f.getvalue()), protocol=5)
+
+
+def _loads(raw: bytes):
+    if not raw.startswith(_SHM_MAGIC):
+        return pickle.loads(raw)
+    from multiprocessing import shared_memory
+
+    name, layout, data = pickle.loads(raw[len(_SHM_MAGIC):])
+    shm = shared_memory.SharedMemory(name=name)
+    try:
+        bufs = [bytearray(shm.buf[o:o + n]) for o, n in layout]   # the one copy on this side; the segment goes away below
+    finally:
+        shm.close()
+        try:
+            shm.unlink()
+        except FileNotFoundError:
+            pass
+    return pickle.loads(data, buffers=bufs)
+
+
+def _sweep_segments() -> None:
+    from multiprocessing import shared_memory
+
+    for name in _shm_sent:
+        try:
+            seg = shared_memory.SharedMemory(name=name)
+        except (FileNotFoundError, OSError):
+            continue
+        seg.close()
+        try:
+            seg.unlink()
+        except FileNotFoundError:
+            pass
+
+
+atexit.register(_sweep_segments)
+
+
 def _send(conn, obj) -> None:
-    """Plain pickle by value.  (``Connection.send`` would use multiprocessing's ForkingPickler, for which
-    torch registers shared-memory / file-descriptor passing of tensors - a second channel between the
-    processes that we neither need nor want for small control messages.)"""
-    conn.send_bytes(pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL))
+    """Pickle by value (bulk buffers through shared memory, see above).  (``Connection.send`` would use multiprocessing's
+    ForkingPickler, for which torch registers file-descriptor passing of tensors - a second channel between the processes
+    whose lifetime rules we do not want for messages that are consumed once.)"""
+    conn.send_bytes(_dumps(obj))
 
 
 def _recv(conn):
-    return pickle.loads(conn.recv_bytes())
+    return _loads(conn.recv_bytes())
 
 
 class ActorError(RuntimeError):

@@ -24,6 +24,9 @@ class Counter:
         q.put(item)
         return q.qsize()
 
+    def twice(self, t):
+        return {"out": t * 2, "n": t.numel()}
+
 
 def test_actor_calls_and_errors():
     from open_instruct_b200.actors import ray_compat as ray
@@ -54,3 +57,49 @@ def test_actor_calls_and_errors():
             ray.get(a.add.remote(1), timeout=5)
     finally:
         ray.shutdown()
+
+
+def test_bulk_payloads_go_through_shared_memory():
+    """Tensors and arrays above the threshold leave the pickle stream and cross in one shared-memory segment that the receiver
+    unlinks; small messages stay plain pickles; values, dtypes (bf16 included), shapes and non-contiguous views survive."""
+    import glob
+    import pickle
+
+    import numpy as np
+    import torch
+
+    from open_instruct_b200.actors import ray_compat as rc
+
+    small = {"a": torch.arange(10), "s": "text", "n": np.arange(5)}
+    raw = rc._dumps(small)
+    assert not raw.startswith(rc._SHM_MAGIC)
+    back = rc._loads(raw)
+    assert torch.equal(back["a"], small["a"]) and back["s"] == "text" and (back["n"] == small["n"]).all()
+    big = {"ids": torch.randint(0, 1000, (64, 4096)), "w": torch.randn(300, 700).bfloat16(), "view": torch.randn(512, 512)[:, ::2],
+           "arr": np.random.rand(200_000), "nested": [torch.ones(3), ("x", torch.full((70_000,), 2.5))], "scalar": 7}
+    before = set(glob.glob("/dev/shm/psm_*"))
+    raw = rc._dumps(big)
+    assert raw.startswith(rc._SHM_MAGIC) and len(raw) < 20_000          # only names, layout and the pickle skeleton travel on the socket
+    name, layout, _ = pickle.loads(raw[len(rc._SHM_MAGIC):])
+    assert len(set(glob.glob("/dev/shm/psm_*")) - before) == 1 and sum(n for _, n in layout) > 3_000_000
+    back = rc._loads(raw)
+    assert set(glob.glob("/dev/shm/psm_*")) - before == set()                 # the receiver removed the segment
+    assert torch.equal(back["ids"], big["ids"]) and back["w"].dtype == torch.bfloat16 and torch.equal(back["w"], big["w"])
+    assert torch.equal(back["view"], big["view"]) and back["view"].is_contiguous()
+    assert (back["arr"] == big["arr"]).all() and torch.equal(back["nested"][1][1], big["nested"][1][1]) and back["scalar"] == 7
+    back["ids"][0, 0] = -1                                                     # received tensors own writable memory
+    assert back["ids"][0, 0] == -1
+
+
+def test_actor_call_with_a_bulk_argument_and_result():
+    import torch
+
+    from open_instruct_b200.actors import ray_compat as rc
+
+    h = rc.remote(Counter).remote()
+    try:
+        x = torch.randn(1024, 1024)   # 4 MiB each way
+        res = rc.get(h.twice.remote(x))
+        assert res["n"] == x.numel() and torch.equal(res["out"], x * 2)
+    finally:
+        rc.kill(h)
