@@ -58,6 +58,16 @@ _pool = cf.ThreadPoolExecutor(max_workers=64, thread_name_prefix="actor-call")
 # carries the segment's name and the layout, the receiver copies them out and unlinks the segment.
 _SHM_MAGIC = b"B2SHM1"
 _SHM_MIN = int(os.environ.get("B200_ACTOR_SHM_MIN_BYTES", str(1 << 20)))
+_SHM_MAX = int(os.environ.get("B200_ACTOR_SHM_MAX_BYTES", str(2 << 30)))   # larger payloads (whole models) keep to the socket
+
+
+def _shm_has_room(nbytes: int) -> bool:
+    """A segment is only created when /dev/shm can hold twice its size: running the tmpfs full ends in SIGBUS, not in an error."""
+    try:
+        st = os.statvfs("/dev/shm")
+    except OSError:
+        return False
+    return st.f_bavail * st.f_frsize >= 2 * nbytes
 _shm_sent: list[str] = []   # the last segments this process created: swept at exit in case a receiver died first
 
 
@@ -91,10 +101,10 @@ def _dumps(obj) -> bytes:
     _BulkPickler(f, protocol=5, buffer_callback=bufs.append).dump(obj)
     views = [b.raw() for b in bufs]
     total = sum(v.nbytes for v in views)
-    if total < _SHM_MIN:
+    if total < _SHM_MIN or total > _SHM_MAX or not _shm_has_room(total):
         if not bufs:
             return f.getvalue()
-        g = io.BytesIO()   # small payload: keep the buffers in band
+        g = io.BytesIO()   # small (or far too large) payload: keep the buffers in band
         _BulkPickler(g, protocol=5).dump(obj)
         return g.getvalue()
     from multiprocessing import resource_tracker, shared_memory

@@ -185,7 +185,9 @@ class TrainTP:
         """Sum ``t`` over the tensor-parallel group, in place.  bf16 ``[tokens, hidden]`` activations on a GPU go through the
         one-shot kernel the rollout engine uses (every rank stores its partial in a symmetric buffer, exchanges one flag and
         adds all ranks' slots with 16-byte peer loads in rank order: the same bits on every rank, one kernel instead of a
-        library ring); everything else, and ``B200_TP_FUSED_ALLREDUCE=0``, through ``torch.distributed``."""
+        library ring) when ``B200_TP_FUSED_ALLREDUCE=1``; everything else through ``torch.distributed``.  The fused route is
+        opt-in: it was written after the last multi-GPU run of this build and has only been exercised on CPU (where it is
+        not taken)."""
         ctx = self._fused_ctx(t)
         if ctx is None:
             dist.all_reduce(t, group=self.group)
@@ -201,7 +203,7 @@ class TrainTP:
         import os
 
         if (not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or not t.is_contiguous() or self.world < 2 or self.world > 8
-                or t.shape[1] % 128 or t.shape[1] > 8192 or os.environ.get("B200_TP_FUSED_ALLREDUCE", "1") == "0"):
+                or t.shape[1] % 128 or t.shape[1] > 8192 or os.environ.get("B200_TP_FUSED_ALLREDUCE", "0") != "1"):
             return None
         ctxs = self.__dict__.setdefault("_ctxs", {})
         D = t.shape[1]

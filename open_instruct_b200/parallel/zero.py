@@ -105,8 +105,13 @@ class ZeroOptimizer:
                 self.v = torch.zeros_like(self.master)
         self.grad_shard = torch.zeros(self.shard, dtype=torch.float32, device=flat.device) if self.world > 1 else None
         self._stage = None
-        # start reducing a layer's gradients as soon as the last micro-batch's backward has produced them
-        self.overlap = os.environ.get("B200_OVERLAP_GRADS", "1") != "0"
+        # B200_OVERLAP_GRADS=1: start reducing a layer's gradients as soon as the last micro-batch's backward has produced them.
+        # Off by default.  Measured at 8B: on 2 GPUs the optimizer step shrinks from 66.9 to 38.8 ms but the backward slows by
+        # as much (the step is power-capped and the reduce kernel's CTAs cannot share an SM with the weight-gradient GEMM's:
+        # 136 x 256 + 255 x 192 registers exceed the file), step time unchanged; on 8 GPUs the per-layer reductions wait on the
+        # slowest of eight backwards each time and the step got SLOWER (3307 ms, optimizer step 325 ms, against about 3200 / 180
+        # without overlap).  The exchange after the backward costs 42 + 21 ms at 8 GPUs (0.86 / 0.85 of the link rate).
+        self.overlap = os.environ.get("B200_OVERLAP_GRADS", "0") == "1"
         self.step_count = 0
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._gscale = torch.ones(1, dtype=torch.float32, device=self.device)

@@ -45,14 +45,18 @@ def main():
     base = dict(learning_rate=1e-3, lr_scheduler_type="constant", max_grad_norm=1.0, weight_decay=0.01, seed=7,
                 ops="fused" if cuda else "ref")
     flats = {}
-    for comm in args.comms.split(","):
+    for name in args.comms.split(","):
+        comm = name.split("+")[0]
+        # "fused+overlap": the gradient exchange starts under the last micro-batch's backward (opt-in, read when the optimizer is built)
+        os.environ["B200_OVERLAP_GRADS"] = "1" if name.endswith("+overlap") else "0"
         lr_ = Learner(spec, LearnerConfig(comm=comm, **base), device=device)
+        os.environ.pop("B200_OVERLAP_GRADS", None)
         outs = run(lr_, [rank], args.steps, device, spec, seq)
         if cuda:
             from open_instruct_b200.ops import lib
 
             lib.check_status()
-        flats[comm] = (lr_.model.flat.detach().float().cpu().clone(), float(outs[-1]["grad_norm"].item()))
+        flats[name] = (lr_.model.flat.detach().float().cpu().clone(), float(outs[-1]["grad_norm"].item()))
         del lr_
     names = list(flats)
     for other in names[1:]:

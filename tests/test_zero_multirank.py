@@ -31,4 +31,4 @@ def test_gloo_ranks_match_single_process(world):
 def test_fused_comm_matches_nccl_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    _launch(2, ["--device", "cuda", "--comms", "nccl,fused"], free_port(), env={"NCCL_NVLS_ENABLE": "0"})
+    _launch(2, ["--device", "cuda", "--comms", "nccl,fused,fused+overlap"], free_port(), env={"NCCL_NVLS_ENABLE": "0"})
