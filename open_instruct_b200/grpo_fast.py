@@ -322,11 +322,10 @@ class EngineWorker:
                                 timeout=datetime.timedelta(seconds=600), device_id=dev)
         self._tp_cmd_group = dist.new_group(backend="gloo")
         ls = local_spec(spec, self.tp_size)
-        if flat is None:
-            raise ValueError("a tensor-parallel engine needs the initial weights")
         self.full_flat = None  # a full-size staging copy exists only while a host-supplied update is applied (CPU path)
         self._tp_spec = spec
-        local = shard_flat(flat, spec, self.tp_rank, self.tp_size)
+        # without initial weights the shard starts random: the driver pushes the learners' weights before any prompt is queued
+        local = shard_flat(flat, spec, self.tp_rank, self.tp_size) if flat is not None else None
         tp = TPContext(spec.hidden_size, max(4096, max_model_len), dev)
         if num_blocks is None:
             free, total = torch.cuda.mem_get_info(dev)
@@ -482,12 +481,13 @@ class EngineWorker:
                 return
             if self.full_flat is None:
                 self.full_flat = torch.empty(ParamLayoutTotal(self._tp_spec), dtype=self.engine.model.flat.dtype, device=self.engine.device)
+            n = min(flat.numel(), self.full_flat.numel())  # the sender's buffer may carry padding for its world size
             if self.tp_rank == 0:  # followers reshard when the leader's command reaches them, at the same point of the schedule
-                self.full_flat[: flat.numel()].copy_(flat.to(self.full_flat.dtype))
+                self.full_flat[:n].copy_(flat[:n].to(self.full_flat.dtype))
                 self.engine.send([("reshard", model_step)])
                 self._reshard(model_step)
             else:
-                self.full_flat[: flat.numel()].copy_(flat.to(self.full_flat.dtype))
+                self.full_flat[:n].copy_(flat[:n].to(self.full_flat.dtype))
             return
         if flat is not None:
             self.engine.update_weights(flat, model_step)
@@ -989,6 +989,7 @@ class GRPORun:
         per_step = streaming.num_unique_prompts_rollout * streaming.num_samples_per_prompt_rollout
         qsize = (streaming.async_steps + 1) * streaming.num_unique_prompts_rollout
         last: dict = {}
+        init_by_push = False
 
         if single:
             prompt_q, results_q, eval_q = ray.Queue(local=True), ray.Queue(maxsize=qsize, local=True), ray.Queue(local=True)
@@ -1016,7 +1017,12 @@ class GRPORun:
                                   spec, args, model_config, args.num_training_steps, None if cuda else "cpu")
                         for r in range(args.world_size)]
                 learners = [f.result() for f in futs]
-            init_flat = ray.get(learners[0].flat_weights_cpu.remote())
+            # On GPUs the engines start with random weights and receive the learners' through the first weight sync (the same
+            # push kernel as every later one) instead of a by-value copy of the whole model in every engine process: for 8B that
+            # copy is 16 GB pickled once per engine rank, all at the same time - with 4 engine ranks more than 200 GB of host
+            # memory in flight, the likely reason an 8-GPU run (4 learners + 2 engines x 2 ranks) never reached its first step.
+            init_by_push = (cuda and os.environ.get("B200_GRPO_INIT_BY_PUSH", "1") == "1") or os.environ.get("B200_GRPO_INIT_BY_PUSH") == "force"
+            init_flat = None if init_by_push else ray.get(learners[0].flat_weights_cpu.remote())
             tp = vllm.vllm_tensor_parallel_size if cuda else 1
             followers = []
             if tp == 1:
@@ -1064,6 +1070,12 @@ class GRPORun:
         self.last: dict = {}
         self.ref_update_in_step = True  # False: a callback of the driver updates the reference policy after the step
         self._closed = False
+        if init_by_push:
+            self.weight_sync(0)  # the engines' first weights
+            if args.verify_weight_sync:
+                diff = self._checksum_diff(0)
+                if not diff <= 1e-3:
+                    raise RuntimeError(f"engines did not receive the learners' initial weights (checksum difference {diff})")
 
     # ------------------------------------------------------------------ actor calls
     def call(self, obj, method, *a):
@@ -1135,6 +1147,14 @@ class GRPORun:
         self._t_step = t_step
         return self.last
 
+    def _checksum_diff(self, step: int) -> float:
+        """Largest difference between an engine rank's weight checksum and the learner's checksum of the same shard."""
+        err = 0.0
+        for h in list(self.engines) + list(self.followers):
+            got, r, n = self.call(h, "weights_checksum", step)
+            err = max(err, abs(got - self.call(self.learners[0], "weights_checksum", r, n)))
+        return err
+
     def sync_step(self, step: int) -> float:
         """Pause the engines, push the new weights, (optionally) compare checksums, resume."""
         args = self.args
@@ -1144,11 +1164,7 @@ class GRPORun:
         if t_sync > WEIGHT_SYNC_TIMEOUT_S:
             raise TimeoutError("weight sync exceeded its time limit")
         if args.verify_weight_sync and not self.single_objs:
-            sync_err = 0.0
-            for h in list(self.engines) + list(self.followers):
-                got, r, n = self.call(h, "weights_checksum", step)
-                sync_err = max(sync_err, abs(got - self.call(self.learners[0], "weights_checksum", r, n)))
-            self.last["debug/weight_sync_checksum_diff"] = sync_err
+            self.last["debug/weight_sync_checksum_diff"] = self._checksum_diff(step)
         self.call_all(self.engines, "set_should_stop", False)
         self.manager.set_should_stop(False)
         self.prep.set_model_step(step)

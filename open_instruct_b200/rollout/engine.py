@@ -232,7 +232,8 @@ class RolloutEngine:
     def update_weights(self, flat: torch.Tensor, model_step: int | None = None) -> None:
         """Replace the weights (same flat layout) between steps; cached KV of running sequences stays."""
         with torch.no_grad():
-            self.model.flat[: flat.numel()].copy_(flat.to(self.model.flat.dtype), non_blocking=True)
+            n = min(flat.numel(), self.model.flat.numel())  # the two buffers may be padded for different world sizes
+            self.model.flat[:n].copy_(flat[:n].to(self.model.flat.dtype), non_blocking=True)
         if model_step is not None:
             self.model_step = model_step
 

@@ -3,6 +3,8 @@
 import json
 import os
 
+import pytest
+
 import torch
 
 from helpers import make_rlvr_jsonl, make_tokenizer
@@ -107,8 +109,12 @@ def test_grpo_train_step_label_space_matches_token_space():
         assert abs(m0[k] - m1[k]) < 1e-5 * max(1.0, abs(m0[k])), (k, m0[k], m1[k])
 
 
-def test_grpo_multi_process_actors(tmp_path):
-    """Two learner processes (gloo) + one engine process + cross-process queues, CPU."""
+@pytest.mark.parametrize("init", ["by_value", "by_first_sync"])
+def test_grpo_multi_process_actors(tmp_path, init, monkeypatch):
+    """Two learner processes (gloo) + one engine process + cross-process queues, CPU.  ``by_first_sync``: the engine starts with
+    random weights and gets the learners' through the first weight sync (the GPU default), checked against the learner's checksum."""
+    if init == "by_first_sync":
+        monkeypatch.setenv("B200_GRPO_INIT_BY_PUSH", "force")
     from open_instruct_b200.actors import ray_compat as ray
     from open_instruct_b200.config.schemas import ModelConfig
     from open_instruct_b200.data.tokenize import TokenizerConfig
@@ -121,7 +127,8 @@ def test_grpo_multi_process_actors(tmp_path):
     tok = make_tokenizer(os.path.join(tmp, "tok"))
     data = make_rlvr_jsonl(os.path.join(tmp, "rl.jsonl"), n=12)
     args = GRPOExperimentConfig(total_episodes=2 * 4 * 4, learning_rate=1e-3, beta=0.0, load_ref_policy=False, output_dir=os.path.join(tmp, "out"),
-                                num_learners_per_node=[2], ops="ref", seed=3, save_freq=-1, lr_scheduler_type="constant")
+                                num_learners_per_node=[2], ops="ref", seed=3, save_freq=-1, lr_scheduler_type="constant",
+                                verify_weight_sync=True)
     streaming = StreamingDataLoaderConfig(max_prompt_token_length=64, response_length=8, pack_length=128, async_steps=1,
                                           num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=4, dataset_mixer_list=[data, "1.0"],
                                           dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False)
