@@ -186,8 +186,7 @@ class TrainTP:
         one-shot kernel the rollout engine uses (every rank stores its partial in a symmetric buffer, exchanges one flag and
         adds all ranks' slots with 16-byte peer loads in rank order: the same bits on every rank, one kernel instead of a
         library ring) when ``B200_TP_FUSED_ALLREDUCE=1``; everything else through ``torch.distributed``.  The fused route is
-        opt-in: it was written after the last multi-GPU run of this build and has only been exercised on CPU (where it is
-        not taken)."""
+        opt-in: it has not run on GPUs yet (on CPU it is never taken)."""
         ctx = self._fused_ctx(t)
         if ctx is None:
             dist.all_reduce(t, group=self.group)
