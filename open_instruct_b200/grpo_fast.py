@@ -249,10 +249,12 @@ class EngineWorker:
     def __init__(self, spec, prompt_queue, results_queue, eval_queue, reward_config: RewardConfig | None, tokenizer=None,
                  device="cuda", ops: str = "auto", seed: int = 0, max_model_len: int = 8192, num_blocks: int | None = None,
                  gpu_memory_utilization: float = 0.85, flat: torch.Tensor | None = None, inflight_updates: bool = True,
-                 max_running: int = 256, envs_config=None, tp_rank: int = 0, tp_size: int = 1, tp_addr: str = "127.0.0.1", tp_port: int = 0):
+                 max_running: int = 256, envs_config=None, tp_rank: int = 0, tp_size: int = 1, tp_addr: str = "127.0.0.1", tp_port: int = 0,
+                 enable_prefix_caching: bool = False):
         from .rollout.engine import RolloutEngine
 
         self.tp_rank, self.tp_size = tp_rank, tp_size
+        self._prefix_caching = bool(enable_prefix_caching)
         if isinstance(tokenizer, TokenizerConfig):  # built in the worker's own process
             tokenizer = tokenizer.tokenizer
         if device == "auto":
@@ -271,7 +273,7 @@ class EngineWorker:
         else:
             self.engine = RolloutEngine(spec, device=device, ops=ops, seed=seed, max_model_len=max_model_len, num_blocks=num_blocks,
                                         gpu_memory_utilization=gpu_memory_utilization, flat=flat, tokenizer=tokenizer,
-                                        max_running=max_running)
+                                        max_running=max_running, enable_prefix_caching=self._prefix_caching)
         self.prompt_q, self.results_q, self.eval_q = prompt_queue, results_queue, eval_queue
         self.reward_fn = reward_config.build() if reward_config is not None else None
         self.tokenizer = tokenizer
@@ -334,7 +336,7 @@ class EngineWorker:
             dist.all_reduce(n, op=dist.ReduceOp.MIN)  # every rank must see the same number of KV blocks: same schedule
             num_blocks = int(n.item())
         eng = RolloutEngine(ls, device=dev, ops=ops, seed=seed, max_model_len=max_model_len, num_blocks=num_blocks, flat=local, tokenizer=tokenizer,
-                            max_running=max_running, tp=tp)
+                            max_running=max_running, tp=tp, enable_prefix_caching=self._prefix_caching)
         return _TPLeader(eng, self._tp_cmd_group) if self.tp_rank == 0 else eng
 
     def _reshard(self, model_step: int) -> None:
@@ -342,6 +344,7 @@ class EngineWorker:
 
         shard_flat(self.full_flat, self._tp_spec, self.tp_rank, self.tp_size, out=self.engine.model.flat.detach())
         self.engine.model_step = model_step
+        self.engine.reset_prefix_cache()  # every rank, at the same point of the command stream: the schedules stay identical
 
     def _follow(self) -> None:
         """Ranks > 0 of a tensor-parallel engine: apply the leader's command batches in order."""
@@ -366,6 +369,7 @@ class EngineWorker:
                         dist.barrier(group=self._tp_cmd_group)
                     elif cmd[0] == "set_step":
                         self.engine.model_step = cmd[1]
+                        self.engine.reset_prefix_cache()
                     elif cmd[0] == "stop":
                         self.shutdown_flag.set()
         except BaseException as e:  # noqa: BLE001
@@ -478,6 +482,7 @@ class EngineWorker:
                 if self.tp_rank == 0:
                     self.engine.send([("set_step", model_step)])
                     self.engine._e.model_step = model_step
+                    self.engine._e.reset_prefix_cache()
                 return
             if self.full_flat is None:
                 self.full_flat = torch.empty(ParamLayoutTotal(self._tp_spec), dtype=self.engine.model.flat.dtype, device=self.engine.device)
@@ -493,6 +498,7 @@ class EngineWorker:
             self.engine.update_weights(flat, model_step)
         else:
             self.engine.model_step = model_step
+            self.engine.reset_prefix_cache()  # K/V cached for later requests belong to the old weights
 
     def weights_checksum(self, expect_step: int | None = None) -> tuple[float, int, int]:
         """(sum of the weights this rank computes with, tp rank, tp size) - compared with the learner's after a sync.
@@ -999,7 +1005,8 @@ class GRPORun:
             engine = EngineWorker(spec, prompt_q, results_q, eval_q, reward_cfg, tokenizer, device=device, ops=args.ops, seed=args.seed,
                                   max_model_len=max_len, num_blocks=None if torch.cuda.is_available() else 512,
                                   gpu_memory_utilization=0.25 if torch.cuda.is_available() else 0.9,
-                                  flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates, envs_config=tools_config)
+                                  flat=learner.flat_weights().clone(), inflight_updates=streaming.inflight_updates, envs_config=tools_config,
+                                  enable_prefix_caching=vllm.vllm_enable_prefix_caching)
             learners, engines = [learner], [engine]
             single_objs = True
         else:
@@ -1028,7 +1035,8 @@ class GRPORun:
             if tp == 1:
                 engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
                     spec, prompt_q, results_q, eval_q, reward_cfg, tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len,
-                    None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates, 256, tools_config)
+                    None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat, streaming.inflight_updates, 256, tools_config,
+                    enable_prefix_caching=vllm.vllm_enable_prefix_caching)
                     for i in range(vllm.vllm_num_engines)]
             else:
                 # every rank of a tensor-parallel engine is its own process on its own GPU; the ranks of one engine rendezvous in
@@ -1037,7 +1045,8 @@ class GRPORun:
                 with ThreadPoolExecutor(max_workers=tp * vllm.vllm_num_engines) as ex:
                     futs = [[ex.submit(EW.options(num_gpus=1, max_concurrency=8).remote, spec, prompt_q, results_q, eval_q, reward_cfg if r == 0 else None,
                                        tc_plain, "auto", args.ops, args.seed + 100 * i, max_len, None, vllm.vllm_gpu_memory_utilization, init_flat,
-                                       streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", tp_ports[i])
+                                       streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", tp_ports[i],
+                                       enable_prefix_caching=vllm.vllm_enable_prefix_caching)
                              for r in range(tp)] for i in range(vllm.vllm_num_engines)]
                     handles = [[f.result() for f in row] for row in futs]
                 engines = [row[0] for row in handles]

@@ -14,6 +14,7 @@
 #include <cstring>
 #include <deque>
 #include <fstream>
+#include <list>
 #include <mutex>
 #include <sstream>
 #include <string>
@@ -34,6 +35,8 @@ struct Seq {
   bool running = false;
   bool needs_prefill = true;
   int64_t arrival = 0;
+  std::vector<int> tokens;    // prompt token ids (prefix cache only)
+  int cached_tokens = 0;      // tokens at the start of the sequence whose K/V were found in the prefix cache at admission
 };
 
 struct Engine {
@@ -51,15 +54,105 @@ struct Engine {
   int64_t preemptions = 0;
   std::mutex mu;
 
+  // ---- prefix cache: full blocks keep their content after their last user is gone.  A block is identified by the chain
+  // hash of all tokens up to and including its own (so equal hashes mean equal PREFIXES), verified against the stored
+  // parent hash and token ids on every hit; unreferenced cached blocks wait in an LRU list and are taken back only when
+  // the free list is empty.
+  bool prefix_cache = false;
+  std::vector<uint64_t> block_hash;              // 0 = not cached
+  std::vector<uint64_t> block_parent;
+  std::vector<std::vector<int>> block_tokens;
+  std::unordered_map<uint64_t, int> cached;      // chain hash -> block
+  std::list<int> evictable;                      // cached blocks with no user, least recently released first
+  std::unordered_map<int, std::list<int>::iterator> ev_pos;
+  int64_t cache_queries = 0, cache_hits = 0, cache_evictions = 0;   // in blocks
+
+  static uint64_t chain_hash(uint64_t parent, const int* tok, int n) {
+    uint64_t h = 1469598103934665603ull ^ (parent * 0x9E3779B97F4A7C15ull);
+    for (int i = 0; i < n; ++i) {
+      h ^= static_cast<uint32_t>(tok[i]);
+      h *= 1099511628211ull;
+    }
+    return h ? h : 1;
+  }
+  void uncache(int b) {
+    auto it = cached.find(block_hash[b]);
+    if (it != cached.end() && it->second == b) cached.erase(it);
+    block_hash[b] = 0;
+    block_tokens[b].clear();
+  }
   int alloc_block() {
-    if (free_list.empty()) return -1;
-    int b = free_list.back();
-    free_list.pop_back();
+    int b;
+    if (!free_list.empty()) {
+      b = free_list.back();
+      free_list.pop_back();
+    } else if (!evictable.empty()) {
+      b = evictable.front();
+      evictable.pop_front();
+      ev_pos.erase(b);
+      uncache(b);
+      cache_evictions++;
+    } else {
+      return -1;
+    }
     refcnt[b] = 1;
     return b;
   }
+  int available_blocks() const { return static_cast<int>(free_list.size() + evictable.size()); }
   void release_block(int b) {
-    if (--refcnt[b] == 0) free_list.push_back(b);
+    if (--refcnt[b] != 0) return;
+    if (prefix_cache && block_hash[b] != 0) {
+      evictable.push_back(b);
+      ev_pos[b] = std::prev(evictable.end());
+    } else {
+      free_list.push_back(b);
+    }
+  }
+  // one more user of a cached block (it may have been waiting in the LRU list)
+  void retain_cached(int b) {
+    if (refcnt[b]++ == 0) {
+      auto it = ev_pos.find(b);
+      if (it != ev_pos.end()) {
+        evictable.erase(it->second);
+        ev_pos.erase(it);
+      }
+    }
+  }
+  // Blocks of the longest cached prefix of `tok` (whole blocks only, at most `max_blocks`).
+  std::vector<int> lookup_prefix(const std::vector<int>& tok, int max_blocks) {
+    std::vector<int> out;
+    uint64_t parent = 0;
+    for (int i = 0; i < max_blocks; ++i) {
+      const int* t = tok.data() + static_cast<size_t>(i) * block_size;
+      const uint64_t h = chain_hash(parent, t, block_size);
+      cache_queries++;
+      auto it = cached.find(h);
+      if (it == cached.end()) break;
+      const int b = it->second;
+      if (block_parent[b] != parent || !std::equal(block_tokens[b].begin(), block_tokens[b].end(), t)) break;  // hash collision
+      out.push_back(b);
+      parent = h;
+    }
+    cache_hits += static_cast<int64_t>(out.size());
+    return out;
+  }
+  // The first `n_tokens` tokens of `s` have their K/V in `s.blocks`: make its full blocks findable.
+  void publish_blocks(const Seq& s, const int* tok, int n_tokens) {
+    if (!prefix_cache) return;
+    const int full = std::min<int>(n_tokens / block_size, static_cast<int>(s.blocks.size()));
+    uint64_t parent = 0;
+    for (int i = 0; i < full; ++i) {
+      const int* t = tok + static_cast<size_t>(i) * block_size;
+      const uint64_t h = chain_hash(parent, t, block_size);
+      const int b = s.blocks[i];
+      if (block_hash[b] == 0 && cached.find(h) == cached.end()) {
+        block_hash[b] = h;
+        block_parent[b] = parent;
+        block_tokens[b].assign(t, t + block_size);
+        cached.emplace(h, b);
+      }
+      parent = h;
+    }
   }
   int blocks_needed(int tokens) const { return (tokens + block_size - 1) / block_size; }
 
@@ -88,6 +181,9 @@ void* b200_engine_create(int num_blocks, int block_size, int max_running) {
   e->block_size = block_size;
   e->max_running = max_running;
   e->refcnt.assign(num_blocks, 0);
+  e->block_hash.assign(num_blocks, 0);
+  e->block_parent.assign(num_blocks, 0);
+  e->block_tokens.resize(num_blocks);
   e->free_list.reserve(num_blocks);
   for (int i = num_blocks - 1; i >= 0; --i) e->free_list.push_back(i);
   return e;
@@ -98,8 +194,69 @@ void b200_engine_destroy(void* h) { delete static_cast<Engine*>(h); }
 int b200_engine_free_blocks(void* h) {
   auto* e = static_cast<Engine*>(h);
   std::lock_guard<std::mutex> g(e->mu);
-  return static_cast<int>(e->free_list.size());
+  return e->available_blocks();
 }
+
+// Prefix cache on / off (off also forgets everything cached).
+int b200_engine_enable_prefix_cache(void* h, int on) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  e->prefix_cache = on != 0;
+  if (!on) {
+    for (int b : e->evictable) { e->uncache(b); e->free_list.push_back(b); }
+    e->evictable.clear();
+    e->ev_pos.clear();
+    for (size_t b = 0; b < e->block_hash.size(); ++b)
+      if (e->block_hash[b]) e->uncache(static_cast<int>(b));
+  }
+  return 0;
+}
+
+// Forget every cached prefix (after a weight update: K/V computed with older weights must not serve new requests).
+// Blocks in use stay with their users and return to the free list when released.
+int b200_engine_reset_prefix_cache(void* h) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  for (int b : e->evictable) { e->uncache(b); e->free_list.push_back(b); }
+  e->evictable.clear();
+  e->ev_pos.clear();
+  for (size_t b = 0; b < e->block_hash.size(); ++b)
+    if (e->block_hash[b]) e->uncache(static_cast<int>(b));
+  return 0;
+}
+
+// out[0..2] = block lookups, block hits, evictions since creation; out[3] = cached blocks now
+int b200_engine_prefix_cache_stats(void* h, int64_t* out) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  out[0] = e->cache_queries;
+  out[1] = e->cache_hits;
+  out[2] = e->cache_evictions;
+  out[3] = static_cast<int64_t>(e->cached.size());
+  return 0;
+}
+
+// Prompt token ids of a queued sequence (needed for prefix-cache lookups; call right after b200_engine_add).
+int b200_engine_set_tokens(void* h, int64_t seq_id, const int* tokens, int n) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  auto it = e->seqs.find(seq_id);
+  if (it == e->seqs.end()) return -1;
+  it->second.tokens.assign(tokens, tokens + n);
+  return 0;
+}
+
+// Tokens at the start of the sequence that need no prompt pass (their K/V came from the prefix cache at admission).
+int b200_engine_cached_tokens(void* h, int64_t seq_id) {
+  auto* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> g(e->mu);
+  auto it = e->seqs.find(seq_id);
+  return it == e->seqs.end() ? -1 : it->second.cached_tokens;
+}
+
+// A sequence is done and `tokens[0..n)` is everything it holds (prompt + generated): the full blocks whose K/V were
+// written (all but the last sampled token) become findable, then the sequence is removed like b200_engine_finish.
+int b200_engine_finish_tokens(void* h, int64_t seq_id, const int* tokens, int n);
 
 int64_t b200_engine_preemptions(void* h) {
   auto* e = static_cast<Engine*>(h);
@@ -139,6 +296,18 @@ int b200_engine_finish(void* h, int64_t seq_id) {
   e->drop_group_ref(s.group);
   e->seqs.erase(it);
   return 0;
+}
+
+int b200_engine_finish_tokens(void* h, int64_t seq_id, const int* tokens, int n) {
+  {
+    auto* e = static_cast<Engine*>(h);
+    std::lock_guard<std::mutex> g(e->mu);
+    auto it = e->seqs.find(seq_id);
+    if (it == e->seqs.end()) return -1;
+    const Seq& s = it->second;
+    if (s.running && !s.needs_prefill && n > 1) e->publish_blocks(s, tokens, std::min(n, s.len) - 1);
+  }
+  return b200_engine_finish(h, seq_id);
 }
 
 // One scheduling step.
@@ -205,11 +374,23 @@ int b200_engine_schedule(void* h, int64_t* prefill_ids, int* n_prefill, int64_t*
     auto shared = e->group_prompt_blocks.find(s.group);
     const bool can_share = shared != e->group_prompt_blocks.end() && s.len == s.prompt_len;
     const int total_needed = e->blocks_needed(s.len + 1);
-    const int fresh = can_share ? total_needed - full_prompt_blocks : total_needed;
-    if (fresh > static_cast<int>(e->free_list.size())) break;
+    std::vector<int> hit;
+    if (e->prefix_cache && !can_share && !s.tokens.empty()) {
+      // whole blocks of the prompt, leaving at least one token to compute (its logits start the generation)
+      const int known = std::min<int>(static_cast<int>(s.tokens.size()), s.len);
+      hit = e->lookup_prefix(s.tokens, std::max(0, (known - 1) / e->block_size));
+    }
+    const int fresh = can_share ? total_needed - full_prompt_blocks : total_needed - static_cast<int>(hit.size());
+    int hit_waiting = 0;  // hit blocks that sit in the LRU list are not available as fresh blocks
+    for (int b : hit) hit_waiting += e->refcnt[b] == 0;
+    if (fresh > e->available_blocks() - hit_waiting) break;
     s.blocks.clear();
+    s.cached_tokens = 0;
     if (can_share) {
       for (int b : shared->second) { e->refcnt[b]++; s.blocks.push_back(b); }
+    } else {
+      for (int b : hit) { e->retain_cached(b); s.blocks.push_back(b); }
+      s.cached_tokens = static_cast<int>(hit.size()) * e->block_size;
     }
     while (static_cast<int>(s.blocks.size()) < total_needed) s.blocks.push_back(e->alloc_block());
     if (!can_share && s.len == s.prompt_len && full_prompt_blocks > 0 && e->group_users[s.group] > 1) {
@@ -232,9 +413,12 @@ int b200_engine_advance(void* h, int64_t seq_id, int new_tokens) {
   std::lock_guard<std::mutex> g(e->mu);
   auto it = e->seqs.find(seq_id);
   if (it == e->seqs.end()) return -1;
-  it->second.len += new_tokens;
-  it->second.needs_prefill = false;
-  return it->second.len;
+  Seq& s = it->second;
+  if (s.needs_prefill && !s.tokens.empty())  // the prompt pass has written these K/V: later requests may start from them
+    e->publish_blocks(s, s.tokens.data(), std::min<int>(static_cast<int>(s.tokens.size()), s.len));
+  s.len += new_tokens;
+  s.needs_prefill = false;
+  return s.len;
 }
 
 // Block ids of a sequence; returns the count (or -1).  `shared_prefix_tokens` = tokens whose K/V
@@ -300,8 +484,11 @@ int b200_engine_advance_many(void* h, const int64_t* ids, int n) {
   for (int i = 0; i < n; ++i) {
     auto it = e->seqs.find(ids[i]);
     if (it == e->seqs.end()) return -1;
-    it->second.len += 1;
-    it->second.needs_prefill = false;
+    Seq& s = it->second;
+    if (s.needs_prefill && !s.tokens.empty())
+      e->publish_blocks(s, s.tokens.data(), std::min<int>(static_cast<int>(s.tokens.size()), s.len));
+    s.len += 1;
+    s.needs_prefill = false;
   }
   return 0;
 }

@@ -12,6 +12,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <random>
 #include <set>
 #include <thread>
@@ -29,6 +30,12 @@ int b200_engine_schedule(void* h, int64_t* prefill_ids, int* n_prefill, int64_t*
 int b200_engine_advance(void* h, int64_t seq_id, int new_tokens);
 int b200_engine_blocks(void* h, int64_t seq_id, int* out, int cap, int* shared_prefix_tokens);
 int b200_engine_counts(void* h, int* waiting, int* running);
+int b200_engine_enable_prefix_cache(void* h, int on);
+int b200_engine_reset_prefix_cache(void* h);
+int b200_engine_prefix_cache_stats(void* h, int64_t* out);
+int b200_engine_set_tokens(void* h, int64_t seq_id, const int* tokens, int n);
+int b200_engine_cached_tokens(void* h, int64_t seq_id);
+int b200_engine_finish_tokens(void* h, int64_t seq_id, const int* tokens, int n);
 int b200_pack_plan(const int* lens, int n, int budget, int max_per_row, int* row_of);
 int b200_pack_row(const int64_t* tokens, const int64_t* labels, const int64_t* starts, int first, int last, int64_t* out_ids,
                   int64_t* out_labels, int64_t* out_shifted, int64_t* out_pos, int32_t* out_cu);
@@ -43,9 +50,14 @@ int b200_numa_bind(int node);
     }                                                                          \
   } while (0)
 
-static void engine_stress(int num_blocks, int requests_per_producer) {
+// `prefix_cache`: prompts are cut from five shared documents, so later requests start from blocks earlier ones left behind;
+// sequences finish with their whole token list; an observer thread resets the cache now and then.
+static void engine_stress(int num_blocks, int requests_per_producer, bool prefix_cache = false) {
   constexpr int BS = 16, PRODUCERS = 3, SAMPLES = 4;
   void* e = b200_engine_create(num_blocks, BS, 24);
+  if (prefix_cache) b200_engine_enable_prefix_cache(e, 1);
+  std::vector<std::vector<int>> toks(PRODUCERS * requests_per_producer * SAMPLES);
+  std::mutex toks_mu;
   std::atomic<int64_t> next_seq{0};
   std::atomic<int> added{0}, finished{0};
   std::atomic<bool> producing{true};
@@ -60,6 +72,14 @@ static void engine_stress(int num_blocks, int requests_per_producer) {
         const int64_t id = next_seq.fetch_add(1);
         target[id] = gen;
         while (b200_engine_add(e, id, group, prompt, prompt + gen) != 0) std::this_thread::yield();
+        if (prefix_cache) {
+          std::vector<int> t(prompt);
+          const int doc = static_cast<int>(group % 5);
+          for (int i = 0; i < prompt; ++i) t[i] = (doc * 131 + i * 7) % 1000;
+          b200_engine_set_tokens(e, id, t.data(), prompt);
+          std::lock_guard<std::mutex> g(toks_mu);
+          toks[id] = std::move(t);
+        }
         added.fetch_add(1);
       }
       if (r % 7 == 0) std::this_thread::yield();
@@ -71,6 +91,12 @@ static void engine_stress(int num_blocks, int requests_per_producer) {
       b200_engine_counts(e, &w, &r);
       CHECK(w >= 0 && r >= 0 && r <= 24);
       CHECK(b200_engine_free_blocks(e) <= num_blocks);
+      if (prefix_cache) {
+        int64_t st[4];
+        b200_engine_prefix_cache_stats(e, st);
+        CHECK(st[1] <= st[0] && st[3] >= 0 && st[3] <= num_blocks);
+        if ((st[0] & 63) == 63) b200_engine_reset_prefix_cache(e);
+      }
       std::this_thread::yield();
     }
   };
@@ -93,9 +119,27 @@ static void engine_stress(int num_blocks, int requests_per_producer) {
         const int nb = b200_engine_blocks(e, id, blk.data(), 4096, &shared);
         CHECK(nb > 0 && shared >= 0);
         for (int b = 0; b < nb; ++b) CHECK(blk[b] >= 0 && blk[b] < num_blocks);
+        if (prefix_cache && i < np) {
+          const int c = b200_engine_cached_tokens(e, id);
+          std::lock_guard<std::mutex> g(toks_mu);
+          CHECK(c >= 0 && c % BS == 0 && c < static_cast<int>(toks[id].size()) + produced[id] + 1);
+        }
         b200_engine_advance(e, id, 1);
+        if (prefix_cache) {
+          std::lock_guard<std::mutex> g(toks_mu);
+          toks[id].push_back(static_cast<int>(id % 997));  // the "sampled" token
+        }
         if (++produced[id] >= target[id]) {
-          b200_engine_finish(e, id);
+          if (prefix_cache) {
+            std::vector<int> all;
+            {
+              std::lock_guard<std::mutex> g(toks_mu);
+              all = toks[id];
+            }
+            b200_engine_finish_tokens(e, id, all.data(), static_cast<int>(all.size()));
+          } else {
+            b200_engine_finish(e, id);
+          }
           finished.fetch_add(1);
         }
       }
@@ -159,6 +203,8 @@ static void packer_stress(int seed) {
 int main() {
   engine_stress(4096, 60);  // roomy cache
   engine_stress(40, 25);    // tiny cache: admission stalls and preemption-by-recompute
+  engine_stress(4096, 40, true);  // prefix cache with room: hits, resets from another thread
+  engine_stress(48, 25, true);    // prefix cache under pressure: eviction before preemption
   std::vector<std::thread> ts;
   for (int t = 0; t < 4; ++t) ts.emplace_back([t] { for (int k = 0; k < 20; ++k) packer_stress(1000 * t + k); });
   for (auto& t : ts) t.join();

@@ -262,6 +262,7 @@ def sync_in_process(learner_flat: torch.Tensor, engines: list, model_step: int, 
             torch.cuda.synchronize(learner_flat.device)
         for e in engines:
             e.engine.model_step = model_step
+            e.engine.reset_prefix_cache()  # K/V kept for later requests belong to the old weights
     finally:
         for e in engines:
             e.lock.release()

@@ -48,6 +48,12 @@ class _Host:
         h.b200_engine_schedule.argtypes = [p, PI64, PI32, PI64, PI32, PI64, PI32, i32]
         h.b200_engine_blocks.argtypes = [p, i64, PI32, i32, PI32]
         h.b200_engine_counts.argtypes = [p, PI32, PI32]
+        h.b200_engine_enable_prefix_cache.argtypes = [p, i32]
+        h.b200_engine_reset_prefix_cache.argtypes = [p]
+        h.b200_engine_prefix_cache_stats.argtypes = [p, PI64]
+        h.b200_engine_set_tokens.argtypes = [p, i64, PI32, i32]
+        h.b200_engine_cached_tokens.argtypes = [p, i64]
+        h.b200_engine_finish_tokens.argtypes = [p, i64, PI32, i32]
         h.b200_engine_pack_decode.argtypes = [p, p, i32, i32, p, p, p, p, p, i64, PI32]
         h.b200_engine_advance_many.argtypes = [p, p, i32]
         self.h = h
@@ -92,8 +98,31 @@ class _Host:
             raise KeyError("decode step names a sequence the scheduler does not hold")
         return w.value
 
-    def finish(self, sid):
-        self.h.b200_engine_finish(self.e, sid)
+    def finish(self, sid, tokens=None):
+        """Remove a sequence; with ``tokens`` (everything it holds) its full blocks stay findable in the prefix cache."""
+        if tokens is not None:
+            arr = (ctypes.c_int * len(tokens))(*tokens)
+            self.h.b200_engine_finish_tokens(self.e, sid, arr, len(tokens))
+        else:
+            self.h.b200_engine_finish(self.e, sid)
+
+    def enable_prefix_cache(self, on: bool) -> None:
+        self.h.b200_engine_enable_prefix_cache(self.e, int(on))
+
+    def reset_prefix_cache(self) -> None:
+        self.h.b200_engine_reset_prefix_cache(self.e)
+
+    def prefix_cache_stats(self) -> dict:
+        out = (ctypes.c_int64 * 4)()
+        self.h.b200_engine_prefix_cache_stats(self.e, out)
+        return {"block_lookups": out[0], "block_hits": out[1], "evictions": out[2], "cached_blocks": out[3]}
+
+    def set_tokens(self, sid, tokens) -> None:
+        arr = (ctypes.c_int * len(tokens))(*tokens)
+        self.h.b200_engine_set_tokens(self.e, sid, arr, len(tokens))
+
+    def cached_tokens(self, sid) -> int:
+        return max(0, self.h.b200_engine_cached_tokens(self.e, sid))
 
     def free_blocks(self):
         return self.h.b200_engine_free_blocks(self.e)
@@ -142,7 +171,12 @@ class RolloutEngine:
 
     def __init__(self, spec: ModelSpec, device="cuda", ops: str = "auto", num_blocks: int | None = None,
                  gpu_memory_utilization: float = 0.85, max_running: int = 256, max_model_len: int = 8192, seed: int = 0,
-                 flat: torch.Tensor | None = None, eos_token_ids: list[int] | None = None, tokenizer=None, tp=None):
+                 flat: torch.Tensor | None = None, eos_token_ids: list[int] | None = None, tokenizer=None, tp=None,
+                 enable_prefix_caching: bool = False):
+        # ``enable_prefix_caching``: full KV blocks outlive their request and serve later requests that start with the same
+        # tokens (multi-turn conversations re-submit their history; the reference reaches this through vLLM's
+        # ``enable_prefix_caching``, ``open_instruct/vllm_utils.py:1057-1070``).  Without it only the ``n`` samples of one
+        # request share their prompt blocks.
         # ``tp``: a ``parallel.tp.TPContext``; ``spec`` and ``flat`` are then this rank's shard (``local_spec`` / ``shard_flat``)
         self.tp = tp
         self.spec = spec
@@ -170,6 +204,9 @@ class RolloutEngine:
         self.k_cache = torch.zeros(shape, dtype=dtype, device=self.device)
         self.v_cache = torch.zeros(shape, dtype=dtype, device=self.device)
         self.host = _Host(num_blocks, max_running)
+        self.prefix_caching = bool(enable_prefix_caching)
+        if self.prefix_caching:
+            self.host.enable_prefix_cache(True)
         self.max_running = max_running
         self._next_sid = 0
         self._next_rid = 0
@@ -212,6 +249,8 @@ class RolloutEngine:
             req.seqs.append(seq)
             self.seqs[sid] = seq
             self.host.add(sid, rid, len(prompt), len(prompt) + sampling.max_tokens)
+            if self.prefix_caching:
+                self.host.set_tokens(sid, seq.tokens)
         self.requests[rid] = req
         return rid
 
@@ -223,10 +262,9 @@ class RolloutEngine:
         return w + r
 
     def reset_prefix_cache(self) -> bool:
-        """Drop KV blocks that are kept only so that a LATER request can reuse them.  This engine shares a prompt's blocks
-        among the ``n`` samples of one request and frees them with the request, so nothing outlives a request and there
-        is nothing stale to drop after a weight update; the call exists for the reference's control surface
-        (``open_instruct/vllm_utils.py:791-793``) and reports success."""
+        """Drop KV blocks that are kept only so that a LATER request can reuse them: after a weight update they hold K/V of
+        the old policy (``open_instruct/vllm_utils.py:791-793``).  Blocks of running requests stay with them."""
+        self.host.reset_prefix_cache()
         return True
 
     def update_weights(self, flat: torch.Tensor, model_step: int | None = None) -> None:
@@ -234,6 +272,8 @@ class RolloutEngine:
         with torch.no_grad():
             n = min(flat.numel(), self.model.flat.numel())  # the two buffers may be padded for different world sizes
             self.model.flat[:n].copy_(flat[:n].to(self.model.flat.dtype), non_blocking=True)
+        if self.prefix_caching:
+            self.host.reset_prefix_cache()
         if model_step is not None:
             self.model_step = model_step
 
@@ -253,7 +293,7 @@ class RolloutEngine:
             seq = self.seqs.get(sid)
             if seq is None or seq.finish_reason is None:
                 continue
-            self.host.finish(sid)
+            self.host.finish(sid, seq.tokens if self.prefix_caching else None)
             del self.seqs[sid]
             req = seq.request
             req.done += 1
@@ -466,23 +506,30 @@ class RolloutEngine:
             i = j
 
     def _prefill_batch(self, reps: list, members: list) -> None:
+        """Prompt pass of a sub-batch.  A sequence admitted with a cached prefix (``enable_prefix_caching``) runs the layers
+        over its remaining tokens only; its attention sees the cached K/V of the prefix, gathered from the paged cache into
+        the packed layout the varlen kernel reads (prefix rows carry zero queries and their outputs are dropped - the
+        projections, which dominate, are skipped for them)."""
         s = self.spec
-        ids = torch.tensor([t for q in reps for t in q.tokens], dtype=torch.long)
         lens = [len(q.tokens) for q in reps]
+        cached = [min(self.host.cached_tokens(q.sid), n - 1) if self.prefix_caching else 0 for q, n in zip(reps, lens)]
+        ids = torch.tensor([t for q, c in zip(reps, cached) for t in q.tokens[c:]], dtype=torch.long)
+        new_lens = [n - c for n, c in zip(lens, cached)]
         T = int(ids.numel())
-        pos = torch.cat([torch.arange(n) for n in lens])
-        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        pos = torch.cat([torch.arange(c, n) for c, n in zip(cached, lens)])
+        cu = torch.tensor([0] + list(torch.tensor(new_lens).cumsum(0)), dtype=torch.int32)
         n_var = max(len(m) for m in members)
         slot_rows = []
         for v in range(n_var):
             row = []
-            for q, ms, n in zip(reps, members, lens):
+            for q, ms, n, c in zip(reps, members, lens, cached):
                 if v < len(ms):
                     full = (ms[v].prompt_len // KV_BLOCK) * KV_BLOCK if (v > 0) else 0
-                    sl = self._slots_for(ms[v], 0, n)
-                    row += [-1] * min(full, n) + sl[min(full, n):]  # shared full blocks were written by variant 0
+                    sl = self._slots_for(ms[v], c, n)
+                    skip = max(0, min(full, n) - c)
+                    row += [-1] * skip + sl[skip:]  # shared full blocks were written by variant 0 (or came from the cache)
                 else:
-                    row += [-1] * n
+                    row += [-1] * (n - c)
             slot_rows.append(row)
         dev = self.device
         ids_d, pos_d, cu_d = ids.to(dev), pos.to(dev), cu.to(dev)
@@ -491,13 +538,35 @@ class RolloutEngine:
         if self.ops == "fused":
             from ..ops import fused as f
 
-            attn_fn = lambda i, qkv: f.attn_fwd(qkv, cu_d, s.num_heads, s.num_kv_heads, s.head_dim, scale)[0]
+            attend = lambda qkv, cu_: f.attn_fwd(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale)[0]
         else:
-            attn_fn = lambda i, qkv: ref.attention_varlen(qkv, cu_d, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+            attend = lambda qkv, cu_: ref.attention_varlen(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+        if any(cached):
+            # packed layout with the prefixes in place: sequence j occupies rows [o_j, o_j + n_j), its first c_j rows are cached
+            offs = [0]
+            for n in lens:
+                offs.append(offs[-1] + n)
+            new_rows = torch.tensor([offs[j] + t for j, (c, n) in enumerate(zip(cached, lens)) for t in range(c, n)], dtype=torch.long, device=dev)
+            pref_rows = torch.tensor([offs[j] + t for j, c in enumerate(cached) for t in range(c)], dtype=torch.long, device=dev)
+            pslots = [x for q, c in zip(reps, cached) for x in self._slots_for(q, 0, c)]
+            pblk = torch.tensor([x // KV_BLOCK for x in pslots], dtype=torch.long, device=dev)
+            poff = torch.tensor([x % KV_BLOCK for x in pslots], dtype=torch.long, device=dev)
+            cu_ext = torch.tensor(offs, dtype=torch.int32, device=dev)
+            qd, kd = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+
+            def attn_fn(i, qkv):
+                ext = torch.zeros(offs[-1], qkv.shape[1], dtype=qkv.dtype, device=dev)
+                ext[new_rows] = qkv
+                ext[pref_rows, qd:qd + kd] = self.k_cache[i][pblk, :, poff].reshape(len(pslots), kd)
+                ext[pref_rows, qd + kd:] = self.v_cache[i][pblk, :, poff].reshape(len(pslots), kd)
+                return attend(ext, cu_ext)[new_rows].contiguous()
+        else:
+            attn_fn = lambda i, qkv: attend(qkv, cu_d)
         hidden = self._layer_stack(ids_d, pos_d, slots, attn_fn)
         last = cu_d[1:].long() - 1
         logits = self._logits(hidden[last])
         self.stats["prefill_tokens"] += T
+        self.stats["prefix_cached_tokens"] = self.stats.get("prefix_cached_tokens", 0) + sum(cached)
         flat_members = [m for ms in members for m in ms]
         rows = torch.tensor([ri for ri, ms in enumerate(members) for _ in ms], device=dev)
         toks, lps = self._sample(logits[rows].contiguous(), flat_members)

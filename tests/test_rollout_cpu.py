@@ -116,3 +116,94 @@ def test_native_decode_packing_matches_per_sequence_queries():
     assert h.pack_decode(sids, pos, slots, ctx, ctr, np.zeros(3, np.int32)) == -2  # staging too small: the caller grows it
     with pytest.raises(KeyError):
         h.pack_decode(np.asarray([99], np.int64), pos, slots, ctx, ctr, bt)
+
+
+def test_block_manager_prefix_cache():
+    """Full blocks outlive their sequence: a later sequence with the same first tokens starts from them; unreferenced cached
+    blocks are evicted (oldest first) only when no free block is left; a reset forgets them."""
+    from open_instruct_b200.rollout.engine import KV_BLOCK, _Host
+
+    h = _Host(8, 4)
+    h.enable_prefix_cache(True)
+    a = list(range(1000, 1000 + 150))           # 2 full blocks + 22 tokens
+    h.add(1, 1, len(a), len(a) + 20)
+    h.set_tokens(1, a)
+    assert h.schedule()[0] == [1] and h.cached_tokens(1) == 0
+    blocks_a = h.blocks(1)[0]
+    h.advance(1, 1)                                # the prompt pass is done: its full blocks are findable
+    b = a[:130] + [7, 8, 9]                        # shares the first 130 tokens = 2 full blocks
+    h.add(2, 2, len(b), len(b) + 20)
+    h.set_tokens(2, b)
+    assert h.schedule()[0] == [2] and h.cached_tokens(2) == 2 * KV_BLOCK
+    assert h.blocks(2)[0][:2] == blocks_a[:2] and h.blocks(2)[0][2] != blocks_a[2]
+    c = a[:KV_BLOCK]                               # exactly one block: at least one token is always computed
+    h.add(3, 3, len(c), len(c) + 4)
+    h.set_tokens(3, c)
+    assert h.schedule()[0] == [3] and h.cached_tokens(3) == 0
+    st = h.prefix_cache_stats()
+    assert st["block_hits"] == 2 and st["cached_blocks"] == 2
+    # generated tokens become findable when the sequence finishes with its full token list
+    h.advance(2, 1)
+    for _ in range(70):
+        h.schedule()
+        h.advance(2, 1)
+    full_b = b + [11] * 71                          # 133 + 71 = 204 tokens, K/V written for 203: 3 full blocks
+    h.finish(2, full_b)
+    h.finish(1)
+    h.finish(3)
+    assert h.prefix_cache_stats()["cached_blocks"] >= 3 and h.free_blocks() == 8   # cached blocks count as available
+    d = full_b[:200]
+    h.add(4, 4, len(d), len(d) + 8)
+    h.set_tokens(4, d)
+    assert h.schedule()[0] == [4] and h.cached_tokens(4) == 3 * KV_BLOCK           # prompt + generated history of sequence 2
+    h.finish(4)
+    # eviction: a request that needs every block takes the cached ones back
+    e = list(range(5000, 5000 + 8 * KV_BLOCK - 10))
+    h.add(5, 5, len(e), len(e) + 4)
+    h.set_tokens(5, e)
+    assert h.schedule()[0] == [5] and h.cached_tokens(5) == 0
+    assert h.prefix_cache_stats()["evictions"] >= 3 and h.prefix_cache_stats()["cached_blocks"] == 0
+    h.advance(5, 1)
+    assert h.prefix_cache_stats()["cached_blocks"] == 7
+    h.reset_prefix_cache()
+    assert h.prefix_cache_stats()["cached_blocks"] == 0
+    h.finish(5)
+    assert h.free_blocks() == 8
+
+
+@pytest.mark.parametrize("n_samples", [1, 3])
+def test_engine_prefix_cache_gives_the_same_tokens(n_samples):
+    """Generation with the prefix cache equals generation without it, for a repeated prompt and for a follow-up turn that
+    extends prompt + answer; the second and third requests skip the cached part of their prompt pass."""
+    import torch
+
+    from open_instruct_b200.data_types import SamplingConfig
+    from open_instruct_b200.models import get_spec
+    from open_instruct_b200.rollout.engine import RolloutEngine
+
+    spec = get_spec("tiny").replace(eos_token_id=None)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, spec.vocab_size, (150,), generator=g).tolist()
+    cfg = SamplingConfig(temperature=0.0 if n_samples == 1 else 0.8, top_p=1.0, max_tokens=70, n=n_samples, seed=4)
+
+    def run(cache: bool):
+        eng = RolloutEngine(spec, device="cpu", ops="ref", num_blocks=64, seed=2, enable_prefix_caching=cache)
+        first = eng.generate([prompt], cfg)[0]
+        again = eng.generate([prompt], cfg)[0]
+        follow = prompt + first.responses[0] + [3, 1, 4, 1, 5]
+        turn2 = eng.generate([follow], cfg)[0]
+        return eng, [first.responses, again.responses, turn2.responses], [first.logprobs, again.logprobs, turn2.logprobs]
+
+    plain, want, want_lp = run(False)
+    cached, got, got_lp = run(True)
+    assert got == want
+    for a, b in zip(got_lp, want_lp):
+        for x, y in zip(a, b):
+            assert all(abs(p - q) < 1e-4 for p, q in zip(x, y))
+    st = cached.host.prefix_cache_stats()
+    assert st["block_hits"] >= 2 + 3                       # 128 of 150 prompt tokens again, 192 of the 225-token second turn
+    assert cached.stats["prefix_cached_tokens"] >= 128 + 192
+    assert cached.stats["prefill_tokens"] <= plain.stats["prefill_tokens"] - (128 + 192)
+    assert plain.stats.get("prefix_cached_tokens", 0) == 0
+    cached.update_weights(cached.model.flat.detach().clone(), 1)
+    assert cached.host.prefix_cache_stats()["cached_blocks"] == 0   # K/V of the old weights are not served after an update
