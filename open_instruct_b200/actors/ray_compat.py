@@ -330,7 +330,23 @@ class ActorClass:
         proc = ctx.Process(target=_serve, args=(self._cls, args, kwargs, address, ready, self._opts.get("max_concurrency", 8), env),
                            daemon=True)
         proc.start()
-        status, err = ready.get(timeout=self._opts.get("init_timeout", 1200))
+        # wait for the constructor, but notice a process that died in it (killed for memory, a crash in native code): such a
+        # process never reports, and ranks that rendezvous with it would sit in their own timeouts
+        deadline = time.time() + self._opts.get("init_timeout", 1200)
+        while True:
+            try:
+                status, err = ready.get(timeout=0.5)
+                break
+            except _queue.Empty:
+                if not proc.is_alive():
+                    try:
+                        status, err = ready.get(timeout=0.5)  # it may have reported just before exiting
+                        break
+                    except _queue.Empty:
+                        raise ActorError(f"actor {self._cls.__name__} died while starting (exit code {proc.exitcode})") from None
+                if time.time() > deadline:
+                    proc.terminate()
+                    raise ActorError(f"actor {self._cls.__name__} did not finish starting in time") from None
         if status != "ok":
             raise ActorError(f"actor {self._cls.__name__} failed to start:\n{err}")
         _children.append(proc)

@@ -1025,9 +1025,8 @@ class GRPORun:
                         for r in range(args.world_size)]
                 learners = [f.result() for f in futs]
             # On GPUs the engines start with random weights and receive the learners' through the first weight sync (the same
-            # push kernel as every later one) instead of a by-value copy of the whole model in every engine process: for 8B that
-            # copy is 16 GB pickled once per engine rank, all at the same time - with 4 engine ranks (2 engines of
-            # tensor-parallel size 2) more than 200 GB of host memory is in flight at start-up.
+            # push kernel as every later one) instead of a by-value copy of the whole model handed to every engine process
+            # (16 GB at 8B: gathered to the driver, shared with every engine rank, copied to each GPU and re-sharded there).
             init_by_push = (cuda and os.environ.get("B200_GRPO_INIT_BY_PUSH", "1") == "1") or os.environ.get("B200_GRPO_INIT_BY_PUSH") == "force"
             init_flat = None if init_by_push else ray.get(learners[0].flat_weights_cpu.remote())
             tp = vllm.vllm_tensor_parallel_size if cuda else 1

@@ -28,6 +28,22 @@ class Counter:
         return {"out": t * 2, "n": t.numel()}
 
 
+class DiesInInit:
+    def __init__(self):
+        import os
+
+        os._exit(9)  # what the kernel's out-of-memory killer or a native crash looks like from outside
+
+
+def test_an_actor_that_dies_while_starting_is_reported_at_once():
+    from open_instruct_b200.actors import ray_compat as ray
+
+    t0 = time.time()
+    with pytest.raises(ray.ActorError, match="died while starting"):
+        ray.remote(DiesInInit).remote()
+    assert time.time() - t0 < 30
+
+
 def test_actor_calls_and_errors():
     from open_instruct_b200.actors import ray_compat as ray
 
