@@ -80,7 +80,7 @@ class Learner:
         self.device = torch.device(device)
         ops = cfg.ops
         if ops == "auto":
-            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm
                               and torch.cuda.get_device_capability(self.device)[0] == 10) else "ref"
         self.ops = ops
         dtype = cfg.dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)

@@ -74,6 +74,9 @@ class LlamaModel:
                 raise ValueError("the fused path runs bf16 on CUDA")
             if spec.head_dim != 128:
                 raise NotImplementedError("fused attention is built for head_dim 128")
+            if spec.post_norm or spec.qk_norm_full:
+                raise NotImplementedError("the fused layer engine is built for pre-norm blocks (Llama, Qwen, Mistral); OLMo-2 / OLMo-3 "
+                                          "blocks (norm after the sub-layer, q/k norm over all heads) run with ops='ref'")
             from ..ops import lib
 
             if not lib.available():
@@ -246,6 +249,9 @@ class LlamaModel:
 
     def _ref_hidden(self, input_ids, position_ids, cu_seqlens) -> torch.Tensor:
         s = self.spec
+        if s.sliding_window and cu_seqlens.numel() > 1 and int((cu_seqlens[1:] - cu_seqlens[:-1]).max()) > s.sliding_window:
+            raise NotImplementedError(f"documents longer than the model's sliding window ({s.sliding_window}) need windowed attention, "
+                                      "which is not built: every layer here attends to the whole document")
         v = self._ref_params()  # autograd views of the single leaf
         x = v["embed"][input_ids]
         for i in range(s.num_layers):
@@ -259,7 +265,11 @@ class LlamaModel:
         qkv = ref.linear(n1, v[f"l{i}.wqkv"])
         if s.attention_bias:
             qkv = qkv + v[f"l{i}.bqkv"]
-        if s.qk_norm:
+        if s.qk_norm and s.qk_norm_full:  # OLMo-2: one norm over all heads of q, one over all heads of k
+            q = ref.rmsnorm(qkv[:, : s.q_dim], v[f"l{i}.q_norm"], s.rms_norm_eps)
+            k = ref.rmsnorm(qkv[:, s.q_dim : s.q_dim + s.kv_dim], v[f"l{i}.k_norm"], s.rms_norm_eps)
+            qkv = torch.cat([q, k, qkv[:, s.q_dim + s.kv_dim :]], dim=1)
+        elif s.qk_norm:
             T = qkv.shape[0]
             heads = qkv.view(T, s.num_heads + 2 * s.num_kv_heads, s.head_dim)
             q = ref.rmsnorm(heads[:, : s.num_heads], v[f"l{i}.q_norm"], s.rms_norm_eps)
@@ -270,6 +280,15 @@ class LlamaModel:
     def _ref_layer(self, x, v, i, position_ids, cu_seqlens):
         s = self.spec
         tp = self.tp
+        if s.post_norm:  # OLMo-2 / OLMo-3: the sub-layer reads the stream as it is, its OUTPUT is normed before the residual add
+            if tp is not None:
+                raise NotImplementedError("tensor parallelism is not built for post-norm blocks")
+            qkv = self.ref_qkv(x, v, i)
+            qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim)
+            x = x + ref.rmsnorm(ref.linear(attn, v[f"l{i}.wo"]), v[f"l{i}.attn_norm"], s.rms_norm_eps)
+            act = ref.swiglu(ref.linear(x, v[f"l{i}.w_gate_up"]))
+            return x + ref.rmsnorm(ref.linear(act, v[f"l{i}.w_down"]), v[f"l{i}.mlp_norm"], s.rms_norm_eps)
         n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
         if tp is not None:
             n1 = tp.enter(n1)

@@ -16,6 +16,18 @@ from dataclasses import dataclass, field
 from pathlib import Path
 
 
+def _rope_scaling_of(cfg: dict) -> dict | None:
+    """The RoPE scaling rule of a config.json: ``rope_scaling`` (older form), else ``rope_parameters`` when it names a rule
+    other than the default (the form transformers 5 writes)."""
+    sc = cfg.get("rope_scaling")
+    if sc:
+        return sc
+    rp = cfg.get("rope_parameters") or {}
+    if rp.get("rope_type", rp.get("type", "default")) not in ("default", None):
+        return {k: v for k, v in rp.items() if k != "rope_theta"}
+    return None
+
+
 @dataclass
 class ModelSpec:
     vocab_size: int = 128256
@@ -30,7 +42,10 @@ class ModelSpec:
     rope_scaling: dict | None = None
     max_position_embeddings: int = 131072
     tie_word_embeddings: bool = False
-    qk_norm: bool = False  # Qwen3 / OLMo-2 style per-head q/k RMSNorm
+    qk_norm: bool = False  # RMSNorm of q and k before RoPE: per head (Qwen3), or over the whole projection (``qk_norm_full``)
+    qk_norm_full: bool = False  # OLMo-2 / OLMo-3: one norm over all heads of q (weight [q_dim]) and one over all heads of k
+    post_norm: bool = False     # OLMo-2 / OLMo-3 block: h += norm(attn(h)); h += norm(mlp(h)) instead of norming the inputs
+    sliding_window: int | None = None  # some layers attend to the last N tokens only (OLMo-3, Mistral v0.1): documents up to N are exact
     attention_bias: bool = False  # Qwen2 style q/k/v bias
     model_type: str = "llama"
     bos_token_id: int | None = None
@@ -69,10 +84,13 @@ class ModelSpec:
             head_dim=hd,
             rms_norm_eps=cfg.get("rms_norm_eps", 1e-5),
             rope_theta=cfg.get("rope_theta", (cfg.get("rope_parameters") or {}).get("rope_theta", 10000.0)),
-            rope_scaling=cfg.get("rope_scaling"),
+            rope_scaling=_rope_scaling_of(cfg),
             max_position_embeddings=cfg.get("max_position_embeddings", 8192),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
             qk_norm=mt in ("qwen3", "olmo2", "olmo3"),
+            qk_norm_full=mt in ("olmo2", "olmo3"),
+            post_norm=mt in ("olmo2", "olmo3"),
+            sliding_window=cfg.get("sliding_window") if (mt == "olmo3" or cfg.get("use_sliding_window", mt == "mistral")) else None,
             attention_bias=cfg.get("attention_bias", mt == "qwen2"),
             model_type=mt,
             bos_token_id=cfg.get("bos_token_id"),
@@ -86,7 +104,7 @@ class ModelSpec:
 
     def to_hf_config(self) -> dict:
         arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                "mistral": "MistralForCausalLM", "olmo2": "Olmo2ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+                "mistral": "MistralForCausalLM", "olmo2": "Olmo2ForCausalLM", "olmo3": "Olmo3ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
         cfg = {
             "architectures": [arch],
             "model_type": self.model_type,
@@ -101,6 +119,9 @@ class ModelSpec:
             "rms_norm_eps": self.rms_norm_eps,
             "rope_theta": self.rope_theta,
             "rope_scaling": self.rope_scaling,
+            # the form newer transformers releases read and write (``rope_scaling`` above is what older ones and the hub's
+            # Llama-3.1 configs carry)
+            "rope_parameters": {"rope_theta": self.rope_theta, **(self.rope_scaling or {"rope_type": "default"})},
             "max_position_embeddings": self.max_position_embeddings,
             "tie_word_embeddings": self.tie_word_embeddings,
             "attention_bias": self.attention_bias,
@@ -150,7 +171,7 @@ PRESETS: dict[str, ModelSpec] = {
                             model_type="qwen3", tie_word_embeddings=True, max_position_embeddings=40960),
     "olmo2-7b": ModelSpec(vocab_size=100352, hidden_size=4096, intermediate_size=11008, num_layers=32, num_heads=32,
                           num_kv_heads=32, head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2",
-                          max_position_embeddings=4096),
+                          qk_norm=True, qk_norm_full=True, post_norm=True, max_position_embeddings=4096),
 }
 
 
@@ -214,8 +235,8 @@ class ParamLayout:
             add(f"l{i}.attn_norm", (s.hidden_size,), False)
             add(f"l{i}.mlp_norm", (s.hidden_size,), False)
             if s.qk_norm:
-                add(f"l{i}.q_norm", (s.head_dim,), False)
-                add(f"l{i}.k_norm", (s.head_dim,), False)
+                add(f"l{i}.q_norm", (s.q_dim if s.qk_norm_full else s.head_dim,), False)
+                add(f"l{i}.k_norm", (s.kv_dim if s.qk_norm_full else s.head_dim,), False)
             if s.attention_bias:
                 add(f"l{i}.bqkv", (s.qkv_dim,), False)
         add("final_norm", (s.hidden_size,), False)
@@ -251,12 +272,12 @@ class ParamLayout:
                     (p + "mlp.up_proj.weight", s.intermediate_size, 2 * s.intermediate_size)]
         if leaf == "w_down":
             return [(p + "mlp.down_proj.weight", 0, s.hidden_size)]
-        if leaf == "attn_norm":
-            return [(p + "input_layernorm.weight", 0, s.hidden_size)]
-        if leaf == "mlp_norm":
-            return [(p + "post_attention_layernorm.weight", 0, s.hidden_size)]
+        if leaf == "attn_norm":  # post-norm blocks: the norm applied to the attention output
+            return [(p + ("post_attention_layernorm.weight" if s.post_norm else "input_layernorm.weight"), 0, s.hidden_size)]
+        if leaf == "mlp_norm":   # post-norm blocks: the norm applied to the MLP output
+            return [(p + ("post_feedforward_layernorm.weight" if s.post_norm else "post_attention_layernorm.weight"), 0, s.hidden_size)]
         if leaf == "q_norm":
-            return [(p + "self_attn.q_norm.weight", 0, s.head_dim)]
+            return [(p + "self_attn.q_norm.weight", 0, s.q_dim if s.qk_norm_full else s.head_dim)]
         if leaf == "k_norm":
-            return [(p + "self_attn.k_norm.weight", 0, s.head_dim)]
+            return [(p + "self_attn.k_norm.weight", 0, s.kv_dim if s.qk_norm_full else s.head_dim)]
         raise KeyError(name)

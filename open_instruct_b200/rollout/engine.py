@@ -182,7 +182,7 @@ class RolloutEngine:
         self.spec = spec
         self.device = torch.device(device)
         if ops == "auto":
-            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and lib.available()) else "ref"
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and lib.available()) else "ref"
         self.ops = ops
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, seed=seed, flat=flat)
@@ -449,7 +449,8 @@ class RolloutEngine:
             return nf
         x = p["embed"][ids]
         for i in range(s.num_layers):
-            n1 = ref.rmsnorm(x, p[f"l{i}.attn_norm"], s.rms_norm_eps)
+            # pre-norm blocks (Llama, Qwen, Mistral) norm the sub-layer's input; post-norm blocks (OLMo-2 / OLMo-3) its output
+            n1 = x if s.post_norm else ref.rmsnorm(x, p[f"l{i}.attn_norm"], s.rms_norm_eps)
             qkv = ref.rope(self.model.ref_qkv(n1, p, i), pos, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
             heads = qkv.view(T, s.num_heads + 2 * s.num_kv_heads, s.head_dim)
             k_new, v_new = heads[:, s.num_heads : s.num_heads + s.num_kv_heads], heads[:, s.num_heads + s.num_kv_heads :]
@@ -460,9 +461,11 @@ class RolloutEngine:
                 self.k_cache[i][blk, :, off] = k_new[ok]
                 self.v_cache[i][blk, :, off] = v_new[ok]
             attn = attn_fn(i, qkv)
-            x = x + ref.linear(attn, p[f"l{i}.wo"])
-            n2 = ref.rmsnorm(x, p[f"l{i}.mlp_norm"], s.rms_norm_eps)
-            x = x + ref.linear(ref.swiglu(ref.linear(n2, p[f"l{i}.w_gate_up"])), p[f"l{i}.w_down"])
+            o = ref.linear(attn, p[f"l{i}.wo"])
+            x = x + (ref.rmsnorm(o, p[f"l{i}.attn_norm"], s.rms_norm_eps) if s.post_norm else o)
+            n2 = x if s.post_norm else ref.rmsnorm(x, p[f"l{i}.mlp_norm"], s.rms_norm_eps)
+            d = ref.linear(ref.swiglu(ref.linear(n2, p[f"l{i}.w_gate_up"])), p[f"l{i}.w_down"])
+            x = x + (ref.rmsnorm(d, p[f"l{i}.mlp_norm"], s.rms_norm_eps) if s.post_norm else d)
         return ref.rmsnorm(x, p["final_norm"], s.rms_norm_eps)
 
     def _logits(self, hidden: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,107 @@
+"""Logit parity with the Hugging Face implementations, family by family: a small random model built by transformers is saved,
+read back through this package's checkpoint reader into the PyTorch path, and must give the same logits; the export goes the other
+way.  Families: Llama (plain, Llama-3.1 frequency-dependent RoPE scaling, tied embeddings), Qwen2 (q/k/v bias), Qwen3 (per-head q/k
+norm), Mistral, OLMo-2 and OLMo-3 (norm after the sub-layer, q/k norm over all heads)."""
+import tempfile
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+BASE = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            max_position_embeddings=256)
+LLAMA3_SCALING = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
+FAMILIES = {
+    "llama": ("Llama", dict(rope_theta=500000.0)),
+    "llama3.1-rope-scaling": ("Llama", dict(rope_theta=500000.0, rope_scaling=LLAMA3_SCALING)),
+    "llama-tied": ("Llama", dict(tie_word_embeddings=True)),
+    "qwen2": ("Qwen2", {}),
+    "qwen3": ("Qwen3", dict(head_dim=32)),
+    "mistral": ("Mistral", dict(sliding_window=None)),
+    "olmo2": ("Olmo2", {}),
+    "olmo3": ("Olmo3", dict(sliding_window=4096)),
+}
+
+
+def _hf_model(cls_name, extra):
+    if not hasattr(transformers, cls_name + "ForCausalLM"):
+        pytest.skip(f"transformers has no {cls_name}")
+    torch.manual_seed(0)
+    cfg = getattr(transformers, cls_name + "Config")(**{**BASE, **extra})
+    m = getattr(transformers, cls_name + "ForCausalLM")(cfg).eval().float()
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.uniform_(0.5, 1.5)  # norm weights and biases away from their trivial initialisation
+    return m, cfg
+
+
+def _our_logits(model, ids):
+    B, L = ids.shape
+    pos = torch.arange(L).repeat(B)
+    cu = torch.arange(0, (B + 1) * L, L, dtype=torch.int32)
+    with torch.no_grad():
+        return model.logits(ids.reshape(-1), pos, cu).reshape(B, L, -1)
+
+
+@pytest.mark.parametrize("family", list(FAMILIES))
+def test_checkpoint_import_gives_hf_logits(family):
+    from open_instruct_b200.ckpt.hf_io import load_hf_checkpoint
+    from open_instruct_b200.models import LlamaModel
+    from open_instruct_b200.models.spec import ModelSpec
+
+    cls_name, extra = FAMILIES[family]
+    hf, cfg = _hf_model(cls_name, extra)
+    with tempfile.TemporaryDirectory() as d:
+        hf.save_pretrained(d, safe_serialization=True)
+        spec = ModelSpec.from_pretrained(d)
+        ours = LlamaModel(spec, device="cpu", dtype=torch.float32, ops="ref")
+        load_hf_checkpoint(d, ours.flat.detach(), spec, strict=True)
+    ids = torch.randint(0, cfg.vocab_size, (2, 40), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids).logits
+    assert (_our_logits(ours, ids) - want).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2"])
+def test_checkpoint_export_is_read_by_hf(family):
+    from open_instruct_b200.ckpt.hf_io import save_hf_checkpoint
+    from open_instruct_b200.models import LlamaModel
+    from open_instruct_b200.models.spec import ModelSpec
+
+    cls_name, extra = FAMILIES[family]
+    _, cfg = _hf_model(cls_name, extra)
+    with tempfile.TemporaryDirectory() as d0:
+        cfg.save_pretrained(d0)
+        spec = ModelSpec.from_pretrained(d0)
+    ours = LlamaModel(spec, device="cpu", dtype=torch.float32, ops="ref", seed=3)
+    with tempfile.TemporaryDirectory() as d:
+        save_hf_checkpoint(ours.flat.detach(), spec, d, dtype=torch.float32)
+        hf = transformers.AutoModelForCausalLM.from_pretrained(d, torch_dtype=torch.float32).eval()
+    ids = torch.randint(0, spec.vocab_size, (2, 33), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        got = hf(ids).logits
+    assert (got - _our_logits(ours, ids)).abs().max().item() < 1e-5
+
+
+def test_engine_generates_with_a_post_norm_model():
+    """The rollout engine's PyTorch path follows the block structure too: greedy tokens equal argmax decoding with the HF model."""
+    from open_instruct_b200.ckpt.hf_io import load_hf_checkpoint
+    from open_instruct_b200.data_types import SamplingConfig
+    from open_instruct_b200.models.spec import ModelSpec
+    from open_instruct_b200.rollout.engine import RolloutEngine
+
+    hf, cfg = _hf_model("Olmo2", {})
+    with tempfile.TemporaryDirectory() as d:
+        hf.save_pretrained(d, safe_serialization=True)
+        spec = ModelSpec.from_pretrained(d).replace(eos_token_id=None)
+        eng = RolloutEngine(spec, device="cpu", ops="auto", num_blocks=32)
+        load_hf_checkpoint(d, eng.model.flat.detach(), spec)
+    prompt = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(4)).tolist()
+    out = eng.generate([prompt], SamplingConfig(temperature=0.0, max_tokens=6, n=1))[0].responses[0]
+    ids = list(prompt)
+    with torch.no_grad():
+        for _ in range(6):
+            ids.append(int(hf(torch.tensor([ids])).logits[0, -1].argmax()))
+    assert out == ids[len(prompt):]
