@@ -31,7 +31,10 @@ def state_dict_from_flat(flat: torch.Tensor, layout: ParamLayout, dtype=torch.bf
 
 
 def save_hf_checkpoint(flat: torch.Tensor, spec: ModelSpec, out_dir: str, tokenizer=None, layout: ParamLayout | None = None,
-                       dtype=torch.bfloat16, max_shard_bytes: int = MAX_SHARD_BYTES, extra_config: dict | None = None) -> None:
+                       dtype=torch.bfloat16, max_shard_bytes: int = MAX_SHARD_BYTES, extra_config: dict | None = None,
+                       extra_tensors: dict | None = None, skip: set | None = None) -> None:
+    """Write ``flat`` as a Hugging Face checkpoint folder.  ``extra_tensors``: tensors outside the layout that belong in the
+    weight files (a reward model's ``score.weight``); ``skip``: HF tensor names to leave out (its ``lm_head.weight``)."""
     from safetensors.torch import save_file
 
     layout = layout or ParamLayout(spec)
@@ -49,6 +52,8 @@ def save_hf_checkpoint(flat: torch.Tensor, spec: ModelSpec, out_dir: str, tokeni
     for name in layout.entries:
         t = layout.view(flat.detach(), name).to("cpu", dtype)
         for hf_name, a, b in layout.hf_names(name):
+            if skip and hf_name in skip:
+                continue
             piece = t[a:b].contiguous()
             nbytes = piece.numel() * piece.element_size()
             if size + nbytes > max_shard_bytes and shards[-1]:
@@ -56,8 +61,8 @@ def save_hf_checkpoint(flat: torch.Tensor, spec: ModelSpec, out_dir: str, tokeni
                 size = 0
             shards[-1][hf_name] = piece
             size += nbytes
-    if spec.tie_word_embeddings:
-        pass  # lm_head shares the embedding: not written, as HF does for tied models
+    for hf_name, t in (extra_tensors or {}).items():
+        shards[-1][hf_name] = t.detach().to("cpu", dtype).contiguous()
     n = len(shards)
     if n == 1:
         save_file(shards[0], str(out / "model.safetensors"), metadata={"format": "pt"})

@@ -44,14 +44,16 @@ class RewardModelScorer:
         self.tok, self.max_batch_tokens = tokenizer, max_batch_tokens
         device = device or ("cuda" if torch.cuda.is_available() else "cpu")
         spec = get_spec(model_dir)
-        fused = device != "cpu" and spec.head_dim == 128
+        fused = device != "cpu" and spec.head_dim == 128 and not spec.post_norm
         self.model = LlamaModel(spec, device=device, dtype=torch.bfloat16 if fused else torch.float32, ops="fused" if fused else "ref",
                                 with_lm_head=False)
         load_hf_checkpoint(model_dir, self.model.flat, spec, self.model.layout, strict=False)
-        from safetensors.torch import load_file
+        from ..reward_modeling import load_score_weight
 
-        head = os.path.join(model_dir, "score_head.safetensors")
-        self.score = load_file(head)["score.weight"].to(device).float()
+        w = load_score_weight(model_dir)
+        if w is None:
+            raise FileNotFoundError(f"{model_dir} holds no score.weight: not a reward model")
+        self.score = w.to(device).float()
 
     @torch.no_grad()
     def __call__(self, conversations: list[list[dict]]) -> list[float]:

@@ -117,6 +117,38 @@ class RewardHead:
             self.opt.zero_grad(set_to_none=True)
 
 
+def save_reward_model(flat: torch.Tensor, score_weight: torch.Tensor, spec, out_dir: str, tokenizer=None, dtype=torch.bfloat16) -> None:
+    """A folder ``AutoModelForSequenceClassification.from_pretrained`` reads: the backbone under its usual names, the scalar
+    head as ``score.weight`` in the same weight files, no ``lm_head``, the family's ``...ForSequenceClassification``
+    architecture and ``num_labels = 1`` (what the reference saves, ``open_instruct/reward_modeling.py:395-410``)."""
+    arch = spec.to_hf_config()["architectures"][0].replace("ForCausalLM", "ForSequenceClassification")
+    extra = {"architectures": [arch], "num_labels": 1, "id2label": {"0": "LABEL_0"}, "label2id": {"LABEL_0": 0}}
+    if spec.pad_token_id is None and tokenizer is not None and getattr(tokenizer, "pad_token_id", None) is not None:
+        extra["pad_token_id"] = tokenizer.pad_token_id  # HF reads the score at the last non-pad token
+    save_hf_checkpoint(flat, spec, out_dir, tokenizer=tokenizer, dtype=dtype, extra_config=extra,
+                       extra_tensors={"score.weight": score_weight.reshape(1, -1)}, skip={"lm_head.weight"})
+
+
+def load_score_weight(model_dir: str) -> torch.Tensor | None:
+    """``score.weight`` of a reward-model folder (inside the weight files; the separate ``score_head.safetensors`` of earlier
+    exports is still read), or None."""
+    from safetensors import safe_open
+
+    from .ckpt.hf_io import _open_shards
+
+    try:
+        handles, where = _open_shards(model_dir)
+    except FileNotFoundError:
+        handles, where = {}, {}
+    if "score.weight" in where:
+        return handles[where["score.weight"]].get_tensor("score.weight")
+    old = os.path.join(model_dir, "score_head.safetensors")
+    if os.path.exists(old):
+        with safe_open(old, framework="pt", device="cpu") as f:
+            return f.get_tensor("score.weight")
+    return None
+
+
 def pack_preference_batch(rows: list[dict]) -> dict:
     """Chosen documents first, then rejected, as one packed batch."""
     ids = [r[CHOSEN_INPUT_IDS_KEY] for r in rows] + [r[REJECTED_INPUT_IDS_KEY] for r in rows]
@@ -250,12 +282,7 @@ def main(args: Args, tc: TokenizerConfig, model_config: ModelConfig) -> dict:
     pdist.barrier()
     full_weights = learner.full_flat()  # a gather when the parameters are sharded: every rank takes part
     if is_main:
-        save_hf_checkpoint(full_weights, spec, args.output_dir, tokenizer=tokenizer,
-                           extra_config={"architectures": ["LlamaForSequenceClassification"], "num_labels": 1})
-        from safetensors.torch import save_file
-
-        save_file({"score.weight": head.weight.detach().to("cpu", torch.bfloat16).contiguous()},
-                  os.path.join(args.output_dir, "score_head.safetensors"))
+        save_reward_model(full_weights, head.weight, spec, args.output_dir, tokenizer)
     tracker.close()
     pdist.barrier()
     last["seconds"] = time.time() - t0

@@ -105,3 +105,30 @@ def test_engine_generates_with_a_post_norm_model():
         for _ in range(6):
             ids.append(int(hf(torch.tensor([ids])).logits[0, -1].argmax()))
     assert out == ids[len(prompt):]
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen2"])
+def test_reward_model_export_is_read_by_hf_sequence_classification(family):
+    """The reward-model folder loads with ``AutoModelForSequenceClassification`` and scores like this package's ``get_reward``."""
+    from open_instruct_b200.models import LlamaModel
+    from open_instruct_b200.models.spec import ModelSpec
+    from open_instruct_b200.reward_modeling import load_score_weight, save_reward_model
+
+    cls_name, extra = FAMILIES[family]
+    _, cfg = _hf_model(cls_name, extra)
+    with tempfile.TemporaryDirectory() as d0:
+        cfg.save_pretrained(d0)
+        spec = ModelSpec.from_pretrained(d0).replace(pad_token_id=0)
+    ours = LlamaModel(spec, device="cpu", dtype=torch.float32, ops="ref", seed=5)
+    score = torch.randn(1, spec.hidden_size, generator=torch.Generator().manual_seed(6)) * 0.1
+    with tempfile.TemporaryDirectory() as d:
+        save_reward_model(ours.flat.detach(), score, spec, d, dtype=torch.float32)
+        assert torch.equal(load_score_weight(d), score)
+        hf = transformers.AutoModelForSequenceClassification.from_pretrained(d, torch_dtype=torch.float32).eval()
+    assert type(hf).__name__ == cls_name + "ForSequenceClassification"
+    ids = torch.randint(1, spec.vocab_size, (1, 29), generator=torch.Generator().manual_seed(7))
+    with torch.no_grad():
+        want = hf(ids).logits.reshape(-1)
+        h = ours.hidden_states(ids.reshape(-1), torch.arange(29), torch.tensor([0, 29], dtype=torch.int32))
+        got = (h[-1:].float() @ score.t()).reshape(-1)
+    assert (got - want).abs().max().item() < 1e-5
