@@ -240,6 +240,11 @@ def main(args: Args, tc: TokenizerConfig, model_config: ModelConfig) -> dict:
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):
         learner.load_hf(src)
     head = RewardHead(spec.hidden_size, device, args.learning_rate, args.eps, args.seed)
+    if src and os.path.isdir(src):
+        w0 = load_score_weight(src)  # continuing from a reward model: its head comes along with the backbone
+        if w0 is not None:
+            with torch.no_grad():
+                head.weight.copy_(w0.reshape(1, -1).to(head.weight))
     loader = HFDataLoader(train, batch_size=args.micro_batch_size, seed=args.seed, dp_rank=rank, dp_world_size=world,
                           collator=pack_preference_batch, automatic_reshuffle=True)
     eval_loader = None
