@@ -307,7 +307,7 @@ class ZeroOptimizer:
 
 # ---------------------------------------------------------------------- LR schedules
 def lr_at(step: int, base_lr: float, total_steps: int, warmup_steps: int, kind: str = "linear",
-          final_lr_ratio: float | None = None, num_cycles: float = 0.5) -> float:
+          final_lr_ratio: float | None = None, num_cycles: float | None = None) -> float:
     """Learning rate for optimizer step ``step`` (0-based), HF ``get_scheduler`` semantics.
 
     ``linear`` with ``final_lr_ratio`` decays to ``base_lr * final_lr_ratio`` instead of zero
@@ -325,12 +325,12 @@ def lr_at(step: int, base_lr: float, total_steps: int, warmup_steps: int, kind: 
         if final_lr_ratio is not None:
             return base_lr * (final_lr_ratio + (1.0 - final_lr_ratio) * (1.0 - progress))
         return base_lr * max(0.0, 1.0 - progress)
-    if kind == "cosine":
-        return base_lr * max(0.0, 0.5 * (1.0 + math.cos(math.pi * num_cycles * 2.0 * progress)))
-    if kind == "cosine_with_restarts":
+    if kind == "cosine":  # transformers' default: half a cosine wave
+        return base_lr * max(0.0, 0.5 * (1.0 + math.cos(math.pi * (0.5 if num_cycles is None else num_cycles) * 2.0 * progress)))
+    if kind == "cosine_with_restarts":  # transformers' default: one hard restart cycle
         if progress >= 1.0:
             return 0.0
-        return base_lr * max(0.0, 0.5 * (1.0 + math.cos(math.pi * ((num_cycles * progress) % 1.0))))
+        return base_lr * max(0.0, 0.5 * (1.0 + math.cos(math.pi * (((1 if num_cycles is None else num_cycles) * progress) % 1.0))))
     if kind == "polynomial":
         lr_end, power = 1e-7, 1.0
         return (base_lr - lr_end) * (1 - progress) ** power + lr_end

@@ -132,3 +132,17 @@ def test_reward_model_export_is_read_by_hf_sequence_classification(family):
         h = ours.hidden_states(ids.reshape(-1), torch.arange(29), torch.tensor([0, 29], dtype=torch.int32))
         got = (h[-1:].float() @ score.t()).reshape(-1)
     assert (got - want).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("kind", ["linear", "cosine", "constant", "constant_with_warmup", "polynomial", "cosine_with_restarts"])
+def test_learning_rate_schedules_equal_transformers(kind):
+    """Every schedule name the trainers accept gives the multipliers of ``transformers.get_scheduler`` step by step."""
+    from open_instruct_b200.parallel.zero import lr_at
+
+    p = torch.nn.Parameter(torch.zeros(1))
+    opt = torch.optim.SGD([p], lr=1.0)
+    sch = transformers.get_scheduler(kind, opt, num_warmup_steps=10, num_training_steps=100)
+    for step in range(100):
+        assert abs(opt.param_groups[0]["lr"] - lr_at(step, 1.0, 100, 10, kind)) < 1e-12, step
+        opt.step()
+        sch.step()
