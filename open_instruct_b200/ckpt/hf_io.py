@@ -55,6 +55,8 @@ def save_hf_checkpoint(flat: torch.Tensor, spec: ModelSpec, out_dir: str, tokeni
             if skip and hf_name in skip:
                 continue
             piece = t[a:b].contiguous()
+            if spec.num_experts and hf_name.endswith(("experts.gate_up_proj", "experts.down_proj")):
+                piece = piece.view(spec.num_experts, -1, piece.shape[1])  # the stacked [experts, rows, cols] form
             nbytes = piece.numel() * piece.element_size()
             if size + nbytes > max_shard_bytes and shards[-1]:
                 shards.append({})
@@ -110,7 +112,10 @@ def load_hf_checkpoint(model_dir: str, flat: torch.Tensor, spec: ModelSpec | Non
     with torch.no_grad():
         for name in layout.entries:
             dst = layout.view(flat, name)
-            for hf_name, a, b in layout.hf_names(name):
+            names = layout.hf_names(name)
+            if any(n not in where for n, _, _ in names) and layout.hf_names_per_expert(name) is not None:
+                names = layout.hf_names_per_expert(name)  # experts stored one tensor each
+            for hf_name, a, b in names:
                 if hf_name not in where:
                     if hf_name == "lm_head.weight" and "model.embed_tokens.weight" in where:
                         src = handles[where["model.embed_tokens.weight"]].get_tensor("model.embed_tokens.weight")
@@ -119,6 +124,8 @@ def load_hf_checkpoint(model_dir: str, flat: torch.Tensor, spec: ModelSpec | Non
                         continue
                 else:
                     src = handles[where[hf_name]].get_tensor(hf_name)
+                if src.dim() == 3 and src.numel() == dst[a:b].numel():
+                    src = src.reshape(dst[a:b].shape)  # stacked experts [E, rows, cols]
                 if tuple(src.shape) != tuple(dst[a:b].shape):
                     if src.shape[0] < dst[a:b].shape[0] and name in ("embed", "lm_head"):
                         dst[a : a + src.shape[0]].copy_(src)  # resized vocabulary: extra rows keep their init

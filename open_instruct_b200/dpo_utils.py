@@ -152,7 +152,7 @@ class DPOExperimentConfig(ExperimentConfig, ModelConfig, DPOConfig, DPOTrainingC
             raise ValueError("cp_degree > 1: the preference trainer sums log-probs per sequence on one rank and has no context-parallel "
                              "path; use tensor_parallel_degree or shard_parameters for long pairs (SFT and GRPO support sequence parallelism)")
         if self.load_balancing_loss:
-            raise ValueError("load_balancing_loss applies to mixture-of-experts models (OLMoE); the model families built here are dense")
+            raise ValueError("load_balancing_loss is wired into SFT (finetune) for mixture-of-experts models; the preference trainers do not add it")
 
 
 # ---------------------------------------------------------------------------------- losses

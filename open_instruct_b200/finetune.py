@@ -148,8 +148,6 @@ class FlatArguments:
             self.additional_model_arguments = json.loads(self.additional_model_arguments)
         if self.sequence_parallel_size < 1:
             raise ValueError("sequence_parallel_size must be >= 1")
-        if self.load_balancing_loss:
-            raise ValueError("load_balancing_loss applies to mixture-of-experts models (OLMoE); the model families built here are dense")
 
 
 def build_spec(args: FlatArguments):
@@ -240,7 +238,10 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
                         final_lr_ratio=args.final_lr_ratio, gradient_checkpointing=args.gradient_checkpointing, seed=args.seed,
                         sequence_parallel_size=sp, sp_max_tokens=args.max_seq_length * max(1, per_rank) if sp > 1 else 0,
                         offload_optimizer=args.offload_optimizer, shard_parameters=args.shard_parameters,
-                        tensor_parallel_degree=tp, shard_degree=args.fsdp_shard_degree)
+                        tensor_parallel_degree=tp, shard_degree=args.fsdp_shard_degree,
+                        load_balancing_weight=args.load_balancing_weight if args.load_balancing_loss else 0.0)
+    if args.load_balancing_loss and not spec.num_experts:
+        raise ValueError("load_balancing_loss applies to mixture-of-experts models (OLMoE); this model is dense")
     learner = Learner(spec, cfg, device=device)
     src = args.model_name_or_path
     if src and os.path.isdir(src) and os.path.exists(os.path.join(src, "config.json")):

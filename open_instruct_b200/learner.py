@@ -49,6 +49,7 @@ class LearnerConfig:
     # Tensor parallelism of the training engine: groups of this many consecutive ranks split every layer (heads and MLP
     # channels); data parallelism and the optimizer sharding run across the groups.
     tensor_parallel_degree: int = 1
+    load_balancing_weight: float = 0.0  # mixture of experts: weight of the router's load-balancing loss added to the SFT loss
     optimizer_type: str = "adamw"     # "adamw" | "muon" (orthogonalised momentum for the decoder layers' matrices, AdamW elsewhere)
     optimizer_kwargs: dict = field(default_factory=dict)  # Muon: mu, nesterov, ns_steps, adamw_lr_scale
 
@@ -80,7 +81,7 @@ class Learner:
         self.device = torch.device(device)
         ops = cfg.ops
         if ops == "auto":
-            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts
                               and torch.cuda.get_device_capability(self.device)[0] == 10) else "ref"
         self.ops = ops
         dtype = cfg.dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
@@ -377,6 +378,11 @@ class Learner:
         total = -logp.sum()
         # "mean": the sp ranks' partial sums add up in the gradient exchange, which then divides by the world size
         loss = total * self.sp / n.clamp(min=1) if reduce_loss == "mean" else total
+        aux = getattr(self.model, "aux_loss", None)
+        if aux is not None and self.cfg.load_balancing_weight:
+            # mixture of experts: keep the router from collapsing onto few experts (``open_instruct/finetune.py:817-819``)
+            loss = loss + self.cfg.load_balancing_weight * aux
+            self.last_aux_loss = aux.detach()
         if self.sp > 1:
             n = self.local_slice(batch["labels_shifted"] != IGNORE).sum()
         self.backward(loss, last=last)

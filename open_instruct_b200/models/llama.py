@@ -54,6 +54,22 @@ class _LayerStash:
     act: torch.Tensor | None = None
 
 
+def load_balancing_loss(router_logits: list, num_experts: int, top_k: int):
+    """Switch-Transformer auxiliary loss over the router logits of all layers of one forward (what transformers returns as
+    ``aux_loss`` for OLMoE and the reference adds to the SFT loss, ``open_instruct/finetune.py:817-819``): ``num_experts *
+    sum_e f_e * P_e`` with ``f_e`` the share of (token, rank) assignments that went to expert e, per top-k rank, and ``P_e`` the
+    mean router probability of e."""
+    if not router_logits:
+        return None
+    logits = torch.cat(list(router_logits), dim=0).float()
+    probs = torch.softmax(logits, dim=-1)
+    _, sel = probs.topk(top_k, dim=-1)
+    mask = torch.nn.functional.one_hot(sel, num_experts).float()       # [N, k, E]
+    tokens_per_expert = mask.mean(dim=0)                                  # [k, E]
+    prob_per_expert = probs.mean(dim=0)                                   # [E]
+    return (tokens_per_expert * prob_per_expert[None, :]).sum() * num_experts
+
+
 class LlamaModel:
     """Weights + forward/backward engine.  Not an ``nn.Module``: state is one flat tensor."""
 
@@ -74,9 +90,10 @@ class LlamaModel:
                 raise ValueError("the fused path runs bf16 on CUDA")
             if spec.head_dim != 128:
                 raise NotImplementedError("fused attention is built for head_dim 128")
-            if spec.post_norm or spec.qk_norm_full:
-                raise NotImplementedError("the fused layer engine is built for pre-norm blocks (Llama, Qwen, Mistral); OLMo-2 / OLMo-3 "
-                                          "blocks (norm after the sub-layer, q/k norm over all heads) run with ops='ref'")
+            if spec.post_norm or spec.qk_norm_full or spec.num_experts:
+                raise NotImplementedError("the fused layer engine is built for dense pre-norm blocks (Llama, Qwen, Mistral); OLMo-2 / OLMo-3 "
+                                          "blocks (norm after the sub-layer, q/k norm over all heads) and mixture-of-experts layers "
+                                          "run with ops='ref'")
             from ..ops import lib
 
             if not lib.available():
@@ -254,9 +271,38 @@ class LlamaModel:
                                       "which is not built: every layer here attends to the whole document")
         v = self._ref_params()  # autograd views of the single leaf
         x = v["embed"][input_ids]
+        self._router_logits = [] if s.num_experts else None
         for i in range(s.num_layers):
             x = self._ref_layer(x, v, i, position_ids, cu_seqlens)
+        # mixture of experts: the load-balancing loss of THIS forward (a differentiable scalar), for the trainer to add
+        self.aux_loss = load_balancing_loss(self._router_logits, s.num_experts, s.num_experts_per_tok) if s.num_experts else None
         return ref.rmsnorm(x, v["final_norm"], s.rms_norm_eps)
+
+    def ref_mlp(self, n2, v, i):
+        """The layer's feed-forward on normed input ``n2``: one SwiGLU MLP, or (mixture of experts) the router's top-k experts,
+        each token's expert outputs weighted by the router's softmax probabilities."""
+        s = self.spec
+        if not s.num_experts:
+            return ref.linear(ref.swiglu(ref.linear(n2, v[f"l{i}.w_gate_up"])), v[f"l{i}.w_down"])
+        E, F, D, k = s.num_experts, s.intermediate_size, s.hidden_size, s.num_experts_per_tok
+        logits = ref.linear(n2, v[f"l{i}.router"])                      # [T, E]
+        if getattr(self, "_router_logits", None) is not None:
+            self._router_logits.append(logits)
+        probs = torch.softmax(logits.float(), dim=-1)
+        top_w, top_e = probs.topk(k, dim=-1)
+        if s.norm_topk_prob:
+            top_w = top_w / top_w.sum(-1, keepdim=True)
+        top_w = top_w.to(n2.dtype)
+        w_gu = v[f"l{i}.w_gate_up"].view(E, 2 * F, D)
+        w_dn = v[f"l{i}.w_down"].view(E, D, F)
+        out = torch.zeros_like(n2)
+        for e in range(E):
+            tok, slot = torch.where(top_e == e)
+            if tok.numel() == 0:
+                continue
+            y = ref.linear(ref.swiglu(ref.linear(n2[tok], w_gu[e])), w_dn[e])
+            out = out.index_add(0, tok, y * top_w[tok, slot, None])
+        return out
 
     def ref_qkv(self, n1, v, i):
         """QKV projection of the PyTorch path with the family's extras: Qwen2-style bias, Qwen3 / OLMo-2 per-head RMSNorm of
@@ -287,8 +333,7 @@ class LlamaModel:
             qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
             attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim)
             x = x + ref.rmsnorm(ref.linear(attn, v[f"l{i}.wo"]), v[f"l{i}.attn_norm"], s.rms_norm_eps)
-            act = ref.swiglu(ref.linear(x, v[f"l{i}.w_gate_up"]))
-            return x + ref.rmsnorm(ref.linear(act, v[f"l{i}.w_down"]), v[f"l{i}.mlp_norm"], s.rms_norm_eps)
+            return x + ref.rmsnorm(self.ref_mlp(x, v, i), v[f"l{i}.mlp_norm"], s.rms_norm_eps)
         n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
         if tp is not None:
             n1 = tp.enter(n1)
@@ -300,8 +345,9 @@ class LlamaModel:
         n2 = ref.rmsnorm(x, v[f"l{i}.mlp_norm"], s.rms_norm_eps)
         if tp is not None:
             n2 = tp.enter(n2)
-        act = ref.swiglu(ref.linear(n2, v[f"l{i}.w_gate_up"]))
-        d = ref.linear(act, v[f"l{i}.w_down"])
+        if s.num_experts and tp is not None:
+            raise NotImplementedError("tensor parallelism is not built for mixture-of-experts layers")
+        d = self.ref_mlp(n2, v, i)
         return x + (tp.sum_partials(d) if tp is not None else d)
 
     # ------------------------------------------------------------------ fused path

@@ -45,6 +45,12 @@ class ModelSpec:
     qk_norm: bool = False  # RMSNorm of q and k before RoPE: per head (Qwen3), or over the whole projection (``qk_norm_full``)
     qk_norm_full: bool = False  # OLMo-2 / OLMo-3: one norm over all heads of q (weight [q_dim]) and one over all heads of k
     post_norm: bool = False     # OLMo-2 / OLMo-3 block: h += norm(attn(h)); h += norm(mlp(h)) instead of norming the inputs
+    # mixture of experts (OLMoE): every decoder layer's MLP is ``num_experts`` SwiGLU experts of width ``intermediate_size`` behind
+    # a linear router; a token goes to its ``num_experts_per_tok`` best experts, weighted by their softmax probabilities
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    norm_topk_prob: bool = False
+    router_aux_loss_coef: float = 0.01
     sliding_window: int | None = None  # some layers attend to the last N tokens only (OLMo-3, Mistral v0.1): documents up to N are exact
     attention_bias: bool = False  # Qwen2 style q/k/v bias
     model_type: str = "llama"
@@ -87,8 +93,12 @@ class ModelSpec:
             rope_scaling=_rope_scaling_of(cfg),
             max_position_embeddings=cfg.get("max_position_embeddings", 8192),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            qk_norm=mt in ("qwen3", "olmo2", "olmo3"),
-            qk_norm_full=mt in ("olmo2", "olmo3"),
+            qk_norm=mt in ("qwen3", "olmo2", "olmo3", "olmoe"),
+            qk_norm_full=mt in ("olmo2", "olmo3", "olmoe"),
+            num_experts=cfg.get("num_experts", 0) if mt == "olmoe" else 0,
+            num_experts_per_tok=cfg.get("num_experts_per_tok", 0) if mt == "olmoe" else 0,
+            norm_topk_prob=bool(cfg.get("norm_topk_prob", False)),
+            router_aux_loss_coef=cfg.get("router_aux_loss_coef", 0.01),
             post_norm=mt in ("olmo2", "olmo3"),
             sliding_window=cfg.get("sliding_window") if (mt == "olmo3" or cfg.get("use_sliding_window", mt == "mistral")) else None,
             attention_bias=cfg.get("attention_bias", mt == "qwen2"),
@@ -104,7 +114,8 @@ class ModelSpec:
 
     def to_hf_config(self) -> dict:
         arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                "mistral": "MistralForCausalLM", "olmo2": "Olmo2ForCausalLM", "olmo3": "Olmo3ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+                "mistral": "MistralForCausalLM", "olmo2": "Olmo2ForCausalLM", "olmo3": "Olmo3ForCausalLM",
+                "olmoe": "OlmoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
         cfg = {
             "architectures": [arch],
             "model_type": self.model_type,
@@ -132,6 +143,9 @@ class ModelSpec:
             "pad_token_id": self.pad_token_id,
             "use_cache": True,
         }
+        if self.num_experts:
+            cfg.update({"num_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok, "norm_topk_prob": self.norm_topk_prob,
+                        "router_aux_loss_coef": self.router_aux_loss_coef})
         return cfg
 
     def replace(self, **kw) -> "ModelSpec":
@@ -226,8 +240,13 @@ class ParamLayout:
         for i in range(s.num_layers):
             add(f"l{i}.wqkv", (s.qkv_dim, s.hidden_size), True)
             add(f"l{i}.wo", (s.hidden_size, s.q_dim), True)
-            add(f"l{i}.w_gate_up", (2 * s.intermediate_size, s.hidden_size), True)
-            add(f"l{i}.w_down", (s.hidden_size, s.intermediate_size), True)
+            if s.num_experts:  # experts stacked along the rows: expert e owns rows [e * 2F, (e + 1) * 2F) / [e * D, (e + 1) * D)
+                add(f"l{i}.router", (s.num_experts, s.hidden_size), True)
+                add(f"l{i}.w_gate_up", (s.num_experts * 2 * s.intermediate_size, s.hidden_size), True)
+                add(f"l{i}.w_down", (s.num_experts * s.hidden_size, s.intermediate_size), True)
+            else:
+                add(f"l{i}.w_gate_up", (2 * s.intermediate_size, s.hidden_size), True)
+                add(f"l{i}.w_down", (s.hidden_size, s.intermediate_size), True)
         if with_lm_head and not s.tie_word_embeddings:
             add("lm_head", (s.vocab_size, s.hidden_size), True)
         self.decay_end = off
@@ -249,6 +268,22 @@ class ParamLayout:
     def views(self, flat) -> dict:
         return {n: self.view(flat, n) for n in self.entries}
 
+    def hf_names_per_expert(self, name: str) -> list[tuple[str, int, int]] | None:
+        """The per-expert spelling of a stacked expert entry (``mlp.experts.<e>.gate_proj.weight`` ...: what checkpoints
+        written before transformers 5 carry), or None for every other entry."""
+        s = self.spec
+        if not s.num_experts or "." not in name:
+            return None
+        layer, leaf = name.split(".", 1)
+        p = f"model.layers.{int(layer[1:])}.mlp.experts."
+        F, D = s.intermediate_size, s.hidden_size
+        if leaf == "w_gate_up":
+            return [x for e in range(s.num_experts) for x in ((f"{p}{e}.gate_proj.weight", e * 2 * F, e * 2 * F + F),
+                                                              (f"{p}{e}.up_proj.weight", e * 2 * F + F, (e + 1) * 2 * F))]
+        if leaf == "w_down":
+            return [(f"{p}{e}.down_proj.weight", e * D, (e + 1) * D) for e in range(s.num_experts)]
+        return None
+
     # ---- Hugging Face tensor names <-> fused entries
     def hf_names(self, name: str) -> list[tuple[str, int, int]]:
         """For a fused entry: list of (hf_name, row_start, row_end) slices that make it up."""
@@ -267,6 +302,12 @@ class ParamLayout:
                     (p + f"self_attn.v_proj.{suf}", s.q_dim + s.kv_dim, s.qkv_dim)]
         if leaf == "wo":
             return [(p + "self_attn.o_proj.weight", 0, s.hidden_size)]
+        if s.num_experts and leaf == "router":
+            return [(p + "mlp.gate.weight", 0, s.num_experts)]
+        if s.num_experts and leaf == "w_gate_up":   # one stacked tensor [E, 2F, D]: the 2-D entry is its reshape
+            return [(p + "mlp.experts.gate_up_proj", 0, s.num_experts * 2 * s.intermediate_size)]
+        if s.num_experts and leaf == "w_down":      # [E, D, F]
+            return [(p + "mlp.experts.down_proj", 0, s.num_experts * s.hidden_size)]
         if leaf == "w_gate_up":
             return [(p + "mlp.gate_proj.weight", 0, s.intermediate_size),
                     (p + "mlp.up_proj.weight", s.intermediate_size, 2 * s.intermediate_size)]

@@ -182,7 +182,7 @@ class RolloutEngine:
         self.spec = spec
         self.device = torch.device(device)
         if ops == "auto":
-            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and lib.available()) else "ref"
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts and lib.available()) else "ref"
         self.ops = ops
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, seed=seed, flat=flat)
@@ -464,7 +464,7 @@ class RolloutEngine:
             o = ref.linear(attn, p[f"l{i}.wo"])
             x = x + (ref.rmsnorm(o, p[f"l{i}.attn_norm"], s.rms_norm_eps) if s.post_norm else o)
             n2 = x if s.post_norm else ref.rmsnorm(x, p[f"l{i}.mlp_norm"], s.rms_norm_eps)
-            d = ref.linear(ref.swiglu(ref.linear(n2, p[f"l{i}.w_gate_up"])), p[f"l{i}.w_down"])
+            d = self.model.ref_mlp(n2, p, i)  # dense SwiGLU, or the router's experts
             x = x + (ref.rmsnorm(d, p[f"l{i}.mlp_norm"], s.rms_norm_eps) if s.post_norm else d)
         return ref.rmsnorm(x, p["final_norm"], s.rms_norm_eps)
 

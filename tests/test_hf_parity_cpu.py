@@ -21,6 +21,7 @@ FAMILIES = {
     "mistral": ("Mistral", dict(sliding_window=None)),
     "olmo2": ("Olmo2", {}),
     "olmo3": ("Olmo3", dict(sliding_window=4096)),
+    "olmoe": ("Olmoe", dict(intermediate_size=96, num_key_value_heads=4, num_experts=4, num_experts_per_tok=2)),
 }
 
 
@@ -64,7 +65,7 @@ def test_checkpoint_import_gives_hf_logits(family):
     assert (_our_logits(ours, ids) - want).abs().max().item() < 1e-5
 
 
-@pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2"])
+@pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2", "olmoe"])
 def test_checkpoint_export_is_read_by_hf(family):
     from open_instruct_b200.ckpt.hf_io import save_hf_checkpoint
     from open_instruct_b200.models import LlamaModel
@@ -146,3 +147,75 @@ def test_learning_rate_schedules_equal_transformers(kind):
         assert abs(opt.param_groups[0]["lr"] - lr_at(step, 1.0, 100, 10, kind)) < 1e-12, step
         opt.step()
         sch.step()
+
+
+def test_mixture_of_experts_aux_loss_and_per_expert_checkpoints():
+    """OLMoE: the load-balancing loss of a forward equals transformers' ``load_balancing_loss_func`` on the routers' raw logits
+    (the installed transformers feeds that function already-softmaxed values, so its own ``aux_loss`` applies the softmax
+    twice; the definition - and this package - applies it once); a checkpoint that stores one tensor per expert (the spelling
+    older exports use) loads to the same model as the stacked form."""
+    from safetensors.torch import load_file, save_file
+
+    from open_instruct_b200.ckpt.hf_io import load_hf_checkpoint
+    from open_instruct_b200.models import LlamaModel
+    from open_instruct_b200.models.spec import ModelSpec
+
+    hf, cfg = _hf_model(*FAMILIES["olmoe"])
+    ids = torch.randint(0, cfg.vocab_size, (2, 40), generator=torch.Generator().manual_seed(1))
+    raw = []
+    hooks = [layer.mlp.gate.register_forward_pre_hook(lambda mod, args: raw.append(torch.nn.functional.linear(args[0].reshape(-1, args[0].shape[-1]), mod.weight)))
+             for layer in hf.model.layers]
+    with torch.no_grad():
+        want = hf(ids)
+    for h in hooks:
+        h.remove()
+    from transformers.models.olmoe.modeling_olmoe import load_balancing_loss_func
+
+    want_aux = float(load_balancing_loss_func(tuple(raw), 4, 2))
+    with tempfile.TemporaryDirectory() as d:
+        hf.save_pretrained(d, safe_serialization=True)
+        spec = ModelSpec.from_pretrained(d)
+        assert spec.num_experts == 4 and spec.num_experts_per_tok == 2 and spec.qk_norm_full and not spec.post_norm
+        ours = LlamaModel(spec, device="cpu", dtype=torch.float32, ops="ref")
+        load_hf_checkpoint(d, ours.flat.detach(), spec, strict=True)
+        # rewrite the weight file with one tensor per expert
+        import os
+
+        sd = load_file(os.path.join(d, "model.safetensors"))
+        per = {}
+        for k, t in sd.items():
+            if k.endswith("experts.gate_up_proj"):
+                for e in range(t.shape[0]):
+                    g, u = t[e].chunk(2, dim=0)
+                    per[k.replace("gate_up_proj", f"{e}.gate_proj.weight")] = g.contiguous()
+                    per[k.replace("gate_up_proj", f"{e}.up_proj.weight")] = u.contiguous()
+            elif k.endswith("experts.down_proj"):
+                for e in range(t.shape[0]):
+                    per[k.replace("down_proj", f"{e}.down_proj.weight")] = t[e].contiguous()
+            else:
+                per[k] = t
+        save_file(per, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+        other = LlamaModel(spec, device="cpu", dtype=torch.float32, ops="ref", seed=9)
+        load_hf_checkpoint(d, other.flat.detach(), spec, strict=True)
+    assert torch.equal(other.flat.detach()[: ours.layout.total], ours.flat.detach()[: ours.layout.total])
+    got = _our_logits(ours, ids)
+    assert (got - want.logits).abs().max().item() < 1e-5
+    assert abs(float(ours.aux_loss) - want_aux) < 1e-5
+
+
+def test_sft_on_a_mixture_of_experts_model_with_the_balancing_loss():
+    from open_instruct_b200.data.collate import to_device
+    from open_instruct_b200.data.synthetic import sft_step_batches
+    from open_instruct_b200.learner import Learner, LearnerConfig
+    from open_instruct_b200.models.spec import ModelSpec
+
+    spec = ModelSpec(vocab_size=256, hidden_size=64, intermediate_size=96, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=16, rope_theta=1e4,
+                     max_position_embeddings=512, model_type="olmoe", qk_norm=True, qk_norm_full=True, num_experts=4, num_experts_per_tok=2)
+    lr = Learner(spec, LearnerConfig(ops="auto", learning_rate=3e-3, lr_scheduler_type="constant", load_balancing_weight=0.5), device="cpu")
+    assert lr.ops == "ref"
+    mbs = [to_device(b, "cpu") for b in sft_step_batches(2, 96, spec.vocab_size, seed=0)]
+    losses = [float(lr.sft_step(mbs)["loss"]) for _ in range(8)]
+    assert losses[-1] < losses[0] - 0.3                       # the same batch is learned
+    assert 0.9 < float(lr.last_aux_loss) < 4.0                # 1.0 = perfectly balanced routing, num_experts = collapsed
+    g = lr.model.layout.view(lr.opt.m, "l0.router") if hasattr(lr.opt, "m") and lr.world == 1 else None
+    assert g is None or float(g.abs().sum()) > 0              # the router itself is trained
