@@ -331,7 +331,7 @@ class LlamaModel:
                 raise NotImplementedError("tensor parallelism is not built for post-norm blocks")
             qkv = self.ref_qkv(x, v, i)
             qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
-            attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim)
+            attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=True)
             x = x + ref.rmsnorm(ref.linear(attn, v[f"l{i}.wo"]), v[f"l{i}.attn_norm"], s.rms_norm_eps)
             return x + ref.rmsnorm(self.ref_mlp(x, v, i), v[f"l{i}.mlp_norm"], s.rms_norm_eps)
         n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
@@ -339,7 +339,7 @@ class LlamaModel:
             n1 = tp.enter(n1)
         qkv = self.ref_qkv(n1, v, i)
         qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
-        attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim)
+        attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=bool(s.num_experts))
         o = ref.linear(attn, v[f"l{i}.wo"])
         x = x + (tp.sum_partials(o) if tp is not None else o)
         n2 = ref.rmsnorm(x, v[f"l{i}.mlp_norm"], s.rms_norm_eps)

@@ -62,16 +62,34 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return F.silu(gate_up[..., :f]) * gate_up[..., f:]
 
 
+_FORCE_SDPA = False  # tests flip this to run the fused-attention branch on CPU
+
+
+def _use_sdpa(qkv: torch.Tensor, allow: bool) -> bool:
+    return _FORCE_SDPA or (allow and qkv.is_cuda and qkv.dtype in (torch.bfloat16, torch.float16))
+
+
 def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                     scale: float | None = None) -> torch.Tensor:
-    """Causal attention per document over packed tokens, explicit softmax (fp32)."""
+                     scale: float | None = None, allow_sdpa: bool = False) -> torch.Tensor:
+    """Causal attention per document over packed tokens: explicit softmax in fp32 (the oracle of the kernel tests; it
+    materialises a [heads, L, L] score matrix per document).  With ``allow_sdpa`` and half-precision inputs on a GPU -
+    models whose only path this is in production (OLMo-2 / OLMo-3 / OLMoE blocks) - PyTorch's fused scaled-dot-product
+    attention per document instead, which does not."""
     T = qkv.shape[0]
     x = qkv.view(T, n_q + 2 * n_kv, head_dim)
     q, k, v = x[:, :n_q], x[:, n_q : n_q + n_kv], x[:, n_q + n_kv :]
     g = n_q // n_kv
     scale = scale if scale is not None else head_dim**-0.5
-    out = torch.empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device)
     bounds = cu_seqlens.tolist()
+    if _use_sdpa(qkv, allow_sdpa):
+        outs = []
+        for s, e in zip(bounds[:-1], bounds[1:]):
+            if e > s:
+                o = torch.nn.functional.scaled_dot_product_attention(q[s:e].transpose(0, 1)[None], k[s:e].transpose(0, 1)[None],
+                                                                     v[s:e].transpose(0, 1)[None], is_causal=True, scale=scale, enable_gqa=g > 1)
+                outs.append(o[0].transpose(0, 1))
+        return torch.cat(outs, dim=0).reshape(T, n_q * head_dim)
+    out = torch.empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device)
     for s, e in zip(bounds[:-1], bounds[1:]):
         if e <= s:
             continue

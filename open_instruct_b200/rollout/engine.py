@@ -543,7 +543,8 @@ class RolloutEngine:
 
             attend = lambda qkv, cu_: f.attn_fwd(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale)[0]
         else:
-            attend = lambda qkv, cu_: ref.attention_varlen(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+            attend = lambda qkv, cu_: ref.attention_varlen(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale,
+                                                           allow_sdpa=bool(s.post_norm or s.num_experts))
         if any(cached):
             # packed layout with the prefixes in place: sequence j occupies rows [o_j, o_j + n_j), its first c_j rows are cached
             offs = [0]

@@ -219,3 +219,23 @@ def test_sft_on_a_mixture_of_experts_model_with_the_balancing_loss():
     assert 0.9 < float(lr.last_aux_loss) < 4.0                # 1.0 = perfectly balanced routing, num_experts = collapsed
     g = lr.model.layout.view(lr.opt.m, "l0.router") if hasattr(lr.opt, "m") and lr.world == 1 else None
     assert g is None or float(g.abs().sum()) > 0              # the router itself is trained
+
+
+def test_fused_attention_branch_of_the_pytorch_path_equals_the_explicit_softmax():
+    """Models that only run on the PyTorch path use PyTorch's fused attention for half-precision GPU tensors; the branch is forced
+    here on CPU and must agree with the explicit-softmax statement, values and gradients, for packed documents with grouped heads."""
+    from open_instruct_b200.ops import ref
+
+    torch.manual_seed(0)
+    Hq, Hkv, Dh = 4, 2, 16
+    qkv = torch.randn(50, (Hq + 2 * Hkv) * Dh, requires_grad=True)
+    cu = torch.tensor([0, 20, 21, 50], dtype=torch.int32)
+    a = ref.attention_varlen(qkv, cu, Hq, Hkv, Dh)
+    ga, = torch.autograd.grad(a.square().sum(), qkv)
+    ref._FORCE_SDPA = True
+    try:
+        b = ref.attention_varlen(qkv, cu, Hq, Hkv, Dh)
+        gb, = torch.autograd.grad(b.square().sum(), qkv)
+    finally:
+        ref._FORCE_SDPA = False
+    assert (a - b).abs().max().item() < 1e-5 and (ga - gb).abs().max().item() < 1e-4
