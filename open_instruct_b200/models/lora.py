@@ -90,12 +90,22 @@ class LoRAAdapters:
 
     # -------------------------------------------------------------- fused path
     @torch.no_grad()
-    def merge_into(self, model, base_flat: torch.Tensor) -> None:
-        """``model.flat <- base + scale * B A`` for every adapted slice (other entries are copied once by the caller)."""
-        base_v, work_v = model.layout.views(base_flat), model.layout.views(model.flat)
+    def merge_into(self, model, base) -> None:
+        """``model.flat <- base + scale * B A`` for every adapted slice (other entries are copied once by the caller).
+        ``base``: the frozen flat parameters, or a ``QuantizedBase`` that dequantises one entry at a time."""
+        work_v = model.layout.views(model.flat)
+        quant = isinstance(base, QuantizedBase)
+        base_v = None if quant else model.layout.views(base)
+        cur_name, cur = None, None
         for module, entry, a, b, _ in self.slots:
+            if quant:
+                if entry != cur_name:
+                    cur_name, cur = entry, base.entry(entry)
+                w0 = cur[a:b]
+            else:
+                w0 = base_v[entry][a:b]
             d = (self.B[module].float() @ self.A[module].float()) * self.scale
-            work_v[entry][a:b].copy_((base_v[entry][a:b].float() + d).to(model.flat.dtype))
+            work_v[entry][a:b].copy_((w0.float() + d).to(model.flat.dtype))
 
     @torch.no_grad()
     def pull_grads(self, model) -> torch.Tensor:
@@ -202,6 +212,25 @@ if __name__ == "__main__":
     main()
 
 
+class QuantizedBase:
+    """The frozen base of a QLoRA run: every adapted 2-D entry as NF4 blocks (``models/nf4.py``, 4.5 bits per weight), handed
+    out dequantised one entry at a time.  Embeddings, the output head and norm weights are not quantised (they stay in the
+    working buffer, which nothing updates)."""
+
+    def __init__(self, model, entries: list[str]):
+        from .nf4 import NF4Tensor
+
+        views = model.layout.views(model.flat.detach())
+        self.q = {name: NF4Tensor(views[name]) for name in entries}
+        self.dtype = model.flat.dtype
+
+    def entry(self, name: str) -> torch.Tensor:
+        return self.q[name].dequantize(torch.float32)
+
+    def nbytes(self) -> int:
+        return sum(t.nbytes() for t in self.q.values())
+
+
 class LoRATrainer:
     """Adapter training around a ``Learner``: the base weights stay frozen, AdamW runs on the adapters only.
 
@@ -209,11 +238,19 @@ class LoRATrainer:
     on the GPU path) and contract it into adapter gradients (``pull_grads``); adapter gradients are summed over ranks, the
     adapters are updated identically everywhere, and the merged weights are written back into the working buffer."""
 
-    def __init__(self, learner, rank: int = 64, alpha: float = 16.0, dropout: float = 0.0, lr: float = 1e-4, weight_decay: float = 0.0):
+    def __init__(self, learner, rank: int = 64, alpha: float = 16.0, dropout: float = 0.0, lr: float = 1e-4, weight_decay: float = 0.0,
+                 quantize_base: bool = False):
+        """``quantize_base`` (QLoRA, ``open_instruct/finetune.py:551-570``): the frozen copy of the adapted matrices is kept as
+        NF4 blocks and the model computes with their dequantised values, so the adapters learn on top of the quantised base."""
         self.learner = learner
         m = learner.model
         self.adapters = LoRAAdapters(m.spec, m.layout, rank, alpha, dropout, device=m.device, dtype=torch.float32, seed=learner.cfg.seed)
-        self.base = m.flat.detach().clone()
+        if quantize_base:
+            self.base = QuantizedBase(m, sorted({entry for _, entry, _, _, _ in self.adapters.slots}))
+            with torch.no_grad():
+                self.adapters.merge_into(m, self.base)  # B = 0: the working copy now holds the NF4-rounded base
+        else:
+            self.base = m.flat.detach().clone()
         self.opt = torch.optim.AdamW([self.adapters.flat], lr=lr, weight_decay=weight_decay)
 
     def step(self, micro_batches: list[dict], lr: float | None = None) -> dict:

@@ -50,8 +50,9 @@ def test_dpo_and_sft_refuse_switches_they_cannot_honour(tmp_path):
     with pytest.raises(ValueError, match="offload_param is not built"):
         DPOExperimentConfig(**base, zero_stage=3, offload_param=True)
     FlatArguments(model_name_or_path="tiny", dataset_mixer_list=["x.jsonl", "1.0"], load_balancing_loss=True)  # accepted; a dense model refuses at start
+    assert FlatArguments(model_name_or_path="tiny", dataset_mixer_list=["x.jsonl", "1.0"], use_qlora=True).use_lora  # QLoRA is built for SFT
     with pytest.raises(ValueError):
-        FlatArguments(model_name_or_path="tiny", dataset_mixer_list=["x.jsonl", "1.0"], use_qlora=True)
+        FlatArguments(model_name_or_path="tiny", dataset_mixer_list=["x.jsonl", "1.0"], use_8bit_optimizer=True)
 
 
 def test_grpo_eval_on_step_0_needs_local_eval():
