@@ -294,3 +294,23 @@ def test_evolving_rubrics_reach_the_prompts_of_later_steps(tmp_path):
                             num_training_steps=2, rubric_judge=judge)
     other.set_state(json.loads(json.dumps(state)))
     assert other.ground_truth_overrides == prep.ground_truth_overrides and other.rubric_manager.buffer.state_dict() == prep.rubric_manager.buffer.state_dict()
+
+
+def test_decode_gemm_plan_fills_one_wave():
+    """The tile chooser of the decode GEMM: every 8B / Qwen3-8B projection becomes ONE wave of at most 74 CTA pairs, K is only
+    split where the consumer can sum planes, no slice is shorter than the load pipeline, and the choices are the ones measured
+    fastest on the GPU (a sweep over all tile shapes and slice counts at M = 64 and 256)."""
+    from open_instruct_b200.ops.fused import DECODE_SPLIT_TILES, DECODE_TILES, decode_gemm_plan, decode_splits
+
+    want = {("qkv", 6144, 4096, False): (96, 1, 1), ("o", 4096, 4096, True): (128, 1, 2), ("gate_up", 28672, 4096, False): (224, 2, 1),
+            ("down", 4096, 14336, True): (256, 1, 4), ("qwen_gate_up", 24576, 4096, False): (192, 2, 1), ("qwen_down", 4096, 12288, True): (256, 1, 4)}
+    for (name, N, K, split), plan in want.items():
+        got = decode_gemm_plan(N, K, split, 256)
+        assert got == plan, (name, got)
+        bns, nsub, S = got
+        assert (bns, nsub) in DECODE_TILES and (S == 1 or (bns, nsub) in DECODE_SPLIT_TILES)
+        assert -(-N // (bns * nsub)) * S <= 74
+        assert decode_splits(K, S) == S and (S == 1 or -(-(-(-K // 64)) // S) >= 8)
+    assert decode_gemm_plan(6144, 4096, False, 256)[2] == 1            # no K split without a plane-summing consumer
+    assert decode_gemm_plan(128, 512, True, 256) == (64, 1, 1)         # tiny weights: splitting only adds planes
+    assert [decode_splits(1000, s) for s in (2, 3, 4, 5, 16)] == [2, 3, 4, 4, 16]
