@@ -239,3 +239,25 @@ def test_fused_attention_branch_of_the_pytorch_path_equals_the_explicit_softmax(
     finally:
         ref._FORCE_SDPA = False
     assert (a - b).abs().max().item() < 1e-5 and (ga - gb).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("cls_name", ["Olmo2", "Qwen3"])
+def test_sft_starts_from_a_hugging_face_folder_and_exports_the_same_architecture(tmp_path, cls_name):
+    """``model_name_or_path`` pointing at a transformers checkpoint: the trainer reads the architecture and the weights from it,
+    and its export loads as the same transformers class.  With a zero learning rate the exported model gives the source
+    model's logits (up to the bf16 the export is written in)."""
+    import os
+
+    from open_instruct_b200.finetune import main
+    from test_finetune_cpu import _args
+
+    hf, cfg = _hf_model(cls_name, dict(vocab_size=600))
+    src = os.path.join(str(tmp_path), "hf")
+    hf.save_pretrained(src, safe_serialization=True)
+    args, tc = _args(str(tmp_path), model_name_or_path=src, num_train_epochs=1, learning_rate=0.0)
+    main(args, tc)
+    back = transformers.AutoModelForCausalLM.from_pretrained(args.output_dir, dtype=torch.float32).eval()
+    assert type(back) is type(hf)
+    ids = torch.randint(0, 300, (2, 20), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        assert (back(ids).logits - hf(ids).logits).abs().max().item() < 0.03
