@@ -110,7 +110,7 @@ def main(args: Args) -> dict:
     if steps_per_epoch == 0:
         raise ValueError(f"dataset has {len(ds)} windows of {L} tokens; one step needs {win_per_step}")
     max_steps = args.max_train_steps or steps_per_epoch * args.num_epochs
-    ops = args.ops if args.ops != "auto" else ("fused" if device.type == "cuda" and spec.head_dim == 128 else "ref")
+    ops = args.ops if args.ops != "auto" else ("fused" if device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts else "ref")
     cfg = LearnerConfig(ops=ops, comm=args.comm_backend if world > 1 else "none", learning_rate=args.learning_rate,
                         weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm, lr_scheduler_type=args.lr_scheduler_type,
                         warmup_steps=int(max_steps * args.warmup_ratio), total_steps=max_steps,

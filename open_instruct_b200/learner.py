@@ -24,7 +24,7 @@ from .utils.common import nvtx_range
 
 @dataclass
 class LearnerConfig:
-    ops: str = "auto"  # "fused" (sm_100a kernels), "ref" (PyTorch), "auto"
+    ops: str = "auto"  # "fused" (sm_100a kernels), "ref" (PyTorch), "auto"; "emulated": the fused path's driver over PyTorch restatements of the kernels (tests)
     comm: str = "auto"  # "fused" (symmetric-memory kernels), "nccl", "none", "auto"
     learning_rate: float = 2e-5
     weight_decay: float = 0.0
@@ -83,11 +83,17 @@ class Learner:
         if ops == "auto":
             ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts
                               and torch.cuda.get_device_capability(self.device)[0] == 10) else "ref"
+        # "emulated": everything below takes the fused path's branches (fp32 main_grad, hand-driven backward) except the ones
+        # that launch a kernel of this package (optimizer kernels, symmetric-memory exchange, the device status word)
+        self.emulated = ops == "emulated"
+        model_ops = ops
+        if self.emulated:
+            ops = "fused"
         self.ops = ops
         dtype = cfg.dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
         comm = cfg.comm
         if comm == "auto":
-            comm = "none" if self.world == 1 else ("fused" if ops == "fused" else "nccl")
+            comm = "none" if self.world == 1 else ("fused" if (ops == "fused" and not self.emulated) else "nccl")
         if self.tp is not None:
             comm = "none" if self.world == 1 else "nccl"   # the data-parallel exchange of a TP shard goes through NCCL
             if cfg.shard_parameters or cfg.sequence_parallel_size > 1:
@@ -114,10 +120,10 @@ class Learner:
         if shard is None and muon:
             shard = False
         if shard is None:
-            shard = (ops == "fused" and self.world > 1 and self.tp is None and
+            shard = (ops == "fused" and not self.emulated and self.world > 1 and self.tp is None and
                      needs_sharding(layout.total, self.world, torch.cuda.get_device_properties(self.device).total_memory, cfg.offload_optimizer))
         if shard:
-            if ops != "fused":
+            if ops != "fused" or self.emulated:
                 raise NotImplementedError("parameter sharding runs on the fused (CUDA) path")
             from .parallel.zero3 import Zero3State
 
@@ -147,7 +153,7 @@ class Learner:
             flat = self.symm.params
         else:
             flat = torch.zeros(n, dtype=dtype, device=self.device)
-        self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, seed=cfg.seed, flat=flat,
+        self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=model_ops, seed=cfg.seed, flat=flat,
                                 gradient_checkpointing=cfg.gradient_checkpointing)
         if flat_init is not None:
             with torch.no_grad():
@@ -164,12 +170,12 @@ class Learner:
 
             self.opt = MuonOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, muon_matrices(layout), lr=cfg.learning_rate,
                                      betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
-                                     group=group, comm=comm, use_kernels=(ops == "fused"), **dict(cfg.optimizer_kwargs or {}))
+                                     group=group, comm=comm, use_kernels=(ops == "fused" and not self.emulated), **dict(cfg.optimizer_kwargs or {}))
         else:
             self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, lr=cfg.learning_rate,
                                      betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay,
                                      max_grad_norm=cfg.max_grad_norm, group=group, comm=comm, symm=self.symm,
-                                     use_kernels=(ops == "fused"), offload=cfg.offload_optimizer,
+                                     use_kernels=(ops == "fused" and not self.emulated), offload=cfg.offload_optimizer,
                                      norm_weights=self.tp.norm_weights(layout) if self.tp is not None else None,
                                      norm_extra_group=self.tp.group if self.tp is not None else None)
         self.global_step = 0
@@ -187,7 +193,7 @@ class Learner:
         self.sp_group = None
         if sp <= 1:
             return
-        if self.ops != "fused":
+        if self.ops != "fused" or self.emulated:
             raise NotImplementedError("sequence parallelism runs on the fused (CUDA) path")
         if self.world % sp:
             raise ValueError(f"sequence_parallel_size {sp} must divide the number of ranks {self.world}")
@@ -256,7 +262,7 @@ class Learner:
         with nvtx_range("optimizer_step"):
             norm = self.opt.step(grad, lr=self.lr(), grad_scale=grad_scale)
         if self.ops == "fused":
-            if self.world > 1 or self.comm != "none":
+            if self.world > 1 or self.comm != "none" or self.emulated:
                 self.model.main_grad.zero_()
             else:
                 # single rank: AdamW zeroed the (only) shard in place, padding included
@@ -273,7 +279,7 @@ class Learner:
         arrived (the reduce-scatter then summed unfinished buffers) raises here - before the next step runs and before a
         checkpoint of the diverged state can be written.  Ranks that wait on peers read it now (one small device
         synchronisation per optimizer step); a single rank only has its own pipeline waits and uses the non-blocking form."""
-        if self.ops != "fused":
+        if self.ops != "fused" or self.emulated:
             return
         from .ops import lib
 

@@ -1,4 +1,5 @@
-"""Decoder-only transformer (Llama / Qwen / Mistral block structure) over a flat parameter buffer.
+"""Decoder-only transformer (Llama / Qwen / Mistral pre-norm blocks, OLMo-2 / OLMo-3 post-norm blocks, OLMoE mixture of experts)
+over a flat parameter buffer.
 
 Two execution paths share the same weights:
 
@@ -8,8 +9,11 @@ Two execution paths share the same weights:
   the flat ``main_grad`` buffer), varlen packed attention, fused residual-add RMSNorm, in-place
   RoPE, SwiGLU and the in-place log-prob gradient.  Cheap ops (RMSNorm output, SwiGLU
   activation) are recomputed in the backward instead of stored.
+  Post-norm blocks (``h = x + norm(attn(x))``) run through the same kernels; mixture-of-experts layers do not.
 * ``ops="ref"`` - plain PyTorch autograd over the same buffer; runs on CPU (fp32) and is the
   oracle the fused path is tested against, and the compute path of the library baseline.
+* ``ops="emulated"`` - the fused path's driver with every kernel replaced by its PyTorch restatement
+  (``open_instruct_b200.ops.emulated``): any device and dtype; the CPU test bed of the driver's bookkeeping.
 
 The public entry points return per-token log-probabilities (or final hidden states) that are
 differentiable with respect to the flat parameter buffer on both paths, so SFT, DPO, GRPO and
@@ -52,6 +56,8 @@ class _LayerStash:
     n1: torch.Tensor | None = None         # kept instead of recomputed when ``keep_cheap_activations``
     n2: torch.Tensor | None = None
     act: torch.Tensor | None = None
+    o: torch.Tensor | None = None          # post-norm blocks: the attention sub-layer's output before its norm
+    d: torch.Tensor | None = None          # post-norm blocks: the feed-forward sub-layer's output before its norm
 
 
 def load_balancing_loss(router_logits: list, num_experts: int, top_k: int):
@@ -76,8 +82,13 @@ class LlamaModel:
     def __init__(self, spec: ModelSpec, device="cpu", dtype=torch.float32, ops: str = "ref", seed: int = 0,
                  init: str = "normal", with_lm_head: bool = True, flat: torch.Tensor | None = None,
                  gradient_checkpointing: bool = False, sharded: bool = False):
-        if ops not in ("ref", "fused"):
-            raise ValueError("ops must be 'ref' or 'fused'")
+        if ops not in ("ref", "fused", "emulated"):
+            raise ValueError("ops must be 'ref', 'fused' or 'emulated'")
+        # "emulated": the fused path's hand-driven forward / backward with every kernel replaced by its PyTorch restatement
+        # (``ops.emulated``), on any device and dtype - the CPU test bed of the driver; everything else sees ops == "fused"
+        self.emulated = ops == "emulated"
+        if self.emulated:
+            ops = "fused"
         self.spec = spec
         self.ops = ops
         self.device = torch.device(device)
@@ -85,15 +96,20 @@ class LlamaModel:
         self.layout = ParamLayout(spec, with_lm_head=with_lm_head)
         self.with_lm_head = with_lm_head
         self.gradient_checkpointing = gradient_checkpointing
-        if ops == "fused":
+        if self.emulated:
+            from ..ops import emulated
+
+            self.kernels = emulated
+            if spec.num_experts:
+                raise NotImplementedError("mixture-of-experts layers run with ops='ref'")
+        elif ops == "fused":
+            self.kernels = _fused()
             if dtype != torch.bfloat16 or self.device.type != "cuda":
                 raise ValueError("the fused path runs bf16 on CUDA")
             if spec.head_dim != 128:
                 raise NotImplementedError("fused attention is built for head_dim 128")
-            if spec.post_norm or spec.qk_norm_full or spec.num_experts:
-                raise NotImplementedError("the fused layer engine is built for dense pre-norm blocks (Llama, Qwen, Mistral); OLMo-2 / OLMo-3 "
-                                          "blocks (norm after the sub-layer, q/k norm over all heads) and mixture-of-experts layers "
-                                          "run with ops='ref'")
+            if spec.num_experts:
+                raise NotImplementedError("the fused layer engine is built for dense blocks; mixture-of-experts layers run with ops='ref'")
             from ..ops import lib
 
             if not lib.available():
@@ -191,10 +207,10 @@ class LlamaModel:
             self.flat.requires_grad_(True)
 
     def logit_workspace(self, rows: int, vocab: int) -> torch.Tensor:
-        """One reused bf16 ``[rows, vocab]`` buffer for the chunked lm_head (allocated on first use)."""
+        """One reused ``[rows, vocab]`` buffer (bf16 on the kernel path) for the chunked lm_head (allocated on first use)."""
         ws = getattr(self, "_logit_ws", None)
         if ws is None or ws.shape[0] < rows or ws.shape[1] != vocab:
-            ws = self._logit_ws = torch.empty(rows, vocab, dtype=torch.bfloat16, device=self.device)
+            ws = self._logit_ws = torch.empty(rows, vocab, dtype=self.dtype, device=self.device)
         return ws
 
     def layer_grad_range(self, i: int) -> tuple[int, int]:
@@ -252,7 +268,7 @@ class LlamaModel:
         h, _ = self._fused_forward_hidden(input_ids, position_ids, cu_seqlens, keep=False)
         if self.zero3 is not None:
             self.zero3.head()
-        return _fused().gemm(h, self.lm_head_weight())
+        return self.kernels.gemm(h, self.lm_head_weight())
 
     # ------------------------------------------------------------------ ref path
     def _ref_params(self) -> dict:
@@ -353,7 +369,7 @@ class LlamaModel:
     # ------------------------------------------------------------------ fused path
     def _fused_forward_hidden(self, input_ids, position_ids, cu_seqlens, keep: bool):
         """Runs the stack; returns final-norm hidden states.  ``keep`` stores what backward needs."""
-        f = _fused()
+        f = self.kernels
         s, p = self.spec, self.p
         pos = position_ids.to(torch.int32)
         cu = cu_seqlens.to(torch.int32)
@@ -372,6 +388,13 @@ class LlamaModel:
         for i in range(s.num_layers):
             if z is not None:
                 z.layer_fwd(i)  # layer i's parameters are in their workspace; the next layer's gather is under way
+            if s.post_norm:
+                st = self._post_norm_layer(i, stream, pos, cu)
+                stream = st.h_mid + st.n2   # n2 holds norm(d) until here
+                st.n2 = None
+                if keep:
+                    stash.append(_LayerStash(st.h_in, None, None, None, None, None, None, None) if self.gradient_checkpointing else st)
+                continue
             n1, h_in, rstd1 = f.rmsnorm_fwd(delta if delta is not None else stream, p[f"l{i}.attn_norm"], s.rms_norm_eps,
                                             res=stream if delta is not None else None)
             qkv, attn, lse, attn_tok = self._attention_block(i, n1, pos, cu)
@@ -395,17 +418,84 @@ class LlamaModel:
                 else:
                     stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk, n1, n2, act))
             del n1, n2, act
-        nf, h_last, rstd_f = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
+        if delta is None:   # post-norm blocks leave no pending contribution: the stream is complete
+            nf, h_last, rstd_f = f.rmsnorm_fwd(stream, p["final_norm"], s.rms_norm_eps)
+        else:
+            nf, h_last, rstd_f = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
         state = None
         if keep:
             state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu, "rope_tab": self._rope_tab}
         return nf, state
 
+    def _post_norm_layer(self, i: int, x, pos, cu) -> _LayerStash:
+        """Forward of an OLMo-2 / OLMo-3 block: ``h = x + norm(attn(x))``, ``out = h + norm(mlp(h))`` - the sub-layers read the
+        stream as it is and their OUTPUT is normalised.  Returns the stash of the layer with ``n2`` holding ``norm(mlp(h))``
+        (the caller adds it to ``h_mid`` to form the layer's output)."""
+        f = self.kernels
+        s, p = self.spec, self.p
+        if self.tp is not None:
+            raise NotImplementedError("tensor parallelism is not built for post-norm blocks")
+        qkv, attn, lse, attn_tok = self._attention_block(i, x, pos, cu)
+        o = f.gemm(attn_tok if attn_tok is not None else attn, p[f"l{i}.wo"])
+        a_n, _, rstd1 = f.rmsnorm_fwd(o, p[f"l{i}.attn_norm"], s.rms_norm_eps)
+        h_mid = x + a_n
+        del a_n
+        gate_up = f.gemm(h_mid, p[f"l{i}.w_gate_up"])
+        act = f.swiglu_fwd(gate_up)
+        d = f.gemm(act, p[f"l{i}.w_down"])
+        m_n, _, rstd2 = f.rmsnorm_fwd(d, p[f"l{i}.mlp_norm"], s.rms_norm_eps)
+        keep_act = self.keep_cheap_activations and not self.gradient_checkpointing
+        return _LayerStash(x, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk, None, m_n, act if keep_act else None, o, d)
+
+    def _post_norm_layer_bwd(self, i: int, st: _LayerStash, d_out, pos, cu, wgrad_mode):
+        """Backward of ``_post_norm_layer``: gradient of the layer's output in, gradient of its input out."""
+        f = self.kernels
+        s, p, g, sp = self.spec, self.p, self.g, self.sp
+        scale = s.head_dim ** -0.5
+        # ---- out = h_mid + norm(d),  d = down(swiglu(gate_up(h_mid)))
+        d_d = f.rmsnorm_bwd(st.d, p[f"l{i}.mlp_norm"], st.rstd2, d_out, None, g[f"l{i}.mlp_norm"])
+        st.d = None
+        act = st.act if st.act is not None else f.swiglu_fwd(st.gate_up)
+        st.act = None
+        f.gemm(d_d, act, g[f"l{i}.w_down"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+        d_act = f.gemm(d_d, p[f"l{i}.w_down"], b_mn=True)
+        del act, d_d
+        dgu = f.swiglu_bwd_(st.gate_up, d_act)
+        del d_act
+        f.gemm(dgu, st.h_mid, g[f"l{i}.w_gate_up"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+        d_mid = f.gemm(dgu, p[f"l{i}.w_gate_up"], b_mn=True)
+        del dgu
+        d_mid.add_(d_out)
+        del d_out
+        # ---- h_mid = x + norm(o),  o = wo(attn(rope(wqkv(x))))
+        d_o = f.rmsnorm_bwd(st.o, p[f"l{i}.attn_norm"], st.rstd1, d_mid, None, g[f"l{i}.attn_norm"])
+        st.o = None
+        f.gemm(d_o, st.attn_tok if sp is not None else st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+        if sp is None:
+            d_attn = f.gemm(d_o, p[f"l{i}.wo"], b_mn=True)
+            dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+            del d_attn
+            f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True, table=self._rope_tab)
+            self._qkv_bias_and_norm_bwd_(dqkv, i, st.qk)
+        else:
+            d_attn = sp.d_attn_project(d_o, p[f"l{i}.wo"], pos.numel())
+            dqkv_heads = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, sp.hq_l, sp.hk_l, s.head_dim, scale)
+            f.rope_(dqkv_heads, pos, self.inv_freq, sp.hq_l, sp.hk_l, s.head_dim, backward=True, table=self._rope_tab)
+            self._qkv_bias_and_norm_bwd_(dqkv_heads, i, st.qk, sp.hq_l, sp.hk_l, bias=False)
+            dqkv = sp.dqkv_exchange(dqkv_heads)
+            if s.attention_bias:
+                g[f"l{i}.bqkv"].add_(dqkv.float().sum(0))
+        del d_o
+        f.gemm(dqkv, st.h_in, g[f"l{i}.wqkv"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+        d_x = f.gemm(dqkv, p[f"l{i}.wqkv"], b_mn=True)
+        d_x.add_(d_mid)
+        return d_x
+
     def _attention_block(self, i: int, n1, pos, cu):
         """QKV projection, RoPE and attention of layer ``i``.  Returns ``(qkv, attn, lse, attn_tok)``; with sequence
         parallelism ``qkv``/``attn`` cover all tokens for this rank's heads and ``attn_tok`` this rank's tokens for all
         heads (else ``attn_tok`` is None)."""
-        f = _fused()
+        f = self.kernels
         s, p, sp = self.spec, self.p, self.sp
         scale = s.head_dim ** -0.5
         if sp is None:
@@ -426,7 +516,7 @@ class LlamaModel:
         output (before RoPE).  Returns what the backward needs (``None`` when the model has neither).  ``hq`` / ``hk``:
         query / key heads in a row of ``qkv`` (sequence parallelism: this rank's heads only, ``cols`` then indexes their
         columns in the full fused width for the bias)."""
-        f = _fused()
+        f = self.kernels
         s, p = self.spec, self.p
         hq = s.num_heads if hq is None else hq
         hk = s.num_kv_heads if hk is None else hk
@@ -436,8 +526,12 @@ class LlamaModel:
             return None
         T = qkv.shape[0]
         out = []
+        if s.qk_norm_full and (hq != s.num_heads or hk != s.num_kv_heads):
+            raise NotImplementedError("a q/k norm over all heads (OLMo-2 / OLMo-3) cannot run on a rank that holds only some heads: "
+                                      "sequence parallelism is not built for these models")
+        rows = (lambda heads: T) if s.qk_norm_full else (lambda heads: T * heads)   # one norm per row, or one per head
         for lo, heads, name in ((0, hq, "q_norm"), (hq * s.head_dim, hk, "k_norm")):
-            pre = qkv[:, lo:lo + heads * s.head_dim].contiguous().view(T * heads, s.head_dim)
+            pre = qkv[:, lo:lo + heads * s.head_dim].contiguous().view(rows(heads), -1)
             y, _, rstd = f.rmsnorm_fwd(pre, p[f"l{i}.{name}"], s.rms_norm_eps)
             qkv[:, lo:lo + heads * s.head_dim].copy_(y.view(T, heads * s.head_dim))
             out += [pre, rstd]
@@ -447,14 +541,14 @@ class LlamaModel:
         """Backward of ``qkv_bias_and_norm_`` in place on ``dqkv`` (after the RoPE backward); accumulates the norm and
         bias gradients.  ``bias=False``: the caller adds the bias gradient itself (sequence parallelism does it after the
         exchange, on full-width rows)."""
-        f = _fused()
+        f = self.kernels
         s, g, p = self.spec, self.g, self.p
         hq = s.num_heads if hq is None else hq
         hk = s.num_kv_heads if hk is None else hk
         T = dqkv.shape[0]
         if qk is not None:
             for (lo, heads, name), pre, rstd in (((0, hq, "q_norm"), qk[0], qk[1]), ((hq * s.head_dim, hk, "k_norm"), qk[2], qk[3])):
-                dy = dqkv[:, lo:lo + heads * s.head_dim].contiguous().view(T * heads, s.head_dim)
+                dy = dqkv[:, lo:lo + heads * s.head_dim].contiguous().view(pre.shape)
                 dx = f.rmsnorm_bwd(pre, p[f"l{i}.{name}"], rstd, dy, None, g[f"l{i}.{name}"])
                 dqkv[:, lo:lo + heads * s.head_dim].copy_(dx.view(T, heads * s.head_dim))
         if s.attention_bias and bias:
@@ -462,8 +556,12 @@ class LlamaModel:
 
     def _recompute_layer(self, i: int, st: _LayerStash, pos, cu) -> _LayerStash:
         """Gradient checkpointing: rebuild a layer's activations from its input stream."""
-        f = _fused()
+        f = self.kernels
         s, p = self.spec, self.p
+        if s.post_norm:
+            st = self._post_norm_layer(i, st.h_in, pos, cu)
+            st.n2 = None
+            return st
         n1, _, rstd1 = f.rmsnorm_fwd(st.h_in, p[f"l{i}.attn_norm"], s.rms_norm_eps)
         qkv, attn, lse, attn_tok = self._attention_block(i, n1, pos, cu)
         o = f.gemm(attn_tok if attn_tok is not None else attn, p[f"l{i}.wo"])
@@ -475,7 +573,7 @@ class LlamaModel:
 
     def _fused_backward_hidden(self, state: dict, d_nf: torch.Tensor) -> None:
         """Backward from d(final-norm hidden) to the embedding; accumulates into ``main_grad``."""
-        f = _fused()
+        f = self.kernels
         s, p = self.spec, self.p
         self.ensure_main_grad()
         g = self.g
@@ -497,6 +595,13 @@ class LlamaModel:
             if st.qkv is None:
                 st = self._recompute_layer(i, st, pos, cu)
             stash[i] = None
+            if s.post_norm:
+                d_stream = self._post_norm_layer_bwd(i, st, d_stream, pos, cu, wgrad_mode)
+                if z is not None:
+                    z.layer_bwd_done(i)
+                elif self.grad_ready_hook is not None:
+                    self.grad_ready_hook(*self.layer_grad_range(i))
+                continue
             # ---- MLP: out = h_mid + down(swiglu(gate_up(norm(h_mid))))
             act = st.act if st.act is not None else f.swiglu_fwd(st.gate_up)
             st.act = None
@@ -581,7 +686,7 @@ class _FusedLogprobFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, model: LlamaModel, input_ids, position_ids, cu_seqlens, labels, temperature, want_entropy, keep,
                 anchor):
-        f = _fused()
+        f = model.kernels
         needs_grad = keep
         nf, ctx.state = model._fused_forward_hidden(input_ids, position_ids, cu_seqlens, keep=needs_grad)
         if model.sp is not None:  # log-probs of this rank's chunk of the tokens
@@ -634,8 +739,8 @@ class _FusedLogprobFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_logp, _d_ent):
-        f = _fused()
         model = ctx.model
+        f = model.kernels
         nf, logits, lse, labels = ctx.saved_tensors
         model.ensure_main_grad()
         head = "embed" if (model.spec.tie_word_embeddings or "lm_head" not in model.p) else "lm_head"

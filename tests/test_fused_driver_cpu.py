@@ -1,0 +1,105 @@
+"""The fused path's hand-driven forward / backward (layer stash, recomputation, chunked output head, in-place gradient
+rewrites) with every kernel replaced by its PyTorch restatement (``ops="emulated"``), against autograd over the plain PyTorch
+path.  The kernels are tested one by one on the GPU; this is the test of what calls them."""
+import pytest
+import torch
+
+from open_instruct_b200.models import LlamaModel, ModelSpec
+from open_instruct_b200.models import llama as llama_mod
+
+BASE = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16)
+OLMO2 = dict(post_norm=True, qk_norm=True, qk_norm_full=True)
+VARIANTS = {
+    "llama": ({}, {}),
+    "llama-checkpointing": ({}, dict(ckpt=True)),
+    "llama-chunked-head-recompute": ({}, dict(chunk=128, keep_cheap=False, temperature=0.7)),
+    "qwen2-bias": (dict(attention_bias=True), {}),
+    "qwen3-head-norm": (dict(qk_norm=True), {}),
+    "tied-embeddings": (dict(tie_word_embeddings=True), {}),
+    "olmo2": (OLMO2, {}),
+    "olmo2-checkpointing": (OLMO2, dict(ckpt=True)),
+    "olmo2-chunked-head-recompute": (OLMO2, dict(chunk=128, keep_cheap=False)),
+    "olmo2-mha": ({**OLMO2, "num_kv_heads": 4}, {}),
+    "post-norm-only": (dict(post_norm=True), {}),
+}
+
+
+def _pair(spec, ckpt=False):
+    a = LlamaModel(spec, ops="ref", seed=1)
+    with torch.no_grad():
+        for v in a.layout.views(a.flat).values():
+            if v.dim() == 1:
+                v.uniform_(0.5, 1.5)  # norm weights and biases away from their trivial initialisation
+    b = LlamaModel(spec, ops="emulated", seed=1, flat=a.flat.detach().clone(), gradient_checkpointing=ckpt)
+    return a, b
+
+
+def _batch(spec, lens=(70, 130, 33), seed=0):
+    g = torch.Generator().manual_seed(seed)
+    T = sum(lens)
+    ids = torch.randint(0, spec.vocab_size, (T,), generator=g)
+    pos = torch.cat([torch.arange(n) for n in lens])
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+    labels = torch.roll(ids, -1)
+    labels[::7] = -100
+    return ids, pos, cu, labels, torch.randn(T, generator=g)
+
+
+@pytest.mark.parametrize("name", list(VARIANTS))
+def test_hand_driven_backward_equals_autograd(name, monkeypatch):
+    extra, opts = VARIANTS[name]
+    spec = ModelSpec(**{**BASE, **extra})
+    a, b = _pair(spec, ckpt=opts.get("ckpt", False))
+    b.keep_cheap_activations = opts.get("keep_cheap", True)
+    if "chunk" in opts:
+        monkeypatch.setattr(llama_mod, "LOGIT_CHUNK_TOKENS", opts["chunk"])
+    ids, pos, cu, labels, wgt = _batch(spec)
+    got = []
+    for m in (a, b):
+        for _ in range(2):  # two micro-batches: gradients accumulate
+            lp, ent = m.token_logprobs(ids, pos, cu, labels, opts.get("temperature", 1.0), want_entropy=True)
+            (lp * wgt).sum().backward()
+        got.append((lp.detach(), ent.detach(), m.grad_flat().clone()))
+    (lp0, e0, g0), (lp1, e1, g1) = got
+    assert (lp0 - lp1).abs().max().item() < 1e-5
+    assert (e0 - e1).abs().max().item() < 1e-5
+    assert g0.abs().max().item() > 1.0
+    for n, e in a.layout.entries.items():
+        d = (g0[e.offset:e.offset + e.numel] - g1[e.offset:e.offset + e.numel]).abs().max().item()
+        assert d < 2e-4, (n, d)
+
+
+def test_hidden_state_bridge_for_the_reward_head():
+    spec = ModelSpec(**{**BASE, **OLMO2})
+    a, b = _pair(spec)
+    ids, pos, cu, _, _ = _batch(spec)
+    w = torch.randn(sum((70, 130, 33)), spec.hidden_size, generator=torch.Generator().manual_seed(3))
+    for m in (a, b):
+        (m.hidden_states(ids, pos, cu) * w).sum().backward()
+    ga, gb = a.grad_flat(), b.grad_flat()
+    assert (ga - gb).abs().max().item() < 1e-5 * ga.abs().max().item()
+
+
+@pytest.mark.parametrize("family", ["llama", "olmo2"])
+def test_learner_steps_on_the_emulated_path_follow_the_pytorch_path(family):
+    """Three optimizer steps of two micro-batches each through ``Learner``: the fused path's branches of the learner (fp32
+    gradient buffer, zeroing after the step, gradient-ready hook around the last backward) give the parameters of the autograd path."""
+    from open_instruct_b200.learner import Learner, LearnerConfig
+
+    spec = ModelSpec(**{**BASE, **(OLMO2 if family == "olmo2" else {})})
+    flats = []
+    for ops in ("ref", "emulated"):
+        ln = Learner(spec, LearnerConfig(ops=ops, learning_rate=1e-2, warmup_steps=0, total_steps=10, max_grad_norm=1.0, seed=4),
+                     device="cpu")
+        for step in range(3):
+            for mb in range(2):
+                ids, pos, cu, labels, _ = _batch(spec, seed=10 * step + mb)
+                batch = {"input_ids": ids, "position_ids": pos, "cu_seq_lens_q": cu, "labels_shifted": labels}
+                ln.sft_micro_step(batch, last=mb == 1)
+            ln.optimizer_step()
+        flats.append(ln.model.flat.detach().clone())
+    # Adam divides by the gradient's own scale, so entries whose gradient is rounding noise may move differently: the bound
+    # is a small fraction of the distance travelled (three steps of 1e-2)
+    assert (flats[0] - flats[1]).abs().max().item() < 1e-3
+    start = LlamaModel(spec, ops="ref", seed=4).flat.detach()   # the learner pads its buffer to a multiple of the world size
+    assert (flats[0][: start.numel()] - start).abs().max().item() > 1e-2  # it trained

@@ -1,0 +1,42 @@
+"""OLMo-2 / OLMo-3 block structure (norm after the sub-layer, q/k norm over all heads) on the sm_100a kernels against the PyTorch
+fp32 statement of the same model.  The driver logic is covered on CPU (``test_fused_driver_cpu.py``); this file runs the same
+comparison through the real kernels and sorts after the other GPU files."""
+
+import pytest
+import torch
+
+from test_model_gpu import _batch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("kv_heads", [None, "all"], ids=["gqa", "mha"])
+@pytest.mark.parametrize("ckpt", [False, True])
+def test_fused_post_norm_matches_ref(ckpt, kv_heads):
+    from open_instruct_b200.models import LlamaModel, get_spec
+    from open_instruct_b200.ops import lib
+
+    spec = get_spec("tiny128").replace(post_norm=True, qk_norm=True, qk_norm_full=True, model_type="olmo2")
+    if kv_heads == "all":
+        spec = spec.replace(num_kv_heads=spec.num_heads)
+    fused = LlamaModel(spec, device="cuda", dtype=torch.bfloat16, ops="fused", seed=3, gradient_checkpointing=ckpt)
+    with torch.no_grad():
+        for name, v in fused.p.items():
+            if name.endswith("norm"):
+                v.add_(torch.randn_like(v.float()).mul_(0.1).to(v.dtype))
+    refm = LlamaModel(spec, device="cuda", dtype=torch.float32, ops="ref", flat=fused.flat.float().clone())
+    ids, pos, cu, labels = _batch([200, 57, 300], spec.vocab_size, "cuda")
+    lp_f, ent_f = fused.token_logprobs(ids, pos, cu, labels, want_entropy=True)
+    lp_r, ent_r = refm.token_logprobs(ids, pos, cu, labels, want_entropy=True)
+    n = (labels >= 0).sum()
+    assert (lp_f - lp_r).abs().max().item() < 0.05
+    assert (ent_f - ent_r).abs().max().item() < 0.05
+    (-(lp_f.sum()) / n).backward()
+    (-(lp_r.sum()) / n).backward()
+    lib.check_status()
+    gf, gr = fused.grad_flat(), refm.grad_flat()
+    for name, e in fused.layout.entries.items():
+        a = gf[e.offset:e.offset + e.numel]
+        b = gr[e.offset:e.offset + e.numel]
+        rel = ((a - b).norm() / (b.norm() + 1e-9)).item()
+        assert rel < 0.06, f"{name}: rel grad error {rel}"
