@@ -184,6 +184,8 @@ class RolloutEngine:
         if ops == "auto":
             ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts and lib.available()) else "ref"
         self.ops = ops
+        if tp is not None and spec.post_norm:
+            raise NotImplementedError("tensor-parallel engines are not built for post-norm blocks (OLMo-2 / OLMo-3)")
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, seed=seed, flat=flat)
         if ops == "ref":
@@ -429,7 +431,10 @@ class RolloutEngine:
                 return tp.row_gemm(x, w) if push else f.gemm(x, w, row_out(), impl=impl_narrow)
 
             for i in range(s.num_layers):
-                n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
+                if s.post_norm:   # OLMo-2 / OLMo-3: the sub-layers read the stream as it is and their output is normalised
+                    n1 = stream
+                else:
+                    n1, h_in = add_norm(delta if delta is not None else stream, p[f"l{i}.attn_norm"], stream if delta is not None else None)
                 qkv = col_proj(n1, p[f"l{i}.wqkv"], impl_qkv)
                 self.model.qkv_bias_and_norm_(qkv, i)
                 if fuse_rope_kv:  # one destination per token (decode, plain prefill): rotation and cache write in one pass
@@ -441,11 +446,16 @@ class RolloutEngine:
                          s.num_heads, s.num_kv_heads, s.head_dim, stream_ptr())
                 attn = attn_fn(i, qkv)
                 o = row_proj(attn, p[f"l{i}.wo"])
+                if s.post_norm:
+                    stream = stream + add_norm(o, p[f"l{i}.attn_norm"], None)[0]
+                    act = f.swiglu_fwd(col_proj(stream, p[f"l{i}.w_gate_up"], impl))
+                    stream = stream + add_norm(row_proj(act, p[f"l{i}.w_down"], 1), p[f"l{i}.mlp_norm"], None)[0]
+                    continue
                 n2, h_mid = add_norm(o, p[f"l{i}.mlp_norm"], h_in)
                 act = f.swiglu_fwd(col_proj(n2, p[f"l{i}.w_gate_up"], impl))
                 delta = row_proj(act, p[f"l{i}.w_down"], 1)
                 stream = h_mid
-            nf, _ = add_norm(delta, p["final_norm"], stream)
+            nf, _ = add_norm(delta, p["final_norm"], stream) if delta is not None else add_norm(stream, p["final_norm"], None)
             return nf
         x = p["embed"][ids]
         for i in range(s.num_layers):

@@ -103,3 +103,26 @@ def test_learner_steps_on_the_emulated_path_follow_the_pytorch_path(family):
     assert (flats[0] - flats[1]).abs().max().item() < 1e-3
     start = LlamaModel(spec, ops="ref", seed=4).flat.detach()   # the learner pads its buffer to a multiple of the world size
     assert (flats[0][: start.numel()] - start).abs().max().item() > 1e-2  # it trained
+
+
+def test_lora_on_the_emulated_path_follows_the_pytorch_path():
+    """Adapter training contracts ``dL/dW_eff`` from the fused path's fp32 gradient buffer; same adapters as from autograd."""
+    from open_instruct_b200.learner import Learner, LearnerConfig
+    from open_instruct_b200.models.lora import LoRATrainer
+
+    spec = ModelSpec(**BASE)
+    got = []
+    for ops in ("ref", "emulated"):
+        ln = Learner(spec, LearnerConfig(ops=ops, seed=4), device="cpu")
+        tr = LoRATrainer(ln, rank=4, alpha=8.0, lr=1e-2)
+        for step in range(3):
+            mbs = []
+            for mb in range(2):
+                ids, pos, cu, labels, _ = _batch(spec, seed=10 * step + mb)
+                mbs.append({"input_ids": ids, "position_ids": pos, "cu_seq_lens_q": cu, "labels_shifted": labels})
+            out = tr.step(mbs)
+        got.append((tr.adapters.flat.detach().clone(), ln.model.flat.detach().clone(), float(out["loss"])))
+    assert abs(got[0][2] - got[1][2]) < 1e-4
+    assert (got[0][0] - got[1][0]).abs().max().item() < 1e-3
+    assert (got[0][1] - got[1][1]).abs().max().item() < 1e-3
+    assert got[0][0].abs().max().item() > 1e-2

@@ -40,3 +40,29 @@ def test_fused_post_norm_matches_ref(ckpt, kv_heads):
         b = gr[e.offset:e.offset + e.numel]
         rel = ((a - b).norm() / (b.norm() + 1e-9)).item()
         assert rel < 0.06, f"{name}: rel grad error {rel}"
+
+
+def test_fused_engine_generates_like_the_ref_engine_with_post_norm_blocks():
+    from open_instruct_b200.data_types import SamplingConfig
+    from open_instruct_b200.models import get_spec
+    from open_instruct_b200.ops import lib
+    from open_instruct_b200.rollout.engine import RolloutEngine
+
+    spec = get_spec("tiny128").replace(post_norm=True, qk_norm=True, qk_norm_full=True, model_type="olmo2", eos_token_id=None)
+    fused = RolloutEngine(spec, device="cuda", ops="fused", num_blocks=64, seed=2)
+    refe = RolloutEngine(spec, device="cuda", ops="ref", num_blocks=64, seed=2, flat=fused.model.flat.clone())
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, spec.vocab_size, (n,), generator=g).tolist() for n in (7, 64, 150)]
+    cfg = SamplingConfig(temperature=0.0, max_tokens=16, n=2)
+    a, b = fused.generate(prompts, cfg), refe.generate(prompts, cfg)
+    agree = total = 0
+    for ra, rb in zip(a, b):
+        for x, y, lx, ly in zip(ra.responses, rb.responses, ra.logprobs, rb.logprobs):
+            n = next((i for i, (u, v) in enumerate(zip(x, y)) if u != v), len(x))  # bf16 may flip a near tie late
+            agree += n
+            total += len(x)
+            for i in range(n):
+                assert abs(lx[i] - ly[i]) < 0.08
+    assert agree / total > 0.8
+    lib.check_status()
+    assert fused.host.free_blocks() == 64
