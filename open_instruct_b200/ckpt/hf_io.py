@@ -26,8 +26,17 @@ def state_dict_from_flat(flat: torch.Tensor, layout: ParamLayout, dtype=torch.bf
     for name in layout.entries:
         t = layout.view(flat.detach(), name).to("cpu", dtype)
         for hf_name, a, b in layout.hf_names(name):
-            out[hf_name] = t[a:b].contiguous()
+            out[hf_name] = _hf_shape(hf_name, t[a:b].contiguous(), layout.spec)
     return out
+
+
+def _hf_shape(hf_name: str, piece: torch.Tensor, spec: ModelSpec) -> torch.Tensor:
+    """The shape a checkpoint stores ``piece`` in where it differs from the flat layout's 2-D entry."""
+    if spec.num_experts and hf_name.endswith(("experts.gate_up_proj", "experts.down_proj")):
+        return piece.view(spec.num_experts, -1, piece.shape[1])  # the stacked [experts, rows, cols] form
+    if hf_name.endswith("conv1d.weight"):
+        return piece.unsqueeze(1)                                # depthwise convolution: [channels, 1, taps]
+    return piece
 
 
 def save_hf_checkpoint(flat: torch.Tensor, spec: ModelSpec, out_dir: str, tokenizer=None, layout: ParamLayout | None = None,
@@ -54,9 +63,7 @@ def save_hf_checkpoint(flat: torch.Tensor, spec: ModelSpec, out_dir: str, tokeni
         for hf_name, a, b in layout.hf_names(name):
             if skip and hf_name in skip:
                 continue
-            piece = t[a:b].contiguous()
-            if spec.num_experts and hf_name.endswith(("experts.gate_up_proj", "experts.down_proj")):
-                piece = piece.view(spec.num_experts, -1, piece.shape[1])  # the stacked [experts, rows, cols] form
+            piece = _hf_shape(hf_name, t[a:b].contiguous(), spec)
             nbytes = piece.numel() * piece.element_size()
             if size + nbytes > max_shard_bytes and shards[-1]:
                 shards.append({})
@@ -116,6 +123,12 @@ def load_hf_checkpoint(model_dir: str, flat: torch.Tensor, spec: ModelSpec | Non
             if any(n not in where for n, _, _ in names) and layout.hf_names_per_expert(name) is not None:
                 names = layout.hf_names_per_expert(name)  # experts stored one tensor each
             for hf_name, a, b in names:
+                if hf_name not in where and spec.model_type == "olmo_hybrid":
+                    # transformers writes the hybrid's layer norms under these names and reads either spelling
+                    alt = hf_name.replace("input_layernorm", "attention_layer_norm").replace("post_attention_layernorm", "feedforward_layer_norm")
+                    if alt in where:
+                        dst[a:b].copy_(handles[where[alt]].get_tensor(alt))
+                        continue
                 if hf_name not in where:
                     if hf_name == "lm_head.weight" and "model.embed_tokens.weight" in where:
                         src = handles[where["model.embed_tokens.weight"]].get_tensor("model.embed_tokens.weight")

@@ -26,6 +26,7 @@ all tokens of the micro-batch, ``cu_seqlens`` int32 ``[num_docs + 1]`` gives doc
 
 from __future__ import annotations
 
+import math
 import os
 from dataclasses import dataclass
 
@@ -89,6 +90,8 @@ class LlamaModel:
         self.emulated = ops == "emulated"
         if self.emulated:
             ops = "fused"
+        if ops == "fused" and (spec.layer_types is not None or not spec.use_rope):
+            raise NotImplementedError("hybrid models (gated DeltaNet layers) and attention without RoPE run with ops='ref'")
         self.spec = spec
         self.ops = ops
         self.device = torch.device(device)
@@ -162,6 +165,14 @@ class LlamaModel:
                 v.fill_(1.0)
             elif name.endswith("bqkv"):
                 v.zero_()
+            elif name.endswith("gdn_A_log"):     # decay rates A ~ U(0, 16), stored as log A
+                v.copy_(torch.log(torch.rand(v.shape, generator=g) * 16.0 + 1e-3).to(v.dtype))
+            elif name.endswith("gdn_dt_bias"):   # softplus^-1 of a step size drawn log-uniformly from [1e-3, 1e-1]
+                dt = torch.exp(torch.rand(v.shape, generator=g) * (math.log(0.1) - math.log(0.001)) + math.log(0.001)).clamp(min=1e-4)
+                v.copy_((dt + torch.log(-torch.expm1(-dt))).to(v.dtype))
+            elif name.endswith("gdn_conv"):      # depthwise taps: U(-1/sqrt(taps), 1/sqrt(taps))
+                bound = v.shape[1] ** -0.5
+                v.copy_(((torch.rand(v.shape, generator=g) * 2 - 1) * bound).to(v.dtype))
             elif init == "normal":
                 if v.device.type == "cuda":
                     # generate on device in chunks: 8B parameters on the host would take minutes
@@ -342,19 +353,25 @@ class LlamaModel:
     def _ref_layer(self, x, v, i, position_ids, cu_seqlens):
         s = self.spec
         tp = self.tp
+        rope = (lambda qkv: ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)) if s.use_rope else (lambda qkv: qkv)
+        if s.is_gdn(i):  # hybrid models: a pre-norm block whose sequence mixer is a gated DeltaNet
+            if tp is not None:
+                raise NotImplementedError("tensor parallelism is not built for gated-DeltaNet layers")
+            from .gdn import gdn_mixer
+
+            x = x + gdn_mixer(ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps), v, i, s, cu_seqlens)
+            return x + self.ref_mlp(ref.rmsnorm(x, v[f"l{i}.mlp_norm"], s.rms_norm_eps), v, i)
         if s.post_norm:  # OLMo-2 / OLMo-3: the sub-layer reads the stream as it is, its OUTPUT is normed before the residual add
             if tp is not None:
                 raise NotImplementedError("tensor parallelism is not built for post-norm blocks")
-            qkv = self.ref_qkv(x, v, i)
-            qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            qkv = rope(self.ref_qkv(x, v, i))
             attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=True)
             x = x + ref.rmsnorm(ref.linear(attn, v[f"l{i}.wo"]), v[f"l{i}.attn_norm"], s.rms_norm_eps)
             return x + ref.rmsnorm(self.ref_mlp(x, v, i), v[f"l{i}.mlp_norm"], s.rms_norm_eps)
         n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
         if tp is not None:
             n1 = tp.enter(n1)
-        qkv = self.ref_qkv(n1, v, i)
-        qkv = ref.rope(qkv, position_ids, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+        qkv = rope(self.ref_qkv(n1, v, i))
         attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=bool(s.num_experts))
         o = ref.linear(attn, v[f"l{i}.wo"])
         x = x + (tp.sum_partials(o) if tp is not None else o)

@@ -1,7 +1,7 @@
 """Model description and flat parameter layout.
 
 A decoder is described by a ``ModelSpec`` (convertible from / to a Hugging Face ``config.json``
-for the Llama, Qwen2/2.5/3, OLMo-2 and Mistral families, which share this block structure) and
+for the Llama, Qwen2/2.5/3, Mistral, OLMo-2/3, OLMoE and OLMo-Hybrid families) and
 its weights live in ONE flat buffer laid out in consumer order with the fused shapes the
 kernels use (``wqkv`` = q|k|v rows, ``w_gate_up`` = gate|up rows).  Hugging Face names are only a
 view used for checkpoint I/O.  Parameters that take no weight decay (norm weights, biases) are
@@ -53,6 +53,17 @@ class ModelSpec:
     router_aux_loss_coef: float = 0.01
     sliding_window: int | None = None  # some layers attend to the last N tokens only (OLMo-3, Mistral v0.1): documents up to N are exact
     attention_bias: bool = False  # Qwen2 style q/k/v bias
+    # hybrid models (OLMo-Hybrid): ``layer_types[i]`` is "attention" or "gdn" (gated DeltaNet: a linear-attention layer with a
+    # [key_dim, value_dim] state per head instead of a KV cache).  The gdn layers are pre-norm blocks; the attention layers
+    # follow ``post_norm`` / ``qk_norm_full`` like every other attention layer of the model.  None: all layers are attention.
+    layer_types: tuple | None = None
+    gdn_key_heads: int = 0
+    gdn_value_heads: int = 0
+    gdn_key_dim: int = 0       # per head
+    gdn_value_dim: int = 0     # per head
+    gdn_conv: int = 4          # taps of the causal depthwise convolution on q, k and v
+    gdn_neg_eigval: bool = True  # beta in (0, 2) instead of (0, 1)
+    use_rope: bool = True      # False: attention without positional rotation (OLMo-Hybrid without ``rope_theta``)
     model_type: str = "llama"
     bos_token_id: int | None = None
     eos_token_id: int | None = None
@@ -71,6 +82,22 @@ class ModelSpec:
     def qkv_dim(self) -> int:
         return self.q_dim + 2 * self.kv_dim
 
+    def is_gdn(self, i: int) -> bool:
+        return self.layer_types is not None and self.layer_types[i] == "gdn"
+
+    @property
+    def gdn_k_total(self) -> int:
+        return self.gdn_key_heads * self.gdn_key_dim
+
+    @property
+    def gdn_v_total(self) -> int:
+        return self.gdn_value_heads * self.gdn_value_dim
+
+    @property
+    def gdn_in_rows(self) -> int:
+        """Rows of the fused input projection of a gdn layer: q | k | v | output gate | a (decay) | b (beta)."""
+        return 2 * self.gdn_k_total + 2 * self.gdn_v_total + 2 * self.gdn_value_heads
+
     def num_params(self) -> int:
         return ParamLayout(self).total
 
@@ -80,7 +107,20 @@ class ModelSpec:
         mt = cfg.get("model_type", "llama")
         heads = cfg["num_attention_heads"]
         hd = cfg.get("head_dim") or cfg["hidden_size"] // heads
+        hybrid = {}
+        if mt == "olmo_hybrid":
+            n = cfg["num_hidden_layers"]
+            kinds = cfg.get("layer_types") or [("full_attention" if (i % 4 == 3 or (n < 4 and i == n - 1)) else "linear_attention") for i in range(n)]
+            kh = cfg.get("linear_num_key_heads") or heads
+            kd = cfg.get("linear_key_head_dim") or int(0.75 * cfg["hidden_size"] / kh)
+            rp = cfg.get("rope_parameters") or {}
+            hybrid = dict(layer_types=tuple("attention" if k == "full_attention" else "gdn" for k in kinds), gdn_key_heads=kh,
+                          gdn_value_heads=cfg.get("linear_num_value_heads") or heads, gdn_key_dim=kd,
+                          gdn_value_dim=cfg.get("linear_value_head_dim") or 2 * kd, gdn_conv=cfg.get("linear_conv_kernel_dim", 4),
+                          gdn_neg_eigval=bool(cfg.get("linear_allow_neg_eigval", True)),
+                          use_rope=(cfg.get("rope_theta") or rp.get("rope_theta")) is not None)
         return cls(
+            **hybrid,
             vocab_size=cfg["vocab_size"],
             hidden_size=cfg["hidden_size"],
             intermediate_size=cfg["intermediate_size"],
@@ -89,17 +129,17 @@ class ModelSpec:
             num_kv_heads=cfg.get("num_key_value_heads", heads),
             head_dim=hd,
             rms_norm_eps=cfg.get("rms_norm_eps", 1e-5),
-            rope_theta=cfg.get("rope_theta", (cfg.get("rope_parameters") or {}).get("rope_theta", 10000.0)),
+            rope_theta=cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0,
             rope_scaling=_rope_scaling_of(cfg),
             max_position_embeddings=cfg.get("max_position_embeddings", 8192),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            qk_norm=mt in ("qwen3", "olmo2", "olmo3", "olmoe"),
-            qk_norm_full=mt in ("olmo2", "olmo3", "olmoe"),
+            qk_norm=mt in ("qwen3", "olmo2", "olmo3", "olmoe", "olmo_hybrid"),
+            qk_norm_full=mt in ("olmo2", "olmo3", "olmoe", "olmo_hybrid"),
             num_experts=cfg.get("num_experts", 0) if mt == "olmoe" else 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) if mt == "olmoe" else 0,
             norm_topk_prob=bool(cfg.get("norm_topk_prob", False)),
             router_aux_loss_coef=cfg.get("router_aux_loss_coef", 0.01),
-            post_norm=mt in ("olmo2", "olmo3"),
+            post_norm=mt in ("olmo2", "olmo3", "olmo_hybrid"),
             sliding_window=cfg.get("sliding_window") if (mt == "olmo3" or cfg.get("use_sliding_window", mt == "mistral")) else None,
             attention_bias=cfg.get("attention_bias", mt == "qwen2"),
             model_type=mt,
@@ -115,7 +155,7 @@ class ModelSpec:
     def to_hf_config(self) -> dict:
         arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                 "mistral": "MistralForCausalLM", "olmo2": "Olmo2ForCausalLM", "olmo3": "Olmo3ForCausalLM",
-                "olmoe": "OlmoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+                "olmoe": "OlmoeForCausalLM", "olmo_hybrid": "OlmoHybridForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
         cfg = {
             "architectures": [arch],
             "model_type": self.model_type,
@@ -143,6 +183,13 @@ class ModelSpec:
             "pad_token_id": self.pad_token_id,
             "use_cache": True,
         }
+        if self.layer_types is not None:
+            cfg.update({"layer_types": ["full_attention" if k == "attention" else "linear_attention" for k in self.layer_types],
+                        "linear_num_key_heads": self.gdn_key_heads, "linear_num_value_heads": self.gdn_value_heads,
+                        "linear_key_head_dim": self.gdn_key_dim, "linear_value_head_dim": self.gdn_value_dim,
+                        "linear_conv_kernel_dim": self.gdn_conv, "linear_allow_neg_eigval": self.gdn_neg_eigval})
+            if not self.use_rope:
+                cfg.update({"rope_theta": None, "rope_scaling": None, "rope_parameters": {"rope_type": "default", "rope_theta": None}})
         if self.num_experts:
             cfg.update({"num_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok, "norm_topk_prob": self.norm_topk_prob,
                         "router_aux_loss_coef": self.router_aux_loss_coef})
@@ -186,6 +233,11 @@ PRESETS: dict[str, ModelSpec] = {
     "olmo2-7b": ModelSpec(vocab_size=100352, hidden_size=4096, intermediate_size=11008, num_layers=32, num_heads=32,
                           num_kv_heads=32, head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2",
                           qk_norm=True, qk_norm_full=True, post_norm=True, max_position_embeddings=4096),
+    # allenai/Olmo-Hybrid-7B: 24 gated-DeltaNet layers and 8 full-attention layers (every fourth), ``open_instruct/olmo_core_hybrid.py:154-175``
+    "olmo-hybrid-7b": ModelSpec(vocab_size=100352, hidden_size=3840, intermediate_size=11008, num_layers=32, num_heads=30, num_kv_heads=30,
+                                head_dim=128, rms_norm_eps=1e-6, model_type="olmo_hybrid", qk_norm=True, qk_norm_full=True, post_norm=True,
+                                layer_types=tuple("attention" if i % 4 == 3 else "gdn" for i in range(32)), gdn_key_heads=30,
+                                gdn_value_heads=30, gdn_key_dim=96, gdn_value_dim=192, max_position_embeddings=65536),
 }
 
 
@@ -238,8 +290,12 @@ class ParamLayout:
         s = spec
         add("embed", (s.vocab_size, s.hidden_size), True)
         for i in range(s.num_layers):
-            add(f"l{i}.wqkv", (s.qkv_dim, s.hidden_size), True)
-            add(f"l{i}.wo", (s.hidden_size, s.q_dim), True)
+            if s.is_gdn(i):
+                add(f"l{i}.gdn_in", (s.gdn_in_rows, s.hidden_size), True)
+                add(f"l{i}.gdn_out", (s.hidden_size, s.gdn_v_total), True)
+            else:
+                add(f"l{i}.wqkv", (s.qkv_dim, s.hidden_size), True)
+                add(f"l{i}.wo", (s.hidden_size, s.q_dim), True)
             if s.num_experts:  # experts stacked along the rows: expert e owns rows [e * 2F, (e + 1) * 2F) / [e * D, (e + 1) * D)
                 add(f"l{i}.router", (s.num_experts, s.hidden_size), True)
                 add(f"l{i}.w_gate_up", (s.num_experts * 2 * s.intermediate_size, s.hidden_size), True)
@@ -253,6 +309,12 @@ class ParamLayout:
         for i in range(s.num_layers):
             add(f"l{i}.attn_norm", (s.hidden_size,), False)
             add(f"l{i}.mlp_norm", (s.hidden_size,), False)
+            if s.is_gdn(i):
+                add(f"l{i}.gdn_conv", (2 * s.gdn_k_total + s.gdn_v_total, s.gdn_conv), False)  # depthwise taps of q | k | v
+                add(f"l{i}.gdn_o_norm", (s.gdn_value_dim,), False)
+                add(f"l{i}.gdn_A_log", (s.gdn_value_heads,), False)
+                add(f"l{i}.gdn_dt_bias", (s.gdn_value_heads,), False)
+                continue
             if s.qk_norm:
                 add(f"l{i}.q_norm", (s.q_dim if s.qk_norm_full else s.head_dim,), False)
                 add(f"l{i}.k_norm", (s.kv_dim if s.qk_norm_full else s.head_dim,), False)
@@ -295,7 +357,23 @@ class ParamLayout:
         if name == "final_norm":
             return [("model.norm.weight", 0, s.hidden_size)]
         layer, leaf = name.split(".", 1)
-        p = f"model.layers.{int(layer[1:])}."
+        li = int(layer[1:])
+        p = f"model.layers.{li}."
+        if leaf.startswith("gdn_"):
+            g, K, V, H = p + "linear_attn.", s.gdn_k_total, s.gdn_v_total, s.gdn_value_heads
+            if leaf == "gdn_in":
+                cuts = [("q_proj", K), ("k_proj", K), ("v_proj", V), ("g_proj", V), ("a_proj", H), ("b_proj", H)]
+            elif leaf == "gdn_conv":   # stored [channels, 1, taps] in checkpoints
+                cuts = [("q_conv1d", K), ("k_conv1d", K), ("v_conv1d", V)]
+            else:
+                return [{"gdn_out": (g + "o_proj.weight", 0, s.hidden_size), "gdn_o_norm": (g + "o_norm.weight", 0, s.gdn_value_dim),
+                         "gdn_A_log": (g + "A_log", 0, H), "gdn_dt_bias": (g + "dt_bias", 0, H)}[leaf]]
+            out, r = [], 0
+            for nm, rows in cuts:
+                out.append((g + nm + ".weight", r, r + rows))
+                r += rows
+            return out
+        post = s.post_norm and not s.is_gdn(li)   # the gdn layers of a hybrid are pre-norm blocks
         if leaf == "wqkv" or leaf == "bqkv":
             suf = "weight" if leaf == "wqkv" else "bias"
             return [(p + f"self_attn.q_proj.{suf}", 0, s.q_dim), (p + f"self_attn.k_proj.{suf}", s.q_dim, s.q_dim + s.kv_dim),
@@ -314,9 +392,9 @@ class ParamLayout:
         if leaf == "w_down":
             return [(p + "mlp.down_proj.weight", 0, s.hidden_size)]
         if leaf == "attn_norm":  # post-norm blocks: the norm applied to the attention output
-            return [(p + ("post_attention_layernorm.weight" if s.post_norm else "input_layernorm.weight"), 0, s.hidden_size)]
+            return [(p + ("post_attention_layernorm.weight" if post else "input_layernorm.weight"), 0, s.hidden_size)]
         if leaf == "mlp_norm":   # post-norm blocks: the norm applied to the MLP output
-            return [(p + ("post_feedforward_layernorm.weight" if s.post_norm else "post_attention_layernorm.weight"), 0, s.hidden_size)]
+            return [(p + ("post_feedforward_layernorm.weight" if post else "post_attention_layernorm.weight"), 0, s.hidden_size)]
         if leaf == "q_norm":
             return [(p + "self_attn.q_norm.weight", 0, s.q_dim if s.qk_norm_full else s.head_dim)]
         if leaf == "k_norm":

@@ -184,6 +184,9 @@ class RolloutEngine:
         if ops == "auto":
             ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts and lib.available()) else "ref"
         self.ops = ops
+        if spec.layer_types is not None:
+            raise NotImplementedError("the rollout engine keeps a paged KV cache per sequence; the recurrent state of gated-DeltaNet layers "
+                                      "(hybrid models) is not built, so these models can be trained (SFT, DPO, reward model) but not sampled from")
         if tp is not None and spec.post_norm:
             raise NotImplementedError("tensor-parallel engines are not built for post-norm blocks (OLMo-2 / OLMo-3)")
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32

@@ -21,6 +21,10 @@ FAMILIES = {
     "mistral": ("Mistral", dict(sliding_window=None)),
     "olmo2": ("Olmo2", {}),
     "olmo3": ("Olmo3", dict(sliding_window=4096)),
+    "olmo-hybrid": ("OlmoHybrid", dict(num_hidden_layers=4, pad_token_id=0, eos_token_id=1, rope_parameters={"rope_type": "default", "rope_theta": 10000.0})),
+    "olmo-hybrid-grouped-key-heads": ("OlmoHybrid", dict(num_hidden_layers=4, pad_token_id=0, eos_token_id=1, linear_num_key_heads=2, linear_num_value_heads=4,
+                                                         linear_key_head_dim=8, linear_value_head_dim=16, layer_types=["linear_attention", "full_attention", "linear_attention", "full_attention"])),
+    "olmo-hybrid-no-rope": ("OlmoHybrid", dict(num_hidden_layers=4, pad_token_id=0, eos_token_id=1, rope_parameters={"rope_type": "default", "rope_theta": None})),
     "olmoe": ("Olmoe", dict(intermediate_size=96, num_key_value_heads=4, num_experts=4, num_experts_per_tok=2)),
 }
 
@@ -65,7 +69,7 @@ def test_checkpoint_import_gives_hf_logits(family):
     assert (_our_logits(ours, ids) - want).abs().max().item() < 1e-5
 
 
-@pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2", "olmoe"])
+@pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2", "olmoe", "olmo-hybrid", "olmo-hybrid-no-rope"])
 def test_checkpoint_export_is_read_by_hf(family):
     from open_instruct_b200.ckpt.hf_io import save_hf_checkpoint
     from open_instruct_b200.models import LlamaModel
@@ -241,7 +245,7 @@ def test_fused_attention_branch_of_the_pytorch_path_equals_the_explicit_softmax(
     assert (a - b).abs().max().item() < 1e-5 and (ga - gb).abs().max().item() < 1e-4
 
 
-@pytest.mark.parametrize("cls_name", ["Olmo2", "Qwen3"])
+@pytest.mark.parametrize("cls_name", ["Olmo2", "Qwen3", "OlmoHybrid"])
 def test_sft_starts_from_a_hugging_face_folder_and_exports_the_same_architecture(tmp_path, cls_name):
     """``model_name_or_path`` pointing at a transformers checkpoint: the trainer reads the architecture and the weights from it,
     and its export loads as the same transformers class.  With a zero learning rate the exported model gives the source
@@ -251,7 +255,7 @@ def test_sft_starts_from_a_hugging_face_folder_and_exports_the_same_architecture
     from open_instruct_b200.finetune import main
     from test_finetune_cpu import _args
 
-    hf, cfg = _hf_model(cls_name, dict(vocab_size=600))
+    hf, cfg = _hf_model(cls_name, dict(vocab_size=600, **(FAMILIES["olmo-hybrid"][1] if cls_name == "OlmoHybrid" else {})))
     src = os.path.join(str(tmp_path), "hf")
     hf.save_pretrained(src, safe_serialization=True)
     args, tc = _args(str(tmp_path), model_name_or_path=src, num_train_epochs=1, learning_rate=0.0)
@@ -261,3 +265,39 @@ def test_sft_starts_from_a_hugging_face_folder_and_exports_the_same_architecture
     ids = torch.randint(0, 300, (2, 20), generator=torch.Generator().manual_seed(5))
     with torch.no_grad():
         assert (back(ids).logits - hf(ids).logits).abs().max().item() < 0.03
+
+
+def test_gated_delta_rule_in_chunks_equals_the_token_by_token_recurrence():
+    """Outputs, final state and every input gradient; a chunk length that does not divide the sequence."""
+    from open_instruct_b200.models import gdn
+
+    g0 = torch.Generator().manual_seed(0)
+    L, H, dk, dv = 150, 3, 8, 16
+    q = torch.randn(L, H, dk, generator=g0)
+    k = gdn._l2norm(torch.randn(L, H, dk, generator=g0))
+    v = torch.randn(L, H, dv, generator=g0)
+    g = -torch.rand(L, H, generator=g0) * 0.5
+    beta = torch.rand(L, H, generator=g0) * 2
+    s0 = torch.randn(H, dk, dv, generator=g0) * 0.1
+    args = [t.requires_grad_(True) for t in (q, k, v, g, beta, s0)]
+    o1, S1 = gdn.gated_delta_rule_sequential(*args)
+    o2, S2 = gdn.gated_delta_rule(*args, chunk=32)
+    assert (o1 - o2).abs().max().item() < 1e-4 and (S1 - S2).abs().max().item() < 1e-4
+    w, ws = torch.randn(o1.shape, generator=g0), torch.randn(S1.shape, generator=g0)
+    for a, b in zip(torch.autograd.grad((o1 * w).sum() + (S1 * ws).sum(), args), torch.autograd.grad((o2 * w).sum() + (S2 * ws).sum(), args)):
+        assert (a - b).abs().max().item() < 2e-4 * max(1.0, a.abs().max().item())
+
+
+def test_hybrid_layers_do_not_leak_across_packed_documents():
+    """Two documents packed into one row give the logits of each document run alone (state and convolution restart)."""
+    from open_instruct_b200.models import LlamaModel, get_spec
+
+    spec = get_spec("olmo-hybrid-7b").replace(vocab_size=300, hidden_size=64, intermediate_size=128, num_layers=4, num_heads=4, num_kv_heads=2,
+                                              head_dim=16, layer_types=("gdn", "gdn", "gdn", "attention"), gdn_key_heads=2, gdn_value_heads=4,
+                                              gdn_key_dim=12, gdn_value_dim=24)
+    m = LlamaModel(spec, ops="ref", seed=2)
+    ids = torch.randint(0, 300, (100,), generator=torch.Generator().manual_seed(1))
+    packed = m.logits(ids, torch.cat([torch.arange(70), torch.arange(30)]), torch.tensor([0, 70, 100], dtype=torch.int32))
+    alone = m.logits(ids[70:], torch.arange(30), torch.tensor([0, 30], dtype=torch.int32))
+    assert (packed[70:] - alone).abs().max().item() < 1e-5
+    assert (packed[:70] - m.logits(ids[:70], torch.arange(70), torch.tensor([0, 70], dtype=torch.int32))).abs().max().item() < 1e-5
