@@ -10,6 +10,11 @@ server: an in-memory inverted index from word n-grams (default 8) to training ro
 
     python -m open_instruct_b200.decontamination.search --train train.jsonl --eval eval.jsonl --field text \\
         --ngram_size 8 --threshold 0.5 --output_dir out [--decontaminate]
+
+With ``--es_url`` the training side is an Elasticsearch index filled by ``open_instruct_b200.decontamination.index`` (for
+training sets that do not fit in one process); ``--train`` then names the indexed dataset, scores are the reference's
+(exact: every field found as a phrase; ngram: share of the query's tokens inside matching n-grams), and
+``--decontaminate`` still writes the training rows whose best score stays below ``--threshold``.
 """
 
 from __future__ import annotations
@@ -103,8 +108,12 @@ def main(argv=None) -> dict:
     ap.add_argument("--index_type", choices=["exact", "ngram"], default="ngram")
     ap.add_argument("--output_dir", required=True)
     ap.add_argument("--decontaminate", action="store_true")
+    ap.add_argument("--es_url", default=None, help="query an Elasticsearch index of --train instead of indexing it in this process")
+    ap.add_argument("--search_size", type=int, default=100, help="hits fetched per Elasticsearch query")
     a = ap.parse_args(argv)
     load = lambda p: [json.loads(line) for line in open(p) if line.strip()]
+    if a.es_url:
+        return _main_elasticsearch(a, load(a.eval))
     train, ev = load(a.train), load(a.eval)
     rep = find_contamination(train, ev, a.train_field, a.field, a.ngram_size, a.threshold, a.index_type)
     os.makedirs(a.output_dir, exist_ok=True)
@@ -115,6 +124,34 @@ def main(argv=None) -> dict:
         with open(os.path.join(a.output_dir, "train_decontaminated.jsonl"), "w") as f:
             for i, r in enumerate(train):
                 if i not in bad:
+                    f.write(json.dumps(r) + "\n")
+    return rep
+
+
+def _main_elasticsearch(a, eval_rows: list[dict]) -> dict:
+    from . import es as es_mod
+
+    client = es_mod.ElasticClient(a.es_url)
+    index = es_mod.index_name_for(a.train, "text")
+    queries = [[row.get(f) for f in a.field] for row in eval_rows]
+    if a.index_type == "exact":
+        scores, report, ids = es_mod.exact_match(client, index, queries, a.search_size)
+        train_scores = {i: 1.0 for i in ids}
+    else:
+        scores, report, train_scores = es_mod.ngram_match(client, index, queries, a.ngram_size, a.search_size)
+    bad = sorted(i for i, sc in train_scores.items() if sc >= a.threshold)
+    rep = {"eval_contaminated": sum(1 for sc in scores if sc >= a.threshold), "eval_total": len(scores), "train_contaminated": bad,
+           "mean_match_score": sum(scores) / max(1, len(scores)), "matches": report}
+    os.makedirs(a.output_dir, exist_ok=True)
+    with open(os.path.join(a.output_dir, "contamination_report.json"), "w") as f:
+        json.dump(rep, f, indent=1)
+    if a.decontaminate:
+        from ..data.mixer import _load_any
+
+        drop = set(bad)
+        with open(os.path.join(a.output_dir, "train_decontaminated.jsonl"), "w") as f:
+            for i, r in enumerate(_load_any(a.train, "train", None)):
+                if i not in drop:
                     f.write(json.dumps(r) + "\n")
     return rep
 

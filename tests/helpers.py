@@ -69,3 +69,93 @@ def make_rlvr_jsonl(path: str, n: int = 16):
                 "ground_truth": str(i + 1), "dataset": "gsm8k",
             }) + "\n")
     return path
+
+
+class FakeElasticsearch:
+    """An in-process HTTP server that answers the REST calls of the decontamination tools the way Elasticsearch does: index
+    creation (the analyzer's split pattern is read from the settings), HEAD, _count, _bulk and _search with
+    ``bool / filter / match_phrase`` (a phrase matches when its tokens occur contiguously in the analysed text)."""
+
+    def __init__(self):
+        import http.server
+        import json
+        import re
+        import threading
+        from urllib.parse import urlparse
+
+        store = self.indices = {}
+        log = self.requests = []
+
+        def analyse(index, text):
+            return [t for t in store[index]["split"].split(text.lower()) if t]
+
+        def contains(hay, needle):
+            n = len(needle)
+            return n > 0 and any(hay[i:i + n] == needle for i in range(len(hay) - n + 1))
+
+        class Handler(http.server.BaseHTTPRequestHandler):
+            def log_message(self, *a):
+                pass
+
+            def _reply(self, code, body=None):
+                raw = json.dumps(body).encode() if body is not None else b""
+                self.send_response(code)
+                self.send_header("Content-Type", "application/json")
+                self.send_header("Content-Length", str(len(raw)))
+                self.end_headers()
+                if self.command != "HEAD":
+                    self.wfile.write(raw)
+
+            def _body(self):
+                return self.rfile.read(int(self.headers.get("Content-Length") or 0)).decode()
+
+            def do_HEAD(self):
+                name = urlparse(self.path).path.strip("/")
+                log.append(("HEAD", name))
+                self._reply(200 if name in store else 404)
+
+            def do_PUT(self):
+                name = urlparse(self.path).path.strip("/")
+                body = json.loads(self._body())
+                pat = body["settings"]["analysis"]["analyzer"]["tulu_analyzer"]["pattern"]
+                store[name] = {"split": re.compile(pat), "docs": []}
+                log.append(("PUT", name))
+                self._reply(200, {"acknowledged": True})
+
+            def do_GET(self):
+                parts = urlparse(self.path).path.strip("/").split("/")
+                if len(parts) == 2 and parts[1] == "_count" and parts[0] in store:
+                    return self._reply(200, {"count": len(store[parts[0]]["docs"])})
+                self._reply(404, {"error": "no such index"})
+
+            def do_POST(self):
+                path = urlparse(self.path).path.strip("/")
+                if path == "_bulk":
+                    lines = [json.loads(x) for x in self._body().splitlines() if x.strip()]
+                    for action, doc in zip(lines[0::2], lines[1::2]):
+                        idx = store[action["index"]["_index"]]
+                        idx["docs"].append({"_id": f"d{len(idx['docs'])}", "_source": doc, "tokens": None})
+                    log.append(("BULK", len(lines) // 2))
+                    return self._reply(200, {"errors": False})
+                name, op = path.split("/")
+                if op != "_search" or name not in store:
+                    return self._reply(404, {"error": "no such index"})
+                q = json.loads(self._body())
+                phrases = [analyse(name, f["match_phrase"]["text"]) for f in q["query"]["bool"]["filter"]]
+                hits = []
+                for d in store[name]["docs"]:
+                    if d["tokens"] is None:
+                        d["tokens"] = analyse(name, d["_source"]["text"])
+                    if all(contains(d["tokens"], p) for p in phrases):
+                        hits.append({"_id": d["_id"], "_source": d["_source"]})
+                log.append(("SEARCH", name))
+                self._reply(200, {"hits": {"total": len(hits), "hits": hits[: q.get("size", 10)]}})
+
+        self.server = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Handler)
+        self.url = f"http://127.0.0.1:{self.server.server_address[1]}"
+        self.thread = threading.Thread(target=self.server.serve_forever, daemon=True)
+        self.thread.start()
+
+    def close(self):
+        self.server.shutdown()
+        self.server.server_close()

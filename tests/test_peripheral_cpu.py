@@ -617,3 +617,42 @@ def test_every_recipe_parses_with_its_entry_point(path):
     entry = first.split(":", 1)[1].strip()
     out = ArgumentParserPlus(parsers[entry]).parse([path])
     assert out is not None
+
+
+def test_decontamination_through_an_elasticsearch_index(tmp_path):
+    """Index the user turns of a training file into (a fake of) Elasticsearch, query it with evaluation examples, drop the
+    contaminated rows; an interrupted indexing run resumes from the index's document count."""
+    import json
+
+    from helpers import FakeElasticsearch
+    from open_instruct_b200.decontamination import es as es_mod
+    from open_instruct_b200.decontamination import index as index_cli
+    from open_instruct_b200.decontamination import search as search_cli
+
+    leaked = "What is the sum of the first ten positive odd integers, and why is x^2+y^2=z^2 relevant?"
+    train = [{"messages": [{"role": "user", "content": "Tell me a story about a dragon who learns to bake bread."}, {"role": "assistant", "content": "Once..."}]},
+             {"messages": [{"role": "user", "content": f"Please answer carefully. {leaked} Thanks!"}, {"role": "assistant", "content": "100"}]},
+             {"messages": [{"role": "user", "content": "Summarise the plot of Hamlet in two sentences."}, {"role": "assistant", "content": "..."}]}]
+    tp, ep = tmp_path / "train.jsonl", tmp_path / "eval.jsonl"
+    tp.write_text("".join(json.dumps(r) + "\n" for r in train))
+    ep.write_text("".join(json.dumps(r) + "\n" for r in [{"text": leaked}, {"text": "Name three rivers in South America and the countries they cross."}]))
+    fake = FakeElasticsearch()
+    try:
+        added = index_cli.main(["--es_url", fake.url, "--dataset", str(tp), "--text_batch_size", "2"])
+        index = es_mod.index_name_for(str(tp))
+        assert added == {index: 3} and len(fake.indices[index]["docs"]) == 3
+        assert [r for r in fake.requests if r[0] == "BULK"] == [("BULK", 2), ("BULK", 1)]
+        assert index_cli.main(["--es_url", fake.url, "--dataset", str(tp)]) == {index: 0}          # nothing left to add
+        # the analyzer keeps operators together: "x^2+y^2=z^2" is one token on both sides
+        assert "x^2+y^2=z^2" in es_mod.tokenize(leaked)
+        rep = search_cli.main(["--es_url", fake.url, "--train", str(tp), "--eval", str(ep), "--field", "text", "--ngram_size", "8",
+                               "--threshold", "0.5", "--output_dir", str(tmp_path / "out"), "--decontaminate"])
+        assert rep["eval_contaminated"] == 1 and rep["eval_total"] == 2 and rep["train_contaminated"] == [1]
+        assert rep["matches"][0]["score"] == 1.0            # every token of the leaked question lies inside a matching 8-gram
+        kept = [json.loads(l) for l in open(tmp_path / "out" / "train_decontaminated.jsonl")]
+        assert [r["messages"][0]["content"][:4] for r in kept] == ["Tell", "Summ"]
+        rep = search_cli.main(["--es_url", fake.url, "--train", str(tp), "--eval", str(ep), "--field", "text", "--index_type", "exact",
+                               "--output_dir", str(tmp_path / "out2")])
+        assert rep["train_contaminated"] == [1] and rep["eval_contaminated"] == 1
+    finally:
+        fake.close()
