@@ -90,7 +90,7 @@ class LlamaModel:
         self.emulated = ops == "emulated"
         if self.emulated:
             ops = "fused"
-        if ops == "fused" and (spec.layer_types is not None or not spec.use_rope):
+        if ops == "fused" and (spec.has_gdn or not spec.use_rope):
             raise NotImplementedError("hybrid models (gated DeltaNet layers) and attention without RoPE run with ops='ref'")
         self.spec = spec
         self.ops = ops
@@ -293,9 +293,6 @@ class LlamaModel:
 
     def _ref_hidden(self, input_ids, position_ids, cu_seqlens) -> torch.Tensor:
         s = self.spec
-        if s.sliding_window and cu_seqlens.numel() > 1 and int((cu_seqlens[1:] - cu_seqlens[:-1]).max()) > s.sliding_window:
-            raise NotImplementedError(f"documents longer than the model's sliding window ({s.sliding_window}) need windowed attention, "
-                                      "which is not built: every layer here attends to the whole document")
         v = self._ref_params()  # autograd views of the single leaf
         x = v["embed"][input_ids]
         self._router_logits = [] if s.num_experts else None
@@ -365,14 +362,14 @@ class LlamaModel:
             if tp is not None:
                 raise NotImplementedError("tensor parallelism is not built for post-norm blocks")
             qkv = rope(self.ref_qkv(x, v, i))
-            attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=True)
+            attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=True, window=s.window(i))
             x = x + ref.rmsnorm(ref.linear(attn, v[f"l{i}.wo"]), v[f"l{i}.attn_norm"], s.rms_norm_eps)
             return x + ref.rmsnorm(self.ref_mlp(x, v, i), v[f"l{i}.mlp_norm"], s.rms_norm_eps)
         n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
         if tp is not None:
             n1 = tp.enter(n1)
         qkv = rope(self.ref_qkv(n1, v, i))
-        attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=bool(s.num_experts))
+        attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=bool(s.num_experts), window=s.window(i))
         o = ref.linear(attn, v[f"l{i}.wo"])
         x = x + (tp.sum_partials(o) if tp is not None else o)
         n2 = ref.rmsnorm(x, v[f"l{i}.mlp_norm"], s.rms_norm_eps)
@@ -388,6 +385,9 @@ class LlamaModel:
         """Runs the stack; returns final-norm hidden states.  ``keep`` stores what backward needs."""
         f = self.kernels
         s, p = self.spec, self.p
+        if s.min_window and cu_seqlens.numel() > 1 and int((cu_seqlens[1:] - cu_seqlens[:-1]).max()) > s.min_window:
+            raise NotImplementedError(f"documents longer than the model's sliding window ({s.min_window}) need windowed attention; the attention "
+                                      "kernel attends to the whole document: run these with ops='ref'")
         pos = position_ids.to(torch.int32)
         cu = cu_seqlens.to(torch.int32)
         scale = s.head_dim ** -0.5

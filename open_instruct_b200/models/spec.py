@@ -53,9 +53,10 @@ class ModelSpec:
     router_aux_loss_coef: float = 0.01
     sliding_window: int | None = None  # some layers attend to the last N tokens only (OLMo-3, Mistral v0.1): documents up to N are exact
     attention_bias: bool = False  # Qwen2 style q/k/v bias
-    # hybrid models (OLMo-Hybrid): ``layer_types[i]`` is "attention" or "gdn" (gated DeltaNet: a linear-attention layer with a
-    # [key_dim, value_dim] state per head instead of a KV cache).  The gdn layers are pre-norm blocks; the attention layers
-    # follow ``post_norm`` / ``qk_norm_full`` like every other attention layer of the model.  None: all layers are attention.
+    # per-layer kinds: "attention" (attends to the whole document), "sliding" (to the last ``sliding_window`` tokens: three of
+    # four layers in OLMo-3), "gdn" (OLMo-Hybrid's gated DeltaNet: a linear-attention layer with a [key_dim, value_dim] state per
+    # head instead of a KV cache; a pre-norm block, while the attention layers follow ``post_norm`` / ``qk_norm_full``).
+    # None: all layers are attention layers, windowed when ``sliding_window`` is set (Mistral v0.1).
     layer_types: tuple | None = None
     gdn_key_heads: int = 0
     gdn_value_heads: int = 0
@@ -84,6 +85,22 @@ class ModelSpec:
 
     def is_gdn(self, i: int) -> bool:
         return self.layer_types is not None and self.layer_types[i] == "gdn"
+
+    @property
+    def has_gdn(self) -> bool:
+        return self.layer_types is not None and "gdn" in self.layer_types
+
+    def window(self, i: int) -> int | None:
+        """How many of the latest tokens (itself included) a token of layer ``i`` attends to; None: all of them."""
+        if not self.sliding_window:
+            return None
+        return self.sliding_window if (self.layer_types is None or self.layer_types[i] == "sliding") else None
+
+    @property
+    def min_window(self) -> int | None:
+        """The shortest attention window of any layer (None: no layer is windowed)."""
+        ws = [w for w in (self.window(i) for i in range(self.num_layers)) if w]
+        return min(ws) if ws else None
 
     @property
     def gdn_k_total(self) -> int:
@@ -119,6 +136,10 @@ class ModelSpec:
                           gdn_value_dim=cfg.get("linear_value_head_dim") or 2 * kd, gdn_conv=cfg.get("linear_conv_kernel_dim", 4),
                           gdn_neg_eigval=bool(cfg.get("linear_allow_neg_eigval", True)),
                           use_rope=(cfg.get("rope_theta") or rp.get("rope_theta")) is not None)
+        if mt == "olmo3" and cfg.get("sliding_window"):
+            n = cfg["num_hidden_layers"]
+            kinds = cfg.get("layer_types") or [("sliding_attention" if (i + 1) % 4 else "full_attention") for i in range(n)]
+            hybrid = dict(layer_types=tuple("sliding" if k == "sliding_attention" else "attention" for k in kinds))
         return cls(
             **hybrid,
             vocab_size=cfg["vocab_size"],
@@ -183,7 +204,13 @@ class ModelSpec:
             "pad_token_id": self.pad_token_id,
             "use_cache": True,
         }
-        if self.layer_types is not None:
+        if self.sliding_window:
+            cfg["sliding_window"] = self.sliding_window
+            if self.model_type not in ("mistral", "olmo3"):
+                cfg["use_sliding_window"] = True
+        if self.layer_types is not None and not self.has_gdn:
+            cfg["layer_types"] = ["sliding_attention" if k == "sliding" else "full_attention" for k in self.layer_types]
+        if self.has_gdn:
             cfg.update({"layer_types": ["full_attention" if k == "attention" else "linear_attention" for k in self.layer_types],
                         "linear_num_key_heads": self.gdn_key_heads, "linear_num_value_heads": self.gdn_value_heads,
                         "linear_key_head_dim": self.gdn_key_dim, "linear_value_head_dim": self.gdn_value_dim,

@@ -70,11 +70,12 @@ def _use_sdpa(qkv: torch.Tensor, allow: bool) -> bool:
 
 
 def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                     scale: float | None = None, allow_sdpa: bool = False) -> torch.Tensor:
+                     scale: float | None = None, allow_sdpa: bool = False, window: int | None = None) -> torch.Tensor:
     """Causal attention per document over packed tokens: explicit softmax in fp32 (the oracle of the kernel tests; it
     materialises a [heads, L, L] score matrix per document).  With ``allow_sdpa`` and half-precision inputs on a GPU -
     models whose only path this is in production (OLMo-2 / OLMo-3 / OLMoE blocks) - PyTorch's fused scaled-dot-product
-    attention per document instead, which does not."""
+    attention per document instead, which does not.  ``window``: a token attends to the latest ``window`` tokens of its
+    document only, itself included (sliding-window layers)."""
     T = qkv.shape[0]
     x = qkv.view(T, n_q + 2 * n_kv, head_dim)
     q, k, v = x[:, :n_q], x[:, n_q : n_q + n_kv], x[:, n_q + n_kv :]
@@ -85,8 +86,13 @@ def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_q: int, n_kv
         outs = []
         for s, e in zip(bounds[:-1], bounds[1:]):
             if e > s:
+                band = None
+                if window and e - s > window:
+                    idx = torch.arange(e - s, device=qkv.device)
+                    band = (idx[:, None] >= idx[None, :]) & (idx[:, None] - idx[None, :] < window)
                 o = torch.nn.functional.scaled_dot_product_attention(q[s:e].transpose(0, 1)[None], k[s:e].transpose(0, 1)[None],
-                                                                     v[s:e].transpose(0, 1)[None], is_causal=True, scale=scale, enable_gqa=g > 1)
+                                                                     v[s:e].transpose(0, 1)[None], attn_mask=band, is_causal=band is None,
+                                                                     scale=scale, enable_gqa=g > 1)
                 outs.append(o[0].transpose(0, 1))
         return torch.cat(outs, dim=0).reshape(T, n_q * head_dim)
     out = torch.empty(T, n_q, head_dim, dtype=qkv.dtype, device=qkv.device)
@@ -99,6 +105,8 @@ def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_q: int, n_kv
         sc = (qd @ kd.transpose(1, 2)) * scale
         L = e - s
         mask = torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril()
+        if window and L > window:
+            mask &= ~torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril(-window)
         sc = sc.masked_fill(~mask, float("-inf"))
         p = sc.softmax(-1)
         out[s:e] = (p @ vd).transpose(0, 1).to(qkv.dtype)

@@ -182,9 +182,14 @@ class RolloutEngine:
         self.spec = spec
         self.device = torch.device(device)
         if ops == "auto":
-            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts and lib.available()) else "ref"
+            windowed = bool(spec.min_window and max_model_len > spec.min_window)   # the paged attention kernels have no window
+            ops = "fused" if (self.device.type == "cuda" and spec.head_dim == 128 and not spec.post_norm and not spec.num_experts
+                              and not windowed and not spec.has_gdn and lib.available()) else "ref"
         self.ops = ops
-        if spec.layer_types is not None:
+        if ops == "fused" and spec.min_window and max_model_len > spec.min_window:
+            raise NotImplementedError(f"the paged attention kernels attend to the whole context; sequences longer than the model's sliding "
+                                      f"window ({spec.min_window}) need ops='ref' (or a max_model_len within the window)")
+        if spec.has_gdn:
             raise NotImplementedError("the rollout engine keeps a paged KV cache per sequence; the recurrent state of gated-DeltaNet layers "
                                       "(hybrid models) is not built, so these models can be trained (SFT, DPO, reward model) but not sampled from")
         if tp is not None and spec.post_norm:
@@ -554,10 +559,10 @@ class RolloutEngine:
         if self.ops == "fused":
             from ..ops import fused as f
 
-            attend = lambda qkv, cu_: f.attn_fwd(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale)[0]
+            attend = lambda qkv, cu_, i: f.attn_fwd(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale)[0]
         else:
-            attend = lambda qkv, cu_: ref.attention_varlen(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale,
-                                                           allow_sdpa=bool(s.post_norm or s.num_experts))
+            attend = lambda qkv, cu_, i: ref.attention_varlen(qkv, cu_, s.num_heads, s.num_kv_heads, s.head_dim, scale,
+                                                              allow_sdpa=bool(s.post_norm or s.num_experts), window=s.window(i))
         if any(cached):
             # packed layout with the prefixes in place: sequence j occupies rows [o_j, o_j + n_j), its first c_j rows are cached
             offs = [0]
@@ -576,9 +581,9 @@ class RolloutEngine:
                 ext[new_rows] = qkv
                 ext[pref_rows, qd:qd + kd] = self.k_cache[i][pblk, :, poff].reshape(len(pslots), kd)
                 ext[pref_rows, qd + kd:] = self.v_cache[i][pblk, :, poff].reshape(len(pslots), kd)
-                return attend(ext, cu_ext)[new_rows].contiguous()
+                return attend(ext, cu_ext, i)[new_rows].contiguous()
         else:
-            attn_fn = lambda i, qkv: attend(qkv, cu_d)
+            attn_fn = lambda i, qkv: attend(qkv, cu_d, i)
         hidden = self._layer_stack(ids_d, pos_d, slots, attn_fn)
         last = cu_d[1:].long() - 1
         logits = self._logits(hidden[last])
@@ -760,10 +765,12 @@ class RolloutEngine:
             def attn_fn(i, qkv):
                 q = qkv.view(B, s.num_heads + 2 * s.num_kv_heads, s.head_dim)[:, : s.num_heads].float()
                 outs = []
+                w = s.window(i)
                 for b in range(B):
                     blk = bt[b, : -(-ctx_list[b] // KV_BLOCK)].long()
-                    k = self.k_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, : ctx_list[b]].float()
-                    v = self.v_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, : ctx_list[b]].float()
+                    first = max(0, ctx_list[b] - w) if w else 0   # sliding-window layers read the latest w positions only
+                    k = self.k_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, first : ctx_list[b]].float()
+                    v = self.v_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, first : ctx_list[b]].float()
                     k, v = k.repeat_interleave(g, 0), v.repeat_interleave(g, 0)
                     p = torch.softmax((q[b][:, None, :] @ k.transpose(1, 2)) * scale, -1)
                     outs.append((p @ v).squeeze(1).reshape(-1))

@@ -21,6 +21,8 @@ FAMILIES = {
     "mistral": ("Mistral", dict(sliding_window=None)),
     "olmo2": ("Olmo2", {}),
     "olmo3": ("Olmo3", dict(sliding_window=4096)),
+    "olmo3-window-shorter-than-the-text": ("Olmo3", dict(sliding_window=16, num_hidden_layers=4)),
+    "mistral-window-shorter-than-the-text": ("Mistral", dict(sliding_window=16)),
     "olmo-hybrid": ("OlmoHybrid", dict(num_hidden_layers=4, pad_token_id=0, eos_token_id=1, rope_parameters={"rope_type": "default", "rope_theta": 10000.0})),
     "olmo-hybrid-grouped-key-heads": ("OlmoHybrid", dict(num_hidden_layers=4, pad_token_id=0, eos_token_id=1, linear_num_key_heads=2, linear_num_value_heads=4,
                                                          linear_key_head_dim=8, linear_value_head_dim=16, layer_types=["linear_attention", "full_attention", "linear_attention", "full_attention"])),
@@ -69,7 +71,8 @@ def test_checkpoint_import_gives_hf_logits(family):
     assert (_our_logits(ours, ids) - want).abs().max().item() < 1e-5
 
 
-@pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2", "olmoe", "olmo-hybrid", "olmo-hybrid-no-rope"])
+@pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2", "olmoe", "olmo-hybrid", "olmo-hybrid-no-rope", "olmo3-window-shorter-than-the-text",
+                                    "mistral-window-shorter-than-the-text"])
 def test_checkpoint_export_is_read_by_hf(family):
     from open_instruct_b200.ckpt.hf_io import save_hf_checkpoint
     from open_instruct_b200.models import LlamaModel
@@ -90,14 +93,16 @@ def test_checkpoint_export_is_read_by_hf(family):
     assert (got - _our_logits(ours, ids)).abs().max().item() < 1e-5
 
 
-def test_engine_generates_with_a_post_norm_model():
-    """The rollout engine's PyTorch path follows the block structure too: greedy tokens equal argmax decoding with the HF model."""
+@pytest.mark.parametrize("family", ["olmo2", "olmo3-window-shorter-than-the-text"])
+def test_engine_generates_with_a_post_norm_model(family):
+    """The rollout engine's PyTorch path follows the block structure (and the sliding-window layers, with a prompt longer than
+    the window) too: greedy tokens equal argmax decoding with the HF model."""
     from open_instruct_b200.ckpt.hf_io import load_hf_checkpoint
     from open_instruct_b200.data_types import SamplingConfig
     from open_instruct_b200.models.spec import ModelSpec
     from open_instruct_b200.rollout.engine import RolloutEngine
 
-    hf, cfg = _hf_model("Olmo2", {})
+    hf, cfg = _hf_model(*FAMILIES[family])
     with tempfile.TemporaryDirectory() as d:
         hf.save_pretrained(d, safe_serialization=True)
         spec = ModelSpec.from_pretrained(d).replace(eos_token_id=None)
@@ -225,7 +230,8 @@ def test_sft_on_a_mixture_of_experts_model_with_the_balancing_loss():
     assert g is None or float(g.abs().sum()) > 0              # the router itself is trained
 
 
-def test_fused_attention_branch_of_the_pytorch_path_equals_the_explicit_softmax():
+@pytest.mark.parametrize("window", [None, 7])
+def test_fused_attention_branch_of_the_pytorch_path_equals_the_explicit_softmax(window):
     """Models that only run on the PyTorch path use PyTorch's fused attention for half-precision GPU tensors; the branch is forced
     here on CPU and must agree with the explicit-softmax statement, values and gradients, for packed documents with grouped heads."""
     from open_instruct_b200.ops import ref
@@ -234,11 +240,13 @@ def test_fused_attention_branch_of_the_pytorch_path_equals_the_explicit_softmax(
     Hq, Hkv, Dh = 4, 2, 16
     qkv = torch.randn(50, (Hq + 2 * Hkv) * Dh, requires_grad=True)
     cu = torch.tensor([0, 20, 21, 50], dtype=torch.int32)
-    a = ref.attention_varlen(qkv, cu, Hq, Hkv, Dh)
+    a = ref.attention_varlen(qkv, cu, Hq, Hkv, Dh, window=window)
+    if window:  # the window changes the result for the documents longer than it
+        assert (a - ref.attention_varlen(qkv, cu, Hq, Hkv, Dh)).abs().max().item() > 1e-3
     ga, = torch.autograd.grad(a.square().sum(), qkv)
     ref._FORCE_SDPA = True
     try:
-        b = ref.attention_varlen(qkv, cu, Hq, Hkv, Dh)
+        b = ref.attention_varlen(qkv, cu, Hq, Hkv, Dh, window=window)
         gb, = torch.autograd.grad(b.square().sum(), qkv)
     finally:
         ref._FORCE_SDPA = False
