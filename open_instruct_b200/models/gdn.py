@@ -69,46 +69,45 @@ def gated_delta_rule(q, k, v, g, beta, state=None, chunk: int = 64):
     return torch.cat(outs), S
 
 
-def short_conv(x: torch.Tensor, w: torch.Tensor, cu_seqlens: torch.Tensor) -> torch.Tensor:
-    """Causal depthwise convolution + SiLU over packed documents.  x [T, C], w [C, taps] (tap ``taps - 1`` multiplies the
-    current token); nothing leaks across document boundaries."""
-    taps = w.shape[1]
-    out = []
-    bounds = cu_seqlens.tolist()
-    for a, b in zip(bounds[:-1], bounds[1:]):
-        if b > a:
-            seg = F.pad(x[a:b].t()[None], (taps - 1, 0))                  # [1, C, L + taps - 1]
-            out.append(F.conv1d(seg, w[:, None, :], groups=w.shape[0])[0].t())
-    return F.silu(torch.cat(out) if out else x)
-
-
 def _l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
 
 
-def gdn_mixer(x: torch.Tensor, v: dict, i: int, spec, cu_seqlens: torch.Tensor, chunk: int = 64, sequential: bool = False) -> torch.Tensor:
-    """The gated-DeltaNet sub-layer of layer ``i`` on normed input ``x`` [T, D] (packed documents); ``v`` are the parameter views."""
+def gdn_segment(x: torch.Tensor, v: dict, i: int, spec, state=None, chunk: int = 64, sequential: bool = False):
+    """The mixer over ONE run of consecutive tokens ``x`` [L, D] of a single sequence.  ``state`` continues an earlier run of
+    the same sequence: ``(conv_tail, S)`` = the last ``taps - 1`` rows that entered the convolution and the recurrent
+    state; None starts a document.  Returns ``(output [L, D], new state)``."""
     s = spec
     K, V, Hk, Hv, dk, dv = s.gdn_k_total, s.gdn_v_total, s.gdn_key_heads, s.gdn_value_heads, s.gdn_key_dim, s.gdn_value_dim
-    T = x.shape[0]
+    L = x.shape[0]
     proj = x @ v[f"l{i}.gdn_in"].t()
-    q, k, val, gate, a, b = proj.split([K, K, V, V, Hv, Hv], dim=1)
-    conv = short_conv(torch.cat([q, k, val], dim=1), v[f"l{i}.gdn_conv"], cu_seqlens)
+    qkv, gate, a, b = proj.split([2 * K + V, V, Hv, Hv], dim=1)
+    w = v[f"l{i}.gdn_conv"]
+    taps = w.shape[1]
+    tail = qkv.new_zeros(taps - 1, 2 * K + V) if state is None else state[0].to(qkv.dtype)
+    seq = torch.cat([tail, qkv])                                          # [taps - 1 + L, C]
+    conv = F.silu(F.conv1d(seq.t()[None], w[:, None, :], groups=w.shape[0])[0].t())
     q, k, val = conv.split([K, K, V], dim=1)
-    q = _l2norm(q.float().view(T, Hk, dk)) * dk ** -0.5
-    k = _l2norm(k.float().view(T, Hk, dk))
-    val = val.float().view(T, Hv, dv)
+    q = _l2norm(q.float().view(L, Hk, dk)) * dk ** -0.5
+    k = _l2norm(k.float().view(L, Hk, dk))
+    val = val.float().view(L, Hv, dv)
     if Hv > Hk:
         q, k = q.repeat_interleave(Hv // Hk, dim=1), k.repeat_interleave(Hv // Hk, dim=1)
     beta = torch.sigmoid(b.float()) * (2.0 if s.gdn_neg_eigval else 1.0)
     g = -v[f"l{i}.gdn_A_log"].float().exp() * F.softplus(a.float() + v[f"l{i}.gdn_dt_bias"].float())
-    rule = gated_delta_rule_sequential if sequential else (lambda *args: gated_delta_rule(*args, chunk=chunk))
-    outs = []
-    bounds = cu_seqlens.tolist()
-    for lo, hi in zip(bounds[:-1], bounds[1:]):   # every document starts from an empty state
-        if hi > lo:
-            outs.append(rule(q[lo:hi], k[lo:hi], val[lo:hi], g[lo:hi], beta[lo:hi])[0])
-    o = torch.cat(outs)                                                   # [T, Hv, dv] fp32
+    S0 = None if state is None else state[1]
+    if sequential or L == 1:
+        o, S = gated_delta_rule_sequential(q, k, val, g, beta, S0)
+    else:
+        o, S = gated_delta_rule(q, k, val, g, beta, S0, chunk=chunk)
     o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + 1e-5)           # the output norm's epsilon is fixed, not rms_norm_eps
-    o = (v[f"l{i}.gdn_o_norm"] * o.to(x.dtype)).float() * F.silu(gate.float().view(T, Hv, dv))
-    return o.to(x.dtype).reshape(T, V) @ v[f"l{i}.gdn_out"].t()
+    o = (v[f"l{i}.gdn_o_norm"] * o.to(x.dtype)).float() * F.silu(gate.float().view(L, Hv, dv))
+    return o.to(x.dtype).reshape(L, V) @ v[f"l{i}.gdn_out"].t(), (seq[-(taps - 1):].detach(), S.detach())
+
+
+def gdn_mixer(x: torch.Tensor, v: dict, i: int, spec, cu_seqlens: torch.Tensor, chunk: int = 64, sequential: bool = False) -> torch.Tensor:
+    """The gated-DeltaNet sub-layer of layer ``i`` on normed input ``x`` [T, D] of packed documents (``v``: the parameter
+    views): every document starts from an empty state and nothing crosses a document boundary."""
+    bounds = cu_seqlens.tolist()
+    outs = [gdn_segment(x[lo:hi], v, i, spec, None, chunk, sequential)[0] for lo, hi in zip(bounds[:-1], bounds[1:]) if hi > lo]
+    return torch.cat(outs) if outs else x.new_zeros(0, spec.hidden_size)

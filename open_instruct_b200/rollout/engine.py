@@ -189,9 +189,9 @@ class RolloutEngine:
         if ops == "fused" and spec.min_window and max_model_len > spec.min_window:
             raise NotImplementedError(f"the paged attention kernels attend to the whole context; sequences longer than the model's sliding "
                                       f"window ({spec.min_window}) need ops='ref' (or a max_model_len within the window)")
-        if spec.has_gdn:
-            raise NotImplementedError("the rollout engine keeps a paged KV cache per sequence; the recurrent state of gated-DeltaNet layers "
-                                      "(hybrid models) is not built, so these models can be trained (SFT, DPO, reward model) but not sampled from")
+        if spec.has_gdn and (ops != "ref" or tp is not None or enable_prefix_caching):
+            raise NotImplementedError("hybrid models (gated-DeltaNet layers) are sampled on the PyTorch path (ops='ref'), one engine per "
+                                      "model copy, without prefix caching: their per-sequence recurrent state lives beside the paged KV cache")
         if tp is not None and spec.post_norm:
             raise NotImplementedError("tensor-parallel engines are not built for post-norm blocks (OLMo-2 / OLMo-3)")
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
@@ -237,6 +237,9 @@ class RolloutEngine:
         self._graphs: dict = {}
         self._graph_seen: dict = {}
         self._graph_pool = None
+        # hybrid models: (convolution tail, recurrent state) of every gated-DeltaNet layer, per running sequence
+        self._gdn_state: dict[int, dict[int, tuple]] = {}
+        self._gdn_runs: list = []   # (first row, end row, sequence continued or None, sequences that receive the new state) of the pass in flight
         self._stages: dict = {}  # pinned staging blobs of the decode step, by batch size
         self._last_sids = None
 
@@ -304,6 +307,7 @@ class RolloutEngine:
             if seq is None or seq.finish_reason is None:
                 continue
             self.host.finish(sid, seq.tokens if self.prefix_caching else None)
+            self._gdn_state.pop(sid, None)
             del self.seqs[sid]
             req = seq.request
             req.done += 1
@@ -467,9 +471,24 @@ class RolloutEngine:
             return nf
         x = p["embed"][ids]
         for i in range(s.num_layers):
+            if s.is_gdn(i):   # a pre-norm block whose mixer carries a recurrent state per sequence instead of cached keys and values
+                from ..models.gdn import gdn_segment
+
+                n1 = ref.rmsnorm(x, p[f"l{i}.attn_norm"], s.rms_norm_eps)
+                outs = []
+                for lo, hi, src, dsts in self._gdn_runs:
+                    o, st = gdn_segment(n1[lo:hi], p, i, s, None if src is None else self._gdn_state[src][i])
+                    outs.append(o)
+                    for sid in dsts:
+                        self._gdn_state.setdefault(sid, {})[i] = st
+                x = x + torch.cat(outs)
+                x = x + self.model.ref_mlp(ref.rmsnorm(x, p[f"l{i}.mlp_norm"], s.rms_norm_eps), p, i)
+                continue
             # pre-norm blocks (Llama, Qwen, Mistral) norm the sub-layer's input; post-norm blocks (OLMo-2 / OLMo-3) its output
             n1 = x if s.post_norm else ref.rmsnorm(x, p[f"l{i}.attn_norm"], s.rms_norm_eps)
-            qkv = ref.rope(self.model.ref_qkv(n1, p, i), pos, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
+            qkv = self.model.ref_qkv(n1, p, i)
+            if s.use_rope:
+                qkv = ref.rope(qkv, pos, self.model.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim)
             heads = qkv.view(T, s.num_heads + 2 * s.num_kv_heads, s.head_dim)
             k_new, v_new = heads[:, s.num_heads : s.num_heads + s.num_kv_heads], heads[:, s.num_heads + s.num_kv_heads :]
             for rep in range(slots.numel() // T):
@@ -554,6 +573,9 @@ class RolloutEngine:
             slot_rows.append(row)
         dev = self.device
         ids_d, pos_d, cu_d = ids.to(dev), pos.to(dev), cu.to(dev)
+        if s.has_gdn:   # every prompt starts from an empty state; the samples of one request all continue from their prompt's
+            b = cu.tolist()
+            self._gdn_runs = [(b[j], b[j + 1], None, [m.sid for m in members[j]]) for j in range(len(reps))]
         slots = torch.tensor([x for r in slot_rows for x in r], dtype=torch.long, device=dev)
         scale = s.head_dim ** -0.5
         if self.ops == "fused":
@@ -747,6 +769,8 @@ class RolloutEngine:
                 self.stats["decode_steps"] += 1
             return
         ids = torch.tensor([q.last_token for q in seqs], dtype=torch.long, device=dev)
+        if s.has_gdn:
+            self._gdn_runs = [(b, b + 1, q.sid, [q.sid]) for b, q in enumerate(seqs)]
         ctx_list = [len(q.tokens) for q in seqs]  # the new token sits at position len-1
         pos = torch.tensor([n - 1 for n in ctx_list], dtype=torch.long, device=dev)
         tables = [self.host.blocks(q.sid)[0] for q in seqs]

@@ -93,10 +93,11 @@ def test_checkpoint_export_is_read_by_hf(family):
     assert (got - _our_logits(ours, ids)).abs().max().item() < 1e-5
 
 
-@pytest.mark.parametrize("family", ["olmo2", "olmo3-window-shorter-than-the-text"])
+@pytest.mark.parametrize("family", ["olmo2", "olmo3-window-shorter-than-the-text", "olmo-hybrid", "olmo-hybrid-no-rope", "olmo-hybrid-grouped-key-heads"])
 def test_engine_generates_with_a_post_norm_model(family):
-    """The rollout engine's PyTorch path follows the block structure (and the sliding-window layers, with a prompt longer than
-    the window) too: greedy tokens equal argmax decoding with the HF model."""
+    """The rollout engine's PyTorch path follows the block structure (the sliding-window layers, with a prompt longer than the
+    window; the gated-DeltaNet layers, whose recurrent state it keeps per sequence) too: greedy tokens equal argmax decoding
+    with the HF model."""
     from open_instruct_b200.ckpt.hf_io import load_hf_checkpoint
     from open_instruct_b200.data_types import SamplingConfig
     from open_instruct_b200.models.spec import ModelSpec
@@ -109,12 +110,14 @@ def test_engine_generates_with_a_post_norm_model(family):
         eng = RolloutEngine(spec, device="cpu", ops="auto", num_blocks=32)
         load_hf_checkpoint(d, eng.model.flat.detach(), spec)
     prompt = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(4)).tolist()
-    out = eng.generate([prompt], SamplingConfig(temperature=0.0, max_tokens=6, n=1))[0].responses[0]
-    ids = list(prompt)
-    with torch.no_grad():
-        for _ in range(6):
-            ids.append(int(hf(torch.tensor([ids])).logits[0, -1].argmax()))
-    assert out == ids[len(prompt):]
+    outs = eng.generate([prompt, prompt[:33]], SamplingConfig(temperature=0.0, max_tokens=6, n=2))   # the samples share their prompt pass
+    for res, pr in zip(outs, (prompt, prompt[:33])):
+        ids = list(pr)
+        with torch.no_grad():
+            for _ in range(6):
+                ids.append(int(hf(torch.tensor([ids])).logits[0, -1].argmax()))
+        assert res.responses == [ids[len(pr):]] * 2
+    assert eng._gdn_state == {}   # per-sequence recurrent state is dropped with the sequence
 
 
 @pytest.mark.parametrize("family", ["llama", "qwen2"])
