@@ -13,6 +13,7 @@ import dataclasses
 
 FLOP_PER_MAC = 2
 SOFTMAX_FLOPS_PER_SCORE = 4
+GDN_RECURRENCE_PASSES = 4   # state-sized multiply-add passes of the gated delta rule per token: read-out, error, decayed state, update
 
 GPU_SPECS = {
     "a100": {"flops": 312e12, "memory_size": 80e9, "memory_bandwidth": 2.0e12},
@@ -39,6 +40,14 @@ def get_device_name(device_name: str | None = None) -> str:
     raise ValueError(f"unknown device {device_name!r}; known: {sorted(GPU_SPECS)}")
 
 
+def _keys_seen(prompt: int, response: int, window: int | None) -> int:
+    """Sum over the response tokens k = 1..R of the keys token k attends to: ``prompt + k``, capped at ``window``."""
+    if not window:
+        return response * prompt + response * (response + 1) // 2
+    m = max(0, min(response, window - prompt - 1))   # tokens whose context is still shorter than the window
+    return m * prompt + m * (m + 1) // 2 + (response - m) * window
+
+
 @dataclasses.dataclass
 class ModelDims:
     num_layers: int
@@ -52,14 +61,21 @@ class ModelDims:
     device_name: str | None = None
     sliding_window: int | None = None
     num_sliding_window_layers: int = 0
+    # hybrid models: layers whose sequence mixer is a gated DeltaNet (cost linear in the tokens, a fixed-size state per head)
+    num_linear_attn_layers: int = 0
+    linear_attn_num_k_heads: int = 0
+    linear_attn_num_v_heads: int = 0
+    linear_attn_key_head_dim: int = 0
+    linear_attn_value_head_dim: int = 0
+    linear_attn_conv_size: int = 4
 
     def __post_init__(self):
         if self.num_kv_heads is None:
             self.num_kv_heads = self.num_attn_heads
         if self.num_attn_heads % self.num_kv_heads:
             raise ValueError("num_attn_heads must be divisible by num_kv_heads")
-        if self.num_sliding_window_layers > self.num_layers:
-            raise ValueError("more sliding-window layers than layers")
+        if self.num_sliding_window_layers + self.num_linear_attn_layers > self.num_layers:
+            raise ValueError("more sliding-window and linear-attention layers than layers")
         if self.num_params is None:
             self.num_params = self._calculate_num_params()
 
@@ -68,7 +84,12 @@ class ModelDims:
     def from_spec(cls, spec, device_name: str | None = None) -> "ModelDims":
         return cls(num_layers=spec.num_layers, hidden_size=spec.hidden_size, intermediate_size=spec.intermediate_size,
                    vocab_size=spec.vocab_size, num_attn_heads=spec.num_heads, head_dim=spec.head_dim,
-                   num_kv_heads=spec.num_kv_heads, device_name=device_name)
+                   num_kv_heads=spec.num_kv_heads, device_name=device_name, sliding_window=spec.sliding_window,
+                   num_sliding_window_layers=sum(1 for i in range(spec.num_layers) if spec.window(i)),
+                   num_linear_attn_layers=sum(1 for i in range(spec.num_layers) if spec.is_gdn(i)),
+                   linear_attn_num_k_heads=spec.gdn_key_heads, linear_attn_num_v_heads=spec.gdn_value_heads,
+                   linear_attn_key_head_dim=spec.gdn_key_dim, linear_attn_value_head_dim=spec.gdn_value_dim,
+                   linear_attn_conv_size=spec.gdn_conv)
 
     @classmethod
     def from_hf_config(cls, model_name_or_path: str) -> "ModelDims":
@@ -82,7 +103,22 @@ class ModelDims:
         attn = self.hidden_size * (q + 2 * kv) + q * self.hidden_size
         mlp = 3 * self.hidden_size * self.intermediate_size
         norms = 2 * self.hidden_size
-        return self.num_layers * (attn + mlp + norms) + 2 * self.vocab_size * self.hidden_size + self.hidden_size
+        n_attn = self.num_layers - self.num_linear_attn_layers
+        return (n_attn * attn + self.num_linear_attn_layers * self._gdn_layer_params() + self.num_layers * (mlp + norms)
+                + 2 * self.vocab_size * self.hidden_size + self.hidden_size)
+
+    @property
+    def linear_attn_key_dim(self) -> int:
+        return self.linear_attn_num_k_heads * self.linear_attn_key_head_dim
+
+    @property
+    def linear_attn_value_dim(self) -> int:
+        return self.linear_attn_num_v_heads * self.linear_attn_value_head_dim
+
+    def _gdn_layer_params(self) -> int:
+        """Parameters of one gated-DeltaNet mixer (q, k, v, gate, output projections; decay and beta projections; the taps)."""
+        h, kd, vd = self.hidden_size, self.linear_attn_key_dim, self.linear_attn_value_dim
+        return 2 * h * kd + 3 * h * vd + 2 * h * self.linear_attn_num_v_heads + (2 * kd + vd) * self.linear_attn_conv_size
 
     @property
     def device_flops(self) -> float:
@@ -104,13 +140,27 @@ class ModelDims:
         values = FLOP_PER_MAC * query_len * kv_eff * hd * h
         return proj + scores + softmax + values
 
+    def linear_attn_flops(self, seq_len: int) -> int:
+        """One gated-DeltaNet layer over ``seq_len`` tokens (``open_instruct/utils.py:2014-2042``): projections, convolution and
+        ``GDN_RECURRENCE_PASSES`` passes over the [key_dim, value_dim] state of every head per token (read-out, error, decay,
+        update).  Independent of the context length, so prefill and decode cost the same per token."""
+        m, d, kd, vd, hv = FLOP_PER_MAC, self.hidden_size, self.linear_attn_key_dim, self.linear_attn_value_dim, self.linear_attn_num_v_heads
+        proj = m * seq_len * d * (2 * kd + 2 * vd + 2 * hv) + m * seq_len * vd * d
+        conv = m * seq_len * self.linear_attn_conv_size * (2 * kd + vd)
+        rec = m * GDN_RECURRENCE_PASSES * seq_len * hv * self.linear_attn_key_head_dim * self.linear_attn_value_head_dim
+        return proj + conv + rec
+
+    def gdn_state_bytes(self, num_tokens: int, dtype_bytes: int = 2) -> int:
+        """Bytes moved for the recurrent state: every decoded token reads and writes each layer's whole state once."""
+        return self.num_linear_attn_layers * num_tokens * 2 * self.linear_attn_num_v_heads * self.linear_attn_key_head_dim * self.linear_attn_value_head_dim * dtype_bytes
+
     def mlp_flops(self, seq_len: int) -> int:
         return 3 * FLOP_PER_MAC * seq_len * self.hidden_size * self.intermediate_size
 
     def _layer_stack(self, query_len: int, kv_len: int) -> int:
-        full = self.num_layers - self.num_sliding_window_layers
+        full = self.num_layers - self.num_sliding_window_layers - self.num_linear_attn_layers
         return (full * self.attn_flops(query_len, kv_len) + self.num_sliding_window_layers * self.attn_flops(query_len, kv_len, self.sliding_window)
-                + self.num_layers * self.mlp_flops(query_len))
+                + self.num_linear_attn_layers * self.linear_attn_flops(query_len) + self.num_layers * self.mlp_flops(query_len))
 
     def prefill_flops(self, prompt_lengths: list[int]) -> int:
         """Causal prefill: token t attends to t+1 keys -> average kv length (L+1)/2."""
@@ -129,12 +179,14 @@ class ModelDims:
         if len(response_lengths) != len(prompt_lengths) * samples_per_prompt:
             raise ValueError("response_lengths must have len(prompt_lengths) * samples_per_prompt entries")
         total = 0
+        lin = self._layer_stack(1, 0)   # projections, MLP, linear-attention layers: per token, whatever the context
+        full = self.num_layers - self.num_sliding_window_layers - self.num_linear_attn_layers
+        per_key = self.attn_flops(1, 1) - self.attn_flops(1, 0)   # one layer, one more key
         for i, P in enumerate(prompt_lengths):
             for R in response_lengths[i * samples_per_prompt:(i + 1) * samples_per_prompt]:
-                # token k of the response attends to P + k keys: sum over k of one-token layers
-                lin = self._layer_stack(1, 0)
-                per_key = self._layer_stack(1, 1) - lin
-                total += R * lin + per_key * (R * P + R * (R + 1) // 2)
+                # token k of the response attends to P + k keys (at most the window in a sliding-window layer)
+                keys = full * _keys_seen(P, R, None) + self.num_sliding_window_layers * _keys_seen(P, R, self.sliding_window)
+                total += R * lin + per_key * keys
                 total += FLOP_PER_MAC * R * self.hidden_size * self.vocab_size
         return total
 
@@ -150,15 +202,17 @@ class ModelDims:
         """Weights streamed once per forward pass of ``num_tokens`` decode steps (batch-1 view)."""
         q = self.num_attn_heads * self.head_dim
         kv = self.num_kv_heads * self.head_dim
-        per_layer = self.hidden_size * (q + 2 * kv) + q * self.hidden_size + 3 * self.hidden_size * self.intermediate_size
-        return num_tokens * dtype_bytes * (self.num_layers * per_layer + self.vocab_size * self.hidden_size)
+        attn = self.hidden_size * (q + 2 * kv) + q * self.hidden_size
+        mlp = 3 * self.hidden_size * self.intermediate_size
+        layers = (self.num_layers - self.num_linear_attn_layers) * attn + self.num_linear_attn_layers * self._gdn_layer_params() + self.num_layers * mlp
+        return num_tokens * dtype_bytes * (layers + self.vocab_size * self.hidden_size)
 
     def kv_cache_write_bytes(self, num_tokens: int, dtype_bytes: int = 2) -> int:
-        return num_tokens * self.num_layers * 2 * self.num_kv_heads * self.head_dim * dtype_bytes
+        return num_tokens * (self.num_layers - self.num_linear_attn_layers) * 2 * self.num_kv_heads * self.head_dim * dtype_bytes
 
     def kv_cache_read_bytes(self, prompt_lengths: list[int], response_lengths: list[int], samples_per_prompt: int = 1,
                             dtype_bytes: int = 2) -> int:
-        per_tok = self.num_layers * 2 * self.num_kv_heads * self.head_dim * dtype_bytes
+        per_tok = (self.num_layers - self.num_linear_attn_layers) * 2 * self.num_kv_heads * self.head_dim * dtype_bytes
         total = 0
         for i, P in enumerate(prompt_lengths):
             for R in response_lengths[i * samples_per_prompt:(i + 1) * samples_per_prompt]:
@@ -172,7 +226,8 @@ class ModelDims:
                             dtype_bytes: int = 2) -> int:
         steps = max(response_lengths) if response_lengths else 0  # one weight pass per batched decode step
         return (self.weight_memory_bytes(steps, dtype_bytes) + self.kv_cache_write_bytes(sum(response_lengths), dtype_bytes)
-                + self.kv_cache_read_bytes(prompt_lengths, response_lengths, samples_per_prompt, dtype_bytes))
+                + self.kv_cache_read_bytes(prompt_lengths, response_lengths, samples_per_prompt, dtype_bytes)
+                + self.gdn_state_bytes(sum(response_lengths), dtype_bytes))
 
     def memory_bytes(self, prompt_lengths: list[int], response_lengths: list[int] | None = None, samples_per_prompt: int = 1,
                      dtype_bytes: int = 2) -> int:

@@ -314,3 +314,28 @@ def test_decode_gemm_plan_fills_one_wave():
     assert decode_gemm_plan(6144, 4096, False, 256)[2] == 1            # no K split without a plane-summing consumer
     assert decode_gemm_plan(128, 512, True, 256) == (64, 1, 1)         # tiny weights: splitting only adds planes
     assert [decode_splits(1000, s) for s in (2, 3, 4, 5, 16)] == [2, 3, 4, 4, 16]
+
+
+def test_model_dims_account_for_hybrid_and_sliding_window_layers():
+    """Parameter count of the analytic model equals the flat layout's (up to alignment padding and the small vectors it leaves
+    out); gated-DeltaNet layers cost the same per token whatever the context; sliding-window layers stop growing at the window."""
+    from open_instruct_b200.models import get_spec
+    from open_instruct_b200.models.spec import ParamLayout
+    from open_instruct_b200.utils.model_dims import GDN_RECURRENCE_PASSES, ModelDims
+
+    spec = get_spec("olmo-hybrid-7b")
+    d = ModelDims.from_spec(spec, device_name="b200")
+    assert d.num_linear_attn_layers == 24 and d.num_sliding_window_layers == 0
+    assert abs(d.num_params - ParamLayout(spec).total) / d.num_params < 1e-3
+    assert d.linear_attn_flops(2) == 2 * d.linear_attn_flops(1)
+    assert d.gdn_state_bytes(3) == 24 * 3 * 2 * 30 * 96 * 192 * 2
+    rec = 2 * GDN_RECURRENCE_PASSES * 30 * 96 * 192
+    assert d.linear_attn_flops(1) > rec > 0
+    # decode FLOPs grow with the context only through the 8 attention layers
+    a, b = d.decode_flops([1000], [1]), d.decode_flops([2000], [1])
+    full = ModelDims.from_spec(spec.replace(layer_types=None, model_type="olmo2"), device_name="b200")
+    assert 0 < (b - a) < (full.decode_flops([2000], [1]) - full.decode_flops([1000], [1])) / 3.9
+    o3 = get_spec("olmo2-7b").replace(model_type="olmo3", sliding_window=4096, layer_types=tuple("attention" if i % 4 == 3 else "sliding" for i in range(32)))
+    w = ModelDims.from_spec(o3, device_name="b200")
+    assert w.num_sliding_window_layers == 24 and w.sliding_window == 4096
+    assert w.decode_flops([8000], [1]) < ModelDims.from_spec(get_spec("olmo2-7b"), device_name="b200").decode_flops([8000], [1])
