@@ -262,6 +262,9 @@ class EngineWorker:
             device = f"cuda:{ids.split(',')[0]}" if ids and torch.cuda.is_available() else ("cuda:0" if torch.cuda.is_available() else "cpu")
         if str(device).startswith("cuda"):
             torch.cuda.set_device(torch.device(device))
+            from .utils.numa import bind_to_gpu
+
+            bind_to_gpu(device)
 
         if flat is not None:
             want = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
@@ -665,6 +668,9 @@ class LearnerWorker:
         _, _, dev = pdist.init_distributed(backend=None if torch.cuda.is_available() and device != "cpu" else "gloo",
                                            timeout_s=args.backend_timeout * 60)
         self.device = torch.device(device) if device else dev
+        from .utils.numa import bind_to_gpu
+
+        bind_to_gpu(self.device)   # the CPUs (and, by first touch, the pinned host buffers) next to this rank's GPU
         set_seed(args.seed + rank)
         self.args, self.spec = args, spec
         warm = args.warm_up_steps or int(num_training_steps * args.warmup_ratio)

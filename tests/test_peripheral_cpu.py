@@ -656,3 +656,36 @@ def test_decontamination_through_an_elasticsearch_index(tmp_path):
         assert rep["train_contaminated"] == [1] and rep["eval_contaminated"] == 1
     finally:
         fake.close()
+
+
+def test_numa_node_of_a_gpu_and_binding(tmp_path):
+    """The node comes from the GPU's PCI device in sysfs, else from the rank formula; binding goes through the host runtime and
+    leaves the process on that node's CPUs."""
+    import os
+
+    from open_instruct_b200.utils import numa
+
+    root = tmp_path / "sys"
+    for n in (0, 1):
+        (root / f"devices/system/node/node{n}").mkdir(parents=True)
+    dev = root / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    unknown = root / "bus/pci/devices/0000:9d:00.0"
+    unknown.mkdir(parents=True)
+    (unknown / "numa_node").write_text("-1\n")
+    s = str(root)
+    assert numa.numa_node_count(s) == 2
+    assert numa.pci_numa_node("00000000:1B:00.0", s) == 1          # the driver's spelling: 8-digit domain, upper case
+    assert numa.node_for_gpu(0, "0000:1b:00.0", 8, s) == 1
+    assert numa.node_for_gpu(5, "0000:9d:00.0", 8, s) == 1          # sysfs does not say: ranks 4-7 of 8 sit on the second node
+    assert numa.node_for_gpu(2, None, 8, s) == 0
+    assert numa.bind_to_gpu("cpu") is None
+    before = os.sched_getaffinity(0)
+    try:
+        n = numa.bind_to_node(0)
+        if n > 0:   # this machine exposes node 0
+            assert len(os.sched_getaffinity(0)) <= n
+        assert numa.bind_to_node(4096) == 0
+    finally:
+        os.sched_setaffinity(0, before)
