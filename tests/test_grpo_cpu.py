@@ -166,3 +166,40 @@ def test_engine_worker_runs_tool_sessions(tmp_path):
         w.check_background_threads()
     finally:
         w.shutdown()
+
+
+@pytest.mark.parametrize("family", ["olmo-hybrid", "olmo3-window-shorter-than-the-text"])
+def test_grpo_on_hybrid_and_sliding_window_models(tmp_path, family):
+    """The whole loop on an OLMo-Hybrid model (gated-DeltaNet layers: recurrent state in the engine, chunked rule in the learner)
+    and on OLMo-3 with a window shorter than prompt + response: the engine's sampling log-probs equal the learner's at every
+    step (also after a weight sync), and the export loads as the same transformers class."""
+    transformers = pytest.importorskip("transformers")
+    from open_instruct_b200.config.schemas import ModelConfig
+    from open_instruct_b200.data.tokenize import TokenizerConfig
+    from open_instruct_b200.grpo_fast import main
+    from open_instruct_b200.grpo_utils import GRPOExperimentConfig
+    from open_instruct_b200.streaming import StreamingDataLoaderConfig, VLLMConfig
+
+    tmp = str(tmp_path)
+    tok = make_tokenizer(os.path.join(tmp, "tok"))
+    common = dict(vocab_size=600, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                  max_position_embeddings=256, pad_token_id=0, eos_token_id=1)
+    torch.manual_seed(0)
+    if family == "olmo-hybrid":
+        hf = transformers.OlmoHybridForCausalLM(transformers.OlmoHybridConfig(**common))
+    else:
+        hf = transformers.Olmo3ForCausalLM(transformers.Olmo3Config(sliding_window=16, **common))
+    src = os.path.join(tmp, "hf")
+    hf.save_pretrained(src)
+    data = make_rlvr_jsonl(os.path.join(tmp, "rl.jsonl"), n=12)
+    args = GRPOExperimentConfig(total_episodes=2 * 4 * 4, learning_rate=1e-3, beta=0.0, load_ref_policy=False, output_dir=os.path.join(tmp, "out"),
+                                single_gpu_mode=True, ops="ref", seed=3, save_freq=-1, lr_scheduler_type="constant")
+    streaming = StreamingDataLoaderConfig(max_prompt_token_length=64, response_length=12, pack_length=256, async_steps=1,
+                                          num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=4, dataset_mixer_list=[data, "1.0"],
+                                          dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False, temperature=1.0)
+    main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path=src), streaming, VLLMConfig())
+    lines = [json.loads(l) for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
+    assert len(lines) == 2
+    for l in lines:
+        assert l["debug/vllm_vs_local_logprob_diff_mean"] < 1e-5
+    assert type(transformers.AutoModelForCausalLM.from_pretrained(args.output_dir)) is type(hf)
