@@ -391,7 +391,12 @@ class Learner:
             self.last_aux_loss = aux.detach()
         if self.sp > 1:
             n = self.local_slice(batch["labels_shifted"] != IGNORE).sum()
-        self.backward(loss, last=last)
+        # the fused path's ``aux_loss`` is a number: its backward pass adds the balancing loss's gradient itself, with this weight
+        self.model.aux_loss_coef = float(self.cfg.load_balancing_weight or 0.0) if aux is not None else 0.0
+        try:
+            self.backward(loss, last=last)
+        finally:
+            self.model.aux_loss_coef = 0.0
         return loss.detach(), n
 
     def sft_step(self, micro_batches: list[dict], reduce_loss: str = "mean") -> dict:

@@ -59,6 +59,19 @@ class _LayerStash:
     act: torch.Tensor | None = None
     o: torch.Tensor | None = None          # post-norm blocks: the attention sub-layer's output before its norm
     d: torch.Tensor | None = None          # post-norm blocks: the feed-forward sub-layer's output before its norm
+    moe: "_MoEStash | None" = None         # mixture of experts: routing and the experts' intermediate results
+
+
+@dataclass
+class _MoEStash:
+    tok: torch.Tensor       # [T * k] token of every (token, expert) assignment, grouped by expert
+    slot: torch.Tensor      # [T * k] which of the token's k choices the assignment is
+    counts: list            # assignments per expert (the groups' lengths)
+    gu: torch.Tensor        # [T * k, 2F] gate | up of every assignment (overwritten by its gradient in the backward)
+    y: torch.Tensor         # [T * k, D] expert outputs before the routing weight
+    lg: torch.Tensor        # [T, E] fp32 router logits, leaf of the small autograd graph that yields ...
+    probs: torch.Tensor     # ... their softmax and
+    top_w: torch.Tensor     # ... the k routing weights of every token
 
 
 def load_balancing_loss(router_logits: list, num_experts: int, top_k: int):
@@ -103,16 +116,14 @@ class LlamaModel:
             from ..ops import emulated
 
             self.kernels = emulated
-            if spec.num_experts:
-                raise NotImplementedError("mixture-of-experts layers run with ops='ref'")
         elif ops == "fused":
             self.kernels = _fused()
             if dtype != torch.bfloat16 or self.device.type != "cuda":
                 raise ValueError("the fused path runs bf16 on CUDA")
             if spec.head_dim != 128:
                 raise NotImplementedError("fused attention is built for head_dim 128")
-            if spec.num_experts:
-                raise NotImplementedError("the fused layer engine is built for dense blocks; mixture-of-experts layers run with ops='ref'")
+            if spec.num_experts and (spec.post_norm or sharded):
+                raise NotImplementedError("mixture-of-experts layers on the fused path: pre-norm blocks with resident parameters only")
             from ..ops import lib
 
             if not lib.available():
@@ -138,6 +149,9 @@ class LlamaModel:
         # keep the RMSNorm outputs and the SwiGLU activation for the backward pass instead of recomputing them
         # (5.8 GB per 4096-token micro-batch at 8B; about 2.5 % of the step): on by default, off under checkpointing
         self.keep_cheap_activations = os.environ.get("B200_RECOMPUTE_CHEAP", "0") != "1"
+        # mixture of experts: the weight with which the trainer adds ``aux_loss`` to its loss.  On the fused path ``aux_loss`` is a
+        # detached scalar and the backward pass adds this multiple of its gradient to the routers itself.
+        self.aux_loss_coef = 0.0
         self.tp = None  # parallel.tp.TrainTP when the layers are split over a tensor-parallel group (spec is then the LOCAL spec)
         self.sp = None  # parallel.ulysses.UlyssesContext when the sequence is split over ranks (fused path)
         # called with (lo, hi) once the flat gradient range [lo, hi) is final for this optimizer step; the learner sets it
@@ -401,6 +415,7 @@ class LlamaModel:
         if z is not None:
             z.fwd_begin()
         stream = f.embedding_fwd(p["embed"], input_ids)
+        self._routing = [] if s.num_experts else None   # (logits, chosen experts) of every layer, for the load-balancing loss
         delta = None  # pending residual contribution, added inside the next RMSNorm
         for i in range(s.num_layers):
             if z is not None:
@@ -420,9 +435,14 @@ class LlamaModel:
                 self.tp.all_reduce_(o)      # row-parallel projection: sum of the ranks' partials
             n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=h_in)
             del o
-            gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
-            act = f.swiglu_fwd(gate_up)
-            delta = f.gemm(act, p[f"l{i}.w_down"])
+            moe = None
+            if s.num_experts:
+                delta, moe = self._moe_forward(i, n2)
+                gate_up, act = moe.gu, None
+            else:
+                gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
+                act = f.swiglu_fwd(gate_up)
+                delta = f.gemm(act, p[f"l{i}.w_down"])
             if self.tp is not None:
                 self.tp.all_reduce_(delta)
             keep_cheap = keep and self.keep_cheap_activations and not self.gradient_checkpointing
@@ -433,8 +453,8 @@ class LlamaModel:
                 if self.gradient_checkpointing:
                     stash.append(_LayerStash(h_in, None, None, None, None, None, None, None))
                 else:
-                    stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk, n1, n2, act))
-            del n1, n2, act
+                    stash.append(_LayerStash(h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk, n1, n2, act, moe=moe))
+            del n1, n2, act, moe
         if delta is None:   # post-norm blocks leave no pending contribution: the stream is complete
             nf, h_last, rstd_f = f.rmsnorm_fwd(stream, p["final_norm"], s.rms_norm_eps)
         else:
@@ -442,6 +462,16 @@ class LlamaModel:
         state = None
         if keep:
             state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu, "rope_tab": self._rope_tab}
+        if s.num_experts:
+            # the load-balancing loss of this forward (a plain number here: the backward adds ``aux_loss_coef`` times its gradient,
+            # which reaches the routers through the mean probability of every expert, E / N * sum_k f[k, e] per softmax entry)
+            logits = torch.cat([lg for lg, _ in self._routing])
+            sel = torch.cat([te for _, te in self._routing])
+            self.aux_loss = load_balancing_loss([logits], s.num_experts, s.num_experts_per_tok).detach()
+            if keep:
+                share = torch.nn.functional.one_hot(sel, s.num_experts).float().mean(0).sum(0)   # sum over the k ranks of f[k, e]
+                state["aux_dprobs"] = share * (s.num_experts / logits.shape[0])
+            self._routing = None
         return nf, state
 
     def _post_norm_layer(self, i: int, x, pos, cu) -> _LayerStash:
@@ -507,6 +537,95 @@ class LlamaModel:
         d_x = f.gemm(dqkv, p[f"l{i}.wqkv"], b_mn=True)
         d_x.add_(d_mid)
         return d_x
+
+    def _moe_forward(self, i: int, n2):
+        """Mixture-of-experts feed-forward of layer ``i`` on normed input ``n2`` [T, D]: the router's k best experts per token,
+        each a SwiGLU MLP, outputs weighted by the router's softmax probabilities.  The (token, expert) assignments are sorted by
+        expert, so that an expert's tokens are consecutive rows and its two projections are one GEMM each over that row range
+        (the stacked expert weights are row slices of one flat-buffer entry).  Returns ``(delta [T, D], stash)``."""
+        f = self.kernels
+        s, p = self.spec, self.p
+        if self.tp is not None or self.sp is not None:
+            raise NotImplementedError("tensor and sequence parallelism are not built for mixture-of-experts layers")
+        E, F, D, k = s.num_experts, s.intermediate_size, s.hidden_size, s.num_experts_per_tok
+        T = n2.shape[0]
+        logits = f.gemm(n2, p[f"l{i}.router"])
+        with torch.enable_grad():   # [T, E]-sized: softmax, top-k and renormalisation are left to autograd
+            lg = logits.detach().float().requires_grad_(True)
+            probs = torch.softmax(lg, dim=-1)
+            top_w, top_e = probs.topk(k, dim=-1)
+            if s.norm_topk_prob:
+                top_w = top_w / top_w.sum(-1, keepdim=True)
+        if self._routing is not None:
+            self._routing.append((lg.detach(), top_e))
+        flat_e = top_e.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        counts = torch.bincount(flat_e, minlength=E).tolist()   # the one host synchronisation of the layer
+        tok, slot = order // k, order % k
+        x = n2[tok]
+        w_gu, w_dn = p[f"l{i}.w_gate_up"], p[f"l{i}.w_down"]
+        gu = torch.empty(T * k, 2 * F, dtype=n2.dtype, device=n2.device)
+        r = 0
+        for e, n in enumerate(counts):
+            if n:
+                f.gemm(x[r:r + n], w_gu[e * 2 * F:(e + 1) * 2 * F], gu[r:r + n])
+            r += n
+        act = f.swiglu_fwd(gu)
+        y = torch.empty(T * k, D, dtype=n2.dtype, device=n2.device)
+        r = 0
+        for e, n in enumerate(counts):
+            if n:
+                f.gemm(act[r:r + n], w_dn[e * D:(e + 1) * D], y[r:r + n])
+            r += n
+        tw = top_w.detach().to(n2.dtype)[tok, slot]
+        delta = torch.zeros(T, D, dtype=torch.float32, device=n2.device).index_add_(0, tok, (y * tw[:, None]).float()).to(n2.dtype)
+        return delta, _MoEStash(tok, slot, counts, gu, y, lg, probs, top_w)
+
+    def _moe_backward(self, i: int, m: _MoEStash, d_delta, n2, aux_dprobs, wgrad_mode):
+        """Backward of ``_moe_forward``: gradient of its output in, gradient of ``n2`` out; expert and router weight gradients
+        are accumulated into the flat gradient buffer."""
+        f = self.kernels
+        s, p, g = self.spec, self.p, self.g
+        E, F, D, k = s.num_experts, s.intermediate_size, s.hidden_size, s.num_experts_per_tok
+        T = n2.shape[0]
+        tw = m.top_w.detach().to(n2.dtype)[m.tok, m.slot]
+        dwy = d_delta[m.tok]
+        d_tw = torch.zeros(T, k, dtype=torch.float32, device=n2.device)
+        d_tw[m.tok, m.slot] = (dwy.float() * m.y.float()).sum(-1)
+        dy = dwy * tw[:, None]
+        del dwy
+        act = f.swiglu_fwd(m.gu)
+        w_gu, w_dn = p[f"l{i}.w_gate_up"], p[f"l{i}.w_down"]
+        g_gu, g_dn = g[f"l{i}.w_gate_up"], g[f"l{i}.w_down"]
+        d_act = torch.empty_like(act)
+        r = 0
+        for e, n in enumerate(m.counts):
+            if n:
+                f.gemm(dy[r:r + n], act[r:r + n], g_dn[e * D:(e + 1) * D], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+                f.gemm(dy[r:r + n], w_dn[e * D:(e + 1) * D], d_act[r:r + n], b_mn=True)
+            r += n
+        del act, dy
+        dgu = f.swiglu_bwd_(m.gu, d_act)
+        del d_act
+        x = n2[m.tok]
+        dx = torch.empty_like(x)
+        r = 0
+        for e, n in enumerate(m.counts):
+            if n:
+                f.gemm(dgu[r:r + n], x[r:r + n], g_gu[e * 2 * F:(e + 1) * 2 * F], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+                f.gemm(dgu[r:r + n], w_gu[e * 2 * F:(e + 1) * 2 * F], dx[r:r + n], b_mn=True)
+            r += n
+        d_n2 = torch.zeros(T, D, dtype=torch.float32, device=n2.device).index_add_(0, m.tok, dx.float())
+        # routing weights (and the load-balancing loss, when the trainer adds it) back to the router logits, then to the router
+        with torch.enable_grad():   # the backward pass runs with gradient recording off
+            objective = (m.top_w * d_tw).sum()
+            if self.aux_loss_coef and aux_dprobs is not None:
+                objective = objective + self.aux_loss_coef * (m.probs * aux_dprobs).sum()
+            (d_lg,) = torch.autograd.grad(objective, m.lg)
+        d_logits = d_lg.to(n2.dtype)
+        f.gemm(d_logits, n2, g[f"l{i}.router"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+        d_n2 += f.gemm(d_logits, p[f"l{i}.router"], b_mn=True).float()
+        return d_n2.to(n2.dtype)
 
     def _attention_block(self, i: int, n1, pos, cu):
         """QKV projection, RoPE and attention of layer ``i``.  Returns ``(qkv, attn, lse, attn_tok)``; with sequence
@@ -585,6 +704,9 @@ class LlamaModel:
         if self.tp is not None:
             self.tp.all_reduce_(o)
         n2, h_mid, rstd2 = f.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], s.rms_norm_eps, res=st.h_in)
+        if s.num_experts:
+            moe = self._moe_forward(i, n2)[1]
+            return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, moe.gu, attn_tok, self._last_qk, moe=moe)
         gate_up = f.gemm(n2, p[f"l{i}.w_gate_up"])
         return _LayerStash(st.h_in, rstd1, qkv, attn, lse, h_mid, rstd2, gate_up, attn_tok, self._last_qk)
 
@@ -620,21 +742,28 @@ class LlamaModel:
                     self.grad_ready_hook(*self.layer_grad_range(i))
                 continue
             # ---- MLP: out = h_mid + down(swiglu(gate_up(norm(h_mid))))
-            act = st.act if st.act is not None else f.swiglu_fwd(st.gate_up)
-            st.act = None
-            f.gemm(d_stream, act, g[f"l{i}.w_down"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
-            d_act = f.gemm(d_stream, p[f"l{i}.w_down"], b_mn=True)
-            del act
-            dgu = f.swiglu_bwd_(st.gate_up, d_act)
-            del d_act
-            n2 = st.n2 if st.n2 is not None else f.rmsnorm_fwd(st.h_mid, p[f"l{i}.mlp_norm"], s.rms_norm_eps)[0]
-            st.n2 = None
-            f.gemm(dgu, n2, g[f"l{i}.w_gate_up"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
-            del n2
-            d_n2 = f.gemm(dgu, p[f"l{i}.w_gate_up"], b_mn=True)
-            if self.tp is not None:
-                self.tp.all_reduce_(d_n2)   # column-parallel projection: the input gradient is a sum over the ranks
-            del dgu
+            if s.num_experts:
+                n2 = st.n2 if st.n2 is not None else f.rmsnorm_fwd(st.h_mid, p[f"l{i}.mlp_norm"], s.rms_norm_eps)[0]
+                st.n2 = None
+                d_n2 = self._moe_backward(i, st.moe, d_stream, n2, state.get("aux_dprobs"), wgrad_mode)
+                st.moe = None
+                del n2
+            else:
+                act = st.act if st.act is not None else f.swiglu_fwd(st.gate_up)
+                st.act = None
+                f.gemm(d_stream, act, g[f"l{i}.w_down"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+                d_act = f.gemm(d_stream, p[f"l{i}.w_down"], b_mn=True)
+                del act
+                dgu = f.swiglu_bwd_(st.gate_up, d_act)
+                del d_act
+                n2 = st.n2 if st.n2 is not None else f.rmsnorm_fwd(st.h_mid, p[f"l{i}.mlp_norm"], s.rms_norm_eps)[0]
+                st.n2 = None
+                f.gemm(dgu, n2, g[f"l{i}.w_gate_up"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
+                del n2
+                d_n2 = f.gemm(dgu, p[f"l{i}.w_gate_up"], b_mn=True)
+                if self.tp is not None:
+                    self.tp.all_reduce_(d_n2)   # column-parallel projection: the input gradient is a sum over the ranks
+                del dgu
             d_mid = f.rmsnorm_bwd(st.h_mid, p[f"l{i}.mlp_norm"], st.rstd2, d_n2, d_stream, g[f"l{i}.mlp_norm"])
             del d_n2, d_stream
             # ---- attention: h_mid = h_in + wo(attn(rope(wqkv(norm(h_in)))))

@@ -21,6 +21,10 @@ VARIANTS = {
     "olmo2-chunked-head-recompute": (OLMO2, dict(chunk=128, keep_cheap=False)),
     "olmo2-mha": ({**OLMO2, "num_kv_heads": 4}, {}),
     "post-norm-only": (dict(post_norm=True), {}),
+    "olmoe": (dict(qk_norm=True, qk_norm_full=True, num_experts=4, num_experts_per_tok=2, intermediate_size=48), {}),
+    "olmoe-renormalised-checkpointing": (dict(num_experts=4, num_experts_per_tok=2, norm_topk_prob=True, intermediate_size=48), dict(ckpt=True)),
+    "olmoe-balancing-loss": (dict(num_experts=8, num_experts_per_tok=2, intermediate_size=48), dict(aux=0.3)),
+    "olmoe-balancing-loss-checkpointing": (dict(num_experts=8, num_experts_per_tok=3, intermediate_size=48), dict(aux=0.3, ckpt=True, keep_cheap=False)),
 }
 
 
@@ -55,11 +59,18 @@ def test_hand_driven_backward_equals_autograd(name, monkeypatch):
         monkeypatch.setattr(llama_mod, "LOGIT_CHUNK_TOKENS", opts["chunk"])
     ids, pos, cu, labels, wgt = _batch(spec)
     got = []
+    aux = opts.get("aux", 0.0)   # mixture of experts: weight of the load-balancing loss in the trainer's loss
+    b.aux_loss_coef = aux
     for m in (a, b):
         for _ in range(2):  # two micro-batches: gradients accumulate
             lp, ent = m.token_logprobs(ids, pos, cu, labels, opts.get("temperature", 1.0), want_entropy=True)
-            (lp * wgt).sum().backward()
+            loss = (lp * wgt).sum()
+            if aux:   # differentiable on the autograd path; a number on the hand-driven path, whose backward adds the gradient itself
+                loss = loss + aux * m.aux_loss
+            loss.backward()
         got.append((lp.detach(), ent.detach(), m.grad_flat().clone()))
+    if spec.num_experts:
+        assert abs(float(a.aux_loss) - float(b.aux_loss)) < 1e-5 and not b.aux_loss.requires_grad
     (lp0, e0, g0), (lp1, e1, g1) = got
     assert (lp0 - lp1).abs().max().item() < 1e-5
     assert (e0 - e1).abs().max().item() < 1e-5
@@ -80,17 +91,18 @@ def test_hidden_state_bridge_for_the_reward_head():
     assert (ga - gb).abs().max().item() < 1e-5 * ga.abs().max().item()
 
 
-@pytest.mark.parametrize("family", ["llama", "olmo2"])
+@pytest.mark.parametrize("family", ["llama", "olmo2", "olmoe"])
 def test_learner_steps_on_the_emulated_path_follow_the_pytorch_path(family):
     """Three optimizer steps of two micro-batches each through ``Learner``: the fused path's branches of the learner (fp32
     gradient buffer, zeroing after the step, gradient-ready hook around the last backward) give the parameters of the autograd path."""
     from open_instruct_b200.learner import Learner, LearnerConfig
 
-    spec = ModelSpec(**{**BASE, **(OLMO2 if family == "olmo2" else {})})
+    extra = {"olmo2": OLMO2, "olmoe": dict(num_experts=4, num_experts_per_tok=2, intermediate_size=48), "llama": {}}[family]
+    spec = ModelSpec(**{**BASE, **extra})
     flats = []
     for ops in ("ref", "emulated"):
-        ln = Learner(spec, LearnerConfig(ops=ops, learning_rate=1e-2, warmup_steps=0, total_steps=10, max_grad_norm=1.0, seed=4),
-                     device="cpu")
+        ln = Learner(spec, LearnerConfig(ops=ops, learning_rate=1e-2, warmup_steps=0, total_steps=10, max_grad_norm=1.0, seed=4,
+                                         load_balancing_weight=0.5 if family == "olmoe" else 0.0), device="cpu")
         for step in range(3):
             for mb in range(2):
                 ids, pos, cu, labels, _ = _batch(spec, seed=10 * step + mb)

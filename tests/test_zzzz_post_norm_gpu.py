@@ -66,3 +66,28 @@ def test_fused_engine_generates_like_the_ref_engine_with_post_norm_blocks():
     assert agree / total > 0.8
     lib.check_status()
     assert fused.host.free_blocks() == 64
+
+
+def test_fused_mixture_of_experts_matches_ref():
+    """OLMoE-style layers through the kernels (per-expert GEMMs over the sorted assignments) against the PyTorch fp32 model.  The
+    router sees bf16 logits here and fp32 logits there, so a token whose two best experts are nearly tied may be routed
+    differently: the bounds are on averages, not on the worst token."""
+    from open_instruct_b200.models import LlamaModel, get_spec
+    from open_instruct_b200.ops import lib
+
+    spec = get_spec("tiny128").replace(qk_norm=True, qk_norm_full=True, num_experts=4, num_experts_per_tok=2, intermediate_size=256,
+                                       model_type="olmoe")
+    fused = LlamaModel(spec, device="cuda", dtype=torch.bfloat16, ops="fused", seed=3)
+    refm = LlamaModel(spec, device="cuda", dtype=torch.float32, ops="ref", flat=fused.flat.float().clone())
+    ids, pos, cu, labels = _batch([200, 57, 300], spec.vocab_size, "cuda")
+    fused.aux_loss_coef = 0.1
+    lp_f, _ = fused.token_logprobs(ids, pos, cu, labels)
+    lp_r, _ = refm.token_logprobs(ids, pos, cu, labels)
+    n = (labels >= 0).sum()
+    assert (lp_f - lp_r).abs().mean().item() < 0.02
+    assert abs(float(fused.aux_loss) - float(refm.aux_loss)) < 0.02
+    (-(lp_f.sum()) / n).backward()
+    (-(lp_r.sum()) / n + 0.1 * refm.aux_loss).backward()
+    lib.check_status()
+    gf, gr = fused.grad_flat(), refm.grad_flat()
+    assert ((gf - gr).norm() / gr.norm()).item() < 0.15
