@@ -150,3 +150,30 @@ def test_qlora_finetune_trains_on_the_quantised_base(tmp_path):
     assert torch.allclose(v1["l0.wqkv"], tr.base.entry("l0.wqkv"))
     adapted = sum(lr.model.layout.entries[n].numel for n in tr.base.q)
     assert tr.base.nbytes() < 0.3 * adapted * 2
+
+
+def test_training_state_checkpoint_converts_to_a_hugging_face_folder(tmp_path):
+    """A mid-run checkpoint (optimizer shards with the fp32 master weights) becomes an HF folder without the trainer; converting the
+    last checkpoint of a run gives the run's own export."""
+    from safetensors import safe_open
+
+    from open_instruct_b200.ckpt import convert_state_to_hf
+    from open_instruct_b200.finetune import main
+
+    args, tc = _args(str(tmp_path), checkpointing_steps="5", keep_last_n_checkpoints=-1)
+    main(args, tc)
+    assert os.path.exists(os.path.join(args.output_dir, "step_5", "COMPLETED"))
+    out = convert_state_to_hf.main(["--checkpoint-dir", os.path.join(args.output_dir, "step_10"), "--model-name", "tiny",
+                                    "--output-dir", str(tmp_path / "hf10"), "--tokenizer-name", tc.tokenizer_name_or_path])
+    assert os.path.exists(os.path.join(out, "tokenizer.json")) and os.path.exists(os.path.join(out, "config.json"))
+    with safe_open(os.path.join(out, "model.safetensors"), "pt") as a, safe_open(os.path.join(args.output_dir, "model.safetensors"), "pt") as b:
+        assert sorted(a.keys()) == sorted(b.keys())
+        for k in a.keys():
+            assert torch.equal(a.get_tensor(k), b.get_tensor(k)), k
+    mid = convert_state_to_hf.main(["--checkpoint-dir", os.path.join(args.output_dir, "step_5"), "--model-name", "tiny",
+                                    "--output-dir", str(tmp_path / "hf5")])
+    with safe_open(os.path.join(mid, "model.safetensors"), "pt") as a, safe_open(os.path.join(out, "model.safetensors"), "pt") as b:
+        assert any(not torch.equal(a.get_tensor(k), b.get_tensor(k)) for k in a.keys())
+    os.remove(os.path.join(args.output_dir, "step_5", "COMPLETED"))
+    with pytest.raises(RuntimeError, match="COMPLETED"):
+        convert_state_to_hf.main(["--checkpoint-dir", os.path.join(args.output_dir, "step_5"), "--model-name", "tiny", "--output-dir", str(tmp_path / "x")])
