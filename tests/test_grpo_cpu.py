@@ -203,3 +203,33 @@ def test_grpo_on_hybrid_and_sliding_window_models(tmp_path, family):
     for l in lines:
         assert l["debug/vllm_vs_local_logprob_diff_mean"] < 1e-5
     assert type(transformers.AutoModelForCausalLM.from_pretrained(args.output_dir)) is type(hf)
+
+
+def test_grpo_recipe_topology_four_learners_two_tensor_parallel_engines(tmp_path, monkeypatch):
+    """The process layout of the 8-GPU recipe - 4 learner ranks, 2 engines of tensor-parallel size 2 - as CPU processes (gloo):
+    engines start with random weights and take the learners' through the first weight sync (re-laid out per tensor-parallel
+    rank, verified by checksum), two training steps complete."""
+    monkeypatch.setenv("B200_GRPO_INIT_BY_PUSH", "force")
+    from open_instruct_b200.actors import ray_compat as ray
+    from open_instruct_b200.config.schemas import ModelConfig
+    from open_instruct_b200.data.tokenize import TokenizerConfig
+    from open_instruct_b200.grpo_fast import main
+    from open_instruct_b200.grpo_utils import GRPOExperimentConfig
+    from open_instruct_b200.streaming import StreamingDataLoaderConfig, VLLMConfig
+
+    tmp = str(tmp_path)
+    tok = make_tokenizer(os.path.join(tmp, "tok"))
+    data = make_rlvr_jsonl(os.path.join(tmp, "rl.jsonl"), n=16)
+    args = GRPOExperimentConfig(total_episodes=2 * 8 * 4, learning_rate=1e-3, beta=0.0, load_ref_policy=False, output_dir=os.path.join(tmp, "out"),
+                                num_learners_per_node=[4], ops="ref", seed=3, save_freq=-1, lr_scheduler_type="constant", verify_weight_sync=True)
+    streaming = StreamingDataLoaderConfig(max_prompt_token_length=64, response_length=8, pack_length=128, async_steps=1,
+                                          num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=8, dataset_mixer_list=[data, "1.0"],
+                                          dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False)
+    try:
+        out = main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path="tiny"),
+                   streaming, VLLMConfig(vllm_num_engines=2, vllm_tensor_parallel_size=2))
+    finally:
+        ray.shutdown()
+    assert out["training_step"] == 2
+    lines = [json.loads(l) for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
+    assert len(lines) == 2 and lines[0]["debug/vllm_vs_local_logprob_diff_mean"] < 1e-4   # the engines sampled with the learners' weights
