@@ -270,6 +270,7 @@ class EngineWorker:
             want = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
             flat = flat.detach().to(device=device, dtype=want).clone()
         self.full_flat = None  # tensor parallel: staging copy of the whole model that the learners push into
+        self._full_cv, self._full_step = threading.Condition(), None   # which version a follower's staging copy holds
         if tp_size > 1:
             self.engine = self._build_tp_engine(spec, device, ops, seed, max_model_len, num_blocks, gpu_memory_utilization, flat, tokenizer,
                                                 max_running, tp_addr, tp_port)
@@ -323,15 +324,22 @@ class EngineWorker:
         from .rollout.engine import KV_BLOCK, RolloutEngine
 
         dev = torch.device(device)
-        dist.init_process_group(backend="cpu:gloo,cuda:nccl", init_method=f"tcp://{addr}:{port}", rank=self.tp_rank, world_size=self.tp_size,
-                                timeout=datetime.timedelta(seconds=600), device_id=dev)
+        on_gpu = dev.type == "cuda"
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl" if on_gpu else "gloo", init_method=f"tcp://{addr}:{port}", rank=self.tp_rank,
+                                world_size=self.tp_size, timeout=datetime.timedelta(seconds=600), device_id=dev if on_gpu else None)
         self._tp_cmd_group = dist.new_group(backend="gloo")
         ls = local_spec(spec, self.tp_size)
         self.full_flat = None  # a full-size staging copy exists only while a host-supplied update is applied (CPU path)
         self._tp_spec = spec
         # without initial weights the shard starts random: the driver pushes the learners' weights before any prompt is queued
         local = shard_flat(flat, spec, self.tp_rank, self.tp_size) if flat is not None else None
-        tp = TPContext(spec.hidden_size, max(4096, max_model_len), dev)
+        if on_gpu:
+            tp = TPContext(spec.hidden_size, max(4096, max_model_len), dev)
+        else:  # CPU processes: the PyTorch path with gloo all-reduces; same leader / follower command stream and weight updates
+            from .parallel.tp import HostTPContext
+
+            tp = HostTPContext(spec.hidden_size, max(4096, max_model_len), dev)
+            ops = "ref"
         if num_blocks is None:
             free, total = torch.cuda.mem_get_info(dev)
             per_block = 2 * ls.num_layers * ls.num_kv_heads * KV_BLOCK * ls.head_dim * 2
@@ -365,6 +373,10 @@ class EngineWorker:
                     elif cmd[0] == "step":
                         self.engine.step()
                     elif cmd[0] == "reshard":
+                        # the whole model for this version arrives through this rank's own update call, which may still be copying
+                        with self._full_cv:
+                            if not self._full_cv.wait_for(lambda: self._full_step == cmd[1], timeout=600):
+                                raise RuntimeError(f"tensor-parallel follower never received the weights of step {cmd[1]}")
                         self._reshard(cmd[1])
                     elif cmd[0] == "fence":
                         if self.engine.device.type == "cuda":
@@ -496,6 +508,9 @@ class EngineWorker:
                 self._reshard(model_step)
             else:
                 self.full_flat[:n].copy_(flat[:n].to(self.full_flat.dtype))
+                with self._full_cv:   # the leader's "reshard" may reach the follower thread before this copy: it waits for it
+                    self._full_step = model_step
+                    self._full_cv.notify_all()
             return
         if flat is not None:
             self.engine.update_weights(flat, model_step)
@@ -1035,7 +1050,7 @@ class GRPORun:
             # (16 GB at 8B: gathered to the driver, shared with every engine rank, copied to each GPU and re-sharded there).
             init_by_push = (cuda and os.environ.get("B200_GRPO_INIT_BY_PUSH", "1") == "1") or os.environ.get("B200_GRPO_INIT_BY_PUSH") == "force"
             init_flat = None if init_by_push else ray.get(learners[0].flat_weights_cpu.remote())
-            tp = vllm.vllm_tensor_parallel_size if cuda else 1
+            tp = vllm.vllm_tensor_parallel_size
             followers = []
             if tp == 1:
                 engines = [EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote(
@@ -1048,8 +1063,8 @@ class GRPORun:
                 # __init__, so they are created together
                 tp_ports = [pdist.find_free_port() for _ in range(vllm.vllm_num_engines)]  # one rendezvous per engine
                 with ThreadPoolExecutor(max_workers=tp * vllm.vllm_num_engines) as ex:
-                    futs = [[ex.submit(EW.options(num_gpus=1, max_concurrency=8).remote, spec, prompt_q, results_q, eval_q, reward_cfg if r == 0 else None,
-                                       tc_plain, "auto", args.ops, args.seed + 100 * i, max_len, None, vllm.vllm_gpu_memory_utilization, init_flat,
+                    futs = [[ex.submit(EW.options(num_gpus=1 if cuda else 0, max_concurrency=8).remote, spec, prompt_q, results_q, eval_q, reward_cfg if r == 0 else None,
+                                       tc_plain, "auto" if cuda else "cpu", args.ops, args.seed + 100 * i, max_len, None if cuda else 512, vllm.vllm_gpu_memory_utilization, init_flat,
                                        streaming.inflight_updates, 256, tools_config if r == 0 else None, r, tp, "127.0.0.1", tp_ports[i],
                                        enable_prefix_caching=vllm.vllm_enable_prefix_caching)
                              for r in range(tp)] for i in range(vllm.vllm_num_engines)]
@@ -1119,7 +1134,9 @@ class GRPORun:
             self.call_all(self.engines, "update_weights", None, step)
         else:
             flat = self.call(self.learners[0], "flat_weights_cpu")
-            self.call_all(self.engines, "update_weights", flat, step)
+            # every rank of a tensor-parallel engine receives the whole model and cuts its shard out of it when the leader's
+            # command reaches it (the leader sends it after its own copy; a follower waits for its own copy to be complete)
+            self.call_all(list(self.engines) + list(self.followers), "update_weights", flat, step)
         return time.perf_counter() - t0
 
     def begin(self) -> int:

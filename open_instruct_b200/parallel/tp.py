@@ -241,6 +241,22 @@ class TrainTP:
             dist.all_reduce(grads["lm_head"], group=self.group)
 
 
+class HostTPContext:
+    """Tensor-parallel context of the rollout engine's PyTorch path: the row-parallel partial sums are added with a plain
+    ``torch.distributed`` all-reduce (gloo on CPU, NCCL on a GPU).  It lets every host-side part of a tensor-parallel engine -
+    the leader's command stream, the followers, weight updates that arrive as whole models and are re-laid out per rank - run
+    as CPU processes."""
+
+    def __init__(self, hidden: int, max_tokens: int, device, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.device, self.hidden, self.max_tokens = torch.device(device), hidden, max_tokens
+
+    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, group=self.group)
+        return t
+
+
 class TPContext:
     """Two symmetric ``[max_tokens, hidden]`` bf16 buffers for the row-parallel outputs + the fused reduction."""
 

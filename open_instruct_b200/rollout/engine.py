@@ -192,8 +192,9 @@ class RolloutEngine:
         if spec.has_gdn and (ops != "ref" or tp is not None or enable_prefix_caching):
             raise NotImplementedError("hybrid models (gated-DeltaNet layers) are sampled on the PyTorch path (ops='ref'), one engine per "
                                       "model copy, without prefix caching: their per-sequence recurrent state lives beside the paged KV cache")
-        if tp is not None and spec.post_norm:
-            raise NotImplementedError("tensor-parallel engines are not built for post-norm blocks (OLMo-2 / OLMo-3)")
+        if tp is not None and (spec.post_norm or spec.num_experts):
+            raise NotImplementedError("tensor-parallel engines are built for dense pre-norm blocks (a norm or a router over all heads / "
+                                      "experts does not split by rank)")
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, seed=seed, flat=flat)
         if ops == "ref":
@@ -499,9 +500,13 @@ class RolloutEngine:
                 self.v_cache[i][blk, :, off] = v_new[ok]
             attn = attn_fn(i, qkv)
             o = ref.linear(attn, p[f"l{i}.wo"])
+            if self.tp is not None:   # this rank's heads only: the projection's output is a partial sum
+                o = self.tp.all_reduce_sum(o.contiguous())
             x = x + (ref.rmsnorm(o, p[f"l{i}.attn_norm"], s.rms_norm_eps) if s.post_norm else o)
             n2 = x if s.post_norm else ref.rmsnorm(x, p[f"l{i}.mlp_norm"], s.rms_norm_eps)
             d = self.model.ref_mlp(n2, p, i)  # dense SwiGLU, or the router's experts
+            if self.tp is not None:
+                d = self.tp.all_reduce_sum(d.contiguous())
             x = x + (ref.rmsnorm(d, p[f"l{i}.mlp_norm"], s.rms_norm_eps) if s.post_norm else d)
         return ref.rmsnorm(x, p["final_norm"], s.rms_norm_eps)
 

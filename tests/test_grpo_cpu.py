@@ -206,9 +206,11 @@ def test_grpo_on_hybrid_and_sliding_window_models(tmp_path, family):
 
 
 def test_grpo_recipe_topology_four_learners_two_tensor_parallel_engines(tmp_path, monkeypatch):
-    """The process layout of the 8-GPU recipe - 4 learner ranks, 2 engines of tensor-parallel size 2 - as CPU processes (gloo):
-    engines start with random weights and take the learners' through the first weight sync (re-laid out per tensor-parallel
-    rank, verified by checksum), two training steps complete."""
+    """The process layout of the 8-GPU recipe - 4 learner ranks, 2 engines of tensor-parallel size 2 (each rank its own process:
+    a leader that drives and a follower that mirrors its command stream) - as 8 CPU processes over gloo.  The engine ranks start
+    with random weights and take the learners' through the first weight sync (every rank receives the model and cuts out its
+    shard when the leader's command reaches it; verified per shard by checksum), the tensor-parallel engines' sampling log-probs
+    equal the learners', two training steps complete."""
     monkeypatch.setenv("B200_GRPO_INIT_BY_PUSH", "force")
     from open_instruct_b200.actors import ray_compat as ray
     from open_instruct_b200.config.schemas import ModelConfig
