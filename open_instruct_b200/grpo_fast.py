@@ -1040,11 +1040,14 @@ class GRPORun:
             LW, EW = ray.remote(LearnerWorker), ray.remote(EngineWorker)
             from concurrent.futures import ThreadPoolExecutor
 
+            t_up = time.time()
+            stage = lambda what: logger.info("start-up: %s (%.1f s)", what, time.time() - t_up)   # where a stalled start-up stopped
             with ThreadPoolExecutor(max_workers=args.world_size) as ex:  # ranks must start together: they rendezvous in __init__
                 futs = [ex.submit(LW.options(num_gpus=1 if cuda else 0, max_concurrency=4).remote, r, args.world_size, "127.0.0.1", port,
                                   spec, args, model_config, args.num_training_steps, None if cuda else "cpu")
                         for r in range(args.world_size)]
                 learners = [f.result() for f in futs]
+            stage(f"{args.world_size} learner ranks constructed")
             # On GPUs the engines start with random weights and receive the learners' through the first weight sync (the same
             # push kernel as every later one) instead of a by-value copy of the whole model handed to every engine process
             # (16 GB at 8B: gathered to the driver, shared with every engine rank, copied to each GPU and re-sharded there).
@@ -1071,10 +1074,12 @@ class GRPORun:
                     handles = [[f.result() for f in row] for row in futs]
                 engines = [row[0] for row in handles]
                 followers = [h for row in handles for h in row[1:]]
+            stage(f"{len(engines)} engines constructed (tensor-parallel size {tp}, {len(followers)} follower ranks)")
             ray.get([e.ready.remote() for e in engines + followers] + [l.ready.remote() for l in learners])
             if cuda:
                 descs = ray.get([e.weight_buffer_ipc.remote() for e in engines + followers])
                 ray.get([l.connect_engines.remote(descs) for l in learners])
+                stage("learners mapped the engines' parameter buffers")
             single_objs = False
 
         # ---- everything the step methods need
@@ -1100,7 +1105,8 @@ class GRPORun:
         self.ref_update_in_step = True  # False: a callback of the driver updates the reference policy after the step
         self._closed = False
         if init_by_push:
-            self.weight_sync(0)  # the engines' first weights
+            t_first = self.weight_sync(0)  # the engines' first weights
+            logger.info("start-up: first weight sync %.2f s", t_first)
             if args.verify_weight_sync:
                 diff = self._checksum_diff(0)
                 if not diff <= 1e-3:
