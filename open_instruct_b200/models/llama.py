@@ -376,14 +376,14 @@ class LlamaModel:
             if tp is not None:
                 raise NotImplementedError("tensor parallelism is not built for post-norm blocks")
             qkv = rope(self.ref_qkv(x, v, i))
-            attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=True, window=s.window(i))
+            attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, s.attn_scale, allow_sdpa=True, window=s.window(i))
             x = x + ref.rmsnorm(ref.linear(attn, v[f"l{i}.wo"]), v[f"l{i}.attn_norm"], s.rms_norm_eps)
             return x + ref.rmsnorm(self.ref_mlp(x, v, i), v[f"l{i}.mlp_norm"], s.rms_norm_eps)
         n1 = ref.rmsnorm(x, v[f"l{i}.attn_norm"], s.rms_norm_eps)
         if tp is not None:
             n1 = tp.enter(n1)
         qkv = rope(self.ref_qkv(n1, v, i))
-        attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, allow_sdpa=bool(s.num_experts), window=s.window(i))
+        attn = ref.attention_varlen(qkv, cu_seqlens, s.num_heads, s.num_kv_heads, s.head_dim, s.attn_scale, allow_sdpa=bool(s.num_experts), window=s.window(i))
         o = ref.linear(attn, v[f"l{i}.wo"])
         x = x + (tp.sum_partials(o) if tp is not None else o)
         n2 = ref.rmsnorm(x, v[f"l{i}.mlp_norm"], s.rms_norm_eps)
@@ -404,7 +404,7 @@ class LlamaModel:
                                       "kernel attends to the whole document: run these with ops='ref'")
         pos = position_ids.to(torch.int32)
         cu = cu_seqlens.to(torch.int32)
-        scale = s.head_dim ** -0.5
+        scale = s.attn_scale
         stash: list[_LayerStash] = []
         self._rope_tab = f.rope_table(pos, self.inv_freq, s.head_dim)  # cos/sin once per packed batch, for every layer and the backward
         if self.sp is not None:
@@ -498,7 +498,7 @@ class LlamaModel:
         """Backward of ``_post_norm_layer``: gradient of the layer's output in, gradient of its input out."""
         f = self.kernels
         s, p, g, sp = self.spec, self.p, self.g, self.sp
-        scale = s.head_dim ** -0.5
+        scale = s.attn_scale
         # ---- out = h_mid + norm(d),  d = down(swiglu(gate_up(h_mid)))
         d_d = f.rmsnorm_bwd(st.d, p[f"l{i}.mlp_norm"], st.rstd2, d_out, None, g[f"l{i}.mlp_norm"])
         st.d = None
@@ -633,7 +633,7 @@ class LlamaModel:
         heads (else ``attn_tok`` is None)."""
         f = self.kernels
         s, p, sp = self.spec, self.p, self.sp
-        scale = s.head_dim ** -0.5
+        scale = s.attn_scale
         if sp is None:
             qkv = f.gemm(n1, p[f"l{i}.wqkv"])
             self._last_qk = self.qkv_bias_and_norm_(qkv, i)
@@ -722,7 +722,7 @@ class LlamaModel:
         # final norm: h_last = stream + delta ; both get the same gradient
         d_stream = f.rmsnorm_bwd(h_last, p["final_norm"], rstd_f, d_nf, None, g["final_norm"])
         del d_nf
-        scale = s.head_dim ** -0.5
+        scale = s.attn_scale
         z = self.zero3
         # sharded parameters: a layer's gradient workspace is written once per micro-batch and reduced right away, so the
         # weight-gradient GEMMs overwrite it (no zeroing pass, no read in the epilogue); otherwise they accumulate

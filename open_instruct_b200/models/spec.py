@@ -83,6 +83,14 @@ class ModelSpec:
     def qkv_dim(self) -> int:
         return self.q_dim + 2 * self.kv_dim
 
+    @property
+    def attn_scale(self) -> float:
+        """Softmax scale of the attention layers: ``head_dim ** -0.5``, times the square of the factor YaRN puts on cos / sin
+        (q and k both carry it; the rotation itself stays unscaled here)."""
+        from ..ops.ref import rope_attention_factor
+
+        return self.head_dim ** -0.5 * rope_attention_factor(self.rope_scaling) ** 2
+
     def is_gdn(self, i: int) -> bool:
         return self.layer_types is not None and self.layer_types[i] == "gdn"
 
@@ -229,6 +237,9 @@ class ModelSpec:
 LLAMA31_SCALING = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                    "original_max_position_embeddings": 8192}
 
+OLMO3_YARN = {"rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 8192, "attention_factor": 1.2079441541679836,
+              "beta_fast": 32.0, "beta_slow": 1.0}
+
 PRESETS: dict[str, ModelSpec] = {
     # the CPU plumbing configuration: 2 layers, d 64, 4 heads, ffn 256, vocab 512, theta 1e4
     "tiny": ModelSpec(vocab_size=512, hidden_size=64, intermediate_size=256, num_layers=2, num_heads=4,
@@ -260,6 +271,32 @@ PRESETS: dict[str, ModelSpec] = {
     "olmo2-7b": ModelSpec(vocab_size=100352, hidden_size=4096, intermediate_size=11008, num_layers=32, num_heads=32,
                           num_kv_heads=32, head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2",
                           qk_norm=True, qk_norm_full=True, post_norm=True, max_position_embeddings=4096),
+    "olmo2-13b": ModelSpec(vocab_size=100352, hidden_size=5120, intermediate_size=13824, num_layers=40, num_heads=40, num_kv_heads=40,
+                           head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2", qk_norm=True, qk_norm_full=True, post_norm=True,
+                           max_position_embeddings=4096),
+    "olmo2-32b": ModelSpec(vocab_size=100352, hidden_size=5120, intermediate_size=27648, num_layers=64, num_heads=40, num_kv_heads=8,
+                           head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2", qk_norm=True, qk_norm_full=True, post_norm=True,
+                           max_position_embeddings=4096),
+    # OLMo-3: three sliding-window layers (4096 tokens) per full-attention layer, YaRN-extended context
+    "olmo3-7b": ModelSpec(vocab_size=100278, hidden_size=4096, intermediate_size=11008, num_layers=32, num_heads=32, num_kv_heads=32,
+                          head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo3", qk_norm=True, qk_norm_full=True, post_norm=True,
+                          sliding_window=4096, layer_types=tuple("attention" if i % 4 == 3 else "sliding" for i in range(32)),
+                          rope_scaling=dict(OLMO3_YARN), max_position_embeddings=65536),
+    "olmo3-32b": ModelSpec(vocab_size=100278, hidden_size=5120, intermediate_size=27648, num_layers=64, num_heads=40, num_kv_heads=8,
+                           head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo3", qk_norm=True, qk_norm_full=True, post_norm=True,
+                           sliding_window=4096, layer_types=tuple("attention" if i % 4 == 3 else "sliding" for i in range(64)),
+                           rope_scaling=dict(OLMO3_YARN), max_position_embeddings=65536),
+    "olmoe-1b-7b": ModelSpec(vocab_size=50304, hidden_size=2048, intermediate_size=1024, num_layers=16, num_heads=16, num_kv_heads=16,
+                             head_dim=128, rms_norm_eps=1e-5, rope_theta=1e4, model_type="olmoe", qk_norm=True, qk_norm_full=True,
+                             num_experts=64, num_experts_per_tok=8, norm_topk_prob=False, max_position_embeddings=4096),
+    "qwen3-8b": ModelSpec(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_layers=36, num_heads=32, num_kv_heads=8,
+                          head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True, model_type="qwen3", max_position_embeddings=40960),
+    "qwen3-32b": ModelSpec(vocab_size=151936, hidden_size=5120, intermediate_size=25600, num_layers=64, num_heads=64, num_kv_heads=8,
+                           head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True, model_type="qwen3", max_position_embeddings=40960),
+    "mistral-7b-v0.3": ModelSpec(vocab_size=32768, hidden_size=4096, intermediate_size=14336, num_layers=32, num_heads=32, num_kv_heads=8,
+                                 head_dim=128, rms_norm_eps=1e-5, rope_theta=1e6, model_type="mistral", max_position_embeddings=32768),
+    "llama3.2-3b": ModelSpec(vocab_size=128256, hidden_size=3072, intermediate_size=8192, num_layers=28, num_heads=24, num_kv_heads=8,
+                             head_dim=128, rope_scaling=dict(LLAMA31_SCALING, factor=32.0), tie_word_embeddings=True),
     # allenai/Olmo-Hybrid-7B: 24 gated-DeltaNet layers and 8 full-attention layers (every fourth), ``open_instruct/olmo_core_hybrid.py:154-175``
     "olmo-hybrid-7b": ModelSpec(vocab_size=100352, hidden_size=3840, intermediate_size=11008, num_layers=32, num_heads=30, num_kv_heads=30,
                                 head_dim=128, rms_norm_eps=1e-6, model_type="olmo_hybrid", qk_norm=True, qk_norm_full=True, post_norm=True,

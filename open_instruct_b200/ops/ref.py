@@ -41,7 +41,37 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None, devi
         inv = torch.where(is_mid, mid, scaled)
     elif scaling and scaling.get("rope_type", scaling.get("type")) == "linear":
         inv = inv / scaling["factor"]
+    elif scaling and scaling.get("rope_type", scaling.get("type")) == "yarn":
+        # YaRN: dimensions that turn often within the original context keep their frequency (extrapolation), slow ones are
+        # divided by ``factor`` (interpolation), with a linear ramp between the dimensions that make ``beta_fast`` and
+        # ``beta_slow`` turns over the original context.  The accompanying attention factor is ``rope_attention_factor``.
+        factor, old = scaling["factor"], scaling["original_max_position_embeddings"]
+        fast, slow = scaling.get("beta_fast") or 32, scaling.get("beta_slow") or 1
+        dim_of = lambda turns: head_dim * math.log(old / (turns * 2 * math.pi)) / (2 * math.log(theta))
+        low, high = dim_of(fast), dim_of(slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, head_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float64, device=device) - low) / (high - low)).clamp(0, 1)
+        inv = (inv / factor) * ramp + inv * (1 - ramp)
+    elif scaling and scaling.get("rope_type", scaling.get("type")) not in (None, "default"):
+        raise NotImplementedError(f"RoPE scaling rule {scaling.get('rope_type', scaling.get('type'))!r} is not built (built: llama3, linear, yarn)")
     return inv.float()
+
+
+def rope_attention_factor(scaling: dict | None) -> float:
+    """The factor YaRN multiplies cos and sin with (``attention_factor``, else ``0.1 * ln(factor) + 1``, with the ``mscale``
+    pair when both are given); 1 for every other rule.  q and k both carry it, so attention logits carry its square."""
+    if not scaling or scaling.get("rope_type", scaling.get("type")) != "yarn":
+        return 1.0
+    if scaling.get("attention_factor") is not None:
+        return float(scaling["attention_factor"])
+    ms = lambda f, m=1.0: 1.0 if f <= 1 else 0.1 * m * math.log(f) + 1.0
+    if scaling.get("mscale") and scaling.get("mscale_all_dim"):
+        return ms(scaling["factor"], scaling["mscale"]) / ms(scaling["factor"], scaling["mscale_all_dim"])
+    return ms(scaling["factor"])
 
 
 def rope(qkv: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, n_q: int, n_kv: int, head_dim: int) -> torch.Tensor:

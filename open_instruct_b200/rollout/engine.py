@@ -582,7 +582,7 @@ class RolloutEngine:
             b = cu.tolist()
             self._gdn_runs = [(b[j], b[j + 1], None, [m.sid for m in members[j]]) for j in range(len(reps))]
         slots = torch.tensor([x for r in slot_rows for x in r], dtype=torch.long, device=dev)
-        scale = s.head_dim ** -0.5
+        scale = s.attn_scale
         if self.ops == "fused":
             from ..ops import fused as f
 
@@ -628,7 +628,7 @@ class RolloutEngine:
         from ..ops.lib import call, ptr, stream_ptr
 
         s, dev = self.spec, self.device
-        scale = s.head_dim ** -0.5
+        scale = s.attn_scale
         part_o = torch.empty(B * s.num_heads * splits * s.head_dim, dtype=torch.float32, device=dev) if splits > 1 else None
         part_ml = torch.empty(B * s.num_heads * splits * 2, dtype=torch.float32, device=dev) if splits > 1 else None
 
@@ -787,7 +787,7 @@ class RolloutEngine:
         slots = torch.tensor([tables[i][(n - 1) // KV_BLOCK] * KV_BLOCK + (n - 1) % KV_BLOCK for i, n in enumerate(ctx_list)],
                              dtype=torch.long, device=dev)
         ctx = torch.tensor(ctx_list, dtype=torch.int32, device=dev)
-        scale = s.head_dim ** -0.5
+        scale = s.attn_scale
         if True:
             g = s.num_heads // s.num_kv_heads
 

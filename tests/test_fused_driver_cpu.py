@@ -14,6 +14,7 @@ VARIANTS = {
     "llama-checkpointing": ({}, dict(ckpt=True)),
     "llama-chunked-head-recompute": ({}, dict(chunk=128, keep_cheap=False, temperature=0.7)),
     "qwen2-bias": (dict(attention_bias=True), {}),
+    "llama-yarn": (dict(rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32}), {}),
     "qwen3-head-norm": (dict(qk_norm=True), {}),
     "tied-embeddings": (dict(tie_word_embeddings=True), {}),
     "olmo2": (OLMO2, {}),

@@ -16,6 +16,9 @@ FAMILIES = {
     "llama": ("Llama", dict(rope_theta=500000.0)),
     "llama3.1-rope-scaling": ("Llama", dict(rope_theta=500000.0, rope_scaling=LLAMA3_SCALING)),
     "llama-tied": ("Llama", dict(tie_word_embeddings=True)),
+    "llama-yarn": ("Llama", dict(rope_theta=10000.0, rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32})),
+    "olmo3-yarn-with-attention-factor": ("Olmo3", dict(sliding_window=16, num_hidden_layers=4, rope_scaling={
+        "rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 32, "attention_factor": 1.2079441541679836, "beta_fast": 32, "beta_slow": 1})),
     "qwen2": ("Qwen2", {}),
     "qwen3": ("Qwen3", dict(head_dim=32)),
     "mistral": ("Mistral", dict(sliding_window=None)),
@@ -72,7 +75,7 @@ def test_checkpoint_import_gives_hf_logits(family):
 
 
 @pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2", "olmoe", "olmo-hybrid", "olmo-hybrid-no-rope", "olmo3-window-shorter-than-the-text",
-                                    "mistral-window-shorter-than-the-text"])
+                                    "mistral-window-shorter-than-the-text", "llama-yarn"])
 def test_checkpoint_export_is_read_by_hf(family):
     from open_instruct_b200.ckpt.hf_io import save_hf_checkpoint
     from open_instruct_b200.models import LlamaModel
@@ -93,7 +96,7 @@ def test_checkpoint_export_is_read_by_hf(family):
     assert (got - _our_logits(ours, ids)).abs().max().item() < 1e-5
 
 
-@pytest.mark.parametrize("family", ["olmo2", "olmo3-window-shorter-than-the-text", "olmo-hybrid", "olmo-hybrid-no-rope", "olmo-hybrid-grouped-key-heads"])
+@pytest.mark.parametrize("family", ["olmo2", "olmo3-window-shorter-than-the-text", "olmo3-yarn-with-attention-factor", "olmo-hybrid", "olmo-hybrid-no-rope", "olmo-hybrid-grouped-key-heads"])
 def test_engine_generates_with_a_post_norm_model(family):
     """The rollout engine's PyTorch path follows the block structure (the sliding-window layers, with a prompt longer than the
     window; the gated-DeltaNet layers, whose recurrent state it keeps per sequence) too: greedy tokens equal argmax decoding
