@@ -549,7 +549,7 @@ class LlamaModel:
             raise NotImplementedError("tensor and sequence parallelism are not built for mixture-of-experts layers")
         E, F, D, k = s.num_experts, s.intermediate_size, s.hidden_size, s.num_experts_per_tok
         T = n2.shape[0]
-        logits = f.gemm(n2, p[f"l{i}.router"])
+        logits = n2 @ p[f"l{i}.router"].t()   # [T, E]: small, and E need not suit the GEMM kernel's tile and stride rules
         with torch.enable_grad():   # [T, E]-sized: softmax, top-k and renormalisation are left to autograd
             lg = logits.detach().float().requires_grad_(True)
             probs = torch.softmax(lg, dim=-1)
@@ -623,8 +623,8 @@ class LlamaModel:
                 objective = objective + self.aux_loss_coef * (m.probs * aux_dprobs).sum()
             (d_lg,) = torch.autograd.grad(objective, m.lg)
         d_logits = d_lg.to(n2.dtype)
-        f.gemm(d_logits, n2, g[f"l{i}.router"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
-        d_n2 += f.gemm(d_logits, p[f"l{i}.router"], b_mn=True).float()
+        g[f"l{i}.router"].add_((d_logits.t() @ n2).float())
+        d_n2 += (d_logits @ p[f"l{i}.router"]).float()
         return d_n2.to(n2.dtype)
 
     def _attention_block(self, i: int, n1, pos, cu):

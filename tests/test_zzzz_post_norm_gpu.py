@@ -75,7 +75,7 @@ def test_fused_mixture_of_experts_matches_ref():
     from open_instruct_b200.models import LlamaModel, get_spec
     from open_instruct_b200.ops import lib
 
-    spec = get_spec("tiny128").replace(qk_norm=True, qk_norm_full=True, num_experts=4, num_experts_per_tok=2, intermediate_size=256,
+    spec = get_spec("tiny128").replace(qk_norm=True, qk_norm_full=True, num_experts=8, num_experts_per_tok=2, intermediate_size=256,
                                        model_type="olmoe")
     fused = LlamaModel(spec, device="cuda", dtype=torch.bfloat16, ops="fused", seed=3)
     refm = LlamaModel(spec, device="cuda", dtype=torch.float32, ops="ref", flat=fused.flat.float().clone())
