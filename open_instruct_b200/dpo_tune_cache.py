@@ -265,7 +265,10 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
     return last
 
 
+def cli() -> None:
+    """Command line: a YAML / JSON recipe and / or ``--key value`` flags."""
+    main(*ArgumentParserPlus((DPOExperimentConfig, TokenizerConfig)).parse())
+
+
 if __name__ == "__main__":
-    parser = ArgumentParserPlus((DPOExperimentConfig, TokenizerConfig))
-    _args, _tc = parser.parse()
-    main(_args, _tc)
+    cli()

@@ -349,7 +349,10 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
     return final_metrics
 
 
+def cli() -> None:
+    """Command line: a YAML / JSON recipe and / or ``--key value`` flags."""
+    main(*ArgumentParserPlus((FlatArguments, TokenizerConfig)).parse())
+
+
 if __name__ == "__main__":
-    parser = ArgumentParserPlus((FlatArguments, TokenizerConfig))
-    _args, _tc = parser.parse()
-    main(_args, _tc)
+    cli()

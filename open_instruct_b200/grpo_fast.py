@@ -1304,9 +1304,14 @@ def _main(args, tc, model_config, streaming, vllm, tools_config=None) -> dict:
     return run.run()
 
 
-if __name__ == "__main__":
+def cli() -> None:
+    """Command line: a YAML / JSON recipe and / or ``--key value`` flags."""
     from .environments.tools.utils import EnvsConfig
 
     parser = ArgumentParserPlus((GRPOExperimentConfig, TokenizerConfig, ModelConfig, StreamingDataLoaderConfig, VLLMConfig, EnvsConfig))
     parser.set_defaults(exp_name="grpo", warmup_ratio=0.0, max_grad_norm=1.0, per_device_train_batch_size=1)
     main(*parser.parse())
+
+
+if __name__ == "__main__":
+    cli()

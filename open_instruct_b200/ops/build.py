@@ -117,5 +117,44 @@ def build_all(force: bool = False, verbose: bool = True) -> None:
     build_host(force, verbose)
 
 
-if __name__ == "__main__":
+def ptxas_digest() -> str:
+    """Markdown table of registers, stack and spills per kernel, from the ``*.ptxas.txt`` files the last build left beside the
+    objects (``ptxas -v`` output, one file per source)."""
+    import re
+
+    rows, mangled = [], set()
+    pat = re.compile(r"Function properties for (\S+)\n\s+(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads\n"
+                     r"ptxas info\s+: Used (\d+) registers")
+    for path in sorted(OBJ.glob("*.ptxas.txt")):
+        for m in pat.finditer(path.read_text()):
+            rows.append((path.name.replace(".ptxas.txt", ".cu"), m.group(1), *map(int, m.groups()[1:])))
+            mangled.add(m.group(1))
+    names = sorted(mangled)
+    plain = subprocess.run(["c++filt"], input="\n".join(names), capture_output=True, text=True).stdout.split("\n") if shutil.which("c++filt") else names
+    short = {n: re.sub(r"\(.*$", "", d).replace("void ", "").replace("b200::", "") for n, d in zip(names, plain)}
+    out = ["# Registers, stack and spills of every kernel (`nvcc " + " ".join(NVCC_FLAGS[:5]) + " -Xptxas -v`)", "",
+           "Made by `python -m open_instruct_b200.ops.build --force && python -m open_instruct_b200.ops.build --ptxas-digest > profiles/ptxas_registers.md`.",
+           "Kernel entry points only, template arguments kept.  A kernel with a non-zero spill column reads and writes local memory.", "",
+           "| source | kernel | registers | stack B | spill stores B | spill loads B |", "|---|---|---|---|---|---|"]
+    seen, spilled = set(), set()
+    for src, name, stack, sst, sld, regs in rows:
+        key = (src, short[name])
+        if key in seen:
+            continue
+        seen.add(key)
+        out.append(f"| `{src}` | `{short[name]}` | {regs} | {stack} | {sst} | {sld} |")
+        if sst or sld:
+            spilled.add(f"`{short[name]}` ({sst} / {sld} B)")
+    out += ["", f"{len(seen)} kernels; {len(spilled)} with spills" + (": " + ", ".join(sorted(spilled)) if spilled else "") + "."]
+    return "\n".join(out) + "\n"
+
+
+def main() -> None:
+    if "--ptxas-digest" in sys.argv:
+        sys.stdout.write(ptxas_digest())
+        return
     build_all(force="--force" in sys.argv)
+
+
+if __name__ == "__main__":
+    main()

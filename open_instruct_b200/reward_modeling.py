@@ -294,6 +294,10 @@ def main(args: Args, tc: TokenizerConfig, model_config: ModelConfig) -> dict:
     return last
 
 
+def cli() -> None:
+    """Command line: a YAML / JSON recipe and / or ``--key value`` flags."""
+    main(*ArgumentParserPlus((Args, TokenizerConfig, ModelConfig)).parse())
+
+
 if __name__ == "__main__":
-    parser = ArgumentParserPlus((Args, TokenizerConfig, ModelConfig))
-    main(*parser.parse())
+    cli()
