@@ -1051,7 +1051,10 @@ class GRPORun:
             # On GPUs the engines start with random weights and receive the learners' through the first weight sync (the same
             # push kernel as every later one) instead of a by-value copy of the whole model handed to every engine process
             # (16 GB at 8B: gathered to the driver, shared with every engine rank, copied to each GPU and re-sharded there).
-            init_by_push = (cuda and os.environ.get("B200_GRPO_INIT_BY_PUSH", "1") == "1") or os.environ.get("B200_GRPO_INIT_BY_PUSH") == "force"
+            # "auto": for models from a billion parameters up, where the by-value copies cost minutes and tens of GB of host memory
+            mode = os.environ.get("B200_GRPO_INIT_BY_PUSH", "auto")
+            big = ParamLayoutTotal(spec) >= 1_000_000_000
+            init_by_push = (cuda and (mode == "1" or (mode == "auto" and big))) or mode == "force"
             init_flat = None if init_by_push else ray.get(learners[0].flat_weights_cpu.remote())
             tp = vllm.vllm_tensor_parallel_size
             followers = []
