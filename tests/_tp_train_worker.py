@@ -44,7 +44,10 @@ def main():
                     v.add_(0.2 * torch.randn(v.shape, generator=torch.Generator().manual_seed(1)))
             oracle.opt.master.copy_(oracle.model.flat.detach()[oracle.opt.lo:oracle.opt.hi])
     total = ParamLayout(spec).total
-    sharded = Learner(spec, LearnerConfig(**kw, tensor_parallel_degree=tp), device=device, flat_init=oracle.model.flat.detach()[:total].clone())
+    # OPS=emulated: the fused path's hand-driven forward / backward (its all-reduces after the row-parallel projections and
+    # before the column-parallel ones' input gradients, the vocabulary-parallel head) over PyTorch restatements of the kernels
+    kw_sharded = {**kw, "ops": os.environ.get("OPS", "ref")}
+    sharded = Learner(spec, LearnerConfig(**kw_sharded, tensor_parallel_degree=tp), device=device, flat_init=oracle.model.flat.detach()[:total].clone())
     assert sharded.tp is not None and sharded.world == dp_world and sharded.rank == dp_rank
     assert sharded.spec.num_heads == spec.num_heads // tp and sharded.full_spec.num_heads == spec.num_heads
     assert torch.equal(sharded.full_flat(), oracle.model.flat.detach()[:total])   # shard -> unshard round trip

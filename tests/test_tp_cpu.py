@@ -199,7 +199,7 @@ def test_model_dims_utilisation_stays_physical():
     assert b.device_flops > dims.device_flops and b.device_memory_bandwidth > dims.device_memory_bandwidth
 
 
-def _run_tp_train(world, family, port):
+def _run_tp_train(world, family, port, ops="ref"):
     import os
     import subprocess
     import sys
@@ -207,7 +207,7 @@ def _run_tp_train(world, family, port):
     here = os.path.dirname(os.path.abspath(__file__))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(here, "_tp_train_worker.py")]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "FAMILY": family})
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "FAMILY": family, "OPS": ops})
     assert res.returncode == 0 and res.stdout.count("TP_TRAIN_OK") == world, res.stdout[-3000:] + res.stderr[-3000:]
 
 
@@ -217,6 +217,12 @@ def test_training_tensor_parallel_matches_unsharded():
 
 def test_training_tensor_parallel_with_data_parallel_and_qk_norm():
     _run_tp_train(4, "qwen3", free_port())
+
+
+def test_training_tensor_parallel_through_the_hand_driven_path():
+    """The same trajectory check with the fused path's driver (kernels restated in PyTorch): its tensor-parallel branches and
+    the vocabulary-parallel output head."""
+    _run_tp_train(4, "qwen3", free_port(), ops="emulated")
 
 
 def test_tp_push_plan_reproduces_shard_flat():
