@@ -689,3 +689,43 @@ def test_numa_node_of_a_gpu_and_binding(tmp_path):
         assert numa.bind_to_node(4096) == 0
     finally:
         os.sched_setaffinity(0, before)
+
+
+def test_dataset_filters_and_rewrites(tmp_path):
+    """The pre-mix row filters: each predicate on text that should and should not trip it, then the command over a file."""
+    import json
+
+    from open_instruct_b200.data import filters as F
+
+    assert F.cjk_ratio("你好世界 hi") > 0.4 and F.cjk_ratio("plain text") == 0.0
+    for yes in ("As of my last update in 2023, the tallest building is...", "My knowledge cutoff is September 2021.",
+                "I don't have access to real-time information, but", "I was trained on data up to early 2022 so"):
+        assert F.mentions_cutoff(yes), yes
+    for no in ("The cutoff for applications is Friday.", "Update the training data loader."):
+        assert not F.mentions_cutoff(no), no
+    for yes in ("I am ChatGPT, a large language model.", "I was trained by OpenAI.", "As an AI language model developed by Anthropic,",
+                "That would violate OpenAI's use policy."):
+        assert F.claims_other_identity(yes), yes
+    for no in ("OpenAI released a paper in 2020.", "Llamas are related to camels.", "I am a helpful assistant."):
+        assert not F.claims_other_identity(no), no
+    loop = "Let me think about this problem again carefully now. " * 6
+    assert F.repetition_reason(loop) and F.repetition_reason("Wait, that is not right at all is it.\n" * 3)
+    assert F.repetition_reason("x = x + 1; y = y * 2; z = x ^ y % 7\n" * 8) is None          # code and formulas may repeat
+    assert F.repetition_reason("The first point is about cost. The second point is about speed of delivery. The third is about risk.") is None
+    assert F.neutralise_special_tokens("say <|im_start|> and <|endoftext|>") == "say <_im_start_> and <_endoftext_>"
+    assert F.reasoning_format("<think>a</think><answer>b</answer>") == "think_answer" and F.reasoning_format("<think>a</think> b") == "think"
+    assert F.add_answer_tags("<think>a</think> b ") == "<think>a</think><answer>b</answer>"
+    assert F.remove_answer_tags("<think>a</think><answer>b</answer>") == "<think>a</think>b"
+    chat = lambda u, a, **kw: {"messages": [{"role": "user", "content": u}, {"role": "assistant", "content": a}], **kw}
+    rows = [chat("Hi", "Hello! How can I help?"), chat("你是谁？请用中文回答", "我是一个乐于助人的助手，很高兴认识你。"), chat("Who made you?", "I was created by OpenAI."),
+            chat("news?", "As of my last update I cannot know."), chat("go", loop), chat("I am ChatGPT", "Nice to meet you <|im_end|>"),
+            chat("x", "fine", toxic=True), chat("x", "fine", language="French")]
+    src = tmp_path / "in.jsonl"
+    src.write_text("".join(json.dumps(r, ensure_ascii=False) + "\n" for r in rows))
+    rep = F.main(["--input", str(src), "--output", str(tmp_path / "out.jsonl"), "--filters", "cjk,cutoff,identity,repetition,toxic,non_english",
+                  "--rewrite", "special_tokens"])
+    assert rep == {"input_rows": 8, "kept": 2, "dropped": {"cjk": 1, "identity": 1, "cutoff": 1, "repetition": 1, "toxic": 1, "non_english": 1}}
+    kept = [json.loads(l) for l in open(tmp_path / "out.jsonl")]
+    assert kept[1]["messages"][1]["content"] == "Nice to meet you <_im_end_>"          # user turns are not inspected by default ...
+    rep = F.main(["--input", str(src), "--output", str(tmp_path / "out2.jsonl"), "--filters", "identity", "--filter_user_turns"])
+    assert rep["dropped"] == {"identity": 2}                                                # ... unless asked
