@@ -9,10 +9,14 @@
 * ``token_length_histogram``: bucketed token-length distribution of a column (``scripts/data/get_token_distribution.py``
   plots it; here the buckets are returned and optionally written as JSON).
 
+* ``fill_identity_placeholders``: "who are you" seed conversations with ``<|MODEL_NAME|>``-style placeholders -> rows for one
+  model (``scripts/data/build_hardcoded.py``), optionally only the rows tagged for a model family.
+
 Everything works on lists of dicts or JSONL files: no hub access is needed.
 
     python -m open_instruct_b200.data.builders stats --data train.jsonl --tokenizer /path/to/tokenizer
     python -m open_instruct_b200.data.builders env --kind counter --num 100 --out counter.jsonl
+    python -m open_instruct_b200.data.builders identity --data seed.jsonl --out hardcoded.jsonl --model_name "OLMo 2" --license "Apache 2.0"
 """
 
 from __future__ import annotations
@@ -142,6 +146,36 @@ def token_length_histogram(rows: list[dict], tokenizer, column: str = "messages"
             "over_max": int((a > top).sum()) if a.size else 0}
 
 
+IDENTITY_PLACEHOLDERS = {"model_name": "<|MODEL_NAME|>", "posttrain_recipe": "<|POSTTRAIN_RECIPE|>", "context_length": "<|CONTEXT_LENGTH|>",
+                         "base_model": "<|BASE_MODEL|>", "date_cutoff": "<|DATE_CUTOFF|>", "license": "<|LICENSE|>",
+                         "weights_link": "<|WEIGHTS_LINK|>"}
+
+
+def fill_identity_placeholders(rows: list[dict], values: dict, filter_tags: list[str] | None = None, messages_key: str = "messages") -> list[dict]:
+    """Seed conversations about the model itself, with placeholders such as ``<|MODEL_NAME|>`` in any turn, made concrete for one
+    model.  ``values`` maps the names in ``IDENTITY_PLACEHOLDERS`` (or raw placeholder strings) to text; ``filter_tags`` drops
+    rows whose ``tags`` list shares an entry with it (rows written for another family).  A row that still holds a known
+    placeholder afterwards is an error: better no identity data than one that says ``<|MODEL_NAME|>``."""
+    table = {IDENTITY_PLACEHOLDERS.get(k, k): str(v) for k, v in values.items() if v is not None}
+    out = []
+    for row in rows:
+        if filter_tags and set(filter_tags) & set(row.get("tags") or []):
+            continue
+        new = dict(row)
+        msgs = []
+        for m in row[messages_key]:
+            text = m["content"]
+            for ph, val in table.items():
+                text = text.replace(ph, val)
+            left = [ph for ph in IDENTITY_PLACEHOLDERS.values() if ph in text]
+            if left:
+                raise ValueError(f"no value given for {left} (row: {text[:80]!r})")
+            msgs.append({**m, "content": text})
+        new[messages_key] = msgs
+        out.append(new)
+    return out
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -158,8 +192,16 @@ def main(argv=None) -> None:
     g.add_argument("--data", required=True)
     g.add_argument("--out", required=True)
     g.add_argument("--rlvr", action="store_true")
+    h = sub.add_parser("identity")
+    h.add_argument("--data", required=True, help="seed conversations (.jsonl) with placeholders")
+    h.add_argument("--out", required=True)
+    h.add_argument("--filter_tags", nargs="*", default=None)
+    for name in IDENTITY_PLACEHOLDERS:
+        h.add_argument(f"--{name}", default=None)
     args = ap.parse_args(argv)
-    if args.cmd == "env":
+    if args.cmd == "identity":
+        write_jsonl(fill_identity_placeholders(read_jsonl(args.data), {k: getattr(args, k) for k in IDENTITY_PLACEHOLDERS}, args.filter_tags), args.out)
+    elif args.cmd == "env":
         write_jsonl((counter_env_samples if args.kind == "counter" else guess_number_env_samples)(args.num, args.nothink), args.out)
     elif args.cmd == "gsm8k":
         rows = read_jsonl(args.data)

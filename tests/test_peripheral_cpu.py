@@ -729,3 +729,22 @@ def test_dataset_filters_and_rewrites(tmp_path):
     assert kept[1]["messages"][1]["content"] == "Nice to meet you <_im_end_>"          # user turns are not inspected by default ...
     rep = F.main(["--input", str(src), "--output", str(tmp_path / "out2.jsonl"), "--filters", "identity", "--filter_user_turns"])
     assert rep["dropped"] == {"identity": 2}                                                # ... unless asked
+
+
+def test_identity_seed_conversations_are_filled_for_one_model(tmp_path):
+    import json
+
+    from open_instruct_b200.data import builders as B
+
+    seed = [{"messages": [{"role": "user", "content": "Who are you?"}, {"role": "assistant", "content": "I am <|MODEL_NAME|>, trained with the <|POSTTRAIN_RECIPE|> recipe."}], "tags": []},
+            {"messages": [{"role": "user", "content": "license?"}, {"role": "assistant", "content": "<|LICENSE|>, context <|CONTEXT_LENGTH|>."}], "tags": ["olmo"]}]
+    p = tmp_path / "seed.jsonl"
+    p.write_text("".join(json.dumps(r) + "\n" for r in seed))
+    B.main(["identity", "--data", str(p), "--out", str(tmp_path / "o.jsonl"), "--model_name", "Tulu 3", "--posttrain_recipe", "Tulu 3",
+            "--filter_tags", "olmo"])
+    rows = [json.loads(l) for l in open(tmp_path / "o.jsonl")]
+    assert len(rows) == 1 and rows[0]["messages"][1]["content"] == "I am Tulu 3, trained with the Tulu 3 recipe."
+    with pytest.raises(ValueError, match="LICENSE"):
+        B.fill_identity_placeholders(seed, {"model_name": "X", "posttrain_recipe": "Y"})
+    full = B.fill_identity_placeholders(seed, {"model_name": "X", "posttrain_recipe": "Y", "license": "Apache 2.0", "context_length": 4096})
+    assert full[1]["messages"][1]["content"] == "Apache 2.0, context 4096."
