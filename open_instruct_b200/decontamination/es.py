@@ -8,6 +8,10 @@ that equations and code survive), count its documents, bulk-add ``{"text", "orig
 ``open_instruct_b200.decontamination.search --es_url`` queries it; without a server the in-process ``NgramIndex`` does
 the same work for sets that fit in memory.
 
+Embedding search (``index_type vector``): documents carry an L2-normalised ``vector`` (``dense_vector``, dot-product
+similarity) made by ``Embedder`` - any Hugging Face encoder or decoder loaded from a local folder, mean-pooled over the tokens
+(the reference hard-wires one 4096-wide embedding model and its own ``encode`` method) - and queries use the server's kNN search.
+
 ``tokenize`` restates the analyzer on the client: the n-grams sent as phrases and the token-coverage score are computed
 over the same tokens the server matches (the reference tokenises queries with a spaCy model, which this image has not).
 """
@@ -70,6 +74,19 @@ class ElasticClient:
             "mappings": {"properties": {"text": {"type": "text", "index": True, "analyzer": "tulu_analyzer"},
                                         "original_id": {"type": "integer"}}}})
 
+    def create_vector_index(self, name: str, dims: int) -> None:
+        self._request("PUT", f"/{name}", {"mappings": {"properties": {
+            "text": {"type": "text"}, "original_id": {"type": "integer"},
+            "vector": {"type": "dense_vector", "dims": dims, "index": True, "similarity": "dot_product"}}}})
+
+    def knn(self, name: str, vector: list[float], k: int = 10) -> list[dict]:
+        """The ``k`` documents whose vectors are closest to ``vector``: [{"_id", "_score", "_source"}], best first."""
+        out = self._request("POST", f"/{name}/_search", {"knn": {"field": "vector", "query_vector": vector, "k": k, "num_candidates": 10 * k},
+                                                          "_source": ["text", "original_id"]})
+        if out is None:
+            raise RuntimeError(f"Elasticsearch index {name} does not exist: build it with open_instruct_b200.decontamination.index")
+        return list(out["hits"]["hits"])
+
     def count(self, name: str) -> int:
         out = self._request("GET", f"/{name}/_count")
         return int(out["count"]) if out else 0
@@ -77,7 +94,10 @@ class ElasticClient:
     def bulk_add(self, name: str, docs: list[dict]) -> None:
         lines = []
         for d in docs:
-            lines += [{"index": {"_index": name}}, {"text": d["text"], "original_id": d["original_id"]}]
+            src = {"text": d["text"], "original_id": d["original_id"]}
+            if "vector" in d:
+                src["vector"] = d["vector"]
+            lines += [{"index": {"_index": name}}, src]
         out = self._request("POST", "/_bulk?refresh=true", lines, ndjson=True)
         if out and out.get("errors"):
             raise RuntimeError(f"Elasticsearch bulk request into {name} reported errors")
@@ -155,4 +175,79 @@ def ngram_match(es: ElasticClient, name: str, queries: list[list[str]], ngram_si
             train_best[oid] = max(train_best.get(oid, 0.0), sc)
         scores.append(ranked[0][1])
         report.append({"query": fields, "score": ranked[0][1], "matches": [{"doc_id": d, "source": sources[d], "score": sc} for d, sc in ranked]})
+    return scores, report, train_best
+
+
+class Embedder:
+    """Sentence vectors from a local Hugging Face model: mean of the last hidden states over the real tokens, L2-normalised.
+    Texts are batched by a token budget (``max_batch_tokens`` = longest text of the batch x batch size); a single text longer
+    than the budget is skipped (None in the result), as the reference does."""
+
+    def __init__(self, model_name_or_path: str, max_batch_tokens: int = 10000, device: str | None = None, prefix: str = ""):
+        import torch
+        from transformers import AutoModel, AutoTokenizer
+
+        self.torch = torch
+        self.tok = AutoTokenizer.from_pretrained(model_name_or_path)
+        if self.tok.pad_token is None:
+            self.tok.pad_token = self.tok.eos_token or self.tok.unk_token
+        self.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        self.model = AutoModel.from_pretrained(model_name_or_path).eval().to(self.device)
+        self.dims = int(self.model.config.hidden_size)
+        self.max_batch_tokens, self.prefix = max_batch_tokens, prefix
+
+    def __call__(self, texts: list[str]) -> list[list[float] | None]:
+        torch = self.torch
+        lens = [len(self.tok.tokenize(self.prefix + t)) for t in texts]
+        out: list = [None] * len(texts)
+        i = 0
+        while i < len(texts):
+            if lens[i] > self.max_batch_tokens:
+                i += 1
+                continue
+            j, longest = i, 0
+            while j < len(texts) and lens[j] <= self.max_batch_tokens and max(longest, lens[j]) * (j - i + 1) <= self.max_batch_tokens:
+                longest = max(longest, lens[j])
+                j += 1
+            enc = self.tok([self.prefix + t for t in texts[i:j]], return_tensors="pt", padding=True).to(self.device)
+            with torch.no_grad():
+                h = self.model(**enc).last_hidden_state.float()
+            mask = enc["attention_mask"].unsqueeze(-1).float()
+            v = torch.nn.functional.normalize((h * mask).sum(1) / mask.sum(1).clamp(min=1), dim=1)
+            for k, row in enumerate(v.cpu().tolist()):
+                out[i + k] = row
+            i = j
+        return out
+
+
+def index_vectors(es: ElasticClient, name: str, docs: list[dict], embed: Embedder, batch_size: int = 256) -> int:
+    """Like ``index_text`` with a ``vector`` per document; documents too long to embed are left out."""
+    if not es.index_exists(name):
+        es.create_vector_index(name, embed.dims)
+    start, added = es.count(name), 0
+    for i in range(start, len(docs), batch_size):
+        chunk = docs[i:i + batch_size]
+        vecs = embed([d["text"] for d in chunk])
+        ready = [{**d, "vector": v} for d, v in zip(chunk, vecs) if v is not None]
+        if ready:
+            es.bulk_add(name, ready)
+        added += len(ready)
+    return added
+
+
+def vector_match(es: ElasticClient, name: str, queries: list[list[str]], embed: Embedder, size: int = 10):
+    """Per evaluation example (its fields joined by a blank): similarity of the closest training document.  Returns (scores,
+    report rows with the five best documents, {training row id: highest score against any example})."""
+    texts = [" ".join(f for f in fields if f is not None) for fields in queries]
+    scores, report, train_best = [], [], {}
+    for text, vec in zip(texts, embed(texts)):
+        if vec is None:
+            continue
+        hits = es.knn(name, vec, size)[:5]
+        scores.append(hits[0]["_score"] if hits else 0.0)
+        for h in hits:
+            oid = h["_source"]["original_id"]
+            train_best[oid] = max(train_best.get(oid, 0.0), h["_score"])
+        report.append({"query": text, "results": [{"score": h["_score"], "id": h["_id"], "text": h["_source"]["text"],
+                                                   "original_id": h["_source"]["original_id"]} for h in hits]})
     return scores, report, train_best

@@ -6,14 +6,15 @@ reference): one document per message that passes ``--query_filter``, carrying th
 
 ``--dataset`` is a local ``.jsonl`` / ``.json`` / ``.parquet`` file or a dataset name the data layer can load;
 ``--dataset_mixer_config`` indexes every dataset a training recipe mixes (its ``dataset_mixer`` mapping or
-``dataset_mixer_list``).  Embedding (vector) indexes need the reference's 4096-wide embedding model and are not built.
+``dataset_mixer_list``).  ``--index_type vector`` stores an embedding per message made by ``--model`` (a local Hugging Face
+model folder, mean-pooled; the reference's default embedding model is not in this image).
 """
 
 from __future__ import annotations
 
 import argparse
 
-from .es import ElasticClient, index_name_for, index_text, messages_to_index
+from .es import ElasticClient, Embedder, index_name_for, index_text, index_vectors, messages_to_index
 
 
 def _rows(dataset: str, split: str) -> list[dict]:
@@ -44,9 +45,12 @@ def main(argv=None) -> dict:
     ap.add_argument("--query_field", default="content")
     ap.add_argument("--index_type", choices=["text", "vector"], default="text")
     ap.add_argument("--text_batch_size", type=int, default=1000)
+    ap.add_argument("--model", default=None, help="vector indexes: folder of the Hugging Face model that embeds the messages")
+    ap.add_argument("--max_batch_tokens", type=int, default=10000)
     a = ap.parse_args(argv)
-    if a.index_type == "vector":
-        raise NotImplementedError("vector indexes (embedding search) are not built: use --index_type text")
+    if a.index_type == "vector" and not a.model:
+        raise SystemExit("--index_type vector needs --model (a local Hugging Face model folder)")
+    embed = Embedder(a.model, a.max_batch_tokens) if a.index_type == "vector" else None
     if a.dataset_mixer_config:
         names = _mixer_datasets(a.dataset_mixer_config)
     elif a.dataset:
@@ -58,7 +62,7 @@ def main(argv=None) -> dict:
     for name in names:
         docs = messages_to_index(_rows(name, a.split), a.messages_field, a.query_filter, a.query_field)
         index = index_name_for(name, a.index_type)
-        added[index] = index_text(es, index, docs, a.text_batch_size)
+        added[index] = index_text(es, index, docs, a.text_batch_size) if embed is None else index_vectors(es, index, docs, embed)
         print(f"{index}: {added[index]} documents added ({len(docs)} messages in {name})")
     return added
 

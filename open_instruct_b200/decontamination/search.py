@@ -105,7 +105,8 @@ def main(argv=None) -> dict:
     ap.add_argument("--train_field", nargs="+", default=["messages"])
     ap.add_argument("--ngram_size", type=int, default=8)
     ap.add_argument("--threshold", type=float, default=0.5)
-    ap.add_argument("--index_type", choices=["exact", "ngram"], default="ngram")
+    ap.add_argument("--index_type", choices=["exact", "ngram", "vector"], default="ngram")
+    ap.add_argument("--model", default=None, help="vector search: folder of the Hugging Face model that embedded the index")
     ap.add_argument("--output_dir", required=True)
     ap.add_argument("--decontaminate", action="store_true")
     ap.add_argument("--es_url", default=None, help="query an Elasticsearch index of --train instead of indexing it in this process")
@@ -114,6 +115,8 @@ def main(argv=None) -> dict:
     load = lambda p: [json.loads(line) for line in open(p) if line.strip()]
     if a.es_url:
         return _main_elasticsearch(a, load(a.eval))
+    if a.index_type == "vector":
+        raise SystemExit("vector search runs against an Elasticsearch index: give --es_url")
     train, ev = load(a.train), load(a.eval)
     rep = find_contamination(train, ev, a.train_field, a.field, a.ngram_size, a.threshold, a.index_type)
     os.makedirs(a.output_dir, exist_ok=True)
@@ -134,7 +137,12 @@ def _main_elasticsearch(a, eval_rows: list[dict]) -> dict:
     client = es_mod.ElasticClient(a.es_url)
     index = es_mod.index_name_for(a.train, "text")
     queries = [[row.get(f) for f in a.field] for row in eval_rows]
-    if a.index_type == "exact":
+    if a.index_type == "vector":
+        if not a.model:
+            raise SystemExit("--index_type vector needs --model")
+        index = es_mod.index_name_for(a.train, "vector")
+        scores, report, train_scores = es_mod.vector_match(client, index, queries, es_mod.Embedder(a.model), a.search_size)
+    elif a.index_type == "exact":
         scores, report, ids = es_mod.exact_match(client, index, queries, a.search_size)
         train_scores = {i: 1.0 for i in ids}
     else:

@@ -117,8 +117,8 @@ class FakeElasticsearch:
             def do_PUT(self):
                 name = urlparse(self.path).path.strip("/")
                 body = json.loads(self._body())
-                pat = body["settings"]["analysis"]["analyzer"]["tulu_analyzer"]["pattern"]
-                store[name] = {"split": re.compile(pat), "docs": []}
+                pat = body.get("settings", {}).get("analysis", {}).get("analyzer", {}).get("tulu_analyzer", {}).get("pattern", r"\s+")
+                store[name] = {"split": re.compile(pat), "docs": [], "dims": body["mappings"]["properties"].get("vector", {}).get("dims")}
                 log.append(("PUT", name))
                 self._reply(200, {"acknowledged": True})
 
@@ -141,6 +141,13 @@ class FakeElasticsearch:
                 if op != "_search" or name not in store:
                     return self._reply(404, {"error": "no such index"})
                 q = json.loads(self._body())
+                if "knn" in q:   # brute-force dot products, best first
+                    qv = q["knn"]["query_vector"]
+                    assert len(qv) == store[name]["dims"]
+                    scored = sorted(((sum(a * b for a, b in zip(qv, d["_source"]["vector"])), d) for d in store[name]["docs"]), key=lambda t: -t[0])
+                    hits = [{"_id": d["_id"], "_score": sc, "_source": {k: v for k, v in d["_source"].items() if k != "vector"}} for sc, d in scored[: q["knn"]["k"]]]
+                    log.append(("KNN", name))
+                    return self._reply(200, {"hits": {"total": {"value": len(hits)}, "hits": hits}})
                 phrases = [analyse(name, f["match_phrase"]["text"]) for f in q["query"]["bool"]["filter"]]
                 hits = []
                 for d in store[name]["docs"]:

@@ -748,3 +748,45 @@ def test_identity_seed_conversations_are_filled_for_one_model(tmp_path):
         B.fill_identity_placeholders(seed, {"model_name": "X", "posttrain_recipe": "Y"})
     full = B.fill_identity_placeholders(seed, {"model_name": "X", "posttrain_recipe": "Y", "license": "Apache 2.0", "context_length": 4096})
     assert full[1]["messages"][1]["content"] == "Apache 2.0, context 4096."
+
+
+def test_decontamination_by_embedding_search(tmp_path):
+    """Vector index: messages embedded by a local model (mean-pooled, normalised), kNN search through (a fake of) Elasticsearch; the
+    leaked question's nearest neighbour is its own training row with similarity 1."""
+    import json
+
+    transformers = pytest.importorskip("transformers")
+    import torch
+
+    from helpers import FakeElasticsearch, make_tokenizer
+    from open_instruct_b200.decontamination import es as es_mod
+    from open_instruct_b200.decontamination import index as index_cli
+    from open_instruct_b200.decontamination import search as search_cli
+
+    tok_dir = make_tokenizer(str(tmp_path / "enc"))
+    tok = transformers.AutoTokenizer.from_pretrained(tok_dir)
+    torch.manual_seed(0)
+    transformers.LlamaModel(transformers.LlamaConfig(vocab_size=len(tok) + 8, hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                                                     num_attention_heads=2, num_key_value_heads=2)).save_pretrained(tok_dir)
+    leaked = "What is the sum of the first ten positive odd integers?"
+    train = [{"messages": [{"role": "user", "content": "Tell me a story about a dragon who bakes bread."}, {"role": "assistant", "content": "Once"}]},
+             {"messages": [{"role": "user", "content": leaked}, {"role": "assistant", "content": "100"}]},
+             {"messages": [{"role": "user", "content": "Summarise Hamlet in two sentences."}, {"role": "assistant", "content": "..."}]}]
+    tp, ep = tmp_path / "train.jsonl", tmp_path / "eval.jsonl"
+    tp.write_text("".join(json.dumps(r) + "\n" for r in train))
+    ep.write_text(json.dumps({"text": leaked}) + "\n")
+    fake = FakeElasticsearch()
+    try:
+        added = index_cli.main(["--es_url", fake.url, "--dataset", str(tp), "--index_type", "vector", "--model", tok_dir])
+        index = es_mod.index_name_for(str(tp), "vector")
+        assert added == {index: 3} and fake.indices[index]["dims"] == 32
+        v = fake.indices[index]["docs"][0]["_source"]["vector"]
+        assert abs(sum(x * x for x in v) - 1.0) < 1e-4
+        rep = search_cli.main(["--es_url", fake.url, "--train", str(tp), "--eval", str(ep), "--field", "text", "--index_type", "vector",
+                               "--model", tok_dir, "--threshold", "0.999", "--output_dir", str(tmp_path / "out")])
+        assert rep["train_contaminated"] == [1] and rep["eval_contaminated"] == 1
+        assert rep["matches"][0]["results"][0]["original_id"] == 1 and abs(rep["matches"][0]["results"][0]["score"] - 1.0) < 1e-4
+        emb = es_mod.Embedder(tok_dir, max_batch_tokens=4)
+        assert emb(["a much longer text than four tokens allow for sure", "hi"])[0] is None     # too long for the budget: skipped
+    finally:
+        fake.close()
