@@ -105,6 +105,35 @@ def gdn_segment(x: torch.Tensor, v: dict, i: int, spec, state=None, chunk: int =
     return o.to(x.dtype).reshape(L, V) @ v[f"l{i}.gdn_out"].t(), (seq[-(taps - 1):].detach(), S.detach())
 
 
+def gdn_decode_step(x: torch.Tensor, v: dict, i: int, spec, tails: torch.Tensor, S: torch.Tensor):
+    """One token for each of B sequences at once: ``x`` [B, D], ``tails`` [B, taps - 1, C] (what last entered each sequence's
+    convolution), ``S`` [B, Hv, dk, dv].  Returns ``(output [B, D], new tails, new S)``; the same arithmetic as
+    ``gdn_segment`` on a run of length one."""
+    s = spec
+    K, V, Hk, Hv, dk, dv = s.gdn_k_total, s.gdn_v_total, s.gdn_key_heads, s.gdn_value_heads, s.gdn_key_dim, s.gdn_value_dim
+    B = x.shape[0]
+    proj = x @ v[f"l{i}.gdn_in"].t()
+    qkv, gate, a, b = proj.split([2 * K + V, V, Hv, Hv], dim=1)
+    w = v[f"l{i}.gdn_conv"]                                               # [C, taps]
+    seq = torch.cat([tails.to(qkv.dtype), qkv[:, None, :]], dim=1)        # [B, taps, C]
+    conv = F.silu(torch.einsum("btc,ct->bc", seq, w))
+    q, k, val = conv.split([K, K, V], dim=1)
+    q = _l2norm(q.float().view(B, Hk, dk)) * dk ** -0.5
+    k = _l2norm(k.float().view(B, Hk, dk))
+    val = val.float().view(B, Hv, dv)
+    if Hv > Hk:
+        q, k = q.repeat_interleave(Hv // Hk, dim=1), k.repeat_interleave(Hv // Hk, dim=1)
+    beta = torch.sigmoid(b.float()) * (2.0 if s.gdn_neg_eigval else 1.0)
+    g = -v[f"l{i}.gdn_A_log"].float().exp() * F.softplus(a.float() + v[f"l{i}.gdn_dt_bias"].float())
+    S = S * g.exp()[:, :, None, None]
+    d = beta[:, :, None] * (val - torch.einsum("bhkv,bhk->bhv", S, k))
+    S = S + k[:, :, :, None] * d[:, :, None, :]
+    o = torch.einsum("bhkv,bhk->bhv", S, q)
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + 1e-5)
+    o = (v[f"l{i}.gdn_o_norm"] * o.to(x.dtype)).float() * F.silu(gate.float().view(B, Hv, dv))
+    return o.to(x.dtype).reshape(B, V) @ v[f"l{i}.gdn_out"].t(), seq[:, 1:].detach(), S.detach()
+
+
 def gdn_mixer(x: torch.Tensor, v: dict, i: int, spec, cu_seqlens: torch.Tensor, chunk: int = 64, sequential: bool = False) -> torch.Tensor:
     """The gated-DeltaNet sub-layer of layer ``i`` on normed input ``x`` [T, D] of packed documents (``v``: the parameter
     views): every document starts from an empty state and nothing crosses a document boundary."""

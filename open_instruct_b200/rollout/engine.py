@@ -476,13 +476,24 @@ class RolloutEngine:
                 from ..models.gdn import gdn_segment
 
                 n1 = ref.rmsnorm(x, p[f"l{i}.attn_norm"], s.rms_norm_eps)
-                outs = []
-                for lo, hi, src, dsts in self._gdn_runs:
-                    o, st = gdn_segment(n1[lo:hi], p, i, s, None if src is None else self._gdn_state[src][i])
-                    outs.append(o)
-                    for sid in dsts:
-                        self._gdn_state.setdefault(sid, {})[i] = st
-                x = x + torch.cat(outs)
+                if all(hi - lo == 1 and src is not None for lo, hi, src, _ in self._gdn_runs):
+                    # a decode step: one recurrence step for all sequences at once
+                    from ..models.gdn import gdn_decode_step
+
+                    states = [self._gdn_state[src][i] for _, _, src, _ in self._gdn_runs]
+                    mixed, tails, S = gdn_decode_step(n1, p, i, s, torch.stack([t for t, _ in states]), torch.stack([st for _, st in states]))
+                    for b, (_, _, _, dsts) in enumerate(self._gdn_runs):
+                        for sid in dsts:
+                            self._gdn_state[sid][i] = (tails[b], S[b])
+                    x = x + mixed
+                else:
+                    outs = []
+                    for lo, hi, src, dsts in self._gdn_runs:
+                        o, st = gdn_segment(n1[lo:hi], p, i, s, None if src is None else self._gdn_state[src][i])
+                        outs.append(o)
+                        for sid in dsts:
+                            self._gdn_state.setdefault(sid, {})[i] = st
+                    x = x + torch.cat(outs)
                 x = x + self.model.ref_mlp(ref.rmsnorm(x, p[f"l{i}.mlp_norm"], s.rms_norm_eps), p, i)
                 continue
             # pre-norm blocks (Llama, Qwen, Mistral) norm the sub-layer's input; post-norm blocks (OLMo-2 / OLMo-3) its output
@@ -788,22 +799,32 @@ class RolloutEngine:
                              dtype=torch.long, device=dev)
         ctx = torch.tensor(ctx_list, dtype=torch.int32, device=dev)
         scale = s.attn_scale
-        if True:
-            g = s.num_heads // s.num_kv_heads
+        g = s.num_heads // s.num_kv_heads
+        # all sequences at once: their pages gathered into one padded [B, positions] view, positions beyond a sequence's
+        # context (and before a sliding-window layer's window) masked; in groups of sequences so that a group's gathered
+        # keys stay within about a million positions
+        span = max_blocks * KV_BLOCK
+        group = max(1, min(B, (1 << 20) // span))
+        ctx_col = ctx.long()[:, None]
+        where = torch.arange(span, device=dev)[None, :]
 
-            def attn_fn(i, qkv):
-                q = qkv.view(B, s.num_heads + 2 * s.num_kv_heads, s.head_dim)[:, : s.num_heads].float()
-                outs = []
-                w = s.window(i)
-                for b in range(B):
-                    blk = bt[b, : -(-ctx_list[b] // KV_BLOCK)].long()
-                    first = max(0, ctx_list[b] - w) if w else 0   # sliding-window layers read the latest w positions only
-                    k = self.k_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, first : ctx_list[b]].float()
-                    v = self.v_cache[i][blk].permute(1, 0, 2, 3).reshape(s.num_kv_heads, -1, s.head_dim)[:, first : ctx_list[b]].float()
-                    k, v = k.repeat_interleave(g, 0), v.repeat_interleave(g, 0)
-                    p = torch.softmax((q[b][:, None, :] @ k.transpose(1, 2)) * scale, -1)
-                    outs.append((p @ v).squeeze(1).reshape(-1))
-                return torch.stack(outs).to(qkv.dtype)
+        def attn_fn(i, qkv):
+            q = qkv.view(B, s.num_heads + 2 * s.num_kv_heads, s.head_dim)[:, : s.num_heads].float().view(B, s.num_kv_heads, g, s.head_dim)
+            w = s.window(i)
+            live = where < ctx_col
+            if w:   # sliding-window layers read the latest w positions only
+                live = live & (where >= ctx_col - w)
+            out = torch.empty(B, s.num_heads * s.head_dim, dtype=torch.float32, device=dev)
+            for b0 in range(0, B, group):
+                b1 = min(B, b0 + group)
+                pages = bt[b0:b1].long()
+                # [b, blocks, Hkv, BLOCK, D] -> [b, Hkv, blocks * BLOCK, D]
+                k = self.k_cache[i][pages].permute(0, 2, 1, 3, 4).reshape(b1 - b0, s.num_kv_heads, span, s.head_dim).float()
+                v = self.v_cache[i][pages].permute(0, 2, 1, 3, 4).reshape(b1 - b0, s.num_kv_heads, span, s.head_dim).float()
+                sc = torch.einsum("bhgd,bhtd->bhgt", q[b0:b1], k) * scale
+                sc = sc.masked_fill(~live[b0:b1, None, None, :], float("-inf"))
+                out[b0:b1] = torch.einsum("bhgt,bhtd->bhgd", torch.softmax(sc, -1), v).reshape(b1 - b0, -1)
+            return out.to(qkv.dtype)
         hidden = self._layer_stack(ids, pos, slots, attn_fn)
         logits = self._logits(hidden)
         self.stats["decode_tokens"] += B
