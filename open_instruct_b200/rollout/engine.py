@@ -367,7 +367,9 @@ class RolloutEngine:
 
     def _sample(self, logits: torch.Tensor, seqs: list[_Sequence]):
         temp, top_p, seeds, ctr = self._sampling_tensors(seqs)
-        if self.ops == "fused":
+        # the sampler kernel only needs bf16 logits on a B200: the PyTorch path of the model (OLMo-family models on a GPU) uses it
+        # too instead of the row-by-row host sampler, which is the oracle and the CPU path
+        if self.ops == "fused" or (logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(-1) == 1 and lib.available()):
             from ..ops.lib import call, ptr, stream_ptr
 
             B, V = logits.shape
