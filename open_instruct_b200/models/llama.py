@@ -399,9 +399,12 @@ class LlamaModel:
         """Runs the stack; returns final-norm hidden states.  ``keep`` stores what backward needs."""
         f = self.kernels
         s, p = self.spec, self.p
-        if s.min_window and cu_seqlens.numel() > 1 and int((cu_seqlens[1:] - cu_seqlens[:-1]).max()) > s.min_window:
-            raise NotImplementedError(f"documents longer than the model's sliding window ({s.min_window}) need windowed attention; the attention "
-                                      "kernel attends to the whole document: run these with ops='ref'")
+        # sliding-window layers: while every document fits in the window the attention kernel is exact; for longer documents those
+        # layers go through the windowed library attention (``attn_fwd_window``), the only part of the step that is not a kernel of
+        # this package
+        self._max_doc = int((cu_seqlens[1:] - cu_seqlens[:-1]).max()) if (s.min_window and cu_seqlens.numel() > 1) else 0
+        if s.min_window and self._max_doc > s.min_window and self.sp is not None:
+            raise NotImplementedError(f"documents longer than the model's sliding window ({s.min_window}) together with sequence parallelism")
         pos = position_ids.to(torch.int32)
         cu = cu_seqlens.to(torch.int32)
         scale = s.attn_scale
@@ -461,7 +464,8 @@ class LlamaModel:
             nf, h_last, rstd_f = f.rmsnorm_fwd(delta, p["final_norm"], s.rms_norm_eps, res=stream)
         state = None
         if keep:
-            state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu, "rope_tab": self._rope_tab}
+            state = {"stash": stash, "final": (h_last, rstd_f), "ids": input_ids, "pos": pos, "cu": cu, "rope_tab": self._rope_tab,
+                     "max_doc": self._max_doc}
         if s.num_experts:
             # the load-balancing loss of this forward (a plain number here: the backward adds ``aux_loss_coef`` times its gradient,
             # which reaches the routers through the mean probability of every expert, E / N * sum_k f[k, e] per softmax entry)
@@ -520,7 +524,7 @@ class LlamaModel:
         f.gemm(d_o, st.attn_tok if sp is not None else st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
         if sp is None:
             d_attn = f.gemm(d_o, p[f"l{i}.wo"], b_mn=True)
-            dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+            dqkv = self._attn_bwd(i, st, d_attn, cu, scale)
             del d_attn
             f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True, table=self._rope_tab)
             self._qkv_bias_and_norm_bwd_(dqkv, i, st.qk)
@@ -627,6 +631,13 @@ class LlamaModel:
         d_n2 += (d_logits @ p[f"l{i}.router"]).float()
         return d_n2.to(n2.dtype)
 
+    def _attn_bwd(self, i: int, st: _LayerStash, d_attn, cu, scale):
+        """Gradient with respect to the post-RoPE qkv of layer ``i`` (one rank holds all heads)."""
+        f, s = self.kernels, self.spec
+        if st.lse is None:   # the forward of this layer went through the windowed library attention
+            return f.attn_bwd_window(st.qkv, d_attn, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale, s.window(i), self._max_doc)
+        return f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+
     def _attention_block(self, i: int, n1, pos, cu):
         """QKV projection, RoPE and attention of layer ``i``.  Returns ``(qkv, attn, lse, attn_tok)``; with sequence
         parallelism ``qkv``/``attn`` cover all tokens for this rank's heads and ``attn_tok`` this rank's tokens for all
@@ -638,6 +649,9 @@ class LlamaModel:
             qkv = f.gemm(n1, p[f"l{i}.wqkv"])
             self._last_qk = self.qkv_bias_and_norm_(qkv, i)
             f.rope_(qkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, table=self._rope_tab)
+            w = s.window(i)
+            if w and self._max_doc > w:   # lse None marks the layer for the windowed backward
+                return qkv, f.attn_fwd_window(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale, w, self._max_doc), None, None
             attn, lse = f.attn_fwd(qkv, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
             return qkv, attn, lse, None
         qkv = sp.qkv_project(i, n1, p[f"l{i}.wqkv"], pos.numel())
@@ -719,6 +733,7 @@ class LlamaModel:
         h_last, rstd_f = state["final"]
         stash, pos, cu = state["stash"], state["pos"], state["cu"]
         self._rope_tab = state["rope_tab"]
+        self._max_doc = state["max_doc"]   # another forward pass may have run since this one
         # final norm: h_last = stream + delta ; both get the same gradient
         d_stream = f.rmsnorm_bwd(h_last, p["final_norm"], rstd_f, d_nf, None, g["final_norm"])
         del d_nf
@@ -771,7 +786,7 @@ class LlamaModel:
             f.gemm(d_mid, st.attn_tok if sp is not None else st.attn, g[f"l{i}.wo"], a_mn=True, b_mn=True, out_mode=wgrad_mode)
             if sp is None:
                 d_attn = f.gemm(d_mid, p[f"l{i}.wo"], b_mn=True)
-                dqkv = f.attn_bwd(st.qkv, st.attn, d_attn, st.lse, cu, s.num_heads, s.num_kv_heads, s.head_dim, scale)
+                dqkv = self._attn_bwd(i, st, d_attn, cu, scale)
                 del d_attn
                 f.rope_(dqkv, pos, self.inv_freq, s.num_heads, s.num_kv_heads, s.head_dim, backward=True, table=self._rope_tab)
                 self._qkv_bias_and_norm_bwd_(dqkv, i, st.qk)

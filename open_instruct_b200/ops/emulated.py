@@ -168,3 +168,15 @@ def attn_bwd(qkv, out, d_out, lse, cu_seqlens, n_q: int, n_kv: int, head_dim: in
         y = ref.attention_varlen(x, cu_seqlens, n_q, n_kv, head_dim, scale)
         (dx,) = torch.autograd.grad(y, x, d_out.float())
     return dx.to(qkv.dtype)
+
+
+def attn_fwd_window(qkv, cu_seqlens, n_q: int, n_kv: int, head_dim: int, scale: float, window: int, max_len: int):
+    return ref.attention_varlen(qkv.float(), cu_seqlens, n_q, n_kv, head_dim, scale, window=window).to(qkv.dtype)
+
+
+def attn_bwd_window(qkv, d_out, cu_seqlens, n_q: int, n_kv: int, head_dim: int, scale: float, window: int, max_len: int):
+    with torch.enable_grad():
+        x = qkv.detach().float().requires_grad_(True)
+        y = ref.attention_varlen(x, cu_seqlens, n_q, n_kv, head_dim, scale, window=window)
+        (dx,) = torch.autograd.grad(y, x, d_out.float())
+    return dx.to(qkv.dtype)

@@ -354,3 +354,30 @@ def attn_bwd(qkv, out, d_out, lse, cu_seqlens, n_q: int, n_kv: int, head_dim: in
     call("b200_attn_bwd", ptr(qkv), ptr(out), ptr(d_out), ptr(lse), ptr(cu_seqlens), ptr(dqkv), ptr(scratch),
          ptr(status_word(qkv.device)), T, B, n_q, n_kv, head_dim, attn_max_tiles(T, B), scale, stream_ptr())
     return dqkv
+
+
+def _window_attention(qkv, cu_seqlens, n_q: int, n_kv: int, head_dim: int, scale: float, window: int, max_len: int):
+    from flash_attn import flash_attn_varlen_func
+
+    T = qkv.shape[0]
+    x = qkv.view(T, n_q + 2 * n_kv, head_dim)
+    out = flash_attn_varlen_func(x[:, :n_q], x[:, n_q:n_q + n_kv], x[:, n_q + n_kv:], cu_seqlens, cu_seqlens, max_len, max_len, 0.0,
+                                 softmax_scale=scale, causal=True, window_size=(window - 1, 0))
+    return out.reshape(T, n_q * head_dim)
+
+
+def attn_fwd_window(qkv: torch.Tensor, cu_seqlens: torch.Tensor, n_q: int, n_kv: int, head_dim: int, scale: float, window: int, max_len: int):
+    """Varlen causal attention in which a token sees the latest ``window`` tokens of its document only (itself included).  The
+    attention kernels of this package have no window, so layers whose documents outgrow it call the FlashAttention library
+    (``window_size=(window - 1, 0)``); a library call like a cuBLAS GEMM, used by sliding-window layers only."""
+    with torch.no_grad():
+        return _window_attention(qkv, cu_seqlens, n_q, n_kv, head_dim, scale, window, max_len)
+
+
+def attn_bwd_window(qkv, d_out, cu_seqlens, n_q: int, n_kv: int, head_dim: int, scale: float, window: int, max_len: int) -> torch.Tensor:
+    """dqkv of ``attn_fwd_window``: the library recomputes its forward and differentiates it."""
+    with torch.enable_grad():
+        x = qkv.detach().requires_grad_(True)
+        y = _window_attention(x, cu_seqlens, n_q, n_kv, head_dim, scale, window, max_len)
+        (dx,) = torch.autograd.grad(y, x, d_out.reshape(y.shape))
+    return dx

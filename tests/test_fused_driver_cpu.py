@@ -22,6 +22,9 @@ VARIANTS = {
     "olmo2-chunked-head-recompute": (OLMO2, dict(chunk=128, keep_cheap=False)),
     "olmo2-mha": ({**OLMO2, "num_kv_heads": 4}, {}),
     "post-norm-only": (dict(post_norm=True), {}),
+    "olmo3-documents-longer-than-the-window": ({**OLMO2, "num_layers": 4, "sliding_window": 16, "layer_types": ("sliding", "sliding", "sliding", "attention")}, {}),
+    "olmo3-longer-than-the-window-checkpointing": ({**OLMO2, "num_layers": 4, "sliding_window": 16, "layer_types": ("sliding", "sliding", "sliding", "attention")}, dict(ckpt=True)),
+    "mistral-all-layers-windowed": (dict(sliding_window=32), {}),
     "olmoe": (dict(qk_norm=True, qk_norm_full=True, num_experts=4, num_experts_per_tok=2, intermediate_size=48), {}),
     "olmoe-renormalised-checkpointing": (dict(num_experts=4, num_experts_per_tok=2, norm_topk_prob=True, intermediate_size=48), dict(ckpt=True)),
     "olmoe-balancing-loss": (dict(num_experts=8, num_experts_per_tok=2, intermediate_size=48), dict(aux=0.3)),
