@@ -146,6 +146,7 @@ class LlamaModel:
             self.p = self.layout.views(self.flat)
         self._last_qk = None
         self._rope_tab = None
+        self._max_doc = 0   # longest document of the batch in flight when the model has sliding-window layers
         # keep the RMSNorm outputs and the SwiGLU activation for the backward pass instead of recomputing them
         # (5.8 GB per 4096-token micro-batch at 8B; about 2.5 % of the step): on by default, off under checkpointing
         self.keep_cheap_activations = os.environ.get("B200_RECOMPUTE_CHEAP", "0") != "1"
