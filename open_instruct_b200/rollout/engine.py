@@ -804,14 +804,14 @@ class RolloutEngine:
         g = s.num_heads // s.num_kv_heads
         # all sequences at once: their pages gathered into one padded [B, positions] view, positions beyond a sequence's
         # context (and before a sliding-window layer's window) masked; in groups of sequences so that a group's gathered
-        # keys stay within about a million positions
+        # keys and values stay within about 4 GB
         span = max_blocks * KV_BLOCK
-        group = max(1, min(B, (1 << 20) // span))
+        group = max(1, min(B, int(4e9 // (2 * span * s.num_kv_heads * s.head_dim * self.k_cache.element_size()))))
         ctx_col = ctx.long()[:, None]
         where = torch.arange(span, device=dev)[None, :]
 
         def attn_fn(i, qkv):
-            q = qkv.view(B, s.num_heads + 2 * s.num_kv_heads, s.head_dim)[:, : s.num_heads].float().view(B, s.num_kv_heads, g, s.head_dim)
+            q = qkv.view(B, s.num_heads + 2 * s.num_kv_heads, s.head_dim)[:, : s.num_heads].reshape(B, s.num_kv_heads, g, s.head_dim)
             w = s.window(i)
             live = where < ctx_col
             if w:   # sliding-window layers read the latest w positions only
@@ -821,11 +821,11 @@ class RolloutEngine:
                 b1 = min(B, b0 + group)
                 pages = bt[b0:b1].long()
                 # [b, blocks, Hkv, BLOCK, D] -> [b, Hkv, blocks * BLOCK, D]
-                k = self.k_cache[i][pages].permute(0, 2, 1, 3, 4).reshape(b1 - b0, s.num_kv_heads, span, s.head_dim).float()
-                v = self.v_cache[i][pages].permute(0, 2, 1, 3, 4).reshape(b1 - b0, s.num_kv_heads, span, s.head_dim).float()
-                sc = torch.einsum("bhgd,bhtd->bhgt", q[b0:b1], k) * scale
+                k = self.k_cache[i][pages].permute(0, 2, 1, 3, 4).reshape(b1 - b0, s.num_kv_heads, span, s.head_dim)
+                v = self.v_cache[i][pages].permute(0, 2, 1, 3, 4).reshape(b1 - b0, s.num_kv_heads, span, s.head_dim)
+                sc = torch.einsum("bhgd,bhtd->bhgt", q[b0:b1], k).float() * scale   # products accumulate in fp32 inside the matmul
                 sc = sc.masked_fill(~live[b0:b1, None, None, :], float("-inf"))
-                out[b0:b1] = torch.einsum("bhgt,bhtd->bhgd", torch.softmax(sc, -1), v).reshape(b1 - b0, -1)
+                out[b0:b1] = torch.einsum("bhgt,bhtd->bhgd", torch.softmax(sc, -1).to(v.dtype), v).float().reshape(b1 - b0, -1)
             return out.to(qkv.dtype)
         hidden = self._layer_stack(ids, pos, slots, attn_fn)
         logits = self._logits(hidden)
