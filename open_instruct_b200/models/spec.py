@@ -271,6 +271,14 @@ PRESETS: dict[str, ModelSpec] = {
     "olmo2-7b": ModelSpec(vocab_size=100352, hidden_size=4096, intermediate_size=11008, num_layers=32, num_heads=32,
                           num_kv_heads=32, head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2",
                           qk_norm=True, qk_norm_full=True, post_norm=True, max_position_embeddings=4096),
+    "qwen3-1.7b": ModelSpec(vocab_size=151936, hidden_size=2048, intermediate_size=6144, num_layers=28, num_heads=16, num_kv_heads=8,
+                            head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True, model_type="qwen3", tie_word_embeddings=True,
+                            max_position_embeddings=40960),
+    "smollm2-135m": ModelSpec(vocab_size=49152, hidden_size=576, intermediate_size=1536, num_layers=30, num_heads=9, num_kv_heads=3,
+                              head_dim=64, rms_norm_eps=1e-5, rope_theta=1e5, tie_word_embeddings=True, max_position_embeddings=8192),
+    "olmo2-1b": ModelSpec(vocab_size=100352, hidden_size=2048, intermediate_size=8192, num_layers=16, num_heads=16, num_kv_heads=16,
+                          head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2", qk_norm=True, qk_norm_full=True, post_norm=True,
+                          max_position_embeddings=4096),
     "olmo2-13b": ModelSpec(vocab_size=100352, hidden_size=5120, intermediate_size=13824, num_layers=40, num_heads=40, num_kv_heads=40,
                            head_dim=128, rms_norm_eps=1e-6, rope_theta=5e5, model_type="olmo2", qk_norm=True, qk_norm_full=True, post_norm=True,
                            max_position_embeddings=4096),
