@@ -144,10 +144,20 @@ class ModelSpec:
                           gdn_value_dim=cfg.get("linear_value_head_dim") or 2 * kd, gdn_conv=cfg.get("linear_conv_kernel_dim", 4),
                           gdn_neg_eigval=bool(cfg.get("linear_allow_neg_eigval", True)),
                           use_rope=(cfg.get("rope_theta") or rp.get("rope_theta")) is not None)
-        if mt == "olmo3" and cfg.get("sliding_window"):
+        windowed = cfg.get("sliding_window") and (mt == "olmo3" or cfg.get("use_sliding_window", mt == "mistral"))
+        if windowed and mt != "olmo_hybrid":
+            # which layers are windowed: the config's own list, else the family's rule (OLMo-3: three of four; Qwen2 / Qwen3: the
+            # layers from ``max_window_layers`` up; Mistral v0.1: all, which is what ``layer_types`` None means)
             n = cfg["num_hidden_layers"]
-            kinds = cfg.get("layer_types") or [("sliding_attention" if (i + 1) % 4 else "full_attention") for i in range(n)]
-            hybrid = dict(layer_types=tuple("sliding" if k == "sliding_attention" else "attention" for k in kinds))
+            kinds = cfg.get("layer_types")
+            if not kinds and mt == "olmo3":
+                kinds = [("sliding_attention" if (i + 1) % 4 else "full_attention") for i in range(n)]
+            if not kinds and mt in ("qwen2", "qwen3") and cfg.get("max_window_layers") is not None:
+                kinds = [("sliding_attention" if i >= cfg["max_window_layers"] else "full_attention") for i in range(n)]
+            if kinds and "sliding_attention" in kinds and "full_attention" in kinds:
+                hybrid = dict(layer_types=tuple("sliding" if k == "sliding_attention" else "attention" for k in kinds))
+            elif kinds and "sliding_attention" not in kinds:
+                windowed = False
         return cls(
             **hybrid,
             vocab_size=cfg["vocab_size"],
@@ -169,7 +179,7 @@ class ModelSpec:
             norm_topk_prob=bool(cfg.get("norm_topk_prob", False)),
             router_aux_loss_coef=cfg.get("router_aux_loss_coef", 0.01),
             post_norm=mt in ("olmo2", "olmo3", "olmo_hybrid"),
-            sliding_window=cfg.get("sliding_window") if (mt == "olmo3" or cfg.get("use_sliding_window", mt == "mistral")) else None,
+            sliding_window=cfg.get("sliding_window") if windowed else None,
             attention_bias=cfg.get("attention_bias", mt == "qwen2"),
             model_type=mt,
             bos_token_id=cfg.get("bos_token_id"),

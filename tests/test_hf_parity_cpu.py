@@ -315,3 +315,23 @@ def test_hybrid_layers_do_not_leak_across_packed_documents():
     alone = m.logits(ids[70:], torch.arange(30), torch.tensor([0, 30], dtype=torch.int32))
     assert (packed[70:] - alone).abs().max().item() < 1e-5
     assert (packed[:70] - m.logits(ids[:70], torch.arange(70), torch.tensor([0, 70], dtype=torch.int32))).abs().max().item() < 1e-5
+
+
+def test_qwen2_windowed_upper_layers_equal_transformers():
+    """Qwen2 with ``use_sliding_window``: the layers from ``max_window_layers`` up are windowed, the lower ones attend to everything."""
+    from open_instruct_b200.ckpt.hf_io import load_hf_checkpoint
+    from open_instruct_b200.models import LlamaModel
+    from open_instruct_b200.models.spec import ModelSpec
+
+    hf, cfg = _hf_model("Qwen2", dict(num_hidden_layers=4, use_sliding_window=True, sliding_window=16, max_window_layers=2))
+    with tempfile.TemporaryDirectory() as d:
+        hf.save_pretrained(d, safe_serialization=True)
+        spec = ModelSpec.from_pretrained(d)
+        assert spec.layer_types == ("attention", "attention", "sliding", "sliding") and spec.sliding_window == 16
+        ours = LlamaModel(spec, device="cpu", dtype=torch.float32, ops="ref")
+        load_hf_checkpoint(d, ours.flat.detach(), spec, strict=True)
+    ids = torch.randint(0, cfg.vocab_size, (2, 40), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids).logits
+    assert (_our_logits(ours, ids) - want).abs().max().item() < 1e-5
+    assert ModelSpec.from_hf_config({**cfg.to_dict(), "use_sliding_window": False}).sliding_window is None
