@@ -21,6 +21,7 @@ FAMILIES = {
         "rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 32, "attention_factor": 1.2079441541679836, "beta_fast": 32, "beta_slow": 1})),
     "qwen2": ("Qwen2", {}),
     "qwen3": ("Qwen3", dict(head_dim=32)),
+    "qwen2-windowed-upper-layers": ("Qwen2", dict(num_hidden_layers=4, use_sliding_window=True, sliding_window=16, max_window_layers=2)),
     "mistral": ("Mistral", dict(sliding_window=None)),
     "olmo2": ("Olmo2", {}),
     "olmo3": ("Olmo3", dict(sliding_window=4096)),
@@ -75,7 +76,7 @@ def test_checkpoint_import_gives_hf_logits(family):
 
 
 @pytest.mark.parametrize("family", ["llama3.1-rope-scaling", "qwen3", "olmo2", "olmoe", "olmo-hybrid", "olmo-hybrid-no-rope", "olmo3-window-shorter-than-the-text",
-                                    "mistral-window-shorter-than-the-text", "llama-yarn"])
+                                    "mistral-window-shorter-than-the-text", "llama-yarn", "qwen2-windowed-upper-layers"])
 def test_checkpoint_export_is_read_by_hf(family):
     from open_instruct_b200.ckpt.hf_io import save_hf_checkpoint
     from open_instruct_b200.models import LlamaModel
