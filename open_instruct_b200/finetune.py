@@ -142,10 +142,12 @@ class FlatArguments:
             raise ValueError("Need either a dataset name, dataset mixer, or dataset mixer list.")
         if sum(x is not None for x in (self.dataset_name, self.dataset_mixer)) > 1:
             raise ValueError("Cannot provide two dataset selection mechanisms.")
-        if self.use_8bit_optimizer:
-            raise ValueError("8-bit optimizers (bitsandbytes) are not part of this framework; the adapters' AdamW runs in fp32")
         if self.use_qlora:
             self.use_lora = True  # QLoRA = LoRA adapters over an NF4-quantised frozen base
+        if self.use_8bit_optimizer and not self.use_lora:
+            # the reference, too, only builds its 8-bit optimizer next to QLoRA (``open_instruct/finetune.py:668-678``); the
+            # full-parameter optimizer here is the sharded fp32 AdamW
+            raise ValueError("use_8bit_optimizer applies to adapter training (use_lora / use_qlora): 8-bit moments for the adapters' AdamW")
         if isinstance(self.additional_model_arguments, str):
             self.additional_model_arguments = json.loads(self.additional_model_arguments)
         if self.sequence_parallel_size < 1:
@@ -259,7 +261,7 @@ def main(args: FlatArguments, tc: TokenizerConfig) -> dict:
         from .models.lora import LoRATrainer
 
         lora = LoRATrainer(learner, rank=args.lora_rank, alpha=args.lora_alpha, dropout=args.lora_dropout, lr=args.learning_rate,
-                           weight_decay=args.weight_decay, quantize_base=args.use_qlora)
+                           weight_decay=args.weight_decay, quantize_base=args.use_qlora, eight_bit_optimizer=args.use_8bit_optimizer)
         logger.info("LoRA: %d trainable parameters (rank %d) on a frozen base", lora.adapters.num_parameters(), args.lora_rank)
 
     # ------------------------------------------------------------------ resume

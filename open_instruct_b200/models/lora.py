@@ -239,7 +239,7 @@ class LoRATrainer:
     adapters are updated identically everywhere, and the merged weights are written back into the working buffer."""
 
     def __init__(self, learner, rank: int = 64, alpha: float = 16.0, dropout: float = 0.0, lr: float = 1e-4, weight_decay: float = 0.0,
-                 quantize_base: bool = False):
+                 quantize_base: bool = False, eight_bit_optimizer: bool = False):
         """``quantize_base`` (QLoRA, ``open_instruct/finetune.py:551-570``): the frozen copy of the adapted matrices is kept as
         NF4 blocks and the model computes with their dequantised values, so the adapters learn on top of the quantised base."""
         self.learner = learner
@@ -251,7 +251,12 @@ class LoRATrainer:
                 self.adapters.merge_into(m, self.base)  # B = 0: the working copy now holds the NF4-rounded base
         else:
             self.base = m.flat.detach().clone()
-        self.opt = torch.optim.AdamW([self.adapters.flat], lr=lr, weight_decay=weight_decay)
+        if eight_bit_optimizer:   # ``use_8bit_optimizer``: the adapters' two moments in 8 bits, block-wise
+            from ..parallel.adam8bit import AdamW8bit
+
+            self.opt = AdamW8bit([self.adapters.flat], lr=lr, weight_decay=weight_decay)
+        else:
+            self.opt = torch.optim.AdamW([self.adapters.flat], lr=lr, weight_decay=weight_decay)
 
     def step(self, micro_batches: list[dict], lr: float | None = None) -> dict:
         """One optimizer step on the adapters over packed SFT micro-batches (token-mean loss)."""
