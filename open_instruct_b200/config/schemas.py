@@ -53,6 +53,19 @@ class ModelConfig:
         check_model_config(self)
 
 
+def spec_with_rope_flags(spec, cfg):
+    """``--rope_scaling_factor`` (with ``--rope_scaling_beta_fast / _beta_slow / _old_context_len``): train the model with its
+    context extended by YaRN, as the reference's olmo-core path does (``open_instruct/olmo_core_utils.py:448-456``).  Returns the
+    spec with that scaling rule (and a ``max_position_embeddings`` that covers the extended context); unchanged without the flag."""
+    factor = getattr(cfg, "rope_scaling_factor", None)
+    if factor is None:
+        return spec
+    old = int(getattr(cfg, "rope_scaling_old_context_len", 8192))
+    rule = {"rope_type": "yarn", "factor": float(factor), "beta_fast": float(getattr(cfg, "rope_scaling_beta_fast", 32)),
+            "beta_slow": float(getattr(cfg, "rope_scaling_beta_slow", 1)), "original_max_position_embeddings": old}
+    return spec.replace(rope_scaling=rule, max_position_embeddings=max(spec.max_position_embeddings, int(old * factor)))
+
+
 def check_model_config(cfg) -> None:
     """Refuse switches that would otherwise parse and do nothing."""
     if getattr(cfg, "load_in_8bit", False) or getattr(cfg, "load_in_4bit", False) or getattr(cfg, "use_bnb_nested_quant", False):

@@ -108,6 +108,9 @@ def prepare(args: DPOExperimentConfig, tc: TokenizerConfig):
 
     # ------------------------------------------------------------------ model
     spec = get_spec(args.config_name or args.model_name_or_path)
+    from .config.schemas import spec_with_rope_flags
+
+    spec = spec_with_rope_flags(spec, args)   # --rope_scaling_factor: YaRN context extension
     if args.additional_model_arguments:
         spec = spec.replace(**args.additional_model_arguments)
     if len(tokenizer) > spec.vocab_size:
@@ -179,10 +182,23 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
     tracker = Tracker(args.output_dir, args.run_name or args.exp_name, asdict(args),
                       report_to=args.report_to if args.with_tracking else ("jsonl",), wandb_project=args.wandb_project,
                       wandb_entity=args.wandb_entity, enabled=is_main)
+    # adapters (``use_lora``, ``open_instruct/dpo_tune_cache.py:360-376``): the base stays frozen - it is also the reference policy,
+    # whose log-probs were cached above from the same weights - and AdamW runs on the low-rank pairs only
+    lora = None
+    if args.use_lora:
+        if learner.z3 is not None or learner.tp is not None:
+            raise NotImplementedError("LoRA adapters need the resident, unsplit parameter copy (no shard_parameters, no tensor parallelism)")
+        from .models.lora import LoRATrainer
+
+        lora = LoRATrainer(learner, rank=args.lora_rank, alpha=args.lora_alpha, dropout=args.lora_dropout, lr=args.learning_rate,
+                           weight_decay=args.weight_decay)
+        logger.info("LoRA: %d trainable parameters (rank %d) on a frozen base", lora.adapters.num_parameters(), args.lora_rank)
     completed, start_epoch = 0, 0
     ckpt = get_last_checkpoint_path(args.output_dir, args.resume_from_checkpoint)
     if ckpt and is_checkpoint_folder(ckpt):
         st = load_train_state(ckpt, learner.opt)
+        if lora is not None:
+            lora.load_state(ckpt)
         completed, start_epoch = st["completed_steps"], st["epoch"]
         learner.global_step = completed
         loader.load_state_dict(st["loader"])
@@ -208,13 +224,15 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
                 break
             step_t0 = time.time()
             lengths = []
+            if lora is not None:
+                lora.begin()
             for k, mb in enumerate(mbs):
                 mb = to_device(mb, device)
                 pc, pr, aux = forward_fn(learner, mb, average_log_prob=average)
                 losses, c_rew, r_rew = compute_loss(args, mb, pc, pr, reference_cache,
                                                     (aux["chosen_tokens"], aux["rejected_tokens"]))
                 loss = losses.mean()
-                learner.backward(loss, last=(k == len(mbs) - 1))
+                learner.backward(loss, last=(k == len(mbs) - 1) and lora is None)
                 metrics.add("train_loss", loss.detach() / len(mbs))
                 metrics.add("logps/chosen", pc.detach().mean() / len(mbs))
                 metrics.add("logps/rejected", pr.detach().mean() / len(mbs))
@@ -229,7 +247,11 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
                 for k in ("chosen", "rejected"):
                     cu = mb[f"{k}_cu_seq_lens_q"]
                     lengths += (cu[1:] - cu[:-1]).tolist()
-            norm = learner.optimizer_step()
+            if lora is not None:
+                norm = lora.finish(len(mbs), learner.lr(completed), args.max_grad_norm)
+                learner.global_step = completed + 1
+            else:
+                norm = learner.optimizer_step()
             profiler.step()
             completed += 1
             if completed % args.logging_steps == 0:
@@ -249,7 +271,8 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
                 metrics.zero_()
             if args.checkpointing_steps and completed % args.checkpointing_steps == 0:
                 d = os.path.join(args.output_dir, f"step_{completed}")
-                save_train_state(d, learner.opt, {"completed_steps": completed, "epoch": epoch, "loader": loader.state_dict()})
+                save_train_state(d, learner.opt, {"completed_steps": completed, "epoch": epoch, "loader": loader.state_dict()},
+                                 before_complete=lora.save_state if lora is not None else None)
                 if is_main:
                     clean_last_n_checkpoints(args.output_dir, args.keep_last_n_checkpoints)
         if completed >= max_steps:
@@ -257,7 +280,9 @@ def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
     pdist.barrier()
     full_weights = learner.full_flat()  # a gather when the parameters are sharded: every rank takes part
     if is_main:
-        save_hf_checkpoint(full_weights, spec, args.output_dir, tokenizer=tokenizer)
+        save_hf_checkpoint(full_weights, spec, args.output_dir, tokenizer=tokenizer)   # with adapters: the merged model
+        if lora is not None:
+            lora.save(os.path.join(args.output_dir, "adapter"), args.model_name_or_path)
     profiler.close()
     tracker.close()
     pdist.barrier()

@@ -996,6 +996,9 @@ class GRPORun:
             self.cached_only = {"cached": len(dataset)}
             return
         spec = get_spec(model_config.config_name or model_config.model_name_or_path)
+        from .config.schemas import spec_with_rope_flags
+
+        spec = spec_with_rope_flags(spec, model_config)   # --rope_scaling_factor: YaRN context extension
         if len(tokenizer) > spec.vocab_size:
             spec = spec.replace(vocab_size=(len(tokenizer) + 7) // 8 * 8)
         spec = spec.replace(pad_token_id=tokenizer.pad_token_id, eos_token_id=tokenizer.eos_token_id, bos_token_id=tokenizer.bos_token_id)

@@ -263,8 +263,8 @@ class LoRATrainer:
         from ..data.collate import IGNORE
         from ..parallel import dist as pdist
 
-        L, m = self.learner, self.learner.model
-        m.zero_grad()
+        L = self.learner
+        self.begin()
         losses, ntok = [], 0
         for mb in micro_batches:
             logp, _ = L.token_logprobs(mb)
@@ -273,11 +273,30 @@ class LoRATrainer:
             loss.backward()
             losses.append(loss.detach())
             ntok += int(n)
+        g_norm = self.finish(len(micro_batches), lr)
+        return {"loss": torch.stack(losses).mean(), "grad_norm": g_norm, "target_tokens": ntok}
+
+    def begin(self) -> None:
+        """Start an adapter step: clear the model's gradient buffer.  The caller then runs any number of forward / backward
+        passes of ITS loss through the learner's model (whose working weights are the merged ones) and calls ``finish``."""
+        self.learner.model.zero_grad()
+
+    def finish(self, num_micro_batches: int, lr: float | None = None, max_grad_norm: float | None = None) -> torch.Tensor:
+        """Contract the accumulated ``dL/dW_eff`` into adapter gradients (mean over micro-batches and ranks), step the adapters'
+        AdamW and write the merged weights back.  Returns the adapter gradient norm (before clipping)."""
+        from ..parallel import dist as pdist
+
+        L, m = self.learner, self.learner.model
         if m.ops == "ref":
+            if m.flat.grad is None:
+                raise RuntimeError("adapter step without any backward pass")
             m.main_grad = m.flat.grad.float()
         self.adapters.grad = None
-        g = self.adapters.pull_grads(m).div_(len(micro_batches) * L.world)
+        g = self.adapters.pull_grads(m).div_(num_micro_batches * L.world)
         pdist.all_reduce_(g, group=L.group)
+        norm = g.norm()
+        if max_grad_norm and max_grad_norm > 0:
+            g.mul_(torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0))
         self.adapters.flat.grad = g.to(self.adapters.flat.dtype)
         if lr is not None:
             for grp in self.opt.param_groups:
@@ -289,7 +308,8 @@ class LoRATrainer:
         m.zero_grad()
         with torch.no_grad():
             self.adapters.merge_into(m, self.base)
-        return {"loss": torch.stack(losses).mean(), "grad_norm": g.norm(), "target_tokens": ntok}
+        L._accum = 0   # micro-batches that went through ``Learner.backward`` were counted there
+        return norm
 
     def save(self, out_dir: str, base_model_name_or_path: str = "") -> None:
         self.adapters.save(out_dir, base_model_name_or_path)

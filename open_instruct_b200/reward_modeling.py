@@ -230,6 +230,9 @@ def main(args: Args, tc: TokenizerConfig, model_config: ModelConfig) -> dict:
     args.eval_freq = args.eval_freq or max(1, args.num_training_steps // max(1, args.num_evals))
 
     spec = get_spec(model_config.config_name or model_config.model_name_or_path)
+    from .config.schemas import spec_with_rope_flags
+
+    spec = spec_with_rope_flags(spec, model_config)   # --rope_scaling_factor: YaRN context extension
     if len(tokenizer) > spec.vocab_size:
         spec = spec.replace(vocab_size=(len(tokenizer) + 7) // 8 * 8)
     cfg = LearnerConfig(ops=args.ops, comm=args.comm_backend, learning_rate=args.learning_rate, eps=args.eps,

@@ -162,3 +162,14 @@ def test_weight_update_cannot_overlap_an_engine_step():
         w.engine.has_unfinished = lambda: False
         release.set()
         w.shutdown()
+
+
+def test_rope_scaling_flags_become_a_yarn_rule():
+    from open_instruct_b200.config.schemas import ModelConfig, spec_with_rope_flags
+    from open_instruct_b200.models import get_spec
+
+    spec = get_spec("tiny")
+    assert spec_with_rope_flags(spec, ModelConfig(model_name_or_path="tiny")) is spec
+    out = spec_with_rope_flags(spec, ModelConfig(model_name_or_path="tiny", rope_scaling_factor=8.0, rope_scaling_old_context_len=4096))
+    assert out.rope_scaling == {"rope_type": "yarn", "factor": 8.0, "beta_fast": 32.0, "beta_slow": 1.0, "original_max_position_embeddings": 4096}
+    assert out.max_position_embeddings == 32768 and out.attn_scale > spec.attn_scale

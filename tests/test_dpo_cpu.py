@@ -79,3 +79,40 @@ def test_dpo_end_to_end(tmp_path, monkeypatch):
     assert lines[-1]["rewards/accuracy"] >= 0.5
     assert len(os.listdir(os.path.join(tmp, "refcache"))) == 1
     assert os.path.exists(os.path.join(args.output_dir, "model.safetensors"))
+
+
+def test_dpo_with_lora_adapters(tmp_path, monkeypatch):
+    """``use_lora``: the base weights stay what they were (they are the reference policy too), only the adapters learn; the output
+    folder holds the merged model and the adapter files; a checkpoint carries the adapter state."""
+    import torch
+
+    import open_instruct_b200.dpo_tune_cache as dtc
+    import open_instruct_b200.dpo_utils as du
+    from open_instruct_b200.ckpt.hf_io import load_hf_checkpoint
+    from open_instruct_b200.data.tokenize import TokenizerConfig
+    from open_instruct_b200.models import LlamaModel, get_spec
+
+    tmp = str(tmp_path)
+    monkeypatch.setattr(dtc, "REFERENCE_LOGPROBS_CACHE_PATH", os.path.join(tmp, "refcache"))
+    tok = make_tokenizer(os.path.join(tmp, "tok"))
+    data = make_pref_jsonl(os.path.join(tmp, "pref.jsonl"))
+    args = du.DPOExperimentConfig(model_name_or_path="tiny", mixer_list=[data, "1.0"], max_seq_length=96, per_device_train_batch_size=4,
+                                  gradient_accumulation_steps=2, learning_rate=1e-2, num_epochs=3, output_dir=os.path.join(tmp, "out"),
+                                  local_cache_dir=os.path.join(tmp, "cache"), beta=0.5, loss_type="dpo_norm", checkpointing_steps=2, ops="ref",
+                                  seed=1, warmup_ratio=0.0, use_lora=True, lora_rank=4, lora_alpha=8, lora_dropout=0.0, max_grad_norm=1.0)
+    out = dtc.main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"))
+    lines = [json.loads(l) for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
+    assert abs(lines[0]["train_loss"] - math.log(2)) < 0.05 and lines[-1]["train_loss"] < lines[0]["train_loss"]
+    assert os.path.exists(os.path.join(args.output_dir, "adapter", "adapter_config.json"))
+    kept = sorted(d for d in os.listdir(args.output_dir) if d.startswith("step_"))
+    assert kept and all(os.path.exists(os.path.join(args.output_dir, d, "lora_state.pt")) for d in kept)
+    # merged weights = base + low-rank update: embeddings and norms (not adapted) are the base's, the projections moved by a rank <= 4 matrix
+    spec = get_spec("tiny")
+    base = LlamaModel(spec, ops="ref", seed=args.seed)
+    tuned = LlamaModel(spec, ops="ref", seed=args.seed)
+    load_hf_checkpoint(args.output_dir, tuned.flat.detach(), spec)
+    b, t = base.layout.views(base.flat.detach()), tuned.layout.views(tuned.flat.detach())
+    assert (b["embed"] - t["embed"]).abs().max().item() < 4e-3 and (b["final_norm"] - t["final_norm"]).abs().max().item() < 4e-3   # bf16 export
+    delta = (t["l0.wo"] - b["l0.wo"]).float()
+    sv = torch.linalg.svdvals(delta)
+    assert sv[0] > 0.05 and sv[4] < 0.02 * sv[0]
