@@ -1100,7 +1100,8 @@ class GRPORun:
         self.manager.set_kv_cache_max_concurrency(self.call(engines[0], "get_kv_cache_info", max_len))
         self.sp = max(1, args.sequence_parallel_size)  # the ranks of one sequence-parallel group train on the same packs
         self.prep = DataPreparation(dataset, streaming, prompt_q, results_q, tokenizer, args.world_size // self.sp, args.per_device_train_batch_size,
-                                    args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p)
+                                    args.seed, args.num_training_steps, eval_queue=eval_q, top_p=vllm.vllm_top_p,
+                                    run_name=args.run_name or args.exp_name, model_name=model_config.model_name_or_path)
         self.resume_step, self.eval_outstanding, self.total_tokens, self.t_run = 0, 0, 0, time.time()
         self.max_score = streaming.verification_reward + (streaming.r1_style_format_reward if streaming.apply_r1_style_format_reward else 0.0)
         from .utils.notify import ProgressReporter, warn_if_low_disk_space

@@ -14,6 +14,7 @@ The worker runs as a thread in single-process mode and inside an actor otherwise
 
 from __future__ import annotations
 
+import json
 import logging
 import os
 import threading
@@ -111,6 +112,8 @@ class StreamingDataLoaderConfig:
             raise ValueError("advantage_normalization_type must be 'centered' or 'standard'")
         if self.async_steps < 1:
             raise ValueError("async_steps must be >= 1")
+        if self.save_traces and not self.rollouts_save_path:
+            raise ValueError("`rollouts_save_path` must be provided when `save_traces` is True.")
         if self.active_sampling and not self.filter_zero_std_samples:
             raise ValueError("active_sampling only makes sense with filter_zero_std_samples")
         if self.no_resampling_pass_rate is not None and not (0 < self.no_resampling_pass_rate <= 1):
@@ -212,6 +215,42 @@ class PromptIterator:
         self._order = self._perm()
 
 
+ROLLOUT_SHARD_SIZE = 10000   # samples per JSONL shard of saved rollouts
+
+
+def _at(seq, i):
+    """``seq[i]`` when there is such an entry (made JSON-friendly), else None."""
+    try:
+        v = seq[i]
+    except (TypeError, IndexError, KeyError):
+        return None
+    return v if isinstance(v, (str, int, float, bool, list, dict, type(None))) else str(v)
+
+
+def save_rollout_metadata(save_path: str, run_name: str, model_name: str | None) -> None:
+    """``<run>_metadata.jsonl``: which run, model, code revision and when (``open_instruct/rl_utils.py:46-67``)."""
+    import datetime
+    import subprocess
+
+    try:
+        commit = subprocess.run(["git", "rev-parse", "HEAD"], capture_output=True, text=True, timeout=5,
+                                cwd=os.path.dirname(os.path.abspath(__file__))).stdout.strip() or "unknown"
+    except Exception:  # noqa: BLE001
+        commit = "unknown"
+    os.makedirs(save_path, exist_ok=True)
+    with open(os.path.join(save_path, f"{run_name}_metadata.jsonl"), "w") as fh:
+        fh.write(json.dumps({"run_name": run_name, "git_commit": commit, "model_name": model_name or "unknown",
+                             "timestamp": datetime.datetime.now(datetime.timezone.utc).isoformat()}) + "\n")
+
+
+def save_rollouts(save_path: str, run_name: str, shard: int, records: list[dict]) -> None:
+    """Append ``records`` to ``<run>_rollouts_<shard>.jsonl`` (``open_instruct/rl_utils.py:88-128``)."""
+    os.makedirs(save_path, exist_ok=True)
+    with open(os.path.join(save_path, f"{run_name}_rollouts_{shard:06d}.jsonl"), "a") as fh:
+        for r in records:
+            fh.write(json.dumps(r) + "\n")
+
+
 class DataPreparation:
     """Producer of per-step training data (the role of ``DataPreparationActor``, ``data_loader.py:1292-1647``).
 
@@ -222,8 +261,17 @@ class DataPreparation:
 
     def __init__(self, dataset, config: StreamingDataLoaderConfig, prompt_queue, results_queue, tokenizer, dp_world: int,
                  per_device_train_batch_size: int, seed: int, num_training_steps: int, eval_queue=None, top_p: float = 1.0,
-                 rubric_judge=None):
+                 rubric_judge=None, run_name: str = "run", model_name: str | None = None):
         self.cfg, self.tok = config, tokenizer
+        # ``save_traces``: every rollout of every step goes to JSONL shards under ``rollouts_save_path``
+        # (``open_instruct/rl_utils.py:46-159``), written by a background thread so that batch building does not wait for the disk
+        self.run_name, self.model_name = run_name, model_name
+        self._trace_samples, self._trace_pool = 0, None
+        if config.save_traces:
+            from concurrent.futures import ThreadPoolExecutor
+
+            self._trace_pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="rollout-traces")
+            save_rollout_metadata(config.rollouts_save_path, run_name, model_name)
         # evolving rubrics (``open_instruct/data_loader.py:1366-1370, 1462-1470``): after every step the judge proposes new
         # rubric items from the step's answers; prompts queued afterwards carry the updated rubric set as their ground truth
         self.rubric_manager = None
@@ -331,6 +379,15 @@ class DataPreparation:
             scores += list(r.reward_scores)
         scores_np = np.asarray(scores, dtype=np.float64)
         adv = compute_advantages(scores_np, k, c.advantage_normalization_type)
+        if self._trace_pool is not None:
+            owner = [(pi, r) for pi, r in enumerate(results) for _ in r.responses]
+            records = [{"step": step, "sample_idx": i, "prompt_idx": owner[i][0], "prompt_tokens": queries[i], "response_tokens": responses[i],
+                        "reward": float(scores_np[i]), "advantage": float(adv[i]), "finish_reason": finish[i], "logprobs": logps[i],
+                        "dataset": _at([owner[i][1].dataset], 0), "ground_truth": _at([owner[i][1].ground_truth], 0)}
+                       for i in range(len(responses))]
+            shard = self._trace_samples // ROLLOUT_SHARD_SIZE
+            self._trace_samples += len(records)
+            self._trace_pool.submit(save_rollouts, c.rollouts_save_path, self.run_name, shard, records)
         masks = maybe_mask_truncated_completions(masks, finish, c.mask_truncated_completions)
         packed = pack_sequences(queries, responses, masks, c.pack_length, self.pad, logps, min_num_batches=self.dp_world,
                                 mask_tool_use=c.mask_tool_use)
@@ -451,3 +508,6 @@ class DataPreparation:
             self.lock.notify_all()
         if self.thread is not None:
             self.thread.join(timeout=5)
+        if self._trace_pool is not None:
+            self._trace_pool.shutdown(wait=True)   # rollouts still queued for the disk
+            self._trace_pool = None

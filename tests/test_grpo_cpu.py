@@ -28,10 +28,20 @@ def test_grpo_single_process(tmp_path):
     streaming = StreamingDataLoaderConfig(max_prompt_token_length=64, response_length=12, pack_length=256, async_steps=1,
                                           num_samples_per_prompt_rollout=4, num_unique_prompts_rollout=4, dataset_mixer_list=[data, "1.0"],
                                           dataset_mixer_eval_list=[eval_data, "1.0"], dataset_mixer_eval_list_splits=["train"],
-                                          dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False, temperature=1.0)
+                                          dataset_local_cache_dir=os.path.join(tmp, "cache"), filter_zero_std_samples=False, temperature=1.0,
+                                          save_traces=True, rollouts_save_path=os.path.join(tmp, "rollouts"))
     out = main(args, TokenizerConfig(tokenizer_name_or_path=tok, chat_template_name="tulu"), ModelConfig(model_name_or_path="tiny"), streaming,
                VLLMConfig())
     assert out["num_training_steps"] == 3 and out["training_step"] == 3
+    # save_traces: every rollout of the three steps (4 prompts x 4 samples each) with reward, advantage, tokens and log-probs
+    files = sorted(os.listdir(os.path.join(tmp, "rollouts")))
+    assert any(f.endswith("_metadata.jsonl") for f in files) and any("_rollouts_000000.jsonl" in f for f in files)
+    recs = [json.loads(l) for f in files if "_rollouts_" in f for l in open(os.path.join(tmp, "rollouts", f))]
+    assert len(recs) >= 3 * 16 and {r["step"] for r in recs} >= {1, 2, 3}
+    r0 = recs[0]
+    assert len(r0["response_tokens"]) == len(r0["logprobs"]) > 0 and r0["ground_truth"] is not None and r0["finish_reason"] in ("stop", "length")
+    with pytest.raises(ValueError, match="rollouts_save_path"):
+        StreamingDataLoaderConfig(save_traces=True, rollouts_save_path="")
     lines = [json.loads(l) for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
     assert len(lines) == 3
     for l in lines:
