@@ -392,6 +392,17 @@ class LMJudgeVerifier(VerifierFunction):
         from .judge_utils import extract_score_from_string
 
         messages = self.build_messages(prediction, str(label), query)
+        # a judge request must fit the judge's context window: cut the messages to fit, give up (score 0) when even that
+        # does not (``open_instruct/ground_truth_utils.py:773-797``)
+        from . import context_window_checker as cwc
+
+        cfg = self.verifier_config
+        if not cwc.check_context_window_limit(messages, cfg.llm_judge_max_tokens, cfg.llm_judge_model, cfg.llm_judge_max_context_length, 150):
+            messages = cwc.truncate_messages_to_fit_context(messages, cfg.llm_judge_max_tokens, cfg.llm_judge_model,
+                                                            cfg.llm_judge_max_context_length, 200)
+            if not messages or not cwc.check_context_window_limit(messages, cfg.llm_judge_max_tokens, cfg.llm_judge_model,
+                                                                  cfg.llm_judge_max_context_length, 150):
+                return VerificationResult(0.0, reasoning="Error: Context window exceeded")
         for attempt in range(3):
             try:
                 reply = await self._ask(messages)

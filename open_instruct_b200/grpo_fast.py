@@ -694,6 +694,7 @@ class LearnerWorker:
                             total_steps=max(1, num_training_steps * args.num_epochs * args.num_mini_batches),
                             gradient_checkpointing=model_config.gradient_checkpointing, seed=args.seed,
                             offload_optimizer=args.deepspeed_offload_optimizer, shard_parameters=args.shard_parameters,
+                            decay_bias_and_norm=not args.set_weight_decay_on_bias_and_norm,
                             shard_degree=args.fsdp_shard_degree,
                             sequence_parallel_size=max(1, args.sequence_parallel_size),
                             sp_max_tokens=-(-getattr(args, "sp_max_tokens", 0) // max(1, args.sequence_parallel_size)) * max(1, args.sequence_parallel_size))
@@ -1222,7 +1223,8 @@ class GRPORun:
         eval_due = ((args.eval_on_step_0 and step == 1) or step % args.local_eval_every == 0) if args.local_eval_every > 0 else False
         if self.eval_dataset is not None and len(self.eval_dataset) and args.local_eval_every > 0 and (eval_due or is_last) \
                 and self.eval_outstanding == 0:
-            self.eval_outstanding = submit_eval_prompts(self.eval_dataset, self.prompt_q, streaming, args, step, self.vllm.vllm_top_p)
+            self.eval_outstanding = submit_eval_prompts(self.eval_dataset, self.prompt_q, streaming, args, step,
+                                                        args.eval_top_p or self.vllm.vllm_top_p)   # ``open_instruct/grpo_fast.py:1454``
         if self.eval_outstanding:
             em, n_got = collect_eval_results(self.eval_q, self.eval_outstanding, 600.0 if is_last else 0.0, args, self.max_score)
             if n_got >= self.eval_outstanding or is_last:

@@ -49,6 +49,9 @@ class LearnerConfig:
     # Tensor parallelism of the training engine: groups of this many consecutive ranks split every layer (heads and MLP
     # channels); data parallelism and the optimizer sharding run across the groups.
     tensor_parallel_degree: int = 1
+    # weight decay also on norm weights and biases (the reference's ``set_weight_decay_on_bias_and_norm=False``, which hands the
+    # optimizer ungrouped parameters, ``open_instruct/grpo_fast.py:371-374``); default: those take none
+    decay_bias_and_norm: bool = False
     load_balancing_weight: float = 0.0  # mixture of experts: weight of the router's load-balancing loss added to the SFT loss
     optimizer_type: str = "adamw"     # "adamw" | "muon" (orthogonalised momentum for the decoder layers' matrices, AdamW elsewhere)
     optimizer_kwargs: dict = field(default_factory=dict)  # Muon: mu, nesterov, ns_steps, adamw_lr_scale
@@ -116,6 +119,8 @@ class Learner:
             if comm == "fused":
                 comm = "nccl" if self.world > 1 else "none"  # momentum is exchanged through torch.distributed
                 self.comm = comm
+        if cfg.decay_bias_and_norm and (cfg.shard_parameters or muon):
+            raise NotImplementedError("weight decay on norm weights and biases is built for the resident AdamW only")
         shard = cfg.shard_parameters
         if shard is None and muon:
             shard = False
@@ -172,7 +177,7 @@ class Learner:
                                      betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
                                      group=group, comm=comm, use_kernels=(ops == "fused" and not self.emulated), **dict(cfg.optimizer_kwargs or {}))
         else:
-            self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.decay_end, lr=cfg.learning_rate,
+            self.opt = ZeroOptimizer(self.model.flat.detach(), layout.total, layout.total if cfg.decay_bias_and_norm else layout.decay_end, lr=cfg.learning_rate,
                                      betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay,
                                      max_grad_norm=cfg.max_grad_norm, group=group, comm=comm, symm=self.symm,
                                      use_kernels=(ops == "fused" and not self.emulated), offload=cfg.offload_optimizer,

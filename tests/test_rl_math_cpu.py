@@ -51,6 +51,20 @@ def test_code_and_judge_verifiers_with_fakes():
     jv = g.LMJudgeVerifier("quality", g.LMJudgeVerifierConfig(llm_judge_client=judge))
     res = asyncio.run(jv.async_call([], "an answer", "ref", "q"))
     assert abs(res.score - 0.7) < 1e-9
+    # a request that outgrows the judge's context window is cut to fit; when even the cut does not fit, the score is 0 without a call
+    seen = []
+
+    async def recording_judge(messages, **kw):
+        seen.append(messages)
+        return '{"REASONING": "ok", "SCORE": "5"}'
+
+    long_answer = "word " * 5000
+    fit = g.LMJudgeVerifier("quality", g.LMJudgeVerifierConfig(llm_judge_client=recording_judge, llm_judge_max_tokens=64, llm_judge_max_context_length=1500))
+    assert abs(asyncio.run(fit.async_call([], long_answer, "ref", "q")).score - 0.5) < 1e-9
+    assert len(seen) == 1 and len(seen[0][0]["content"]) < len(long_answer) / 2
+    tiny = g.LMJudgeVerifier("quality", g.LMJudgeVerifierConfig(llm_judge_client=recording_judge, llm_judge_max_tokens=64, llm_judge_max_context_length=250))
+    res = asyncio.run(tiny.async_call([], long_answer, "ref", "q"))
+    assert res.score == 0.0 and "Context window" in res.reasoning and len(seen) == 1
     rv = g.RubricVerifier(g.RubricVerifierConfig(llm_judge_client=judge))
     lab = json.dumps({"query": "q", "rubrics": [{"description": "a", "weight": 1.0}, {"description": "b", "weight": -1.0}]})
     assert asyncio.run(rv.async_call([], "ans", lab)).score == 0.0
