@@ -143,6 +143,8 @@ class DPOExperimentConfig(ExperimentConfig, ModelConfig, DPOConfig, DPOTrainingC
         if self.offload_param:
             raise ValueError("offload_param is not built: with shard_parameters every GPU keeps 1/N of the bf16 weights (17.5 GB for a 70B "
                              "model on 8 GPUs), which fits; use offload_optimizer to move the 12 bytes/parameter of optimizer state to host memory")
+        if self.context_parallel_degree > 1:
+            raise NotImplementedError("context parallelism is not supported with DPO: the preference trainer sums log-probs per sequence on one rank")
         if self.use_qlora or self.use_8bit_optimizer:
             raise ValueError("quantised training paths are not part of this framework")
         from .config.schemas import check_context_parallel, check_model_config

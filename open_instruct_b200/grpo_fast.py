@@ -1021,6 +1021,8 @@ class GRPORun:
         qsize = (streaming.async_steps + 1) * streaming.num_unique_prompts_rollout
         last: dict = {}
         init_by_push = False
+        if vllm.vllm_enforce_eager:
+            os.environ["B200_DECODE_GRAPHS"] = "0"   # the engines (this process or its children) launch decode steps kernel by kernel
 
         if single:
             prompt_q, results_q, eval_q = ray.Queue(local=True), ray.Queue(maxsize=qsize, local=True), ray.Queue(local=True)
