@@ -52,6 +52,8 @@ class _StepBatches:
 
 
 def main(args: DPOExperimentConfig, tc: TokenizerConfig) -> dict:
+    if args.use_lora:   # as in the reference (``open_instruct/dpo.py:142-143``): adapters are the other trainer's business
+        raise ValueError("LoRA is not supported by the callback-driven DPO trainer. Use dpo_tune_cache instead.")
     p = prepare(args, tc)
     if p.done is not None:
         return p.done
