@@ -91,3 +91,26 @@ def test_fused_mixture_of_experts_matches_ref():
     lib.check_status()
     gf, gr = fused.grad_flat(), refm.grad_flat()
     assert ((gf - gr).norm() / gr.norm()).item() < 0.15
+
+
+def test_fused_sliding_window_layers_longer_than_the_window_match_ref():
+    """OLMo-3-like layers (three windowed, one full) with documents longer than the window: the windowed layers go through the
+    FlashAttention library on the fused path; log-probs and gradients against the PyTorch fp32 model with its band mask."""
+    pytest.importorskip("flash_attn")
+    from open_instruct_b200.models import LlamaModel, get_spec
+    from open_instruct_b200.ops import lib
+
+    spec = get_spec("tiny128").replace(post_norm=True, qk_norm=True, qk_norm_full=True, model_type="olmo3", num_layers=4, sliding_window=64,
+                                       layer_types=("sliding", "sliding", "sliding", "attention"))
+    fused = LlamaModel(spec, device="cuda", dtype=torch.bfloat16, ops="fused", seed=3)
+    refm = LlamaModel(spec, device="cuda", dtype=torch.float32, ops="ref", flat=fused.flat.float().clone())
+    ids, pos, cu, labels = _batch([200, 57, 300], spec.vocab_size, "cuda")
+    lp_f, _ = fused.token_logprobs(ids, pos, cu, labels)
+    lp_r, _ = refm.token_logprobs(ids, pos, cu, labels)
+    n = (labels >= 0).sum()
+    assert (lp_f - lp_r).abs().max().item() < 0.05
+    (-(lp_f.sum()) / n).backward()
+    (-(lp_r.sum()) / n).backward()
+    lib.check_status()
+    gf, gr = fused.grad_flat(), refm.grad_flat()
+    assert ((gf - gr).norm() / gr.norm()).item() < 0.06
