@@ -269,6 +269,12 @@ class EngineWorker:
         if flat is not None:
             want = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
             flat = flat.detach().to(device=device, dtype=want).clone()
+        if ops == "fused" and ((spec.min_window and max_model_len > spec.min_window) or spec.has_gdn or spec.num_experts):
+            # ``ops`` is one switch for learners and engines: a model the learner's kernel path serves (windowed layers through the
+            # library fallback, experts GEMM by GEMM) may still need the engine's PyTorch path (no window in the paged kernels, no
+            # recurrent-state or expert kernels there)
+            logger.warning("rollout engine: this model runs on the engine's PyTorch path (ops='ref'); the learner keeps ops='fused'")
+            ops = "ref"
         self.full_flat = None  # tensor parallel: staging copy of the whole model that the learners push into
         self._full_cv, self._full_step = threading.Condition(), None   # which version a follower's staging copy holds
         if tp_size > 1:
