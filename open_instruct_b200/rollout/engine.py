@@ -189,6 +189,8 @@ class RolloutEngine:
         if ops == "fused" and spec.min_window and max_model_len > spec.min_window:
             raise NotImplementedError(f"the paged attention kernels attend to the whole context; sequences longer than the model's sliding "
                                       f"window ({spec.min_window}) need ops='ref' (or a max_model_len within the window)")
+        if ops == "fused" and spec.num_experts:
+            raise NotImplementedError("mixture-of-experts layers run on the engine's PyTorch path (ops='ref')")
         if spec.has_gdn and (ops != "ref" or tp is not None or enable_prefix_caching):
             raise NotImplementedError("hybrid models (gated-DeltaNet layers) are sampled on the PyTorch path (ops='ref'), one engine per "
                                       "model copy, without prefix caching: their per-sequence recurrent state lives beside the paged KV cache")
