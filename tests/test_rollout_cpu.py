@@ -207,3 +207,26 @@ def test_engine_prefix_cache_gives_the_same_tokens(n_samples):
     assert plain.stats.get("prefix_cached_tokens", 0) == 0
     cached.update_weights(cached.model.flat.detach().clone(), 1)
     assert cached.host.prefix_cache_stats()["cached_blocks"] == 0   # K/V of the old weights are not served after an update
+
+
+def test_hybrid_model_survives_preemption():
+    """Gated-DeltaNet layers keep a recurrent state per sequence beside the paged KV cache: a sequence that loses its blocks and is
+    recomputed later rebuilds that state from its tokens - same greedy outputs as with a cache that never fills."""
+    import torch
+
+    from open_instruct_b200.data_types import SamplingConfig
+    from open_instruct_b200.models import get_spec
+    from open_instruct_b200.rollout.engine import RolloutEngine
+
+    spec = get_spec("olmo-hybrid-7b").replace(vocab_size=300, hidden_size=64, intermediate_size=128, num_layers=4, num_heads=4, num_kv_heads=2,
+                                              head_dim=16, layer_types=("gdn", "gdn", "gdn", "attention"), gdn_key_heads=2, gdn_value_heads=4,
+                                              gdn_key_dim=12, gdn_value_dim=24, eos_token_id=None)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 300, (n,), generator=g).tolist() for n in (50, 70, 90, 60)]
+    cfg = SamplingConfig(temperature=0.0, max_tokens=80, n=2)
+    roomy = RolloutEngine(spec, device="cpu", ops="auto", num_blocks=256, seed=1)
+    tight = RolloutEngine(spec, device="cpu", ops="auto", num_blocks=14, seed=1, flat=roomy.model.flat.detach().clone())
+    a, b = roomy.generate(prompts, cfg), tight.generate(prompts, cfg)
+    assert tight.host.preemptions() > 0 and roomy.host.preemptions() == 0
+    assert all(x.responses == y.responses for x, y in zip(a, b))
+    assert tight._gdn_state == {} and tight.host.free_blocks() == 14
