@@ -124,11 +124,12 @@ def test_engine_generates_with_a_post_norm_model(family):
     assert eng._gdn_state == {}   # per-sequence recurrent state is dropped with the sequence
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen2"])
+@pytest.mark.parametrize("family", ["llama", "qwen2", "qwen3", "olmo2", "olmo3", "olmoe", "olmo-hybrid"])
 def test_reward_model_export_is_read_by_hf_sequence_classification(family):
     """The reward-model folder loads with ``AutoModelForSequenceClassification`` and scores like this package's ``get_reward``."""
     from open_instruct_b200.models import LlamaModel
     from open_instruct_b200.models.spec import ModelSpec
+    import open_instruct_b200.olmo_adapter  # noqa: F401  (registers the OLMo families' sequence-classification classes)
     from open_instruct_b200.reward_modeling import load_score_weight, save_reward_model
 
     cls_name, extra = FAMILIES[family]
