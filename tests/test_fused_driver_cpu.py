@@ -142,3 +142,33 @@ def test_lora_on_the_emulated_path_follows_the_pytorch_path():
     assert (got[0][0] - got[1][0]).abs().max().item() < 1e-3
     assert (got[0][1] - got[1][1]).abs().max().item() < 1e-3
     assert got[0][0].abs().max().item() > 1e-2
+
+
+def test_grpo_step_on_the_emulated_path_follows_the_pytorch_path():
+    """``grpo_train_step`` (old / new log-probs, clipped ratio, token-level normalisation, entropy) through the hand-driven path."""
+    from open_instruct_b200.data_types import CollatedBatchData
+    from open_instruct_b200.grpo_fast import grpo_train_step
+    from open_instruct_b200.grpo_utils import GRPOExperimentConfig
+    from open_instruct_b200.learner import Learner, LearnerConfig
+    from open_instruct_b200.rl_utils import pack_sequences
+
+    spec = ModelSpec(**BASE)
+    q = [[5, 6, 7, 8]] * 4
+    r = [[10, 11, 12], [20, 21, 22, 23], [30, 31], [40, 41, 42]]
+    lp = [[-1.0] * len(x) for x in r]
+    args = GRPOExperimentConfig(beta=0.0, load_ref_policy=False, use_rho_correction=False, record_entropy=True)
+    args.temperature = 0.8   # copied from the sampling configuration by the trainer's main()
+    outs = []
+    for ops in ("ref", "emulated"):
+        p = pack_sequences(q, r, [[1] * len(x) for x in r], 64, 0, lp)
+        adv = torch.tensor([0.0, 1.0, -1.0, 0.5, -0.5])
+        p.advantages = [adv[m.long()] for m in p.response_masks]
+        data = CollatedBatchData(p.query_responses, p.attention_masks, p.position_ids, p.advantages, p.response_masks, p.vllm_logprobs, p.cu_seqlens)
+        ln = Learner(spec, LearnerConfig(ops=ops, learning_rate=5e-3, lr_scheduler_type="constant", seed=2), device="cpu")
+        metrics = [grpo_train_step(ln, data, args) for _ in range(2)]
+        outs.append((ln.model.flat.detach().clone(), metrics[-1]))
+    (w0, m0), (w1, m1) = outs
+    assert (w0 - w1).abs().max().item() < 1e-3
+    for k in ("loss/total_avg", "policy/entropy_avg", "val/ratio"):
+        if k in m0:
+            assert abs(float(m0[k]) - float(m1[k])) < 1e-4, (k, m0[k], m1[k])
