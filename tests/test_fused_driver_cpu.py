@@ -172,3 +172,31 @@ def test_grpo_step_on_the_emulated_path_follows_the_pytorch_path():
     for k in ("loss/total_avg", "policy/entropy_avg", "val/ratio"):
         if k in m0:
             assert abs(float(m0[k]) - float(m1[k])) < 1e-4, (k, m0[k], m1[k])
+
+
+@pytest.mark.parametrize("forward", ["concatenated", "separate"])
+def test_dpo_forward_and_gradient_on_the_emulated_path(forward):
+    """The preference trainer's two forward forms through the hand-driven path: same sequence log-probs and, after a DPO loss,
+    the same gradient as autograd over the PyTorch path."""
+    from open_instruct_b200.data.collate import TensorDataCollatorWithFlatteningDPO
+    from open_instruct_b200.data.synthetic import dpo_pairs
+    from open_instruct_b200.dpo_utils import concatenated_forward, dpo_loss, separate_forward
+    from open_instruct_b200.learner import Learner, LearnerConfig
+
+    spec = ModelSpec(**BASE)
+    rows = dpo_pairs(3, spec.vocab_size, seed=0, max_len=200)
+    for r in rows:
+        for k in list(r):
+            if k.endswith("input_ids") or k.endswith("labels"):
+                r[k] = r[k][:60]
+    batch = TensorDataCollatorWithFlatteningDPO()(rows)
+    fn = concatenated_forward if forward == "concatenated" else separate_forward
+    got = []
+    for ops in ("ref", "emulated"):
+        ln = Learner(spec, LearnerConfig(ops=ops, seed=3), device="cpu")
+        pc, pr, _ = fn(ln, batch, average_log_prob=True)
+        losses, _, _ = dpo_loss(pc, pr, torch.zeros_like(pc), torch.zeros_like(pr), beta=0.5)
+        ln.backward(losses.mean(), last=True)
+        got.append((pc.detach(), pr.detach(), ln.model.grad_flat().clone()))
+    assert torch.allclose(got[0][0], got[1][0], atol=1e-5) and torch.allclose(got[0][1], got[1][1], atol=1e-5)
+    assert (got[0][2] - got[1][2]).abs().max().item() < 1e-5 * max(1.0, got[0][2].abs().max().item())
