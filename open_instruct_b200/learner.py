@@ -128,18 +128,18 @@ class Learner:
             shard = (ops == "fused" and not self.emulated and self.world > 1 and self.tp is None and
                      needs_sharding(layout.total, self.world, torch.cuda.get_device_properties(self.device).total_memory, cfg.offload_optimizer))
         if shard:
-            if ops != "fused" or self.emulated:
+            if ops != "fused":
                 raise NotImplementedError("parameter sharding runs on the fused (CUDA) path")
             from .parallel.zero3 import Zero3State
 
-            self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=ops, sharded=True,
+            self.model = LlamaModel(spec, device=self.device, dtype=dtype, ops=model_ops, sharded=True,
                                     gradient_checkpointing=cfg.gradient_checkpointing)
             shard_group, replica_group = group, None
             if cfg.shard_degree and cfg.shard_degree != self.world:
                 shard_group, replica_group = pdist.hsdp_groups(cfg.shard_degree)
             self.z3 = Zero3State(layout, self.device, dtype, shard_group, replica_group=replica_group, comm="peer" if comm == "fused" else "nccl", lr=cfg.learning_rate,
                                  betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
-                                 use_kernels=True, offload=cfg.offload_optimizer)
+                                 use_kernels=not self.emulated, offload=cfg.offload_optimizer)
             if flat_init is not None:
                 self.z3.load_full(flat_init)
             else:

@@ -47,3 +47,13 @@ def test_sharding_policy():
     assert not any(needs_sharding(total["llama3.1-8b"], w, hbm) for w in (2, 4, 8))   # the headline config stays resident
     assert needs_sharding(total["qwen2.5-14b"], 2, hbm) and not needs_sharding(total["qwen2.5-14b"], 8, hbm)
     assert all(needs_sharding(total["llama3.1-70b"], w, hbm, offload_optimizer=True) for w in (2, 4, 8))
+
+
+@pytest.mark.parametrize("ckpt", ["0", "1"], ids=["stored-activations", "recomputed-activations"])
+def test_sharded_parameters_with_the_real_model_follow_the_unsharded_trajectory(ckpt):
+    """Two gloo ranks, the model's hand-driven forward / backward (kernels restated in PyTorch) issuing the gather / reduce hooks
+    layer by layer: three optimizer steps of two micro-batches equal one unsharded process fed every rank's micro-batches."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), os.path.join(HERE, "_zero3_emulated_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, "CKPT": ckpt})
+    assert res.returncode == 0 and res.stdout.count("Z3_EMUL_OK") == 2, res.stdout[-3000:] + res.stderr[-3000:]
