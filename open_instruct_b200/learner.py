@@ -198,20 +198,20 @@ class Learner:
         self.sp_group = None
         if sp <= 1:
             return
-        if self.ops != "fused" or self.emulated:
+        if self.ops != "fused":
             raise NotImplementedError("sequence parallelism runs on the fused (CUDA) path")
         if self.world % sp:
             raise ValueError(f"sequence_parallel_size {sp} must divide the number of ranks {self.world}")
         if group is not None and sp != self.world:
             raise ValueError("sequence-parallel groups inside a custom process group are not supported")
-        from .parallel.ulysses import UlyssesContext
+        from .parallel.ulysses import HostUlyssesContext, UlyssesContext
 
         sp_group = group
         if sp != self.world:
             sp_group, _ = pdist.hsdp_groups(sp)  # consecutive ranks; collective: every rank builds every group
         self.sp = sp
         self.sp_group = sp_group
-        self.model.sp = UlyssesContext(spec, cfg.sp_max_tokens, self.device, sp_group)
+        self.model.sp = (HostUlyssesContext if self.emulated else UlyssesContext)(spec, cfg.sp_max_tokens, self.device, sp_group)
 
     def local_slice(self, t: torch.Tensor) -> torch.Tensor:
         """This rank's chunk of a per-token tensor of the packed micro-batch (identity without sequence parallelism)."""

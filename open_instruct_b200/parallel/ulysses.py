@@ -236,3 +236,61 @@ class UlyssesContext:
         self._a2a(dqkv_full, "dqkv_recv", 0, self.spec.qkv_dim, self.dqkv_cols, T)
         self.barrier()
         return self._view("dqkv_recv", 0, T // self.sp, self.spec.qkv_dim)
+
+
+class HostUlyssesContext:
+    """The four exchanges of ``UlyssesContext`` with plain ``torch.distributed`` all-gathers (gloo on CPU): every rank gathers
+    the ranks' pieces and keeps what it owns.  Nothing here is fast; it gives the sequence-parallel branches of the model's
+    hand-driven forward / backward (``ops="emulated"``) the same interface and results, so they run as CPU processes."""
+
+    def __init__(self, spec, max_tokens: int, device, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.sp = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.plan = ExchangePlan(self.sp, spec.num_heads, spec.num_kv_heads, spec.head_dim)
+        if max_tokens % self.sp:
+            raise ValueError("max_tokens must divide by the sequence-parallel size")
+        self.spec, self.device, self.max_tokens = spec, torch.device(device), max_tokens
+        d = spec.head_dim
+        self.hq_l, self.hk_l = spec.num_heads // self.sp, spec.num_kv_heads // self.sp
+        self.cols_l, self.q_l = self.plan.local_cols, self.hq_l * d
+        self._cols = [self._local_cols(r) for r in range(self.sp)]
+        self.local_cols_index = self._cols[self.rank]
+
+    def _local_cols(self, r: int) -> torch.Tensor:
+        """Full-width column index of every element of rank ``r``'s local [q | k | v] row."""
+        s, d = self.spec, self.spec.head_dim
+        k0, v0 = s.q_dim, s.q_dim + s.kv_dim
+        blocks = [(r * self.hq_l + b) * d for b in range(self.hq_l)]
+        blocks += [k0 + (r * self.hk_l + b) * d for b in range(self.hk_l)]
+        blocks += [v0 + (r * self.hk_l + b) * d for b in range(self.hk_l)]
+        return (torch.tensor(blocks, dtype=torch.long, device=self.device)[:, None] + torch.arange(d, device=self.device)[None, :]).reshape(-1)
+
+    def _gather(self, t: torch.Tensor) -> list[torch.Tensor]:
+        parts = [torch.empty_like(t) for _ in range(self.sp)]
+        dist.all_gather(parts, t.contiguous(), group=self.group)
+        return parts
+
+    def local_tokens(self, T: int) -> tuple[int, int]:
+        if T % self.sp or T > self.max_tokens:
+            raise ValueError(f"{T} tokens: need a multiple of {self.sp} and at most {self.max_tokens}")
+        t_l = T // self.sp
+        return self.rank * t_l, (self.rank + 1) * t_l
+
+    def qkv_project(self, layer: int, n1_local: torch.Tensor, wqkv: torch.Tensor, T: int) -> torch.Tensor:
+        full = torch.cat(self._gather((n1_local.float() @ wqkv.float().t()).to(n1_local.dtype)))      # [T, qkv_dim], token order
+        return full[:, self.local_cols_index].contiguous()
+
+    def attn_exchange(self, layer: int, attn_full: torch.Tensor) -> torch.Tensor:
+        lo, hi = self.local_tokens(attn_full.shape[0])
+        return torch.cat([p[lo:hi] for p in self._gather(attn_full)], dim=1).contiguous()          # my tokens, every rank's heads
+
+    def d_attn_project(self, d_mid_local: torch.Tensor, wo: torch.Tensor, T: int) -> torch.Tensor:
+        full = torch.cat(self._gather((d_mid_local.float() @ wo.float()).to(d_mid_local.dtype)))        # [T, q_dim]
+        return full[:, self.rank * self.q_l:(self.rank + 1) * self.q_l].contiguous()
+
+    def dqkv_exchange(self, dqkv_full: torch.Tensor) -> torch.Tensor:
+        lo, hi = self.local_tokens(dqkv_full.shape[0])
+        out = torch.empty(hi - lo, self.spec.qkv_dim, dtype=dqkv_full.dtype, device=dqkv_full.device)
+        for r, p in enumerate(self._gather(dqkv_full)):
+            out[:, self._cols[r]] = p[lo:hi]
+        return out

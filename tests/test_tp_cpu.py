@@ -345,3 +345,17 @@ def test_model_dims_account_for_hybrid_and_sliding_window_layers():
     w = ModelDims.from_spec(o3, device_name="b200")
     assert w.num_sliding_window_layers == 24 and w.sliding_window == 4096
     assert w.decode_flops([8000], [1]) < ModelDims.from_spec(get_spec("olmo2-7b"), device_name="b200").decode_flops([8000], [1])
+
+
+def test_sequence_parallel_branches_of_the_hand_driven_path():
+    """Ulysses on CPU: the model's sequence-parallel branches (projection + head exchange, attention on this rank's heads for all
+    tokens, exchange back, the same in the backward pass) with emulated kernels and all-gather exchanges, two gloo ranks."""
+    import os
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), os.path.join(here, "_sp_emulated_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and res.stdout.count("SP_EMUL_OK") == 2, res.stdout[-3000:] + res.stderr[-3000:]
