@@ -678,8 +678,22 @@ class LlamaModel:
         T = qkv.shape[0]
         out = []
         if s.qk_norm_full and (hq != s.num_heads or hk != s.num_kv_heads):
-            raise NotImplementedError("a q/k norm over all heads (OLMo-2 / OLMo-3) cannot run on a rank that holds only some heads: "
-                                      "sequence parallelism is not built for these models")
+            # sequence parallelism: this rank holds some heads of every token, the norm runs over all heads.  Each rank sums the
+            # squares of its heads, one [T]-sized all-reduce over the group completes the statistic, and the rank scales its own
+            # columns with its slice of the weight
+            import torch.distributed as dist
+
+            sp = self.sp
+            for lo, heads, name, width in ((0, hq, "q_norm", s.q_dim), (hq * s.head_dim, hk, "k_norm", s.kv_dim)):
+                n = heads * s.head_dim
+                pre = qkv[:, lo:lo + n].contiguous()
+                ss = pre.float().pow(2).sum(-1)
+                dist.all_reduce(ss, group=sp.group)
+                rstd = torch.rsqrt(ss / width + s.rms_norm_eps)
+                w = p[f"l{i}.{name}"][sp.rank * n:(sp.rank + 1) * n]
+                qkv[:, lo:lo + n].copy_(w * (pre.float() * rstd[:, None]).to(qkv.dtype))
+                out += [pre, rstd]
+            return tuple(out)
         rows = (lambda heads: T) if s.qk_norm_full else (lambda heads: T * heads)   # one norm per row, or one per head
         for lo, heads, name in ((0, hq, "q_norm"), (hq * s.head_dim, hk, "k_norm")):
             pre = qkv[:, lo:lo + heads * s.head_dim].contiguous().view(rows(heads), -1)
@@ -697,6 +711,21 @@ class LlamaModel:
         hq = s.num_heads if hq is None else hq
         hk = s.num_kv_heads if hk is None else hk
         T = dqkv.shape[0]
+        if qk is not None and s.qk_norm_full and (hq != s.num_heads or hk != s.num_kv_heads):
+            import torch.distributed as dist
+
+            sp = self.sp
+            for (lo, heads, name, width), pre, rstd in (((0, hq, "q_norm", s.q_dim), qk[0], qk[1]), ((hq * s.head_dim, hk, "k_norm", s.kv_dim), qk[2], qk[3])):
+                n = heads * s.head_dim
+                w = p[f"l{i}.{name}"][sp.rank * n:(sp.rank + 1) * n].float()
+                dy = dqkv[:, lo:lo + n].float()
+                xhat = pre.float() * rstd[:, None]
+                g[f"l{i}.{name}"][sp.rank * n:(sp.rank + 1) * n].add_((dy * xhat).sum(0))
+                dxhat = dy * w
+                dot = (dxhat * xhat).sum(-1)
+                dist.all_reduce(dot, group=sp.group)   # the mean in the norm's derivative runs over all heads too
+                dqkv[:, lo:lo + n].copy_((rstd[:, None] * (dxhat - xhat * (dot / width)[:, None])).to(dqkv.dtype))
+            qk = None
         if qk is not None:
             for (lo, heads, name), pre, rstd in (((0, hq, "q_norm"), qk[0], qk[1]), ((hq * s.head_dim, hk, "k_norm"), qk[2], qk[3])):
                 dy = dqkv[:, lo:lo + heads * s.head_dim].contiguous().view(pre.shape)

@@ -21,7 +21,10 @@ def main():
     rank, world, device = pdist.init_distributed()
     base = ModelSpec(vocab_size=300, hidden_size=64, intermediate_size=128, num_layers=3, num_heads=4, num_kv_heads=2, head_dim=16)
     for ckpt, spec in ((False, base), (True, base), (False, base.replace(attention_bias=True, model_type="qwen2")),
-                       (True, base.replace(qk_norm=True, model_type="qwen3"))):
+                       (True, base.replace(qk_norm=True, model_type="qwen3")),
+                       # OLMo-2 blocks: norm after the sub-layer, q/k norm over ALL heads (completed across the ranks by an all-reduce)
+                       (False, base.replace(post_norm=True, qk_norm=True, qk_norm_full=True, model_type="olmo2")),
+                       (True, base.replace(post_norm=True, qk_norm=True, qk_norm_full=True, model_type="olmo2"))):
         full = LlamaModel(spec, ops="emulated", seed=3, gradient_checkpointing=ckpt)
         with torch.no_grad():
             gen = torch.Generator().manual_seed(11)
