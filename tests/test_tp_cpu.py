@@ -359,3 +359,17 @@ def test_sequence_parallel_branches_of_the_hand_driven_path():
            "--master-port", str(free_port()), os.path.join(here, "_sp_emulated_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and res.stdout.count("SP_EMUL_OK") == 2, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+def test_sequence_parallel_inside_data_parallel_on_the_hand_driven_path():
+    """Four gloo ranks = two Ulysses groups of two: the learner's sequence-parallel set-up (groups, loss scaling, gradient exchange
+    over all ranks) with resident and with sharded parameters, Qwen3-style and OLMo-2-style q/k norms, against one unsharded learner."""
+    import os
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), os.path.join(here, "_sp_dp_emulated_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0 and res.stdout.count("SP_DP_EMUL_OK") == 4, res.stdout[-3000:] + res.stderr[-3000:]
