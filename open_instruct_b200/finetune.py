@@ -130,7 +130,7 @@ class FlatArguments:
     shard_parameters: bool | None = field(default=None, metadata={"help": "ZeRO-3 parameter sharding: gather each layer on use. Default: only when the resident design does not fit the GPU"})
     offload_optimizer: bool = field(default=False, metadata={"help": "keep fp32 master weights and Adam moments in pinned host memory"})
     # engine selection (not in the reference: there the back end is fixed by the launcher config)
-    ops: Literal["auto", "fused", "ref"] = "auto"
+    ops: Literal["auto", "fused", "ref", "emulated"] = "auto"
     comm_backend: Literal["auto", "fused", "nccl"] = "auto"
     fsdp_shard_degree: int | None = field(default=None, metadata={"help": "HSDP: shard optimizer state (and parameters) over groups of this many ranks, replicate across the groups"})
     zero_stage: int = field(default=3, metadata={"help": "Kept for recipe compatibility: optimizer states are always sharded, working params resident"})

@@ -213,3 +213,15 @@ def test_eight_bit_adamw_follows_the_fp32_one_and_qlora_trains_with_it(tmp_path)
     out = main(args, tc)
     lines = [json.loads(l) for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
     assert lines[-1]["train_loss"] < lines[0]["train_loss"] and out["completed_steps"] == 15
+
+
+def test_sft_on_the_emulated_kernel_path_gives_the_pytorch_path_losses(tmp_path):
+    """The whole trainer with ``ops: emulated`` (the kernel path's driver, kernels restated in PyTorch): step losses equal ``ops: ref``."""
+    from open_instruct_b200.finetune import main
+
+    losses = {}
+    for ops in ("ref", "emulated"):
+        args, tc = _args(str(tmp_path / ops), ops=ops, num_train_epochs=1)
+        main(args, tc)
+        losses[ops] = [json.loads(l)["train_loss"] for l in open(os.path.join(args.output_dir, "metrics.jsonl"))]
+    assert len(losses["ref"]) == 5 and max(abs(a - b) for a, b in zip(losses["ref"], losses["emulated"])) < 1e-5
